@@ -1,0 +1,582 @@
+// Paged attention for head_dim 128 over 16-token KV pages (bf16 KV cache).
+//
+//   * paged_decode_kernel   flash-decode: one CTA per (sequence, kv head, KV split); the G = Hq/Hkv
+//                           query heads that share a KV head are packed as the rows of one MMA tile, so
+//                           each KV byte is read from HBM exactly once per step. Splits are merged by the
+//                           last CTA to finish (ticket counter), no second launch.
+//   * paged_prefill_kernel  causal flash attention for (chunked) prefill: 64 query rows per CTA, KV
+//                           streamed page by page from the same paged cache (prefix pages included).
+//
+// KV pages are fetched with tiled TMA copies (128-byte swizzle) into a per-warp / per-CTA ring and read
+// back with ldmatrix; the math is mma.sync m16n8k16 bf16 with fp32 online softmax. Decode attention is
+// bandwidth bound (4 FLOP per KV byte at G = 4), so the roofline here is HBM, not the tensor pipe.
+//
+// Semantics follow the reference's CPU attention (src/compat/scalar_ops.rs:196-278, 316-378):
+// scale 1/sqrt(d), kv head = q head / (Hq/Hkv), causal mask, max-subtracted softmax; optional sliding
+// window and learnable sinks (src/arch/auto_graph_fragments/build_graph.inc.rs:1775-1781).
+//
+// Cache layout per layer: [page][K|V][kv_head][16 tokens][128] bf16.
+#include "common.cuh"
+
+namespace gllm {
+
+constexpr int kHD = 128;
+constexpr int kPage = 16;
+constexpr int kPageBytes = kPage * kHD * 2;  // 4 KB per (page, K|V, head)
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Online-softmax state of one warp: rows r0 = lane/4 and r1 = r0 + 8 of a 16-row tile.
+struct SoftmaxState {
+  float m0, m1, l0, l1;
+};
+
+// One 16-token page: S = Q·Kᵀ (16x16), mask, online softmax, O += P·V.
+// k_smem / v_smem: shared addresses of the page's K and V tiles, each two 2 KB boxes
+// ([d half][token][64 bf16], 128-byte swizzle). Row r may attend tokens in [lo_r, hi_r).
+__device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t k_smem, uint32_t v_smem,
+                                            int tok_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
+                                            float (&o)[16][4], SoftmaxState& st) {
+  const int lane = threadIdx.x & 31;
+  float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  {
+    const int tok = (lane & 7) + ((lane >> 4) << 3);
+    const int csel = (lane >> 3) & 1;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int chunk = (ks & 3) * 2 + csel;
+      const uint32_t addr = k_smem + (ks >> 2) * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(addr, b0, b1, b2, b3);
+      mma_bf16_16816(s[0], qf[ks], b0, b1);
+      mma_bf16_16816(s[1], qf[ks], b2, b3);
+    }
+  }
+  // mask + scale (log2 domain)
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int t = tok_base + nt * 8 + (lane & 3) * 2 + e;
+      float v0 = s[nt][e] * scale_log2, v1 = s[nt][2 + e] * scale_log2;
+      if (t < lo0 || t >= hi0) v0 = -INFINITY;
+      if (t < lo1 || t >= hi1) v1 = -INFINITY;
+      s[nt][e] = v0;
+      s[nt][2 + e] = v1;
+      mx0 = fmaxf(mx0, v0);
+      mx1 = fmaxf(mx1, v1);
+    }
+  }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
+  const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0, ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
+  const float corr0 = exp2f(st.m0 - ms0), corr1 = exp2f(st.m1 - ms1);  // exp2(-inf) = 0 on first use
+  st.m0 = mn0;
+  st.m1 = mn1;
+  float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      s[nt][e] = exp2f(s[nt][e] - ms0);
+      s[nt][2 + e] = exp2f(s[nt][2 + e] - ms1);
+      rs0 += s[nt][e];
+      rs1 += s[nt][2 + e];
+    }
+  }
+  rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
+  rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
+  rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
+  rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
+  st.l0 = st.l0 * corr0 + rs0;
+  st.l1 = st.l1 * corr1 + rs1;
+  uint32_t pf[4];
+  pf[0] = pack_bf16x2(s[0][0], s[0][1]);
+  pf[1] = pack_bf16x2(s[0][2], s[0][3]);
+  pf[2] = pack_bf16x2(s[1][0], s[1][1]);
+  pf[3] = pack_bf16x2(s[1][2], s[1][3]);
+  {
+    const int tok = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int csel = lane >> 4;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int chunk = (j * 2 + csel) & 7;
+      const int box = (j * 2) >> 3;
+      const uint32_t addr = v_smem + box * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(addr, b0, b1, b2, b3);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[2 * j][e] *= (e < 2) ? corr0 : corr1;
+        o[2 * j + 1][e] *= (e < 2) ? corr0 : corr1;
+      }
+      mma_bf16_16816(o[2 * j], pf, b0, b1);
+      mma_bf16_16816(o[2 * j + 1], pf, b2, b3);
+    }
+  }
+}
+
+__device__ __forceinline__ void load_page_kv(const CUtensorMap* tmap, uint8_t* dst, uint64_t* bar, int page,
+                                             int n_kv_heads, int kvh) {
+  const int krow = ((page * 2 + 0) * n_kv_heads + kvh) * kPage;
+  const int vrow = ((page * 2 + 1) * n_kv_heads + kvh) * kPage;
+  mbar_expect_tx(bar, 2 * kPageBytes);
+  tma_load_2d(dst, tmap, bar, 0, krow);
+  tma_load_2d(dst + 2048, tmap, bar, 64, krow);
+  tma_load_2d(dst + 4096, tmap, bar, 0, vrow);
+  tma_load_2d(dst + 6144, tmap, bar, 64, vrow);
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------------------------
+struct DecodeParams {
+  const __nv_bfloat16* q;  // [B, Hq, 128]
+  __nv_bfloat16* out;      // [B, Hq, 128]
+  const int* block_tables;  // [B, max_blocks]
+  const int* ctx_lens;      // [B] tokens in the cache including the one just written; <= 0 = empty slot
+  int max_blocks;
+  int n_q_heads, n_kv_heads, group;
+  float scale_log2;
+  int pages_per_split, max_splits;
+  float* part_o;    // [B, Hq, max_splits, 128]
+  float* part_lse;  // [B, Hq, max_splits]
+  int* counters;    // [B, Hkv], zero before the first launch; the kernel leaves them zero
+  int num_pages;
+  int window;          // 0 = full attention
+  const float* sinks;  // [Hq] learnable sink logits or null
+  int* err;
+};
+
+constexpr int kDecWarps = 4;
+constexpr int kDecStages = 3;
+constexpr int kDecSmem = kDecWarps * kDecStages * 2 * kPageBytes + 1024 + 1024;
+
+__global__ void __launch_bounds__(kDecWarps * 32)
+paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecWarps * kDecStages * 2 * kPageBytes);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kDecWarps * kDecStages);
+  int* is_last = const_cast<int*>(abort_flag) + 1;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ctx = p.ctx_lens[b];
+  if (ctx <= 0) return;
+  const int n_pages = (ctx + kPage - 1) / kPage;
+  const int first_tok = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;
+  const int first_page = first_tok / kPage;
+  // never more splits than the scratch was sized for: widen the split when the context is long
+  const int span = n_pages - first_page;
+  const int pps = max(p.pages_per_split, (span + p.max_splits - 1) / p.max_splits);
+  const int n_splits = (span + pps - 1) / pps;
+  if (split >= n_splits) return;
+  const int p0 = first_page + split * pps;
+  const int p1 = min(p0 + pps, n_pages);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < kDecWarps * kDecStages; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_kv);
+  }
+  __syncthreads();
+
+  // Q fragments: rows = the `group` q heads of this kv head (rows >= group are zero)
+  uint32_t qf[8][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const __nv_bfloat16* qb = p.q + (static_cast<long long>(b) * p.n_q_heads + kvh * p.group) * kHD;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c = ks * 16 + (lane & 3) * 2;
+      qf[ks][0] = r0 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r0 * kHD + c) : 0u;
+      qf[ks][1] = r1 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r1 * kHD + c) : 0u;
+      qf[ks][2] = r0 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r0 * kHD + c + 8) : 0u;
+      qf[ks][3] = r1 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r1 * kHD + c + 8) : 0u;
+    }
+  }
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  SoftmaxState st{-INFINITY, -INFINITY, 0.f, 0.f};
+
+  uint8_t* my_ring = smem + warp * kDecStages * 2 * kPageBytes;
+  uint64_t* my_bars = bars + warp * kDecStages;
+  const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+  const int n_my = (p1 - p0 - warp + kDecWarps - 1) / kDecWarps;  // pages p0+warp, p0+warp+4, ...
+
+  auto issue = [&](int i) {
+    const int pg_idx = p0 + warp + i * kDecWarps;
+    int page = bt[pg_idx];
+    if (page < 0 || page >= p.num_pages) {
+      if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
+      page = 0;
+    }
+    const int stg = i % kDecStages;
+    load_page_kv(&tmap_kv, my_ring + stg * 2 * kPageBytes, &my_bars[stg], page, p.n_kv_heads, kvh);
+  };
+  if (lane == 0) {
+    for (int i = 0; i < n_my && i < kDecStages; ++i) issue(i);
+  }
+  __syncwarp();
+  for (int i = 0; i < n_my; ++i) {
+    const int stg = i % kDecStages;
+    // warp-uniform decision: the page body uses warp-synchronous instructions
+    const bool got = mbar_wait(&my_bars[stg], (i / kDecStages) & 1, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL);
+    if (!__all_sync(0xffffffffu, got)) break;
+    const uint32_t kaddr = smem_u32(my_ring + stg * 2 * kPageBytes);
+    const int tok_base = (p0 + warp + i * kDecWarps) * kPage;
+    attend_page(qf, kaddr, kaddr + kPageBytes, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
+    __syncwarp();
+    if (lane == 0 && i + kDecStages < n_my) {
+      fence_proxy_async_smem();
+      issue(i + kDecStages);
+    }
+  }
+  // every issued copy has been waited for above (or the wait was abandoned after the limit)
+  __syncthreads();
+
+  // cross-warp merge through shared memory (the rings are idle now)
+  float* mo = reinterpret_cast<float*>(smem);            // [warp][16][128]
+  float* mml = mo + kDecWarps * 16 * kHD;                // [warp][16][2]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int dt = 0; dt < 16; ++dt) {
+      const int c = dt * 8 + (lane & 3) * 2;
+      float* w0 = mo + (warp * 16 + r0) * kHD + c;
+      float* w1 = mo + (warp * 16 + r1) * kHD + c;
+      w0[0] = o[dt][0];
+      w0[1] = o[dt][1];
+      w1[0] = o[dt][2];
+      w1[1] = o[dt][3];
+    }
+    if ((lane & 3) == 0) {
+      mml[(warp * 16 + r0) * 2 + 0] = st.m0;
+      mml[(warp * 16 + r0) * 2 + 1] = st.l0;
+      mml[(warp * 16 + r1) * 2 + 0] = st.m1;
+      mml[(warp * 16 + r1) * 2 + 1] = st.l1;
+    }
+  }
+  __syncthreads();
+  const int d = threadIdx.x;  // 128 threads <-> 128 features
+  const bool single = (n_splits == 1);
+  for (int r = 0; r < p.group; ++r) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = mml[(w * 16 + r) * 2];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L += mml[(w * 16 + r) * 2 + 1] * f;
+      acc += mo[(w * 16 + r) * kHD + d] * f;
+    }
+    const int qh = kvh * p.group + r;
+    if (single) {
+      if (p.sinks) L += exp2f(p.sinks[qh] * 1.4426950408889634f - M);
+      p.out[(static_cast<long long>(b) * p.n_q_heads + qh) * kHD + d] = __float2bfloat16_rn(acc / L);
+    } else {
+      const long long pi = (static_cast<long long>(b) * p.n_q_heads + qh) * p.max_splits + split;
+      p.part_o[pi * kHD + d] = acc / L;
+      if (d == 0) p.part_lse[pi] = M + log2f(L);
+    }
+  }
+  if (single) return;
+
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&p.counters[b * p.n_kv_heads + kvh], 1);
+    *is_last = (ticket == n_splits - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!*is_last) return;
+  __threadfence();
+  for (int r = 0; r < p.group; ++r) {
+    const int qh = kvh * p.group + r;
+    const long long pb = (static_cast<long long>(b) * p.n_q_heads + qh) * p.max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(&p.part_lse[pb + s]));
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float f = exp2f(__ldcg(&p.part_lse[pb + s]) - M);
+      L += f;
+      acc += __ldcg(&p.part_o[(pb + s) * kHD + d]) * f;
+    }
+    if (p.sinks) L += exp2f(p.sinks[qh] * 1.4426950408889634f - M);
+    p.out[(static_cast<long long>(b) * p.n_q_heads + qh) * kHD + d] = __float2bfloat16_rn(acc / L);
+  }
+  if (threadIdx.x == 0) p.counters[b * p.n_kv_heads + kvh] = 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill (varlen, causal, chunk-aware)
+// ---------------------------------------------------------------------------------------------
+struct PrefillParams {
+  const __nv_bfloat16* q;  // [T, Hq, 128] flat tokens of every sequence in the batch
+  __nv_bfloat16* out;      // [T, Hq, 128]
+  const int* q_start;      // [S] first flat token of sequence i
+  const int* q_len;        // [S] query tokens of sequence i in this step
+  const int* ctx_lens;     // [S] KV tokens after this step (queries are the last q_len of them)
+  const int* block_tables;  // [S, max_blocks]
+  int max_blocks;
+  int n_q_heads, n_kv_heads, group;
+  float scale_log2;
+  int num_pages;
+  int window;
+  int causal;  // 0 = bidirectional over [0, ctx)
+  const float* sinks;
+  int* err;
+};
+
+constexpr int kPfWarps = 4;
+constexpr int kPfRows = kPfWarps * 16;  // 64 query rows per CTA
+constexpr int kPfBlockPages = 4;        // 64 KV tokens per stage
+constexpr int kPfStages = 2;
+constexpr int kPfStageBytes = kPfBlockPages * 2 * kPageBytes;  // 32 KB
+constexpr int kPfSmem = kPfStages * kPfStageBytes + 1024 + 1024;
+
+__global__ void __launch_bounds__(kPfWarps * 32)
+paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPfStages * kPfStageBytes);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kPfStages);
+
+  const int qblk = blockIdx.x, qh = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qlen = p.q_len[seq];
+  if (qblk * kPfRows >= qlen) return;
+  const int ctx = p.ctx_lens[seq];
+  const int qstart = p.q_start[seq];
+  const int kvh = qh / p.group;
+  const int pos0 = ctx - qlen;  // position of query row 0 of this sequence
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < kPfStages; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmap_kv);
+  }
+  __syncthreads();
+
+  const int row0 = qblk * kPfRows + warp * 16 + (lane >> 2), row1 = row0 + 8;
+  uint32_t qf[8][4];
+  {
+    const __nv_bfloat16* q0 = p.q + (static_cast<long long>(qstart + row0) * p.n_q_heads + qh) * kHD;
+    const __nv_bfloat16* q1 = p.q + (static_cast<long long>(qstart + row1) * p.n_q_heads + qh) * kHD;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c = ks * 16 + (lane & 3) * 2;
+      qf[ks][0] = row0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qf[ks][1] = row1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qf[ks][2] = row0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qf[ks][3] = row1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+    }
+  }
+  // allowed token ranges per row
+  int hi0, hi1, lo0 = 0, lo1 = 0;
+  if (p.causal) {
+    hi0 = pos0 + row0 + 1;
+    hi1 = pos0 + row1 + 1;
+  } else {
+    hi0 = hi1 = ctx;
+  }
+  if (p.window > 0) {
+    lo0 = max(0, hi0 - p.window);
+    lo1 = max(0, hi1 - p.window);
+  }
+  if (row0 >= qlen) hi0 = lo0 = 0;
+  if (row1 >= qlen) hi1 = lo1 = 0;
+  // KV range needed by this CTA
+  const int last_row = min(qblk * kPfRows + kPfRows, qlen) - 1;
+  const int kv_hi = p.causal ? (pos0 + last_row + 1) : ctx;
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, (p.causal ? pos0 + qblk * kPfRows + 1 : ctx) - p.window);
+  const int page_lo = kv_lo / kPage;
+  const int page_hi = (kv_hi + kPage - 1) / kPage;
+  const int n_blocks = (page_hi - page_lo + kPfBlockPages - 1) / kPfBlockPages;
+  const int* bt = p.block_tables + static_cast<long long>(seq) * p.max_blocks;
+
+  auto issue = [&](int blk) {
+    const int stg = blk % kPfStages;
+    uint8_t* dst = smem + stg * kPfStageBytes;
+    const int pg0 = page_lo + blk * kPfBlockPages;
+    const int npg = min(kPfBlockPages, page_hi - pg0);
+    mbar_expect_tx(&bars[stg], npg * 2 * kPageBytes);
+    for (int j = 0; j < npg; ++j) {
+      int page = bt[pg0 + j];
+      if (page < 0 || page >= p.num_pages) {
+        if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
+        page = 0;
+      }
+      const int krow = ((page * 2 + 0) * p.n_kv_heads + kvh) * kPage;
+      const int vrow = ((page * 2 + 1) * p.n_kv_heads + kvh) * kPage;
+      uint8_t* d = dst + j * 2 * kPageBytes;
+      tma_load_2d(d, &tmap_kv, &bars[stg], 0, krow);
+      tma_load_2d(d + 2048, &tmap_kv, &bars[stg], 64, krow);
+      tma_load_2d(d + 4096, &tmap_kv, &bars[stg], 0, vrow);
+      tma_load_2d(d + 6144, &tmap_kv, &bars[stg], 64, vrow);
+    }
+  };
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  SoftmaxState st{-INFINITY, -INFINITY, 0.f, 0.f};
+
+  if (threadIdx.x == 0) {
+    for (int blk = 0; blk < n_blocks && blk < kPfStages; ++blk) issue(blk);
+  }
+  // rows of this warp need tokens below warp_hi only
+  const int warp_last_row = min(qblk * kPfRows + warp * 16 + 15, qlen - 1);
+  const int warp_hi = p.causal ? (pos0 + warp_last_row + 1) : ctx;
+  for (int blk = 0; blk < n_blocks; ++blk) {
+    const int stg = blk % kPfStages;
+    // the decision to stop must be CTA-uniform because the loop body contains a block barrier
+    const int got = mbar_wait(&bars[stg], (blk / kPfStages) & 1, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL) ? 1 : 0;
+    if (!__syncthreads_and(got)) break;
+    const int pg0 = page_lo + blk * kPfBlockPages;
+    const int npg = min(kPfBlockPages, page_hi - pg0);
+    const uint32_t base = smem_u32(smem + stg * kPfStageBytes);
+    for (int j = 0; j < npg; ++j) {
+      const int tok_base = (pg0 + j) * kPage;
+      if (tok_base >= warp_hi) break;  // fully masked for every row of this warp
+      attend_page(qf, base + j * 2 * kPageBytes, base + j * 2 * kPageBytes + kPageBytes, tok_base, lo0, hi0, lo1,
+                  hi1, p.scale_log2, o, st);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && blk + kPfStages < n_blocks) {
+      fence_proxy_async_smem();
+      issue(blk + kPfStages);
+    }
+  }
+
+  float L0 = st.l0, L1 = st.l1;
+  if (p.sinks) {
+    const float sk = p.sinks[qh] * 1.4426950408889634f;
+    L0 += exp2f(sk - (st.m0 == -INFINITY ? 0.f : st.m0));
+    L1 += exp2f(sk - (st.m1 == -INFINITY ? 0.f : st.m1));
+  }
+  const float inv0 = L0 > 0.f ? 1.f / L0 : 0.f, inv1 = L1 > 0.f ? 1.f / L1 : 0.f;
+  __nv_bfloat16* o0 = p.out + (static_cast<long long>(qstart + row0) * p.n_q_heads + qh) * kHD;
+  __nv_bfloat16* o1 = p.out + (static_cast<long long>(qstart + row1) * p.n_q_heads + qh) * kHD;
+#pragma unroll
+  for (int dt = 0; dt < 16; ++dt) {
+    const int c = dt * 8 + (lane & 3) * 2;
+    if (row0 < qlen) *reinterpret_cast<uint32_t*>(o0 + c) = pack_bf16x2(o[dt][0] * inv0, o[dt][1] * inv0);
+    if (row1 < qlen) *reinterpret_cast<uint32_t*>(o1 + c) = pack_bf16x2(o[dt][2] * inv1, o[dt][3] * inv1);
+  }
+}
+
+static int kv_tmap(CUtensorMap* t, const void* kv_cache, int num_pages, int n_kv_heads) {
+  const uint64_t rows = uint64_t(num_pages) * 2 * n_kv_heads * kPage;
+  return make_tmap_2d(t, kv_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHD, kHD, kPage, 64);
+}
+
+}  // namespace gllm
+
+using namespace gllm;
+extern "C" int* gllm_error_word();
+
+// Scratch sizes for the split-KV decode path (floats / ints).
+GLLM_API long long gllm_decode_scratch_floats(int batch, int n_q_heads, int max_splits) {
+  return static_cast<long long>(batch) * n_q_heads * max_splits * (kHD + 1);
+}
+
+GLLM_API int gllm_paged_decode(const void* q, void* out, const void* kv_cache, int num_pages,
+                               const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
+                               int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
+                               float* scratch, int* counters, int window, const float* sinks, void* stream) {
+  if (n_q_heads % n_kv_heads != 0 || n_q_heads / n_kv_heads > 16) {
+    set_last_error("paged_decode: group size %d/%d unsupported (must divide, <= 16)", n_q_heads, n_kv_heads);
+    return -1;
+  }
+  if (max_splits > 1 && (!scratch || !counters)) {
+    set_last_error("paged_decode: split-KV needs scratch and counters");
+    return -1;
+  }
+  CUtensorMap t;
+  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads)) return -1;
+  DecodeParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.max_blocks = max_blocks;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.pages_per_split = pages_per_split > 0 ? pages_per_split : (1 << 30);
+  p.max_splits = max_splits > 0 ? max_splits : 1;
+  p.part_o = scratch;
+  p.part_lse = scratch ? scratch + static_cast<long long>(batch) * n_q_heads * p.max_splits * kHD : nullptr;
+  p.counters = counters; p.num_pages = num_pages; p.window = window; p.sinks = sinks;
+  p.err = gllm_error_word();
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+    if (e != cudaSuccess) { set_last_error("paged_decode: %s", cudaGetErrorString(e)); return -1; }
+    attr_set = true;
+  }
+  dim3 grid(p.max_splits, n_kv_heads, batch);
+  paged_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, (cudaStream_t)stream>>>(t, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("paged_decode launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+GLLM_API int gllm_paged_prefill(const void* q, void* out, const void* kv_cache, int num_pages,
+                                const int* block_tables, int max_blocks, const int* q_start, const int* q_len,
+                                const int* ctx_lens, int num_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
+                                float scale, int causal, int window, const float* sinks, void* stream) {
+  if (n_q_heads % n_kv_heads != 0) {
+    set_last_error("paged_prefill: heads %d not divisible by kv heads %d", n_q_heads, n_kv_heads);
+    return -1;
+  }
+  CUtensorMap t;
+  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads)) return -1;
+  PrefillParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.q_start = q_start; p.q_len = q_len; p.ctx_lens = ctx_lens;
+  p.block_tables = block_tables; p.max_blocks = max_blocks;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.num_pages = num_pages; p.window = window; p.causal = causal; p.sinks = sinks;
+  p.err = gllm_error_word();
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
+    if (e != cudaSuccess) { set_last_error("paged_prefill: %s", cudaGetErrorString(e)); return -1; }
+    attr_set = true;
+  }
+  dim3 grid((max_q_len + kPfRows - 1) / kPfRows, n_q_heads, num_seqs);
+  paged_prefill_kernel<<<grid, kPfWarps * 32, kPfSmem, (cudaStream_t)stream>>>(t, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}

@@ -1,0 +1,129 @@
+"""ctypes binding to ``libgllm_kernels.so`` (the hand-written sm_100a kernels).
+
+The library is mandatory whenever a CUDA tensor reaches an op: a missing or stale library is an
+error, never a silent fallback to PyTorch. CPU tensors take the PyTorch reference path, which is
+also the numerical oracle used by the tests.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from pathlib import Path
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "_lib"
+_lock = threading.Lock()
+_lib = None
+
+P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
+
+_SIGNATURES = {
+    "gllm_last_error": (ctypes.c_char_p, []),
+    "gllm_error_word": (P, []),
+    "gllm_check_error": (I, []),
+    "gllm_sm_count": (I, []),
+    "gllm_kernels_abi_version": (I, []),
+    "gllm_gemm_bf16": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, I]),
+    "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I]),
+    "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I]),
+    "gllm_gemm_bf16_grouped": (I, [P, L, P, L, P, L, I, I, I, P, I, I, P, I]),
+    "gllm_gemm_bf16_qkv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, P, I]),
+    "gllm_gemm_fp8": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, P, I]),
+    "gllm_decode_scratch_floats": (L, [I, I, I]),
+    "gllm_paged_decode": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, P]),
+    "gllm_paged_prefill": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, P]),
+    "gllm_embed_gather": (I, [P, P, I, I, F, P, P, I, P]),
+    "gllm_rmsnorm": (I, [P, P, P, I, I, F, I, P, P, P, P]),
+    "gllm_layernorm": (I, [P, P, P, P, I, I, F, P, P]),
+    "gllm_glu": (I, [P, L, I, I, I, P, P]),
+    "gllm_rope_kv_write": (I, [P, L, I, I, I, I, I, P, P, P, P, I, P, P, F, P, P, I, P]),
+    "gllm_paged_attention_generic": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, P]),
+    "gllm_pool": (I, [P, P, P, I, I, I, P, P]),
+    "gllm_sample": (I, [P, L, I, I, I, P, U, P, P, P, P]),
+    "gllm_argmax": (I, [P, L, I, I, I, P, P, P]),
+}
+
+_OPTIONAL = set()
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_DIR / "libgllm_kernels.so"
+
+
+def available() -> bool:
+    return lib_path().exists()
+
+
+def lib():
+    """Load (once) and return the kernel library; raises NativeLibraryError if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = lib_path()
+        if not path.exists():
+            raise NativeLibraryError(
+                f"{path} is missing: run `python -m gllm_b200.build` (needs nvcc) before using CUDA tensors")
+        handle = ctypes.CDLL(str(path))
+        for name, (res, args) in _SIGNATURES.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError:
+                if name in _OPTIONAL:
+                    continue
+                raise NativeLibraryError(f"{path} is stale: symbol {name} not found; rebuild with --force")
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def register(name, restype, argtypes, optional=False):
+    """Let other op modules declare entry points that live in the same library."""
+    _SIGNATURES[name] = (restype, argtypes)
+    if optional:
+        _OPTIONAL.add(name)
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.restype, fn.argtypes = restype, argtypes
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = lib().gllm_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed: {msg}")
+
+
+def device_error() -> int:
+    """Read-and-clear the device error word (synchronises). 0 means no kernel reported a problem."""
+    return int(lib().gllm_check_error())
+
+
+ERROR_NAMES = {
+    0: "ok", 1: "timeout waiting for a TMA stage", 2: "timeout waiting for a free smem stage",
+    3: "timeout waiting for an accumulator", 4: "timeout waiting for a free accumulator slot",
+    5: "timeout waiting for a peer rank", 6: "page id outside the pool", 7: "expert id out of range",
+    8: "timeout waiting for another CTA", 9: "bad argument",
+}
+
+
+def raise_on_device_error(where: str = ""):
+    code = device_error()
+    if code != 0:
+        raise RuntimeError(f"device kernel reported status {code} ({ERROR_NAMES.get(code, '?')}) {where}")
+
+
+def ptr(t):
+    """Device/host pointer of a tensor or None."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr():
+    import torch
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,96 @@
+"""Paged attention kernels vs the fp32 reference (run with -m gpu on a B200)."""
+import pytest
+import torch
+
+from gllm_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _setup(ctx_lens, n_kv, D, extra_pages=8, seed=0):
+    torch.manual_seed(seed)
+    B = len(ctx_lens)
+    need = [(c + 15) // 16 for c in ctx_lens]
+    total = sum(need) + extra_pages
+    kv = (torch.randn(total, 2, n_kv, 16, D, device=DEV)).to(torch.bfloat16)
+    perm = torch.randperm(total, device=DEV).to(torch.int32)
+    max_blocks = max(need) + 2
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32, device=DEV)
+    o = 0
+    for i, n in enumerate(need):
+        bt[i, :n] = perm[o:o + n]
+        o += n
+    return kv, bt
+
+
+def _close(got, ref, tol=2e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    assert err < tol * (ref.abs().max().item() + 1e-6), f"max err {err}"
+
+
+@pytest.mark.parametrize("n_q,n_kv,pps", [(8, 2, 32), (4, 1, 4), (32, 8, 8), (16, 1, 1000)])
+def test_paged_decode(n_q, n_kv, pps):
+    D = 128
+    ctx = [1, 16, 17, 100, 515, 2304, 33, 64]
+    kv, bt = _setup(ctx, n_kv, D)
+    B = len(ctx)
+    q = torch.randn(B, n_q * D, device=DEV).to(torch.bfloat16)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    out = ops.paged_decode(q, kv, bt, cl, n_q=n_q, n_kv=n_kv, pages_per_split=pps)
+    ar = torch.arange(B, dtype=torch.int32, device=DEV)
+    ref = ops.attention_ref(q, kv, bt, ar, torch.ones_like(cl), cl, n_q, n_kv, D ** -0.5)
+    _close(out, ref)
+    # second launch reuses the ticket counters: must give the same answer
+    out2 = ops.paged_decode(q, kv, bt, cl, n_q=n_q, n_kv=n_kv, pages_per_split=pps)
+    _close(out2, ref)
+
+
+def test_paged_decode_empty_slots_window_sinks():
+    D, n_q, n_kv = 128, 8, 2
+    ctx = [0, 300, 0, 40]
+    kv, bt = _setup([max(c, 1) for c in ctx], n_kv, D, seed=1)
+    q = torch.randn(4, n_q * D, device=DEV).to(torch.bfloat16)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    sinks = torch.randn(n_q, device=DEV)
+    out = torch.zeros_like(q)
+    ops.paged_decode(q, kv, bt, cl, n_q=n_q, n_kv=n_kv, out=out, pages_per_split=4, window=100, sinks=sinks)
+    ar = torch.arange(4, dtype=torch.int32, device=DEV)
+    ref = ops.attention_ref(q, kv, bt, ar, (cl > 0).int(), cl, n_q, n_kv, D ** -0.5, True, 100, sinks)
+    _close(out, ref)
+
+
+@pytest.mark.parametrize("n_q,n_kv", [(8, 2), (4, 4)])
+def test_paged_prefill(n_q, n_kv):
+    D = 128
+    q_len = [5, 64, 130, 1, 257]
+    ctx = [5, 200, 130, 77, 1000]   # some sequences have a cached prefix (chunked prefill / prefix reuse)
+    kv, bt = _setup(ctx, n_kv, D, seed=2)
+    T = sum(q_len)
+    q = torch.randn(T, n_q * D, device=DEV).to(torch.bfloat16)
+    qs = torch.tensor([sum(q_len[:i]) for i in range(len(q_len))], dtype=torch.int32, device=DEV)
+    ql = torch.tensor(q_len, dtype=torch.int32, device=DEV)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    out = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=max(q_len), n_q=n_q, n_kv=n_kv)
+    ref = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5)
+    _close(out, ref)
+    out_b = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=max(q_len), n_q=n_q, n_kv=n_kv, causal=False)
+    ref_b = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5, causal=False)
+    _close(out_b, ref_b)
+    out_w = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=max(q_len), n_q=n_q, n_kv=n_kv, window=48)
+    ref_w = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5, window=48)
+    _close(out_w, ref_w)
+
+
+def test_generic_attention_head_dim_64():
+    D, n_q, n_kv = 64, 9, 3
+    q_len, ctx = [7, 33], [7, 50]
+    kv, bt = _setup(ctx, n_kv, D, seed=3)
+    q = torch.randn(sum(q_len), n_q * D, device=DEV).to(torch.bfloat16)
+    qs = torch.tensor([0, 7], dtype=torch.int32, device=DEV)
+    ql = torch.tensor(q_len, dtype=torch.int32, device=DEV)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    out = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=33, n_q=n_q, n_kv=n_kv)
+    ref = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5)
+    _close(out, ref)

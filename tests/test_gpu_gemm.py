@@ -1,0 +1,134 @@
+"""tcgen05 GEMM family vs an fp32 PyTorch reference of the same op (run with -m gpu on a B200)."""
+import pytest
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.ops import linear as L
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol=2e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"max abs err {err} vs ref max {denom}"
+    cos = torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item()
+    assert cos > 0.9995, f"cosine {cos}"
+
+
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 128, 64, 128), (128, 256, 64, 256), (256, 4096, 4096, 256), (256, 4096, 4096, 128),
+    (100, 384, 192, 128), (1, 128, 64, 128), (300, 1024, 520, 256), (777, 2176, 1000, 128),
+    (2048, 6144, 4096, 128), (129, 32, 4096, 128),
+])
+def test_gemm_plain(M, N, K, bn):
+    torch.manual_seed(0)
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    out = ops.gemm(a, w, bn=bn)
+    _close(out, a.float() @ w.float().t())
+
+
+def test_gemm_fp32_out_bias_rowscale():
+    torch.manual_seed(1)
+    M, N, K = 200, 512, 1024
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    bias = torch.randn(N, device=DEV)
+    ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+    out = ops.gemm(a, w, out_dtype=torch.float32, bias=bias, row_ss=ss, norm_dim=K, eps=1e-6, bn=128)
+    ref = (a.float() @ w.float().t()) * torch.rsqrt(ss / K + 1e-6) + bias
+    _close(out, ref, 5e-3)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(256, 4096, 4096, 256), (100, 1024, 512, 128), (300, 4096, 1536, 128)])
+def test_gemm_residual(M, N, K, bn):
+    torch.manual_seed(2)
+    a, w, r = _rand(M, K), _rand(N, K, scale=0.05), _rand(M, N)
+    out, ss = ops.gemm_residual(a, w, r, bn=bn)
+    ref = (a.float() @ w.float().t() + r.float())
+    _close(out, ref)
+    ss_ref = out.float().pow(2).sum(-1)
+    torch.testing.assert_close(ss.sum(-1), ss_ref, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("M,I,K,bn,act", [(256, 1024, 512, 256, 0), (100, 768, 2048, 128, 0), (64, 512, 256, 256, 1)])
+def test_gemm_glu(M, I, K, bn, act):
+    torch.manual_seed(3)
+    a, g, u = _rand(M, K), _rand(I, K, scale=0.05), _rand(I, K, scale=0.05)
+    ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+    wp = ops.interleave_gate_up(g, u, bn)
+    out = ops.gemm_glu(a, wp, act=act, row_ss=ss, norm_dim=K, eps=1e-5, bn=bn)
+    rs = torch.rsqrt(ss / K + 1e-5)
+    gv, uv = (a.float() @ g.float().t()) * rs, (a.float() @ u.float().t()) * rs
+    actf = torch.nn.functional.silu if act == 0 else (lambda x: torch.nn.functional.gelu(x, approximate="tanh"))
+    _close(out, actf(gv) * uv)
+
+
+def test_gemm_grouped_and_glu_grouped():
+    torch.manual_seed(4)
+    E, N, K = 4, 512, 256
+    mblk = torch.tensor([2, 0, 3, 3, 1], dtype=torch.int32, device=DEV)
+    M = 128 * mblk.numel()
+    a, w = _rand(M, K), _rand(E * N, K, scale=0.05)
+    out = ops.gemm_grouped(a, w, mblk, E, bn=128)
+    ref = torch.cat([a[i * 128:(i + 1) * 128].float() @ w[int(e) * N:(int(e) + 1) * N].float().t()
+                     for i, e in enumerate(mblk.tolist())])
+    _close(out, ref)
+    out2 = ops.gemm_glu(a, w, act=0, bn=128, mblk_group=mblk, num_groups=E)
+    ref2 = L.gemm_glu(a.cpu(), w.cpu(), act=0, bn=128, mblk_group=mblk.cpu(), num_groups=E)
+    _close(out2, ref2.to(DEV))
+
+
+@pytest.mark.parametrize("qk_norm", [True, False])
+def test_gemm_qkv_fused(qk_norm):
+    torch.manual_seed(5)
+    M, K, n_q, n_kv, D = 150, 1024, 8, 2, 128
+    pages, max_pos = 32, 512
+    a = _rand(M, K)
+    w = _rand((n_q + 2 * n_kv) * D, K, scale=0.05)
+    ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+    qn = (torch.rand(D, device=DEV) + 0.5) if qk_norm else None
+    kn = (torch.rand(D, device=DEV) + 0.5) if qk_norm else None
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=DEV).double() / D))
+    ang = torch.arange(max_pos, device=DEV).double()[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    positions = torch.randint(0, max_pos, (M,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * 16, device=DEV)[:M].to(torch.int32)
+    slots[3] = -1
+    kv = torch.zeros(pages, 2, n_kv, 16, D, device=DEV, dtype=torch.bfloat16)
+    q_out = torch.zeros(M, n_q * D, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_qkv(a, w, n_q=n_q, n_kv=n_kv, q_out=q_out, kv_cache=kv, slot_mapping=slots, positions=positions,
+                 cos_t=cos_t, sin_t=sin_t, q_norm_w=qn, k_norm_w=kn, qk_eps=1e-6, row_ss=ss, norm_dim=K, eps=1e-6)
+    acc = (a.float() @ w.float().t()) * torch.rsqrt(ss / K + 1e-6)
+    q, k, v = L.qkv_post_ref(acc, n_q, n_kv, D, positions, cos_t, sin_t, qn, kn, 1e-6)
+    _close(q_out, q.reshape(M, -1))
+    kv_ref = torch.zeros_like(kv)
+    L.kv_write_ref(kv_ref, k, v, slots)
+    _close(kv, kv_ref)
+
+
+def test_gemm_fp8():
+    torch.manual_seed(6)
+    M, N, K = 256, 512, 1024
+    a = (torch.randn(M, K, device=DEV)).to(torch.float8_e4m3fn)
+    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.float8_e4m3fn)
+    sa = torch.rand(M, device=DEV) + 0.5
+    sb = torch.rand(N, device=DEV) + 0.5
+    out = ops.gemm_fp8(a, w, sa, sb, bn=128)
+    ref = (a.float() @ w.float().t()) * sa[:, None] * sb[None, :]
+    _close(out, ref)
+
+
+def test_gemm_determinism_and_reuse():
+    """Same launch twice must be bit-identical (catches races in the barrier protocol)."""
+    torch.manual_seed(7)
+    a, w = _rand(512, 2048), _rand(4096, 2048, scale=0.05)
+    o1 = ops.gemm(a, w).clone()
+    for _ in range(3):
+        o2 = ops.gemm(a, w)
+    assert torch.equal(o1, o2)

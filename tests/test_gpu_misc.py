@@ -1,0 +1,102 @@
+"""Bandwidth-bound kernels and the sampler vs fp32 references (run with -m gpu on a B200)."""
+import pytest
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.ops import linear as L
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_embed_gather():
+    torch.manual_seed(0)
+    table = torch.randn(1000, 576, device=DEV).to(torch.bfloat16)
+    ids = torch.randint(0, 1000, (37,), device=DEV, dtype=torch.int32)
+    ss = torch.zeros(37, device=DEV)
+    out = ops.embed_gather(ids, table, ss_out=ss)
+    assert torch.equal(out, table[ids.long()])
+    torch.testing.assert_close(ss, out.float().pow(2).sum(-1), rtol=1e-4, atol=1e-4)
+
+
+def test_rmsnorm_layernorm_glu():
+    torch.manual_seed(1)
+    x = torch.randn(33, 1536, device=DEV).to(torch.bfloat16)
+    r = torch.randn(33, 1536, device=DEV).to(torch.bfloat16)
+    w, b = torch.rand(1536, device=DEV) + 0.5, torch.randn(1536, device=DEV)
+    h = torch.empty_like(x)
+    y = ops.rmsnorm(x, w, 1e-5, residual=r, h_out=h)
+    hr = (x.float() + r.float()).to(torch.bfloat16)
+    assert torch.equal(h, hr)
+    yr = hr.float() * torch.rsqrt(hr.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    y2 = ops.layernorm(x, w, b, 1e-5)
+    torch.testing.assert_close(y2.float(), torch.nn.functional.layer_norm(x.float(), (1536,), w, b, 1e-5),
+                               rtol=2e-2, atol=2e-2)
+    gu = torch.randn(20, 2 * 768, device=DEV).to(torch.bfloat16)
+    g = ops.glu(gu, 0)
+    torch.testing.assert_close(g.float(), torch.nn.functional.silu(gu[:, :768].float()) * gu[:, 768:].float(),
+                               rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("D,rot", [(64, 64), (128, 128), (96, 48), (256, 256)])
+def test_rope_kv_write(D, rot):
+    torch.manual_seed(2)
+    M, n_q, n_kv, pages, max_pos = 45, 6, 2, 8, 256
+    qkv = torch.randn(M, (n_q + 2 * n_kv) * D, device=DEV).to(torch.bfloat16)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, device=DEV).double() / rot))
+    ang = torch.arange(max_pos, device=DEV).double()[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    pos = torch.randint(0, max_pos, (M,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * 16, device=DEV)[:M].to(torch.int32)
+    qn, kn = torch.rand(D, device=DEV) + 0.5, torch.rand(D, device=DEV) + 0.5
+    kv = torch.zeros(pages, 2, n_kv, 16, D, device=DEV, dtype=torch.bfloat16)
+    q_out = torch.zeros(M, n_q * D, device=DEV, dtype=torch.bfloat16)
+    ops.rope_kv_write(qkv, n_q=n_q, n_kv=n_kv, head_dim=D, rot_dim=rot, positions=pos, slot_mapping=slots,
+                      cos_t=cos_t, sin_t=sin_t, q_out=q_out, kv_cache=kv, q_norm_w=qn, k_norm_w=kn)
+    q, k, v = L.qkv_post_ref(qkv, n_q, n_kv, D, pos, cos_t, sin_t, qn, kn, 1e-6)
+    torch.testing.assert_close(q_out.float(), q.reshape(M, -1), rtol=3e-2, atol=3e-2)
+    kv_ref = torch.zeros_like(kv)
+    L.kv_write_ref(kv_ref, k, v, slots)
+    torch.testing.assert_close(kv.float(), kv_ref.float(), rtol=3e-2, atol=3e-2)
+
+
+def test_argmax_and_greedy():
+    torch.manual_seed(3)
+    lg = torch.randn(16, 151936, device=DEV)
+    lg[2, 5] = float("nan")
+    lg[3, 100] = lg[3, 7] = 50.0
+    out = ops.argmax(lg)
+    ref = torch.where(torch.isnan(lg), torch.full_like(lg, float("-inf")), lg).argmax(-1)
+    assert torch.equal(out.long(), ref)
+    assert int(out[3]) == 7
+    params = torch.zeros(16, 4, device=DEV)
+    assert torch.equal(ops.sample(lg, params).long(), ref)
+    assert torch.equal(ops.argmax(lg.to(torch.bfloat16), vocab=1000).long(),
+                       lg.to(torch.bfloat16)[:, :1000].float().nan_to_num(float("-inf")).argmax(-1))
+
+
+def test_sampler_distribution():
+    """Empirical token frequencies follow the top-k / top-p filtered softmax of the reference order."""
+    torch.manual_seed(4)
+    V, B = 512, 4096
+    row = torch.randn(V, device=DEV) * 2
+    lg = row[None].expand(B, V).contiguous()
+    for (t, k, p) in [(0.7, 0, 1.0), (1.0, 20, 1.0), (0.9, 0, 0.8), (1.3, 50, 0.6)]:
+        params = torch.tensor([t, k, p, 0], device=DEV).repeat(B, 1).contiguous()
+        offs = torch.arange(B, device=DEV, dtype=torch.int64)
+        toks = ops.sample(lg, params, seed=1234, step_offsets=offs)
+        freq = torch.bincount(toks.long(), minlength=V).float() / B
+        want = ops.filtered_probs_ref(row.cpu(), t, k, p).to(DEV)
+        assert float(freq[want == 0].sum()) < 2e-3, "sampled a filtered-out token"
+        assert float((freq - want).abs().sum()) < 0.2, f"total variation too large for {(t, k, p)}"
+
+
+def test_pool():
+    h = torch.randn(30, 64, device=DEV).to(torch.bfloat16)
+    st = torch.tensor([0, 10], dtype=torch.int32, device=DEV)
+    ln = torch.tensor([10, 20], dtype=torch.int32, device=DEV)
+    out = ops.pool(h, st, ln, "mean")
+    torch.testing.assert_close(out[1], h[10:30].float().mean(0), rtol=1e-3, atol=1e-3)
+    assert torch.equal(ops.pool(h, st, ln, "cls")[1], h[10].float())
+    assert torch.equal(ops.pool(h, st, ln, "last")[0], h[9].float())
