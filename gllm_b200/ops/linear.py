@@ -107,7 +107,7 @@ def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=No
         acc = a.float() @ w.float().t()
         if bias is not None:
             acc = acc + bias.float()
-        res = (acc + residual.float()).to(torch.bfloat16)
+        res = (acc + residual.float()).to(a.dtype)
         ss = res.float().pow(2)
         pad = parts * bn - N
         if pad:
@@ -152,7 +152,7 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
         N = w_packed.shape[0] // num_groups
     if not a.is_cuda:
         rs = row_scale_ref(row_ss, norm_dim, eps)
-        res = torch.empty((M, N // 2), dtype=torch.bfloat16)
+        res = torch.empty((M, N // 2), dtype=a.dtype)
         groups = [(0, M, 0)] if mblk_group is None else [
             (i * 128, min(M, (i + 1) * 128), int(mblk_group[i])) for i in range((M + 127) // 128)]
         for (r0, r1, g) in groups:
@@ -162,7 +162,7 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
             gv, uv = x @ gw.float().t(), x @ uw.float().t()
             if rs is not None:
                 gv, uv = gv * rs[r0:r1, None], uv * rs[r0:r1, None]
-            res[r0:r1] = (_act_ref(gv, act) * uv).to(torch.bfloat16)
+            res[r0:r1] = (_act_ref(gv, act) * uv).to(a.dtype)
         if out is not None:
             out.copy_(res)
             return out
@@ -183,7 +183,7 @@ def gemm_grouped(a, w_stack, mblk_group, num_groups, *, out=None, bn=128, max_ct
     M, K = a.shape
     N = w_stack.shape[0] // num_groups
     if not a.is_cuda:
-        res = torch.empty((M, N), dtype=torch.bfloat16)
+        res = torch.empty((M, N), dtype=a.dtype)
         for i in range((M + 127) // 128):
             g = int(mblk_group[i])
             res[i * 128:(i + 1) * 128] = (a[i * 128:(i + 1) * 128].float() @ w_stack[g * N:(g + 1) * N].float().t()).to(
