@@ -1,0 +1,273 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode tokens/s of the Qwen3-8B-shape dense decoder (bf16) under continuous
+batching of 256 concurrent synthetic requests (prompt lengths uniform 128-2048, 16-token KV pages,
+a 512-token shared prefix on half of the requests), tensor-parallel over N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 32 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+A "step" is one decode iteration of the serving engine over all running sequences. Two numbers are
+reported: ``value`` is device-timed (CUDA events around K replays of the captured decode step, max over
+ranks); ``e2e`` times the same K steps through the public engine API, including every step's pinned-host
+-> device upload of scheduler inputs and the device -> host read of the sampled tokens.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-8b")
+    ap.add_argument("--concurrency", type=int, default=256)
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=2048)
+    ap.add_argument("--output-tokens", type=int, default=256)
+    ap.add_argument("--shared-prefix", type=int, default=512)
+    ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 marks the result invalid")
+    return ap.parse_args()
+
+
+REFERENCE_UNAVAILABLE = (
+    "reference is a Rust-nightly crate whose kernels and NCCL layer live in two sibling repositories "
+    "(../gllm-kernels, ../gllm-nccl) that are not present; no Rust toolchain in this image, so pip cannot build it")
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_prompts(n, lo, hi, shared_prefix, vocab, seed=1234):
+    import numpy as np
+    rng = np.random.RandomState(seed)
+    prefix = rng.randint(0, vocab, size=shared_prefix).tolist()
+    prompts = []
+    for i in range(n):
+        ln = int(rng.randint(lo, hi + 1))
+        if i % 2 == 0 and ln > shared_prefix:
+            prompts.append(prefix + rng.randint(0, vocab, size=ln - shared_prefix).tolist())
+        else:
+            prompts.append(rng.randint(0, vocab, size=ln).tolist())
+    return prompts
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # relaunch under torchrun so that `python bench.py --gpus N` works on its own
+            port = 29500 + (os.getpid() % 2000)
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.ops import _native as nv
+
+    cfg = preset(args.model)
+    if args.layers:
+        cfg.num_layers = args.layers
+    tp = None
+    if world > 1:
+        from gllm_b200.parallel.tensor_parallel import TPContext
+        tp = TPContext(rank, world, dev, mode=args.tp_mode, max_tokens=8192, hidden=cfg.hidden_size)
+    max_len = args.max_prompt + args.output_tokens + 16
+    src = RandomWeights(cfg, dev, torch.bfloat16, seed=0)
+    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len)
+    ecfg = EngineConfig(max_num_seqs=args.concurrency, max_model_len=max_len, max_batch_tokens=8192,
+                        prefill_chunk=8192, use_cuda_graphs=not args.no_graphs)
+    ecfg.num_pages = args.concurrency * ((max_len + 15) // 16) + 64
+    engine = LLMEngine(model, ecfg)
+    prompts = make_prompts(args.concurrency, args.min_prompt, args.max_prompt, args.shared_prefix, cfg.vocab_size)
+
+    W, K = max(args.warmup, 3), args.steps
+    # every request generates the configured number of tokens; the timed window sits in the middle of it
+    budget_tokens = max(args.output_tokens, W + K + 4)
+    center_steps = max(0, (budget_tokens - K) // 2 - W)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- phase 1: admit + prefill everything (untimed for the decode metric; gives TTFT) ----
+    t_submit = time.perf_counter()
+    ids = [engine.add_request(p, max_tokens=budget_tokens, temperature=0.0, eos_ids=[]) for p in prompts]
+    first_token_at = {}
+    guard = 0
+    while engine.batcher.num_running < args.concurrency and guard < 10000:
+        engine.step()
+        now = time.perf_counter()
+        for rid, st in engine.reqs.items():
+            if st.n_out > 0 and rid not in first_token_at:
+                first_token_at[rid] = st.t_first - t_submit
+        guard += 1
+    ttft = sorted(first_token_at.values())
+    prefill_s = time.perf_counter() - t_submit
+    # ---- phase 2: warm-up decode steps through the public API (captures the graph) ----
+    for _ in range(W + center_steps):
+        engine.step()
+    err = nv.device_error()
+    if err:
+        raise SystemExit(f"device error word {err} after warm-up")
+
+    # ---- phase 3: e2e timed region: K engine steps incl. H2D of inputs and D2H of tokens ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    h2d0, d2h0 = engine.stats["h2d_bytes"], engine.stats["d2h_bytes"]
+    tok0 = engine.stats["decode_tokens"]
+    barrier()
+    t0 = time.perf_counter()
+    step_times = []
+    for _ in range(K):
+        ts = time.perf_counter()
+        engine.step()
+        step_times.append(time.perf_counter() - ts)
+    torch.cuda.synchronize(dev)
+    e2e_s = time.perf_counter() - t0
+    e2e_tokens = engine.stats["decode_tokens"] - tok0
+    h2d = (engine.stats["h2d_bytes"] - h2d0) / K
+    d2h = (engine.stats["d2h_bytes"] - d2h0) / K
+
+    # ---- phase 4: device-timed region: K replays of the captured decode step ----
+    B = engine._bucket(args.concurrency)
+    nv_calls0 = nv.CALLS[0]
+    engine._decode_body(B) if args.no_graphs else None
+    launches_per_step = (nv.CALLS[0] - nv_calls0) if args.no_graphs else engine.launches_per_graph.get(B, 0)
+    graph = engine.graphs.get(B)
+    run = (lambda: graph.replay()) if graph is not None else (lambda: engine._decode_body(B))
+    for _ in range(3):
+        run()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(K):
+        run()
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    dev_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+    err = nv.device_error()
+    if err:
+        raise SystemExit(f"device error word {err} in the timed region")
+
+    t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(t[0]), float(t[1])
+    n_active = args.concurrency
+    value = n_active * K / (dev_ms / 1e3)
+    e2e_value = e2e_tokens / (e2e_ms / 1e3)
+    if rank == 0:
+        med = lambda xs: (sorted(xs)[len(xs) // 2] if xs else None)
+        out = {
+            "metric": "decode tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, uniform-random token ids)",
+            "config": {"model": f"{args.model}-shape dense decoder", "global_batch": n_active,
+                       "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {budget_tokens} out",
+                       "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
+                       "l2": "inputs larger than L2: every step streams all weights and the KV cache",
+                       "tp_mode": getattr(tp, "mode", "none"), "cuda_graphs": not args.no_graphs,
+                       "layers": cfg.num_layers, "valid": args.layers == 0},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms / K, 4)},
+            "gpu_launches": int(launches_per_step * K),
+            "clocks": clocks,
+            "p50_ttft_ms": round(med(ttft) * 1e3, 2) if ttft else None,
+            "p50_tpot_ms": round(med(step_times) * 1e3, 4),
+            "prefill_tokens_per_s": round(engine.stats["prefill_tokens"] / prefill_s, 1),
+            "prefix_cache_hits": int(engine.batcher.prefix_hits),
+            "kv_pages": engine.num_pages,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        if tp is not None:
+            tp.close()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

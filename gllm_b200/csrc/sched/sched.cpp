@@ -425,7 +425,10 @@ StepPlan ContinuousBatcher::schedule() {
     const int remaining = known - s.num_computed;
     if (remaining <= 0 || budget <= 0) return false;
     int chunk = std::min(remaining, std::min(budget, cfg_.prefill_chunk));
-    if (chunk < remaining && chunk < cfg_.min_prefill_chunk) return false;  // not worth a sliver
+    // A sliver left over by the budget is not worth a launch, unless the step would otherwise be empty
+    // (progress guarantee) or the configured chunk cap itself is that small.
+    const int min_chunk = std::min(cfg_.min_prefill_chunk, cfg_.prefill_chunk);
+    if (chunk < remaining && chunk < min_chunk && (plan.num_decode > 0 || !plan.prefill.empty())) return false;
     if (!ensure_pages(s, s.num_computed + chunk)) {
       // take what fits in the pages we can still get
       const int have = static_cast<int>(s.block_table.size()) * page_size_ - s.num_computed;

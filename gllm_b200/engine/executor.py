@@ -1,0 +1,345 @@
+"""The serving engine: C++ continuous batcher + paged KV pool + model + CUDA-graph decode steps.
+
+Reference parity (behaviour, not structure):
+  * ``Executor::{enqueue, step, generate_batch}`` (src/engine/executor_api.rs:540-580, executor_step.rs:113-255)
+  * decode first, prefill backfill, phase-isolated launches (src/scheduler/batcher.rs:217-293, SPEC 32)
+  * stop on EOS or max_new_tokens (src/engine/executor_step.rs:1464-1471); length guard
+    ``prompt + max_new <= max positions`` (src/engine/executor.rs:315-325)
+  * per-step hooks Continue / Veto / Terminate (src/engine/executor_step.rs:1406-1455)
+
+B200 design: the host never touches activations. Each decode step is one CUDA-graph replay per batch
+bucket; its inputs are a single packed int32 upload from pinned memory (tokens, positions, slot mapping,
+context lengths) plus the block tables; its only download is the sampled token per slot. Prefill
+chunks run as ordinary launches between decode replays.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from .. import scheduler as S
+from ..models.config import ModelConfig
+from ..models.decoder import DecoderModel
+from .batch import ForwardBatch, GenerateResult, SequenceTelemetry
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024)
+
+
+@dataclass
+class EngineConfig:
+    max_num_seqs: int = 256
+    max_model_len: int = 4096
+    max_batch_tokens: int = 8192
+    prefill_chunk: int = 8192
+    num_pages: int = 0                 # 0 = size from memory_fraction
+    memory_fraction: float = 0.85
+    enable_prefix_cache: bool = True
+    use_cuda_graphs: bool = True
+    pages_per_split: int = 32
+    seed: int = 0
+    order: int = S.ORDER_STRICT_REQUEST_ID
+
+
+@dataclass
+class _ReqState:
+    t_submit: float
+    t_first: float = 0.0
+    t_last: float = 0.0
+    hook: Optional[Callable] = None
+    stream: Optional[Callable] = None
+    n_out: int = 0
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None):
+        self.model, self.cfg, self.tokenizer = model, cfg or EngineConfig(), tokenizer
+        self.mc: ModelConfig = model.cfg
+        self.device = model.device
+        ec = self.cfg
+        ec.max_model_len = min(ec.max_model_len, model.max_positions)
+        self.max_blocks = (ec.max_model_len + 15) // 16
+        self.num_pages = ec.num_pages or self._auto_pages()
+        self.kv_caches = model.alloc_kv_cache(self.num_pages)
+        pc = S.PolicyConfig()
+        pc.max_batch_size = ec.max_num_seqs
+        pc.max_batch_tokens = ec.max_batch_tokens
+        pc.prefill_chunk = ec.prefill_chunk
+        pc.enable_prefix_cache = ec.enable_prefix_cache
+        pc.order = ec.order
+        self.batcher = S.ContinuousBatcher(self.num_pages, 16, ec.max_num_seqs, self.max_blocks, pc)
+        self.ms = ec.max_num_seqs
+        dev = self.device
+        cuda = dev.type == "cuda"
+        pin = dict(pin_memory=True) if cuda else {}
+        # host staging (pinned) and device mirrors
+        self.h_dec = torch.zeros(4 * self.ms, dtype=torch.int32, **pin)
+        self.h_bt = torch.zeros((self.ms, self.max_blocks), dtype=torch.int32, **pin)
+        self.h_params = torch.zeros((self.ms, 4), dtype=torch.float32, **pin)
+        self.h_out = torch.zeros(self.ms, dtype=torch.int32, **pin)
+        self.d_dec = torch.zeros(4 * self.ms, dtype=torch.int32, device=dev)
+        self.d_bt = torch.zeros((self.ms, self.max_blocks), dtype=torch.int32, device=dev)
+        self.d_params = torch.zeros((self.ms, 4), dtype=torch.float32, device=dev)
+        self.d_out = torch.zeros(self.ms, dtype=torch.int32, device=dev)
+        self.d_offsets = torch.zeros(self.ms, dtype=torch.int64, device=dev)
+        self.slot_params = np.zeros((self.ms, 4), dtype=np.float32)
+        max_splits = max(1, (self.max_blocks + ec.pages_per_split - 1) // ec.pages_per_split)
+        self.decode_ws = (ops.DecodeWorkspace(self.ms, model.n_q_local, model.n_kv_local, max_splits, dev)
+                          if cuda and self.mc.head_dim == 128 else None)
+        model.workspace(max(ec.max_batch_tokens, self.ms))
+        self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
+        self.reqs: Dict[int, _ReqState] = {}
+        self.results: Dict[int, GenerateResult] = {}
+        self._next_id = 0
+        self.stats = dict(decode_steps=0, prefill_steps=0, decode_tokens=0, prefill_tokens=0, h2d_bytes=0,
+                          d2h_bytes=0, kernel_launches=0, preemptions=0)
+        self.launches_per_graph: Dict[int, int] = {}
+        self.gen = torch.Generator().manual_seed(ec.seed)
+        self._req_params: Dict[int, tuple] = {}
+        self._vetoed: Dict[int, str] = {}
+
+    # ------------------------------------------------------------------------------------------
+    def _auto_pages(self) -> int:
+        per_page = 16 * self.mc.kv_bytes_per_token(self.model.tp_size) * len(self.model.layer_ids) // max(
+            self.mc.num_layers, 1)
+        if self.device.type != "cuda":
+            return max(64, min(4096, (self.cfg.max_num_seqs * self.cfg.max_model_len) // 16 + 8))
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(free - (1.0 - self.cfg.memory_fraction) * total)
+        want = self.cfg.max_num_seqs * self.max_blocks + 64
+        return int(max(64, min(want, budget // max(per_page, 1))))
+
+    # ------------------------------------------------------------------------------------------
+    def add_request(self, prompt_ids: List[int], *, max_tokens=256, temperature=0.7, top_k=0, top_p=1.0,
+                    eos_ids=None, session_id: Optional[str] = None, hook=None, stream=None,
+                    request_id: Optional[int] = None) -> int:
+        if len(prompt_ids) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt_ids) + max_tokens > self.cfg.max_model_len:
+            raise ValueError(f"SequenceTooLong: {len(prompt_ids)} + {max_tokens} > {self.cfg.max_model_len}")
+        rid = self._next_id if request_id is None else request_id
+        self._next_id = max(self._next_id, rid) + 1
+        eos = list(self.mc.eos_token_ids) if eos_ids is None else list(eos_ids)
+        sp = S.SamplingParams(temperature=float(temperature), top_k=int(top_k), top_p=float(top_p),
+                              max_new_tokens=int(max_tokens), eos_ids=eos)
+        self.batcher.add_request(rid, [int(t) for t in prompt_ids], sp, session_id or "")
+        self.reqs[rid] = _ReqState(t_submit=time.perf_counter(), hook=hook, stream=stream)
+        self._req_params[rid] = (float(temperature), int(top_k), float(top_p))
+        return rid
+
+    submit = add_request
+
+    def has_work(self) -> bool:
+        return bool(self.reqs)
+
+    # ------------------------------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in DECODE_BUCKETS:
+            if b >= n:
+                return min(b, self.ms)
+        return self.ms
+
+    def _decode_batch(self, B: int) -> ForwardBatch:
+        ms = self.ms
+        return ForwardBatch(token_ids=self.d_dec[0:B], positions=self.d_dec[ms:ms + B],
+                            slot_mapping=self.d_dec[2 * ms:2 * ms + B], block_tables=self.d_bt[:B],
+                            ctx_lens=self.d_dec[3 * ms:3 * ms + B], is_decode=True)
+
+    def _decode_body(self, B: int):
+        logits = self.model.forward(self._decode_batch(B), self.kv_caches, decode_ws=self.decode_ws)
+        self._sample(logits, self.d_params[:B], self.d_offsets[:B], self.d_out[:B])
+        self.d_offsets[:B] += 1
+
+    def _sample(self, logits, params, offsets, out):
+        tp = self.model.tp
+        if tp is not None and tp.size > 1:
+            tp.sample_vocab_parallel(logits, self.model.vocab_local, self.model.vocab_start, params, self.cfg.seed,
+                                     offsets, out, self.mc.vocab_size)
+        else:
+            ops.sample(logits, params, vocab=self.mc.vocab_size, seed=self.cfg.seed, step_offsets=offsets, out=out,
+                       generator=self.gen)
+
+    def _run_decode(self, plan) -> np.ndarray:
+        ms = self.ms
+        plan.pack_decode_into(self.h_dec.numpy())
+        self.batcher.copy_slot_block_tables_into(self.h_bt.numpy().reshape(-1))
+        ids = plan.dec_seq_ids
+        active = np.nonzero(ids >= 0)[0]
+        B = self._bucket(int(active[-1]) + 1)
+        self.h_params.numpy()[:] = self.slot_params
+        cuda = self.device.type == "cuda"
+        self.d_dec.copy_(self.h_dec, non_blocking=cuda)
+        self.d_bt.copy_(self.h_bt, non_blocking=cuda)
+        self.d_params.copy_(self.h_params, non_blocking=cuda)
+        self.stats["h2d_bytes"] += self.h_dec.numel() * 4 + self.h_bt.numel() * 4 + self.h_params.numel() * 4
+        if cuda and self.cfg.use_cuda_graphs:
+            g = self.graphs.get(B)
+            if g is None:
+                g = self._capture(B)
+            g.replay()
+        else:
+            self._decode_body(B)
+        self.h_out.copy_(self.d_out, non_blocking=False)
+        self.stats["d2h_bytes"] += self.h_out.numel() * 4
+        self.stats["decode_steps"] += 1
+        self.stats["decode_tokens"] += int(plan.num_decode)
+        return self.h_out.numpy()
+
+    def _capture(self, B: int):
+        # warm up outside capture so lazy initialisation (attribute setting, descriptor cache) is done
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._decode_body(B)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self.d_offsets[:B] -= 1
+        g = torch.cuda.CUDAGraph()
+        from ..ops import _native as nv
+        n0 = nv.CALLS[0]
+        with torch.cuda.graph(g, stream=s):
+            self._decode_body(B)
+        self.launches_per_graph[B] = nv.CALLS[0] - n0
+        self.graphs[B] = g
+        return g
+
+    def _run_prefill(self, plan) -> np.ndarray:
+        dev = self.device
+        T = plan.num_prefill_tokens
+        S_ = plan.num_prefill_seqs
+        t = lambda a: torch.from_numpy(a)
+        pack = np.concatenate([plan.pf_tokens, plan.pf_positions, plan.pf_slot_mapping, plan.pf_q_start,
+                               plan.pf_q_len, plan.pf_ctx_lens]).astype(np.int32)
+        hp = t(pack)
+        hb = t(plan.pf_block_tables)
+        if dev.type == "cuda":
+            hp, hb = hp.pin_memory(), hb.pin_memory()
+        dp = hp.to(dev, non_blocking=True)
+        db = hb.to(dev, non_blocking=True)
+        self.stats["h2d_bytes"] += hp.numel() * 4 + hb.numel() * 4
+        items = plan.prefill
+        last_rows, last_slots = [], []
+        for i, it in enumerate(items):
+            if it.last:
+                last_rows.append(int(plan.pf_q_start[i]) + it.len - 1)
+                last_slots.append(it.slot)
+        rows = torch.tensor(last_rows, dtype=torch.int64, device=dev) if last_rows else None
+        batch = ForwardBatch(token_ids=dp[0:T], positions=dp[T:2 * T], slot_mapping=dp[2 * T:3 * T],
+                             block_tables=db, ctx_lens=dp[3 * T + 2 * S_:3 * T + 3 * S_], is_decode=False,
+                             q_start=dp[3 * T:3 * T + S_], q_len=dp[3 * T + S_:3 * T + 2 * S_],
+                             max_q_len=int(plan.pf_q_len.max()), logits_rows=rows)
+        self.stats["prefill_steps"] += 1
+        self.stats["prefill_tokens"] += int(T)
+        if rows is None:
+            self.model.forward(batch, self.kv_caches, return_hidden=True)
+            return np.zeros(0, np.int32)
+        logits = self.model.forward(batch, self.kv_caches)
+        sl = torch.tensor(last_slots, dtype=torch.int64)
+        params = torch.from_numpy(self.slot_params[last_slots]).to(dev)
+        offs = self.d_offsets.index_select(0, sl.to(dev))
+        out = torch.empty(len(last_rows), dtype=torch.int32, device=dev)
+        self._sample(logits, params, offs, out)
+        self.d_offsets.index_add_(0, sl.to(dev), torch.ones(len(last_rows), dtype=torch.int64, device=dev))
+        res = out.cpu().numpy()
+        self.stats["d2h_bytes"] += res.size * 4
+        return res
+
+    # ------------------------------------------------------------------------------------------
+    def step(self) -> List[GenerateResult]:
+        """One scheduler iteration: decode replay for the running set, then one prefill chunk batch."""
+        plan = self.batcher.schedule()
+        self.stats["preemptions"] += len(plan.preempted)
+        if plan.idle:
+            return self._collect()
+        for it in plan.prefill:
+            if it.start == 0 or self.slot_params[it.slot, 3] != float(it.seq_id):
+                sp = self._params_of(it.seq_id)
+                self.slot_params[it.slot] = (sp[0], sp[1], sp[2], float(it.seq_id))
+        dec_tokens = np.zeros(self.ms, np.int32)
+        pf_tokens = np.zeros(0, np.int32)
+        if plan.num_decode > 0:
+            dec_tokens = self._run_decode(plan).copy()
+        if plan.num_prefill_seqs > 0:
+            pf_tokens = self._run_prefill(plan)
+        now = time.perf_counter()
+        ids = plan.dec_seq_ids
+        # hooks / streaming observe the sampled tokens before they are committed
+        for sl in np.nonzero(ids >= 0)[0]:
+            self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
+        k = 0
+        for it in plan.prefill:
+            if it.last:
+                self._observe(int(it.seq_id), int(pf_tokens[k]), now)
+                k += 1
+        self.batcher.commit(plan, dec_tokens, pf_tokens)
+        return self._collect()
+
+    def _params_of(self, rid):
+        return self._req_params.get(rid, (0.0, 0, 1.0))
+
+    def _observe(self, rid: int, tok: int, now: float):
+        st = self.reqs.get(rid)
+        if st is None:
+            return
+        if st.n_out == 0:
+            st.t_first = now
+        st.t_last = now
+        st.n_out += 1
+        if st.stream is not None:
+            st.stream(rid, tok)
+        if st.hook is not None:
+            decision = st.hook(rid, tok, st.n_out)
+            if decision in ("veto", "terminate"):
+                self._vetoed[rid] = decision
+
+    def _collect(self) -> List[GenerateResult]:
+        out = []
+        vetoed = self._vetoed
+        for rid in list(vetoed):
+            self.batcher.abort(rid)
+        for f in self.batcher.pop_finished():
+            st = self.reqs.pop(f.id, None)
+            self._req_params.pop(f.id, None)
+            toks = [int(t) for t in f.tokens]
+            reason = S.FINISH_REASONS.get(f.finish, "length")
+            if f.id in vetoed:
+                how = vetoed.pop(f.id)
+                reason = how
+                if how == "veto" and toks:
+                    toks = toks[:-1]  # the vetoed token is dropped
+            tel = SequenceTelemetry(prompt_tokens=f.prompt_len, generated_tokens=len(toks),
+                                    cached_prefix_tokens=f.cached_prefix, preemptions=f.preemptions)
+            if st is not None:
+                tel.ttft_ms = (st.t_first - st.t_submit) * 1e3 if st.t_first else 0.0
+                tel.e2e_ms = (st.t_last - st.t_submit) * 1e3 if st.t_last else 0.0
+                tel.tpot_ms = ((st.t_last - st.t_first) * 1e3 / max(st.n_out - 1, 1)) if st.n_out > 1 else 0.0
+            text = self.tokenizer.decode(toks) if self.tokenizer is not None else ""
+            r = GenerateResult(request_id=f.id, token_ids=toks, text=text, finish_reason=reason, telemetry=tel)
+            self.results[f.id] = r
+            out.append(r)
+        return out
+
+    # ------------------------------------------------------------------------------------------
+    def run_until_done(self, max_steps: int = 10 ** 9) -> List[GenerateResult]:
+        done = []
+        steps = 0
+        while steps < max_steps:
+            plan_results = self.step()
+            done.extend(plan_results)
+            steps += 1
+            if not self.reqs:
+                break
+        return done
+
+    def generate_batch(self, prompts: List[List[int]], *, max_tokens=256, temperature=0.7, top_k=0, top_p=1.0,
+                       eos_ids=None) -> List[GenerateResult]:
+        """All requests in one call; results come back in request order."""
+        mt = max_tokens if isinstance(max_tokens, (list, tuple)) else [max_tokens] * len(prompts)
+        ids = [self.submit(p, max_tokens=m, temperature=temperature, top_k=top_k, top_p=top_p, eos_ids=eos_ids)
+               for p, m in zip(prompts, mt)]
+        self.run_until_done()
+        return [self.results.pop(i) for i in ids]

@@ -1,0 +1,205 @@
+"""Config-driven decoder (Llama / Qwen2 / Qwen3 / Mistral / Gemma-style dense, Qwen3-MoE, and the
+DeepSeek MLA variants through ``models/mla.py``) that only calls ops.
+
+Per layer the reference's graph is: input norm -> q/k/v -> head norm -> RoPE -> attention(kv write) ->
+o_proj -> residual -> post-attn norm -> gate/up -> SwiGLU -> down -> residual
+(src/arch/auto_graph_fragments/build_graph.inc.rs:1445-2045). On B200 that becomes five launches:
+
+    fused QKV GEMM   [RMSNorm as row scale] -> per-head norm -> RoPE -> q buffer + paged KV write
+    paged attention  (flash-decode or chunked prefill)
+    o_proj GEMM      + residual, leaves the next norm's row statistics behind
+    gate/up GEMM     [RMSNorm as row scale] -> SwiGLU epilogue
+    down GEMM        + residual, row statistics for the next layer
+
+Architectures the fused kernels do not cover (head_dim != 128, partial rotary, LayerNorm, ...) take the
+unfused path built from the same op library. CPU tensors run every op's fp32 oracle, so the same class is
+the CPU reference model.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..engine.batch import ForwardBatch
+from ..ops import linear as L
+from . import rope
+from .config import ModelConfig
+from .weights import DenseLayerWeights, can_fuse, layer_prefix, pack_dense_layer, shard_range, shard_tensor, _fold
+
+
+class Workspace:
+    """Static activation buffers (needed for CUDA-graph replay; also avoids allocator traffic)."""
+
+    def __init__(self, model: "DecoderModel", max_tokens: int):
+        c, dev, dt = model.cfg, model.device, model.dtype
+        T = max_tokens
+        self.max_tokens = T
+        H = c.hidden_size
+        self.x = torch.zeros((T, H), dtype=dt, device=dev)
+        self.h = torch.zeros((T, H), dtype=dt, device=dev)
+        self.q = torch.zeros((T, model.n_q_local * c.head_dim), dtype=dt, device=dev)
+        self.attn = torch.zeros((T, model.n_q_local * c.head_dim), dtype=dt, device=dev)
+        self.qkv = None if model.fused else torch.zeros((T, (model.n_q_local + 2 * model.n_kv_local) * c.head_dim),
+                                                        dtype=dt, device=dev)
+        inter = max(model.inter_local, 1)
+        self.act = torch.zeros((T, inter), dtype=dt, device=dev)
+        self.gu = None if model.fused else torch.zeros((T, 2 * inter), dtype=dt, device=dev)
+        self.parts = max(1, (H + 127) // 128)
+        self.ss0 = torch.zeros((T, 1), dtype=torch.float32, device=dev)
+        self.ss_a = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
+        self.ss_b = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
+        self.partial = torch.zeros((T, H), dtype=dt, device=dev) if model.tp_size > 1 else None
+
+
+class DecoderModel:
+    def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
+                 fused: Optional[bool] = None, layers: Optional[range] = None):
+        """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
+        ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
+        self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
+        self.tp_rank = tp.rank if tp else 0
+        self.tp_size = tp.size if tp else 1
+        self.layer_ids = list(layers) if layers is not None else list(range(cfg.num_layers))
+        self.first_stage = 0 in self.layer_ids
+        self.last_stage = (cfg.num_layers - 1) in self.layer_ids
+        self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and self.device.type == "cuda"
+        if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size):
+            raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} not divisible by tp={self.tp_size}")
+        self.n_q_local = cfg.num_heads // self.tp_size
+        self.n_kv_local = max(1, cfg.num_kv_heads // self.tp_size)
+        self.inter_local = (cfg.moe_intermediate_size if (cfg.is_moe and cfg.first_k_dense == 0) else
+                            cfg.intermediate_size // self.tp_size)
+        self.max_positions = max_positions or cfg.max_position_embeddings
+        self.cos, self.sin = rope.build_tables(cfg, self.max_positions, self.device)
+        self.act_id = L.ACT_IDS.get(cfg.hidden_act, 0)
+        self.scale = cfg.attention_scale()
+
+        to = lambda t: t.to(self.device, dtype if t.is_floating_point() and t.dtype != torch.float32 else None)
+        self.embed = to(src.get("embed_tokens")).contiguous() if self.first_stage or cfg.tie_word_embeddings else None
+        self.layers: List[DenseLayerWeights] = []
+        for i in self.layer_ids:
+            lw = pack_dense_layer(cfg, src, i, self.tp_rank, self.tp_size, self.fused)
+            if cfg.layer_is_moe(i):
+                from .moe import pack_moe_layer
+                lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
+                                        ep=getattr(tp, "ep", None))
+            self.layers.append(lw)
+        self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
+        self.lm_head = None
+        self.vocab_local = cfg.vocab_size
+        self.vocab_start = 0
+        if self.last_stage:
+            head = src.get("lm_head") if src.has("lm_head") else src.get("embed_tokens")
+            a, b = shard_range(cfg.vocab_size, self.tp_rank, self.tp_size)
+            self.vocab_start, self.vocab_local = a, b - a
+            head = head[a:b].to(self.device, dtype)
+            if self.fused:
+                head = _fold(head, self.final_norm, cfg.norm_one_plus_w)
+            self.lm_head = L.pad_rows(head, 128).contiguous()
+        self._ws: Optional[Workspace] = None
+
+    # ------------------------------------------------------------------------------------------
+    def kv_cache_shape(self, num_pages: int):
+        return (num_pages, 2, self.n_kv_local, 16, self.cfg.head_dim)
+
+    def alloc_kv_cache(self, num_pages: int) -> List[torch.Tensor]:
+        return [torch.zeros(self.kv_cache_shape(num_pages), dtype=self.dtype, device=self.device)
+                for _ in self.layer_ids]
+
+    def workspace(self, tokens: int) -> Workspace:
+        if self._ws is None or self._ws.max_tokens < tokens:
+            self._ws = Workspace(self, max(tokens, 256))
+        return self._ws
+
+    # ------------------------------------------------------------------------------------------
+    def _attention(self, q, kv, batch: ForwardBatch, out, layer: int, decode_ws):
+        window = self.cfg.layer_window(layer)
+        if batch.is_decode:
+            return ops.paged_decode(q, kv, batch.block_tables, batch.ctx_lens, n_q=self.n_q_local, n_kv=self.n_kv_local,
+                                    scale=self.scale, out=out, workspace=decode_ws, window=window)
+        return ops.paged_prefill(q, kv, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_lens,
+                                 max_q_len=batch.max_q_len, n_q=self.n_q_local, n_kv=self.n_kv_local, scale=self.scale,
+                                 out=out, causal=batch.causal and self.cfg.causal, window=window)
+
+    def _row_parallel(self, a, w, x, ss_out, T):
+        """x <- a @ w.T + x, row statistics into ss_out. With TP the partial sums are all-reduced."""
+        if self.tp_size == 1:
+            ops.gemm_residual(a, w, x, out=x, row_ss_out=ss_out, bn=128)
+            return
+        self.tp.gemm_allreduce_residual(a, w, x, ss_out, self._ws.partial[:T])
+
+    def forward(self, batch: ForwardBatch, kv_caches: List[torch.Tensor], *, hidden_in=None, decode_ws=None,
+                return_hidden: bool = False, capture_layers=None):
+        """Returns fp32 logits [R, vocab_local_padded] on the last pipeline stage, else the hidden states."""
+        c = self.cfg
+        T = batch.num_tokens
+        ws = self.workspace(T)
+        x = ws.x[:T]
+        H = c.hidden_size
+        captured = {}
+        if self.first_stage:
+            ops.embed_gather(batch.token_ids, self.embed, scale=c.embedding_scale, out=x, ss_out=ws.ss0[:T])
+        else:
+            x.copy_(hidden_in)
+            if self.fused:
+                ops.rmsnorm(x, None, c.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)
+        ss_in = ws.ss0[:T]
+        for li, lw in zip(self.layer_ids, self.layers):
+            kv = kv_caches[li - self.layer_ids[0]]
+            if self.fused:
+                ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
+                             slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
+                             sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
+                             row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias)
+                self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+                self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
+                if lw.moe is not None:
+                    lw.moe.forward(self, x, ws.ss_b[:T], ws.ss_a[:T], T)
+                else:
+                    ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
+                                 row_ss=ws.ss_b[:T], norm_dim=H, eps=c.rms_norm_eps, bn=lw.glu_bn)
+                    self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
+                ss_in = ws.ss_a[:T]
+            else:
+                h = ws.h[:T]
+                ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)
+                qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
+                ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
+                                  positions=batch.positions, slot_mapping=batch.slot_mapping, cos_t=self.cos,
+                                  sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
+                                  k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps)
+                self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+                self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
+                ops.rmsnorm(x, lw.post_attn_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)
+                if lw.moe is not None:
+                    lw.moe.forward_unfused(self, x, h, T)
+                else:
+                    gu = ops.gemm(h, lw.w_gate_up, out=ws.gu[:T, :lw.w_gate_up.shape[0]], out_dtype=self.dtype, bn=128)
+                    act = ops.glu(gu, self.act_id, out=ws.act[:T, :lw.w_down.shape[1]])
+                    self._row_parallel(act, lw.w_down, x, ws.ss_a[:T], T)
+            if capture_layers is not None and li in capture_layers:
+                captured[li] = x.clone()
+        if capture_layers is not None:
+            self.captured = captured
+        if not self.last_stage or return_hidden:
+            return x
+        rows = batch.logits_rows
+        if self.fused:
+            xr, sr = (x, ss_in) if rows is None else (x.index_select(0, rows), ss_in.index_select(0, rows))
+            logits = ops.gemm(xr, self.lm_head, out_dtype=torch.float32, row_ss=sr, norm_dim=H, eps=c.rms_norm_eps,
+                              bn=128)
+        else:
+            xr = x if rows is None else x.index_select(0, rows)
+            hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
+            logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=128)
+        if c.logit_softcap:
+            logits = torch.tanh(logits / c.logit_softcap) * c.logit_softcap
+        return logits
+
+    # ------------------------------------------------------------------------------------------
+    def final_hidden(self, x):
+        """Final-norm hidden states (embedding / head-routing consumers)."""
+        return ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, one_plus_w=self.cfg.norm_one_plus_w)

@@ -94,7 +94,11 @@ def register(name, restype, argtypes, optional=False):
         fn.restype, fn.argtypes = restype, argtypes
 
 
+CALLS = [0]  # number of kernel-launching entry points called so far (bench.py reports launches)
+
+
 def check(rc: int, what: str):
+    CALLS[0] += 1
     if rc != 0:
         msg = lib().gllm_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{what} failed: {msg}")
