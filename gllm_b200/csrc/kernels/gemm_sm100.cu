@@ -5,12 +5,20 @@
 // the reference's graph uses for every linear (src/arch/auto_graph_fragments/build_graph.inc.rs:1618).
 //
 // One CTA per SM, 256 threads:
-//   warp 0      TMA producer: 128xBK A tile + BNxBK B tile per stage, 128-byte swizzle
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16|32) into TMEM
+//   warp 0      TMA producer: MT x (128 x BK) A tiles + one BN x BK B tile per stage, 128-byte swizzle
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16|32) into TMEM, MT
+//               accumulators per B tile so a weight tile fetched once serves up to 256 rows
 //   warp 2      TMEM allocator
 //   warps 4..7  epilogue: tcgen05.ld -> registers -> fused epilogue -> global
-// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps
-// the main loop of tile i+1.
+// When two accumulator sets fit in TMEM (2*MT*BN <= 512 columns) they are double-buffered so the
+// epilogue of work item i overlaps the main loop of item i+1.
+//
+// Small-M (decode) shapes have too few output tiles to occupy 148 SMs and are bound by how fast
+// one SM can pull bytes into shared memory (about 100 GB/s), so the K dimension is split across
+// CTAs. The kernel then has two phases separated by a grid barrier (all CTAs are resident: one per
+// SM): phase 1 streams distinct weight slices and dumps fp32 partial tiles to scratch; phase 2 has
+// every warp of every CTA sum the partials in split order (deterministic) with coalesced loads and
+// apply the same fused epilogue.
 //
 // Fused epilogues (the reference lowers these as separate graph ops; see build_graph.inc.rs
 // RmsNorm :275, Add :1865, SwiGlu :1983, HeadRmsNorm :1708, RoPE :1754, attention kv_write :1777):
@@ -31,10 +39,14 @@ constexpr int kBM = 128;
 constexpr int kTileKBytes = 128;  // one swizzle row
 constexpr int kGemmThreads = 256;
 constexpr int kPageTokens = 16;
+constexpr int kMaxSplits = 16;
 
 struct GemmParams {
   int M, N, K;
-  int num_m, num_n, num_kb;
+  int num_m, num_n, num_kb;  // num_m counts MT*128-row super tiles
+  int splits;
+  float* sk_scratch;        // [split][M][num_n*BN] fp32 partial sums
+  unsigned int* sk_barrier;  // {arrival count, generation} of the grid barrier
   // output
   void* out;
   long long ldo;
@@ -53,12 +65,12 @@ struct GemmParams {
   const float* b_scale;
   // GLU
   int glu_act;  // 0 = silu, 1 = gelu_tanh
-  // grouped GEMM: m-block -> group id; B rows of group g start at g * group_rows
+  // grouped GEMM: 128-row m-block -> group id; B rows of group g start at g * group_rows
   const int* mblk_group;
   int group_rows;
   // QKV epilogue
   int n_q_heads, n_kv_heads;
-  __nv_bfloat16* q_out;  // [M, n_q_heads*128]
+  __nv_bfloat16* q_out;     // [M, n_q_heads*128]
   __nv_bfloat16* kv_cache;  // [pages][2][n_kv_heads][16][128]
   int num_pages;
   const int* slot_mapping;  // [M] slot = page*16 + offset, or -1
@@ -72,11 +84,13 @@ struct GemmParams {
   int* err;
 };
 
-template <int BN>
+template <int BN, int MT>
 struct GemmCfg {
-  static constexpr int kStageBytes = kBM * kTileKBytes + BN * kTileKBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int kStageBytes = MT * kBM * kTileKBytes + BN * kTileKBytes;
+  static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
+  static constexpr int kAccStages = (2 * MT * BN <= 512) ? 2 : 1;
+  static constexpr int kCols = kAccStages * MT * BN;
+  static constexpr int kTmemCols = kCols <= 32 ? 32 : (kCols <= 64 ? 64 : (kCols <= 128 ? 128 : (kCols <= 256 ? 256 : 512)));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*align slack*/;
 };
 
@@ -101,15 +115,266 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&
   }
 }
 
-template <int BN, int EPI, bool FP8>
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Accumulator access for the epilogue: 32 consecutive fp32 columns of this thread's TMEM lane.
+struct AccReader {
+  uint32_t taddr;  // TMEM address of (lane quadrant, accumulator, column 0)
+  __device__ __forceinline__ void load(int col, float (&v)[32]) const {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + col, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  }
+};
+
+// Sense-reversing grid barrier over {count, generation}; bounded. Returns false on timeout.
+__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num_ctas, int* err) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    __threadfence();
+    const unsigned int gen = *reinterpret_cast<volatile unsigned int*>(bar + 1);
+    if (atomicAdd(bar, 1u) == num_ctas - 1) {
+      *reinterpret_cast<volatile unsigned int*>(bar) = 0u;
+      __threadfence();
+      atomicAdd(bar + 1, 1u);
+    } else {
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned int spins = 0;
+      while (*reinterpret_cast<volatile unsigned int*>(bar + 1) == gen) {
+        if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+          if (err) atomicCAS(err, 0, ERR_TIMEOUT_GRID);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    __threadfence();
+    ok_flag = ok;
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+__device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
+
+// Phase 2 of a split-K GEMM: a warp owns (row, n tile) units, four at a time; lanes cover a unit's
+// columns with vector loads. Loads of several units and several splits are issued together (the phase
+// is latency bound: few threads, L2 round trips), the adds happen in split order so the result does
+// not depend on timing, then the fused epilogue of EPI is applied.
+template <int BN, int EPI>
+__device__ void splitk_reduce_phase(const GemmParams& p) {
+  constexpr bool kGlu = (EPI == EPI_GLU), kQkv = (EPI == EPI_QKV);
+  constexpr int NSEG = (kGlu || kQkv) ? 2 : BN / 128;            // vector segments per lane and unit
+  constexpr int SEGW = (kQkv || (kGlu && BN == 128)) ? 2 : 4;    // floats per segment
+  constexpr int NV = NSEG * SEGW;
+  constexpr int U = 4;                                           // units in flight per warp
+  constexpr int SU = (NV == 8) ? 2 : 4;                          // splits in flight
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const long long split_stride = static_cast<long long>(p.M) * n_pad;
+  const int units = p.M * p.num_n;
+  int seg_off[NSEG];
+  if constexpr (kGlu || kQkv) {
+    seg_off[0] = lane * SEGW;
+    seg_off[1] = BN / 2 + lane * SEGW;
+  } else {
+#pragma unroll
+    for (int g = 0; g < NSEG; ++g) seg_off[g] = lane * NV + g * 4;
+  }
+  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
+       u0 += gridDim.x * warps_per_cta * U) {
+    float acc[U][NV];
+    const float* base[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      base[k] = p.sk_scratch + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
+    }
+    for (int s0 = 0; s0 < p.splits; s0 += SU) {
+      float tmp[SU][U][NV];
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        const int s = min(s0 + ds, p.splits - 1);
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+#pragma unroll
+          for (int g = 0; g < NSEG; ++g) {
+            const float* src = base[k] + s * split_stride + seg_off[g];
+            if constexpr (SEGW == 4) {
+              const float4 f = ldcg4(src);
+              tmp[ds][k][g * 4 + 0] = f.x; tmp[ds][k][g * 4 + 1] = f.y;
+              tmp[ds][k][g * 4 + 2] = f.z; tmp[ds][k][g * 4 + 3] = f.w;
+            } else {
+              const float2 f = ldcg2(src);
+              tmp[ds][k][g * 2 + 0] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        if (s0 + ds < p.splits) {
+#pragma unroll
+          for (int k = 0; k < U; ++k)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) acc[k][j] += tmp[ds][k][j];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {  // fully unrolled: acc[k] must stay in registers
+      const int u = u0 + k;
+      if (u >= units) continue;
+      const int n_blk = u % p.num_n;
+      const int m = u / p.num_n;
+      float v[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
+      float rs = row_scale_of(p, m);
+      if (p.a_scale) rs *= p.a_scale[m];
+      if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+        const int n0 = n_blk * BN + lane * NV;
+        float ss = 0.f;
+        if (n0 < p.N) {
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            v[j] *= rs;
+            if (p.b_scale) v[j] *= p.b_scale[n0 + j];
+            if (p.bias) v[j] += p.bias[n0 + j];
+          }
+          if constexpr (EPI == EPI_RESIDUAL) {
+            const __nv_bfloat16* r = p.residual + static_cast<long long>(m) * p.ldr + n0;
+#pragma unroll
+            for (int j = 0; j < NV; j += 2) {
+              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r + j));
+              v[j] = bf16_round(v[j] + f.x);
+              v[j + 1] = bf16_round(v[j + 1] + f.y);
+              ss += v[j] * v[j] + v[j + 1] * v[j + 1];
+            }
+          }
+          if (p.out_f32) {
+            float* o = static_cast<float*>(p.out) + static_cast<long long>(m) * p.ldo + n0;
+#pragma unroll
+            for (int j = 0; j < NV; j += 4)
+              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0;
+#pragma unroll
+            for (int j = 0; j < NV; j += 4) {
+              uint2 w;
+              w.x = pack_bf16x2(v[j], v[j + 1]);
+              w.y = pack_bf16x2(v[j + 2], v[j + 3]);
+              *reinterpret_cast<uint2*>(o + j) = w;
+            }
+          }
+        }
+        if constexpr (EPI == EPI_RESIDUAL) {
+          ss = warp_sum(ss);
+          if (p.row_ss_out && lane == 0) p.row_ss_out[static_cast<long long>(m) * p.num_n + n_blk] = ss;
+        }
+      } else if constexpr (EPI == EPI_GLU) {
+        constexpr int kHalf = BN / 2;
+        const int n0 = n_blk * kHalf + lane * SEGW;
+        if (n0 < p.N / 2) {
+          float o4[SEGW];
+#pragma unroll
+          for (int j = 0; j < SEGW; ++j) {
+            float gv = v[j] * rs, uv = v[SEGW + j] * rs;
+            if (p.b_scale) {
+              gv *= p.b_scale[n_blk * BN + lane * SEGW + j];
+              uv *= p.b_scale[n_blk * BN + kHalf + lane * SEGW + j];
+            }
+            o4[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+          }
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0;
+          if constexpr (SEGW == 4) {
+            uint2 w;
+            w.x = pack_bf16x2(o4[0], o4[1]);
+            w.y = pack_bf16x2(o4[2], o4[3]);
+            *reinterpret_cast<uint2*>(o) = w;
+          } else {
+            *reinterpret_cast<uint32_t*>(o) = pack_bf16x2(o4[0], o4[1]);
+          }
+        }
+      } else {  // EPI_QKV: the tile is one head; lane covers features {2l, 2l+1} and their RoPE partners
+        const int head = n_blk;
+        const bool is_q = head < p.n_q_heads;
+        const bool is_k = !is_q && head < p.n_q_heads + p.n_kv_heads;
+        float x0[2] = {v[0] * rs, v[1] * rs}, x1[2] = {v[2] * rs, v[3] * rs};
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            x0[j] += p.bias[head * 128 + lane * 2 + j];
+            x1[j] += p.bias[head * 128 + 64 + lane * 2 + j];
+          }
+        }
+        const float* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+        if (nw) {
+          float ss = x0[0] * x0[0] + x0[1] * x0[1] + x1[0] * x1[0] + x1[1] * x1[1];
+          ss = warp_sum(ss);
+          const float inv_rms = rsqrtf(ss * (1.0f / 128.0f) + p.qk_eps);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            x0[j] *= inv_rms * nw[lane * 2 + j];
+            x1[j] *= inv_rms * nw[64 + lane * 2 + j];
+          }
+        }
+        int pos = p.positions[m];
+        if (pos < 0 || pos >= p.max_pos) pos = 0;
+        const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
+        __nv_bfloat16* dst = nullptr;
+        if (is_q) {
+          dst = p.q_out + (static_cast<long long>(m) * p.n_q_heads + head) * 128;
+        } else if (slot >= 0) {
+          const int page = slot / kPageTokens, off = slot % kPageTokens;
+          if (page >= p.num_pages) {
+            if (p.err && lane == 0) atomicCAS(p.err, 0, ERR_BAD_PAGE);
+          } else {
+            const int kvh = is_k ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads;
+            const long long b2 = ((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh);
+            dst = p.kv_cache + (b2 * kPageTokens + off) * 128;
+          }
+        }
+        if (dst) {
+          float a[2], b[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            if (is_q || is_k) {
+              const float cs = p.cos_table[static_cast<long long>(pos) * 64 + lane * 2 + j];
+              const float sn = p.sin_table[static_cast<long long>(pos) * 64 + lane * 2 + j];
+              a[j] = x0[j] * cs - x1[j] * sn;
+              b[j] = x1[j] * cs + x0[j] * sn;
+            } else {
+              a[j] = x0[j];
+              b[j] = x1[j];
+            }
+          }
+          *reinterpret_cast<uint32_t*>(dst + lane * 2) = pack_bf16x2(a[0], a[1]);
+          *reinterpret_cast<uint32_t*>(dst + 64 + lane * 2) = pack_bf16x2(b[0], b[1]);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, int MT, int EPI, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, MT>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kABytes = kBM * kTileKBytes;
   constexpr int kStageBytes = Cfg::kStageBytes;
   constexpr int kElemsPerKB = FP8 ? 128 : 64;
+  constexpr int kAcc = Cfg::kAccStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -123,7 +388,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m * p.num_n;
+  const int splits = p.splits;
+  const int num_items = p.num_m * p.num_n * splits;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -151,26 +417,39 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
 
+  // work item -> (k split, m super tile, n tile); the splits of one output tile are adjacent so
+  // they run at the same time and the reduction does not wait long
+  auto decode_item = [&](int t, int& ks, int& m_sup, int& n_blk, int& kb0, int& kb1) {
+    ks = t % splits;
+    const int r = t / splits;
+    m_sup = r % p.num_m;
+    n_blk = r / p.num_m;
+    kb0 = static_cast<int>(static_cast<long long>(ks) * p.num_kb / splits);
+    kb1 = static_cast<int>(static_cast<long long>(ks + 1) * p.num_kb / splits);
+  };
+
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m_blk = t % p.num_m;
-        const int n_blk = t / p.num_m;
+      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
+        int ks, m_sup, n_blk, kb0, kb1;
+        decode_item(t, ks, m_sup, n_blk, kb0, kb1);
         int b_row = n_blk * BN;
-        if (p.mblk_group) b_row += p.mblk_group[m_blk] * p.group_rows;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (p.mblk_group) b_row += p.mblk_group[m_sup * MT] * p.group_rows;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_SMEM_EMPTY)) {
             ok = false;
             break;
           }
           uint8_t* sa = tiles + stage * kStageBytes;
-          uint8_t* sb = sa + kABytes;
+          uint8_t* sb = sa + MT * kABytes;
           mbar_expect_tx(&full_bar[stage], kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * kElemsPerKB, m_blk * kBM);
+#pragma unroll
+          for (int i = 0; i < MT; ++i)
+            tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
           tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
           if (++stage == kStages) {
             stage = 0;
@@ -188,30 +467,36 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x, ++it) {
+        int ks, m_sup, n_blk, kb0, kb1;
+        decode_item(t, ks, m_sup, n_blk, kb0, kb1);
+        const int acc = it % kAcc;
+        const uint32_t acc_phase = (it / kAcc) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        const uint32_t d_tmem = tmem_base + acc * (MT * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
-          const uint64_t a_desc = umma_desc_sw128(sa);
-          const uint64_t b_desc = umma_desc_sw128(sa + kABytes);
+          const uint64_t b_desc = umma_desc_sw128(sa + MT * kABytes);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {  // 4 x 32-byte K slices per 128-byte swizzle row
-            if (FP8)
-              umma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
-            else
-              umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+          for (int i = 0; i < MT; ++i) {
+            const uint64_t a_desc = umma_desc_sw128(sa + i * kABytes);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // 4 x 32-byte K slices per 128-byte swizzle row
+              const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+              if (FP8)
+                umma_f8f6f4(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
+              else
+                umma_f16(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
+            }
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == kStages) {
@@ -228,11 +513,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-      const int m_blk = t % p.num_m;
-      const int n_blk = t / p.num_m;
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+    for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x, ++it) {
+      int ks, m_sup, n_blk, kb0, kb1;
+      decode_item(t, ks, m_sup, n_blk, kb0, kb1);
+      const int acc = it % kAcc;
+      const uint32_t acc_phase = (it / kAcc) & 1;
       // warp-uniform decision: tcgen05.ld below is warp-collective
       const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, ERR_TIMEOUT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) {
@@ -240,167 +525,199 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
-      const int m = m_blk * kBM + q * 32 + lane;
-      const bool row_ok = m < p.M;
-      const int mm = row_ok ? m : (p.M - 1);
-      float rs = row_scale_of(p, mm);
-      if (p.a_scale) rs *= p.a_scale[mm];
+      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * BN);
 
-      if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
-        float ss = 0.f;
+      // ---- split-K phase 1: dump this CTA's fp32 partial tile; the fused epilogue runs in phase 2 ----
+      bool finisher = true;
+      if (splits > 1) {
+        finisher = false;
+        const long long n_pad = static_cast<long long>(p.num_n) * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          const int n0 = n_blk * BN + c * 32;
-          if (n0 >= p.N) continue;
-          float v[32];
+        for (int i = 0; i < MT; ++i) {
+          const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
+          float* dst = p.sk_scratch + (static_cast<long long>(ks) * p.M + m) * n_pad + static_cast<long long>(n_blk) * BN;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr0 + i * BN + c * 32, r);
+            tmem_ld_wait();
+            if (m < p.M) {
+              float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rs;
-          if (p.b_scale) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= p.b_scale[n0 + j];
+              for (int j = 0; j < 8; ++j)
+                __stcg(d4 + j, make_float4(__uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]),
+                                           __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3])));
+            }
           }
-          if (p.bias) {
+        }
+      }
+
+      if (finisher) {
+#pragma unroll 1
+        for (int i = 0; i < MT; ++i) {
+          const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
+          const bool row_ok = m < p.M;
+          const int mm = row_ok ? m : (p.M - 1);
+          float rs = row_scale_of(p, mm);
+          if (p.a_scale) rs *= p.a_scale[mm];
+          AccReader rd;
+          rd.taddr = taddr0 + i * BN;
+
+          if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              float v[32];
+              rd.load(c * 32, v);
+              const int n0 = n_blk * BN + c * 32;
+              if (n0 >= p.N) continue;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += p.bias[n0 + j];
-          }
-          if constexpr (EPI == EPI_RESIDUAL) {
-            if (row_ok) {
-              const uint4* r4 = reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+              for (int j = 0; j < 32; ++j) v[j] *= rs;
+              if (p.b_scale) {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 u = r4[i];
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+                for (int j = 0; j < 32; ++j) v[j] *= p.b_scale[n0 + j];
+              }
+              if (p.bias) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = __bfloat1622float2(h[e]);
-                  v[i * 8 + e * 2] += f.x;
-                  v[i * 8 + e * 2 + 1] += f.y;
+                for (int j = 0; j < 32; ++j) v[j] += p.bias[n0 + j];
+              }
+              if constexpr (EPI == EPI_RESIDUAL) {
+                if (row_ok) {
+                  const uint4* r4 =
+                      reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+#pragma unroll
+                  for (int ii = 0; ii < 4; ++ii) {
+                    uint4 u = r4[ii];
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      float2 f = __bfloat1622float2(h[e]);
+                      v[ii * 8 + e * 2] += f.x;
+                      v[ii * 8 + e * 2 + 1] += f.y;
+                    }
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  v[j] = bf16_round(v[j]);
+                  ss += v[j] * v[j];
+                }
+              }
+              if (row_ok) {
+                if (p.out_f32) {
+                  float4* o4 =
+                      reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<long long>(m) * p.ldo + n0);
+#pragma unroll
+                  for (int ii = 0; ii < 8; ++ii)
+                    o4[ii] = make_float4(v[ii * 4], v[ii * 4 + 1], v[ii * 4 + 2], v[ii * 4 + 3]);
+                } else {
+                  store_bf16x32(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0, v);
                 }
               }
             }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              v[j] = bf16_round(v[j]);
-              ss += v[j] * v[j];
+            if constexpr (EPI == EPI_RESIDUAL) {
+              if (p.row_ss_out && row_ok) p.row_ss_out[static_cast<long long>(m) * p.num_n + n_blk] = ss;
             }
-          }
-          if (row_ok) {
-            if (p.out_f32) {
-              float4* o4 = reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<long long>(m) * p.ldo + n0);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o4[i] = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
-            } else {
-              store_bf16x32(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0, v);
-            }
-          }
-        }
-        if constexpr (EPI == EPI_RESIDUAL) {
-          if (p.row_ss_out && row_ok) p.row_ss_out[static_cast<long long>(m) * p.num_n + n_blk] = ss;
-        }
-      } else if constexpr (EPI == EPI_GLU) {
-        // tile columns [0, BN/2) hold gate rows, [BN/2, BN) the matching up rows
-        constexpr int kHalf = BN / 2;
+          } else if constexpr (EPI == EPI_GLU) {
+            // tile columns [0, BN/2) hold gate rows, [BN/2, BN) the matching up rows
+            constexpr int kHalf = BN / 2;
 #pragma unroll 1
-        for (int c = 0; c < kHalf / 32; ++c) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c * 32, g);
-          tmem_ld_32x32(taddr + kHalf + c * 32, u);
-          tmem_ld_wait();
-          const int n0 = n_blk * kHalf + c * 32;  // output column
-          if (n0 >= p.N / 2) continue;
-          float v[32];
+            for (int c = 0; c < kHalf / 32; ++c) {
+              float g[32], u[32];
+              rd.load(c * 32, g);
+              rd.load(kHalf + c * 32, u);
+              const int n0 = n_blk * kHalf + c * 32;  // output column
+              if (n0 >= p.N / 2) continue;
+              float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float gv = __uint_as_float(g[j]) * rs;
-            float uv = __uint_as_float(u[j]) * rs;
-            if (p.b_scale) {
-              gv *= p.b_scale[n_blk * BN + c * 32 + j];
-              uv *= p.b_scale[n_blk * BN + kHalf + c * 32 + j];
+              for (int j = 0; j < 32; ++j) {
+                float gv = g[j] * rs;
+                float uv = u[j] * rs;
+                if (p.b_scale) {
+                  gv *= p.b_scale[n_blk * BN + c * 32 + j];
+                  uv *= p.b_scale[n_blk * BN + kHalf + c * 32 + j];
+                }
+                v[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+              }
+              if (row_ok)
+                store_bf16x32(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0, v);
             }
-            v[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
-          }
-          if (row_ok) store_bf16x32(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0, v);
-        }
-      } else {  // EPI_QKV, BN == 128 == head_dim: this tile is exactly one head
-        static_assert(EPI != EPI_QKV || BN == 128, "QKV epilogue needs BN == head_dim == 128");
-        const int head = n_blk;
-        const bool is_q = head < p.n_q_heads;
-        const bool is_k = !is_q && head < p.n_q_heads + p.n_kv_heads;
-        const float* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
-        float inv_rms = 1.f;
-        if (nw) {  // per-head RMSNorm over the 128 features of this row
-          float ss = 0.f;
+          } else {  // EPI_QKV, BN == 128 == head_dim: this tile is exactly one head
+            static_assert(EPI != EPI_QKV || BN == 128, "QKV epilogue needs BN == head_dim == 128");
+            const int head = n_blk;
+            const bool is_q = head < p.n_q_heads;
+            const bool is_k = !is_q && head < p.n_q_heads + p.n_kv_heads;
+            const float* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+            float inv_rms = 1.f;
+            if (nw) {  // per-head RMSNorm over the 128 features of this row
+              float ss = 0.f;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
+              for (int c = 0; c < 4; ++c) {
+                float v[32];
+                rd.load(c * 32, v);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = __uint_as_float(r[j]) * rs;
-              if (p.bias) x += p.bias[head * 128 + c * 32 + j];
-              ss += x * x;
+                for (int j = 0; j < 32; ++j) {
+                  float x = v[j] * rs;
+                  if (p.bias) x += p.bias[head * 128 + c * 32 + j];
+                  ss += x * x;
+                }
+              }
+              inv_rms = rsqrtf(ss * (1.0f / 128.0f) + p.qk_eps);
             }
-          }
-          inv_rms = rsqrtf(ss * (1.0f / 128.0f) + p.qk_eps);
-        }
-        int pos = 0, slot = -1;
-        if (row_ok) {
-          pos = p.positions[m];
-          slot = p.slot_mapping ? p.slot_mapping[m] : -1;
-          if (pos < 0 || pos >= p.max_pos) pos = 0;
-        }
-        __nv_bfloat16* dst = nullptr;
-        if (row_ok) {
-          if (is_q) {
-            dst = p.q_out + (static_cast<long long>(m) * p.n_q_heads + head) * 128;
-          } else if (slot >= 0) {
-            const int page = slot / kPageTokens, off = slot % kPageTokens;
-            if (page >= p.num_pages) {
-              if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
-            } else {
-              const int kvh = is_k ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads;
-              const long long base = ((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh);
-              dst = p.kv_cache + (base * kPageTokens + off) * 128;
+            int pos = 0, slot = -1;
+            if (row_ok) {
+              pos = p.positions[m];
+              slot = p.slot_mapping ? p.slot_mapping[m] : -1;
+              if (pos < 0 || pos >= p.max_pos) pos = 0;
             }
-          }
-        }
+            __nv_bfloat16* dst = nullptr;
+            if (row_ok) {
+              if (is_q) {
+                dst = p.q_out + (static_cast<long long>(m) * p.n_q_heads + head) * 128;
+              } else if (slot >= 0) {
+                const int page = slot / kPageTokens, off = slot % kPageTokens;
+                if (page >= p.num_pages) {
+                  if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
+                } else {
+                  const int kvh = is_k ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads;
+                  const long long base = ((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh);
+                  dst = p.kv_cache + (base * kPageTokens + off) * 128;
+                }
+              }
+            }
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {  // columns [32c, 32c+32) pair with [64+32c, 64+32c+32)
-          uint32_t lo[32], hi[32];
-          tmem_ld_32x32(taddr + c * 32, lo);
-          tmem_ld_32x32(taddr + 64 + c * 32, hi);
-          tmem_ld_wait();
-          float a[32], b[32];
+            for (int c = 0; c < 2; ++c) {  // columns [32c, 32c+32) pair with [64+32c, 64+32c+32)
+              float lo[32], hi[32];
+              rd.load(c * 32, lo);
+              rd.load(64 + c * 32, hi);
+              float a[32], b[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x0 = __uint_as_float(lo[j]) * rs;
-            float x1 = __uint_as_float(hi[j]) * rs;
-            if (p.bias) {
-              x0 += p.bias[head * 128 + c * 32 + j];
-              x1 += p.bias[head * 128 + 64 + c * 32 + j];
+              for (int j = 0; j < 32; ++j) {
+                float x0 = lo[j] * rs;
+                float x1 = hi[j] * rs;
+                if (p.bias) {
+                  x0 += p.bias[head * 128 + c * 32 + j];
+                  x1 += p.bias[head * 128 + 64 + c * 32 + j];
+                }
+                if (nw) {
+                  x0 *= inv_rms * nw[c * 32 + j];
+                  x1 *= inv_rms * nw[64 + c * 32 + j];
+                }
+                if (is_q || is_k) {
+                  const float cs = p.cos_table[static_cast<long long>(pos) * 64 + c * 32 + j];
+                  const float sn = p.sin_table[static_cast<long long>(pos) * 64 + c * 32 + j];
+                  a[j] = x0 * cs - x1 * sn;
+                  b[j] = x1 * cs + x0 * sn;
+                } else {
+                  a[j] = x0;
+                  b[j] = x1;
+                }
+              }
+              if (dst) {
+                store_bf16x32(dst + c * 32, a);
+                store_bf16x32(dst + 64 + c * 32, b);
+              }
             }
-            if (nw) {
-              x0 *= inv_rms * nw[c * 32 + j];
-              x1 *= inv_rms * nw[64 + c * 32 + j];
-            }
-            if (is_q || is_k) {
-              const float cs = p.cos_table[static_cast<long long>(pos) * 64 + c * 32 + j];
-              const float sn = p.sin_table[static_cast<long long>(pos) * 64 + c * 32 + j];
-              a[j] = x0 * cs - x1 * sn;
-              b[j] = x1 * cs + x0 * sn;
-            } else {
-              a[j] = x0;
-              b[j] = x1;
-            }
-          }
-          if (dst) {
-            store_bf16x32(dst + c * 32, a);
-            store_bf16x32(dst + 64 + c * 32, b);
           }
         }
       }
@@ -415,18 +732,61 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+
+  if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
+    if (splits > 1) {
+      // every partial of every CTA must be visible before anyone reduces
+      if (grid_barrier(p.sk_barrier, gridDim.x, p.err)) splitk_reduce_phase<BN, EPI>(p);
+    }
+  }
 }
 
-template <int BN, int EPI, bool FP8>
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct SplitKWorkspace {
+  float* scratch = nullptr;
+  long long scratch_floats = 0;
+  unsigned int* barrier = nullptr;
+};
+static SplitKWorkspace g_splitk[64];
+
+// Pick the number of K splits with a small cost model (microseconds): one SM pulls about 100 GB/s into
+// shared memory, work items run in waves of `sms`, a split costs the dump of its partial tile, and the
+// reduce phase re-reads all partials at a few TB/s after one grid barrier.
+static int choose_splits(int tiles, int num_kb, int stage_bytes, long long tile_floats, long long out_floats, int sms,
+                         long long scratch_floats) {
+  if (tiles >= 2 * sms || num_kb < 4) return 1;
+  double best = 1e30;
+  int best_s = 1;
+  for (int s = 1; s <= kMaxSplits && s * 2 <= num_kb; ++s) {
+    if (s > 1 && s * out_floats > scratch_floats) break;
+    const int items = tiles * s;
+    const int waves = (items + sms - 1) / sms;
+    const double kb = (num_kb + s - 1) / s;
+    double t_item = kb * stage_bytes / 100e3 + 2.0;
+    double total;
+    if (s == 1) {
+      total = waves * (t_item + tile_floats * 4 / 200e3);
+    } else {
+      t_item += tile_floats * 4 / 100e3;
+      total = waves * t_item + 2.0 + (double)s * out_floats * 4 / 3.5e6 + 1.5;
+    }
+    if (total < best * 0.95) {  // prefer fewer splits unless clearly better
+      best = total;
+      best_s = s;
+    }
+  }
+  return best_s;
+}
+
+template <int BN, int MT, int EPI, bool FP8>
 static int launch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows, GemmParams p,
-                       cudaStream_t stream, int max_ctas) {
-  using Cfg = GemmCfg<BN>;
+                       cudaStream_t stream, int max_ctas, int force_splits) {
+  using Cfg = GemmCfg<BN, MT>;
   constexpr int kElemsPerKB = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  p.num_m = (p.M + kBM - 1) / kBM;
-  p.num_n = (p.N + BN - 1) / BN;
-  p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) {
     set_last_error("gemm: empty problem M=%d N=%d K=%d", p.M, p.N, p.K);
     return -1;
@@ -435,11 +795,14 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     set_last_error("gemm: N=%d must be a multiple of 32 (pad the weight at load time)", p.N);
     return -1;
   }
+  p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
+  p.num_n = (p.N + BN - 1) / BN;
+  p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
   CUtensorMap ta, tb;
   if (make_tmap_2d(&ta, A, dt, esz, uint64_t(p.M), uint64_t(p.K), uint64_t(lda), kBM, kElemsPerKB)) return -1;
   if (make_tmap_2d(&tb, B, dt, esz, uint64_t(b_rows), uint64_t(p.K), uint64_t(ldb), BN, kElemsPerKB)) return -1;
   static bool attr_set = false;
-  auto kern = gemm_tn_kernel<BN, EPI, FP8>;
+  auto kern = gemm_tn_kernel<BN, MT, EPI, FP8>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) {
@@ -448,14 +811,32 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     }
     attr_set = true;
   }
+  int dev = 0;
+  cudaGetDevice(&dev);
   int sms = max_ctas;
-  if (sms <= 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  if (sms <= 0) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = p.num_m * p.num_n;
-  const int grid = tiles < sms ? tiles : sms;
+  const SplitKWorkspace& ws = g_splitk[dev & 63];
+  const long long tile_floats = static_cast<long long>(MT) * kBM * BN;
+  const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
+  int splits = 1;
+  if (p.mblk_group || BN % 128 != 0) force_splits = 1;  // grouped GEMMs have plenty of tiles
+  if (force_splits > 0)
+    splits = force_splits;
+  else if (ws.scratch)
+    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats);
+  if (splits > 1) {
+    if (!ws.scratch || splits * out_floats > ws.scratch_floats || splits > p.num_kb || splits > kMaxSplits) {
+      set_last_error("gemm: split-K=%d needs %lld scratch floats (have %lld), K blocks %d", splits,
+                     splits * out_floats, ws.scratch_floats, p.num_kb);
+      return -1;
+    }
+  }
+  p.splits = splits;
+  p.sk_scratch = ws.scratch;
+  p.sk_barrier = ws.barrier;
+  const int items = tiles * splits;
+  const int grid = items < sms ? items : sms;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -463,6 +844,30 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     return -1;
   }
   return 0;
+}
+
+// Dispatch on (tile width, rows per CTA). Small M uses 256-row CTA tiles so a weight tile is pulled
+// into shared memory once for the whole batch; large M keeps 128 x 256 tiles with a double-buffered
+// accumulator so the epilogue overlaps the next main loop.
+template <int EPI, bool FP8>
+static int dispatch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
+                         const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
+  const bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr;
+  if constexpr (EPI == EPI_GLU) {
+    // 192-wide tiles: 128 tiles for a 24576-row gate/up weight fill one wave of 148 SMs without splitting
+    if (bn == 192) {
+      if (two_rows) return launch_gemm<192, 2, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, 1);
+      return launch_gemm<192, 1, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, 1);
+    }
+  }
+  if constexpr (EPI != EPI_QKV) {
+    if (bn == 256) {
+      if (two_rows) return launch_gemm<256, 2, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+      return launch_gemm<256, 1, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+    }
+  }
+  if (two_rows) return launch_gemm<128, 2, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+  return launch_gemm<128, 1, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
 }
 
 }  // namespace gllm
@@ -475,30 +880,50 @@ extern "C" int* gllm_error_word();
 // C entry points. All pointers are device pointers; `stream` is a cudaStream_t.
 // ---------------------------------------------------------------------------------------------
 
+// Registers the split-K scratch of the current device (caller-owned memory: `scratch_floats` fp32 for
+// the partial sums and at least two zeroed int32 for the grid barrier). All GEMMs of a device share it,
+// so GEMMs that may use split-K must not overlap on different streams, and a split-K launch needs every
+// CTA of its grid resident at once (the grid never exceeds the SM count and uses one CTA per SM).
+// Passing null pointers disables split-K.
+GLLM_API int gllm_gemm_set_splitk_workspace(float* scratch, long long scratch_floats, int* counters,
+                                            int num_counters) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  SplitKWorkspace& ws = g_splitk[dev & 63];
+  if (scratch && (!counters || num_counters < 2)) {
+    set_last_error("split-K workspace needs at least two zeroed counters for the grid barrier");
+    return -1;
+  }
+  ws.scratch = scratch;
+  ws.scratch_floats = scratch ? scratch_floats : 0;
+  ws.barrier = reinterpret_cast<unsigned int*>(counters);
+  return 0;
+}
+
 // out[M,N] = rowscale(A) · Bᵀ (+bias).  bn: 128 or 256.  row_ss_in may be null.
 GLLM_API int gllm_gemm_bf16(const void* A, long long lda, const void* B, long long ldb, void* out, long long ldo,
                             int M, int N, int K, int out_f32, const float* bias, const float* row_ss_in,
-                            int ss_in_parts, float norm_inv_dim, float norm_eps, int bn, void* stream, int max_ctas) {
+                            int ss_in_parts, float norm_inv_dim, float norm_eps, int bn, void* stream, int max_ctas,
+                            int force_splits) {
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32; p.bias = bias;
   p.row_ss_in = row_ss_in; p.ss_in_parts = ss_in_parts; p.norm_inv_dim = norm_inv_dim; p.norm_eps = norm_eps;
   p.err = gllm_error_word();
-  if (bn == 256) return launch_gemm<256, EPI_STORE, false>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
-  return launch_gemm<128, EPI_STORE, false>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
 // out[M,N] = A · Bᵀ (+bias) + residual ; row_ss_out[M, ceil(N/bn)] receives per-tile sums of squares.
 GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B, long long ldb, void* out,
                                      long long ldo, const void* residual, long long ldr, float* row_ss_out, int M,
-                                     int N, int K, const float* bias, int bn, void* stream, int max_ctas) {
+                                     int N, int K, const float* bias, int bn, void* stream, int max_ctas,
+                                     int force_splits) {
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.bias = bias;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.row_ss_out = row_ss_out;
   p.err = gllm_error_word();
-  if (bn == 256) return launch_gemm<256, EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
-  return launch_gemm<128, EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
 // out[M,N/2] = act(rowscale*gate) * rowscale*up ; B is the tile-interleaved gate/up weight [N,K]:
@@ -506,7 +931,7 @@ GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B
 GLLM_API int gllm_gemm_bf16_glu(const void* A, long long lda, const void* B, long long ldb, void* out, long long ldo,
                                 int M, int N, int K, int act, const float* row_ss_in, int ss_in_parts,
                                 float norm_inv_dim, float norm_eps, int bn, const int* mblk_group, int num_groups,
-                                void* stream, int max_ctas) {
+                                void* stream, int max_ctas, int force_splits) {
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.glu_act = act;
@@ -514,8 +939,7 @@ GLLM_API int gllm_gemm_bf16_glu(const void* A, long long lda, const void* B, lon
   p.mblk_group = mblk_group; p.group_rows = N;
   p.err = gllm_error_word();
   const long long b_rows = mblk_group ? static_cast<long long>(num_groups) * N : N;  // groups are stacked
-  if (bn == 256) return launch_gemm<256, EPI_GLU, false>(A, lda, B, ldb, b_rows, p, (cudaStream_t)stream, max_ctas);
-  return launch_gemm<128, EPI_GLU, false>(A, lda, B, ldb, b_rows, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_GLU, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
 // Grouped plain GEMM (MoE down projection): m-block i multiplies group mblk_group[i]'s [N,K] weight.
@@ -528,8 +952,7 @@ GLLM_API int gllm_gemm_bf16_grouped(const void* A, long long lda, const void* B,
   p.mblk_group = mblk_group; p.group_rows = N;
   p.err = gllm_error_word();
   const long long b_rows = static_cast<long long>(num_groups) * N;
-  if (bn == 256) return launch_gemm<256, EPI_STORE, false>(A, lda, B, ldb, b_rows, p, (cudaStream_t)stream, max_ctas);
-  return launch_gemm<128, EPI_STORE, false>(A, lda, B, ldb, b_rows, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, 1);
 }
 
 // Fused QKV projection for head_dim 128: rowscale -> per-head RMSNorm (optional) -> RoPE -> q buffer and
@@ -539,7 +962,7 @@ GLLM_API int gllm_gemm_bf16_qkv(const void* A, long long lda, const void* B, lon
                                 const int* slot_mapping, const int* positions, const float* cos_table,
                                 const float* sin_table, int max_pos, const float* q_norm_w, const float* k_norm_w,
                                 float qk_eps, const float* row_ss_in, int ss_in_parts, float norm_inv_dim,
-                                float norm_eps, const float* bias, void* stream, int max_ctas) {
+                                float norm_eps, const float* bias, void* stream, int max_ctas, int force_splits) {
   GemmParams p = {};
   p.M = M; p.N = (n_q_heads + 2 * n_kv_heads) * 128; p.K = K;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
@@ -550,18 +973,17 @@ GLLM_API int gllm_gemm_bf16_qkv(const void* A, long long lda, const void* B, lon
   p.row_ss_in = row_ss_in; p.ss_in_parts = ss_in_parts; p.norm_inv_dim = norm_inv_dim; p.norm_eps = norm_eps;
   p.bias = bias;
   p.err = gllm_error_word();
-  return launch_gemm<128, EPI_QKV, false>(A, lda, B, ldb, p.N, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_QKV, false>(A, lda, B, ldb, p.N, p, 128, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
 // FP8 (e4m3) GEMM with per-row activation scale and per-column weight scale applied in the epilogue.
 GLLM_API int gllm_gemm_fp8(const void* A, long long lda, const void* B, long long ldb, void* out, long long ldo,
                            int M, int N, int K, int out_f32, const float* a_scale, const float* b_scale, int bn,
-                           void* stream, int max_ctas) {
+                           void* stream, int max_ctas, int force_splits) {
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
   p.a_scale = a_scale; p.b_scale = b_scale;
   p.err = gllm_error_word();
-  if (bn == 256) return launch_gemm<256, EPI_STORE, true>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
-  return launch_gemm<128, EPI_STORE, true>(A, lda, B, ldb, N, p, (cudaStream_t)stream, max_ctas);
+  return dispatch_gemm<EPI_STORE, true>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }

@@ -87,9 +87,17 @@ class LLMEngine:
         self.d_out = torch.zeros(self.ms, dtype=torch.int32, device=dev)
         self.d_offsets = torch.zeros(self.ms, dtype=torch.int64, device=dev)
         self.slot_params = np.zeros((self.ms, 4), dtype=np.float32)
-        max_splits = max(1, (self.max_blocks + ec.pages_per_split - 1) // ec.pages_per_split)
+        # Split the KV range of a sequence across CTAs only when (sequences x kv heads) alone cannot fill
+        # the machine: an unsplit flash-decode CTA streams its pages at full speed, splits add a merge.
+        want_splits = max(1, -(-4 * 148 // max(1, self.ms * model.n_kv_local)))
+        pps = ec.pages_per_split if want_splits > 1 else 1 << 20
+        if want_splits > 1:
+            pps = max(8, -(-self.max_blocks // want_splits))
+        max_splits = max(1, -(-self.max_blocks // pps))
         self.decode_ws = (ops.DecodeWorkspace(self.ms, model.n_q_local, model.n_kv_local, max_splits, dev)
                           if cuda and self.mc.head_dim == 128 else None)
+        if self.decode_ws is not None:
+            self.decode_ws.pages_per_split = pps
         model.workspace(max(ec.max_batch_tokens, self.ms))
         self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
         self.reqs: Dict[int, _ReqState] = {}

@@ -47,7 +47,7 @@ class Workspace:
         inter = max(model.inter_local, 1)
         self.act = torch.zeros((T, inter), dtype=dt, device=dev)
         self.gu = None if model.fused else torch.zeros((T, 2 * inter), dtype=dt, device=dev)
-        self.parts = max(1, (H + 127) // 128)
+        self.parts = max(1, (H + model.res_bn - 1) // model.res_bn)
         self.ss0 = torch.zeros((T, 1), dtype=torch.float32, device=dev)
         self.ss_a = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
         self.ss_b = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
@@ -75,6 +75,7 @@ class DecoderModel:
         self.max_positions = max_positions or cfg.max_position_embeddings
         self.cos, self.sin = rope.build_tables(cfg, self.max_positions, self.device)
         self.act_id = L.ACT_IDS.get(cfg.hidden_act, 0)
+        self.res_bn = 256 if cfg.hidden_size % 256 == 0 else 128  # tile width of the residual GEMMs
         self.scale = cfg.attention_scale()
 
         to = lambda t: t.to(self.device, dtype if t.is_floating_point() and t.dtype != torch.float32 else None)
@@ -98,7 +99,7 @@ class DecoderModel:
             head = head[a:b].to(self.device, dtype)
             if self.fused:
                 head = _fold(head, self.final_norm, cfg.norm_one_plus_w)
-            self.lm_head = L.pad_rows(head, 128).contiguous()
+            self.lm_head = L.pad_rows(head, 256).contiguous()
         self._ws: Optional[Workspace] = None
 
     # ------------------------------------------------------------------------------------------
@@ -119,7 +120,8 @@ class DecoderModel:
         window = self.cfg.layer_window(layer)
         if batch.is_decode:
             return ops.paged_decode(q, kv, batch.block_tables, batch.ctx_lens, n_q=self.n_q_local, n_kv=self.n_kv_local,
-                                    scale=self.scale, out=out, workspace=decode_ws, window=window)
+                                    scale=self.scale, out=out, workspace=decode_ws, window=window,
+                                    pages_per_split=getattr(decode_ws, "pages_per_split", 32))
         return ops.paged_prefill(q, kv, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_lens,
                                  max_q_len=batch.max_q_len, n_q=self.n_q_local, n_kv=self.n_kv_local, scale=self.scale,
                                  out=out, causal=batch.causal and self.cfg.causal, window=window)
@@ -127,7 +129,7 @@ class DecoderModel:
     def _row_parallel(self, a, w, x, ss_out, T):
         """x <- a @ w.T + x, row statistics into ss_out. With TP the partial sums are all-reduced."""
         if self.tp_size == 1:
-            ops.gemm_residual(a, w, x, out=x, row_ss_out=ss_out, bn=128)
+            ops.gemm_residual(a, w, x, out=x, row_ss_out=ss_out, bn=self.res_bn)
             return
         self.tp.gemm_allreduce_residual(a, w, x, ss_out, self._ws.partial[:T])
 
@@ -190,11 +192,11 @@ class DecoderModel:
         if self.fused:
             xr, sr = (x, ss_in) if rows is None else (x.index_select(0, rows), ss_in.index_select(0, rows))
             logits = ops.gemm(xr, self.lm_head, out_dtype=torch.float32, row_ss=sr, norm_dim=H, eps=c.rms_norm_eps,
-                              bn=128)
+                              bn=256)
         else:
             xr = x if rows is None else x.index_select(0, rows)
             hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
-            logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=128)
+            logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256)
         if c.logit_softcap:
             logits = torch.tanh(logits / c.logit_softcap) * c.logit_softcap
         return logits

@@ -221,14 +221,23 @@ def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: 
     return wqkv.contiguous(), bias, qn, kn, wo.contiguous(), input_norm.contiguous(), q.shape[0] // D, k.shape[0] // D
 
 
+def glu_tile_width(inter: int, sms: int = 148) -> int:
+    """Tile width of the packed gate/up weight. 192 when that yields one nearly full wave of CTAs
+    (e.g. 128 tiles for intermediate 12288), else the widest power-of-two tile that divides."""
+    if inter % 96 == 0 and 0.8 * sms <= (2 * inter) // 192 <= sms:
+        return 192
+    return 256 if inter % 128 == 0 else 128
+
+
 def pack_mlp(cfg: ModelConfig, src, prefix: str, rank: int, world: int, fused: bool, norm_w=None, bn=None):
     g = shard_tensor(prefix + "gate_proj", src.get(prefix + "gate_proj"), rank, world)
     u = shard_tensor(prefix + "up_proj", src.get(prefix + "up_proj"), rank, world)
     d = shard_tensor(prefix + "down_proj", src.get(prefix + "down_proj"), rank, world)
     inter = g.shape[0]
     if fused:
-        # 128-wide tiles (64 gate + 64 up rows) give more tiles per wave at decode batch sizes
-        bn = bn or (128 if inter % 64 == 0 else 256)
+        # 256-wide tiles (128 gate + 128 up rows): a weight tile pulled into shared memory once serves
+        # the most rows; split-K supplies the parallelism at decode batch sizes
+        bn = bn or glu_tile_width(inter)
         if norm_w is not None:
             g, u = _fold(g, norm_w, cfg.norm_one_plus_w), _fold(u, norm_w, cfg.norm_one_plus_w)
         return L.interleave_gate_up(g, u, bn), d.contiguous(), bn

@@ -23,12 +23,13 @@ _SIGNATURES = {
     "gllm_check_error": (I, []),
     "gllm_sm_count": (I, []),
     "gllm_kernels_abi_version": (I, []),
-    "gllm_gemm_bf16": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, I]),
-    "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I]),
-    "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I]),
+    "gllm_gemm_bf16": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, I, I]),
+    "gllm_gemm_set_splitk_workspace": (I, [P, L, P, I]),
+    "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I]),
+    "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I, I]),
     "gllm_gemm_bf16_grouped": (I, [P, L, P, L, P, L, I, I, I, P, I, I, P, I]),
-    "gllm_gemm_bf16_qkv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, P, I]),
-    "gllm_gemm_fp8": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, P, I]),
+    "gllm_gemm_bf16_qkv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, P, I, I]),
+    "gllm_gemm_fp8": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, P, I, I]),
     "gllm_decode_scratch_floats": (L, [I, I, I]),
     "gllm_paged_decode": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, P]),
     "gllm_paged_prefill": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, P]),
@@ -121,6 +122,26 @@ def raise_on_device_error(where: str = ""):
     code = device_error()
     if code != 0:
         raise RuntimeError(f"device kernel reported status {code} ({ERROR_NAMES.get(code, '?')}) {where}")
+
+
+_splitk_ws = {}
+
+
+def ensure_splitk_workspace(device, scratch_floats: int = 64 << 20, num_counters: int = 8192):
+    """Allocate (once per device) and register the scratch that split-K GEMMs reduce through.
+    It is shared by every GEMM on the device, so split-K GEMMs must run on one stream at a time."""
+    import torch
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx in _splitk_ws:
+        return _splitk_ws[idx]
+    with torch.cuda.device(idx):
+        scratch = torch.empty(scratch_floats, dtype=torch.float32, device=device)
+        counters = torch.zeros(num_counters, dtype=torch.int32, device=device)
+        rc = lib().gllm_gemm_set_splitk_workspace(scratch.data_ptr(), scratch_floats, counters.data_ptr(), num_counters)
+        if rc != 0:
+            raise RuntimeError("could not register the split-K workspace")
+    _splitk_ws[idx] = (scratch, counters)
+    return _splitk_ws[idx]
 
 
 def ptr(t):

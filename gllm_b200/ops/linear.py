@@ -65,7 +65,7 @@ def row_scale_ref(row_ss, norm_dim, eps):
 # plain GEMM (+ RMSNorm-as-row-scale prologue, + bias)
 # --------------------------------------------------------------------------------------------
 def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, norm_dim=0, eps=0.0,
-         bn=None, max_ctas=0):
+         bn=None, max_ctas=0, splits=0):
     """out[M,N] = rowscale(a) @ w.T (+ bias). ``row_ss`` [M, parts] are partial sums of squares of ``a``'s
     rows; when given, each output row is scaled by rsqrt(sum/norm_dim + eps) (the norm weight must
     already be folded into ``w``)."""
@@ -88,15 +88,17 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     bn = bn or _bn_for(N, M)
+    nv.ensure_splitk_workspace(a.device)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
     rc = nv.lib().gllm_gemm_bf16(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
                                  M, N, K, 1 if out.dtype == torch.float32 else 0, nv.ptr(bias), nv.ptr(row_ss),
-                                 parts, 1.0 / norm_dim if norm_dim else 0.0, eps, bn, nv.stream_ptr(), max_ctas)
+                                 parts, 1.0 / norm_dim if norm_dim else 0.0, eps, bn, nv.stream_ptr(), max_ctas,
+                                 splits)
     nv.check(rc, "gemm_bf16")
     return out
 
 
-def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=None, max_ctas=0):
+def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=None, max_ctas=0, splits=0):
     """out = a @ w.T (+bias) + residual (bf16). Returns (out, row_ss) where row_ss[M, ceil(N/bn)] holds the
     per-tile sums of squares of ``out``: the next layer's RMSNorm statistics."""
     M, K = a.shape
@@ -125,9 +127,11 @@ def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=No
     if row_ss_out is None:
         row_ss_out = torch.empty((M, parts), dtype=torch.float32, device=a.device)
     assert row_ss_out.shape[-1] == parts and row_ss_out.is_contiguous()
+    nv.ensure_splitk_workspace(a.device)
     rc = nv.lib().gllm_gemm_bf16_residual(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
                                           out.stride(0), residual.data_ptr(), residual.stride(0),
-                                          row_ss_out.data_ptr(), M, N, K, nv.ptr(bias), bn, nv.stream_ptr(), max_ctas)
+                                          row_ss_out.data_ptr(), M, N, K, nv.ptr(bias), bn, nv.stream_ptr(), max_ctas,
+                                          splits)
     nv.check(rc, "gemm_bf16_residual")
     return out, row_ss_out
 
@@ -142,7 +146,7 @@ def _act_ref(g, act):
 
 
 def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, bn=256, mblk_group=None,
-             num_groups=0, max_ctas=0):
+             num_groups=0, max_ctas=0, splits=0):
     """out[M, N/2] = act(rowscale*gate) * (rowscale*up) with gate/up packed by ``interleave_gate_up``.
     With ``mblk_group`` (int32 per 128-row block) the weight is a stack of per-expert matrices."""
     M, K = a.shape
@@ -170,10 +174,11 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
+    nv.ensure_splitk_workspace(a.device)
     rc = nv.lib().gllm_gemm_bf16_glu(a.data_ptr(), a.stride(0), w_packed.data_ptr(), w_packed.stride(0),
                                      out.data_ptr(), out.stride(0), M, N, K, act, nv.ptr(row_ss), parts,
                                      1.0 / norm_dim if norm_dim else 0.0, eps, bn, nv.ptr(mblk_group), num_groups,
-                                     nv.stream_ptr(), max_ctas)
+                                     nv.stream_ptr(), max_ctas, 1 if mblk_group is not None else splits)
     nv.check(rc, "gemm_bf16_glu")
     return out
 
@@ -237,7 +242,7 @@ def kv_write_ref(kv_cache, k, v, slot_mapping):
 
 
 def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, cos_t, sin_t, q_norm_w=None,
-             k_norm_w=None, qk_eps=1e-6, row_ss=None, norm_dim=0, eps=0.0, bias=None, max_ctas=0):
+             k_norm_w=None, qk_eps=1e-6, row_ss=None, norm_dim=0, eps=0.0, bias=None, max_ctas=0, splits=0):
     """Fused QKV projection for head_dim 128. ``w_qkv`` rows: q heads, k heads, v heads."""
     M, K = a.shape
     D = 128
@@ -254,12 +259,13 @@ def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, c
             kv_write_ref(kv_cache, k, v, slot_mapping)
         return q_out
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
+    nv.ensure_splitk_workspace(a.device)
     rc = nv.lib().gllm_gemm_bf16_qkv(a.data_ptr(), a.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), M, K, n_q, n_kv,
                                      q_out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0], nv.ptr(slot_mapping),
                                      positions.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), cos_t.shape[0],
                                      nv.ptr(q_norm_w), nv.ptr(k_norm_w), qk_eps, nv.ptr(row_ss), parts,
                                      1.0 / norm_dim if norm_dim else 0.0, eps, nv.ptr(bias), nv.stream_ptr(),
-                                     max_ctas)
+                                     max_ctas, splits)
     nv.check(rc, "gemm_bf16_qkv")
     return q_out
 
@@ -267,7 +273,7 @@ def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, c
 # --------------------------------------------------------------------------------------------
 # FP8 e4m3 GEMM with per-row / per-column scales
 # --------------------------------------------------------------------------------------------
-def gemm_fp8(a8, w8, a_scale, b_scale, *, out=None, out_dtype=torch.bfloat16, bn=None, max_ctas=0):
+def gemm_fp8(a8, w8, a_scale, b_scale, *, out=None, out_dtype=torch.bfloat16, bn=None, max_ctas=0, splits=0):
     M, K = a8.shape
     N = w8.shape[0]
     if not a8.is_cuda:
@@ -284,8 +290,9 @@ def gemm_fp8(a8, w8, a_scale, b_scale, *, out=None, out_dtype=torch.bfloat16, bn
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a8.device)
     bn = bn or _bn_for(N, M)
+    nv.ensure_splitk_workspace(a8.device)
     rc = nv.lib().gllm_gemm_fp8(a8.data_ptr(), a8.stride(0), w8.data_ptr(), w8.stride(0), out.data_ptr(),
                                 out.stride(0), M, N, K, 1 if out.dtype == torch.float32 else 0, nv.ptr(a_scale),
-                                nv.ptr(b_scale), bn, nv.stream_ptr(), max_ctas)
+                                nv.ptr(b_scale), bn, nv.stream_ptr(), max_ctas, splits)
     nv.check(rc, "gemm_fp8")
     return out

@@ -34,6 +34,23 @@ def test_gemm_plain(M, N, K, bn):
     _close(out, a.float() @ w.float().t())
 
 
+@pytest.mark.parametrize("M,N,K,bn,splits", [
+    (256, 4096, 4096, 256, 9), (256, 4096, 12288, 256, 16), (100, 512, 1024, 128, 4), (256, 6144, 4096, 128, 3),
+    (200, 768, 2048, 256, 2), (512, 1024, 1024, 256, 5), (256, 4096, 4096, 256, 0),
+])
+def test_gemm_split_k(M, N, K, bn, splits):
+    """Split-K with in-kernel ticket reduction: same answer as one pass, bit-identical across launches."""
+    torch.manual_seed(8)
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    out = ops.gemm(a, w, bn=bn, splits=splits).clone()
+    _close(out, a.float() @ w.float().t())
+    assert torch.equal(out, ops.gemm(a, w, bn=bn, splits=splits))
+    r = _rand(M, N)
+    o2, ss = ops.gemm_residual(a, w, r, bn=bn, splits=splits)
+    _close(o2, a.float() @ w.float().t() + r.float())
+    torch.testing.assert_close(ss.sum(-1), o2.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+
+
 def test_gemm_fp32_out_bias_rowscale():
     torch.manual_seed(1)
     M, N, K = 200, 512, 1024
@@ -56,13 +73,16 @@ def test_gemm_residual(M, N, K, bn):
     torch.testing.assert_close(ss.sum(-1), ss_ref, rtol=1e-3, atol=1e-3)
 
 
-@pytest.mark.parametrize("M,I,K,bn,act", [(256, 1024, 512, 256, 0), (100, 768, 2048, 128, 0), (64, 512, 256, 256, 1)])
-def test_gemm_glu(M, I, K, bn, act):
+@pytest.mark.parametrize("splits", [0, 1, 3])
+@pytest.mark.parametrize("M,I,K,bn,act", [(256, 1024, 512, 256, 0), (100, 768, 2048, 128, 0), (64, 512, 256, 256, 1),
+                                          (256, 12288, 4096, 256, 0), (256, 1536, 1024, 192, 0),
+                                          (100, 960, 512, 192, 1)])
+def test_gemm_glu(M, I, K, bn, act, splits):
     torch.manual_seed(3)
     a, g, u = _rand(M, K), _rand(I, K, scale=0.05), _rand(I, K, scale=0.05)
     ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
     wp = ops.interleave_gate_up(g, u, bn)
-    out = ops.gemm_glu(a, wp, act=act, row_ss=ss, norm_dim=K, eps=1e-5, bn=bn)
+    out = ops.gemm_glu(a, wp, act=act, row_ss=ss, norm_dim=K, eps=1e-5, bn=bn, splits=splits)
     rs = torch.rsqrt(ss / K + 1e-5)
     gv, uv = (a.float() @ g.float().t()) * rs, (a.float() @ u.float().t()) * rs
     actf = torch.nn.functional.silu if act == 0 else (lambda x: torch.nn.functional.gelu(x, approximate="tanh"))
@@ -84,11 +104,12 @@ def test_gemm_grouped_and_glu_grouped():
     _close(out2, ref2.to(DEV))
 
 
+@pytest.mark.parametrize("M,splits", [(150, 0), (150, 1), (256, 3), (64, 4), (700, 0)])
 @pytest.mark.parametrize("qk_norm", [True, False])
-def test_gemm_qkv_fused(qk_norm):
+def test_gemm_qkv_fused(qk_norm, M, splits):
     torch.manual_seed(5)
-    M, K, n_q, n_kv, D = 150, 1024, 8, 2, 128
-    pages, max_pos = 32, 512
+    K, n_q, n_kv, D = 1024, 8, 2, 128
+    pages, max_pos = 64, 512
     a = _rand(M, K)
     w = _rand((n_q + 2 * n_kv) * D, K, scale=0.05)
     ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
@@ -103,7 +124,8 @@ def test_gemm_qkv_fused(qk_norm):
     kv = torch.zeros(pages, 2, n_kv, 16, D, device=DEV, dtype=torch.bfloat16)
     q_out = torch.zeros(M, n_q * D, device=DEV, dtype=torch.bfloat16)
     ops.gemm_qkv(a, w, n_q=n_q, n_kv=n_kv, q_out=q_out, kv_cache=kv, slot_mapping=slots, positions=positions,
-                 cos_t=cos_t, sin_t=sin_t, q_norm_w=qn, k_norm_w=kn, qk_eps=1e-6, row_ss=ss, norm_dim=K, eps=1e-6)
+                 cos_t=cos_t, sin_t=sin_t, q_norm_w=qn, k_norm_w=kn, qk_eps=1e-6, row_ss=ss, norm_dim=K, eps=1e-6,
+                 splits=splits)
     acc = (a.float() @ w.float().t()) * torch.rsqrt(ss / K + 1e-6)
     q, k, v = L.qkv_post_ref(acc, n_q, n_kv, D, positions, cos_t, sin_t, qn, kn, 1e-6)
     _close(q_out, q.reshape(M, -1))
