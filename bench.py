@@ -214,7 +214,7 @@ def main():
     nv_calls0 = nv.CALLS[0]
     engine._decode_body(B) if args.no_graphs else None
     launches_per_step = (nv.CALLS[0] - nv_calls0) if args.no_graphs else engine.launches_per_graph.get(B, 0)
-    graph = engine.graphs.get(B)
+    graph = engine.graphs.get((B, True))
     run = (lambda: graph.replay()) if graph is not None else (lambda: engine._decode_body(B))
     for _ in range(3):
         run()

@@ -81,6 +81,17 @@ struct GemmParams {
   const float* q_norm_w;  // [128] or null
   const float* k_norm_w;  // [128] or null
   float qk_eps;
+  // fused all-reduce (row-parallel GEMM across `ar_world` GPUs). Partial tiles are added into the
+  // fp32 accumulation buffer of every rank: one multimem.red through NVSwitch when a multicast mapping
+  // exists, else one red per peer pointer. ar_world == 0 disables it.
+  int ar_world;
+  float* ar_mc_acc;                       // multicast address of the accumulation buffers, or null
+  float* ar_peer_acc[8];                  // unicast addresses (index = rank); [ar_rank] is local
+  unsigned long long* ar_mc_counter;      // multicast address of the arrival counter, or null
+  unsigned long long* ar_peer_counter[8];
+  unsigned long long* ar_state;           // local {expected arrivals, launch index}
+  int ar_rank;
+  long long ar_buf_floats;                // size of one accumulation buffer (two alternate per launch)
   int* err;
 };
 
@@ -129,6 +140,53 @@ struct AccReader {
   }
 };
 
+__device__ __forceinline__ void multimem_red_add_v4(float* mc, float a, float b, float c, float d) {
+  asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* ptr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Cross-GPU arrival barrier of the fused all-reduce: every CTA of every rank adds one to the arrival
+// counter of every rank (one multimem.red, or one red per peer) after a system-scope fence, then waits
+// until its own rank's counter has reached `target`. Bounded; returns false on timeout.
+__device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long long target) {
+  __shared__ int ok_flag;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    if (p.ar_mc_counter) {
+      asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_mc_counter), "l"(1ull) : "memory");
+    } else {
+      for (int r = 0; r < p.ar_world; ++r)
+        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_peer_counter[r]), "l"(1ull) : "memory");
+    }
+    const unsigned long long* mine = p.ar_peer_counter[p.ar_rank];
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned int spins = 0;
+    while (ld_acquire_sys_u64(mine) < target) {
+      if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > kPeerWaitLimitNs) {
+        if (p.err) atomicCAS(p.err, 0, ERR_TIMEOUT_PEER);
+        ok = 0;
+        break;
+      }
+    }
+    ok_flag = ok;
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
 // Sense-reversing grid barrier over {count, generation}; bounded. Returns false on timeout.
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num_ctas, int* err) {
   __shared__ int ok_flag;
@@ -167,7 +225,7 @@ __device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterp
 // is latency bound: few threads, L2 round trips), the adds happen in split order so the result does
 // not depend on timing, then the fused epilogue of EPI is applied.
 template <int BN, int EPI>
-__device__ void splitk_reduce_phase(const GemmParams& p) {
+__device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int nsplits, bool zero_after) {
   constexpr bool kGlu = (EPI == EPI_GLU), kQkv = (EPI == EPI_QKV);
   constexpr int NSEG = (kGlu || kQkv) ? 2 : BN / 128;            // vector segments per lane and unit
   constexpr int SEGW = (kQkv || (kGlu && BN == 128)) ? 2 : 4;    // floats per segment
@@ -190,19 +248,19 @@ __device__ void splitk_reduce_phase(const GemmParams& p) {
   for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
        u0 += gridDim.x * warps_per_cta * U) {
     float acc[U][NV];
-    const float* base[U];
+    float* base[U];
 #pragma unroll
     for (int k = 0; k < U; ++k) {
       const int u = min(u0 + k, units - 1);
-      base[k] = p.sk_scratch + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
+      base[k] = src_base + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
 #pragma unroll
       for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
     }
-    for (int s0 = 0; s0 < p.splits; s0 += SU) {
+    for (int s0 = 0; s0 < nsplits; s0 += SU) {
       float tmp[SU][U][NV];
 #pragma unroll
       for (int ds = 0; ds < SU; ++ds) {
-        const int s = min(s0 + ds, p.splits - 1);
+        const int s = min(s0 + ds, nsplits - 1);
 #pragma unroll
         for (int k = 0; k < U; ++k) {
 #pragma unroll
@@ -221,11 +279,25 @@ __device__ void splitk_reduce_phase(const GemmParams& p) {
       }
 #pragma unroll
       for (int ds = 0; ds < SU; ++ds) {
-        if (s0 + ds < p.splits) {
+        if (s0 + ds < nsplits) {
 #pragma unroll
           for (int k = 0; k < U; ++k)
 #pragma unroll
             for (int j = 0; j < NV; ++j) acc[k][j] += tmp[ds][k][j];
+        }
+      }
+    }
+    if (zero_after) {  // the all-reduce accumulation buffer must be zero again before its next use
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        if (u0 + k < units) {
+#pragma unroll
+          for (int g = 0; g < NSEG; ++g) {
+            if constexpr (SEGW == 4)
+              __stcg(reinterpret_cast<float4*>(base[k] + seg_off[g]), make_float4(0.f, 0.f, 0.f, 0.f));
+            else
+              __stcg(reinterpret_cast<float2*>(base[k] + seg_off[g]), make_float2(0.f, 0.f));
+          }
         }
       }
     }
@@ -389,6 +461,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int splits = p.splits;
+  const bool fused_ar = p.ar_world > 0;
+  __shared__ unsigned long long ar_expected_s;
+  __shared__ unsigned int ar_launch_s;
+  if (fused_ar && threadIdx.x == 0) {
+    ar_expected_s = p.ar_state[0];
+    ar_launch_s = static_cast<unsigned int>(p.ar_state[1]);
+  }
   const int num_items = p.num_m * p.num_n * splits;
 
   if (threadIdx.x == 0) {
@@ -529,9 +608,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
       // ---- split-K phase 1: dump this CTA's fp32 partial tile; the fused epilogue runs in phase 2 ----
       bool finisher = true;
-      if (splits > 1) {
+      if (splits > 1 || fused_ar) {
         finisher = false;
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
+        const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_floats : 0;
 #pragma unroll 1
         for (int i = 0; i < MT; ++i) {
           const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
@@ -541,7 +621,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t r[32];
             tmem_ld_32x32(taddr0 + i * BN + c * 32, r);
             tmem_ld_wait();
-            if (m < p.M) {
+            if (m < p.M && fused_ar) {
+              // every K split of every rank adds into the same fp32 tile on all ranks
+              const long long off = ar_off + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN + c * 32;
+              if (p.ar_mc_acc) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  multimem_red_add_v4(p.ar_mc_acc + off + j * 4, __uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]),
+                                      __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3]));
+              } else {
+                for (int pr = 0; pr < p.ar_world; ++pr) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    red_add_v4(p.ar_peer_acc[pr] + off + j * 4, __uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]),
+                               __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3]));
+                }
+              }
+            } else if (m < p.M) {
               float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
               for (int j = 0; j < 8; ++j)
@@ -734,9 +830,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
-    if (splits > 1) {
+    if (fused_ar) {
+      // all CTAs of all ranks have added their tiles once the local counter reaches the target
+      const unsigned long long target = ar_expected_s + static_cast<unsigned long long>(p.ar_world) * gridDim.x;
+      float* local = p.ar_peer_acc[p.ar_rank] + static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_floats;
+      if (ar_barrier(p, target)) splitk_reduce_phase<BN, EPI>(p, local, 1, true);
+      // Safe to advance the launch state: every CTA of this rank read it before arriving at the barrier.
+      if (blockIdx.x == 0 && threadIdx.x == 0) {
+        p.ar_state[0] = target;
+        p.ar_state[1] = static_cast<unsigned long long>(ar_launch_s) + 1ull;
+      }
+    } else if (splits > 1) {
       // every partial of every CTA must be visible before anyone reduces
-      if (grid_barrier(p.sk_barrier, gridDim.x, p.err)) splitk_reduce_phase<BN, EPI>(p);
+      if (grid_barrier(p.sk_barrier, gridDim.x, p.err)) splitk_reduce_phase<BN, EPI>(p, p.sk_scratch, splits, false);
     }
   }
 }
@@ -823,9 +929,17 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   if (p.mblk_group || BN % 128 != 0) force_splits = 1;  // grouped GEMMs have plenty of tiles
   if (force_splits > 0)
     splits = force_splits;
+  else if (p.ar_world > 0)  // partial tiles go straight into the all-reduce buffers: no local scratch limit
+    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, 1LL << 60);
   else if (ws.scratch)
     splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats);
-  if (splits > 1) {
+  if (p.ar_world > 0) {
+    if (out_floats > p.ar_buf_floats) {
+      set_last_error("fused all-reduce: output needs %lld floats per buffer, have %lld", out_floats, p.ar_buf_floats);
+      return -1;
+    }
+    if (splits > p.num_kb) splits = p.num_kb;
+  } else if (splits > 1) {
     if (!ws.scratch || splits * out_floats > ws.scratch_floats || splits > p.num_kb || splits > kMaxSplits) {
       set_last_error("gemm: split-K=%d needs %lld scratch floats (have %lld), K blocks %d", splits,
                      splits * out_floats, ws.scratch_floats, p.num_kb);
@@ -922,6 +1036,38 @@ GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.bias = bias;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.row_ss_out = row_ss_out;
+  p.err = gllm_error_word();
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
+}
+
+// Row-parallel GEMM fused with the tensor-parallel all-reduce: out = sum over ranks(A_r · B_rᵀ) (+bias)
+// + residual, with the next norm's row statistics. Every CTA adds its fp32 partial tile into the
+// accumulation buffer of all `world` ranks (one multimem.red through NVSwitch when `mc_acc` is given,
+// else one red per peer pointer over NVLink), all CTAs of all ranks meet at an arrival counter, then
+// each rank finishes from its own replica and zeroes it for reuse. Two buffers of `buf_floats` fp32
+// alternate between launches. Every rank must issue the same sequence of these calls.
+// peer_acc / peer_counter: arrays of `world` pointers, index = rank. state: two local u64, zero at start.
+GLLM_API int gllm_gemm_bf16_residual_allreduce(const void* A, long long lda, const void* B, long long ldb, void* out,
+                                               long long ldo, const void* residual, long long ldr, float* row_ss_out,
+                                               int M, int N, int K, const float* bias, int bn, void* stream,
+                                               int max_ctas, int force_splits, int world, int rank, float* mc_acc,
+                                               float* const* peer_acc, unsigned long long* mc_counter,
+                                               unsigned long long* const* peer_counter, unsigned long long* state,
+                                               long long buf_floats) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_acc || !peer_counter || !state) {
+    set_last_error("gemm_allreduce: bad world/rank/pointers (world %d rank %d)", world, rank);
+    return -1;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.row_ss_out = row_ss_out;
+  p.ar_world = world; p.ar_rank = rank; p.ar_mc_acc = mc_acc; p.ar_mc_counter = mc_counter;
+  for (int r = 0; r < world; ++r) {
+    p.ar_peer_acc[r] = peer_acc[r];
+    p.ar_peer_counter[r] = peer_counter[r];
+  }
+  p.ar_state = state; p.ar_buf_floats = buf_floats;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }

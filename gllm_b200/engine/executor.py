@@ -107,6 +107,7 @@ class LLMEngine:
                           d2h_bytes=0, kernel_launches=0, preemptions=0)
         self.launches_per_graph: Dict[int, int] = {}
         self.gen = torch.Generator().manual_seed(ec.seed)
+        self._all_greedy = True
         self._req_params: Dict[int, tuple] = {}
         self._vetoed: Dict[int, str] = {}
 
@@ -165,8 +166,9 @@ class LLMEngine:
     def _sample(self, logits, params, offsets, out):
         tp = self.model.tp
         if tp is not None and tp.size > 1:
+            # the greedy fast path (pairs instead of full logit rows) is fixed per captured graph
             tp.sample_vocab_parallel(logits, self.model.vocab_local, self.model.vocab_start, params, self.cfg.seed,
-                                     offsets, out, self.mc.vocab_size)
+                                     offsets, out, self.mc.vocab_size, greedy=self._all_greedy)
         else:
             ops.sample(logits, params, vocab=self.mc.vocab_size, seed=self.cfg.seed, step_offsets=offsets, out=out,
                        generator=self.gen)
@@ -184,8 +186,10 @@ class LLMEngine:
         self.d_bt.copy_(self.h_bt, non_blocking=cuda)
         self.d_params.copy_(self.h_params, non_blocking=cuda)
         self.stats["h2d_bytes"] += self.h_dec.numel() * 4 + self.h_bt.numel() * 4 + self.h_params.numel() * 4
+        self._all_greedy = bool((self.slot_params[:, 0] <= 0).all())
         if cuda and self.cfg.use_cuda_graphs:
-            g = self.graphs.get(B)
+            key = (B, self._all_greedy)
+            g = self.graphs.get(key)
             if g is None:
                 g = self._capture(B)
             g.replay()
@@ -212,7 +216,7 @@ class LLMEngine:
         with torch.cuda.graph(g, stream=s):
             self._decode_body(B)
         self.launches_per_graph[B] = nv.CALLS[0] - n0
-        self.graphs[B] = g
+        self.graphs[(B, self._all_greedy)] = g
         return g
 
     def _run_prefill(self, plan) -> np.ndarray:
@@ -246,6 +250,7 @@ class LLMEngine:
             self.model.forward(batch, self.kv_caches, return_hidden=True)
             return np.zeros(0, np.int32)
         logits = self.model.forward(batch, self.kv_caches)
+        self._all_greedy = bool((self.slot_params[last_slots, 0] <= 0).all())
         sl = torch.tensor(last_slots, dtype=torch.int64)
         params = torch.from_numpy(self.slot_params[last_slots]).to(dev)
         offs = self.d_offsets.index_select(0, sl.to(dev))

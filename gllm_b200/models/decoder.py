@@ -130,8 +130,8 @@ class DecoderModel:
         """x <- a @ w.T + x, row statistics into ss_out. With TP the partial sums are all-reduced."""
         if self.tp_size == 1:
             ops.gemm_residual(a, w, x, out=x, row_ss_out=ss_out, bn=self.res_bn)
-            return
-        self.tp.gemm_allreduce_residual(a, w, x, ss_out, self._ws.partial[:T])
+            return ss_out
+        return self.tp.gemm_allreduce_residual(a, w, x, ss_out, self._ws.partial[:T], bn=self.res_bn)
 
     def forward(self, batch: ForwardBatch, kv_caches: List[torch.Tensor], *, hidden_in=None, decode_ws=None,
                 return_hidden: bool = False, capture_layers=None):
@@ -157,14 +157,13 @@ class DecoderModel:
                              sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                              row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias)
                 self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
-                self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
+                ss_mid = self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
                 if lw.moe is not None:
-                    lw.moe.forward(self, x, ws.ss_b[:T], ws.ss_a[:T], T)
+                    ss_in = lw.moe.forward(self, x, ss_mid, ws.ss_a[:T], T)
                 else:
                     ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
-                                 row_ss=ws.ss_b[:T], norm_dim=H, eps=c.rms_norm_eps, bn=lw.glu_bn)
-                    self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
-                ss_in = ws.ss_a[:T]
+                                 row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=lw.glu_bn)
+                    ss_in = self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
             else:
                 h = ws.h[:T]
                 ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)

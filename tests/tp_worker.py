@@ -1,0 +1,48 @@
+"""Worker for the multi-GPU tensor-parallel tests (launched by torchrun, one rank per GPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.parallel.tensor_parallel import TPContext
+    H = 2048
+    tp = TPContext(rank, world, dev, mode=mode, max_tokens=512, hidden=H)
+    if mode != "nccl":
+        assert tp.mode == "fused", getattr(tp, "setup_error", "")
+    g = torch.Generator(device="cpu").manual_seed(7)
+    for it, (M, K) in enumerate([(256, 1024), (77, 512), (256, 1024), (512, 2048)]):
+        a_full = torch.randn(M, K * world, generator=g).to(torch.bfloat16)
+        w_full = (torch.randn(H, K * world, generator=g) * 0.05).to(torch.bfloat16)
+        x0 = torch.randn(M, H, generator=g).to(torch.bfloat16)
+        ref = (a_full.float() @ w_full.float().t() + x0.float())
+        a = a_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        w = w_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
+        x = x0.clone().to(dev)
+        ss_buf = torch.zeros(512, 8, device=dev)
+        part = torch.empty(512, H, device=dev, dtype=torch.bfloat16)
+        ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, part, bn=256)
+        torch.cuda.synchronize()
+        err = (x.float().cpu() - ref).abs().max().item()
+        assert err < 0.05 * ref.abs().max().item(), f"rank {rank} iter {it} mode {mode} err {err}"
+        got = ss.reshape(M, -1).sum(-1).cpu()
+        torch.testing.assert_close(got, x.float().pow(2).sum(-1).cpu(), rtol=2e-3, atol=2e-3)
+    code = nv.device_error()
+    assert code == 0, f"device error {code}"
+    dist.barrier()
+    if rank == 0:
+        print("TP_WORKER_OK", mode, "multimem" if tp.uses_multimem else "p2p/nccl", flush=True)
+    tp.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
