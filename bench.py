@@ -248,7 +248,7 @@ def main():
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {budget_tokens} out",
                        "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
-                       "tp_mode": getattr(tp, "mode", "none"), "cuda_graphs": not args.no_graphs,
+                       "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
                        "layers": cfg.num_layers, "valid": args.layers == 0},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms / K, 4)},
@@ -262,10 +262,12 @@ def main():
         }
         print(json.dumps(out), flush=True)
     if world > 1:
+        # Leave without tearing NCCL down: communicators referenced by captured CUDA graphs do not
+        # destroy cleanly, and every rank has already contributed its numbers.
         dist.barrier()
-        if tp is not None:
-            tp.close()
-        dist.destroy_process_group()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 

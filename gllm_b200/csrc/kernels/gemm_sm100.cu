@@ -81,17 +81,18 @@ struct GemmParams {
   const float* q_norm_w;  // [128] or null
   const float* k_norm_w;  // [128] or null
   float qk_eps;
-  // fused all-reduce (row-parallel GEMM across `ar_world` GPUs). Partial tiles are added into the
-  // fp32 accumulation buffer of every rank: one multimem.red through NVSwitch when a multicast mapping
-  // exists, else one red per peer pointer. ar_world == 0 disables it.
+  // fused all-reduce (row-parallel GEMM across `ar_world` GPUs): every rank stores its bf16 partial
+  // tiles in its own symmetric buffer as they retire; after the arrival barrier each rank pulls the
+  // sum of all ranks' partials (multimem.ld_reduce through NVSwitch when a multicast mapping exists,
+  // else plain peer loads over NVLink) and finishes locally. ar_world == 0 disables it.
   int ar_world;
-  float* ar_mc_acc;                       // multicast address of the accumulation buffers, or null
-  float* ar_peer_acc[8];                  // unicast addresses (index = rank); [ar_rank] is local
+  __nv_bfloat16* ar_mc_buf;               // multicast address of the partial buffers, or null
+  __nv_bfloat16* ar_peer_buf[8];          // unicast addresses (index = rank); [ar_rank] is local
   unsigned long long* ar_mc_counter;      // multicast address of the arrival counter, or null
   unsigned long long* ar_peer_counter[8];
   unsigned long long* ar_state;           // local {expected arrivals, launch index}
   int ar_rank;
-  long long ar_buf_floats;                // size of one accumulation buffer (two alternate per launch)
+  long long ar_buf_elems;                 // elements of one partial buffer (two alternate per launch)
   int* err;
 };
 
@@ -140,15 +141,14 @@ struct AccReader {
   }
 };
 
-__device__ __forceinline__ void multimem_red_add_v4(float* mc, float a, float b, float c, float d) {
-  asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(a), "f"(b),
-               "f"(c), "f"(d)
+// Sum over all GPUs of a multicast group of 8 bf16 values (fp32 accumulation inside the switch).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
                : "memory");
-}
-__device__ __forceinline__ void red_add_v4(float* ptr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
+  return v;
 }
 __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
   unsigned long long v;
@@ -437,6 +437,98 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
   }
 }
 
+// Phase 2 of the fused all-reduce: a warp owns (row, 256-column group) units, four at a time; a lane
+// covers 8 columns = one 16-byte vector. The sum over ranks comes from one multimem.ld_reduce per
+// vector (NVSwitch adds in fp32) or from one plain load per peer; then residual add, bf16 store and
+// the row statistics for the next norm.
+template <int BN>
+__device__ void ar_reduce_phase(const GemmParams& p, long long buf_off) {
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const int groups = static_cast<int>(n_pad / 256);
+  const int units = p.M * groups;
+  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
+       u0 += gridDim.x * warps_per_cta * U) {
+    float acc[U][8];
+    long long off[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      off[k] = buf_off + static_cast<long long>(u / groups) * n_pad + static_cast<long long>(u % groups) * 256 + lane * 8;
+    }
+    if (p.ar_mc_buf) {
+      uint4 raw[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) raw[k] = multimem_ld_reduce_bf16x8(p.ar_mc_buf + off[k]);
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[k][2 * e] = f.x;
+          acc[k][2 * e + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+      for (int r = 0; r < p.ar_world; ++r) {  // rank order: every rank computes the identical sum
+        uint4 raw[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.ar_peer_buf[r] + off[k]));
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            acc[k][2 * e] += f.x;
+            acc[k][2 * e + 1] += f.y;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = u0 + k;
+      if (u >= units) continue;
+      const int m = u / groups, grp = u % groups;
+      const int n0 = grp * 256 + lane * 8;
+      float ss = 0.f;
+      if (n0 < p.N) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] = acc[k][j];
+          if (p.bias) v[j] += p.bias[n0 + j];
+        }
+        const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[2 * e] = bf16_round(v[2 * e] + f.x);
+          v[2 * e + 1] = bf16_round(v[2 * e + 1] + f.y);
+          ss += v[2 * e] * v[2 * e] + v[2 * e + 1] * v[2 * e + 1];
+        }
+        uint4 w;
+        w.x = pack_bf16x2(v[0], v[1]);
+        w.y = pack_bf16x2(v[2], v[3]);
+        w.z = pack_bf16x2(v[4], v[5]);
+        w.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0) = w;
+      }
+      ss = warp_sum(ss);
+      if (p.row_ss_out && lane == 0) p.row_ss_out[static_cast<long long>(m) * groups + grp] = ss;
+    }
+  }
+}
+
 template <int BN, int MT, int EPI, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -611,7 +703,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (splits > 1 || fused_ar) {
         finisher = false;
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
-        const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_floats : 0;
+        const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems : 0;
 #pragma unroll 1
         for (int i = 0; i < MT; ++i) {
           const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
@@ -622,21 +714,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tmem_ld_32x32(taddr0 + i * BN + c * 32, r);
             tmem_ld_wait();
             if (m < p.M && fused_ar) {
-              // every K split of every rank adds into the same fp32 tile on all ranks
+              // this rank's bf16 partial tile, in its own symmetric buffer (peers pull it after the barrier)
               const long long off = ar_off + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN + c * 32;
-              if (p.ar_mc_acc) {
+              float v[32];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  multimem_red_add_v4(p.ar_mc_acc + off + j * 4, __uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]),
-                                      __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3]));
-              } else {
-                for (int pr = 0; pr < p.ar_world; ++pr) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j)
-                    red_add_v4(p.ar_peer_acc[pr] + off + j * 4, __uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]),
-                               __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3]));
-                }
-              }
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              store_bf16x32(p.ar_peer_buf[p.ar_rank] + off, v);
             } else if (m < p.M) {
               float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
@@ -833,8 +916,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (fused_ar) {
       // all CTAs of all ranks have added their tiles once the local counter reaches the target
       const unsigned long long target = ar_expected_s + static_cast<unsigned long long>(p.ar_world) * gridDim.x;
-      float* local = p.ar_peer_acc[p.ar_rank] + static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_floats;
-      if (ar_barrier(p, target)) splitk_reduce_phase<BN, EPI>(p, local, 1, true);
+      if (ar_barrier(p, target)) {
+        if constexpr (EPI == EPI_RESIDUAL)
+          ar_reduce_phase<BN>(p, static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems);
+      }
       // Safe to advance the launch state: every CTA of this rank read it before arriving at the barrier.
       if (blockIdx.x == 0 && threadIdx.x == 0) {
         p.ar_state[0] = target;
@@ -929,16 +1014,17 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   if (p.mblk_group || BN % 128 != 0) force_splits = 1;  // grouped GEMMs have plenty of tiles
   if (force_splits > 0)
     splits = force_splits;
-  else if (p.ar_world > 0)  // partial tiles go straight into the all-reduce buffers: no local scratch limit
-    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, 1LL << 60);
+  else if (p.ar_world > 0)  // each rank publishes exactly one partial per tile
+    splits = 1;
   else if (ws.scratch)
     splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats);
   if (p.ar_world > 0) {
-    if (out_floats > p.ar_buf_floats) {
-      set_last_error("fused all-reduce: output needs %lld floats per buffer, have %lld", out_floats, p.ar_buf_floats);
+    if (out_floats > p.ar_buf_elems || (static_cast<long long>(p.num_n) * BN) % 256 != 0) {
+      set_last_error("fused all-reduce: output needs %lld elements per buffer (have %lld), padded width %% 256",
+                     out_floats, p.ar_buf_elems);
       return -1;
     }
-    if (splits > p.num_kb) splits = p.num_kb;
+    splits = 1;
   } else if (splits > 1) {
     if (!ws.scratch || splits * out_floats > ws.scratch_floats || splits > p.num_kb || splits > kMaxSplits) {
       set_last_error("gemm: split-K=%d needs %lld scratch floats (have %lld), K blocks %d", splits,
@@ -966,7 +1052,8 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
 template <int EPI, bool FP8>
 static int dispatch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
                          const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
-  const bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr;
+  // The fused all-reduce never splits K locally, so it keeps 128-row tiles: more tiles in flight.
+  const bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr && p.ar_world == 0;
   if constexpr (EPI == EPI_GLU) {
     // 192-wide tiles: 128 tiles for a 24576-row gate/up weight fill one wave of 148 SMs without splitting
     if (bn == 192) {
@@ -1041,20 +1128,21 @@ GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B
 }
 
 // Row-parallel GEMM fused with the tensor-parallel all-reduce: out = sum over ranks(A_r · B_rᵀ) (+bias)
-// + residual, with the next norm's row statistics. Every CTA adds its fp32 partial tile into the
-// accumulation buffer of all `world` ranks (one multimem.red through NVSwitch when `mc_acc` is given,
-// else one red per peer pointer over NVLink), all CTAs of all ranks meet at an arrival counter, then
-// each rank finishes from its own replica and zeroes it for reuse. Two buffers of `buf_floats` fp32
-// alternate between launches. Every rank must issue the same sequence of these calls.
-// peer_acc / peer_counter: arrays of `world` pointers, index = rank. state: two local u64, zero at start.
+// + residual, with the next norm's row statistics [M, ceil(N/256)]. Each rank stores its bf16 partial tiles
+// in its own symmetric buffer as they retire; all CTAs of all ranks meet at an arrival counter (one
+// multimem.red per CTA, or one red per peer); then every rank pulls the sum of all partials — one
+// multimem.ld_reduce per 16 bytes through NVSwitch when `mc_buf` is given, else plain peer loads over
+// NVLink — and finishes locally. Two buffers of `buf_elems` bf16 alternate between launches.
+// Every rank must issue the same sequence of these calls. peer_buf / peer_counter: arrays of `world`
+// pointers, index = rank. state: two local u64, zero at start.
 GLLM_API int gllm_gemm_bf16_residual_allreduce(const void* A, long long lda, const void* B, long long ldb, void* out,
                                                long long ldo, const void* residual, long long ldr, float* row_ss_out,
                                                int M, int N, int K, const float* bias, int bn, void* stream,
-                                               int max_ctas, int force_splits, int world, int rank, float* mc_acc,
-                                               float* const* peer_acc, unsigned long long* mc_counter,
+                                               int max_ctas, int force_splits, int world, int rank, void* mc_buf,
+                                               void* const* peer_buf, unsigned long long* mc_counter,
                                                unsigned long long* const* peer_counter, unsigned long long* state,
-                                               long long buf_floats) {
-  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_acc || !peer_counter || !state) {
+                                               long long buf_elems) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_buf || !peer_counter || !state) {
     set_last_error("gemm_allreduce: bad world/rank/pointers (world %d rank %d)", world, rank);
     return -1;
   }
@@ -1062,12 +1150,13 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce(const void* A, long long lda, con
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.bias = bias;
   p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr; p.row_ss_out = row_ss_out;
-  p.ar_world = world; p.ar_rank = rank; p.ar_mc_acc = mc_acc; p.ar_mc_counter = mc_counter;
+  p.ar_world = world; p.ar_rank = rank; p.ar_mc_buf = static_cast<__nv_bfloat16*>(mc_buf);
+  p.ar_mc_counter = mc_counter;
   for (int r = 0; r < world; ++r) {
-    p.ar_peer_acc[r] = peer_acc[r];
+    p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(peer_buf[r]);
     p.ar_peer_counter[r] = peer_counter[r];
   }
-  p.ar_state = state; p.ar_buf_floats = buf_floats;
+  p.ar_state = state; p.ar_buf_elems = buf_elems;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }

@@ -4,14 +4,15 @@
 The reference does every TP collective on host f32 slices through its NCCL wrapper
 (src/engine/coordinator/compute.rs:122-436: tp_all_reduce / tp_reduce_scatter / tp_all_gather,
 src/engine/distributed_config.rs:424-495). Here the row-parallel GEMM and its all-reduce are ONE kernel
-(``gllm_gemm_bf16_residual_allreduce``): tcgen05 tiles are added into every rank's fp32 accumulation
-buffer as they retire — a single ``multimem.red`` per vector through NVSwitch when the symmetric buffer has a
-multicast mapping, otherwise one ``red`` per peer pointer over NVLink — all CTAs of all ranks meet at an
-arrival counter, and each rank finishes (residual add, bf16 store, next norm's row statistics) from its
-own replica. The NCCL path (unfused GEMM -> ncclAllReduce -> residual/norm-stat kernel) is kept as the
+(``gllm_gemm_bf16_residual_allreduce``): each rank stores its bf16 partial tiles into its own symmetric
+buffer as the tcgen05 tiles retire, all CTAs of all ranks meet at an arrival counter, and every rank then
+pulls the sum of all partials — one ``multimem.ld_reduce`` per 16 bytes, added in fp32 inside NVSwitch, when
+the buffer has a multicast mapping, otherwise plain peer loads over NVLink — and finishes locally (residual
+add, bf16 store, next norm's row statistics). Bulk data never goes through atomics: accumulating partial
+tiles with ``red``/``multimem.red`` was measured at roughly 20x the time of this pull design. The NCCL path (unfused GEMM -> ncclAllReduce -> residual/norm-stat kernel) is kept as the
 selectable baseline.
 
-Modes: ``fused`` (multimem if available, else peer reds), ``fused_p2p`` (force peer reds), ``nccl``,
+Modes: ``fused`` (multimem if available, else peer loads), ``fused_p2p`` (force peer loads), ``nccl``,
 ``auto`` (fused when symmetric memory can be set up, else nccl).
 """
 from __future__ import annotations
@@ -35,7 +36,7 @@ class TPContext:
         self.uses_multimem = False
         self.max_fused_tokens = min(max_fused_tokens, max_tokens)
         self.n_pad = ((hidden + 255) // 256) * 256
-        self.buf_floats = self.max_fused_tokens * self.n_pad
+        self.buf_elems = self.max_fused_tokens * self.n_pad
         self._symm = None
         self._handle = None
         if mode in ("auto", "fused", "fused_p2p") and self.device.type == "cuda":
@@ -51,14 +52,14 @@ class TPContext:
     # ------------------------------------------------------------------------------------------
     def _setup_symmetric(self, force_p2p: bool):
         import torch.distributed as dist
-        total_floats = 2 * self.buf_floats + 64
+        total = 2 * self.buf_elems + 64
         if self.size == 1:
-            buf = torch.zeros(total_floats, dtype=torch.float32, device=self.device)
+            buf = torch.zeros(total, dtype=torch.bfloat16, device=self.device)
             peer_ptrs, mc_ptr = [buf.data_ptr()], 0
         else:
             import torch.distributed._symmetric_memory as symm_mem
             group = self.group or dist.group.WORLD
-            buf = symm_mem.empty(total_floats, dtype=torch.float32, device=self.device)
+            buf = symm_mem.empty(total, dtype=torch.bfloat16, device=self.device)
             self._handle = symm_mem.rendezvous(buf, group.group_name)
             buf.zero_()
             torch.cuda.synchronize(self.device)
@@ -67,7 +68,7 @@ class TPContext:
             mc_ptr = 0 if force_p2p else int(getattr(self._handle, "multicast_ptr", 0) or 0)
         self._symm = buf
         self.uses_multimem = mc_ptr != 0
-        counter_off = 2 * self.buf_floats * 4  # bytes; 8-byte aligned because buf_floats is a multiple of 256
+        counter_off = 2 * self.buf_elems * 2  # bytes; 8-byte aligned because buf_elems is a multiple of 256
         n = len(peer_ptrs)
         self._peer_acc = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
         self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
@@ -81,15 +82,18 @@ class TPContext:
         M, K = a.shape
         N = w.shape[0]
         if self.mode == "fused" and M <= self.max_fused_tokens and N <= self.n_pad:
-            parts = (N + bn - 1) // bn
+            parts = (N + 255) // 256  # the fused kernel reports statistics per 256-column group
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
                 raise ValueError("row statistics buffer must be [tokens, parts] contiguous")
+            # few output tiles: prefer 128-wide tiles so more SMs stream weights (the pull phase works on
+            # 256-column groups either way)
+            tile_bn = 256 if (N // 256) * ((M + 127) // 128) >= 148 else 128
             rc = nv.lib().gllm_gemm_bf16_residual_allreduce(
                 a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), x.data_ptr(),
-                x.stride(0), ss.data_ptr(), M, N, K, None, bn, nv.stream_ptr(), 0, 0, self.size, self.rank,
+                x.stride(0), ss.data_ptr(), M, N, K, None, tile_bn, nv.stream_ptr(), 0, 0, self.size, self.rank,
                 self._mc_acc, ctypes.cast(self._peer_acc, ctypes.c_void_p), self._mc_cnt,
-                ctypes.cast(self._peer_cnt, ctypes.c_void_p), self._state.data_ptr(), self.buf_floats)
+                ctypes.cast(self._peer_cnt, ctypes.c_void_p), self._state.data_ptr(), self.buf_elems)
             nv.check(rc, "gemm_bf16_residual_allreduce")
             return ss
         # NCCL baseline: unfused GEMM -> all-reduce -> residual add + row statistics
@@ -142,5 +146,5 @@ class TPContext:
 
 def single_gpu_context(device, hidden: int, max_tokens: int = 1024) -> TPContext:
     """A world-size-1 context on ordinary device memory: exercises the fused kernel's protocol (alternating
-    buffers, arrival counter, self-zeroing) on one GPU."""
+    buffers, arrival counter, launch state) on one GPU."""
     return TPContext(0, 1, device, mode="fused_p2p", max_tokens=max_tokens, hidden=hidden)

@@ -1,5 +1,5 @@
 """Fused row-parallel GEMM + all-reduce kernel: single-GPU protocol test (world size 1 on ordinary device
-memory: alternating buffers, arrival counter, self-zeroing) and 2-GPU tests over NVLink (peer reds and
+memory: alternating buffers, arrival counter, launch state) and 2-GPU tests over NVLink (peer reds and
 multimem), each against an fp32 reference. Run with -m gpu on a B200."""
 import os
 import subprocess
@@ -26,15 +26,13 @@ def test_fused_allreduce_world1_protocol():
         w = (torch.randn(H, K, device=dev) * 0.05).to(torch.bfloat16)
         x = torch.randn(M, H, device=dev).to(torch.bfloat16)
         ref = (a.float() @ w.float().t() + x.float()).to(torch.bfloat16)
-        ss_buf = torch.zeros(512, 4, device=dev)
+        ss_buf = torch.zeros(512, H // 256, device=dev)
         part = torch.empty(512, H, device=dev, dtype=torch.bfloat16)
         ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, part, bn=256)
         err = (x.float() - ref.float()).abs().max().item()
         assert err < 0.05 * ref.float().abs().max().item(), (it, err)
         torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
-    # both accumulation buffers must be zero again
-    assert float(tp._symm[: 2 * tp.buf_floats].abs().max()) == 0.0
-    assert int(tp._state[1]) == 5
+    assert int(tp._state[1]) == 5  # five launches advanced the launch state five times
 
 
 @pytest.mark.multigpu

@@ -27,7 +27,7 @@ def main():
         a = a_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
         w = w_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
         x = x0.clone().to(dev)
-        ss_buf = torch.zeros(512, 8, device=dev)
+        ss_buf = torch.zeros(512, H // 256, device=dev)
         part = torch.empty(512, H, device=dev, dtype=torch.bfloat16)
         ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, part, bn=256)
         torch.cuda.synchronize()
