@@ -580,3 +580,121 @@ GLLM_API int gllm_paged_prefill(const void* q, void* out, const void* kv_cache, 
   if (e != cudaSuccess) { set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of gllm_paged_decode (declared and documented in gllm_noalloc.h).
+//
+// Who needs it: callers that cannot allocate device memory when they need attention — under a fixed
+// start-up memory plan, on a thread where the owning framework forbids allocator calls, or in a
+// latency-critical loop. The split-KV scratch is the
+// static array below; the caller still owns q, out, the KV cache and the index tensors.
+// ---------------------------------------------------------------------------------------------
+#include "gllm_noalloc.h"
+
+namespace gllm {
+// partial outputs [units][128] followed by their log-sum-exps [units]; units = batch * n_q * max_splits
+static __device__ __align__(256) float g_noalloc_scratch[GLLM_NOALLOC_MAX_UNITS * (kHD + 1)];
+static __device__ __align__(256) int g_noalloc_counters[GLLM_NOALLOC_MAX_COUNTERS];
+static __device__ __align__(256) int g_noalloc_err[4];
+
+struct NoAllocDeviceState {
+  bool ready = false;
+  float* scratch = nullptr;   // device addresses obtained with cudaGetSymbolAddress: in host code the
+  int* counters = nullptr;    // array names above are only host-side stand-ins, never device pointers
+  int* err = nullptr;
+};
+static NoAllocDeviceState g_noalloc_state[64];
+}  // namespace gllm
+
+GLLM_API int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_cache, int num_pages,
+                                       const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
+                                       int n_q_heads, int n_kv_heads, float scale, int pages_per_split,
+                                       int max_splits, int window, const float* sinks, void* stream) {
+  if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 ||
+      n_q_heads / n_kv_heads > 16) {
+    set_last_error("paged_decode_noalloc: bad shape batch %d heads %d/%d", batch, n_q_heads, n_kv_heads);
+    return -1;
+  }
+  if (max_splits < 1) max_splits = 1;
+  const long long units = static_cast<long long>(batch) * n_q_heads * max_splits;
+  if (units > GLLM_NOALLOC_MAX_UNITS) {
+    set_last_error("paged_decode_noalloc: batch*heads*splits = %lld exceeds the built-in scratch (%d); lower "
+                   "max_splits or use gllm_paged_decode with caller scratch", units, GLLM_NOALLOC_MAX_UNITS);
+    return -1;
+  }
+  if (static_cast<long long>(batch) * n_kv_heads > GLLM_NOALLOC_MAX_COUNTERS) {
+    set_last_error("paged_decode_noalloc: batch*kv_heads = %lld exceeds the built-in counters (%d)",
+                   static_cast<long long>(batch) * n_kv_heads, GLLM_NOALLOC_MAX_COUNTERS);
+    return -1;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_error("paged_decode_noalloc: no current device");
+    return -1;
+  }
+  NoAllocDeviceState& st = g_noalloc_state[dev];
+  if (!st.ready) {
+    // one-time set-up for this device (do it before any stream capture): resolve the device addresses
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.scratch), g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.counters), g_noalloc_counters);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.err), g_noalloc_err);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+    if (e != cudaSuccess) {
+      set_last_error("paged_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
+      return -1;
+    }
+    st.ready = true;
+  }
+  // tensor map built on the stack (the cached encoder used elsewhere grows a host-side table)
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (!enc) {
+    set_last_error("paged_decode_noalloc: cuTensorMapEncodeTiled is not available from this driver");
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(kv_cache) & 15) != 0) {
+    set_last_error("paged_decode_noalloc: kv_cache must be 16-byte aligned");
+    return -1;
+  }
+  CUtensorMap t;
+  {
+    cuuint64_t gdim[2] = {kHD, static_cast<cuuint64_t>(num_pages) * 2 * n_kv_heads * kPage};
+    cuuint64_t gstride[1] = {kHD * 2};
+    cuuint32_t box[2] = {64, kPage};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv_cache), gdim, gstride, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      set_last_error("paged_decode_noalloc: tensor map encode failed (CUresult %d)", int(r));
+      return -1;
+    }
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the scratch keeps the last call's contents; only the ticket counters must start at zero
+  cudaError_t e = cudaMemsetAsync(st.counters, 0, sizeof(int) * static_cast<size_t>(batch) * n_kv_heads, s);
+  if (e != cudaSuccess) {
+    set_last_error("paged_decode_noalloc: counter clear failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  DecodeParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.max_blocks = max_blocks;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.pages_per_split = pages_per_split > 0 ? pages_per_split : (1 << 30);
+  p.max_splits = max_splits;
+  p.part_o = st.scratch;
+  p.part_lse = st.scratch + units * kHD;
+  p.counters = st.counters; p.num_pages = num_pages; p.window = window; p.sinks = sinks;
+  p.err = st.err;
+  dim3 grid(max_splits, n_kv_heads, batch);
+  paged_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, s>>>(t, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("paged_decode_noalloc launch: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
