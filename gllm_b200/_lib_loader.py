@@ -29,5 +29,5 @@ def shared_lib_path(name: str, subdir: str) -> Path:
     path = _LIB / (name + ".so")
     if not path.exists():
         from . import build
-        build.build_cxx_module(name, subdir, pybind=False)
+        build.build_cxx_module(name, subdir, pybind=False, extra=("-fopenmp",))
     return path

@@ -103,10 +103,11 @@ def build_cxx_module(name: str, subdir: str, pybind=True, force=False, verbose=F
 
 def build_all(force=False, verbose=False):
     outs = [build_kernels(force, verbose)]
-    for name, sub, pyb in (("_sched", "sched", True), ("libgllm_cpuref", "ref", False),
-                           ("libgllm_loader", "loader", False), ("libgllm_ffi", "ffi", False)):
+    for name, sub, pyb, extra in (("_sched", "sched", True, ()), ("libgllm_cpuref", "ref", False, ("-fopenmp",)),
+                                  ("libgllm_loader", "loader", False, ("-fopenmp",)),
+                                  ("libgllm_ffi", "ffi", False, ())):
         if any((CSRC / sub).glob("*.cpp")):
-            outs.append(build_cxx_module(name, sub, pybind=pyb, force=force, verbose=verbose))
+            outs.append(build_cxx_module(name, sub, pybind=pyb, force=force, verbose=verbose, extra=extra))
     return outs
 
 

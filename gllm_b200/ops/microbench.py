@@ -1,0 +1,145 @@
+"""Kernel microbenchmarks: ``python -m gllm_b200.ops.microbench --op <name> [--iters N]``.
+
+Each op runs a small, fixed case (inputs larger than L2, a few hundred MB on the device at most) so it can
+also be captured with ``ncu`` in a minute or two. Timing uses CUDA events on the launching stream after
+warm-up; the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root if
+present) is printed as JSON.
+
+ops: gemm_prefill  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from .. import ops
+
+
+def _peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3  # seconds
+
+
+def run(op: str, iters: int):
+    dev = torch.device("cuda")
+    hbm, tf, src = _peaks()
+    torch.manual_seed(0)
+    rnd = lambda *s, scale=1.0: (torch.randn(*s, device=dev) * scale).to(torch.bfloat16)
+    out = {"op": op, "peaks": src}
+    if op == "gemm_prefill":
+        M, N, K = 8192, 8192, 4096
+        a, w = rnd(M, K), rnd(N, K, scale=0.05)
+        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: ops.gemm(a, w, out=o, bn=256), iters)
+        out.update(shape=[M, N, K], us=t * 1e6, tflops=2 * M * N * K / t / 1e12, frac_of_bf16_peak=2 * M * N * K / t / 1e12 / tf)
+    elif op == "gemm_decode":
+        M, N, K = 256, 4096, 12288
+        ws = [rnd(N, K, scale=0.05) for _ in range(3)]
+        a, r = rnd(M, K), rnd(M, N)
+        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def f():
+            i[0] = (i[0] + 1) % 3
+            ops.gemm_residual(a, ws[i[0]], r, out=o, bn=256)
+        t = _time(f, iters)
+        byts = N * K * 2
+        out.update(shape=[M, N, K], us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
+    elif op == "gemm_glu":
+        M, I, K = 256, 12288, 4096
+        from ..models.weights import glu_tile_width
+        bn = glu_tile_width(I)
+        ws = [ops.interleave_gate_up(rnd(I, K, scale=0.05), rnd(I, K, scale=0.05), bn) for _ in range(2)]
+        a = rnd(M, K)
+        ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+        o = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def f():
+            i[0] ^= 1
+            ops.gemm_glu(a, ws[i[0]], out=o, row_ss=ss, norm_dim=K, eps=1e-6, bn=bn)
+        t = _time(f, iters)
+        byts = 2 * I * K * 2
+        out.update(shape=[M, 2 * I, K], bn=bn, us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
+    elif op == "gemm_qkv":
+        M, K, nq, nkv = 2048, 4096, 32, 8
+        a, w = rnd(M, K), rnd((nq + 2 * nkv) * 128, K, scale=0.05)
+        ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+        kv = torch.zeros(M // 16 + 1, 2, nkv, 16, 128, device=dev, dtype=torch.bfloat16)
+        q = torch.empty(M, nq * 128, device=dev, dtype=torch.bfloat16)
+        pos = torch.arange(M, device=dev, dtype=torch.int32)
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, device=dev).double() / 128))
+        ang = torch.arange(M, device=dev).double()[:, None] * inv[None]
+        cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+        qn = torch.ones(128, device=dev)
+        t = _time(lambda: ops.gemm_qkv(a, w, n_q=nq, n_kv=nkv, q_out=q, kv_cache=kv, slot_mapping=pos, positions=pos,
+                                       cos_t=cos, sin_t=sin, q_norm_w=qn, k_norm_w=qn, row_ss=ss, norm_dim=K, eps=1e-6),
+                  iters)
+        fl = 2 * M * (nq + 2 * nkv) * 128 * K
+        out.update(shape=[M, (nq + 2 * nkv) * 128, K], us=t * 1e6, tflops=fl / t / 1e12, frac_of_bf16_peak=fl / t / 1e12 / tf)
+    elif op in ("decode_attn", "prefill_attn"):
+        nq, nkv, D = 32, 8, 128
+        if op == "decode_attn":
+            B, ctx = 64, 2048
+            pages = B * ctx // 16
+            kv = torch.randn(pages, 2, nkv, 16, D, device=dev).to(torch.bfloat16)
+            bt = torch.randperm(pages, device=dev).to(torch.int32).reshape(B, ctx // 16).contiguous()
+            cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            q = rnd(B, nq * D)
+            o = torch.empty_like(q)
+            wsp = ops.DecodeWorkspace(B, nq, nkv, 1, dev)
+            t = _time(lambda: ops.paged_decode(q, kv, bt, cl, n_q=nq, n_kv=nkv, out=o, workspace=wsp,
+                                               pages_per_split=1 << 20), iters)
+            byts = kv.numel() * 2
+            out.update(batch=B, ctx=ctx, us=t * 1e6, kv_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
+        else:
+            S, L = 8, 2048
+            pages = S * L // 16
+            kv = torch.randn(pages, 2, nkv, 16, D, device=dev).to(torch.bfloat16)
+            bt = torch.arange(pages, device=dev, dtype=torch.int32).reshape(S, L // 16).contiguous()
+            q = rnd(S * L, nq * D)
+            o = torch.empty_like(q)
+            qs = torch.arange(S, device=dev, dtype=torch.int32) * L
+            ql = torch.full((S,), L, dtype=torch.int32, device=dev)
+            t = _time(lambda: ops.paged_prefill(q, kv, bt, qs, ql, ql, max_q_len=L, n_q=nq, n_kv=nkv, out=o), iters)
+            fl = 4 * S * L * L * D * nq / 2
+            out.update(seqs=S, len=L, us=t * 1e6, tflops=fl / t / 1e12, frac_of_bf16_peak=fl / t / 1e12 / tf)
+    elif op == "sample":
+        B, V = 256, 151936
+        lg = torch.randn(B, V, device=dev)
+        params = torch.tensor([0.7, 50, 0.9, 0], device=dev).repeat(B, 1).contiguous()
+        t = _time(lambda: ops.sample(lg, params, seed=1), iters)
+        out.update(batch=B, vocab=V, us=t * 1e6, logits_gbs=B * V * 4 / t / 1e9)
+    else:
+        raise SystemExit(f"unknown op {op}")
+    from . import _native as nv
+    out["device_error"] = nv.device_error()
+    print(json.dumps(out))
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    run(a.op, a.iters)
