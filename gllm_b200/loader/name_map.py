@@ -56,9 +56,9 @@ class TensorRole(str, Enum):
 
 # (regex on the part after the layer prefix, canonical suffix, role)
 _LAYER_RULES = [
-    (r"(self_attn|attention|attn)\.(q_proj|query|wq|q)$|^attn_q$", "q_proj", TensorRole.ATTN_QUERY),
-    (r"(self_attn|attention|attn)\.(k_proj|key|wk|k)$|^attn_k$", "k_proj", TensorRole.ATTN_KEY),
-    (r"(self_attn|attention|attn)\.(v_proj|value|wv|v)$|^attn_v$", "v_proj", TensorRole.ATTN_VALUE),
+    (r"(self_attn|attention\.self|attention|attn)\.(q_proj|query|wq|q)$|^attn_q$", "q_proj", TensorRole.ATTN_QUERY),
+    (r"(self_attn|attention\.self|attention|attn)\.(k_proj|key|wk|k)$|^attn_k$", "k_proj", TensorRole.ATTN_KEY),
+    (r"(self_attn|attention\.self|attention|attn)\.(v_proj|value|wv|v)$|^attn_v$", "v_proj", TensorRole.ATTN_VALUE),
     (r"(self_attn|attention|attn)\.(o_proj|out_proj|wo|dense|output\.dense)$|^attn_output$", "o_proj",
      TensorRole.ATTN_OUTPUT),
     (r"(self_attn|attention|attn)\.(qkv_proj|query_key_value|c_attn|Wqkv)$|^attn_qkv$", "qkv_proj",

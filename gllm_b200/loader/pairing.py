@@ -92,7 +92,7 @@ def dequant_gptq(qweight, scales, qzeros, g_idx=None) -> torch.Tensor:
     w = qweight.t().contiguous()                                      # [N, K/8]
     q = _unpack_int32_nibbles(w).float()                              # [N, K]
     K = q.shape[1]
-    z = _unpack_int32_nibbles(qzeros).float() + 1.0                   # [K/g, N]
+    z = ((_unpack_int32_nibbles(qzeros).to(torch.int32) + 1) & 0xF).float()   # stored as (zero - 1) mod 16
     if g_idx is None:
         g = K // scales.shape[0]
         g_idx = torch.arange(K) // g

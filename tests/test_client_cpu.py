@@ -1,0 +1,128 @@
+"""Client surface on CPU with synthetic tiny models: generate / stream / hooks / sessions / batch / embed / rerank / classify."""
+import torch
+
+from gllm_b200.client import AsyncClient, Client, GllmError, InvalidModelTypeError, NoModelLoadedError
+from gllm_b200.engine.batch import GenerateRequest
+from gllm_b200.generation import GenerationHook, HookDecision, split_thinking_content
+from gllm_b200.models.config import preset
+from gllm_b200.models.registry import ModelKind
+from gllm_b200.models.weights import RandomWeights
+import pytest
+
+
+def _chat():
+    cfg = preset("tiny-qwen3")
+    return Client.from_model(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=3), device="cpu", dtype=torch.float32,
+                             max_num_seqs=4, max_model_len=256, max_batch_tokens=64)
+
+
+def test_generate_defaults_greedy_determinism_and_stream():
+    c = _chat()
+    b = c.generate("hello")
+    assert (b._max_tokens, b._temperature, b._top_k, b._top_p) == (256, 0.7, 0, 1.0)   # reference defaults
+    r1 = c.generate("hello world").max_tokens(6).temperature(0.0).generate()
+    r2 = c.generate("hello world").max_tokens(6).temperature(0.0).generate()
+    assert r1.token_ids == r2.token_ids and len(r1.token_ids) <= 6 and r1.prompt_tokens == 11
+    assert r2.cached_prefix_tokens == 0          # 11 tokens never fill a 16-token page
+    pieces = list(c.generate("hello world").max_tokens(6).temperature(0.0).stream().generate())
+    assert "".join(pieces) == r1.text
+    sampled = c.generate("hello world").max_tokens(6).temperature(0.9).top_k(5).top_p(0.9).generate()
+    assert len(sampled.token_ids) <= 6
+
+
+def test_hooks_veto_and_terminate_and_length_guard():
+    c = _chat()
+
+    class StopAt(GenerationHook):
+        def __init__(self, n, how):
+            self.n, self.how = n, how
+
+        def post_step(self, token_id, n_generated):
+            return self.how if n_generated == self.n else HookDecision.CONTINUE
+    full = c.generate("abc").max_tokens(8).temperature(0.0).generate()
+    t = c.generate("abc").max_tokens(8).temperature(0.0).hook(StopAt(3, HookDecision.TERMINATE)).generate()
+    v = c.generate("abc").max_tokens(8).temperature(0.0).hook(StopAt(3, HookDecision.VETO)).generate()
+    assert t.token_ids == full.token_ids[:3] and t.finish_reason == "terminate"
+    assert v.token_ids == full.token_ids[:2] and v.finish_reason == "veto"   # the vetoed token is dropped
+    with pytest.raises(GllmError):
+        c.generate("x" * 300).max_tokens(10).generate()
+
+
+def test_generate_batch_matches_single_and_session_prefix_reuse():
+    c = _chat()
+    prompts = ["the quick brown fox jumps over the lazy dog " * 2, "short", "another prompt of medium length here"]
+    singles = [c.generate(p).max_tokens(5).temperature(0.0).generate().token_ids for p in prompts]
+    batch = c.generate_batch([GenerateRequest(prompt=p, max_tokens=5, temperature=0.0) for p in prompts])
+    eos = c._st().tokenizer.eos_ids(c._st().model.cfg.eos_token_ids)
+    strip = lambda t: t[:-1] if t and t[-1] in eos else t
+    assert [strip(r.token_ids) for r in batch] == singles
+    # second turn of a conversation re-uses the cached pages of the first
+    first = c.generate(prompts[0]).max_tokens(4).temperature(0.0).session_id("s1").generate()
+    second = c.generate(prompts[0] + " and more").max_tokens(4).temperature(0.0).session_id("s1").generate()
+    assert second.cached_prefix_tokens >= 64 and first.token_ids
+
+
+def test_embed_rerank_classify_with_encoder():
+    cfg = preset("tiny-bert")
+    cfg.num_labels = 3
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=5)
+
+    class Enc:  # canonical names of an encoder checkpoint on top of the random generator
+        shapes = {"position_embeddings": (512, 128), "token_type_embeddings": (2, 128), "embed_norm": (128,),
+                  "embed_norm_bias": (128,), "classifier": (3, 128), "classifier_bias": (3,), "pooler": (128, 128),
+                  "pooler_bias": (128,)}
+
+        def has(self, n):
+            base = n.split(".")[-1]
+            return n in self.shapes or base in ("q_proj", "k_proj", "v_proj", "o_proj", "up_proj", "down_proj",
+                                                "post_attn_norm", "post_ffn_norm", "embed_tokens") or base.endswith("_bias")
+
+        def get(self, n):
+            base = n.split(".")[-1]
+            if n in self.shapes:
+                return src._gen(n, self.shapes[n], ones=n.endswith("norm"))
+            if base.endswith("_bias"):
+                stem = base[:-5]
+                dim = {"up_proj": 256, "post_attn_norm": 128, "post_ffn_norm": 128}.get(stem, 128)
+                return src._gen(n, (dim,))
+            if base in ("post_attn_norm", "post_ffn_norm"):
+                return src._gen(n, (128,), ones=True)
+            return src.get(n)
+    c = Client.from_model(cfg, Enc(), kind=ModelKind.CLASSIFIER, device="cpu", dtype=torch.float32)
+    e = c.embed(["hello", "a longer sentence for the encoder"]).generate()
+    assert len(e) == 2 and len(e[0]) == 128 and abs(sum(x * x for x in e[0]) - 1.0) < 1e-4
+    e64 = c.embed(["hello"]).dimension(64).generate()
+    assert len(e64[0]) == 64 and abs(sum(x * x for x in e64[0]) - 1.0) < 1e-4
+    raw = c.embed(["hello"]).normalize(False).generate()[0]
+    assert abs(sum(x * x for x in raw) - 1.0) > 1e-3
+    # batched encoding equals one-at-a-time encoding (flat varlen batch with bidirectional attention)
+    one = c.embed(["a longer sentence for the encoder"]).generate()[0]
+    assert max(abs(a - b) for a, b in zip(one, e[1])) < 1e-4
+    rr = c.rerank("query", ["doc one", "doc two", "doc three"]).top_n(2).generate()
+    assert len(rr) == 2 and rr[0].score >= rr[1].score and rr[0].document.startswith("doc")
+    cl = c.classify(["some text", "other"]).generate()
+    assert len(cl) == 2 and 0 <= cl[0].label < 3 and abs(sum(cl[0].probabilities) - 1) < 1e-5
+    with pytest.raises(InvalidModelTypeError):
+        c.generate("x").generate()
+
+
+def test_misc_api():
+    with pytest.raises(NoModelLoadedError):
+        Client().encode("x")
+    c = _chat()
+    assert c.decode(c.encode("round trip")) == "round trip"
+    assert split_thinking_content("<think>plan</think> answer") == ("plan", "answer")
+    assert split_thinking_content("plan</think>answer") == ("plan", "answer")
+    ac = AsyncClient(c)
+    f = ac.generate("hi", max_tokens=3, temperature=0.0)
+    assert len(f.result(timeout=60).token_ids) <= 3
+    ac.shutdown()
+    d = c.diagnostics()
+    assert d["backend"] == "cpu" and d["stats"]["decode_steps"] > 0
+    s = c.score_tokens("hello", [1, 2, 3])
+    assert len(s) == 3
+    h = c.encode_to_layer(["hello there"], layer=0)
+    assert h.shape == (1, 256)
+    c.unload_model()
+    with pytest.raises(NoModelLoadedError):
+        c.generate("x").generate()
