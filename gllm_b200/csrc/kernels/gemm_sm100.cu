@@ -609,7 +609,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int ks, m_sup, n_blk, kb0, kb1;
         decode_item(t, ks, m_sup, n_blk, kb0, kb1);
         int b_row = n_blk * BN;
-        if (p.mblk_group) b_row += p.mblk_group[m_sup * MT] * p.group_rows;
+        if (p.mblk_group) {
+          const int grp = p.mblk_group[m_sup * MT];
+          if (grp < 0) continue;  // inactive row block of a grouped GEMM (fewer routed rows than the launch was sized for)
+          b_row += grp * p.group_rows;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_SMEM_EMPTY)) {
             ok = false;
@@ -638,11 +642,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
         int ks, m_sup, n_blk, kb0, kb1;
         decode_item(t, ks, m_sup, n_blk, kb0, kb1);
-        const int acc = it % kAcc;
-        const uint32_t acc_phase = (it / kAcc) & 1;
+        if (p.mblk_group && p.mblk_group[m_sup * MT] < 0) continue;  // skipped by every role alike
+        const int it_cur = it++;
+        const int acc = it_cur % kAcc;
+        const uint32_t acc_phase = (it_cur / kAcc) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_TMEM_EMPTY)) {
           ok = false;
           break;
@@ -684,11 +690,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
       int ks, m_sup, n_blk, kb0, kb1;
       decode_item(t, ks, m_sup, n_blk, kb0, kb1);
-      const int acc = it % kAcc;
-      const uint32_t acc_phase = (it / kAcc) & 1;
+      if (p.mblk_group && p.mblk_group[m_sup * MT] < 0) continue;  // skipped by every role alike
+      const int it_cur = it++;
+      const int acc = it_cur % kAcc;
+      const uint32_t acc_phase = (it_cur / kAcc) & 1;
       // warp-uniform decision: tcgen05.ld below is warp-collective
       const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, ERR_TIMEOUT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) {

@@ -1,0 +1,138 @@
+"""Mixture-of-experts FFN block (Qwen3-MoE / Mixtral / DeepSeek-style) for the decoder.
+
+Per token: router -> top-k -> the k experts' SwiGLU FFNs -> weighted sum (+ shared expert), added to the
+residual stream. Expert weights are stacked ``[E_local * 2I, H]`` (tile-interleaved gate/up) and
+``[E_local * H, I]`` so one grouped tcgen05 GEMM serves every routed row; with expert parallelism each rank
+holds ``E / ep`` experts and ``parallel/expert_parallel.py`` moves the rows.
+
+Reference parity: MoEGate -> TopK -> masked per-expert template -> MoEConditionalAdd + shared expert
+(src/arch/auto_graph_fragments/build_graph.inc.rs:2046-2178), scalar semantics
+(src/compat/scalar_ops.rs:70-181).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..ops import linear as L
+from ..ops import moe as M
+from .config import ModelConfig
+from .weights import _fold, layer_prefix, shard_range
+
+
+@dataclass
+class MoeLayerWeights:
+    router: torch.Tensor                 # [E, H] (post-attention norm folded in when fused)
+    router_bias: Optional[torch.Tensor]  # selection bias (DeepSeek) fp32 [E]
+    w_gate_up: torch.Tensor              # [E_local * 2I, H], per expert tile-interleaved
+    w_down: torch.Tensor                 # [E_local * H, I]
+    glu_bn: int
+    e0: int
+    e_local: int
+    inter: int
+    shared_gate_up: Optional[torch.Tensor] = None
+    shared_down: Optional[torch.Tensor] = None
+    shared_bn: int = 128
+    cfg: Optional[ModelConfig] = None
+    fused: bool = True
+    ep: Optional[object] = None
+    _ws: Optional[M.MoeWorkspace] = None
+
+    # ------------------------------------------------------------------------------------------
+    def workspace(self, model, T):
+        holder = model.__dict__.setdefault("_moe_ws", {})
+        key = (self.e_local, self.inter)
+        ws = holder.get(key)
+        if ws is None or ws.ids.shape[0] < T:
+            c = self.cfg
+            ws = M.MoeWorkspace(max(T, 256), c.num_experts_per_tok, c.hidden_size, self.inter, self.e_local,
+                                model.device, model.dtype)
+            ws.logits = torch.zeros((max(T, 256), self.router.shape[0]), dtype=torch.float32, device=model.device)
+            holder[key] = ws
+        return ws
+
+    def _route(self, x, row_ss, ws, T, norm_dim, eps):
+        c = self.cfg
+        logits = ops.gemm(x, self.router, out=ws.logits[:T], out_dtype=torch.float32, row_ss=row_ss,
+                          norm_dim=norm_dim, eps=eps, bn=128)
+        E = c.num_experts
+        return M.route(logits[:, :E], c.num_experts_per_tok, norm_topk=c.norm_topk_prob, scoring=c.router_scoring,
+                       sel_bias=self.router_bias, scale=c.routed_scaling_factor,
+                       out_ids=ws.ids[:T] if x.is_cuda else None, out_w=ws.w[:T] if x.is_cuda else None)
+
+    def forward(self, model, x, ss_in, ss_out, T):
+        """Fused path: ``x`` is the residual stream (bf16), ``ss_in`` its row statistics; the post-attention
+        RMSNorm is folded into the router and gate/up weights. Returns the statistics tensor of the new x."""
+        c = self.cfg
+        H = c.hidden_size
+        ws = self.workspace(model, T)
+        ids, w = self._route(x, ss_in, ws, T, H, c.rms_norm_eps)
+        if self.ep is not None:
+            return self.ep.moe_forward(self, model, x, ss_in, ss_out, ids, w, ws, T)
+        M.permute(x, ss_in, ids, ws, self.e0, self.e_local)
+        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, row_ss=ws.ss_perm, norm_dim=H,
+                   eps=c.rms_norm_eps, bn=self.glu_bn, mblk_group=ws.blk_group, num_groups=self.e_local)
+        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        shared = None
+        if self.shared_gate_up is not None:
+            sa = L.gemm_glu(x, self.shared_gate_up, act=model.act_id, row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps,
+                            bn=self.shared_bn)
+            shared = ops.gemm(sa, self.shared_down, bn=128)
+        ss = ss_out.reshape(-1)[:T].view(T, 1)
+        M.combine(x, ws.y_perm, ws.dest, w, shared=shared, ss_out=ss)
+        return ss
+
+    def forward_unfused(self, model, x, h, T):
+        """Unfused path: ``h`` is the already normalised input; adds the MoE output into ``x``."""
+        c = self.cfg
+        ws = self.workspace(model, T)
+        ids, w = self._route(h, None, ws, T, 0, 0.0)
+        M.permute(h, None, ids, ws, self.e0, self.e_local)
+        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
+                   num_groups=self.e_local)
+        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        shared = None
+        if self.shared_gate_up is not None:
+            sa = L.gemm_glu(h, self.shared_gate_up, act=model.act_id, bn=self.shared_bn)
+            shared = ops.gemm(sa, self.shared_down, out_dtype=x.dtype, bn=128)
+        M.combine(x, ws.y_perm, ws.dest, w, shared=shared)
+
+
+def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, device, dtype, ep=None, fused=True):
+    """Experts are split over the expert-parallel group (``ep``), or kept whole when there is none; the shared
+    expert and the router are replicated."""
+    p = layer_prefix(i)
+    ep_rank, ep_size = (ep.rank, ep.size) if ep is not None else (0, 1)
+    e0, e1 = shard_range(cfg.num_experts, ep_rank, ep_size)
+    post = src.get(p + "post_attn_norm").float().to(device)
+    inter = cfg.moe_intermediate_size
+    bn = 256 if inter % 128 == 0 else 128
+    gus, downs = [], []
+    for e in range(e0, e1):
+        g = src.get(f"{p}experts.{e}.gate_proj").to(device, dtype)
+        u = src.get(f"{p}experts.{e}.up_proj").to(device, dtype)
+        d = src.get(f"{p}experts.{e}.down_proj").to(device, dtype)
+        if fused:
+            g, u = _fold(g, post, cfg.norm_one_plus_w), _fold(u, post, cfg.norm_one_plus_w)
+        gus.append(L.interleave_gate_up(g, u, bn))
+        downs.append(L.pad_rows(d, 128))
+    router = src.get(p + "router").to(device, dtype)
+    if fused:
+        router = _fold(router, post, cfg.norm_one_plus_w)
+    router = L.pad_rows(router, 128).contiguous()
+    rb = src.get(p + "router_bias").float().to(device) if src.has(p + "router_bias") else None
+    lw = MoeLayerWeights(router=router, router_bias=rb, w_gate_up=torch.cat(gus, 0).contiguous(),
+                         w_down=torch.cat(downs, 0).contiguous(), glu_bn=bn, e0=e0, e_local=e1 - e0, inter=inter,
+                         cfg=cfg, fused=fused, ep=ep)
+    if cfg.num_shared_experts and src.has(p + "shared_expert.gate_proj"):
+        g = src.get(p + "shared_expert.gate_proj").to(device, dtype)
+        u = src.get(p + "shared_expert.up_proj").to(device, dtype)
+        if fused:
+            g, u = _fold(g, post, cfg.norm_one_plus_w), _fold(u, post, cfg.norm_one_plus_w)
+        lw.shared_bn = 256 if g.shape[0] % 128 == 0 else 128
+        lw.shared_gate_up = L.interleave_gate_up(g, u, lw.shared_bn)
+        lw.shared_down = L.pad_rows(src.get(p + "shared_expert.down_proj").to(device, dtype), 128).contiguous()
+    return lw

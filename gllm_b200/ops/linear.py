@@ -156,10 +156,12 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
         N = w_packed.shape[0] // num_groups
     if not a.is_cuda:
         rs = row_scale_ref(row_ss, norm_dim, eps)
-        res = torch.empty((M, N // 2), dtype=a.dtype)
+        res = torch.zeros((M, N // 2), dtype=a.dtype)
         groups = [(0, M, 0)] if mblk_group is None else [
             (i * 128, min(M, (i + 1) * 128), int(mblk_group[i])) for i in range((M + 127) // 128)]
         for (r0, r1, g) in groups:
+            if g < 0:  # inactive row block of a grouped launch
+                continue
             wg = w_packed[g * N:(g + 1) * N]
             gw, uw = deinterleave_gate_up(wg, bn)
             x = a[r0:r1].float()
@@ -188,11 +190,12 @@ def gemm_grouped(a, w_stack, mblk_group, num_groups, *, out=None, bn=128, max_ct
     M, K = a.shape
     N = w_stack.shape[0] // num_groups
     if not a.is_cuda:
-        res = torch.empty((M, N), dtype=a.dtype)
+        res = torch.zeros((M, N), dtype=a.dtype)
         for i in range((M + 127) // 128):
             g = int(mblk_group[i])
-            res[i * 128:(i + 1) * 128] = (a[i * 128:(i + 1) * 128].float() @ w_stack[g * N:(g + 1) * N].float().t()).to(
-                torch.bfloat16)
+            if g < 0:
+                continue
+            res[i * 128:(i + 1) * 128] = (a[i * 128:(i + 1) * 128].float() @ w_stack[g * N:(g + 1) * N].float().t()).to(a.dtype)
         if out is not None:
             out.copy_(res)
             return out

@@ -1,0 +1,76 @@
+"""MoE block on CPU: routing semantics, permutation into 128-row expert blocks, and the full layer against
+the reference's dense-masked formulation (loop over all experts with gate masks)."""
+import torch
+import torch.nn.functional as F
+
+from gllm_b200.models.config import preset
+from gllm_b200.models.decoder import DecoderModel
+from gllm_b200.models.weights import RandomWeights
+from gllm_b200.ops import moe as M
+
+
+def test_route_softmax_topk_renorm_and_sigmoid_bias():
+    torch.manual_seed(0)
+    lg = torch.randn(9, 16)
+    ids, w = M.route_ref(lg, 4)
+    p = torch.softmax(lg, -1)
+    tv, ti = torch.topk(p, 4, -1)
+    assert torch.equal(ids.long(), ti)
+    torch.testing.assert_close(w, tv / tv.sum(-1, keepdim=True))
+    assert torch.allclose(w.sum(-1), torch.ones(9))
+    ids2, w2 = M.route_ref(lg, 4, norm_topk=False)
+    torch.testing.assert_close(w2, tv)
+    bias = torch.zeros(16); bias[5] = 10.0
+    ids3, w3 = M.route_ref(lg, 2, scoring="sigmoid", sel_bias=bias, scale=2.5)
+    assert (ids3[:, 0] == 5).all()                                   # the bias steers selection ...
+    s = torch.sigmoid(lg)
+    picked = torch.gather(s, 1, ids3.long())
+    torch.testing.assert_close(w3, picked / picked.sum(-1, keepdim=True) * 2.5)   # ... but not the weights
+
+
+def test_permute_blocks_belong_to_one_expert():
+    torch.manual_seed(1)
+    T, k, H, E = 37, 2, 64, 6
+    x = torch.randn(T, H)
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32)
+    ws = M.MoeWorkspace(T, k, H, 32, E, "cpu", torch.float32)
+    M.permute(x, None, ids, ws, 0, E)
+    offs = ws.offsets.tolist()
+    assert all(o % 128 == 0 for o in offs) and offs[-1] == int(ws.total_rows[0])
+    dest = ws.dest[:T * k].reshape(T, k)
+    for t in range(T):
+        for j in range(k):
+            d, e = int(dest[t, j]), int(ids[t, j])
+            assert offs[e] <= d < offs[e + 1] and torch.equal(ws.a_perm[d], x[t])
+            assert int(ws.blk_group[d // 128]) == e
+    assert len(set(dest.reshape(-1).tolist())) == T * k
+    assert (ws.blk_group[offs[-1] // 128:] == -1).all()
+    # expert-parallel view: only experts [2, 4) are local, other pairs get dest -1
+    ws2 = M.MoeWorkspace(T, k, H, 32, 2, "cpu", torch.float32)
+    M.permute(x, None, ids, ws2, 2, 2)
+    local = (ids >= 2) & (ids < 4)
+    assert torch.equal(ws2.dest[:T * k].reshape(T, k) >= 0, local)
+
+
+def test_moe_layer_matches_dense_masked_reference_and_generates():
+    cfg = preset("tiny-moe")
+    cfg.num_shared_experts = 1
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    m = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256)
+    x = torch.randn(11, cfg.hidden_size)
+    p = "L1."
+    h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * src.get(p + "post_attn_norm")
+    probs = torch.softmax(h @ src.get(p + "router").t(), -1)
+    w, ids = torch.topk(probs, cfg.num_experts_per_tok, -1)
+    w = w / w.sum(-1, keepdim=True)
+    ffn = lambda pre, v: (F.silu(v @ src.get(pre + "gate_proj").t()) * (v @ src.get(pre + "up_proj").t())) @ src.get(pre + "down_proj").t()
+    want = x + ffn(p + "shared_expert.", h)
+    for e in range(cfg.num_experts):
+        want = want + ((w * (ids == e)).sum(-1, keepdim=True)) * ffn(f"{p}experts.{e}.", h)
+    got = x.clone()
+    m.layers[1].moe.forward_unfused(m, got, h, 11)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    eng = LLMEngine(m, EngineConfig(max_num_seqs=4, max_model_len=128, max_batch_tokens=64, prefill_chunk=32))
+    out = eng.generate_batch([[1, 2, 3, 4, 5], list(range(40))], max_tokens=4, temperature=0.0, eos_ids=[])
+    assert [len(r.token_ids) for r in out] == [4, 4]
