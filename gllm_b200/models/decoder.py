@@ -78,11 +78,17 @@ class DecoderModel:
         self.res_bn = 256 if cfg.hidden_size % 256 == 0 else 128  # tile width of the residual GEMMs
         self.scale = cfg.attention_scale()
 
-        to = lambda t: t.to(self.device, dtype if t.is_floating_point() and t.dtype != torch.float32 else None)
-        self.embed = to(src.get("embed_tokens")).contiguous() if self.first_stage or cfg.tie_word_embeddings else None
+        self.embed = (src.get("embed_tokens").to(self.device, dtype).contiguous()
+                      if self.first_stage or cfg.tie_word_embeddings else None)
         self.layers: List[DenseLayerWeights] = []
         for i in self.layer_ids:
             lw = pack_dense_layer(cfg, src, i, self.tp_rank, self.tp_size, self.fused)
+            # the source may live on the host (checkpoint files): every packed tensor moves to the model's
+            # device here; fp32 tensors (norm weights, biases) stay fp32, the rest takes the compute dtype
+            for name, val in list(vars(lw).items()):
+                if isinstance(val, torch.Tensor):
+                    setattr(lw, name, val.to(self.device, None if val.dtype == torch.float32 and (
+                        name.endswith("norm") or name.endswith("bias")) else (dtype if val.is_floating_point() else None)).contiguous())
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,

@@ -99,11 +99,20 @@ def register(name, restype, argtypes, optional=False):
 CALLS = [0]  # number of kernel-launching entry points called so far (bench.py reports launches)
 
 
+_SYNC_EACH_CALL = __import__("os").environ.get("GLLM_SYNC_EACH_CALL", "0") == "1"
+
+
 def check(rc: int, what: str):
     CALLS[0] += 1
     if rc != 0:
         msg = lib().gllm_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"{what} failed: {msg}")
+    if _SYNC_EACH_CALL:  # debugging aid: attribute an asynchronous fault to the call that caused it
+        import torch
+        try:
+            torch.cuda.synchronize()
+        except RuntimeError as e:
+            raise RuntimeError(f"{what}: device fault surfaced right after this call: {e}") from e
 
 
 def device_error() -> int:

@@ -54,6 +54,13 @@ def deinterleave_gate_up(w: torch.Tensor, bn: int = 256):
     return t[:, 0].reshape(n // 2, k), t[:, 1].reshape(n // 2, k)
 
 
+def _on_device(a, **tensors):
+    """A host tensor handed to a device kernel is an illegal address on the GPU: refuse it on the host."""
+    for name, t in tensors.items():
+        if t is not None and t.device != a.device:
+            raise ValueError(f"{name} is on {t.device} but the activations are on {a.device}")
+
+
 def row_scale_ref(row_ss, norm_dim, eps):
     if row_ss is None:
         return None
@@ -85,6 +92,7 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
         return res
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert a.stride(-1) == 1 and w.stride(-1) == 1
+    _on_device(a, weight=w, bias=bias, row_ss=row_ss, out=out)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
     bn = bn or _bn_for(N, M)
@@ -122,6 +130,7 @@ def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=No
             row_ss_out[:M, :parts].copy_(ss)
             ss = row_ss_out
         return res, ss
+    _on_device(a, weight=w, residual=residual, bias=bias, out=out, row_ss_out=row_ss_out)
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     if row_ss_out is None:
@@ -173,6 +182,7 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
             out.copy_(res)
             return out
         return res
+    _on_device(a, weight=w_packed, row_ss=row_ss, out=out, mblk_group=mblk_group)
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
@@ -200,6 +210,7 @@ def gemm_grouped(a, w_stack, mblk_group, num_groups, *, out=None, bn=128, max_ct
             out.copy_(res)
             return out
         return res
+    _on_device(a, weight=w_stack, mblk_group=mblk_group, out=out)
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     rc = nv.lib().gllm_gemm_bf16_grouped(a.data_ptr(), a.stride(0), w_stack.data_ptr(), w_stack.stride(0),
@@ -261,6 +272,8 @@ def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, c
         if slot_mapping is not None:
             kv_write_ref(kv_cache, k, v, slot_mapping)
         return q_out
+    _on_device(a, weight=w_qkv, q_out=q_out, kv_cache=kv_cache, slot_mapping=slot_mapping, positions=positions,
+               cos=cos_t, sin=sin_t, q_norm=q_norm_w, k_norm=k_norm_w, row_ss=row_ss, bias=bias)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
     nv.ensure_splitk_workspace(a.device)
     rc = nv.lib().gllm_gemm_bf16_qkv(a.data_ptr(), a.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), M, K, n_q, n_kv,

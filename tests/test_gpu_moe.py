@@ -78,3 +78,35 @@ def test_moe_decoder_fused_matches_cpu_oracle():
     cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
     assert cos > 0.995, cos
     assert (a.argmax(-1) == b.argmax(-1)).float().mean() > 0.8
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-llama"])
+def test_dense_decoder_fused_matches_cpu_oracle(name):
+    """Whole fused GPU forward (bf16) against the fp32 CPU oracle, layer by layer."""
+    from gllm_b200.engine.batch import ForwardBatch
+    cfg = preset(name)
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    ref = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256)
+    gpu = DecoderModel(cfg, src, device=DEV, dtype=torch.bfloat16, max_positions=256)
+    assert gpu.fused
+    T = 150
+    ids = torch.randint(0, cfg.vocab_size, (T,), dtype=torch.int32)
+
+    def run(m, dev):
+        kv = m.alloc_kv_cache(12)
+        b = ForwardBatch(token_ids=ids.to(dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                         slot_mapping=torch.arange(T, dtype=torch.int32, device=dev),
+                         block_tables=torch.arange(12, dtype=torch.int32, device=dev)[None],
+                         ctx_lens=torch.tensor([T], dtype=torch.int32, device=dev),
+                         q_start=torch.tensor([0], dtype=torch.int32, device=dev),
+                         q_len=torch.tensor([T], dtype=torch.int32, device=dev), max_q_len=T)
+        lg = m.forward(b, kv, capture_layers=set(range(cfg.num_layers)))
+        return lg[:, :cfg.vocab_size].float().cpu(), {k: v.float().cpu() for k, v in m.captured.items()}
+    la, ca = run(gpu, torch.device(DEV))
+    lb, cb = run(ref, torch.device("cpu"))
+    for l in ca:
+        assert not torch.isnan(ca[l]).any()
+        cos = torch.nn.functional.cosine_similarity(ca[l].flatten(), cb[l].flatten(), dim=0).item()
+        assert cos > 0.998, (l, cos)
+    assert torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0).item() > 0.995
+    assert (la.argmax(-1) == lb.argmax(-1)).float().mean() > 0.85
