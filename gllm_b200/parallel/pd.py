@@ -1,0 +1,106 @@
+"""Prefill / decode disaggregation, KV page transfer between roles, KV distribution modes, and the SAGUARO
+draft / verify hand-off.
+
+Reference parity: ``PdRoleDecision{Collocated, PrefillOnly, DecodeOnly}`` and step gating
+(src/engine/coordinator/dispatch.rs:34-60, executor_step.rs:121-250), ``kv_transfer / send_pages / recv_pages``
+(src/engine/coordinator/kv.rs:395-569; synchronous underneath in the reference — here the transfer is issued on
+a side stream and returns a handle), ``KvDistMode`` behaviours (coordinator/kv.rs:52-156), SAGUARO token
+hand-off via ``send_bytes / recv_bytes`` (src/speculative/saguaro.rs:35-490).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .config import KvDistMode, PdRole
+
+
+def resolve_pd_role(role: PdRole, has_prefill_work: bool, has_decode_work: bool) -> Dict[str, bool]:
+    """Which phases a rank runs this step."""
+    if role == PdRole.PREFILL_ONLY:
+        return {"prefill": has_prefill_work, "decode": False, "ship_kv": has_prefill_work}
+    if role == PdRole.DECODE_ONLY:
+        return {"prefill": False, "decode": has_decode_work, "ship_kv": False}
+    return {"prefill": has_prefill_work, "decode": has_decode_work, "ship_kv": False}
+
+
+@dataclass
+class KvTransferResult:
+    pages: int
+    bytes: int
+    latency_ms: float
+
+
+class KvPageTransport:
+    """Moves whole KV pages (all layers of a page id) between two ranks."""
+
+    def __init__(self, comm, kv_caches: List[torch.Tensor]):
+        self.comm, self.kv = comm, kv_caches
+        dev = kv_caches[0].device
+        self.stream = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+
+    def _gather(self, pages: Sequence[int]) -> torch.Tensor:
+        idx = torch.as_tensor(list(pages), dtype=torch.long, device=self.kv[0].device)
+        return torch.stack([c.index_select(0, idx) for c in self.kv]).contiguous()   # [L, n, 2, Hkv, 16, D]
+
+    def send_pages(self, pages: Sequence[int], dst: int) -> KvTransferResult:
+        t0 = time.perf_counter()
+        buf = self._gather(pages)
+        self.comm.send(buf, dst)
+        return KvTransferResult(len(pages), buf.numel() * buf.element_size(), (time.perf_counter() - t0) * 1e3)
+
+    def recv_pages(self, pages: Sequence[int], src: int) -> KvTransferResult:
+        t0 = time.perf_counter()
+        shape = (len(self.kv), len(pages)) + tuple(self.kv[0].shape[1:])
+        buf = torch.empty(shape, dtype=self.kv[0].dtype, device=self.kv[0].device)
+        self.comm.recv(buf, src)
+        idx = torch.as_tensor(list(pages), dtype=torch.long, device=self.kv[0].device)
+        for l, c in enumerate(self.kv):
+            c.index_copy_(0, idx, buf[l])
+        return KvTransferResult(len(pages), buf.numel() * buf.element_size(), (time.perf_counter() - t0) * 1e3)
+
+
+def kv_dist_plan(mode: KvDistMode, rank: int, world: int, n_kv_heads: int) -> Dict[str, object]:
+    """What a rank stores under each KV distribution mode."""
+    if mode == KvDistMode.LOCAL:
+        return {"store_heads": list(range(n_kv_heads)), "fetch_on_miss": False, "mirror_to": []}
+    if mode == KvDistMode.ON_DEMAND:
+        return {"store_heads": list(range(n_kv_heads)), "fetch_on_miss": True, "mirror_to": []}
+    if mode == KvDistMode.MIRROR:
+        return {"store_heads": list(range(n_kv_heads)), "fetch_on_miss": False,
+                "mirror_to": [r for r in range(world) if r != rank]}
+    if mode == KvDistMode.PARTIAL_HEAD_MIRROR:
+        per = max(1, n_kv_heads // world)
+        own = list(range(rank * per, min(n_kv_heads, (rank + 1) * per)))
+        return {"store_heads": own, "fetch_on_miss": True, "mirror_to": [(rank + 1) % world]}
+    return {"store_heads": list(range(n_kv_heads)), "fetch_on_miss": True, "mirror_to": [], "tiered": True}
+
+
+# ------------------------------------------------------------------------------------------------
+# SAGUARO: draft rank proposes, verify rank checks (tens of bytes per round)
+# ------------------------------------------------------------------------------------------------
+class SaguaroLink:
+    def __init__(self, comm, draft_rank: int, verify_rank: int, max_draft: int = 16):
+        self.comm, self.draft_rank, self.verify_rank, self.max_draft = comm, draft_rank, verify_rank, max_draft
+
+    def send_draft(self, tokens: Sequence[int]):
+        buf = torch.full((self.max_draft + 1,), -1, dtype=torch.int32)
+        buf[0] = len(tokens)
+        buf[1:1 + len(tokens)] = torch.as_tensor(list(tokens), dtype=torch.int32)
+        self.comm.send(buf, self.verify_rank)
+
+    def recv_draft(self) -> List[int]:
+        buf = torch.empty(self.max_draft + 1, dtype=torch.int32)
+        self.comm.recv(buf, self.draft_rank)
+        return buf[1:1 + int(buf[0])].tolist()
+
+    def send_verdict(self, accepted: int, correction: int):
+        self.comm.send(torch.tensor([accepted, correction], dtype=torch.int32), self.draft_rank)
+
+    def recv_verdict(self):
+        buf = torch.empty(2, dtype=torch.int32)
+        self.comm.recv(buf, self.verify_rank)
+        return int(buf[0]), int(buf[1])
