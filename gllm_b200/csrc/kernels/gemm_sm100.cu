@@ -93,6 +93,11 @@ struct GemmParams {
   unsigned long long* ar_state;           // local {expected arrivals, launch index}
   int ar_rank;
   long long ar_buf_elems;                 // elements of one partial buffer (two alternate per launch)
+  // row scatter (expert-parallel return path): output row m goes to scatter_peer[meta >> 24] + (meta & 0xFFFFFF) * ldo
+  // where meta = scatter_meta[m]; a negative meta drops the row. The stores go straight into the token owner's
+  // memory over NVLink as each tile retires.
+  const int* scatter_meta;
+  __nv_bfloat16* scatter_peer[8];
   int* err;
 };
 
@@ -790,7 +795,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   ss += v[j] * v[j];
                 }
               }
-              if (row_ok) {
+              if (p.scatter_meta) {
+                if (row_ok) {
+                  const int meta = p.scatter_meta[m];
+                  if (meta >= 0)
+                    store_bf16x32(p.scatter_peer[meta >> 24] + static_cast<long long>(meta & 0xFFFFFF) * p.ldo + n0, v);
+                }
+              } else if (row_ok) {
                 if (p.out_f32) {
                   float4* o4 =
                       reinterpret_cast<float4*>(static_cast<float*>(p.out) + static_cast<long long>(m) * p.ldo + n0);
@@ -1193,6 +1204,26 @@ GLLM_API int gllm_gemm_bf16_grouped(const void* A, long long lda, const void* B,
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo;
   p.mblk_group = mblk_group; p.group_rows = N;
+  p.err = gllm_error_word();
+  const long long b_rows = static_cast<long long>(num_groups) * N;
+  return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, 1);
+}
+
+// Grouped GEMM whose output rows are scattered by `scatter_meta` into up to 8 peers' buffers (see GemmParams).
+GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const void* B, long long ldb, long long ldo,
+                                            int M, int N, int K, const int* mblk_group, int num_groups, int bn,
+                                            const int* scatter_meta, void* const* scatter_peer, int world,
+                                            void* stream, int max_ctas) {
+  if (world < 1 || world > 8 || scatter_meta == nullptr) {
+    set_last_error("gemm_grouped_scatter: world must be 1..8 and scatter_meta non-null");
+    return -1;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = scatter_peer[0]; p.ldo = ldo;
+  p.mblk_group = mblk_group; p.group_rows = N;
+  p.scatter_meta = scatter_meta;
+  for (int r = 0; r < world; ++r) p.scatter_peer[r] = static_cast<__nv_bfloat16*>(scatter_peer[r]);
   p.err = gllm_error_word();
   const long long b_rows = static_cast<long long>(num_groups) * N;
   return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, 1);

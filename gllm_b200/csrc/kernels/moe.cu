@@ -251,13 +251,13 @@ GLLM_API int gllm_moe_permute(const void* x, const float* row_ss, int ss_parts, 
   cudaStream_t s = (cudaStream_t)stream;
   const int n = T * k;
   cudaMemsetAsync(counts, 0, sizeof(int) * e_local, s);
-  moe_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, n, e0, e_local, counts);
+  if (n > 0) moe_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, n, e0, e_local, counts);
   MOE_CHECK("moe_count");
   moe_plan_kernel<<<1, 256, 0, s>>>(counts, e_local, offsets, cursors, blk_group, max_blocks, total_rows);
   MOE_CHECK("moe_plan");
   const int threads = 256;
   const long long blocks = (static_cast<long long>(n) * 32 + threads - 1) / threads;
-  moe_scatter_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+  if (n > 0) moe_scatter_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
       static_cast<const __nv_bfloat16*>(x), row_ss, ss_parts, ids, T, k, hidden, e0, e_local, offsets, cursors,
       static_cast<__nv_bfloat16*>(a_perm), ss_perm, dest_rows, max_blocks * kMoeBlockRows);
   MOE_CHECK("moe_scatter");
@@ -270,6 +270,7 @@ GLLM_API int gllm_moe_combine(const void* y_perm, const int* dest_rows, const fl
     set_last_error("moe_combine: hidden %d must be even", hidden);
     return -1;
   }
+  if (T <= 0) return 0;
   moe_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(static_cast<const __nv_bfloat16*>(y_perm), dest_rows, weights,
                                                           k, hidden, static_cast<const __nv_bfloat16*>(shared),
                                                           static_cast<__nv_bfloat16*>(x), ss_out);

@@ -90,6 +90,9 @@ class MoeLayerWeights:
         c = self.cfg
         ws = self.workspace(model, T)
         ids, w = self._route(h, None, ws, T, 0, 0.0)
+        if self.ep is not None:
+            self.ep.moe_forward(self, model, x, None, None, ids, w, ws, T, normalised_input=h)
+            return
         M.permute(h, None, ids, ws, self.e0, self.e_local)
         L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
                    num_groups=self.e_local)

@@ -1,0 +1,86 @@
+"""Multi-head latent attention ops: latent cache write and attention over the latent cache.
+
+CUDA path: ``csrc/kernels/mla.cu``. CPU path / oracle: plain fp32 PyTorch of the same math.
+Reference parity: MlaKvCompress / MlaQAbsorb / MlaAttention
+(src/arch/auto_graph_fragments/build_graph.inc.rs:1486-1578).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as nv
+from ._native import F, I, L, P
+
+nv.register("gllm_mla_latent_write", I, [P, L, I, I, I, P, F, P, P, P, P, I, P, I, P])
+nv.register("gllm_mla_attention", I, [P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P])
+
+PAGE = 16
+
+
+def rope_half(x, cos, sin):
+    """x [..., d] half-split rotation with cos/sin [..., d/2]."""
+    h = x.shape[-1] // 2
+    x0, x1 = x[..., :h], x[..., h:]
+    return torch.cat([x0 * cos - x1 * sin, x1 * cos + x0 * sin], -1)
+
+
+def latent_write(kv_a, d_c, norm_w, eps, positions, slot_mapping, cos_t, sin_t, cache):
+    """kv_a [T, d_c + d_r] -> cache[page, slot] = [RMSNorm(c_kv) * w | RoPE(k_pe)]."""
+    T = kv_a.shape[0]
+    d_r = kv_a.shape[1] - d_c
+    if not kv_a.is_cuda:
+        c = kv_a[:, :d_c].float()
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+        pos = positions.long().clamp(0, cos_t.shape[0] - 1)
+        kpe = rope_half(kv_a[:, d_c:].float(), cos_t[pos], sin_t[pos])
+        row = torch.cat([c, kpe], -1).to(cache.dtype)
+        ok = slot_mapping >= 0
+        sl = slot_mapping[ok].long()
+        cache.view(-1, d_c + d_r)[sl] = row[ok]
+        return
+    rc = nv.lib().gllm_mla_latent_write(kv_a.data_ptr(), kv_a.stride(0), T, d_c, d_r, norm_w.data_ptr(), float(eps),
+                                        positions.data_ptr(), slot_mapping.data_ptr(), cos_t.data_ptr(),
+                                        sin_t.data_ptr(), cos_t.shape[0], cache.data_ptr(), cache.shape[0],
+                                        nv.stream_ptr())
+    nv.check(rc, "mla_latent_write")
+
+
+def latent_attention_ref(q, cache, block_tables, q_start, q_len, ctx_lens, n_heads, d_v, scale, causal=True):
+    d_k = cache.shape[-1]
+    out = torch.zeros((q.shape[0], n_heads * d_v), dtype=q.dtype, device=q.device)
+    for s in range(len(q_len)):
+        ql, ctx, st = int(q_len[s]), int(ctx_lens[s]), int(q_start[s])
+        if ql <= 0 or ctx <= 0:
+            continue
+        nb = (ctx + PAGE - 1) // PAGE
+        rows = cache[block_tables[s, :nb].long()].reshape(-1, d_k)[:ctx].float()
+        qs = q[st:st + ql].float().reshape(ql, n_heads, d_k)
+        sc = torch.einsum("qhd,kd->hqk", qs, rows) * scale
+        if causal:
+            pq = torch.arange(ctx - ql, ctx, device=q.device)[:, None]
+            pk = torch.arange(ctx, device=q.device)[None, :]
+            sc = sc.masked_fill(~(pk <= pq)[None], float("-inf"))
+        o = torch.einsum("hqk,kd->qhd", torch.softmax(sc, -1), rows[:, :d_v])
+        out[st:st + ql] = o.reshape(ql, n_heads * d_v).to(q.dtype)
+    return out
+
+
+def latent_attention(q, cache, block_tables, q_start, q_len, ctx_lens, row_seq, *, n_heads, d_v, scale, causal=True,
+                     out=None):
+    """q [T, n_heads * d_k] with rows [q_abs | q_pe]; cache [pages, 16, d_k]; returns [T, n_heads * d_v]."""
+    if not q.is_cuda:
+        r = latent_attention_ref(q, cache, block_tables, q_start, q_len, ctx_lens, n_heads, d_v, scale, causal)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    T = q.shape[0]
+    d_k = cache.shape[-1]
+    if out is None:
+        out = torch.empty((T, n_heads * d_v), dtype=q.dtype, device=q.device)
+    rc = nv.lib().gllm_mla_attention(q.data_ptr(), out.data_ptr(), cache.data_ptr(), cache.shape[0],
+                                     block_tables.data_ptr(), block_tables.shape[1], row_seq.data_ptr(),
+                                     q_start.data_ptr(), q_len.data_ptr(), ctx_lens.data_ptr(), T, n_heads, d_k, d_v,
+                                     float(scale), 1 if causal else 0, nv.stream_ptr())
+    nv.check(rc, "mla_attention")
+    return out

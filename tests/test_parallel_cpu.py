@@ -275,3 +275,14 @@ def test_rank_failure_is_detected_on_the_host(tmp_path):
            "--master-port", "29741", str(script)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=120)
     assert "SURVIVOR_SAW_ERROR" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_all_to_all_matches_full_layer(world):
+    """Every rank routes its own tokens; experts are split over the ranks; result equals the unsplit layer."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29760 + world), os.path.join(ROOT, "tests", "ep_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("EP_WORKER_OK") == world
