@@ -40,10 +40,10 @@ class Workspace:
         H = c.hidden_size
         self.x = torch.zeros((T, H), dtype=dt, device=dev)
         self.h = torch.zeros((T, H), dtype=dt, device=dev)
-        self.q = torch.zeros((T, model.n_q_local * c.head_dim), dtype=dt, device=dev)
-        self.attn = torch.zeros((T, model.n_q_local * c.head_dim), dtype=dt, device=dev)
-        self.qkv = None if model.fused else torch.zeros((T, (model.n_q_local + 2 * model.n_kv_local) * c.head_dim),
-                                                        dtype=dt, device=dev)
+        self.q = torch.zeros((T, model.attn_width), dtype=dt, device=dev)
+        self.attn = torch.zeros((T, model.attn_width), dtype=dt, device=dev)
+        self.qkv = None if (model.fused or c.is_mla) else torch.zeros(
+            (T, (model.n_q_local + 2 * model.n_kv_local) * c.head_dim), dtype=dt, device=dev)
         inter = max(model.inter_local, 1)
         self.act = torch.zeros((T, inter), dtype=dt, device=dev)
         self.gu = None if model.fused else torch.zeros((T, 2 * inter), dtype=dt, device=dev)
@@ -70,6 +70,7 @@ class DecoderModel:
             raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} not divisible by tp={self.tp_size}")
         self.n_q_local = cfg.num_heads // self.tp_size
         self.n_kv_local = max(1, cfg.num_kv_heads // self.tp_size)
+        self.attn_width = self.n_q_local * (max(cfg.head_dim, cfg.v_head_dim) if cfg.is_mla else cfg.head_dim)
         self.inter_local = (cfg.moe_intermediate_size if (cfg.is_moe and cfg.first_k_dense == 0) else
                             cfg.intermediate_size // self.tp_size)
         self.max_positions = max_positions or cfg.max_position_embeddings
@@ -83,6 +84,9 @@ class DecoderModel:
         self.layers: List[DenseLayerWeights] = []
         for i in self.layer_ids:
             lw = pack_dense_layer(cfg, src, i, self.tp_rank, self.tp_size, self.fused)
+            if cfg.is_mla:
+                from .mla import pack_mla
+                lw.mla = pack_mla(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype)
             # the source may live on the host (checkpoint files): every packed tensor moves to the model's
             # device here; fp32 tensors (norm weights, biases) stay fp32, the rest takes the compute dtype
             for name, val in list(vars(lw).items()):
@@ -110,6 +114,8 @@ class DecoderModel:
 
     # ------------------------------------------------------------------------------------------
     def kv_cache_shape(self, num_pages: int):
+        if self.cfg.is_mla:   # one latent row per token, shared by all heads (and replicated over TP ranks)
+            return (num_pages, 16, self.cfg.kv_lora_rank + self.cfg.qk_rope_head_dim)
         return (num_pages, 2, self.n_kv_local, 16, self.cfg.head_dim)
 
     def alloc_kv_cache(self, num_pages: int) -> List[torch.Tensor]:
@@ -173,13 +179,18 @@ class DecoderModel:
             else:
                 h = ws.h[:T]
                 ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)
-                qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
-                ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
-                                  positions=batch.positions, slot_mapping=batch.slot_mapping, cos_t=self.cos,
-                                  sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
-                                  k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps)
-                self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
-                self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
+                if lw.mla is not None:
+                    from .mla import mla_attention
+                    attn = mla_attention(self, lw.mla, h, batch, kv, ws.attn[:T])
+                    self._row_parallel(attn, lw.wo, x, ws.ss_b[:T], T)
+                else:
+                    qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
+                    ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
+                                      positions=batch.positions, slot_mapping=batch.slot_mapping, cos_t=self.cos,
+                                      sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
+                                      k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps)
+                    self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+                    self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
                 ops.rmsnorm(x, lw.post_attn_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)
                 if lw.moe is not None:
                     lw.moe.forward_unfused(self, x, h, T)

@@ -102,6 +102,9 @@ class RandomWeights:
             "o_proj": (H, c.num_heads * D), "q_proj_bias": (c.num_heads * D,), "k_proj_bias": (c.num_kv_heads * D,),
             "v_proj_bias": (c.num_kv_heads * D,), "router": (c.num_experts, H),
         }
+        if c.is_mla:
+            table["o_proj"] = (H, c.num_heads * c.v_head_dim)
+            table["q_proj"] = (c.num_heads * (c.qk_nope_head_dim + c.qk_rope_head_dim), H)
         if base in table:
             return table[base]
         inter = c.intermediate_size
@@ -187,6 +190,7 @@ class DenseLayerWeights:
     n_q: int = 0
     n_kv: int = 0
     moe: Optional[object] = None
+    mla: Optional[object] = None
     extra: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
@@ -206,6 +210,11 @@ def can_fuse(cfg: ModelConfig, tp: int = 1) -> bool:
 def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: bool):
     p = layer_prefix(i)
     D = cfg.head_dim
+    if cfg.is_mla:   # projections live in models/mla.py; only o_proj (row-parallel over heads * v) is packed here
+        wo = shard_tensor(p + "o_proj", src.get(p + "o_proj"), rank, world, head_dim=cfg.v_head_dim)
+        empty = torch.zeros((0, cfg.hidden_size), dtype=wo.dtype)
+        return empty, None, None, None, wo.contiguous(), src.get(p + "input_norm").float().contiguous(), \
+            cfg.num_heads // world, 0
     sh = lambda n: shard_tensor(n, src.get(p + n), rank, world, head_dim=D)
     q, k, v = sh("q_proj"), sh("k_proj"), sh("v_proj")
     wqkv = torch.cat([q, k, v], 0)
