@@ -1,0 +1,100 @@
+import torch
+
+from gllm_b200.engine.arbiter import (Archetype, HardwareSummary, InferenceMode, OverlapHint, ScenarioHint, StrategyArbiter,
+                                      archetype_of)
+from gllm_b200.engine.batch_context import BatchContext
+from gllm_b200.engine.callbacks import (CallbackAction, CallbackChain, CallbackTable, EarlyExitCallback, GateSkipCallback,
+                                        MidLayerEncodeCallback, ProbeVetoCallback, RagInjectCallback, port_layers,
+                                        SLOT_GUARDRAIL)
+from gllm_b200.engine.guard import CanaryDeviceBuffer, GuardedHostBuffer, NanTrap
+from gllm_b200.engine.weight_blob import WeightBlob
+from gllm_b200.models.config import preset
+import pytest
+
+
+def test_arbiter_plans():
+    arb = StrategyArbiter(HardwareSummary(gpus=8))
+    q8 = preset("qwen3-8b")
+    assert archetype_of(q8) == Archetype.DENSE_MEDIUM and archetype_of(preset("qwen3-30b-a3b")) == Archetype.MOE
+    assert archetype_of(preset("deepseek-v3")) == Archetype.MLA_MOE and archetype_of(preset("tiny-bert")) == Archetype.ENCODER
+    thr = arb.arbitrate(q8, InferenceMode.THROUGHPUT)
+    lat = arb.arbitrate(q8, InferenceMode.LATENCY)
+    assert thr.tp == 1 and lat.tp >= 2 and lat.max_num_seqs < thr.max_num_seqs and lat.speculative and not thr.speculative
+    big = arb.arbitrate(preset("llama-3-70b"), InferenceMode.THROUGHPUT)
+    assert big.tp >= 2 and big.fused_collectives
+    moe = arb.arbitrate(preset("qwen3-30b-a3b"))
+    assert moe.ep == 8 and moe.tp == 1
+    ds = arb.arbitrate(preset("deepseek-v3"))
+    assert ds.ep == 8 and ds.weight_dtype == "fp8"
+    iso = arb.arbitrate(preset("llama-3-70b"), overlap=OverlapHint.PREFER_ISOLATED)
+    assert not iso.fused_collectives
+    lc = arb.arbitrate(q8, scenario=ScenarioHint.LONG_CONTEXT)
+    assert lc.kv_dtype == "fp8"
+    one = StrategyArbiter(HardwareSummary(gpus=1)).arbitrate(q8)
+    assert (one.tp, one.pp, one.ep) == (1, 1, 1) and not one.fused_collectives
+
+
+def test_callback_chain_and_table():
+    assert port_layers(32) == {"rag_inject": 16, "early_exit": 25, "intent": 24, "guardrail": 30, "sg_detect": 16}
+    h = torch.randn(4, 8)
+    enc = MidLayerEncodeCallback(2)
+    rag = RagInjectCallback(2, torch.ones(8), scale=2.0)
+    chain = CallbackChain([enc, rag])
+    assert chain.layers_of_interest(6) == [2]
+    r = chain.run("pre", 2, h)
+    assert r.action == CallbackAction.REPLACE and torch.allclose(r.hidden[-1], h[-1] + 2) and torch.equal(r.hidden[0], h[0])
+    chain.run("post", 2, h); assert torch.equal(enc.captured, h)
+    ee = EarlyExitCallback(layer=5)
+    assert ee.post_layer(4, h).action == CallbackAction.CONTINUE
+    assert ee.post_layer(5, h * 1.001).action == CallbackAction.EXIT_EARLY
+    assert ee.post_layer(4, h).action == CallbackAction.CONTINUE and ee.post_layer(5, -h).action == CallbackAction.CONTINUE
+    veto = ProbeVetoCallback(1, weight=torch.ones(8) * 10, threshold=0.5)
+    chain2 = CallbackChain([MidLayerEncodeCallback(1), veto])
+    assert chain2.callbacks[0] is veto                                     # priority order
+    assert chain2.run("post", 1, torch.ones(2, 8)).action == CallbackAction.VETO
+    assert chain2.run("post", 1, -torch.ones(2, 8)).action == CallbackAction.CONTINUE
+    gs = GateSkipCallback([3]); gs.pre_layer(3, h)
+    assert torch.equal(gs.post_layer(3, h * 5).hidden, h)
+    t = CallbackTable(); t.register(SLOT_GUARDRAIL, lambda x: x + 1)
+    assert t.call(SLOT_GUARDRAIL, 1) == 2 and t.call(0) is None
+    with pytest.raises(IndexError):
+        t.register(8, print)
+
+
+def test_batch_context_layout():
+    bc = BatchContext(8)
+    seqs = [dict(request_id=7, q_len=1, ctx_len=100, slot=0, temperature=0.7, top_k=0, top_p=1.0, eos=2, generated=5, max_tokens=256),
+            dict(request_id=9, q_len=33, ctx_len=33, slot=1, temperature=0.0, top_k=40, top_p=0.9, eos=2, generated=0, max_tokens=16)]
+    bc.fill(seqs, step=12, seed=99, max_blocks=64)
+    assert bc.nbytes() == 96 + 128 and int(bc.header["num_tokens"][0]) == 34 and int(bc.header["num_decode"][0]) == 1
+    assert int(bc.seqs[1]["q_start"]) == 1 and int(bc.seqs[1]["block_table_off"]) == 64
+    raw = bytes(bc.buf[:96].numpy())
+    assert raw[:4] == (0x474C4C4D).to_bytes(4, "little")
+    sp = bc.sampling_params()
+    assert sp.shape == (2, 4) and sp[1].tolist() == [0.0, 40.0, 0.8999999761581421, 2.0]
+    assert bc.upload("cpu").numel() == bc.nbytes()
+
+
+def test_guards_nan_trap_and_blob(tmp_path):
+    g = GuardedHostBuffer(5000)
+    t = g.tensor()
+    t.fill_(7)
+    assert t.numel() == 5000 and int(t.sum()) == 35000
+    lo, hi = g.guard_addresses()
+    assert g.address - lo == 4096 and hi > g.address + 5000 - 1
+    c = CanaryDeviceBuffer(100, torch.float32, "cpu")
+    c.data.fill_(1.0); assert c.intact()
+    c.raw[c.pad + 400] = 0; assert not c.intact()
+    trap = NanTrap(enabled=True, dump_dir=str(tmp_path))
+    trap.check("ok", torch.ones(3))
+    with pytest.raises(FloatingPointError):
+        trap.check("bad", torch.tensor([1.0, float("nan")]))
+    assert (tmp_path / "bad.pt").exists()
+    NanTrap(enabled=False).check("bad", torch.tensor([float("inf")]))
+    ts = {f"L{l}.{n}": torch.randn(3, 5).to(dt) for l in range(2) for n, dt in (("w", torch.bfloat16), ("s", torch.float32))}
+    ts["lm_head"] = torch.randn(7)
+    blob = WeightBlob.pack(ts)
+    for n, t0 in ts.items():
+        assert torch.equal(blob.view(n), t0) and blob.entries[n].offset % 256 == 0
+    assert blob.layer_stride("L0.", "L1.") == 512 and blob.layer_stride("L0.", "lm") is None
+    assert blob.offset_table()[0][0] == "L0.w" and blob.total_bytes() % 256 == 0
