@@ -101,11 +101,19 @@ def build_cxx_module(name: str, subdir: str, pybind=True, force=False, verbose=F
     return out
 
 
+def _python_embed_flags():
+    """Compiler / linker flags to embed the running interpreter (the C ABI shim)."""
+    inc = sysconfig.get_paths()["include"]
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    return ("-I", inc, "-L", libdir, f"-lpython{ver}", f"-Wl,-rpath,{libdir}")
+
+
 def build_all(force=False, verbose=False):
     outs = [build_kernels(force, verbose)]
     for name, sub, pyb, extra in (("_sched", "sched", True, ()), ("libgllm_cpuref", "ref", False, ("-fopenmp",)),
                                   ("libgllm_loader", "loader", False, ("-fopenmp",)),
-                                  ("libgllm_ffi", "ffi", False, ())):
+                                  ("libgllm_ffi", "ffi", False, _python_embed_flags())):
         if any((CSRC / sub).glob("*.cpp")):
             outs.append(build_cxx_module(name, sub, pybind=pyb, force=force, verbose=verbose, extra=extra))
     return outs
