@@ -1,0 +1,68 @@
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gllm_b200.models.audio import (AudioConfig, AudioWeights, ConformerEncoder, depthwise_conv1d, log_mel_spectrogram,
+                                    mel_filterbank)
+from gllm_b200.models.multimodal import MultimodalEncoder, MultimodalSpec, expand_placeholders, splice_embeddings
+from gllm_b200.models.vision import VisionConfig, VisionTower, VisionWeights, patchify
+
+
+def test_patchify_equals_strided_conv():
+    torch.manual_seed(0)
+    img = torch.randn(2, 3, 28, 28)
+    w = torch.randn(16, 3, 14, 14)
+    want = F.conv2d(img, w, stride=14).flatten(2).transpose(1, 2)
+    got = patchify(img, 14) @ w.reshape(16, -1).t()
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_vision_tower_shapes_and_determinism():
+    cfg = VisionConfig(image_size=28, patch_size=7, hidden=32, layers=2, heads=4, mlp=64, out_hidden=48, pool=2)
+    tower = VisionTower(cfg, VisionWeights(cfg, seed=1))
+    img = torch.randn(2, 3, 28, 28)
+    out = tower.forward(img)
+    assert out.shape == (2, 4, 48) and torch.isfinite(out).all()
+    torch.testing.assert_close(tower.forward(img), out)
+    # attention is bidirectional: changing the LAST patch changes the FIRST token's output
+    img2 = img.clone(); img2[:, :, 21:, 21:] += 1.0
+    assert (tower.forward(img2)[:, 0] - out[:, 0]).abs().max() > 1e-6
+
+
+def test_mel_and_conformer():
+    fb = mel_filterbank(20, 400, 16000)
+    assert fb.shape == (20, 201) and (fb >= 0).all() and (fb.sum(1) > 0).all()
+    sr = 16000
+    t = torch.arange(sr) / sr
+    wave = torch.sin(2 * math.pi * 1000 * t)[None]
+    cfg = AudioConfig(n_mels=20, hidden=32, layers=2, heads=4, conv_kernel=7, out_hidden=24)
+    mel = log_mel_spectrogram(wave, cfg)
+    assert mel.shape[0] == 1 and mel.shape[2] == 20
+    peak = int(mel[0].mean(0).argmax())
+    centre = [float((fb[i] * torch.linspace(0, 8000, 201)).sum() / fb[i].sum()) for i in range(20)]
+    assert abs(centre[peak] - 1000) < 400                        # energy lands in the band around 1 kHz
+    x = torch.randn(2, 9, 6); w = torch.randn(6, 1, 3)
+    y = depthwise_conv1d(x, w)
+    assert y.shape == x.shape
+    torch.testing.assert_close(y[0, 4, 2], (x[0, 3:6, 2] * w[2, 0]).sum())
+    enc = ConformerEncoder(cfg, AudioWeights(cfg, seed=2))
+    out = enc.forward(wave)
+    assert out.shape == (1, mel.shape[1] // 4, 24) and torch.isfinite(out).all()
+
+
+def test_placeholder_expansion_and_splice():
+    spec = MultimodalSpec(image_token_id=900, audio_token_id=901)
+    ids, spans = expand_placeholders([1, 900, 2, 901, 3], spec, [4], [2])
+    assert ids == [1, 900, 900, 900, 900, 2, 901, 901, 3] and spans == [("image", 0, 1, 4), ("audio", 0, 6, 2)]
+    with pytest.raises(ValueError):
+        expand_placeholders([1, 2], spec, [4])
+    emb = torch.zeros(9, 8)
+    out = splice_embeddings(emb, spans, [torch.ones(4, 8)], [torch.full((2, 8), 2.0)])
+    assert out[1:5].eq(1).all() and out[6:8].eq(2).all() and out[0].eq(0).all()
+    vcfg = VisionConfig(image_size=14, patch_size=7, hidden=16, layers=1, heads=2, mlp=32, out_hidden=8)
+    mm = MultimodalEncoder(vision=VisionTower(vcfg, VisionWeights(vcfg)), spec=spec)
+    table = torch.randn(1000, 8)
+    ids2, x = mm.prepare([5, 900, 6], table, images=torch.randn(1, 3, 14, 14))
+    assert len(ids2) == 6 and x.shape == (6, 8) and torch.equal(x[0], table[5]) and not torch.equal(x[1], table[900])
