@@ -286,3 +286,13 @@ def test_expert_parallel_all_to_all_matches_full_layer(world):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("EP_WORKER_OK") == world
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_parallel_generation_matches_single_process(world):
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29780 + world), os.path.join(ROOT, "tests", "pp_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("PP_WORKER_OK") == world
