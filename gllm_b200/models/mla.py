@@ -42,7 +42,8 @@ def pack_mla(cfg: ModelConfig, src, i: int, rank: int, world: int, device, dtype
     nope, rope_d, v, d_c = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
     h0, h1 = shard_range(cfg.num_heads, rank, world)
     qd = nope + rope_d
-    mv = lambda t: t.to(device, dtype).contiguous()
+    from ..ops import linear as L
+    mv = lambda t: L.pad_rows(t.to(device, dtype), 128).contiguous()     # GEMM weights: rows padded to the tile
     if cfg.q_lora_rank:
         q_a = mv(src.get(p + "q_a_proj"))
         q_a_norm = src.get(p + "q_a_norm").float().to(device).contiguous()
@@ -53,7 +54,8 @@ def pack_mla(cfg: ModelConfig, src, i: int, rank: int, world: int, device, dtype
     kv_b = src.get(p + "kv_b_proj").reshape(cfg.num_heads, nope + v, d_c)[h0:h1]
     return MlaWeights(q_a=q_a, q_a_norm=q_a_norm, q_b=q_b, kv_a=mv(src.get(p + "kv_a_proj")),
                       kv_a_norm=src.get(p + "kv_a_norm").float().to(device).contiguous(),
-                      w_uk=mv(kv_b[:, :nope, :]), w_uv=mv(kv_b[:, nope:, :].transpose(1, 2)), n_heads=h1 - h0)
+                      w_uk=kv_b[:, :nope, :].to(device, dtype).contiguous(),
+                      w_uv=kv_b[:, nope:, :].transpose(1, 2).to(device, dtype).contiguous(), n_heads=h1 - h0)
 
 
 def _row_index(batch, T, device):
@@ -84,7 +86,7 @@ def mla_attention(model, w: MlaWeights, h, batch, cache, out):
         row_seq, q_start, q_len = _row_index(batch, T, h.device)
     # queries
     if w.q_a is not None:
-        qa = ops.gemm(h, w.q_a, out_dtype=h.dtype, bn=128)
+        qa = ops.gemm(h, w.q_a, out_dtype=h.dtype, bn=128)[:, :c.q_lora_rank].contiguous()
         qa = ops.rmsnorm(qa, w.q_a_norm, c.rms_norm_eps)
         q = ops.gemm(qa, w.q_b, out_dtype=h.dtype, bn=128)
     else:
