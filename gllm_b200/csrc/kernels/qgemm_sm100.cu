@@ -7,7 +7,9 @@
 // signal the MMA warp. A is loaded by TMA already swizzled. Accumulators live in TMEM; the epilogue reads them
 // with tcgen05.ld and stores bf16 (or fp32 partials when K is split across CTAs, reduced by a second tiny kernel).
 //
-// Warp roles (384 threads): 0 TMA producer, 1 MMA issuer, 2 TMEM allocator, 3 idle, 4-7 epilogue, 8-11 transform.
+// Warp roles (512 threads): 0 TMA producer, 1 MMA issuer, 2 TMEM allocator, 3 idle, 4-7 epilogue, 8-15 transform
+// (two groups of four warps taking alternate stages, so one group's scale-load latency hides behind the other's
+// conversion).
 //
 // Canonical weight form (built by the Python packer from MXFP8 / FP8-block / NVFP4 / MXFP4 / AWQ / GPTQ / GGUF
 // blocks): codes uint8 [N, K*bits/8] row-major (4-bit: low nibble = even k), scales bf16 [N, K/group],
@@ -26,15 +28,14 @@ namespace gllm {
 constexpr int kQBM = 128;       // rows of A per tile (UMMA M)
 constexpr int kQBN = 128;       // rows of W per tile (UMMA N)
 constexpr int kQBK = 64;        // k elements per stage (128 bytes of bf16)
-constexpr int kQThreads = 384;
-constexpr int kQStages = 4;
+constexpr int kQThreads = 512;
 
 enum QMode { Q_FP8 = 0, Q_FP4 = 1, Q_INT4 = 2, Q_INT8 = 3 };
 
 struct QGemmParams {
   int M, N, K;
   int num_m, num_n, num_kb, splits;
-  int mode, group;                 // group: k elements per scale
+  int mode, group, group_shift;    // group: k elements per scale (a power of two); group_shift = log2(group)
   const __nv_bfloat16* scales;     // [N, K/group]
   const __nv_bfloat16* offsets;    // [N, K/group] or null
   int offset_in_codes;             // 1: value = (code + offset) * scale; 0: value = code * scale + offset
@@ -48,12 +49,16 @@ struct QGemmParams {
   int* err;
 };
 
-template <int BYTES_PER_ROW>
+// MT = 128-row A tiles sharing one W tile: with MT = 2 every weight tile is fetched and expanded once for 256 rows.
+template <int BYTES_PER_ROW, int MT>
 struct QStage {
-  static constexpr int kA = kQBM * 128;               // swizzled bf16 A tile
+  static constexpr int kA1 = kQBM * 128;              // one swizzled bf16 A tile
+  static constexpr int kA = MT * kA1;
   static constexpr int kB = kQBN * 128;               // swizzled bf16 W tile (written by the transform warps)
   static constexpr int kRaw = kQBN * BYTES_PER_ROW;   // raw codes
   static constexpr int kBytes = kA + kB + ((kRaw + 1023) / 1024) * 1024;
+  static constexpr int kStages = MT == 1 ? 4 : 3;
+  static constexpr int kTmemCols = 2 * MT * kQBN;     // double-buffered accumulators
 };
 
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -95,12 +100,13 @@ __device__ __forceinline__ void decode16(const uint8_t* bytes, float (&v)[16]) {
   }
 }
 
-template <int MODE>
+template <int MODE, int MT>
 __global__ void __launch_bounds__(kQThreads, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w, const QGemmParams p) {
   constexpr int kBits = (MODE == Q_FP8 || MODE == Q_INT8) ? 8 : 4;
   constexpr int kRowBytes = kQBK * kBits / 8;         // raw bytes of one W row per stage: 64 or 32
-  using St = QStage<kRowBytes>;
+  using St = QStage<kRowBytes, MT>;
+  constexpr int kQStages = St::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem + kQStages * St::kBytes);
@@ -134,7 +140,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     tma_prefetch_desc(&tmap_w);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_base_ptr, 256);   // two 128-column accumulators
+    tmem_alloc(tmem_base_ptr, St::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -167,7 +173,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           uint8_t* sa = smem + stage * St::kBytes;
           uint8_t* sraw = sa + St::kA + St::kB;
           mbar_expect_tx(&raw_full[stage], St::kA + St::kRaw);
-          tma_load_2d(sa, &tmap_a, &raw_full[stage], kb * kQBK, m_blk * kQBM);
+#pragma unroll
+          for (int i = 0; i < MT; ++i)
+            tma_load_2d(sa + i * St::kA1, &tmap_a, &raw_full[stage], kb * kQBK, (m_blk * MT + i) * kQBM);
           tma_load_2d(sraw, &tmap_w, &raw_full[stage], kb * kRowBytes, n_blk * kQBN);
           if (++stage == kQStages) {
             stage = 0;
@@ -194,7 +202,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kQBN;
+        const uint32_t d_tmem = tmem_base + acc * (MT * kQBN);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL)) {
             ok = false;
@@ -202,11 +210,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * St::kBytes);
-          const uint64_t a_desc = umma_desc_sw128(sa);
           const uint64_t b_desc = umma_desc_sw128(sa + St::kA);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int i = 0; i < MT; ++i) {
+            const uint64_t a_desc = umma_desc_sw128(sa + i * St::kA1);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16(d_tmem + i * kQBN, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(&empty_bar[stage]);
           if (++stage == kQStages) {
             stage = 0;
@@ -219,17 +230,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     __syncwarp();
   } else if (warp >= 8) {
     // ------------------------------- transform: codes -> swizzled bf16 -------------------------------
-    const int tt = threadIdx.x - 256;                 // 0..127
+    const int grp = (warp - 8) >> 2;                  // transform group 0 / 1
+    const int tt = threadIdx.x - 256 - grp * 128;     // 0..127 inside the group
     constexpr int kChunksPerRow = kRowBytes / 16;     // 16-byte raw chunks per row: 4 (8-bit) or 2 (4-bit)
     constexpr int kElemsPerChunk = 16 * 8 / kBits;    // 16 or 32
     constexpr int kChunks = kQBN * kChunksPerRow;
-    int stage = 0;
-    uint32_t phase = 0;
+    int seq = 0;                                      // running stage counter over all (tile, k block) pairs
     bool ok = true;
     for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
       int ks, m_blk, n_blk, kb0, kb1;
       decode_item(t, ks, m_blk, n_blk, kb0, kb1);
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb, ++seq) {
+        if ((seq & 1) != grp) continue;               // the other group's stage
+        const int stage = seq % kQStages;
+        const uint32_t phase = (seq / kQStages) & 1;
         const bool got = mbar_wait(&raw_full[stage], phase, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
@@ -237,24 +251,39 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
         uint8_t* sb = smem + stage * St::kBytes + St::kA;
         const uint8_t* sraw = sb + St::kB;
-#pragma unroll 1
-        for (int c = tt; c < kChunks; c += 128) {
+        // issue every load of this stage first (raw codes from shared memory, scales / offsets from L2), then
+        // convert: one memory latency per stage instead of one per chunk
+        constexpr int kPer = kChunks / 128;                 // chunks per thread: 4 (8-bit) or 2 (4-bit)
+        constexpr int kHalves = kElemsPerChunk / 16;        // 16-element pieces per chunk: 1 or 2
+        uint4 raw[kPer];
+        float sc[kPer][kHalves], of[kPer][kHalves];
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+          const int c = tt + i * 128;
           const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
-          const uint4 raw = *reinterpret_cast<const uint4*>(sraw + r * kRowBytes + cc * 16);
-          const uint8_t* bytes = reinterpret_cast<const uint8_t*>(&raw);
+          raw[i] = *reinterpret_cast<const uint4*>(sraw + r * kRowBytes + cc * 16);
           const int n = n_blk * kQBN + r;
-          const int k0 = kb * kQBK + cc * kElemsPerChunk;
           const int nn = n < p.N ? n : p.N - 1;
 #pragma unroll
-          for (int half = 0; half < kElemsPerChunk / 16; ++half) {
+          for (int half = 0; half < kHalves; ++half) {
+            // 16 consecutive k share a scale when group >= 16 (every supported format)
+            const int kk = kb * kQBK + cc * kElemsPerChunk + half * 16;
+            const long long si = static_cast<long long>(nn) * p.ld_scale + (kk >> p.group_shift);
+            sc[i][half] = __bfloat162float(p.scales[si]);
+            of[i][half] = p.offsets ? __bfloat162float(p.offsets[si]) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+          const int c = tt + i * 128;
+          const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
+          const uint8_t* bytes = reinterpret_cast<const uint8_t*>(&raw[i]);
+#pragma unroll
+          for (int half = 0; half < kHalves; ++half) {
             float v[16];
             decode16<MODE>(bytes + half * (16 * kBits / 8), v);
-            const int kk = k0 + half * 16;
-            // 16 consecutive k share a scale when group >= 16 (every supported format)
-            const long long si = static_cast<long long>(nn) * p.ld_scale + kk / p.group;
-            const float s = __bfloat162float(p.scales[si]);
-            float o = p.offsets ? __bfloat162float(p.offsets[si]) : 0.f;
-            if (p.offset_in_codes) o *= s;
+            const float s = sc[i][half];
+            const float o = p.offset_in_codes ? of[i][half] * s : of[i][half];
             uint4 w0, w1;
             w0.x = bf16x2_from(v[0] * s + o, v[1] * s + o);
             w0.y = bf16x2_from(v[2] * s + o, v[3] * s + o);
@@ -274,10 +303,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         fence_async_proxy();   // generic-proxy writes above must be visible to the tensor core's async-proxy reads
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_bar[stage]);
-        if (++stage == kQStages) {
-          stage = 0;
-          phase ^= 1;
-        }
       }
     }
   } else if (warp >= 4) {
@@ -297,8 +322,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kQBN;
-      const int m = m_blk * kQBM + q * 32 + lane;
+#pragma unroll 1
+      for (int mi = 0; mi < MT; ++mi) {
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * kQBN) + mi * kQBN;
+      const int m = (m_blk * MT + mi) * kQBM + q * 32 + lane;
       const bool row_ok = m < p.M;
       float rs = 1.f;
       if (p.row_ss_in && row_ok) {
@@ -334,6 +361,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -342,7 +370,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 2) tmem_dealloc(tmem_base, 256);
+  if (warp == 2) tmem_dealloc(tmem_base, St::kTmemCols);
 }
 
 // out[m][n] = bf16(rowscale(m) * sum_s partial[s][m][n])
@@ -393,25 +421,30 @@ static int make_raw_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint
   return 0;
 }
 
-template <int MODE>
-static int launch_qgemm(const CUtensorMap& ta, const CUtensorMap& tw, const QGemmParams& p, int ctas, cudaStream_t s) {
+template <int MODE, int MT>
+static int launch_qgemm_mt(const CUtensorMap& ta, const CUtensorMap& tw, const QGemmParams& p, int ctas, cudaStream_t s) {
   constexpr int kBits = (MODE == Q_FP8 || MODE == Q_INT8) ? 8 : 4;
-  using St = QStage<kQBK * kBits / 8>;
-  const int smem = kQStages * St::kBytes + 1024 + 1024;
+  using St = QStage<kQBK * kBits / 8, MT>;
+  const int smem = St::kStages * St::kBytes + 1024 + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaFuncSetAttribute(qgemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(qgemm_kernel<MODE, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     attr_done[dev & 63] = true;
   }
-  qgemm_kernel<MODE><<<ctas, kQThreads, smem, s>>>(ta, tw, p);
+  qgemm_kernel<MODE, MT><<<ctas, kQThreads, smem, s>>>(ta, tw, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("qgemm launch failed: %s", cudaGetErrorString(e));
     return -1;
   }
   return 0;
+}
+
+template <int MODE>
+static int launch_qgemm(const CUtensorMap& ta, const CUtensorMap& tw, const QGemmParams& p, int mt, int ctas, cudaStream_t s) {
+  return mt == 2 ? launch_qgemm_mt<MODE, 2>(ta, tw, p, ctas, s) : launch_qgemm_mt<MODE, 1>(ta, tw, p, ctas, s);
 }
 
 }  // namespace gllm
@@ -435,8 +468,11 @@ GLLM_API int gllm_qgemm(const void* A, long long lda, const void* codes, long lo
   const int bits = (mode == Q_FP8 || mode == Q_INT8) ? 8 : 4;
   QGemmParams p = {};
   p.M = M; p.N = N; p.K = K;
-  p.num_m = (M + kQBM - 1) / kQBM; p.num_n = (N + kQBN - 1) / kQBN; p.num_kb = K / kQBK;
+  const int mt = M > kQBM ? 2 : 1;
+  p.num_m = (M + mt * kQBM - 1) / (mt * kQBM); p.num_n = (N + kQBN - 1) / kQBN; p.num_kb = K / kQBK;
   p.mode = mode; p.group = group;
+  p.group_shift = 0;
+  while ((1 << p.group_shift) < group) ++p.group_shift;
   p.scales = static_cast<const __nv_bfloat16*>(scales);
   p.offsets = static_cast<const __nv_bfloat16*>(offsets);
   p.offset_in_codes = offset_in_codes;
@@ -449,10 +485,17 @@ GLLM_API int gllm_qgemm(const void* A, long long lda, const void* codes, long lo
   int splits = 1;
   if (force_splits > 0) {
     splits = force_splits;
-  } else if (partial && tiles < sms) {
-    splits = sms / tiles;
-    if (splits > p.num_kb / 2) splits = p.num_kb / 2;
-    if (splits > 16) splits = 16;
+  } else if (partial && tiles < 2 * sms) {
+    // fewest waves of work per unit of K, with a small charge per split for the partial dump and the reduce
+    double best = 1e30;
+    for (int sp = 1; sp <= 16 && sp * 4 <= p.num_kb; ++sp) {
+      const int waves = (tiles * sp + sms - 1) / sms;
+      const double cost = static_cast<double>(waves) / sp + 0.03 * (sp - 1);
+      if (cost < best - 1e-9) {
+        best = cost;
+        splits = sp;
+      }
+    }
   }
   if (splits < 1) splits = 1;
   if (splits > p.num_kb) splits = p.num_kb;
@@ -468,10 +511,10 @@ GLLM_API int gllm_qgemm(const void* A, long long lda, const void* codes, long lo
   cudaStream_t s = (cudaStream_t)stream;
   int rc = 0;
   switch (mode) {
-    case Q_FP8: rc = launch_qgemm<Q_FP8>(ta, tw, p, ctas, s); break;
-    case Q_FP4: rc = launch_qgemm<Q_FP4>(ta, tw, p, ctas, s); break;
-    case Q_INT4: rc = launch_qgemm<Q_INT4>(ta, tw, p, ctas, s); break;
-    default: rc = launch_qgemm<Q_INT8>(ta, tw, p, ctas, s); break;
+    case Q_FP8: rc = launch_qgemm<Q_FP8>(ta, tw, p, mt, ctas, s); break;
+    case Q_FP4: rc = launch_qgemm<Q_FP4>(ta, tw, p, mt, ctas, s); break;
+    case Q_INT4: rc = launch_qgemm<Q_INT4>(ta, tw, p, mt, ctas, s); break;
+    default: rc = launch_qgemm<Q_INT8>(ta, tw, p, mt, ctas, s); break;
   }
   if (rc) return rc;
   if (splits > 1) {

@@ -5,7 +5,8 @@ also be captured with ``ncu`` in a minute or two. Timing uses CUDA events on the
 warm-up; the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root if
 present) is printed as JSON.
 
-ops: gemm_prefill  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample
+ops: gemm_prefill  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
+     mla_attn
 """
 from __future__ import annotations
 
@@ -96,6 +97,42 @@ def run(op: str, iters: int):
                   iters)
         fl = 2 * M * (nq + 2 * nkv) * 128 * K
         out.update(shape=[M, (nq + 2 * nkv) * 128, K], us=t * 1e6, tflops=fl / t / 1e12, frac_of_bf16_peak=fl / t / 1e12 / tf)
+    elif op.startswith("qgemm_"):
+        # decode-shaped weight streaming: the quantised codes are what crosses HBM
+        from . import quant_gemm as Q
+        mode = op.split("_", 1)[1]
+        M, N, K = 256, 12288, 4096
+        group = 16 if mode == "fp4" else 32
+        ws = [Q.quantize(torch.randn(N, K) * 0.05, mode, group).to(dev) for _ in range(3)]
+        a = rnd(M, K)
+        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def f():
+            i[0] = (i[0] + 1) % 3
+            Q.qgemm(a, ws[i[0]], out=o)
+        t = _time(f, iters)
+        byts = ws[0].nbytes()
+        dense = N * K * 2
+        out.update(shape=[M, N, K], mode=mode, group=group, us=t * 1e6, weight_bytes=byts, weight_gbs=byts / t / 1e9,
+                   frac_of_hbm_peak=byts / t / 1e9 / hbm, bf16_equivalent_gbs=dense / t / 1e9,
+                   tflops=2 * M * N * K / t / 1e12)
+    elif op == "mla_attn":
+        from . import mla as MLA
+        nh, d_c, d_r, B, ctx = 16, 512, 64, 64, 1024
+        pages = B * ctx // 16
+        cache = rnd(pages, 16, d_c + d_r, scale=0.3)
+        q = rnd(B, nh * (d_c + d_r), scale=0.3)
+        bt = torch.arange(pages, device=dev, dtype=torch.int32).reshape(B, ctx // 16)
+        idx = torch.arange(B, device=dev, dtype=torch.int32)
+        one = torch.ones(B, device=dev, dtype=torch.int32)
+        cl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        o = torch.empty(B, nh * d_c, device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: MLA.latent_attention(q, cache, bt, idx, one, cl, idx, n_heads=nh, d_v=d_c, scale=0.04, out=o), iters)
+        byts = cache.numel() * 2
+        fl = 2 * B * nh * ctx * (2 * d_c + d_r)
+        out.update(shape=dict(batch=B, heads=nh, ctx=ctx, d_c=d_c, d_rope=d_r), us=t * 1e6, kv_gbs=byts / t / 1e9,
+                   frac_of_hbm_peak=byts / t / 1e9 / hbm, tflops=fl / t / 1e12)
     elif op in ("decode_attn", "prefill_attn"):
         nq, nkv, D = 32, 8, 128
         if op == "decode_attn":
