@@ -56,7 +56,8 @@ class Workspace:
 
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
-                 fused: Optional[bool] = None, layers: Optional[range] = None):
+                 fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
+                 quant_group: int = 32):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
@@ -65,6 +66,9 @@ class DecoderModel:
         self.layer_ids = list(layers) if layers is not None else list(range(cfg.num_layers))
         self.first_stage = 0 in self.layer_ids
         self.last_stage = (cfg.num_layers - 1) in self.layer_ids
+        self.weight_quant = weight_quant
+        if weight_quant is not None:
+            fused = False        # quantised linears run through the dequantising GEMM; epilogue fusions need bf16 weights
         self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and self.device.type == "cuda"
         if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size):
             raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} not divisible by tp={self.tp_size}")
@@ -93,6 +97,8 @@ class DecoderModel:
                 if isinstance(val, torch.Tensor):
                     setattr(lw, name, val.to(self.device, None if val.dtype == torch.float32 and (
                         name.endswith("norm") or name.endswith("bias")) else (dtype if val.is_floating_point() else None)).contiguous())
+            if weight_quant is not None:
+                self._quantize_layer(lw, weight_quant, quant_group)
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
@@ -113,6 +119,27 @@ class DecoderModel:
         self._ws: Optional[Workspace] = None
 
     # ------------------------------------------------------------------------------------------
+    def _quantize_layer(self, lw, mode: str, group: int):
+        """Load-time quantisation of the dense projections of one layer into the canonical quantised form (a
+        checkpoint that is already quantised arrives here as ``QuantWeight`` and is left alone)."""
+        from ..ops.quant_gemm import QuantWeight, quantize
+        for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+            w = getattr(lw, name, None)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[0] > 0 and w.shape[1] % 64 == 0 and w.shape[1] % group == 0 \
+                    and w.shape[0] % 8 == 0:
+                setattr(lw, name, quantize(w.float().cpu(), mode, group).to(self.device))
+
+    def weight_bytes(self) -> int:
+        from ..ops.quant_gemm import QuantWeight
+        total = 0
+        for lw in self.layers:
+            for v in vars(lw).values():
+                if isinstance(v, QuantWeight):
+                    total += v.nbytes()
+                elif isinstance(v, torch.Tensor):
+                    total += v.numel() * v.element_size()
+        return total
+
     def kv_cache_shape(self, num_pages: int):
         if self.cfg.is_mla:   # one latent row per token, shared by all heads (and replicated over TP ranks)
             return (num_pages, 16, self.cfg.kv_lora_rank + self.cfg.qk_rope_head_dim)

@@ -76,6 +76,15 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
     """out[M,N] = rowscale(a) @ w.T (+ bias). ``row_ss`` [M, parts] are partial sums of squares of ``a``'s
     rows; when given, each output row is scaled by rsqrt(sum/norm_dim + eps) (the norm weight must
     already be folded into ``w``)."""
+    from .quant_gemm import QuantWeight, qgemm
+    if isinstance(w, QuantWeight):      # quantised weight: dequantisation fused into the GEMM main loop
+        y = qgemm(a, w, row_ss=row_ss, norm_dim=norm_dim, eps=eps)
+        if bias is not None or out_dtype != y.dtype:
+            y = (y.float() + bias.float() if bias is not None else y.float()).to(out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     M, K = a.shape
     N = w.shape[0]
     if not a.is_cuda:
@@ -109,6 +118,21 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
 def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=None, max_ctas=0, splits=0):
     """out = a @ w.T (+bias) + residual (bf16). Returns (out, row_ss) where row_ss[M, ceil(N/bn)] holds the
     per-tile sums of squares of ``out``: the next layer's RMSNorm statistics."""
+    from .quant_gemm import QuantWeight, qgemm
+    if isinstance(w, QuantWeight):
+        from .elementwise import rmsnorm
+        M = a.shape[0]
+        y = qgemm(a, w)
+        if bias is not None:
+            y = (y.float() + bias.float()).to(y.dtype)
+        out = residual if out is None else out
+        ss = row_ss_out if row_ss_out is not None else torch.empty((M, 1), dtype=torch.float32, device=a.device)
+        rmsnorm(y, None, 0.0, residual=residual, h_out=out, ss_out=ss, want_y=False)
+        if ss.dim() > 1 and ss.shape[1] > 1:      # statistics land in column 0; the other tile columns are zero
+            flat = ss.reshape(-1)[:M].clone()
+            ss[:M].zero_()
+            ss[:M, 0] = flat
+        return out, ss
     M, K = a.shape
     N = w.shape[0]
     bn = bn or _bn_for(N, M)

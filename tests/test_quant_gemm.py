@@ -85,3 +85,47 @@ def test_qgemm_kernel_matches_dequantised_reference(mode, group, M, N, K, splits
     assert (gotn - wantn).abs().max().item() < 0.02 * wantn.abs().max().item() + 1e-3
     from gllm_b200.ops import _native as nv
     assert nv.device_error() == 0
+
+
+def _logits(model, ids, dev):
+    from gllm_b200.engine.batch import ForwardBatch
+    T = len(ids)
+    b = ForwardBatch(token_ids=torch.tensor(ids, dtype=torch.int32, device=dev), positions=torch.arange(T, dtype=torch.int32, device=dev),
+                     slot_mapping=torch.arange(T, dtype=torch.int32, device=dev),
+                     block_tables=torch.arange(8, dtype=torch.int32, device=dev)[None],
+                     ctx_lens=torch.tensor([T], dtype=torch.int32, device=dev), q_start=torch.tensor([0], dtype=torch.int32, device=dev),
+                     q_len=torch.tensor([T], dtype=torch.int32, device=dev), max_q_len=T)
+    return model.forward(b, model.alloc_kv_cache(8))[:, :model.cfg.vocab_size].float().cpu()
+
+
+def test_model_with_load_time_quantised_weights_cpu():
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    dense = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=128)
+    ids = list(range(3, 40))
+    want = _logits(dense, ids, "cpu")
+    for mode, tol in (("int8", 0.999), ("fp8", 0.995), ("int4", 0.96)):
+        qm = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=128, weight_quant=mode)
+        assert isinstance(qm.layers[0].wqkv, Q.QuantWeight) and qm.weight_bytes() < dense.weight_bytes() * (0.4 if mode != "int4" else 0.25)
+        got = _logits(qm, ids, "cpu")
+        cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0).item()
+        assert cos > tol, (mode, cos)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["fp8", "int4"])
+def test_quantised_model_gpu_matches_cpu(mode):
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    cpu = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=128, weight_quant=mode)
+    gpu = DecoderModel(cfg, src, device="cuda", dtype=torch.bfloat16, max_positions=128, weight_quant=mode)
+    ids = list(range(3, 80))
+    a, b = _logits(gpu, ids, "cuda"), _logits(cpu, ids, "cpu")
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    assert cos > 0.99, cos
