@@ -98,6 +98,8 @@ struct GemmParams {
   // memory over NVLink as each tile retires.
   const int* scatter_meta;
   __nv_bfloat16* scatter_peer[8];
+  int cluster_sk;     // 1: the splits of a tile form a thread-block cluster and reduce through distributed shared memory
+  long long* trace;   // debugging aid: when set, CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
 };
 
@@ -225,96 +227,11 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num
 __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
 __device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
 
-// Phase 2 of a split-K GEMM: a warp owns (row, n tile) units, four at a time; lanes cover a unit's
-// columns with vector loads. Loads of several units and several splits are issued together (the phase
-// is latency bound: few threads, L2 round trips), the adds happen in split order so the result does
-// not depend on timing, then the fused epilogue of EPI is applied.
-template <int BN, int EPI>
-__device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int nsplits, bool zero_after) {
-  constexpr bool kGlu = (EPI == EPI_GLU), kQkv = (EPI == EPI_QKV);
-  constexpr int NSEG = (kGlu || kQkv) ? 2 : BN / 128;            // vector segments per lane and unit
-  constexpr int SEGW = (kQkv || (kGlu && BN == 128)) ? 2 : 4;    // floats per segment
-  constexpr int NV = NSEG * SEGW;
-  constexpr int U = 4;                                           // units in flight per warp
-  constexpr int SU = (NV == 8) ? 2 : 4;                          // splits in flight
-  const int lane = threadIdx.x & 31;
-  const int warps_per_cta = blockDim.x >> 5;
-  const long long n_pad = static_cast<long long>(p.num_n) * BN;
-  const long long split_stride = static_cast<long long>(p.M) * n_pad;
-  const int units = p.M * p.num_n;
-  int seg_off[NSEG];
-  if constexpr (kGlu || kQkv) {
-    seg_off[0] = lane * SEGW;
-    seg_off[1] = BN / 2 + lane * SEGW;
-  } else {
-#pragma unroll
-    for (int g = 0; g < NSEG; ++g) seg_off[g] = lane * NV + g * 4;
-  }
-  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
-       u0 += gridDim.x * warps_per_cta * U) {
-    float acc[U][NV];
-    float* base[U];
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const int u = min(u0 + k, units - 1);
-      base[k] = src_base + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
-#pragma unroll
-      for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
-    }
-    for (int s0 = 0; s0 < nsplits; s0 += SU) {
-      float tmp[SU][U][NV];
-#pragma unroll
-      for (int ds = 0; ds < SU; ++ds) {
-        const int s = min(s0 + ds, nsplits - 1);
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-#pragma unroll
-          for (int g = 0; g < NSEG; ++g) {
-            const float* src = base[k] + s * split_stride + seg_off[g];
-            if constexpr (SEGW == 4) {
-              const float4 f = ldcg4(src);
-              tmp[ds][k][g * 4 + 0] = f.x; tmp[ds][k][g * 4 + 1] = f.y;
-              tmp[ds][k][g * 4 + 2] = f.z; tmp[ds][k][g * 4 + 3] = f.w;
-            } else {
-              const float2 f = ldcg2(src);
-              tmp[ds][k][g * 2 + 0] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int ds = 0; ds < SU; ++ds) {
-        if (s0 + ds < nsplits) {
-#pragma unroll
-          for (int k = 0; k < U; ++k)
-#pragma unroll
-            for (int j = 0; j < NV; ++j) acc[k][j] += tmp[ds][k][j];
-        }
-      }
-    }
-    if (zero_after) {  // the all-reduce accumulation buffer must be zero again before its next use
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        if (u0 + k < units) {
-#pragma unroll
-          for (int g = 0; g < NSEG; ++g) {
-            if constexpr (SEGW == 4)
-              __stcg(reinterpret_cast<float4*>(base[k] + seg_off[g]), make_float4(0.f, 0.f, 0.f, 0.f));
-            else
-              __stcg(reinterpret_cast<float2*>(base[k] + seg_off[g]), make_float2(0.f, 0.f));
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < U; ++k) {  // fully unrolled: acc[k] must stay in registers
-      const int u = u0 + k;
-      if (u >= units) continue;
-      const int n_blk = u % p.num_n;
-      const int m = u / p.num_n;
-      float v[NV];
-#pragma unroll
-      for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
+// The fused epilogue of EPI for one (row m, n tile) unit whose summed accumulator values a lane holds in v
+// (lane -> column mapping as in splitk_reduce_phase). Shared by the global-memory and the cluster reduce phases.
+template <int BN, int EPI, int NV, int SEGW>
+__device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, int n_blk, int lane, float (&v)[NV],
+                                                    const uint2* pre_residual = nullptr) {
       float rs = row_scale_of(p, m);
       if (p.a_scale) rs *= p.a_scale[m];
       if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
@@ -328,7 +245,9 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
             if (p.bias) v[j] += p.bias[n0 + j];
           }
           if constexpr (EPI == EPI_RESIDUAL) {
-            const __nv_bfloat16* r = p.residual + static_cast<long long>(m) * p.ldr + n0;
+            // pre_residual: the 4 residual values of this lane, loaded by the caller ahead of a long-latency phase
+            const __nv_bfloat16* r = (NV == 4 && pre_residual) ? reinterpret_cast<const __nv_bfloat16*>(pre_residual)
+                                                               : p.residual + static_cast<long long>(m) * p.ldr + n0;
 #pragma unroll
             for (int j = 0; j < NV; j += 2) {
               const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r + j));
@@ -438,6 +357,99 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
           *reinterpret_cast<uint32_t*>(dst + 64 + lane * 2) = pack_bf16x2(b[0], b[1]);
         }
       }
+}
+
+// Phase 2 of a split-K GEMM: a warp owns (row, n tile) units, four at a time; lanes cover a unit's
+// columns with vector loads. Loads of several units and several splits are issued together (the phase
+// is latency bound: few threads, L2 round trips), the adds happen in split order so the result does
+// not depend on timing, then the fused epilogue of EPI is applied.
+template <int BN, int EPI>
+__device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int nsplits, bool zero_after) {
+  constexpr bool kGlu = (EPI == EPI_GLU), kQkv = (EPI == EPI_QKV);
+  constexpr int NSEG = (kGlu || kQkv) ? 2 : BN / 128;            // vector segments per lane and unit
+  constexpr int SEGW = (kQkv || (kGlu && BN == 128)) ? 2 : 4;    // floats per segment
+  constexpr int NV = NSEG * SEGW;
+  constexpr int U = 4;                                           // units in flight per warp
+  constexpr int SU = (NV == 8) ? 2 : 4;                          // splits in flight
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const long long split_stride = static_cast<long long>(p.M) * n_pad;
+  const int units = p.M * p.num_n;
+  int seg_off[NSEG];
+  if constexpr (kGlu || kQkv) {
+    seg_off[0] = lane * SEGW;
+    seg_off[1] = BN / 2 + lane * SEGW;
+  } else {
+#pragma unroll
+    for (int g = 0; g < NSEG; ++g) seg_off[g] = lane * NV + g * 4;
+  }
+  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
+       u0 += gridDim.x * warps_per_cta * U) {
+    float acc[U][NV];
+    float* base[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      base[k] = src_base + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
+    }
+    for (int s0 = 0; s0 < nsplits; s0 += SU) {
+      float tmp[SU][U][NV];
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        const int s = min(s0 + ds, nsplits - 1);
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+#pragma unroll
+          for (int g = 0; g < NSEG; ++g) {
+            const float* src = base[k] + s * split_stride + seg_off[g];
+            if constexpr (SEGW == 4) {
+              const float4 f = ldcg4(src);
+              tmp[ds][k][g * 4 + 0] = f.x; tmp[ds][k][g * 4 + 1] = f.y;
+              tmp[ds][k][g * 4 + 2] = f.z; tmp[ds][k][g * 4 + 3] = f.w;
+            } else {
+              const float2 f = ldcg2(src);
+              tmp[ds][k][g * 2 + 0] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        if (s0 + ds < nsplits) {
+#pragma unroll
+          for (int k = 0; k < U; ++k)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) acc[k][j] += tmp[ds][k][j];
+        }
+      }
+    }
+    if (zero_after) {  // the all-reduce accumulation buffer must be zero again before its next use
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        if (u0 + k < units) {
+#pragma unroll
+          for (int g = 0; g < NSEG; ++g) {
+            if constexpr (SEGW == 4)
+              __stcg(reinterpret_cast<float4*>(base[k] + seg_off[g]), make_float4(0.f, 0.f, 0.f, 0.f));
+            else
+              __stcg(reinterpret_cast<float2*>(base[k] + seg_off[g]), make_float2(0.f, 0.f));
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {  // fully unrolled: acc[k] must stay in registers
+      const int u = u0 + k;
+      if (u >= units) continue;
+      const int n_blk = u % p.num_n;
+      const int m = u / p.num_n;
+      float v[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
+      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v);
     }
   }
 }
@@ -534,6 +546,160 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// split-K inside a thread-block cluster: the S CTAs that share an output tile park their fp32 partial tiles in
+// their own shared memory, write the rows that OTHER members will finish to the global scratch with coalesced
+// stores, meet at one cluster barrier (instead of a grid-wide one) and each finishes 1/S of the rows: its own
+// partial from shared memory, the others' from L2. Measured on B200: reading peers' tiles through distributed
+// shared memory was 3-4x slower than through L2 (the SM-to-SM path moves far fewer bytes per clock than the
+// 64 B/clk L2 port), so DSMEM is not used for the bulk data.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t cta) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(cta));
+  return ra;
+}
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_dsmem_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+
+constexpr int kClusterPartStride = 128 + 4;  // floats per row of the shared-memory partial tile (padded: no bank conflicts)
+
+// Rows of the tile that cluster member `rank` finishes.
+__device__ __forceinline__ void cluster_row_range(int rows, int S, int rank, int& b, int& e) {
+  b = static_cast<int>(static_cast<long long>(rank) * rows / S);
+  e = static_cast<int>(static_cast<long long>(rank + 1) * rows / S);
+}
+
+// part: this CTA's partial tile [rows][kClusterPartStride] fp32 in shared memory. Writes every row that another
+// member finishes to scratch[ks][m][n_pad] (one warp per row: 512 contiguous bytes per store instruction).
+__device__ void cluster_publish_partials(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int S,
+                                         int ks) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * 128;
+  int own_b, own_e;
+  cluster_row_range(rows, S, ks, own_b, own_e);
+  float* dst_base = p.sk_scratch + (static_cast<long long>(ks) * p.M) * n_pad + static_cast<long long>(n_blk) * 128 + lane * 4;
+  for (int r = warp; r < rows; r += nwarps) {
+    if (r >= own_b && r < own_e) continue;
+    const int m = m_row0 + r;
+    if (m >= p.M) continue;
+    const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    __stcg(reinterpret_cast<float4*>(dst_base + static_cast<long long>(m) * n_pad), v);
+  }
+}
+
+// After the cluster barrier: this member (split index ks == cluster rank) finishes its rows of tile (m_sup, n_blk).
+template <int EPI>
+__device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int S,
+                                     int ks) {
+  constexpr int BN = 128;
+  constexpr bool kGlu = (EPI == EPI_GLU), kQkv = (EPI == EPI_QKV);
+  constexpr int NSEG = (kGlu || kQkv) ? 2 : 1;
+  constexpr int SEGW = (kGlu || kQkv) ? 2 : 4;
+  constexpr int NV = NSEG * SEGW;
+  constexpr int U = (SEGW == 4) ? 8 : 4;   // rows in flight per warp: with 8 warps that is the whole share of a 4-way split
+  constexpr int SU = 4;   // splits in flight
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int r_begin, r_end;
+  cluster_row_range(rows, S, ks, r_begin, r_end);
+  int seg_off[NSEG];
+  if constexpr (kGlu || kQkv) {
+    seg_off[0] = lane * SEGW;
+    seg_off[1] = BN / 2 + lane * SEGW;
+  } else {
+    seg_off[0] = lane * 4;
+  }
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const long long split_stride = static_cast<long long>(p.M) * n_pad;
+  for (int r0 = r_begin + warp; r0 < r_end; r0 += nwarps * U) {
+    float acc[U][NV];
+    uint2 pre[U];
+    const float* gbase[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
+      pre[k] = make_uint2(0u, 0u);
+      const int r = min(r0 + k * nwarps, r_end - 1);
+      const int m = min(m_row0 + r, p.M - 1);
+      gbase[k] = p.sk_scratch + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN;
+      if constexpr (EPI == EPI_RESIDUAL) {   // ask for the residual together with the partials
+        const int n0 = n_blk * BN + lane * 4;
+        if (n0 < p.N) pre[k] = *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+      }
+    }
+    for (int s0 = 0; s0 < S; s0 += SU) {   // split order: the sum does not depend on timing
+      float tmp[SU][U][NV];
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        const int sidx = min(s0 + ds, S - 1);
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+          const int r = min(r0 + k * nwarps, r_end - 1);
+#pragma unroll
+          for (int g = 0; g < NSEG; ++g) {
+            if (sidx == ks) {   // own partial: shared memory
+              const float* src = part + r * kClusterPartStride + seg_off[g];
+              if constexpr (SEGW == 4) {
+                const float4 f = *reinterpret_cast<const float4*>(src);
+                tmp[ds][k][0] = f.x; tmp[ds][k][1] = f.y; tmp[ds][k][2] = f.z; tmp[ds][k][3] = f.w;
+              } else {
+                const float2 f = *reinterpret_cast<const float2*>(src);
+                tmp[ds][k][g * 2] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
+              }
+            } else {
+              const float* src = gbase[k] + sidx * split_stride + seg_off[g];
+              if constexpr (SEGW == 4) {
+                const float4 f = ldcg4(src);
+                tmp[ds][k][0] = f.x; tmp[ds][k][1] = f.y; tmp[ds][k][2] = f.z; tmp[ds][k][3] = f.w;
+              } else {
+                const float2 f = ldcg2(src);
+                tmp[ds][k][g * 2] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int ds = 0; ds < SU; ++ds) {
+        if (s0 + ds < S) {
+#pragma unroll
+          for (int k = 0; k < U; ++k)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) acc[k][j] += tmp[ds][k][j];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int r = r0 + k * nwarps;
+      if (r >= r_end) continue;
+      const int m = m_row0 + r;
+      if (m >= p.M) continue;
+      float v[NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
+      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v, EPI == EPI_RESIDUAL ? &pre[k] : nullptr);
+    }
+  }
+}
+
 template <int BN, int MT, int EPI, bool FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -559,6 +725,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int splits = p.splits;
   const bool fused_ar = p.ar_world > 0;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  if (tracing && threadIdx.x == 0) p.trace[0] = clock64();
   __shared__ unsigned long long ar_expected_s;
   __shared__ unsigned int ar_launch_s;
   if (fused_ar && threadIdx.x == 0) {
@@ -592,6 +760,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
+  if (tracing && threadIdx.x == 0) p.trace[1] = clock64();
 
   // work item -> (k split, m super tile, n tile); the splits of one output tile are adjacent so
   // they run at the same time and the reduction does not wait long
@@ -666,6 +835,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             break;
           }
           tc_fence_after();
+          if (tracing && it_cur == 0 && kb == kb0) p.trace[2] = clock64();
           const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
           const uint64_t b_desc = umma_desc_sw128(sa + MT * kABytes);
 #pragma unroll
@@ -687,6 +857,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
         if (ok) umma_commit(&tmem_full[acc]);
+        if (tracing && it_cur == 0) p.trace[3] = clock64();
       }
     }
     __syncwarp();
@@ -709,11 +880,35 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         break;
       }
       tc_fence_after();
+      if (tracing && it_cur == 0 && warp == 4 && lane == 0) p.trace[4] = clock64();
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * BN);
 
       // ---- split-K phase 1: dump this CTA's fp32 partial tile; the fused epilogue runs in phase 2 ----
       bool finisher = true;
-      if (splits > 1 || fused_ar) {
+      if constexpr (BN == 128) {
+        if (p.cluster_sk) {
+          // cluster split-K: park the fp32 partial tile in shared memory (the pipeline stages are idle: every load of
+          // this CTA's only work item was consumed before the accumulator became ready)
+          finisher = false;
+          float* part = reinterpret_cast<float*>(tiles);
+#pragma unroll 1
+          for (int i = 0; i < MT; ++i) {
+            float* prow = part + static_cast<long long>(i * kBM + q * 32 + lane) * kClusterPartStride;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(taddr0 + i * BN + c * 32, r);
+              tmem_ld_wait();
+              float4* d4 = reinterpret_cast<float4*>(prow + c * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                d4[j] = make_float4(__uint_as_float(r[j * 4]), __uint_as_float(r[j * 4 + 1]), __uint_as_float(r[j * 4 + 2]),
+                                    __uint_as_float(r[j * 4 + 3]));
+            }
+          }
+        }
+      }
+      if (!p.cluster_sk && (splits > 1 || fused_ar)) {
         finisher = false;
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
         const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems : 0;
@@ -923,6 +1118,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (tracing && it_cur == 0 && warp == 4 && lane == 0) p.trace[5] = clock64();
     }
   }
 
@@ -930,7 +1126,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
 
+  if constexpr (BN == 128) {
+    if (p.cluster_sk) {
+      // one work item per CTA: blockIdx.x is the item; its splits are the CTAs of this cluster
+      int ks, m_sup, n_blk, kb0, kb1;
+      decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
+      const float* part = reinterpret_cast<const float*>(tiles);
+      cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, splits, ks);
+      cluster_barrier();   // release / acquire at cluster scope: the members' scratch rows are visible
+      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      cluster_reduce_phase<EPI>(p, part, MT * kBM, m_sup * MT * kBM, n_blk, splits, ks);
+      if (tracing && threadIdx.x == 0) p.trace[8] = clock64();
+      return;
+    }
+  }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
     if (fused_ar) {
       // all CTAs of all ranks have added their tiles once the local counter reaches the target
@@ -946,14 +1157,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     } else if (splits > 1) {
       // every partial of every CTA must be visible before anyone reduces
-      if (grid_barrier(p.sk_barrier, gridDim.x, p.err)) splitk_reduce_phase<BN, EPI>(p, p.sk_scratch, splits, false);
+      const bool bar_ok = grid_barrier(p.sk_barrier, gridDim.x, p.err);
+      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      if (bar_ok) splitk_reduce_phase<BN, EPI>(p, p.sk_scratch, splits, false);
     }
   }
+  if (tracing && threadIdx.x == 0) p.trace[8] = clock64();
 }
 
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
+static long long* g_trace_ptr = nullptr;
+
 struct SplitKWorkspace {
   float* scratch = nullptr;
   long long scratch_floats = 0;
@@ -965,7 +1181,7 @@ static SplitKWorkspace g_splitk[64];
 // shared memory, work items run in waves of `sms`, a split costs the dump of its partial tile, and the
 // reduce phase re-reads all partials at a few TB/s after one grid barrier.
 static int choose_splits(int tiles, int num_kb, int stage_bytes, long long tile_floats, long long out_floats, int sms,
-                         long long scratch_floats) {
+                         long long scratch_floats, bool cluster_ok) {
   if (tiles >= 2 * sms || num_kb < 4) return 1;
   double best = 1e30;
   int best_s = 1;
@@ -978,6 +1194,9 @@ static int choose_splits(int tiles, int num_kb, int stage_bytes, long long tile_
     double total;
     if (s == 1) {
       total = waves * (t_item + tile_floats * 4 / 200e3);
+    } else if (cluster_ok && s <= 8 && items <= sms) {
+      // cluster split-K: partials stay in shared memory, one cluster barrier, rows reduced through DSMEM
+      total = t_item + 2.5;
     } else {
       t_item += tile_floats * 4 / 100e3;
       total = waves * t_item + 2.0 + (double)s * out_floats * 4 / 3.5e6 + 1.5;
@@ -1005,6 +1224,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     set_last_error("gemm: N=%d must be a multiple of 32 (pad the weight at load time)", p.N);
     return -1;
   }
+  p.trace = g_trace_ptr;
   p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1036,7 +1256,8 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   else if (p.ar_world > 0)  // each rank publishes exactly one partial per tile
     splits = 1;
   else if (ws.scratch)
-    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats);
+    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats,
+                           BN == 128 && max_ctas <= 0 && !(getenv("GLLM_NO_CLUSTER_SK") && getenv("GLLM_NO_CLUSTER_SK")[0] == '1'));
   if (p.ar_world > 0) {
     if (out_floats > p.ar_buf_elems || (static_cast<long long>(p.num_n) * BN) % 256 != 0) {
       set_last_error("fused all-reduce: output needs %lld elements per buffer (have %lld), padded width %% 256",
@@ -1056,6 +1277,46 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   p.sk_barrier = ws.barrier;
   const int items = tiles * splits;
   const int grid = items < sms ? items : sms;
+  // Cluster split-K: the splits of a tile become one thread-block cluster (one work item per CTA) and reduce through
+  // distributed shared memory instead of global scratch + grid barrier.
+  static const bool cluster_allowed = [] {
+    const char* v = getenv("GLLM_NO_CLUSTER_SK");
+    return !(v && v[0] == '1');
+  }();
+  const bool part_fits = static_cast<long long>(MT) * kBM * kClusterPartStride * 4 <= static_cast<long long>(Cfg::kStages) * Cfg::kStageBytes;
+  if (BN == 128 && cluster_allowed && splits >= 2 && splits <= 8 && items <= sms && part_fits && p.ar_world == 0 &&
+      p.mblk_group == nullptr && max_ctas <= 0) {
+    p.cluster_sk = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(items, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // Clusters are placed inside one GPC; when the GPC sizes do not let every cluster of this launch run at once the
+    // launch would take a second wave, which costs more than the reduce saves: use the global-scratch path then.
+    static int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};   // per cluster size, 0 = not queried yet
+    if (max_clusters[splits] == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = -1;
+      }
+      max_clusters[splits] = n > 0 ? n : -1;
+    }
+    if (max_clusters[splits] >= tiles) {
+      cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+      if (ce == cudaSuccess) return 0;
+      (void)cudaGetLastError();   // this cluster shape cannot be scheduled here: fall back
+    }
+    p.cluster_sk = 0;
+  }
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1228,6 +1489,11 @@ GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const 
   const long long b_rows = static_cast<long long>(num_groups) * N;
   return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, 1);
 }
+
+// Debugging aid: CTA 0 of every following GEMM launch writes 9 SM-clock stamps to `buf` (device memory, 9 x int64):
+// entry, set-up done, first stage landed, MMAs of the first item issued, first accumulator ready, first epilogue
+// done, main loop left, split-K barrier passed, exit. Pass null to switch it off.
+GLLM_API void gllm_gemm_set_trace(long long* buf) { g_trace_ptr = buf; }
 
 // Fused QKV projection for head_dim 128: rowscale -> per-head RMSNorm (optional) -> RoPE -> q buffer and
 // paged KV write.  B is [(Hq+2Hkv)*128, K] with q heads first, then k heads, then v heads.
