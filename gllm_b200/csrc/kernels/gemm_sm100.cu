@@ -98,6 +98,8 @@ struct GemmParams {
   // memory over NVLink as each tile retires.
   const int* scatter_meta;
   __nv_bfloat16* scatter_peer[8];
+  int park;           // 1: one work item per CTA: the fp32 accumulator tile is parked in shared memory and written out
+                      //    by all warps with row-contiguous stores (split-K scratch or the all-reduce buffer)
   int cluster_sk;     // 1: the splits of a tile form a thread-block cluster and reduce through distributed shared memory
   long long* trace;   // debugging aid: when set, CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
@@ -589,11 +591,11 @@ __device__ __forceinline__ void cluster_row_range(int rows, int S, int rank, int
 // part: this CTA's partial tile [rows][kClusterPartStride] fp32 in shared memory. Writes every row that another
 // member finishes to scratch[ks][m][n_pad] (one warp per row: 512 contiguous bytes per store instruction).
 __device__ void cluster_publish_partials(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int S,
-                                         int ks) {
+                                         int ks, bool skip_own = true) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const long long n_pad = static_cast<long long>(p.num_n) * 128;
-  int own_b, own_e;
-  cluster_row_range(rows, S, ks, own_b, own_e);
+  int own_b = 0, own_e = 0;
+  if (skip_own) cluster_row_range(rows, S, ks, own_b, own_e);
   float* dst_base = p.sk_scratch + (static_cast<long long>(ks) * p.M) * n_pad + static_cast<long long>(n_blk) * 128 + lane * 4;
   for (int r = warp; r < rows; r += nwarps) {
     if (r >= own_b && r < own_e) continue;
@@ -886,8 +888,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // ---- split-K phase 1: dump this CTA's fp32 partial tile; the fused epilogue runs in phase 2 ----
       bool finisher = true;
       if constexpr (BN == 128) {
-        if (p.cluster_sk) {
-          // cluster split-K: park the fp32 partial tile in shared memory (the pipeline stages are idle: every load of
+        if (p.cluster_sk || p.park) {
+          // park the fp32 partial tile in shared memory (the pipeline stages are idle: every load of
           // this CTA's only work item was consumed before the accumulator became ready)
           finisher = false;
           float* part = reinterpret_cast<float*>(tiles);
@@ -908,7 +910,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-      if (!p.cluster_sk && (splits > 1 || fused_ar)) {
+      if (!p.cluster_sk && !p.park && (splits > 1 || fused_ar)) {
         finisher = false;
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
         const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems : 0;
@@ -1142,6 +1144,31 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       return;
     }
   }
+  if constexpr (BN == 128) {
+    if (p.park) {
+      // every warp writes whole rows of the parked tile: 512 (fp32 scratch) or 256 (bf16 all-reduce buffer)
+      // contiguous bytes per store instruction instead of 64-byte pieces of 32 different rows
+      int ks, m_sup, n_blk, kb0, kb1;
+      decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
+      const float* part = reinterpret_cast<const float*>(tiles);
+      if (fused_ar) {
+        const long long n_pad = static_cast<long long>(p.num_n) * BN;
+        __nv_bfloat16* dst = p.ar_peer_buf[p.ar_rank] + static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems +
+                             static_cast<long long>(n_blk) * BN + lane * 4;
+        for (int r = warp; r < MT * kBM; r += kGemmThreads / 32) {
+          const int m = m_sup * MT * kBM + r;
+          if (m >= p.M) continue;
+          const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+          uint2 w;
+          w.x = pack_bf16x2(v.x, v.y);
+          w.y = pack_bf16x2(v.z, v.w);
+          *reinterpret_cast<uint2*>(dst + static_cast<long long>(m) * n_pad) = w;
+        }
+      } else {
+        cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, /*S=*/1, /*ks=*/ks, /*skip_own=*/false);
+      }
+    }
+  }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
     if (fused_ar) {
       // all CTAs of all ranks have added their tiles once the local counter reaches the target
@@ -1317,6 +1344,12 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     }
     p.cluster_sk = 0;
   }
+  static const bool park_allowed = [] {
+    const char* v = getenv("GLLM_NO_PARK");
+    return !(v && v[0] == '1');
+  }();
+  p.park = (BN == 128 && park_allowed && (splits > 1 || p.ar_world > 0) && items <= grid && part_fits &&
+            p.mblk_group == nullptr) ? 1 : 0;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
