@@ -102,7 +102,7 @@ class DecoderModel:
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
-                                        ep=getattr(tp, "ep", None), fused=self.fused)
+                                        ep=getattr(tp, "ep", None), fused=self.fused, tp=tp)
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
         self.lm_head = None

@@ -39,6 +39,7 @@ class MoeLayerWeights:
     cfg: Optional[ModelConfig] = None
     fused: bool = True
     ep: Optional[object] = None
+    tp_experts: Optional[object] = None  # tensor-parallel context when the experts are split over the TP ranks
     _ws: Optional[M.MoeWorkspace] = None
 
     # ------------------------------------------------------------------------------------------
@@ -72,6 +73,8 @@ class MoeLayerWeights:
         ids, w = self._route(x, ss_in, ws, T, H, c.rms_norm_eps)
         if self.ep is not None:
             return self.ep.moe_forward(self, model, x, ss_in, ss_out, ids, w, ws, T)
+        if self.tp_experts is not None:
+            return self._forward_tp_experts(model, x, x, ss_in, ss_out, ids, w, ws, T, fused_norm=True)
         M.permute(x, ss_in, ids, ws, self.e0, self.e_local)
         L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, row_ss=ws.ss_perm, norm_dim=H,
                    eps=c.rms_norm_eps, bn=self.glu_bn, mblk_group=ws.blk_group, num_groups=self.e_local)
@@ -85,6 +88,37 @@ class MoeLayerWeights:
         M.combine(x, ws.y_perm, ws.dest, w, shared=shared, ss_out=ss)
         return ss
 
+    def _forward_tp_experts(self, model, x, src, ss_in, ss_out, ids, w, ws, T, fused_norm: bool):
+        """Tensor-parallel attention + expert-parallel FFN on the same ranks: the tokens are replicated, so each
+        rank runs only ITS experts on the rows routed to them and the weighted partial sums are all-reduced
+        (same bytes on the wire as dispatch + combine, no token exchange). ``src`` is what the experts read
+        (the residual stream with the norm folded into the weights, or the normalised hidden)."""
+        import torch.distributed as dist
+        c = self.cfg
+        H = c.hidden_size
+        M.permute(src, ss_in if fused_norm else None, ids, ws, self.e0, self.e_local)
+        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, row_ss=ws.ss_perm if fused_norm else None,
+                   norm_dim=H if fused_norm else 0, eps=c.rms_norm_eps if fused_norm else 0.0, bn=self.glu_bn,
+                   mblk_group=ws.blk_group, num_groups=self.e_local)
+        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        holder = model.__dict__.setdefault("_moe_partial", {})
+        part = holder.get("buf")
+        if part is None or part.shape[0] < T:
+            part = holder["buf"] = torch.zeros((max(T, 256), H), dtype=x.dtype, device=x.device)
+        p = part[:T]
+        p.zero_()
+        M.combine(p, ws.y_perm, ws.dest, w)            # this rank's share of sum_k w_k * expert_k(x)
+        tp = self.tp_experts
+        if tp.size > 1:
+            dist.all_reduce(p, group=tp.group)
+        if self.shared_gate_up is not None:               # replicated: added once, after the reduction
+            sa = L.gemm_glu(src, self.shared_gate_up, act=model.act_id, row_ss=ss_in if fused_norm else None,
+                            norm_dim=H if fused_norm else 0, eps=c.rms_norm_eps if fused_norm else 0.0, bn=self.shared_bn)
+            p.add_(ops.gemm(sa, self.shared_down, out_dtype=x.dtype, bn=128))
+        ss = None if ss_out is None else ss_out.reshape(-1)[:T].view(T, 1)
+        ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
+        return ss
+
     def forward_unfused(self, model, x, h, T):
         """Unfused path: ``h`` is the already normalised input; adds the MoE output into ``x``."""
         c = self.cfg
@@ -92,6 +126,9 @@ class MoeLayerWeights:
         ids, w = self._route(h, None, ws, T, 0, 0.0)
         if self.ep is not None:
             self.ep.moe_forward(self, model, x, None, None, ids, w, ws, T, normalised_input=h)
+            return
+        if self.tp_experts is not None:
+            self._forward_tp_experts(model, x, h, None, None, ids, w, ws, T, fused_norm=False)
             return
         M.permute(h, None, ids, ws, self.e0, self.e_local)
         L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
@@ -104,11 +141,15 @@ class MoeLayerWeights:
         M.combine(x, ws.y_perm, ws.dest, w, shared=shared)
 
 
-def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, device, dtype, ep=None, fused=True):
+def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, device, dtype, ep=None, fused=True, tp=None):
     """Experts are split over the expert-parallel group (``ep``), or kept whole when there is none; the shared
     expert and the router are replicated."""
     p = layer_prefix(i)
     ep_rank, ep_size = (ep.rank, ep.size) if ep is not None else (0, 1)
+    tp_experts = None
+    if ep is None and tp is not None and tp_size > 1 and cfg.num_experts % tp_size == 0 and getattr(tp, "shard_experts", True):
+        # tensor-parallel attention + expert-parallel FFN on the same ranks
+        ep_rank, ep_size, tp_experts = tp_rank, tp_size, tp
     e0, e1 = shard_range(cfg.num_experts, ep_rank, ep_size)
     post = src.get(p + "post_attn_norm").float().to(device)
     inter = cfg.moe_intermediate_size
@@ -129,7 +170,7 @@ def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, de
     rb = src.get(p + "router_bias").float().to(device) if src.has(p + "router_bias") else None
     lw = MoeLayerWeights(router=router, router_bias=rb, w_gate_up=torch.cat(gus, 0).contiguous(),
                          w_down=torch.cat(downs, 0).contiguous(), glu_bn=bn, e0=e0, e_local=e1 - e0, inter=inter,
-                         cfg=cfg, fused=fused, ep=ep)
+                         cfg=cfg, fused=fused, ep=ep, tp_experts=tp_experts)
     if cfg.num_shared_experts and src.has(p + "shared_expert.gate_proj"):
         g = src.get(p + "shared_expert.gate_proj").to(device, dtype)
         u = src.get(p + "shared_expert.up_proj").to(device, dtype)

@@ -94,7 +94,7 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
             acc = acc * rs[:, None]
         if bias is not None:
             acc = acc + bias.float()
-        res = acc.to(out_dtype)
+        res = acc.to(out.dtype if out is not None else out_dtype)
         if out is not None:
             out.copy_(res)
             return out

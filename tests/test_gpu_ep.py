@@ -31,3 +31,15 @@ def test_ep_two_gpus(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(2, mode, 29832 + (mode == "a2a"))
+
+
+@pytest.mark.multigpu
+def test_tp_attention_plus_expert_sharded_moe_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29839", os.path.join(ROOT, "tests", "tp_moe_worker.py"), "gpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_MOE_WORKER_OK") == 2

@@ -296,3 +296,12 @@ def test_pipeline_parallel_generation_matches_single_process(world):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("PP_WORKER_OK") == world
+
+
+def test_tp_attention_with_expert_sharded_moe_matches_unsplit_model():
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29795", os.path.join(ROOT, "tests", "tp_moe_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_MOE_WORKER_OK") == 2
