@@ -25,6 +25,8 @@ from .. import ops
 from .. import scheduler as S
 from ..models.config import ModelConfig
 from ..models.decoder import DecoderModel
+from ..utils.metrics import GLOBAL as METRICS
+from ..utils.tracing import nvtx_range
 from .batch import ForwardBatch, GenerateResult, SequenceTelemetry
 
 DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024)
@@ -275,9 +277,13 @@ class LLMEngine:
         dec_tokens = np.zeros(self.ms, np.int32)
         pf_tokens = np.zeros(0, np.int32)
         if plan.num_decode > 0:
-            dec_tokens = self._run_decode(plan).copy()
+            with nvtx_range("decode_step"):
+                dec_tokens = self._run_decode(plan).copy()
         if plan.num_prefill_seqs > 0:
-            pf_tokens = self._run_prefill(plan)
+            with nvtx_range("prefill_chunk"):
+                pf_tokens = self._run_prefill(plan)
+        METRICS.set("kv_free_pages", float(self.batcher.num_free_pages))
+        METRICS.set("running_requests", float(len(self.reqs)))
         now = time.perf_counter()
         ids = plan.dec_seq_ids
         # hooks / streaming observe the sampled tokens before they are committed
@@ -332,6 +338,7 @@ class LLMEngine:
                 tel.tpot_ms = ((st.t_last - st.t_first) * 1e3 / max(st.n_out - 1, 1)) if st.n_out > 1 else 0.0
             text = self.tokenizer.decode(toks) if self.tokenizer is not None else ""
             r = GenerateResult(request_id=f.id, token_ids=toks, text=text, finish_reason=reason, telemetry=tel)
+            METRICS.record_request(tel)
             self.results[f.id] = r
             out.append(r)
         return out
