@@ -35,6 +35,7 @@ class TPContext:
         self.mode = "nccl"
         self.uses_multimem = False
         self.max_fused_tokens = min(max_fused_tokens, max_tokens)
+        self.fused_max_k = 1536      # `auto` mode: longest local K that still takes the fused kernel
         self.n_pad = ((hidden + 255) // 256) * 256
         self.buf_elems = self.max_fused_tokens * self.n_pad
         self._symm = None
@@ -81,7 +82,11 @@ class TPContext:
         """x <- sum_ranks(a @ w.T) + x ; returns the tensor holding the row statistics of the new x."""
         M, K = a.shape
         N = w.shape[0]
-        if self.mode == "fused" and M <= self.max_fused_tokens and N <= self.n_pad:
+        # The fused kernel publishes one partial per tile, so it cannot split K inside the rank: with a long local K
+        # (few ranks) 64 CTAs stream it alone and the unfused split-K GEMM + all-reduce wins. Measured on B200 at
+        # Qwen3-8B shapes: fused ahead at 8 ranks (local K 512 / 1536), behind at 2 ranks (2048 / 6144).
+        k_ok = self.requested_mode != "auto" or K <= self.fused_max_k
+        if self.mode == "fused" and k_ok and M <= self.max_fused_tokens and N <= self.n_pad:
             parts = (N + 255) // 256  # the fused kernel reports statistics per 256-column group
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
