@@ -1366,7 +1366,16 @@ template <int EPI, bool FP8>
 static int dispatch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
                          const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
   // The fused all-reduce never splits K locally, so it keeps 128-row tiles: more tiles in flight.
-  const bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr && p.ar_world == 0;
+  bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr && p.ar_world == 0;
+  if constexpr (EPI == EPI_QKV) {
+    // The QKV epilogue needs one head (128 columns) per tile, so its tiles cannot widen; 256 rows per CTA is what
+    // lets a weight tile serve twice the MMAs at prefill sizes too.
+    static const bool wide = [] {
+      const char* v = getenv("GLLM_QKV_TWO_ROWS");
+      return !(v && v[0] == '0');
+    }();
+    if (wide && p.M > 128) two_rows = true;
+  }
   if constexpr (EPI == EPI_GLU) {
     // 192-wide tiles: 128 tiles for a 24576-row gate/up weight fill one wave of 148 SMs without splitting
     if (bn == 192) {

@@ -101,8 +101,12 @@ def mla_attention(model, w: MlaWeights, h, batch, cache, out):
     q_pe = MLA.rope_half(q[..., nope:].float(), model.cos[pos][:, None, :], model.sin[pos][:, None, :]).to(h.dtype)
     q_abs = torch.bmm(q[..., :nope].transpose(0, 1), w.w_uk).transpose(0, 1)          # [T, nh, d_c]
     q_full = torch.cat([q_abs, q_pe], -1).reshape(T, nh * (d_c + rope_d)).contiguous()
-    lat = MLA.latent_attention(q_full, cache, batch.block_tables, q_start, q_len, batch.ctx_lens, row_seq, n_heads=nh,
-                               d_v=d_c, scale=model.scale, causal=batch.causal and c.causal)
+    if batch.is_decode and h.is_cuda and d_c == 512 and rope_d == 64:
+        lat = MLA.latent_decode(q_full, cache, batch.block_tables, batch.ctx_lens, n_heads=nh, scale=model.scale,
+                                max_ctx=model.max_positions)
+    else:
+        lat = MLA.latent_attention(q_full, cache, batch.block_tables, q_start, q_len, batch.ctx_lens, row_seq, n_heads=nh,
+                                   d_v=d_c, scale=model.scale, causal=batch.causal and c.causal)
     o = torch.bmm(lat.reshape(T, nh, d_c).transpose(0, 1), w.w_uv).transpose(0, 1)     # [T, nh, v]
     out[:, :nh * v].copy_(o.reshape(T, nh * v))
     return out[:, :nh * v]

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 from pathlib import Path
 
 import torch
@@ -119,7 +120,8 @@ def run(op: str, iters: int):
                    tflops=2 * M * N * K / t / 1e12)
     elif op == "mla_attn":
         from . import mla as MLA
-        nh, d_c, d_r, B, ctx = 16, 512, 64, 64, 1024
+        nh, d_c, d_r = 16, 512, 64
+        B, ctx = int(os.environ.get("GLLM_MLA_BATCH", 256)), 1024
         pages = B * ctx // 16
         cache = rnd(pages, 16, d_c + d_r, scale=0.3)
         q = rnd(B, nh * (d_c + d_r), scale=0.3)
@@ -128,7 +130,10 @@ def run(op: str, iters: int):
         one = torch.ones(B, device=dev, dtype=torch.int32)
         cl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
         o = torch.empty(B, nh * d_c, device=dev, dtype=torch.bfloat16)
-        t = _time(lambda: MLA.latent_attention(q, cache, bt, idx, one, cl, idx, n_heads=nh, d_v=d_c, scale=0.04, out=o), iters)
+        if os.environ.get("GLLM_MLA_CUDA_CORES", "0") == "1":
+            t = _time(lambda: MLA.latent_attention(q, cache, bt, idx, one, cl, idx, n_heads=nh, d_v=d_c, scale=0.04, out=o), iters)
+        else:
+            t = _time(lambda: MLA.latent_decode(q, cache, bt, cl, n_heads=nh, scale=0.04, out=o), iters)
         byts = cache.numel() * 2
         fl = 2 * B * nh * ctx * (2 * d_c + d_r)
         out.update(shape=dict(batch=B, heads=nh, ctx=ctx, d_c=d_c, d_rope=d_r), us=t * 1e6, kv_gbs=byts / t / 1e9,

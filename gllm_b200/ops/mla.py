@@ -13,6 +13,8 @@ from ._native import F, I, L, P
 
 nv.register("gllm_mla_latent_write", I, [P, L, I, I, I, P, F, P, P, P, P, I, P, I, P])
 nv.register("gllm_mla_attention", I, [P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P])
+nv.register("gllm_mla_decode_scratch_floats", L, [I, I, I])
+nv.register("gllm_mla_decode", I, [P, P, P, I, P, I, P, I, I, I, F, I, P, L, P])
 
 PAGE = 16
 
@@ -83,4 +85,31 @@ def latent_attention(q, cache, block_tables, q_start, q_len, ctx_lens, row_seq, 
                                      q_start.data_ptr(), q_len.data_ptr(), ctx_lens.data_ptr(), T, n_heads, d_k, d_v,
                                      float(scale), 1 if causal else 0, nv.stream_ptr())
     nv.check(rc, "mla_attention")
+    return out
+
+
+_decode_scratch = {}
+
+
+def latent_decode(q, cache, block_tables, ctx_lens, *, n_heads, scale, max_ctx=4096, splits=0, out=None):
+    """Decode step (one query row per sequence) of the absorbed attention on tensor cores
+    (``csrc/kernels/mla_decode.cu``): q [B, n_heads * 576], cache [pages, 16, 576] -> [B, n_heads * 512].
+    Needs the DeepSeek geometry (d_c 512, rope 64); other shapes take ``latent_attention``."""
+    B = q.shape[0]
+    d_k = cache.shape[-1]
+    if not q.is_cuda or d_k != 576:
+        idx = torch.arange(B, dtype=torch.int32, device=q.device)
+        return latent_attention(q, cache, block_tables, idx, torch.ones_like(idx), ctx_lens, idx, n_heads=n_heads, d_v=d_k - 64,
+                                scale=scale, out=out)
+    if out is None:
+        out = torch.empty((B, n_heads * 512), dtype=q.dtype, device=q.device)
+    need = int(nv.lib().gllm_mla_decode_scratch_floats(B, n_heads, 16))
+    key = (q.device.index, need)
+    sc = _decode_scratch.get(key)
+    if sc is None:
+        sc = _decode_scratch[key] = torch.empty(max(need, 1), dtype=torch.float32, device=q.device)
+    rc = nv.lib().gllm_mla_decode(q.data_ptr(), out.data_ptr(), cache.data_ptr(), cache.shape[0], block_tables.data_ptr(),
+                                  block_tables.shape[1], ctx_lens.data_ptr(), B, n_heads, int(max_ctx), float(scale), int(splits),
+                                  sc.data_ptr(), sc.numel(), nv.stream_ptr())
+    nv.check(rc, "mla_decode")
     return out

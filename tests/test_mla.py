@@ -109,3 +109,22 @@ def test_mla_moe_model_generates_through_the_client():
     r1 = c.generate(prompt).max_tokens(5).temperature(0.0).generate()
     r2 = c.generate(prompt).max_tokens(5).temperature(0.0).generate()
     assert r1.token_ids == r2.token_ids and 1 <= len(r1.token_ids) <= 5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_heads,splits", [(16, 1), (16, 4), (20, 0), (128, 1), (4, 2)])
+def test_mla_tensor_core_decode_matches_reference(n_heads, splits):
+    dev = torch.device("cuda")
+    torch.manual_seed(3)
+    pages = 96
+    ctx = torch.tensor([1, 15, 16, 17, 63, 64, 65, 200, 333, 0], dtype=torch.int32)
+    B = ctx.numel()
+    q = (torch.randn(B, n_heads * 576) * 0.3).to(torch.bfloat16)
+    cache = (torch.randn(pages, 16, 576) * 0.5).to(torch.bfloat16)
+    bt = torch.stack([torch.randperm(pages)[:24] for _ in range(B)]).to(torch.int32)
+    idx = torch.arange(B, dtype=torch.int32)
+    want = MLA.latent_attention_ref(q.float(), cache.float(), bt, idx, torch.ones_like(idx), ctx, n_heads, 512, 0.07)
+    got = MLA.latent_decode(q.to(dev), cache.to(dev), bt.to(dev), ctx.to(dev), n_heads=n_heads, scale=0.07, splits=splits)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=2e-2)
+    from gllm_b200.ops import _native as nv
+    assert nv.device_error() == 0
