@@ -58,8 +58,12 @@ class _ReqState:
 
 
 class LLMEngine:
-    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None):
+    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None, lockstep_group=None):
+        """``lockstep_group``: a process group whose ranks serve DIFFERENT requests but share collective kernels
+        inside the model (data-parallel attention + expert-parallel MoE). Every rank then runs the same sequence of
+        forwards per step (a rank without work runs an empty one), agreed on by one tiny all-reduce per step."""
         self.model, self.cfg, self.tokenizer = model, cfg or EngineConfig(), tokenizer
+        self.lockstep = lockstep_group
         self.mc: ModelConfig = model.cfg
         self.device = model.device
         ec = self.cfg
@@ -192,9 +196,12 @@ class LLMEngine:
         if cuda and self.cfg.use_cuda_graphs:
             key = (B, self._all_greedy)
             g = self.graphs.get(key)
-            if g is None:
+            if g is None and self.lockstep is None:
                 g = self._capture(B)
-            g.replay()
+            if g is not None:
+                g.replay()
+            else:     # lockstep: a capture (with its warm-up run) cannot happen on one rank alone; see precapture()
+                self._decode_body(B)
         else:
             self._decode_body(B)
         self.h_out.copy_(self.d_out, non_blocking=False)
@@ -268,6 +275,8 @@ class LLMEngine:
         """One scheduler iteration: decode replay for the running set, then one prefill chunk batch."""
         plan = self.batcher.schedule()
         self.stats["preemptions"] += len(plan.preempted)
+        if self.lockstep is not None:
+            return self._step_lockstep(plan)
         if plan.idle:
             return self._collect()
         for it in plan.prefill:
@@ -287,6 +296,78 @@ class LLMEngine:
         now = time.perf_counter()
         ids = plan.dec_seq_ids
         # hooks / streaming observe the sampled tokens before they are committed
+        for sl in np.nonzero(ids >= 0)[0]:
+            self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
+        k = 0
+        for it in plan.prefill:
+            if it.last:
+                self._observe(int(it.seq_id), int(pf_tokens[k]), now)
+                k += 1
+        self.batcher.commit(plan, dec_tokens, pf_tokens)
+        return self._collect()
+
+    # ---- lockstep (data-parallel attention + expert parallelism) -----------------------------------
+    def _agree(self, plan):
+        import torch.distributed as dist
+        f = torch.tensor([1 if plan.num_decode > 0 else 0, 1 if plan.num_prefill_seqs > 0 else 0, 1 if self.reqs else 0],
+                         dtype=torch.int32, device=self.device)
+        dist.all_reduce(f, op=dist.ReduceOp.MAX, group=self.lockstep)
+        return [bool(x) for x in f.tolist()]
+
+    def _empty_decode(self):
+        """A decode forward with no live slot: this rank's experts still serve the other ranks' tokens."""
+        ms = self.ms
+        self.h_dec.zero_()
+        self.h_dec[2 * ms:3 * ms] = -1          # no KV write
+        self.d_dec.copy_(self.h_dec, non_blocking=self.device.type == "cuda")
+        B = self._bucket(1)
+        self._all_greedy = True
+        if self.device.type == "cuda" and self.cfg.use_cuda_graphs and (B, True) in self.graphs:
+            self.graphs[(B, True)].replay()
+        else:
+            self._decode_body(B)
+
+    def _empty_prefill(self):
+        dev = self.device
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        batch = ForwardBatch(token_ids=i32([0]), positions=i32([0]), slot_mapping=i32([-1]),
+                             block_tables=torch.zeros((1, self.max_blocks), dtype=torch.int32, device=dev),
+                             ctx_lens=i32([1]), is_decode=False, q_start=i32([0]), q_len=i32([1]), max_q_len=1)
+        self.model.forward(batch, self.kv_caches, return_hidden=True)
+
+    def precapture(self, buckets=None):
+        """Capture the decode graphs up front. In lockstep mode every rank must call this with the same buckets:
+        a capture's warm-up run executes the collective kernels, so it cannot happen on one rank alone later."""
+        if self.device.type != "cuda" or not self.cfg.use_cuda_graphs:
+            return
+        for B in (buckets or [b for b in DECODE_BUCKETS if b <= self.ms]):
+            self._all_greedy = True
+            if (B, True) not in self.graphs:
+                self._capture(B)
+
+    def _step_lockstep(self, plan) -> List[GenerateResult]:
+        any_decode, any_prefill, any_work = self._agree(plan)
+        self.global_has_work = any_work
+        for it in plan.prefill:
+            if it.start == 0 or self.slot_params[it.slot, 3] != float(it.seq_id):
+                sp = self._params_of(it.seq_id)
+                self.slot_params[it.slot] = (sp[0], sp[1], sp[2], float(it.seq_id))
+        dec_tokens = np.zeros(self.ms, np.int32)
+        pf_tokens = np.zeros(0, np.int32)
+        if any_decode:
+            if plan.num_decode > 0:
+                dec_tokens = self._run_decode(plan).copy()
+            else:
+                self._empty_decode()
+        if any_prefill:
+            if plan.num_prefill_seqs > 0:
+                pf_tokens = self._run_prefill(plan)
+            else:
+                self._empty_prefill()
+        if plan.idle:
+            return self._collect()
+        now = time.perf_counter()
+        ids = plan.dec_seq_ids
         for sl in np.nonzero(ids >= 0)[0]:
             self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
         k = 0
@@ -351,7 +432,10 @@ class LLMEngine:
             plan_results = self.step()
             done.extend(plan_results)
             steps += 1
-            if not self.reqs:
+            if self.lockstep is not None:
+                if not self.global_has_work:      # every rank of the group is drained
+                    break
+            elif not self.reqs:
                 break
         return done
 

@@ -57,7 +57,7 @@ class Workspace:
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
-                 quant_group: int = 32):
+                 quant_group: int = 32, ep=None):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
@@ -102,7 +102,7 @@ class DecoderModel:
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
-                                        ep=getattr(tp, "ep", None), fused=self.fused, tp=tp)
+                                        ep=ep if ep is not None else getattr(tp, "ep", None), fused=self.fused, tp=tp)
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
         self.lm_head = None

@@ -43,3 +43,15 @@ def test_tp_attention_plus_expert_sharded_moe_two_gpus():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_MOE_WORKER_OK") == 2
+
+
+@pytest.mark.multigpu
+def test_lockstep_engines_with_fused_expert_parallel_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29841", os.path.join(ROOT, "tests", "ep_engine_worker.py"), "gpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("EP_ENGINE_WORKER_OK") == 2

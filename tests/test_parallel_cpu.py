@@ -305,3 +305,13 @@ def test_tp_attention_with_expert_sharded_moe_matches_unsplit_model():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_MOE_WORKER_OK") == 2
+
+
+def test_lockstep_engines_with_expert_parallel_moe_match_unsplit_engine():
+    """Two serving engines, each with its own requests, share the expert-parallel MoE; outputs equal the plain engine's."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29798", os.path.join(ROOT, "tests", "ep_engine_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("EP_ENGINE_WORKER_OK") == 2
