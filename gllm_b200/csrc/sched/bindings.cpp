@@ -209,6 +209,10 @@ PYBIND11_MODULE(_sched, m) {
            })
       .def("set_system_state", &ContinuousBatcher::set_system_state)
       .def("session_cached_tokens", &ContinuousBatcher::session_cached_tokens)
+      .def("session_ids", &ContinuousBatcher::session_ids)
+      .def("session_tokens", &ContinuousBatcher::session_tokens)
+      .def("lookup_prefix_pages", &ContinuousBatcher::lookup_prefix_pages)
+      .def("import_prefix", &ContinuousBatcher::import_prefix)
       .def_property_readonly("num_waiting", &ContinuousBatcher::num_waiting)
       .def_property_readonly("num_running", &ContinuousBatcher::num_running)
       .def_property_readonly("num_free_pages", &ContinuousBatcher::num_free_pages)

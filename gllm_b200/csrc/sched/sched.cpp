@@ -276,6 +276,46 @@ int ContinuousBatcher::session_cached_tokens(const std::string& session) const {
   return it == sessions_.end() ? 0 : static_cast<int>(it->second.tokens.size());
 }
 
+std::vector<std::string> ContinuousBatcher::session_ids() const {
+  std::vector<std::string> out;
+  for (auto& kv : sessions_) out.push_back(kv.first);
+  return out;
+}
+
+std::vector<int32_t> ContinuousBatcher::session_tokens(const std::string& session) const {
+  auto it = sessions_.find(session);
+  return it == sessions_.end() ? std::vector<int32_t>() : it->second.tokens;
+}
+
+std::vector<int> ContinuousBatcher::lookup_prefix_pages(const std::vector<int32_t>& tokens) {
+  std::vector<int> pages;
+  prefix_.find_longest_prefix(tokens.data(), static_cast<int>(tokens.size()), &pages);
+  return pages;
+}
+
+std::vector<int> ContinuousBatcher::import_prefix(const std::vector<int32_t>& tokens, const std::string& session) {
+  const int n_pages = static_cast<int>(tokens.size()) / page_size_;
+  std::vector<int> have;
+  prefix_.find_longest_prefix(tokens.data(), n_pages * page_size_, &have);
+  std::vector<int> all(have.begin(), have.end()), out(have.size(), -1);
+  for (int i = static_cast<int>(have.size()); i < n_pages; ++i) {
+    const int p = take_page();
+    if (p == kNoPage) break;
+    all.push_back(p);
+    out.push_back(p);
+  }
+  const int got = static_cast<int>(all.size());
+  prefix_.insert(tokens.data(), got * page_size_, all.data(), got);
+  // the index holds its own reference now; drop the allocation reference of the new pages
+  for (size_t i = have.size(); i < all.size(); ++i) alloc_.release(all[i]);
+  if (!session.empty()) {
+    SessionEntry e;
+    e.tokens.assign(tokens.begin(), tokens.begin() + got * page_size_);
+    sessions_[session] = std::move(e);
+  }
+  return out;
+}
+
 bool ContinuousBatcher::abort(int64_t id) {
   auto it = seqs_.find(id);
   if (it == seqs_.end()) return false;

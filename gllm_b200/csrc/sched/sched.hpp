@@ -209,6 +209,14 @@ class ContinuousBatcher {
   void set_system_state(const SystemState& s) { sys_ = s; }
   // sessions: keep the pages of a finished request alive for the next turn of the same session
   int session_cached_tokens(const std::string& session) const;
+  // persistence of the prefix cache / sessions (snapshot to disk and back):
+  std::vector<std::string> session_ids() const;
+  std::vector<int32_t> session_tokens(const std::string& session) const;
+  // pages that currently cache the longest whole-page prefix of `tokens` (empty when nothing is cached)
+  std::vector<int> lookup_prefix_pages(const std::vector<int32_t>& tokens);
+  // allocate pages for the whole-page prefix of `tokens`, register them in the prefix index and return them so
+  // the caller can fill their contents; pages already cached are reused (-1 marks "already there, skip").
+  std::vector<int> import_prefix(const std::vector<int32_t>& tokens, const std::string& session);
 
  private:
   bool ensure_pages(Sequence& s, int upto_tokens);

@@ -5,7 +5,7 @@ also be captured with ``ncu`` in a minute or two. Timing uses CUDA events on the
 warm-up; the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root if
 present) is printed as JSON.
 
-ops: gemm_prefill  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
+ops: gemm_prefill  gemm_prefill_glu  gemm_prefill_residual  gemm_prefill_qkv  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
      mla_attn
 """
 from __future__ import annotations
@@ -53,6 +53,42 @@ def run(op: str, iters: int):
         o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         t = _time(lambda: ops.gemm(a, w, out=o, bn=256), iters)
         out.update(shape=[M, N, K], us=t * 1e6, tflops=2 * M * N * K / t / 1e12, frac_of_bf16_peak=2 * M * N * K / t / 1e12 / tf)
+    elif op in ("gemm_prefill_glu", "gemm_prefill_residual", "gemm_prefill_qkv"):
+        # the epilogue variants at a prefill chunk (M = 8192), Qwen3-8B shapes
+        M, K = 8192, 4096
+        a = rnd(M, K)
+        ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+        if op == "gemm_prefill_glu":
+            I_ = 12288
+            bn = int(os.environ.get("GLLM_GLU_BN", "0")) or __import__("gllm_b200.models.weights", fromlist=["x"]).glu_tile_width(I_)
+            w = ops.interleave_gate_up(rnd(I_, K, scale=0.05), rnd(I_, K, scale=0.05), bn)
+            o = torch.empty(M, I_, device=dev, dtype=torch.bfloat16)
+            t = _time(lambda: ops.gemm_glu(a, w, out=o, row_ss=ss, norm_dim=K, eps=1e-6, bn=bn), iters)
+            fl = 2 * M * 2 * I_ * K
+            out.update(shape=[M, 2 * I_, K], bn=bn)
+        elif op == "gemm_prefill_residual":
+            N, K2 = 4096, 12288
+            a2, w = rnd(M, K2), rnd(N, K2, scale=0.05)
+            r = rnd(M, N)
+            o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            t = _time(lambda: ops.gemm_residual(a2, w, r, out=o, bn=256), iters)
+            fl = 2 * M * N * K2
+            out.update(shape=[M, N, K2])
+        else:
+            nq, nkv = 32, 8
+            w = rnd((nq + 2 * nkv) * 128, K, scale=0.05)
+            kv = torch.zeros(M // 16 + 1, 2, nkv, 16, 128, device=dev, dtype=torch.bfloat16)
+            q = torch.empty(M, nq * 128, device=dev, dtype=torch.bfloat16)
+            pos = torch.arange(M, device=dev, dtype=torch.int32)
+            inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, device=dev).double() / 128))
+            ang = torch.arange(M, device=dev).double()[:, None] * inv[None]
+            cos, sin = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+            qn = torch.ones(128, device=dev)
+            t = _time(lambda: ops.gemm_qkv(a, w, n_q=nq, n_kv=nkv, q_out=q, kv_cache=kv, slot_mapping=pos, positions=pos,
+                                           cos_t=cos, sin_t=sin, q_norm_w=qn, k_norm_w=qn, row_ss=ss, norm_dim=K, eps=1e-6), iters)
+            fl = 2 * M * (nq + 2 * nkv) * 128 * K
+            out.update(shape=[M, (nq + 2 * nkv) * 128, K])
+        out.update(us=t * 1e6, tflops=fl / t / 1e12, frac_of_bf16_peak=fl / t / 1e12 / tf)
     elif op == "gemm_decode":
         M, N, K = 256, 4096, 12288
         ws = [rnd(N, K, scale=0.05) for _ in range(3)]
