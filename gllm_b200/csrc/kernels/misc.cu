@@ -5,6 +5,8 @@
 // Reference semantics: src/compat/scalar_ops.rs:11-63 (rms norm, half-split RoPE),
 // src/compat/sampling.rs:28-135 (greedy if T<=0, else top-k -> 1/T -> softmax -> top-p -> multinomial),
 // src/arch/auto_graph_fragments/build_graph.inc.rs:213 (Gather), :2424 (MeanPool).
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace gllm {
@@ -136,11 +138,16 @@ __global__ void glu_kernel(const __nv_bfloat16* gu, long long ld, int inter, int
 // Standalone per-head norm + RoPE + paged KV write for any even head_dim <= 256.
 // qkv: [M, (Hq + 2 Hkv) * D] (q heads, k heads, v heads). One warp per (token, head).
 // ---------------------------------------------------------------------------------------------
+// KV8: the cache holds fp8 e4m3 (value / kv_scale, saturating) instead of bf16; q stays bf16.
+template <bool KV8>
 __global__ void rope_kv_write_kernel(const __nv_bfloat16* qkv, long long ld, int M, int n_q, int n_kv, int D,
                                      int rot_dim, const int* positions, const int* slot_mapping,
                                      const float* cos_t, const float* sin_t, int max_pos, const float* q_norm_w,
                                      const float* k_norm_w, float qk_eps, __nv_bfloat16* q_out,
-                                     __nv_bfloat16* kv_cache, int num_pages, int* err) {
+                                     void* kv_cache_v, int num_pages, float kv_inv_scale, int* err) {
+  __nv_bfloat16* kv_cache = static_cast<__nv_bfloat16*>(kv_cache_v);
+  uint8_t* kv_cache8 = static_cast<uint8_t*>(kv_cache_v);
+  uint8_t* dst8 = nullptr;
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int heads = n_q + 2 * n_kv;
@@ -176,11 +183,18 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* qkv, long long ld, int
         if (err && lane == 0) atomicCAS(err, 0, ERR_BAD_PAGE);
       } else {
         const int kvh = is_k ? head - n_q : head - n_q - n_kv;
-        dst = kv_cache + (((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * n_kv + kvh) * 16 + off) * D;
+        const long long eoff = (((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * n_kv + kvh) * 16 + off) * D;
+        if (KV8) dst8 = kv_cache8 + eoff; else dst = kv_cache + eoff;
       }
     }
   }
-  if (!dst) return;
+  if (!dst && !dst8) return;
+  auto put = [&](int d, float v) {
+    if (KV8 && dst8)
+      dst8[d] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v * kv_inv_scale, __NV_SATFINITE, __NV_E4M3));
+    else
+      dst[d] = __float2bfloat16_rn(v);
+  };
   if ((is_q || is_k) && rot_dim > 0) {
     int pos = positions[m];
     if (pos < 0 || pos >= max_pos) pos = 0;
@@ -208,12 +222,12 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* qkv, long long ld, int
     }
     for (int i = 0; i < per; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) dst[d] = __float2bfloat16_rn(y[i]);
+      if (d < D) put(d, y[i]);
     }
   } else {
     for (int i = 0; i < per; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) dst[d] = __float2bfloat16_rn(x[i]);
+      if (d < D) put(d, x[i]);
     }
   }
 }
@@ -222,11 +236,21 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* qkv, long long ld, int
 // Generic paged attention (CUDA cores) for head dims other than 128: one warp per (query token, head).
 // Used by small / encoder models; the tensor-core kernels cover head_dim 128.
 // ---------------------------------------------------------------------------------------------
+template <bool KV8>
 __global__ void paged_attention_generic_kernel(const __nv_bfloat16* q, __nv_bfloat16* out,
-                                               const __nv_bfloat16* kv_cache, const int* block_tables,
+                                               const void* kv_cache_v, const int* block_tables,
                                                int max_blocks, const int* q_start, const int* q_len,
                                                const int* ctx_lens, int n_q, int n_kv, int D, float scale,
-                                               int causal, int window, int num_pages) {
+                                               int causal, int window, int num_pages, float kv_scale) {
+  const __nv_bfloat16* kv_cache = static_cast<const __nv_bfloat16*>(kv_cache_v);
+  const uint8_t* kv_cache8 = static_cast<const uint8_t*>(kv_cache_v);
+  auto ld_kv = [&](long long eoff) -> float {
+    if (KV8) {
+      const __half_raw h = __nv_cvt_fp8_to_halfraw(kv_cache8[eoff], __NV_E4M3);
+      return __half2float(*reinterpret_cast<const __half*>(&h)) * kv_scale;
+    }
+    return __bfloat162float(kv_cache[eoff]);
+  };
   const int seq = blockIdx.z, head = blockIdx.y;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -249,12 +273,12 @@ __global__ void paged_attention_generic_kernel(const __nv_bfloat16* q, __nv_bflo
   for (int t = lo; t < hi; ++t) {
     int page = bt[t / 16];
     if (page < 0 || page >= num_pages) page = 0;
-    const __nv_bfloat16* kp = kv_cache + (((static_cast<long long>(page) * 2) * n_kv + kvh) * 16 + (t % 16)) * D;
-    const __nv_bfloat16* vp = kv_cache + (((static_cast<long long>(page) * 2 + 1) * n_kv + kvh) * 16 + (t % 16)) * D;
+    const long long kp = (((static_cast<long long>(page) * 2) * n_kv + kvh) * 16 + (t % 16)) * D;
+    const long long vp = (((static_cast<long long>(page) * 2 + 1) * n_kv + kvh) * 16 + (t % 16)) * D;
     float s = 0.f;
     for (int i = 0; i < per; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) s += qv[i] * __bfloat162float(kp[d]);
+      if (d < D) s += qv[i] * ld_kv(kp + d);
     }
     s = warp_sum(s);
     const float mn = fmaxf(mx, s);
@@ -262,7 +286,7 @@ __global__ void paged_attention_generic_kernel(const __nv_bfloat16* q, __nv_bflo
     l = l * c + pnew;
     for (int i = 0; i < per; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) acc[i] = acc[i] * c + pnew * __bfloat162float(vp[d]);
+      if (d < D) acc[i] = acc[i] * c + pnew * ld_kv(vp + d);
     }
     mx = mn;
   }
@@ -629,11 +653,29 @@ GLLM_API int gllm_rope_kv_write(const void* qkv, long long ld, int M, int n_q, i
   const long long warps = static_cast<long long>(M) * (n_q + 2 * n_kv);
   const int threads = 256;
   const long long blocks = (warps * 32 + threads - 1) / threads;
-  rope_kv_write_kernel<<<static_cast<unsigned>(blocks), threads, 0, (cudaStream_t)stream>>>(
+  rope_kv_write_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, (cudaStream_t)stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), ld, M, n_q, n_kv, D, rot_dim, positions, slot_mapping, cos_t, sin_t,
-      max_pos, q_norm_w, k_norm_w, qk_eps, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(kv_cache),
-      num_pages, gllm_error_word());
+      max_pos, q_norm_w, k_norm_w, qk_eps, static_cast<__nv_bfloat16*>(q_out), kv_cache, num_pages, 1.0f,
+      gllm_error_word());
   CHECK_LAUNCH("rope_kv_write");
+}
+
+// Same with an fp8 e4m3 KV cache: stored value = x / kv_scale.
+GLLM_API int gllm_rope_kv_write_fp8(const void* qkv, long long ld, int M, int n_q, int n_kv, int D, int rot_dim,
+                                    const int* positions, const int* slot_mapping, const float* cos_t,
+                                    const float* sin_t, int max_pos, const float* q_norm_w, const float* k_norm_w,
+                                    float qk_eps, void* q_out, void* kv_cache, int num_pages, float kv_scale,
+                                    void* stream) {
+  if (D > 256 || kv_scale <= 0.f) { set_last_error("rope_kv_write_fp8: head_dim %d > 256 or bad scale", D); return -1; }
+  if (M <= 0) return 0;
+  const long long warps = static_cast<long long>(M) * (n_q + 2 * n_kv);
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  rope_kv_write_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, (cudaStream_t)stream>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld, M, n_q, n_kv, D, rot_dim, positions, slot_mapping, cos_t, sin_t,
+      max_pos, q_norm_w, k_norm_w, qk_eps, static_cast<__nv_bfloat16*>(q_out), kv_cache, num_pages, 1.0f / kv_scale,
+      gllm_error_word());
+  CHECK_LAUNCH("rope_kv_write_fp8");
 }
 
 GLLM_API int gllm_paged_attention_generic(const void* q, void* out, const void* kv_cache, int num_pages,
@@ -643,11 +685,26 @@ GLLM_API int gllm_paged_attention_generic(const void* q, void* out, const void* 
                                           void* stream) {
   if (D > 256) { set_last_error("paged_attention_generic: head_dim %d > 256", D); return -1; }
   dim3 grid((max_q_len + 3) / 4, n_q, num_seqs);
-  paged_attention_generic_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out),
-      static_cast<const __nv_bfloat16*>(kv_cache), block_tables, max_blocks, q_start, q_len, ctx_lens, n_q, n_kv, D,
-      scale, causal, window, num_pages);
+  paged_attention_generic_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), kv_cache, block_tables, max_blocks,
+      q_start, q_len, ctx_lens, n_q, n_kv, D, scale, causal, window, num_pages, 1.0f);
   CHECK_LAUNCH("paged_attention_generic");
+}
+
+// fp8 e4m3 KV cache (value = stored * kv_scale); any head_dim <= 256. Halves the cache footprint and the bytes
+// the attention streams; CUDA-core kernel.
+GLLM_API int gllm_paged_attention_fp8kv(const void* q, void* out, const void* kv_cache, int num_pages,
+                                        const int* block_tables, int max_blocks, const int* q_start,
+                                        const int* q_len, const int* ctx_lens, int num_seqs, int max_q_len,
+                                        int n_q, int n_kv, int D, float scale, int causal, int window,
+                                        float kv_scale, void* stream) {
+  if (D > 256) { set_last_error("paged_attention_fp8kv: head_dim %d > 256", D); return -1; }
+  if (num_seqs <= 0 || max_q_len <= 0) return 0;
+  dim3 grid((max_q_len + 3) / 4, n_q, num_seqs);
+  paged_attention_generic_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), kv_cache, block_tables, max_blocks,
+      q_start, q_len, ctx_lens, n_q, n_kv, D, scale, causal, window, num_pages, kv_scale);
+  CHECK_LAUNCH("paged_attention_fp8kv");
 }
 
 GLLM_API int gllm_pool(const void* h, const int* seq_start, const int* seq_len, int num_seqs, int hidden, int mode,

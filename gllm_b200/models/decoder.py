@@ -57,7 +57,7 @@ class Workspace:
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
-                 quant_group: int = 32, ep=None):
+                 quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
@@ -66,6 +66,10 @@ class DecoderModel:
         self.layer_ids = list(layers) if layers is not None else list(range(cfg.num_layers))
         self.first_stage = 0 in self.layer_ids
         self.last_stage = (cfg.num_layers - 1) in self.layer_ids
+        self.kv_dtype = kv_dtype or dtype      # torch.float8_e4m3fn: half the cache bytes; value = stored * kv_scale
+        self.kv_scale = float(kv_scale)
+        if self.kv_dtype == torch.float8_e4m3fn:
+            fused = False        # the fused QKV epilogue and the tensor-core attention kernels read / write bf16 pages
         self.weight_quant = weight_quant
         if weight_quant is not None:
             fused = False        # quantised linears run through the dequantising GEMM; epilogue fusions need bf16 weights
@@ -146,6 +150,9 @@ class DecoderModel:
         return (num_pages, 2, self.n_kv_local, 16, self.cfg.head_dim)
 
     def alloc_kv_cache(self, num_pages: int) -> List[torch.Tensor]:
+        if self.kv_dtype == torch.float8_e4m3fn:
+            return [torch.zeros(self.kv_cache_shape(num_pages), dtype=torch.uint8, device=self.device).view(torch.float8_e4m3fn)
+                    for _ in self.layer_ids]
         return [torch.zeros(self.kv_cache_shape(num_pages), dtype=self.dtype, device=self.device)
                 for _ in self.layer_ids]
 
@@ -160,10 +167,10 @@ class DecoderModel:
         if batch.is_decode:
             return ops.paged_decode(q, kv, batch.block_tables, batch.ctx_lens, n_q=self.n_q_local, n_kv=self.n_kv_local,
                                     scale=self.scale, out=out, workspace=decode_ws, window=window,
-                                    pages_per_split=getattr(decode_ws, "pages_per_split", 32))
+                                    pages_per_split=getattr(decode_ws, "pages_per_split", 32), kv_scale=self.kv_scale)
         return ops.paged_prefill(q, kv, batch.block_tables, batch.q_start, batch.q_len, batch.ctx_lens,
                                  max_q_len=batch.max_q_len, n_q=self.n_q_local, n_kv=self.n_kv_local, scale=self.scale,
-                                 out=out, causal=batch.causal and self.cfg.causal, window=window)
+                                 out=out, causal=batch.causal and self.cfg.causal, window=window, kv_scale=self.kv_scale)
 
     def _row_parallel(self, a, w, x, ss_out, T):
         """x <- a @ w.T + x, row statistics into ss_out. With TP the partial sums are all-reduced."""
@@ -215,7 +222,7 @@ class DecoderModel:
                     ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
                                       positions=batch.positions, slot_mapping=batch.slot_mapping, cos_t=self.cos,
                                       sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
-                                      k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps)
+                                      k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, kv_scale=self.kv_scale)
                     self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
                     self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
                 ops.rmsnorm(x, lw.post_attn_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)

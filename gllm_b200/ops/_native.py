@@ -40,6 +40,8 @@ _SIGNATURES = {
     "gllm_glu": (I, [P, L, I, I, I, P, P]),
     "gllm_rope_kv_write": (I, [P, L, I, I, I, I, I, P, P, P, P, I, P, P, F, P, P, I, P]),
     "gllm_paged_attention_generic": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, P]),
+    "gllm_paged_attention_fp8kv": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P]),
+    "gllm_rope_kv_write_fp8": (I, [P, L, I, I, I, I, I, P, P, P, P, I, P, P, F, P, P, I, F, P]),
     "gllm_pool": (I, [P, P, P, I, I, I, P, P]),
     "gllm_sample": (I, [P, L, I, I, I, P, U, P, P, P, P]),
     "gllm_argmax": (I, [P, L, I, I, I, P, P, P]),

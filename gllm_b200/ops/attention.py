@@ -25,6 +25,11 @@ def gather_kv_ref(kv_cache, block_table, ctx_len):
     return k[:ctx_len].float(), v[:ctx_len].float()
 
 
+def _dequant_cache(kv_cache, kv_scale):
+    """fp8 cache -> fp32 values (oracle path)."""
+    return kv_cache.float() * kv_scale if kv_cache.dtype == torch.float8_e4m3fn else kv_cache
+
+
 def attention_ref(q, kv_cache, block_tables, q_start, q_len, ctx_lens, n_q, n_kv, scale, causal=True, window=0,
                   sinks=None):
     """q: [T, n_q*D]. Returns [T, n_q*D] in q.dtype. Works on any device (used as the oracle)."""
@@ -71,7 +76,7 @@ class DecodeWorkspace:
 
 
 def paged_decode(q, kv_cache, block_tables, ctx_lens, *, n_q, n_kv, scale=None, out=None, workspace=None,
-                 pages_per_split=32, window=0, sinks=None):
+                 pages_per_split=32, window=0, sinks=None, kv_scale: float = 1.0):
     """One query token per sequence. q: [B, n_q*D]; ctx_lens includes the token just written."""
     B = q.shape[0]
     D = kv_cache.shape[-1]
@@ -81,9 +86,10 @@ def paged_decode(q, kv_cache, block_tables, ctx_lens, *, n_q, n_kv, scale=None, 
     if not q.is_cuda:
         ar = torch.arange(B, dtype=torch.int32)
         ones = (ctx_lens > 0).to(torch.int32)
-        out.copy_(attention_ref(q, kv_cache, block_tables, ar, ones, ctx_lens, n_q, n_kv, scale, True, window, sinks))
+        out.copy_(attention_ref(q, _dequant_cache(kv_cache, kv_scale), block_tables, ar, ones, ctx_lens, n_q, n_kv, scale,
+                                True, window, sinks))
         return out
-    if D == 128:
+    if D == 128 and kv_cache.dtype != torch.float8_e4m3fn:
         max_blocks = block_tables.shape[1]
         if workspace is None:
             max_splits = max(1, (max_blocks + pages_per_split - 1) // pages_per_split)
@@ -97,11 +103,11 @@ def paged_decode(q, kv_cache, block_tables, ctx_lens, *, n_q, n_kv, scale=None, 
     ar = torch.arange(B, dtype=torch.int32, device=q.device)
     ones = (ctx_lens > 0).to(torch.int32)
     return paged_prefill(q, kv_cache, block_tables, ar, ones, ctx_lens, max_q_len=1, n_q=n_q, n_kv=n_kv, scale=scale,
-                         out=out, window=window)
+                         out=out, window=window, kv_scale=kv_scale)
 
 
 def paged_prefill(q, kv_cache, block_tables, q_start, q_len, ctx_lens, *, max_q_len, n_q, n_kv, scale=None,
-                  out=None, causal=True, window=0, sinks=None):
+                  out=None, causal=True, window=0, sinks=None, kv_scale: float = 1.0):
     """Variable-length (chunked) prefill. q: [T, n_q*D] flat tokens; sequence i owns rows
     [q_start[i], q_start[i]+q_len[i]) which are the last q_len[i] of its ctx_lens[i] cached tokens."""
     D = kv_cache.shape[-1]
@@ -109,10 +115,19 @@ def paged_prefill(q, kv_cache, block_tables, q_start, q_len, ctx_lens, *, max_q_
     if out is None:
         out = torch.empty_like(q)
     if not q.is_cuda:
-        out.copy_(attention_ref(q, kv_cache, block_tables, q_start, q_len, ctx_lens, n_q, n_kv, scale, causal, window,
-                                sinks))
+        out.copy_(attention_ref(q, _dequant_cache(kv_cache, kv_scale), block_tables, q_start, q_len, ctx_lens, n_q, n_kv, scale,
+                                causal, window, sinks))
         return out
     S = q_len.shape[0]
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        if sinks is not None:
+            raise NotImplementedError("attention sinks with an fp8 KV cache")
+        rc = nv.lib().gllm_paged_attention_fp8kv(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
+                                                 block_tables.data_ptr(), block_tables.shape[1], q_start.data_ptr(),
+                                                 q_len.data_ptr(), ctx_lens.data_ptr(), S, max_q_len, n_q, n_kv, D, scale,
+                                                 1 if causal else 0, window, float(kv_scale), nv.stream_ptr())
+        nv.check(rc, "paged_attention_fp8kv")
+        return out
     if D == 128:
         rc = nv.lib().gllm_paged_prefill(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
                                          block_tables.data_ptr(), block_tables.shape[1], q_start.data_ptr(),

@@ -98,7 +98,7 @@ def glu(gu, act=0, *, out=None):
 
 
 def rope_kv_write(qkv, *, n_q, n_kv, head_dim, rot_dim, positions, slot_mapping, cos_t, sin_t, q_out, kv_cache,
-                  q_norm_w=None, k_norm_w=None, qk_eps=1e-6):
+                  q_norm_w=None, k_norm_w=None, qk_eps=1e-6, kv_scale: float = 1.0):
     """Unfused counterpart of the QKV epilogue for any head_dim: per-head norm -> RoPE -> q buffer / KV pages."""
     M = qkv.shape[0]
     if not qkv.is_cuda:
@@ -106,7 +106,15 @@ def rope_kv_write(qkv, *, n_q, n_kv, head_dim, rot_dim, positions, slot_mapping,
                                k_norm_w, qk_eps)
         q_out[:M].copy_(q.reshape(M, n_q * head_dim).to(q_out.dtype))
         if slot_mapping is not None:
-            kv_write_ref(kv_cache, k, v, slot_mapping)
+            kv_write_ref(kv_cache, k, v, slot_mapping, kv_scale)
+        return q_out
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        rc = nv.lib().gllm_rope_kv_write_fp8(qkv.data_ptr(), qkv.stride(0), M, n_q, n_kv, head_dim, rot_dim,
+                                             positions.data_ptr(), nv.ptr(slot_mapping), nv.ptr(cos_t), nv.ptr(sin_t),
+                                             cos_t.shape[0] if cos_t is not None else 1, nv.ptr(q_norm_w), nv.ptr(k_norm_w),
+                                             qk_eps, q_out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0], float(kv_scale),
+                                             nv.stream_ptr())
+        nv.check(rc, "rope_kv_write_fp8")
         return q_out
     rc = nv.lib().gllm_rope_kv_write(qkv.data_ptr(), qkv.stride(0), M, n_q, n_kv, head_dim, rot_dim,
                                      positions.data_ptr(), nv.ptr(slot_mapping), nv.ptr(cos_t), nv.ptr(sin_t),

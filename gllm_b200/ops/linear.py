@@ -270,11 +270,17 @@ def qkv_post_ref(qkv, n_q, n_kv, D, positions, cos_t, sin_t, q_norm_w, k_norm_w,
     return q, k, v
 
 
-def kv_write_ref(kv_cache, k, v, slot_mapping):
-    """kv_cache: [pages, 2, n_kv, 16, D]."""
+def kv_write_ref(kv_cache, k, v, slot_mapping, kv_scale: float = 1.0):
+    """kv_cache: [pages, 2, n_kv, 16, D]; an fp8 cache stores value / kv_scale (saturating)."""
     slots = slot_mapping.long()
     ok = slots >= 0
     pages, offs = slots[ok] // PAGE, slots[ok] % PAGE
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        enc = lambda t: (t[ok].float() / kv_scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        raw = kv_cache.view(torch.uint8)
+        raw[pages, 0, :, offs] = enc(k)
+        raw[pages, 1, :, offs] = enc(v)
+        return
     kv_cache[pages, 0, :, offs] = k[ok].to(kv_cache.dtype)
     kv_cache[pages, 1, :, offs] = v[ok].to(kv_cache.dtype)
 
