@@ -291,6 +291,8 @@ class Client:
             raise InvalidModelTypeError("generate() needs a decoder model")
         ids = self._prompt_ids(b._prompt)
         eos = st.tokenizer.eos_ids(st.model.cfg.eos_token_ids) + list(b._stop)
+        if b._images or b._audio:
+            return self._execute_multimodal(b, ids, eos)
         with self._lock:
             try:
                 rid = st.engine.add_request(ids, max_tokens=b._max_tokens, temperature=b._temperature, top_k=b._top_k,
@@ -309,6 +311,31 @@ class Client:
         return GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
                                   prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
                                   ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms)
+
+    def _execute_multimodal(self, b: GenerationBuilder, ids, eos) -> GenerationResponse:
+        """Prompts with image / audio inputs: the encoder's features replace the placeholder tokens' embeddings and
+        the sequence runs on a private KV cache (client_impl.inc.rs generate_with_multimodal)."""
+        from .engine.simple_generate import generate_single
+        st = self._st()
+        enc = self._multimodal_encoder
+        if enc is None:
+            raise InvalidModelTypeError("image / audio inputs need set_multimodal_encoder(...) first")
+        images = torch.stack([torch.as_tensor(i) for i in b._images]) if b._images else None
+        waves = torch.stack([torch.as_tensor(a) for a in b._audio]) if b._audio else None
+        table = st.model.embed
+        if st.model.cfg.embedding_scale not in (None, 0, 1.0):
+            table = table.float() * st.model.cfg.embedding_scale
+        with self._lock:
+            ids2, embeds = enc.prepare(ids, table, images=images, waves=waves)
+            toks = generate_single(st.model, ids2, b._max_tokens, input_embeds=embeds, temperature=b._temperature,
+                                   top_k=b._top_k, top_p=b._top_p, eos_ids=eos)
+        reason = "eos" if toks and toks[-1] in eos else "length"
+        if reason == "eos":
+            toks = toks[:-1]
+        text = st.tokenizer.decode(toks)
+        thinking, answer = split_thinking_content(text) if b._reasoning else ("", text)
+        return GenerationResponse(text=answer, token_ids=toks, finish_reason=reason, thinking=thinking,
+                                  prompt_tokens=len(ids2), cached_prefix_tokens=0, ttft_ms=0.0, tpot_ms=0.0)
 
     def _execute_generation_stream(self, b: GenerationBuilder) -> GenerationStream:
         st = self._st()

@@ -188,9 +188,9 @@ class DecoderModel:
         x = ws.x[:T]
         H = c.hidden_size
         captured = {}
-        if self.first_stage:
+        if self.first_stage and hidden_in is None:
             ops.embed_gather(batch.token_ids, self.embed, scale=c.embedding_scale, out=x, ss_out=ws.ss0[:T])
-        else:
+        else:      # a later pipeline stage, or input embeddings prepared by the caller (multimodal prompts)
             x.copy_(hidden_in)
             if self.fused:
                 ops.rmsnorm(x, None, c.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)

@@ -66,3 +66,31 @@ def test_placeholder_expansion_and_splice():
     table = torch.randn(1000, 8)
     ids2, x = mm.prepare([5, 900, 6], table, images=torch.randn(1, 3, 14, 14))
     assert len(ids2) == 6 and x.shape == (6, 8) and torch.equal(x[0], table[5]) and not torch.equal(x[1], table[900])
+
+
+def test_client_generation_with_image_input():
+    from gllm_b200.client import Client
+    from gllm_b200.engine.simple_generate import generate_single
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-llama")
+    c = Client.from_model(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=3, std=0.05), device="cpu", dtype=torch.float32,
+                          max_num_seqs=2, max_model_len=256, max_batch_tokens=64)
+    # plain generation through generate_single equals the engine's greedy output
+    ids = c.encode("hello world")
+    eng = c.generate("hello world").max_tokens(6).temperature(0.0).generate()
+    assert generate_single(c._st().model, ids, 6)[:len(eng.token_ids)] == eng.token_ids
+    img_tok = 900
+    vcfg = VisionConfig(image_size=14, patch_size=7, hidden=16, layers=1, heads=2, mlp=32, out_hidden=cfg.hidden_size)
+    c.set_multimodal_encoder(MultimodalEncoder(vision=VisionTower(vcfg, VisionWeights(vcfg, seed=1)),
+                                               spec=MultimodalSpec(image_token_id=img_tok)))
+    c._prompt_ids = lambda prompt: [5, img_tok, 6, 7]          # a prompt with one image placeholder
+    img_a, img_b = torch.randn(3, 14, 14), torch.randn(3, 14, 14) * 3
+    ra = c.generate("x").max_tokens(5).temperature(0.0).image(img_a).generate()
+    ra2 = c.generate("x").max_tokens(5).temperature(0.0).image(img_a).generate()
+    rb = c.generate("x").max_tokens(5).temperature(0.0).image(img_b).generate()
+    assert ra.prompt_tokens == 3 + 4 and ra.token_ids == ra2.token_ids and len(ra.token_ids) >= 1
+    assert len(rb.token_ids) >= 1
+    with pytest.raises(Exception):
+        Client.from_model(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=3), device="cpu", dtype=torch.float32,
+                          max_num_seqs=2, max_model_len=64, max_batch_tokens=32).generate("x").image(img_a).max_tokens(2).generate()
