@@ -1,0 +1,108 @@
+"""The engine's responsibilities under the names the reference uses for its six coordinators
+(src/engine/executor.rs:27-35; src/engine/coordinator/*): thin views over ``LLMEngine`` so that code written against
+that vocabulary finds the same seams here.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+from ..parallel.config import KvDistMode, PdRole
+from ..parallel.pd import kv_dist_plan, resolve_pd_role
+from ..scheduler.observer import BasicObserver
+
+
+class DispatchCoordinator:
+    """Scheduler + batcher + requests + policy, and the prefill / decode role of this rank."""
+
+    def __init__(self, engine, pd_role: PdRole = PdRole.COLLOCATED):
+        self.engine, self.pd_role = engine, pd_role
+
+    def enqueue(self, prompt_ids, **kw) -> int:
+        return self.engine.add_request(prompt_ids, **kw)
+
+    def phases(self) -> Dict[str, bool]:
+        b = self.engine.batcher
+        return resolve_pd_role(self.pd_role, b.num_waiting > 0, b.num_running > 0)
+
+    def queue_depths(self):
+        b = self.engine.batcher
+        return {"waiting": b.num_waiting, "running": b.num_running}
+
+
+class KvCoordinator:
+    """The paged pool, its distribution mode and the optional swap tier."""
+
+    def __init__(self, engine, mode: KvDistMode = KvDistMode.LOCAL, swap=None, rank: int = 0, world: int = 1):
+        self.engine, self.mode, self.swap, self.rank, self.world = engine, mode, swap, rank, world
+
+    def plan(self):
+        return kv_dist_plan(self.mode, self.rank, self.world, self.engine.mc.num_kv_heads)
+
+    def occupancy(self) -> float:
+        b = self.engine.batcher
+        return 1.0 - b.num_free_pages / max(b.num_total_pages, 1)
+
+    def reclaim(self, pages: int) -> int:
+        """Ask the swap tier (when there is one) to make room."""
+        if self.swap is None:
+            return 0
+        return len(self.swap.eviction_pass(hbm_used_ratio=1.0)[:pages])
+
+
+class ComputeCoordinator:
+    """Tensor-parallel context of the model and which collective path it takes."""
+
+    def __init__(self, engine):
+        self.engine = engine
+
+    def tp_mode(self) -> str:
+        tp = self.engine.model.tp
+        return "none" if tp is None else (tp.mode + ("+multimem" if getattr(tp, "uses_multimem", False) else ""))
+
+
+class InferenceCoordinator:
+    def __init__(self, engine):
+        self.engine = engine
+
+    def step(self):
+        return self.engine.step()
+
+    def drain(self):
+        return self.engine.run_until_done()
+
+
+class ModelContextHolder:
+    def __init__(self, engine):
+        self.model, self.config, self.tokenizer = engine.model, engine.mc, engine.tokenizer
+
+
+class ObservabilityCoordinator:
+    """Captures a ``SystemState`` every step and feeds it back to the scheduler policy."""
+
+    def __init__(self, engine):
+        self.engine, self.observer = engine, BasicObserver()
+
+    def capture(self):
+        b = self.engine.batcher
+        st = self.observer.system_state(free_pages=b.num_free_pages, total_pages=b.num_total_pages,
+                                        fragmentation=b.fragmentation, running=b.num_running, waiting=b.num_waiting)
+        b.set_system_state(st)
+        return st
+
+
+@dataclass
+class Coordinators:
+    dispatch: DispatchCoordinator
+    kv: KvCoordinator
+    compute: ComputeCoordinator
+    inference: InferenceCoordinator
+    model_ctx: ModelContextHolder
+    observability: ObservabilityCoordinator
+
+    @staticmethod
+    def of(engine, **kw) -> "Coordinators":
+        return Coordinators(DispatchCoordinator(engine, kw.get("pd_role", PdRole.COLLOCATED)),
+                            KvCoordinator(engine, kw.get("kv_mode", KvDistMode.LOCAL), kw.get("swap")),
+                            ComputeCoordinator(engine), InferenceCoordinator(engine), ModelContextHolder(engine),
+                            ObservabilityCoordinator(engine))

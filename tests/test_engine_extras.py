@@ -98,3 +98,25 @@ def test_guards_nan_trap_and_blob(tmp_path):
         assert torch.equal(blob.view(n), t0) and blob.entries[n].offset % 256 == 0
     assert blob.layer_stride("L0.", "L1.") == 512 and blob.layer_stride("L0.", "lm") is None
     assert blob.offset_table()[0][0] == "L0.w" and blob.total_bytes() % 256 == 0
+
+
+def test_coordinators_and_backend_context():
+    from gllm_b200.backend import BackendContext
+    from gllm_b200.engine.coordinators import Coordinators
+    from gllm_b200.engine.executor import EngineConfig
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.parallel.config import PdRole
+    cfg = preset("tiny-llama")
+    model = DecoderModel(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=1), device="cpu", dtype=torch.float32, max_positions=128)
+    ctx = BackendContext("cpu")
+    assert ctx.backend.info.name == "cpu" and 0.0 <= ctx.backend.get_memory_pressure() <= 1.0
+    eng = ctx.build_executor(model, EngineConfig(max_num_seqs=2, max_model_len=128, max_batch_tokens=64, num_pages=32))
+    co = Coordinators.of(eng, pd_role=PdRole.COLLOCATED)
+    rid = co.dispatch.enqueue([1, 2, 3, 4], max_tokens=3, temperature=0.0, eos_ids=[])
+    assert co.dispatch.queue_depths() == {"waiting": 1, "running": 0} and co.dispatch.phases()["prefill"]
+    st = co.observability.capture()
+    assert st.waiting == 1 and co.kv.occupancy() == 0.0 and co.compute.tp_mode() == "none"
+    co.inference.drain()
+    assert len(eng.results[rid].token_ids) == 3 and co.model_ctx.config is cfg
+    assert co.kv.plan()["store_heads"] == list(range(cfg.num_kv_heads))
