@@ -2,11 +2,12 @@
 //
 // One CTA (4 warps) serves one (sequence, tile of 16 query heads, KV split). Every head attends over the SAME
 // latent rows [c_kv (d_c = 512) | k_pe (d_r = 64)], so the 16 heads are the 16 rows of the MMA tile and each
-// latent byte is read from HBM once per head tile. Per 64-token tile:
-//   phase 1  warp w: S_w[16 heads x 16 tokens] = Q[16 x 576] . K_w^T   (36 k-steps, A and B through ldmatrix)
+// latent byte is read from HBM once per head tile. Per 32-token tile:
+//   phase 1  warp w: S_w[16 heads x 8 tokens] = Q[16 x 576] . K_w^T   (36 k-steps, A and B through ldmatrix)
 //            block-wide online softmax (row maxima / sums exchanged through shared memory), P written as bf16
-//   phase 2  warp w: O_w[16 x 128 columns] += P[16 x 64] . V[64 x (its 128 of the 512 latent columns)]
-// The latent tile is fetched by TMA (boxes of 16 tokens x 64 columns, 128-byte swizzle) into a two-stage ring.
+//   phase 2  warp w: O_w[16 x 128 columns] += P[16 x 32] . V[32 x (its 128 of the 512 latent columns)]
+// The latent tile is fetched by TMA (boxes of 16 tokens x 64 columns, 128-byte swizzle) into a two-stage ring;
+// two CTAs share an SM so that one computes while the other waits for its tile.
 // With more than one KV split the unnormalised partial outputs and their (max, sum) go to scratch and a second
 // small kernel merges them.
 //
@@ -18,9 +19,10 @@ namespace gllm {
 
 constexpr int kMdDc = 512, kMdDr = 64, kMdDk = kMdDc + kMdDr;   // 576
 constexpr int kMdPage = 16;
-constexpr int kMdTile = 64;                 // tokens per stage
+constexpr int kMdTile = 32;                 // tokens per stage (two CTAs per SM hide each other's load latency)
 constexpr int kMdChunks = kMdDk / 64;       // 9 column chunks of 64 bf16 (128 bytes)
-constexpr int kMdStageBytes = kMdChunks * kMdTile * 128;   // 73728
+constexpr int kMdStageBytes = kMdChunks * kMdTile * 128;   // 36864
+constexpr int kMdPStride = kMdTile + 8;     // bf16 elements per row of the probability tile (16-byte rows, odd multiple)
 constexpr int kMdQBytes = kMdChunks * 16 * 128;            // 18432
 constexpr int kMdThreads = 128;
 
@@ -59,14 +61,14 @@ __device__ __forceinline__ uint32_t md_addr(uint32_t base, int rows, int row, in
   return base + c * rows * 128 + row * 128 + ((j ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kMdThreads, 1)
+__global__ void __launch_bounds__(kMdThreads, 2)
 mla_decode_kernel(const __grid_constant__ CUtensorMap tmap, const MlaDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* s_kv = smem;                                   // 2 stages
   uint8_t* s_q = smem + 2 * kMdStageBytes;                // Q tile, same swizzled layout with 16 rows
-  __nv_bfloat16* s_p = reinterpret_cast<__nv_bfloat16*>(s_q + kMdQBytes);        // P [16][64 + 8] bf16
-  float* s_red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_p) + 16 * 72 * 2);   // [4 warps][16 rows][2]
+  __nv_bfloat16* s_p = reinterpret_cast<__nv_bfloat16*>(s_q + kMdQBytes);        // P [16][kMdPStride] bf16
+  float* s_red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s_p) + 16 * kMdPStride * 2);   // [4 warps][16 rows][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + 4 * 16 * 2);              // full[2]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2);
 
@@ -96,7 +98,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap, const MlaDecodeParam
   }
   __syncthreads();
 
-  auto issue_tile = [&](int t, int stage) {   // one thread: 4 pages x 9 boxes
+  auto issue_tile = [&](int t, int stage) {   // one thread: 2 pages x 9 boxes
     uint8_t* dst = s_kv + stage * kMdStageBytes;
     const int tok0 = t * kMdTile;
     int n_pages = (min(ctx, tok0 + kMdTile) - tok0 + kMdPage - 1) / kMdPage;
@@ -138,35 +140,34 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap, const MlaDecodeParam
         }
       }
     }
-    // ---------------- phase 1: S_w = Q . K_w^T for tokens [16w, 16w+16) of the tile ----------------
-    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ---------------- phase 1: S_w = Q . K_w^T for tokens [8w, 8w+8) of the tile ----------------
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
     {
-      const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3);      // A: rows 0-15, k halves
+      const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3);      // A: rows 0-15, two k halves per k-step
       const int a_csel = lane >> 4;
-      const int b_tok = warp * 16 + (lane & 7) + ((lane >> 4) << 3);  // B: token rows, k halves
-      const int b_csel = (lane >> 3) & 1;
-#pragma unroll 4
-      for (int ks = 0; ks < kMdDk / 16; ++ks) {
-        uint32_t a[4], b0, b1, b2, b3;
-        md_ldsm_x4(md_addr(q_base, 16, a_row, ks * 2 + a_csel), a[0], a[1], a[2], a[3]);
-        md_ldsm_x4(md_addr(kv_base, kMdTile, b_tok, ks * 2 + b_csel), b0, b1, b2, b3);
-        md_mma(s[0], a, b0, b1);
-        md_mma(s[1], a, b2, b3);
+      const int b_tok = warp * 8 + (lane & 7);                      // B: 8 token rows, four k chunks = two k-steps
+      const int b_csel = lane >> 3;
+#pragma unroll 3
+      for (int ks2 = 0; ks2 < kMdDk / 32; ++ks2) {
+        uint32_t a0[4], a1[4], b0, b1, b2, b3;
+        md_ldsm_x4(md_addr(q_base, 16, a_row, ks2 * 4 + a_csel), a0[0], a0[1], a0[2], a0[3]);
+        md_ldsm_x4(md_addr(q_base, 16, a_row, ks2 * 4 + 2 + a_csel), a1[0], a1[1], a1[2], a1[3]);
+        md_ldsm_x4(md_addr(kv_base, kMdTile, b_tok, ks2 * 4 + b_csel), b0, b1, b2, b3);
+        md_mma(s, a0, b0, b1);
+        md_mma(s, a1, b2, b3);
       }
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int tok = tok0 + warp * 16 + nt * 8 + (lane & 3) * 2 + e;
-        float v0 = s[nt][e] * p.scale_log2, v1 = s[nt][2 + e] * p.scale_log2;
-        if (tok >= ctx) v0 = v1 = -INFINITY;
-        s[nt][e] = v0;
-        s[nt][2 + e] = v1;
-        mx0 = fmaxf(mx0, v0);
-        mx1 = fmaxf(mx1, v1);
-      }
+    for (int e = 0; e < 2; ++e) {
+      const int tok = tok0 + warp * 8 + (lane & 3) * 2 + e;
+      float v0 = s[e] * p.scale_log2, v1 = s[2 + e] * p.scale_log2;
+      if (tok >= ctx) v0 = v1 = -INFINITY;
+      s[e] = v0;
+      s[2 + e] = v1;
+      mx0 = fmaxf(mx0, v0);
+      mx1 = fmaxf(mx1, v1);
+    }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -189,15 +190,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap, const MlaDecodeParam
     m0 = mn0;
     m1 = mn1;
     float rs0 = 0.f, rs1 = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const float p00 = exp2f(s[nt][0] - ms0), p01 = exp2f(s[nt][1] - ms0);
-      const float p10 = exp2f(s[nt][2] - ms1), p11 = exp2f(s[nt][3] - ms1);
-      rs0 += p00 + p01;
-      rs1 += p10 + p11;
-      const int col = warp * 16 + nt * 8 + (lane & 3) * 2;
-      *reinterpret_cast<uint32_t*>(s_p + r0 * 72 + col) = md_pack(p00, p01);
-      *reinterpret_cast<uint32_t*>(s_p + r1 * 72 + col) = md_pack(p10, p11);
+    {
+      const float p00 = exp2f(s[0] - ms0), p01 = exp2f(s[1] - ms0);
+      const float p10 = exp2f(s[2] - ms1), p11 = exp2f(s[3] - ms1);
+      rs0 = p00 + p01;
+      rs1 = p10 + p11;
+      const int col = warp * 8 + (lane & 3) * 2;
+      *reinterpret_cast<uint32_t*>(s_p + r0 * kMdPStride + col) = md_pack(p00, p01);
+      *reinterpret_cast<uint32_t*>(s_p + r1 * kMdPStride + col) = md_pack(p10, p11);
     }
     rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
     rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
@@ -233,7 +233,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap tmap, const MlaDecodeParam
 #pragma unroll
       for (int kt = 0; kt < kMdTile / 16; ++kt) {
         uint32_t a[4];
-        md_ldsm_x4(p_base + (a_row * 72 + kt * 16 + a_csel * 8) * 2, a[0], a[1], a[2], a[3]);
+        md_ldsm_x4(p_base + (a_row * kMdPStride + kt * 16 + a_csel * 8) * 2, a[0], a[1], a[2], a[3]);
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {     // 16 output columns per ldmatrix.x4.trans
           uint32_t b0, b1, b2, b3;
@@ -328,7 +328,7 @@ GLLM_API int gllm_mla_decode(const void* q, void* out, const void* cache, int nu
     const int tiles = (max_ctx + kMdTile - 1) / kMdTile;
     splits = 1;
     const int sms = gllm_sm_count();
-    while (ctas * splits < sms && splits * 2 <= tiles && splits < 16) splits *= 2;
+    while (ctas * splits < 2 * sms && splits * 2 <= tiles && splits < 16) splits *= 2;   // two CTAs fit on an SM
   }
   if (splits > 1 && (!scratch || gllm_mla_decode_scratch_floats(batch, n_heads, splits) > scratch_floats)) splits = 1;
   CUtensorMap tmap;
@@ -345,7 +345,7 @@ GLLM_API int gllm_mla_decode(const void* q, void* out, const void* cache, int nu
   p.part_o = scratch;
   p.part_ml = scratch ? scratch + static_cast<long long>(batch) * head_tiles * splits * 16 * kMdDc : nullptr;
   p.err = gllm_error_word();
-  const int smem = 2 * kMdStageBytes + kMdQBytes + 16 * 72 * 2 + 4 * 16 * 2 * 4 + 64 + 1024;
+  const int smem = 2 * kMdStageBytes + kMdQBytes + 16 * kMdPStride * 2 + 4 * 16 * 2 * 4 + 64 + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

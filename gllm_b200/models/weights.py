@@ -235,7 +235,11 @@ def glu_tile_width(inter: int, sms: int = 148) -> int:
     (e.g. 128 tiles for intermediate 12288), else the widest power-of-two tile that divides."""
     if inter % 96 == 0 and 0.8 * sms <= (2 * inter) // 192 <= sms:
         return 192
-    return 256 if inter % 128 == 0 else 128
+    if inter % 128 == 0 and (2 * inter) // 256 >= 32:
+        return 256
+    # a narrow gate/up weight (a tensor-parallel shard): 128-wide tiles give twice the tiles, and the decode-shaped
+    # split-K paths (cluster reduce, parked partial tiles) exist for 128-wide tiles only
+    return 128
 
 
 def pack_mlp(cfg: ModelConfig, src, prefix: str, rank: int, world: int, fused: bool, norm_w=None, bn=None):

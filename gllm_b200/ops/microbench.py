@@ -103,9 +103,9 @@ def run(op: str, iters: int):
         byts = N * K * 2
         out.update(shape=[M, N, K], us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
     elif op == "gemm_glu":
-        M, I, K = 256, 12288, 4096
+        M, I, K = 256, int(os.environ.get("GLLM_GLU_I", 12288)), 4096    # GLLM_GLU_I=1536: one rank's share at TP8
         from ..models.weights import glu_tile_width
-        bn = glu_tile_width(I)
+        bn = int(os.environ.get("GLLM_GLU_BN", "0")) or glu_tile_width(I)
         ws = [ops.interleave_gate_up(rnd(I, K, scale=0.05), rnd(I, K, scale=0.05), bn) for _ in range(2)]
         a = rnd(M, K)
         ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
@@ -177,18 +177,27 @@ def run(op: str, iters: int):
     elif op in ("decode_attn", "prefill_attn"):
         nq, nkv, D = 32, 8, 128
         if op == "decode_attn":
-            B, ctx = 64, 2048
+            # defaults: the committed case. GLLM_ATTN_* reshape it, e.g. one rank's share under 8-way tensor
+            # parallelism: GLLM_ATTN_NQ=4 GLLM_ATTN_NKV=1 GLLM_ATTN_BATCH=256 GLLM_ATTN_RAGGED=1 GLLM_ATTN_PPS=16
+            nq, nkv = int(os.environ.get("GLLM_ATTN_NQ", nq)), int(os.environ.get("GLLM_ATTN_NKV", nkv))
+            B, ctx = int(os.environ.get("GLLM_ATTN_BATCH", 64)), 2048
+            pps = int(os.environ.get("GLLM_ATTN_PPS", 1 << 20))
             pages = B * ctx // 16
             kv = torch.randn(pages, 2, nkv, 16, D, device=dev).to(torch.bfloat16)
             bt = torch.randperm(pages, device=dev).to(torch.int32).reshape(B, ctx // 16).contiguous()
-            cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+            if os.environ.get("GLLM_ATTN_RAGGED", "0") == "1":
+                cl = torch.randint(128, ctx + 1, (B,), device=dev).to(torch.int32)
+            else:
+                cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
             q = rnd(B, nq * D)
             o = torch.empty_like(q)
-            wsp = ops.DecodeWorkspace(B, nq, nkv, 1, dev)
+            max_splits = max(1, -(-(ctx // 16) // pps))
+            wsp = ops.DecodeWorkspace(B, nq, nkv, max_splits, dev)
             t = _time(lambda: ops.paged_decode(q, kv, bt, cl, n_q=nq, n_kv=nkv, out=o, workspace=wsp,
-                                               pages_per_split=1 << 20), iters)
-            byts = kv.numel() * 2
-            out.update(batch=B, ctx=ctx, us=t * 1e6, kv_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
+                                               pages_per_split=pps), iters)
+            byts = int(cl.sum().item()) * 2 * nkv * D * 2
+            out.update(batch=B, ctx=ctx, n_q=nq, n_kv=nkv, pages_per_split=pps, us=t * 1e6, kv_gbs=byts / t / 1e9,
+                       frac_of_hbm_peak=byts / t / 1e9 / hbm)
         else:
             S, L = 8, 2048
             pages = S * L // 16
