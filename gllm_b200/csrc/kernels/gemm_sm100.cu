@@ -286,9 +286,11 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
 #pragma unroll
           for (int j = 0; j < SEGW; ++j) {
             float gv = v[j] * rs, uv = v[SEGW + j] * rs;
-            if (p.b_scale) {
-              gv *= p.b_scale[n_blk * BN + lane * SEGW + j];
-              uv *= p.b_scale[n_blk * BN + kHalf + lane * SEGW + j];
+            if (p.b_scale) {   // gate column of output o sits at 64 * (o / 32) + o % 32 of the tile, its up column 32 further
+              const int o_in = lane * SEGW + j;
+              const int gcol = n_blk * BN + (o_in >> 5) * 64 + (o_in & 31);
+              gv *= p.b_scale[gcol];
+              uv *= p.b_scale[gcol + 32];
             }
             o4[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
           }
@@ -379,7 +381,13 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
   const long long split_stride = static_cast<long long>(p.M) * n_pad;
   const int units = p.M * p.num_n;
   int seg_off[NSEG];
-  if constexpr (kGlu || kQkv) {
+  if constexpr (kGlu) {
+    // gate / up are interleaved in 64-column groups (32 gate, 32 up): output o of the tile pairs columns
+    // 64 * (o / 32) + o % 32 and that + 32, whatever the tile width
+    const int o_in = lane * SEGW;
+    seg_off[0] = (o_in >> 5) * 64 + (o_in & 31);
+    seg_off[1] = seg_off[0] + 32;
+  } else if constexpr (kQkv) {
     seg_off[0] = lane * SEGW;
     seg_off[1] = BN / 2 + lane * SEGW;
   } else {
@@ -621,7 +629,11 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
   int r_begin, r_end;
   cluster_row_range(rows, S, ks, r_begin, r_end);
   int seg_off[NSEG];
-  if constexpr (kGlu || kQkv) {
+  if constexpr (kGlu) {
+    const int o_in = lane * SEGW;
+    seg_off[0] = (o_in >> 5) * 64 + (o_in & 31);
+    seg_off[1] = seg_off[0] + 32;
+  } else if constexpr (kQkv) {
     seg_off[0] = lane * SEGW;
     seg_off[1] = BN / 2 + lane * SEGW;
   } else {
@@ -1014,13 +1026,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (p.row_ss_out && row_ok) p.row_ss_out[static_cast<long long>(m) * p.num_n + n_blk] = ss;
             }
           } else if constexpr (EPI == EPI_GLU) {
-            // tile columns [0, BN/2) hold gate rows, [BN/2, BN) the matching up rows
+            // every 64 tile columns hold 32 gate rows followed by the matching 32 up rows (independent of BN)
             constexpr int kHalf = BN / 2;
 #pragma unroll 1
             for (int c = 0; c < kHalf / 32; ++c) {
               float g[32], u[32];
-              rd.load(c * 32, g);
-              rd.load(kHalf + c * 32, u);
+              rd.load(c * 64, g);
+              rd.load(c * 64 + 32, u);
               const int n0 = n_blk * kHalf + c * 32;  // output column
               if (n0 >= p.N / 2) continue;
               float v[32];
@@ -1029,8 +1041,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 float gv = g[j] * rs;
                 float uv = u[j] * rs;
                 if (p.b_scale) {
-                  gv *= p.b_scale[n_blk * BN + c * 32 + j];
-                  uv *= p.b_scale[n_blk * BN + kHalf + c * 32 + j];
+                  gv *= p.b_scale[n_blk * BN + c * 64 + j];
+                  uv *= p.b_scale[n_blk * BN + c * 64 + 32 + j];
                 }
                 v[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
               }

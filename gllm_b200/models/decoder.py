@@ -207,8 +207,11 @@ class DecoderModel:
                 if lw.moe is not None:
                     ss_in = lw.moe.forward(self, x, ss_mid, ws.ss_a[:T], T)
                 else:
+                    # the packing is tile-width independent: the width recorded with the weight fills one wave of SMs
+                    # at decode sizes, prefill chunks take the widest tile (best tensor-core rate)
+                    glu_bn = 256 if (T > 1024 and lw.w_gate_up.shape[0] % 256 == 0) else lw.glu_bn
                     ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
-                                 row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=lw.glu_bn)
+                                 row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=glu_bn)
                     ss_in = self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
             else:
                 h = ws.h[:T]

@@ -32,14 +32,19 @@ def pad_rows(w: torch.Tensor, multiple: int = 128) -> torch.Tensor:
     return torch.cat([w, w.new_zeros((pad,) + tuple(w.shape[1:]))], 0).contiguous()
 
 
-def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int = 256) -> torch.Tensor:
-    """Pack gate/up weights so each bn-row tile holds bn/2 gate rows followed by the matching up rows.
+GLU_GROUP = 64   # packed gate/up rows come in groups of 64: 32 gate rows, then the matching 32 up rows
 
-    The GLU epilogue then finds both halves of every output feature inside one accumulator tile.
-    Requires intermediate size to be a multiple of bn/2.
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int = 256) -> torch.Tensor:
+    """Pack gate/up weights so that every 64 rows hold 32 gate rows followed by the matching 32 up rows.
+
+    The GLU epilogue then finds both halves of an output feature inside one accumulator tile whatever the tile
+    width (128, 192 or 256 columns are all multiples of 64), so the width can be chosen per call: wide tiles for
+    prefill, a width that fills one wave of SMs for decode. ``bn`` is accepted for callers that record the decode
+    tile width next to the weight; the packing does not depend on it. Requires intermediate size % 32 == 0.
     """
     inter, k = gate.shape
-    half = bn // 2
+    half = GLU_GROUP // 2
     if inter % half != 0:
         raise ValueError(f"intermediate size {inter} must be a multiple of {half}")
     g = gate.reshape(inter // half, half, k)
@@ -48,9 +53,9 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int = 256) -> t
 
 
 def deinterleave_gate_up(w: torch.Tensor, bn: int = 256):
-    half = bn // 2
+    half = GLU_GROUP // 2
     n, k = w.shape
-    t = w.reshape(n // bn, 2, half, k)
+    t = w.reshape(n // GLU_GROUP, 2, half, k)
     return t[:, 0].reshape(n // 2, k), t[:, 1].reshape(n // 2, k)
 
 

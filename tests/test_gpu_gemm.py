@@ -76,7 +76,7 @@ def test_gemm_residual(M, N, K, bn):
 @pytest.mark.parametrize("splits", [0, 1, 3])
 @pytest.mark.parametrize("M,I,K,bn,act", [(256, 1024, 512, 256, 0), (100, 768, 2048, 128, 0), (64, 512, 256, 256, 1),
                                           (256, 12288, 4096, 256, 0), (256, 1536, 1024, 192, 0),
-                                          (100, 960, 512, 192, 1)])
+                                          (100, 960, 512, 192, 1), (2048, 1024, 512, 256, 0), (300, 1536, 1024, 128, 0)])
 def test_gemm_glu(M, I, K, bn, act, splits):
     torch.manual_seed(3)
     a, g, u = _rand(M, K), _rand(I, K, scale=0.05), _rand(I, K, scale=0.05)
