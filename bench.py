@@ -257,6 +257,10 @@ def main():
             "p50_ttft_ms": round(med(ttft) * 1e3, 2) if ttft else None,
             "p50_tpot_ms": round(med(step_times) * 1e3, 4),
             "prefill_tokens_per_s": round(engine.stats["prefill_tokens"] / prefill_s, 1),
+            "prefill_breakdown_ms": {"phase_wall": round(prefill_s * 1e3, 1),
+                                     "prefill_calls_wall": round(engine.stats.get("prefill_wall_ms", 0.0), 1),
+                                     "prefill_calls_device": round(engine.stats.get("prefill_device_ms", 0.0), 1),
+                                     "prefill_steps": engine.stats["prefill_steps"]},
             "prefix_cache_hits": int(engine.batcher.prefix_hits),
             "kv_pages": engine.num_pages,
         }

@@ -229,6 +229,21 @@ class LLMEngine:
         return g
 
     def _run_prefill(self, plan) -> np.ndarray:
+        t_host0 = time.perf_counter()
+        ev = None
+        if self.device.type == "cuda":
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        try:
+            return self._run_prefill_inner(plan)
+        finally:
+            if ev is not None:
+                ev[1].record()
+                ev[1].synchronize()
+                self.stats["prefill_device_ms"] = self.stats.get("prefill_device_ms", 0.0) + ev[0].elapsed_time(ev[1])
+            self.stats["prefill_wall_ms"] = self.stats.get("prefill_wall_ms", 0.0) + (time.perf_counter() - t_host0) * 1e3
+
+    def _run_prefill_inner(self, plan) -> np.ndarray:
         dev = self.device
         T = plan.num_prefill_tokens
         S_ = plan.num_prefill_seqs
