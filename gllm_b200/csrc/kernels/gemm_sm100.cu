@@ -105,9 +105,10 @@ struct GemmParams {
   int* err;
 };
 
-template <int BN, int MT>
+template <int BN, int MT, bool PAIR = false>
 struct GemmCfg {
-  static constexpr int kStageBytes = MT * kBM * kTileKBytes + BN * kTileKBytes;
+  // PAIR: each CTA of a pair stages its own 128 rows of A and half of the B tile's rows
+  static constexpr int kStageBytes = MT * kBM * kTileKBytes + (PAIR ? BN / 2 : BN) * kTileKBytes;
   static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   static constexpr int kAccStages = (2 * MT * BN <= 512) ? 2 : 1;
   static constexpr int kCols = kAccStages * MT * BN;
@@ -714,11 +715,19 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
   }
 }
 
-template <int BN, int MT, int EPI, bool FP8>
+template <int BN, int MT, int EPI, bool FP8, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
-  using Cfg = GemmCfg<BN, MT>;
+  static_assert(!PAIR || (MT == 1 && !FP8), "CTA pairs: one 128-row block per CTA, bf16");
+  using Cfg = GemmCfg<BN, MT, PAIR>;
+  // CTA pair (launched as clusters of two): one work item is a 256-row x BN tile; the even CTA issues the MMAs for
+  // both, each CTA loads its own operand halves and finishes its own 128 accumulator rows.
+  constexpr int MTE = PAIR ? 2 : MT;          // 128-row blocks per work item
+  const uint32_t crank = PAIR ? cluster_cta_rank() : 0u;
+  const bool leader = crank == 0;
+  const int work_id = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int work_stride = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   constexpr int kStages = Cfg::kStages;
   constexpr int kABytes = kBM * kTileKBytes;
   constexpr int kStageBytes = Cfg::kStageBytes;
@@ -757,7 +766,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], PAIR ? 8 : 4);   // the epilogue warps of both CTAs of a pair
     }
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -767,11 +776,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_base_ptr, Cfg::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_base_ptr, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_ptr, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_barrier();   // the partner's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_ptr;
   if (tracing && threadIdx.x == 0) p.trace[1] = clock64();
@@ -793,12 +808,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
+      for (int t = work_id; t < num_items && ok; t += work_stride) {
         int ks, m_sup, n_blk, kb0, kb1;
         decode_item(t, ks, m_sup, n_blk, kb0, kb1);
         int b_row = n_blk * BN;
         if (p.mblk_group) {
-          const int grp = p.mblk_group[m_sup * MT];
+          const int grp = p.mblk_group[m_sup * MTE];
           if (grp < 0) continue;  // inactive row block of a grouped GEMM (fewer routed rows than the launch was sized for)
           b_row += grp * p.group_rows;
         }
@@ -809,11 +824,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
           uint8_t* sa = tiles + stage * kStageBytes;
           uint8_t* sb = sa + MT * kABytes;
-          mbar_expect_tx(&full_bar[stage], kStageBytes);
+          if constexpr (PAIR) {
+            // both CTAs' bytes are credited to the even CTA's barrier, which expects the sum
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * kStageBytes);
+            const uint32_t bar0 = cluster_map_addr(smem_u32(&full_bar[stage]), 0);
+            tma_load_2d_pair(sa, &tmap_a, bar0, kb * kElemsPerKB, (m_sup * 2 + static_cast<int>(crank)) * kBM);
+            tma_load_2d_pair(sb, &tmap_b, bar0, kb * kElemsPerKB, b_row + static_cast<int>(crank) * (BN / 2));
+          } else {
+            mbar_expect_tx(&full_bar[stage], kStageBytes);
 #pragma unroll
-          for (int i = 0; i < MT; ++i)
-            tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
-          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
+            for (int i = 0; i < MT; ++i)
+              tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -824,16 +847,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(kBM, BN, FP8 ? 0 : 1, FP8 ? 0 : 1);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc(PAIR ? 2 * kBM : kBM, BN, FP8 ? 0 : 1, FP8 ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
+      for (int t = work_id; t < num_items && ok; t += work_stride) {
         int ks, m_sup, n_blk, kb0, kb1;
         decode_item(t, ks, m_sup, n_blk, kb0, kb1);
-        if (p.mblk_group && p.mblk_group[m_sup * MT] < 0) continue;  // skipped by every role alike
+        if (p.mblk_group && p.mblk_group[m_sup * MTE] < 0) continue;  // skipped by every role alike
         const int it_cur = it++;
         const int acc = it_cur % kAcc;
         const uint32_t acc_phase = (it_cur / kAcc) & 1;
@@ -858,19 +881,33 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
             for (int k = 0; k < 4; ++k) {  // 4 x 32-byte K slices per 128-byte swizzle row
               const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
-              if (FP8)
+              if constexpr (PAIR)
+                umma_f16_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
+              else if (FP8)
                 umma_f8f6f4(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
               else
                 umma_f16(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
             }
           }
-          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if constexpr (PAIR) {   // the stage is free in both CTAs once these MMAs retire
+            umma_commit_pair(smem_u32(&empty_bar[stage]));
+            umma_commit_pair(cluster_map_addr(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        if (ok) {
+          if constexpr (PAIR) {
+            umma_commit_pair(smem_u32(&tmem_full[acc]));
+            umma_commit_pair(cluster_map_addr(smem_u32(&tmem_full[acc]), 1));
+          } else {
+            umma_commit(&tmem_full[acc]);
+          }
+        }
         if (tracing && it_cur == 0) p.trace[3] = clock64();
       }
     }
@@ -880,10 +917,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
+    for (int t = work_id; t < num_items && ok; t += work_stride) {
       int ks, m_sup, n_blk, kb0, kb1;
       decode_item(t, ks, m_sup, n_blk, kb0, kb1);
-      if (p.mblk_group && p.mblk_group[m_sup * MT] < 0) continue;  // skipped by every role alike
+      if (p.mblk_group && p.mblk_group[m_sup * MTE] < 0) continue;  // skipped by every role alike
       const int it_cur = it++;
       const int acc = it_cur % kAcc;
       const uint32_t acc_phase = (it_cur / kAcc) & 1;
@@ -928,7 +965,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems : 0;
 #pragma unroll 1
         for (int i = 0; i < MT; ++i) {
-          const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
+          const int m = (m_sup * MTE + (PAIR ? static_cast<int>(crank) : i)) * kBM + q * 32 + lane;
           float* dst = p.sk_scratch + (static_cast<long long>(ks) * p.M + m) * n_pad + static_cast<long long>(n_blk) * BN;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
@@ -956,7 +993,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (finisher) {
 #pragma unroll 1
         for (int i = 0; i < MT; ++i) {
-          const int m = (m_sup * MT + i) * kBM + q * 32 + lane;
+          const int m = (m_sup * MTE + (PAIR ? static_cast<int>(crank) : i)) * kBM + q * 32 + lane;
           const bool row_ok = m < p.M;
           const int mm = row_ok ? m : (p.M - 1);
           float rs = row_scale_of(p, mm);
@@ -1131,15 +1168,27 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       // hand the accumulator slot back to the MMA issuer
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (PAIR && !leader)
+          mbar_arrive_cluster(cluster_map_addr(smem_u32(&tmem_empty[acc]), 0));
+        else
+          mbar_arrive(&tmem_empty[acc]);
+      }
       if (tracing && it_cur == 0 && warp == 4 && lane == 0) p.trace[5] = clock64();
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  // a pair leaves together: the even CTA's MMAs read the partner's shared memory and signal its barriers
+  if constexpr (PAIR) cluster_barrier();
   tc_fence_after();
-  if (warp == 2) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 2) {
+    if constexpr (PAIR)
+      tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else
+      tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
   if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
 
   if constexpr (BN == 128) {
@@ -1371,12 +1420,136 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   return 0;
 }
 
+// Which GEMMs run on CTA pairs: 128 < M <= g_pair_max_m and the epilogue's bit set in g_pair_epi_mask. Measured at
+// M = 256 (B200): the pair main loop issues one 256 x N x 16 MMA per ~150 clocks for N = 128 and N = 256 alike, so it
+// pays for wide tiles (gate/up with 192-wide tiles: 65.7 vs 68.6 us; 256-wide residual tiles: 42 vs 51 us) and loses
+// to the 128-wide single-CTA tiles with parked split-K partials (o_proj 24 vs 28 us, QKV 33 vs 41 us).
+static int g_pair_max_m = -1;   // -1: not read yet
+static int g_pair_epi_mask = 1 << EPI_GLU;
+static int pair_max_m_setting() {
+  if (g_pair_max_m < 0) {
+    const char* on = getenv("GLLM_PAIR");          // "0": off; "1": every epilogue; unset: the default mask
+    const char* m = getenv("GLLM_PAIR_MAX_M");
+    g_pair_max_m = (on && on[0] == '0') ? 0 : (m ? atoi(m) : 256);
+    if (on && on[0] == '1') g_pair_epi_mask = 0xF;
+  }
+  return g_pair_max_m;
+}
+
+// CTA-pair launch (clusters of two, `tcgen05.mma.cta_group::2`): a work item is a 256-row x BN tile. Per 64-deep K
+// block each SM ingests 16 KB of A and BN/2 rows of B instead of 32 KB + BN rows for a 256-row single-CTA tile, and the
+// tensor core reads half as much B from shared memory per MMA; that is what decode-sized M (129..256 rows) is bound by.
+template <int BN, int EPI>
+static int launch_gemm_pair(const void* A, long long lda, const void* B, long long ldb, long long b_rows, GemmParams p,
+                            cudaStream_t stream, int force_splits) {
+  using Cfg = GemmCfg<BN, 1, true>;
+  constexpr int kElemsPerKB = 64;
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.N % 32 != 0) {
+    set_last_error("gemm (pair): bad problem M=%d N=%d K=%d", p.M, p.N, p.K);
+    return -1;
+  }
+  p.trace = g_trace_ptr;
+  p.num_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+  p.num_n = (p.N + BN - 1) / BN;
+  p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
+  p.cluster_sk = 0;
+  p.park = 0;
+  CUtensorMap ta, tb;
+  if (make_tmap_2d(&ta, A, dt, 2, uint64_t(p.M), uint64_t(p.K), uint64_t(lda), kBM, kElemsPerKB)) return -1;
+  if (make_tmap_2d(&tb, B, dt, 2, uint64_t(b_rows), uint64_t(p.K), uint64_t(ldb), BN / 2, kElemsPerKB)) return -1;
+  auto kern = gemm_tn_kernel<BN, 1, EPI, false, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) {
+      set_last_error("gemm (pair): cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+      return -1;
+    }
+    attr_set = true;
+  }
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // how many pairs can be resident at once (the split-K grid barrier needs every CTA of the launch running)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cfg.gridDim = dim3(sms & ~1, 1, 1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = -1;
+    }
+    max_pairs = n > 0 ? n : -1;
+  }
+  if (max_pairs <= 0) {
+    set_last_error("gemm (pair): clusters of two cannot be scheduled on this device");
+    return -1;
+  }
+  const int tiles = p.num_m * p.num_n;
+  const SplitKWorkspace& ws = g_splitk[dev & 63];
+  const long long tile_floats = 2ll * kBM * BN;
+  const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
+  int splits = 1;
+  if (BN % 128 != 0) force_splits = 1;
+  if (force_splits > 0)
+    splits = force_splits;
+  else if (ws.scratch)
+    splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats / 2, out_floats, max_pairs, ws.scratch_floats, false);
+  if (splits > 1 && (!ws.scratch || splits * out_floats > ws.scratch_floats || splits > p.num_kb || splits > kMaxSplits)) {
+    set_last_error("gemm (pair): split-K=%d needs %lld scratch floats (have %lld), K blocks %d", splits,
+                   splits * out_floats, ws.scratch_floats, p.num_kb);
+    return -1;
+  }
+  p.splits = splits;
+  p.sk_scratch = ws.scratch;
+  p.sk_barrier = ws.barrier;
+  const int items = tiles * splits;
+  const int pairs = items < max_pairs ? items : max_pairs;
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  if (ce != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_last_error("gemm (pair) launch failed: %s", cudaGetErrorString(ce));
+    return -1;
+  }
+  return 0;
+}
+
 // Dispatch on (tile width, rows per CTA). Small M uses 256-row CTA tiles so a weight tile is pulled
 // into shared memory once for the whole batch; large M keeps 128 x 256 tiles with a double-buffered
 // accumulator so the epilogue overlaps the next main loop.
 template <int EPI, bool FP8>
 static int dispatch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
                          const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
+  if constexpr (!FP8) {
+    // decode-sized M: CTA pairs (gllm_gemm_set_pair / GLLM_PAIR / GLLM_PAIR_MAX_M choose where they are used)
+    const int pair_max_m = pair_max_m_setting();
+    bool use_pair = p.M > 128 && p.M <= pair_max_m && ((g_pair_epi_mask >> EPI) & 1) && p.mblk_group == nullptr &&
+                    p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0;
+    if (EPI == EPI_GLU && g_pair_epi_mask != 0xF && bn < 192) use_pair = false;   // narrow GLU tiles: single CTAs win
+    if (use_pair) {
+      if constexpr (EPI == EPI_GLU) {
+        if (bn == 192) return launch_gemm_pair<192, EPI>(A, lda, B, ldb, b_rows, p, stream, 1);
+      }
+      if constexpr (EPI != EPI_QKV) {
+        if (bn == 256) return launch_gemm_pair<256, EPI>(A, lda, B, ldb, b_rows, p, stream, force_splits);
+      }
+      return launch_gemm_pair<128, EPI>(A, lda, B, ldb, b_rows, p, stream, force_splits);
+    }
+  }
   // The fused all-reduce never splits K locally, so it keeps 128-row tiles: more tiles in flight.
   bool two_rows = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr && p.ar_world == 0;
   if constexpr (EPI == EPI_QKV) {
@@ -1410,6 +1583,15 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
 using namespace gllm;
 
 extern "C" int* gllm_error_word();
+// Largest M that runs on CTA pairs (0 = never) and the set of epilogues (bit = EPI id; 0xF = all) that use them.
+// Returns the previous setting as (mask << 16) | max_m.
+GLLM_API int gllm_gemm_set_pair(int max_m, int epi_mask) {
+  const int old = (g_pair_epi_mask << 16) | pair_max_m_setting();
+  g_pair_max_m = max_m < 0 ? 0 : max_m;
+  g_pair_epi_mask = epi_mask & 0xF;
+  return old;
+}
+
 
 // ---------------------------------------------------------------------------------------------
 // C entry points. All pointers are device pointers; `stream` is a cudaStream_t.

@@ -94,8 +94,9 @@ class LLMEngine:
         self.d_offsets = torch.zeros(self.ms, dtype=torch.int64, device=dev)
         self.slot_params = np.zeros((self.ms, 4), dtype=np.float32)
         # Split the KV range of a sequence across CTAs only when (sequences x kv heads) alone cannot fill
-        # the machine: an unsplit flash-decode CTA streams its pages at full speed, splits add a merge.
-        want_splits = max(1, -(-4 * 148 // max(1, self.ms * model.n_kv_local)))
+        # the machine: an unsplit flash-decode CTA streams its pages at full speed, splits add a merge
+        # (measured at 256 sequences x 1 kv head, ragged contexts: unsplit 39.9 us, 3 splits 42.1 us).
+        want_splits = max(1, -(-3 * 148 // 2 // max(1, self.ms * model.n_kv_local)))
         pps = ec.pages_per_split if want_splits > 1 else 1 << 20
         if want_splits > 1:
             pps = max(8, -(-self.max_blocks // want_splits))

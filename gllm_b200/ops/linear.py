@@ -174,6 +174,14 @@ def gemm_residual(a, w, residual, *, out=None, row_ss_out=None, bias=None, bn=No
     return out, row_ss_out
 
 
+def set_pair_max_m(max_m: int, epi_mask: int = 0xF):
+    """GEMMs with 128 < M <= ``max_m`` whose epilogue is in ``epi_mask`` (bit 0 store, 1 residual, 2 GLU, 3 QKV) run on
+    CTA pairs (`tcgen05.mma.cta_group::2`, clusters of two); ``max_m`` 0 turns the path off. Returns the previous
+    ``(max_m, epi_mask)`` so a caller can restore it."""
+    old = int(nv.lib().gllm_gemm_set_pair(int(max_m), int(epi_mask)))
+    return old & 0xFFFF, old >> 16
+
+
 ACT_IDS = {"silu": 0, "swiglu": 0, "gelu_tanh": 1, "gelu_new": 1, "gelu_pytorch_tanh": 1, "geglu": 1, "gelu": 1}
 
 

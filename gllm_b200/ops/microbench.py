@@ -32,6 +32,22 @@ def _time(fn, iters, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if os.environ.get("GLLM_BENCH_GRAPH", "0") == "1":
+        # device time without per-call host overhead: `iters` calls captured in one CUDA graph
+        g = torch.cuda.CUDAGraph()
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            with torch.cuda.graph(g, stream=st):
+                for _ in range(iters):
+                    fn()
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e-3
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -90,15 +106,18 @@ def run(op: str, iters: int):
             out.update(shape=[M, (nq + 2 * nkv) * 128, K])
         out.update(us=t * 1e6, tflops=fl / t / 1e12, frac_of_bf16_peak=fl / t / 1e12 / tf)
     elif op == "gemm_decode":
-        M, N, K = 256, 4096, 12288
+        # default: the down projection; GLLM_DEC_N / GLLM_DEC_K / GLLM_DEC_BN / GLLM_DEC_SPLITS reshape it
+        M, N, K = 256, int(os.environ.get("GLLM_DEC_N", 4096)), int(os.environ.get("GLLM_DEC_K", 12288))
+        bn, sp = int(os.environ.get("GLLM_DEC_BN", 256)), int(os.environ.get("GLLM_DEC_SPLITS", 0))
         ws = [rnd(N, K, scale=0.05) for _ in range(3)]
         a, r = rnd(M, K), rnd(M, N)
         o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         i = [0]
+        out.update(bn=bn, splits=sp)
 
         def f():
             i[0] = (i[0] + 1) % 3
-            ops.gemm_residual(a, ws[i[0]], r, out=o, bn=256)
+            ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
         t = _time(f, iters)
         byts = N * K * 2
         out.update(shape=[M, N, K], us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
@@ -119,7 +138,7 @@ def run(op: str, iters: int):
         byts = 2 * I * K * 2
         out.update(shape=[M, 2 * I, K], bn=bn, us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
     elif op == "gemm_qkv":
-        M, K, nq, nkv = 2048, 4096, 32, 8
+        M, K, nq, nkv = int(os.environ.get("GLLM_QKV_M", 2048)), 4096, 32, 8
         a, w = rnd(M, K), rnd((nq + 2 * nkv) * 128, K, scale=0.05)
         ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
         kv = torch.zeros(M // 16 + 1, 2, nkv, 16, 128, device=dev, dtype=torch.bfloat16)

@@ -154,3 +154,41 @@ def test_gemm_determinism_and_reuse():
     for _ in range(3):
         o2 = ops.gemm(a, w)
     assert torch.equal(o1, o2)
+
+
+@pytest.fixture
+def cta_pairs():
+    """Route 128 < M <= 256 through the CTA-pair kernels (tcgen05.mma.cta_group::2) for the duration of a test."""
+    old = ops.set_pair_max_m(256, 0xF)
+    try:
+        yield
+    finally:
+        ops.set_pair_max_m(*old)
+
+
+def test_cta_pair_kernels_match_reference(cta_pairs):
+    """Every fused epilogue on the CTA-pair path: the existing cases whose M falls in the pair range."""
+    for M, N, K, bn in [(256, 4096, 4096, 256), (256, 4096, 4096, 128), (129, 32, 4096, 128), (200, 384, 520, 128)]:
+        test_gemm_plain(M, N, K, bn)
+    for M, N, K, bn, sp in [(256, 4096, 4096, 256, 9), (256, 4096, 12288, 256, 4), (256, 6144, 4096, 128, 3),
+                            (200, 768, 2048, 256, 2), (256, 4096, 4096, 128, 0)]:
+        test_gemm_split_k(M, N, K, bn, sp)
+    test_gemm_residual(256, 4096, 4096, 256)
+    test_gemm_residual(150, 1024, 512, 128)
+    for M, I, K, bn, act in [(256, 1024, 512, 256, 0), (256, 12288, 4096, 256, 0), (256, 1536, 1024, 192, 0),
+                             (130, 960, 512, 192, 1), (256, 1536, 1024, 128, 0)]:
+        for sp in (0, 1, 3):
+            test_gemm_glu(M, I, K, bn, act, sp)
+    for qk_norm in (True, False):
+        for M, sp in [(150, 0), (256, 3), (256, 1)]:
+            test_gemm_qkv_fused(qk_norm, M, sp)
+
+
+def test_cta_pair_kernels_are_deterministic(cta_pairs):
+    torch.manual_seed(11)
+    a, w, r = _rand(256, 4096), _rand(4096, 4096, scale=0.05), _rand(256, 4096)
+    o1, s1 = ops.gemm_residual(a, w, r, bn=128)
+    o1, s1 = o1.clone(), s1.clone()
+    for _ in range(3):
+        o2, s2 = ops.gemm_residual(a, w, r, bn=128)
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
