@@ -1424,14 +1424,21 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
 // M = 256 (B200): the pair main loop issues one 256 x N x 16 MMA per ~150 clocks for N = 128 and N = 256 alike, so it
 // pays for wide tiles (gate/up with 192-wide tiles: 65.7 vs 68.6 us; 256-wide residual tiles: 42 vs 51 us) and loses
 // to the 128-wide single-CTA tiles with parked split-K partials (o_proj 24 vs 28 us, QKV 33 vs 41 us).
+// At prefill sizes (M = 8192) 256 x 256 pair tiles run 1.4-3.5 % faster than 256 x 256 single-CTA tiles (plain
+// 1333 vs 1288 TFLOP/s, residual 1324 vs 1292, gate/up 1340 vs 1321), so 256-wide launches with M >= g_pair_big_m
+// use them too; the one-head-per-tile QKV GEMM does not (729 vs 948 TFLOP/s).
 static int g_pair_max_m = -1;   // -1: not read yet
 static int g_pair_epi_mask = 1 << EPI_GLU;
+static int g_pair_big_m = 1024;
 static int pair_max_m_setting() {
   if (g_pair_max_m < 0) {
     const char* on = getenv("GLLM_PAIR");          // "0": off; "1": every epilogue; unset: the default mask
     const char* m = getenv("GLLM_PAIR_MAX_M");
     g_pair_max_m = (on && on[0] == '0') ? 0 : (m ? atoi(m) : 256);
     if (on && on[0] == '1') g_pair_epi_mask = 0xF;
+    const char* big = getenv("GLLM_PAIR_BIG_M");    // 0: no pairs at prefill sizes
+    if (big) g_pair_big_m = atoi(big);
+    if (on && on[0] == '0') g_pair_big_m = 0;
   }
   return g_pair_max_m;
 }
@@ -1540,6 +1547,9 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
     bool use_pair = p.M > 128 && p.M <= pair_max_m && ((g_pair_epi_mask >> EPI) & 1) && p.mblk_group == nullptr &&
                     p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0;
     if (EPI == EPI_GLU && g_pair_epi_mask != 0xF && bn < 192) use_pair = false;   // narrow GLU tiles: single CTAs win
+    if (EPI != EPI_QKV && bn == 256 && g_pair_big_m > 0 && p.M >= g_pair_big_m && p.mblk_group == nullptr &&
+        p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0)
+      use_pair = true;
     if (use_pair) {
       if constexpr (EPI == EPI_GLU) {
         if (bn == 192) return launch_gemm_pair<192, EPI>(A, lda, B, ldb, b_rows, p, stream, 1);
@@ -1585,6 +1595,12 @@ using namespace gllm;
 extern "C" int* gllm_error_word();
 // Largest M that runs on CTA pairs (0 = never) and the set of epilogues (bit = EPI id; 0xF = all) that use them.
 // Returns the previous setting as (mask << 16) | max_m.
+GLLM_API int gllm_gemm_set_pair_big_m(int big_m) {   // 256-wide GEMMs with M >= big_m run on CTA pairs; 0 = never
+  pair_max_m_setting();
+  const int old = g_pair_big_m;
+  g_pair_big_m = big_m < 0 ? 0 : big_m;
+  return old;
+}
 GLLM_API int gllm_gemm_set_pair(int max_m, int epi_mask) {
   const int old = (g_pair_epi_mask << 16) | pair_max_m_setting();
   g_pair_max_m = max_m < 0 ? 0 : max_m;

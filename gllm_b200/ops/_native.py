@@ -27,6 +27,7 @@ _SIGNATURES = {
     "gllm_gemm_set_splitk_workspace": (I, [P, L, P, I]),
     "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I]),
     "gllm_gemm_set_pair": (I, [I, I]),
+    "gllm_gemm_set_pair_big_m": (I, [I]),
     "gllm_gemm_bf16_residual_allreduce": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, I, I, P, P, P, P, P, L]),
     "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I, I]),
     "gllm_gemm_bf16_grouped": (I, [P, L, P, L, P, L, I, I, I, P, I, I, P, I]),

@@ -182,6 +182,11 @@ def set_pair_max_m(max_m: int, epi_mask: int = 0xF):
     return old & 0xFFFF, old >> 16
 
 
+def set_pair_big_m(big_m: int) -> int:
+    """256-wide GEMMs with M >= ``big_m`` run on CTA pairs (0 = never). Returns the previous threshold."""
+    return int(nv.lib().gllm_gemm_set_pair_big_m(int(big_m)))
+
+
 ACT_IDS = {"silu": 0, "swiglu": 0, "gelu_tanh": 1, "gelu_new": 1, "gelu_pytorch_tanh": 1, "geglu": 1, "gelu": 1}
 
 

@@ -5,7 +5,7 @@ also be captured with ``ncu`` in a minute or two. Timing uses CUDA events on the
 warm-up; the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root if
 present) is printed as JSON.
 
-ops: gemm_prefill  gemm_prefill_glu  gemm_prefill_residual  gemm_prefill_qkv  gemm_decode  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
+ops: gemm_prefill  gemm_prefill_glu  gemm_prefill_residual  gemm_prefill_qkv  gemm_decode  gemm_decode_trace  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
      mla_attn
 """
 from __future__ import annotations
@@ -121,6 +121,36 @@ def run(op: str, iters: int):
         t = _time(f, iters)
         byts = N * K * 2
         out.update(shape=[M, N, K], us=t * 1e6, weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm)
+    elif op == "gemm_decode_trace":
+        # SM-clock stamps of CTA 0's phases for one decode-shaped residual GEMM (same GLLM_DEC_* knobs; GLLM_PAIR=1 for
+        # the CTA-pair kernel); weights rotate over three sets so that they stream from HBM
+        import ctypes
+        from . import _native as nv
+        lib = nv.lib()
+        lib.gllm_gemm_set_trace.argtypes = [ctypes.c_void_p]
+        lib.gllm_gemm_set_trace.restype = None
+        M, N, K = 256, int(os.environ.get("GLLM_DEC_N", 4096)), int(os.environ.get("GLLM_DEC_K", 12288))
+        bn, sp = int(os.environ.get("GLLM_DEC_BN", 256)), int(os.environ.get("GLLM_DEC_SPLITS", 0))
+        ws = [rnd(N, K, scale=0.05) for _ in range(3)]
+        a, r = rnd(M, K), rnd(M, N)
+        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def f():
+            i[0] = (i[0] + 1) % 3
+            ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
+        os.environ["GLLM_BENCH_GRAPH"] = "1"
+        t = _time(f, iters)
+        tr = torch.zeros(9, dtype=torch.int64, device=dev)
+        lib.gllm_gemm_set_trace(tr.data_ptr())
+        f()
+        torch.cuda.synchronize()
+        lib.gllm_gemm_set_trace(None)
+        st = tr.tolist()
+        names = ["set_up", "first_stage", "main_loop", "accumulator_ready", "epilogue_or_dump", "drain", "grid_barrier",
+                 "reduce"]
+        out.update(shape=[M, N, K], bn=bn, splits=sp, us=t * 1e6,
+                   clocks={n: (st[j + 1] - st[j] if st[j + 1] and st[j] else 0) for j, n in enumerate(names)})
     elif op == "gemm_glu":
         M, I, K = 256, int(os.environ.get("GLLM_GLU_I", 12288)), 4096    # GLLM_GLU_I=1536: one rank's share at TP8
         from ..models.weights import glu_tile_width

@@ -192,3 +192,17 @@ def test_cta_pair_kernels_are_deterministic(cta_pairs):
     for _ in range(3):
         o2, s2 = ops.gemm_residual(a, w, r, bn=128)
     assert torch.equal(o1, o2) and torch.equal(s1, s2)
+
+
+def test_large_m_kernels_with_and_without_cta_pairs():
+    """256-wide tiles at prefill sizes: the CTA-pair kernels (default) and the single-CTA kernels give the same answer."""
+    for big in (1024, 0):
+        old = ops.set_pair_big_m(big)
+        try:
+            test_gemm_plain(2048, 4096, 1024, 256)
+            test_gemm_plain(1100, 768, 520, 256)
+            test_gemm_residual(2048, 4096, 1536, 256)
+            test_gemm_glu(2048, 1024, 512, 256, 0, 0)
+            test_gemm_glu(3000, 1536, 1024, 256, 1, 0)
+        finally:
+            ops.set_pair_big_m(old)
