@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--shared-prefix", type=int, default=512)
     ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--op-breakdown", action="store_true",
+                    help="after the timed regions, time every op of one captured decode step with in-graph events")
     ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 marks the result invalid")
     return ap.parse_args()
 
@@ -231,6 +233,15 @@ def main():
     if err:
         raise SystemExit(f"device error word {err} in the timed region")
 
+    breakdown = None
+    if args.op_breakdown and not args.no_graphs:
+        res = engine.decode_breakdown(B)
+        names = sorted(res)
+        bt = torch.tensor([res[n] for n in names], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+        breakdown = {n: round(float(v), 4) for n, v in zip(names, bt.tolist())}
+
     t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -264,6 +275,8 @@ def main():
             "prefix_cache_hits": int(engine.batcher.prefix_hits),
             "kv_pages": engine.num_pages,
         }
+        if breakdown is not None:
+            out["decode_breakdown_ms"] = breakdown
         print(json.dumps(out), flush=True)
     if world > 1:
         # Leave without tearing NCCL down: communicators referenced by captured CUDA graphs do not

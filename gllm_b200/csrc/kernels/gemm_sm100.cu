@@ -90,7 +90,7 @@ struct GemmParams {
   __nv_bfloat16* ar_peer_buf[8];          // unicast addresses (index = rank); [ar_rank] is local
   unsigned long long* ar_mc_counter;      // multicast address of the arrival counter, or null
   unsigned long long* ar_peer_counter[8];
-  unsigned long long* ar_state;           // local {expected arrivals, launch index}
+  unsigned long long* ar_state;           // local {expected rank arrivals, launch index, CTA arrivals, expected CTA arrivals}
   int ar_rank;
   long long ar_buf_elems;                 // elements of one partial buffer (two alternate per launch)
   // row scatter (expert-parallel return path): output row m goes to scatter_peer[meta >> 24] + (meta & 0xFFFFFF) * ldo
@@ -166,20 +166,27 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned 
   return v;
 }
 
-// Cross-GPU arrival barrier of the fused all-reduce: every CTA of every rank adds one to the arrival
-// counter of every rank (one multimem.red, or one red per peer) after a system-scope fence, then waits
-// until its own rank's counter has reached `target`. Bounded; returns false on timeout.
-__device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long long target) {
+// Cross-GPU arrival barrier of the fused all-reduce, in two levels so that a rank's counter takes one remote atomic
+// per rank and launch instead of one per CTA: every CTA adds one to a LOCAL counter after a device-scope fence; the CTA
+// that completes the local count (`local_target`) issues a system-scope fence and adds one to the arrival counter of
+// every rank (one multimem.red, or one red per peer); everybody then waits until the own rank's counter has reached
+// `target`. Bounded; returns false on timeout.
+__device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long long target,
+                                           unsigned long long local_target) {
   __shared__ int ok_flag;
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    if (p.ar_mc_counter) {
-      asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_mc_counter), "l"(1ull) : "memory");
-    } else {
-      for (int r = 0; r < p.ar_world; ++r)
-        asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_peer_counter[r]), "l"(1ull) : "memory");
+    __threadfence();
+    const unsigned long long prev = atomicAdd(p.ar_state + 2, 1ull);
+    if (prev + 1ull == local_target) {
+      __threadfence_system();
+      if (p.ar_mc_counter) {
+        asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_mc_counter), "l"(1ull) : "memory");
+      } else {
+        for (int r = 0; r < p.ar_world; ++r)
+          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_peer_counter[r]), "l"(1ull) : "memory");
+      }
     }
     const unsigned long long* mine = p.ar_peer_counter[p.ar_rank];
     const unsigned long long t0 = globaltimer_ns();
@@ -469,8 +476,10 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
 // covers 8 columns = one 16-byte vector. The sum over ranks comes from one multimem.ld_reduce per
 // vector (NVSwitch adds in fp32) or from one plain load per peer; then residual add, bf16 store and
 // the row statistics for the next norm.
+// When the rank split K locally (`nsplits` partial buffers, `split_elems` apart) every split is pulled and added in
+// split order, identically on every rank.
 template <int BN>
-__device__ void ar_reduce_phase(const GemmParams& p, long long buf_off) {
+__device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nsplits, long long split_elems) {
   constexpr int U = 4;
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
@@ -486,29 +495,53 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off) {
       const int u = min(u0 + k, units - 1);
       off[k] = buf_off + static_cast<long long>(u / groups) * n_pad + static_cast<long long>(u % groups) * 256 + lane * 8;
     }
+#pragma unroll
+    for (int k = 0; k < U; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
     if (p.ar_mc_buf) {
-      uint4 raw[U];
+      if (nsplits == 2) {   // both splits' round trips through the switch in flight together
+        uint4 raw[2][U];
 #pragma unroll
-      for (int k = 0; k < U; ++k) raw[k] = multimem_ld_reduce_bf16x8(p.ar_mc_buf + off[k]);
+        for (int sp = 0; sp < 2; ++sp)
 #pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+          for (int k = 0; k < U; ++k) raw[sp][k] = multimem_ld_reduce_bf16x8(p.ar_mc_buf + off[k] + sp * split_elems);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h[e]);
-          acc[k][2 * e] = f.x;
-          acc[k][2 * e + 1] = f.y;
+        for (int sp = 0; sp < 2; ++sp)
+#pragma unroll
+          for (int k = 0; k < U; ++k) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[sp][k]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h[e]);
+              acc[k][2 * e] += f.x;
+              acc[k][2 * e + 1] += f.y;
+            }
+          }
+      } else {
+        for (int sp = 0; sp < nsplits; ++sp) {
+          uint4 raw[U];
+#pragma unroll
+          for (int k = 0; k < U; ++k) raw[k] = multimem_ld_reduce_bf16x8(p.ar_mc_buf + off[k] + sp * split_elems);
+#pragma unroll
+          for (int k = 0; k < U; ++k) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h[e]);
+              acc[k][2 * e] += f.x;
+              acc[k][2 * e + 1] += f.y;
+            }
+          }
         }
       }
     } else {
-#pragma unroll
-      for (int k = 0; k < U; ++k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
-      for (int r = 0; r < p.ar_world; ++r) {  // rank order: every rank computes the identical sum
+      for (int rs = 0; rs < p.ar_world * nsplits; ++rs) {  // (split, rank) order: every rank computes the identical sum
+        const int r = rs % p.ar_world;
+        const long long soff = static_cast<long long>(rs / p.ar_world) * split_elems;
         uint4 raw[U];
 #pragma unroll
-        for (int k = 0; k < U; ++k) raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.ar_peer_buf[r] + off[k]));
+        for (int k = 0; k < U; ++k) raw[k] = __ldcg(reinterpret_cast<const uint4*>(p.ar_peer_buf[r] + off[k] + soff));
 #pragma unroll
         for (int k = 0; k < U; ++k) {
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
@@ -752,9 +785,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (tracing && threadIdx.x == 0) p.trace[0] = clock64();
   __shared__ unsigned long long ar_expected_s;
   __shared__ unsigned int ar_launch_s;
+  __shared__ unsigned long long ar_local_base_s;
   if (fused_ar && threadIdx.x == 0) {
     ar_expected_s = p.ar_state[0];
     ar_launch_s = static_cast<unsigned int>(p.ar_state[1]);
+    ar_local_base_s = p.ar_state[3];
   }
   const int num_items = p.num_m * p.num_n * splits;
 
@@ -1209,14 +1244,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (p.park) {
       // every warp writes whole rows of the parked tile: 512 (fp32 scratch) or 256 (bf16 all-reduce buffer)
       // contiguous bytes per store instruction instead of 64-byte pieces of 32 different rows
-      int ks, m_sup, n_blk, kb0, kb1;
-      decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
+      int ks = 0, m_sup = 0, n_blk = 0, kb0, kb1;
+      const bool has_item = static_cast<int>(blockIdx.x) < num_items;   // the fused all-reduce launches every SM
+      if (has_item) decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
       const float* part = reinterpret_cast<const float*>(tiles);
       if (fused_ar) {
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
         __nv_bfloat16* dst = p.ar_peer_buf[p.ar_rank] + static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems +
-                             static_cast<long long>(n_blk) * BN + lane * 4;
-        for (int r = warp; r < MT * kBM; r += kGemmThreads / 32) {
+                             static_cast<long long>(ks) * p.M * n_pad + static_cast<long long>(n_blk) * BN + lane * 4;
+        for (int r = warp; has_item && r < MT * kBM; r += kGemmThreads / 32) {
           const int m = m_sup * MT * kBM + r;
           if (m >= p.M) continue;
           const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
@@ -1226,22 +1262,28 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           *reinterpret_cast<uint2*>(dst + static_cast<long long>(m) * n_pad) = w;
         }
       } else {
-        cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, /*S=*/1, /*ks=*/ks, /*skip_own=*/false);
+        if (has_item)
+          cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, /*S=*/1, /*ks=*/ks, /*skip_own=*/false);
       }
     }
   }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
     if (fused_ar) {
-      // all CTAs of all ranks have added their tiles once the local counter reaches the target
-      const unsigned long long target = ar_expected_s + static_cast<unsigned long long>(p.ar_world) * gridDim.x;
-      if (ar_barrier(p, target)) {
+      // one arrival per rank once all of that rank's CTAs have published their tiles
+      const unsigned long long target = ar_expected_s + static_cast<unsigned long long>(p.ar_world);
+      const unsigned long long local_target = ar_local_base_s + gridDim.x;
+      const bool ar_ok = ar_barrier(p, target, local_target);
+      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      if (ar_ok) {
         if constexpr (EPI == EPI_RESIDUAL)
-          ar_reduce_phase<BN>(p, static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems);
+          ar_reduce_phase<BN>(p, static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems, splits,
+                              static_cast<long long>(p.M) * p.num_n * BN);
       }
       // Safe to advance the launch state: every CTA of this rank read it before arriving at the barrier.
       if (blockIdx.x == 0 && threadIdx.x == 0) {
         p.ar_state[0] = target;
         p.ar_state[1] = static_cast<unsigned long long>(ar_launch_s) + 1ull;
+        p.ar_state[3] = local_target;
       }
     } else if (splits > 1) {
       // every partial of every CTA must be visible before anyone reduces
@@ -1257,6 +1299,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // host side
 // ---------------------------------------------------------------------------------------------
 static long long* g_trace_ptr = nullptr;
+static int g_trace_k = 0;   // when non-zero only launches with this K are traced
 
 struct SplitKWorkspace {
   float* scratch = nullptr;
@@ -1312,7 +1355,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     set_last_error("gemm: N=%d must be a multiple of 32 (pad the weight at load time)", p.N);
     return -1;
   }
-  p.trace = g_trace_ptr;
+  p.trace = (g_trace_k == 0 || g_trace_k == p.K) ? g_trace_ptr : nullptr;
   p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1339,20 +1382,41 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
   int splits = 1;
   if (p.mblk_group || BN % 128 != 0) force_splits = 1;  // grouped GEMMs have plenty of tiles
-  if (force_splits > 0)
-    splits = force_splits;
-  else if (p.ar_world > 0)  // each rank publishes exactly one partial per tile
+  static const bool park_allowed = [] {
+    const char* v = getenv("GLLM_NO_PARK");
+    return !(v && v[0] == '1');
+  }();
+  const bool part_fits = static_cast<long long>(MT) * kBM * kClusterPartStride * 4 <= static_cast<long long>(Cfg::kStages) * Cfg::kStageBytes;
+  if (p.ar_world > 0) {
+    // Fused all-reduce: a rank may split K locally when every work item gets its own CTA (the parked-tile path):
+    // split s publishes its bf16 partial in buffer slice s and the pull adds the slices of every rank. Halves the
+    // main loop of the decode-sized row-parallel GEMMs (64 tiles on 148 SMs).
     splits = 1;
+    static const bool ar_split_allowed = [] {
+      const char* v = getenv("GLLM_AR_SPLIT");
+      return !(v && v[0] == '0');
+    }();
+    // Only with two ranks: the pull moves (ranks x splits) partial buffers per output element, and from four ranks
+    // on that traffic (every rank reads every rank's buffer) costs more than the shorter main loop saves.
+    if (BN == 128 && park_allowed && part_fits && ar_split_allowed && force_splits <= 0 && p.mblk_group == nullptr &&
+        p.ar_world <= 2) {
+      int sp = sms / (tiles > 0 ? tiles : 1);
+      if (sp > 4) sp = 4;
+      if (sp > p.num_kb / 8) sp = p.num_kb / 8;
+      while (sp > 1 && sp * out_floats > p.ar_buf_elems) --sp;
+      if (sp >= 2) splits = sp;
+    }
+  } else if (force_splits > 0)
+    splits = force_splits;
   else if (ws.scratch)
     splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats,
                            BN == 128 && max_ctas <= 0 && !(getenv("GLLM_NO_CLUSTER_SK") && getenv("GLLM_NO_CLUSTER_SK")[0] == '1'));
   if (p.ar_world > 0) {
-    if (out_floats > p.ar_buf_elems || (static_cast<long long>(p.num_n) * BN) % 256 != 0) {
+    if (splits * out_floats > p.ar_buf_elems || (static_cast<long long>(p.num_n) * BN) % 256 != 0) {
       set_last_error("fused all-reduce: output needs %lld elements per buffer (have %lld), padded width %% 256",
-                     out_floats, p.ar_buf_elems);
+                     splits * out_floats, p.ar_buf_elems);
       return -1;
     }
-    splits = 1;
   } else if (splits > 1) {
     if (!ws.scratch || splits * out_floats > ws.scratch_floats || splits > p.num_kb || splits > kMaxSplits) {
       set_last_error("gemm: split-K=%d needs %lld scratch floats (have %lld), K blocks %d", splits,
@@ -1364,14 +1428,14 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   p.sk_scratch = ws.scratch;
   p.sk_barrier = ws.barrier;
   const int items = tiles * splits;
-  const int grid = items < sms ? items : sms;
+  // the fused all-reduce launches every SM: CTAs without a tile still pull and finish their share of the rows
+  const int grid = (p.ar_world > 0) ? sms : (items < sms ? items : sms);
   // Cluster split-K: the splits of a tile become one thread-block cluster (one work item per CTA) and reduce through
   // distributed shared memory instead of global scratch + grid barrier.
   static const bool cluster_allowed = [] {
     const char* v = getenv("GLLM_NO_CLUSTER_SK");
     return !(v && v[0] == '1');
   }();
-  const bool part_fits = static_cast<long long>(MT) * kBM * kClusterPartStride * 4 <= static_cast<long long>(Cfg::kStages) * Cfg::kStageBytes;
   if (BN == 128 && cluster_allowed && splits >= 2 && splits <= 8 && items <= sms && part_fits && p.ar_world == 0 &&
       p.mblk_group == nullptr && max_ctas <= 0) {
     p.cluster_sk = 1;
@@ -1405,10 +1469,6 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     }
     p.cluster_sk = 0;
   }
-  static const bool park_allowed = [] {
-    const char* v = getenv("GLLM_NO_PARK");
-    return !(v && v[0] == '1');
-  }();
   p.park = (BN == 128 && park_allowed && (splits > 1 || p.ar_world > 0) && items <= grid && part_fits &&
             p.mblk_group == nullptr) ? 1 : 0;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
@@ -1456,7 +1516,7 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
     set_last_error("gemm (pair): bad problem M=%d N=%d K=%d", p.M, p.N, p.K);
     return -1;
   }
-  p.trace = g_trace_ptr;
+  p.trace = (g_trace_k == 0 || g_trace_k == p.K) ? g_trace_ptr : nullptr;
   p.num_m = (p.M + 2 * kBM - 1) / (2 * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1746,6 +1806,7 @@ GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const 
 // entry, set-up done, first stage landed, MMAs of the first item issued, first accumulator ready, first epilogue
 // done, main loop left, split-K barrier passed, exit. Pass null to switch it off.
 GLLM_API void gllm_gemm_set_trace(long long* buf) { g_trace_ptr = buf; }
+GLLM_API void gllm_gemm_set_trace_k(int k) { g_trace_k = k; }
 
 // Fused QKV projection for head_dim 128: rowscale -> per-head RMSNorm (optional) -> RoPE -> q buffer and
 // paged KV write.  B is [(Hq+2Hkv)*128, K] with q heads first, then k heads, then v heads.

@@ -14,6 +14,7 @@ chunks run as ordinary launches between decode replays.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional
@@ -169,6 +170,47 @@ class LLMEngine:
         logits = self.model.forward(self._decode_batch(B), self.kv_caches, decode_ws=self.decode_ws)
         self._sample(logits, self.d_params[:B], self.d_offsets[:B], self.d_out[:B])
         self.d_offsets[:B] += 1
+        tm = getattr(self.model, "op_timer", None)
+        if tm is not None:
+            tm.mark("sample")
+
+    def decode_breakdown(self, B: int, replays: int = 3):
+        """Per-op device milliseconds of one captured decode step of bucket ``B`` (event nodes inside a fresh graph of
+        the same step; the graph used for serving is left as it was)."""
+        from ..utils.tracing import GraphTimer
+        key = (B, self._all_greedy)
+        keep = self.graphs.get(key)
+        self.model.op_timer = GraphTimer()
+        trace_k = int(os.environ.get("GLLM_TRACE_K", "0"))   # also stamp the phases of the GEMMs with this K
+        trace = None
+        if trace_k:
+            import ctypes
+            from ..ops import _native as nv
+            lib = nv.lib()
+            lib.gllm_gemm_set_trace.argtypes = [ctypes.c_void_p]
+            lib.gllm_gemm_set_trace.restype = None
+            lib.gllm_gemm_set_trace_k.argtypes = [ctypes.c_int]
+            lib.gllm_gemm_set_trace_k.restype = None
+            trace = torch.zeros(9, dtype=torch.int64, device=self.device)
+            lib.gllm_gemm_set_trace_k(trace_k)
+            lib.gllm_gemm_set_trace(trace.data_ptr())
+        try:
+            g = self._capture(B)
+            for _ in range(replays):
+                g.replay()
+            res = self.model.op_timer.results()
+            if trace is not None:
+                st = trace.tolist()
+                res.update({f"_clk{j}": float(st[j + 1] - st[j]) if st[j + 1] and st[j] else 0.0 for j in range(8)})
+        finally:
+            if trace is not None:
+                lib.gllm_gemm_set_trace(None)
+                lib.gllm_gemm_set_trace_k(0)
+            self.model.op_timer = None
+            if keep is not None:
+                self.graphs[key] = keep
+        self.d_offsets[:B] -= replays
+        return res
 
     def _sample(self, logits, params, offsets, out):
         tp = self.model.tp

@@ -196,6 +196,9 @@ class DecoderModel:
         x = ws.x[:T]
         H = c.hidden_size
         captured = {}
+        tm = getattr(self, "op_timer", None)      # utils.tracing.GraphTimer: per-op device time inside a CUDA graph
+        mark = tm.mark if tm is not None else (lambda name: None)
+        mark("begin")
         if self.first_stage and hidden_in is None:
             ops.embed_gather(batch.token_ids, self.embed, scale=c.embedding_scale, out=x, ss_out=ws.ss0[:T])
         else:      # a later pipeline stage, or input embeddings prepared by the caller (multimodal prompts)
@@ -210,17 +213,23 @@ class DecoderModel:
                              slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
                              sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                              row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias)
+                mark("qkv_gemm")
                 self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+                mark("attention")
                 ss_mid = self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
+                mark("o_proj")
                 if lw.moe is not None:
                     ss_in = lw.moe.forward(self, x, ss_mid, ws.ss_a[:T], T)
+                    mark("moe")
                 else:
                     # the packing is tile-width independent: the width recorded with the weight fills one wave of SMs
                     # at decode sizes, prefill chunks take the widest tile (best tensor-core rate)
                     glu_bn = 256 if (T > 1024 and lw.w_gate_up.shape[0] % 256 == 0) else lw.glu_bn
                     ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
                                  row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=glu_bn)
+                    mark("gate_up_gemm")
                     ss_in = self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
+                    mark("down_proj")
             else:
                 h = ws.h[:T]
                 ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)
@@ -258,6 +267,7 @@ class DecoderModel:
             xr = x if rows is None else x.index_select(0, rows)
             hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
             logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256)
+        mark("lm_head")
         if c.logit_softcap:
             logits = torch.tanh(logits / c.logit_softcap) * c.logit_softcap
         return logits

@@ -75,7 +75,7 @@ class TPContext:
         self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
         self._mc_acc = mc_ptr or None
         self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
-        self._state = torch.zeros(2, dtype=torch.int64, device=self.device)
+        self._state = torch.zeros(4, dtype=torch.int64, device=self.device)
 
     # ------------------------------------------------------------------------------------------
     def gemm_allreduce_residual(self, a, w, x, ss_out, partial, *, bn: int = 256):

@@ -78,6 +78,42 @@ class DeviceTimer:
         return dict(zip(names, t.tolist()))
 
 
+class GraphTimer:
+    """Per-op device time of a step that runs as a CUDA graph. ``mark(name)`` after an op records an event (an
+    external event-record node when called during stream capture); ``results`` attributes the interval since the
+    previous mark of the same capture to ``name``. Marks whose events did not fire in the last replay are skipped."""
+
+    def __init__(self):
+        self.marks: List[tuple] = []
+
+    def mark(self, name: str):
+        if not torch.cuda.is_available() or not torch.cuda.is_current_stream_capturing():
+            return      # only the captured step is timed, not its eager warm-up
+        e = torch.cuda.Event(enable_timing=True, external=True)
+        e.record()
+        self.marks.append((name, e))
+
+    def results(self) -> Dict[str, float]:
+        if not self.marks:
+            return {}
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        prev = None
+        for name, e in self.marks:
+            if name == "begin" or prev is None:
+                prev = e
+                continue
+            try:
+                dt = prev.elapsed_time(e)
+            except Exception:      # not part of the last replayed graph
+                prev = e
+                continue
+            if dt >= 0:
+                out[name] = out.get(name, 0.0) + dt
+            prev = e
+        return out
+
+
 class ChromeTrace:
     """Host-side spans in the Chrome / Perfetto trace-event format."""
 

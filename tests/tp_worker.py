@@ -19,7 +19,8 @@ def main():
     if mode != "nccl":
         assert tp.mode == "fused", getattr(tp, "setup_error", "")
     g = torch.Generator(device="cpu").manual_seed(7)
-    for it, (M, K) in enumerate([(256, 1024), (77, 512), (256, 1024), (512, 2048)]):
+    for it, (M, K) in enumerate([(256, 1024), (77, 512), (256, 1024), (512, 2048), (128, 2048), (64, 4096),
+                                   (256, 3072)]):
         a_full = torch.randn(M, K * world, generator=g).to(torch.bfloat16)
         w_full = (torch.randn(H, K * world, generator=g) * 0.05).to(torch.bfloat16)
         x0 = torch.randn(M, H, generator=g).to(torch.bfloat16)
