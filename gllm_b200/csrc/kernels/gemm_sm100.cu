@@ -1108,15 +1108,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               const int n0 = n_blk * kHalf + c * 32;  // output column
               if (n0 >= p.N / 2) continue;
               float v[32];
+              if (p.b_scale) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                float gv = g[j] * rs;
-                float uv = u[j] * rs;
-                if (p.b_scale) {
-                  gv *= p.b_scale[n_blk * BN + c * 64 + j];
-                  uv *= p.b_scale[n_blk * BN + c * 64 + 32 + j];
+                for (int j = 0; j < 32; ++j) {
+                  g[j] *= p.b_scale[n_blk * BN + c * 64 + j];
+                  u[j] *= p.b_scale[n_blk * BN + c * 64 + 32 + j];
                 }
-                v[j] = (p.glu_act == 0 ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+              }
+              if (p.glu_act == 0) {   // the activation choice is hoisted out of the element loop
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = silu_f(g[j] * rs) * (u[j] * rs);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(g[j] * rs) * (u[j] * rs);
               }
               if (row_ok)
                 store_bf16x32(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0, v);
@@ -1182,14 +1186,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   x0 *= inv_rms * nw[c * 32 + j];
                   x1 *= inv_rms * nw[64 + c * 32 + j];
                 }
-                if (is_q || is_k) {
-                  const float cs = p.cos_table[static_cast<long long>(pos) * 64 + c * 32 + j];
-                  const float sn = p.sin_table[static_cast<long long>(pos) * 64 + c * 32 + j];
-                  a[j] = x0 * cs - x1 * sn;
-                  b[j] = x1 * cs + x0 * sn;
-                } else {
-                  a[j] = x0;
-                  b[j] = x1;
+                a[j] = x0;
+                b[j] = x1;
+              }
+              if (is_q || is_k) {
+                // this row's 32 cos / sin values as 16-byte loads (table rows are 256 bytes, 128-byte aligned here)
+                const float4* c4 = reinterpret_cast<const float4*>(p.cos_table + static_cast<long long>(pos) * 64 + c * 32);
+                const float4* s4 = reinterpret_cast<const float4*>(p.sin_table + static_cast<long long>(pos) * 64 + c * 32);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                  const float4 cs = __ldg(c4 + jj), sn = __ldg(s4 + jj);
+                  const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float x0 = a[jj * 4 + e], x1 = b[jj * 4 + e];
+                    a[jj * 4 + e] = x0 * cv[e] - x1 * sv[e];
+                    b[jj * 4 + e] = x1 * cv[e] + x0 * sv[e];
+                  }
                 }
               }
               if (dst) {
@@ -1482,13 +1495,13 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
 
 // Which GEMMs run on CTA pairs: 128 < M <= g_pair_max_m and the epilogue's bit set in g_pair_epi_mask. Measured at
 // M = 256 (B200): the pair main loop issues one 256 x N x 16 MMA per ~150 clocks for N = 128 and N = 256 alike, so it
-// pays for wide tiles (gate/up with 192-wide tiles: 65.7 vs 68.6 us; 256-wide residual tiles: 42 vs 51 us) and loses
-// to the 128-wide single-CTA tiles with parked split-K partials (o_proj 24 vs 28 us, QKV 33 vs 41 us).
+// only pays for wide tiles, and at decode sizes the single-CTA kernels end up ahead everywhere (gate/up with 192-wide
+// tiles: 52.9 vs 57.0 us; o_proj 22 vs 28 us; QKV 33 vs 41 us), so no decode epilogue uses pairs by default.
 // At prefill sizes (M = 8192) 256 x 256 pair tiles run 1.4-3.5 % faster than 256 x 256 single-CTA tiles (plain
 // 1333 vs 1288 TFLOP/s, residual 1324 vs 1292, gate/up 1340 vs 1321), so 256-wide launches with M >= g_pair_big_m
 // use them too; the one-head-per-tile QKV GEMM does not (729 vs 948 TFLOP/s).
 static int g_pair_max_m = -1;   // -1: not read yet
-static int g_pair_epi_mask = 1 << EPI_GLU;
+static int g_pair_epi_mask = 0;
 static int g_pair_big_m = 1024;
 static int pair_max_m_setting() {
   if (g_pair_max_m < 0) {

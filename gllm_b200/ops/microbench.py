@@ -135,10 +135,15 @@ def run(op: str, iters: int):
         a, r = rnd(M, K), rnd(M, N)
         o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         i = [0]
+        glu = os.environ.get("GLLM_DEC_EPI", "residual") == "glu"    # N counts gate + up rows then
+        ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
 
         def f():
             i[0] = (i[0] + 1) % 3
-            ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
+            if glu:
+                ops.gemm_glu(a, ws[i[0]], out=o[:, :N // 2], row_ss=ss, norm_dim=K, eps=1e-6, bn=bn, splits=sp)
+            else:
+                ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
         os.environ["GLLM_BENCH_GRAPH"] = "1"
         t = _time(f, iters)
         tr = torch.zeros(9, dtype=torch.int64, device=dev)
