@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--shared-prefix", type=int, default=512)
     ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="fp8: e4m3 KV cache (half the KV bytes); not the headline configuration, reported as invalid for it")
     ap.add_argument("--op-breakdown", action="store_true",
                     help="after the timed regions, time every op of one captured decode step with in-graph events")
     ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 marks the result invalid")
@@ -155,7 +157,8 @@ def main():
         tp = TPContext(rank, world, dev, mode=args.tp_mode, max_tokens=8192, hidden=cfg.hidden_size)
     max_len = args.max_prompt + args.output_tokens + 16
     src = RandomWeights(cfg, dev, torch.bfloat16, seed=0)
-    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len)
+    kv_kw = dict(kv_dtype=torch.float8_e4m3fn, kv_scale=0.05) if args.kv_dtype == "fp8" else {}
+    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len, **kv_kw)
     ecfg = EngineConfig(max_num_seqs=args.concurrency, max_model_len=max_len, max_batch_tokens=8192,
                         prefill_chunk=8192, use_cuda_graphs=not args.no_graphs)
     ecfg.num_pages = args.concurrency * ((max_len + 15) // 16) + 64
@@ -173,6 +176,9 @@ def main():
         torch.cuda.synchronize(dev)
 
     # ---- phase 1: admit + prefill everything (untimed for the decode metric; gives TTFT) ----
+    if args.op_breakdown:
+        from gllm_b200.utils.tracing import GraphTimer
+        engine.prefill_timer = GraphTimer(eager=True)
     t_submit = time.perf_counter()
     ids = [engine.add_request(p, max_tokens=budget_tokens, temperature=0.0, eos_ids=[]) for p in prompts]
     first_token_at = {}
@@ -233,6 +239,10 @@ def main():
     if err:
         raise SystemExit(f"device error word {err} in the timed region")
 
+    prefill_ops = None
+    if args.op_breakdown:
+        prefill_ops = {n: round(v, 1) for n, v in engine.prefill_timer.results().items()}
+        engine.prefill_timer = None
     breakdown = None
     if args.op_breakdown and not args.no_graphs:
         res = engine.decode_breakdown(B)
@@ -260,7 +270,8 @@ def main():
                        "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
                        "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
-                       "layers": cfg.num_layers, "valid": args.layers == 0},
+                       "layers": cfg.num_layers, "kv_dtype": args.kv_dtype,
+                       "valid": args.layers == 0 and args.kv_dtype == "bf16"},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms / K, 4)},
             "gpu_launches": int(launches_per_step * K),
@@ -277,6 +288,8 @@ def main():
         }
         if breakdown is not None:
             out["decode_breakdown_ms"] = breakdown
+        if prefill_ops is not None:
+            out["prefill_ops_ms"] = prefill_ops
         print(json.dumps(out), flush=True)
     if world > 1:
         # Leave without tearing NCCL down: communicators referenced by captured CUDA graphs do not

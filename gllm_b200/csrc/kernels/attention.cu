@@ -15,7 +15,14 @@
 // scale 1/sqrt(d), kv head = q head / (Hq/Hkv), causal mask, max-subtracted softmax; optional sliding
 // window and learnable sinks (src/arch/auto_graph_fragments/build_graph.inc.rs:1775-1781).
 //
-// Cache layout per layer: [page][K|V][kv_head][16 tokens][128] bf16.
+// Cache layout per layer: [page][K|V][kv_head][16 tokens][128] bf16, or the same shape in fp8 (e4m3, one per-tensor
+// scale). The fp8 variants of both kernels (template parameter KV8) fetch 2 KB page tiles, convert the ldmatrix
+// fragments to f16 in registers (cvt.f16x2.e4m3x2) and run the same tiles on mma.sync f16: a 16-byte shared-memory
+// chunk then holds 16 features instead of 8, so the K fragments pair features (4t..4t+3) with a matching permutation
+// of the Q fragment's k index, and a transposed V fragment yields the even and the odd features of a 16-feature block
+// as two n-tiles; the output columns are un-permuted when they are written.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace gllm {
@@ -23,6 +30,10 @@ namespace gllm {
 constexpr int kHD = 128;
 constexpr int kPage = 16;
 constexpr int kPageBytes = kPage * kHD * 2;  // 4 KB per (page, K|V, head)
+template <bool KV8>
+struct KvFmt {
+  static constexpr int kBytes = KV8 ? kPage * kHD : kPage * kHD * 2;   // one K or V tile of a page
+};
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -41,6 +52,60 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two e4m3 bytes (low 16 bits of x) -> f16x2, low byte in the low half
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t x) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(x & 0xFFFFu), __NV_E4M3);
+  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t x) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x));
+  return pack_f16x2(f.x, f.y);
+}
+
+// Q fragments of one 16-row tile. bf16 cache: the standard m16n8k16 A layout over feature blocks of 16. fp8 cache:
+// f16 values, and within each block thread t holds features 4t, 4t+1 (k = 2t, 2t+1) and 4t+2, 4t+3 (k = 2t+8, 2t+9),
+// the order in which a 16-byte ldmatrix chunk of fp8 K delivers them.
+template <bool KV8>
+__device__ __forceinline__ void load_q_frags(const __nv_bfloat16* q0, const __nv_bfloat16* q1, bool ok0, bool ok1,
+                                             uint32_t (&qf)[8][4]) {
+  const int t = threadIdx.x & 3;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    if constexpr (KV8) {
+      const int c = ks * 16 + t * 4;
+      const uint2 v0 = ok0 ? *reinterpret_cast<const uint2*>(q0 + c) : make_uint2(0u, 0u);
+      const uint2 v1 = ok1 ? *reinterpret_cast<const uint2*>(q1 + c) : make_uint2(0u, 0u);
+      qf[ks][0] = bf16x2_to_f16x2(v0.x);
+      qf[ks][1] = bf16x2_to_f16x2(v1.x);
+      qf[ks][2] = bf16x2_to_f16x2(v0.y);
+      qf[ks][3] = bf16x2_to_f16x2(v1.y);
+    } else {
+      const int c = ks * 16 + t * 2;
+      qf[ks][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qf[ks][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qf[ks][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qf[ks][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+    }
+  }
+}
+// Feature index of accumulator element e (0/1: the two columns of the row) of n-tile dt.
+template <bool KV8>
+__device__ __forceinline__ int out_feature(int dt, int e) {
+  const int t = threadIdx.x & 3;
+  if constexpr (KV8) return 16 * (dt >> 1) + 4 * t + 2 * e + (dt & 1);
+  return dt * 8 + t * 2 + e;
+}
+
 // Online-softmax state of one warp: rows r0 = lane/4 and r1 = r0 + 8 of a 16-row tile.
 struct SoftmaxState {
   float m0, m1, l0, l1;
@@ -49,12 +114,28 @@ struct SoftmaxState {
 // One 16-token page: S = Q·Kᵀ (16x16), mask, online softmax, O += P·V.
 // k_smem / v_smem: shared addresses of the page's K and V tiles, each two 2 KB boxes
 // ([d half][token][64 bf16], 128-byte swizzle). Row r may attend tokens in [lo_r, hi_r).
+template <bool KV8>
 __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t k_smem, uint32_t v_smem,
                                             int tok_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
                                             float (&o)[16][4], SoftmaxState& st) {
   const int lane = threadIdx.x & 31;
   float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  {
+  if constexpr (KV8) {
+    // K tile: [16 tokens][128 bytes]; one x4 load = tokens 0-7 / 8-15 x feature blocks 2i, 2i+1
+    const int tok = (lane & 7) + ((lane >> 4) << 3);
+    const int csel = (lane >> 3) & 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = 2 * i + csel;
+      const uint32_t addr = k_smem + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(addr, b0, b1, b2, b3);
+      mma_f16_16816(s[0], qf[2 * i], e4m3x2_to_f16x2(b0), e4m3x2_to_f16x2(b0 >> 16));
+      mma_f16_16816(s[0], qf[2 * i + 1], e4m3x2_to_f16x2(b1), e4m3x2_to_f16x2(b1 >> 16));
+      mma_f16_16816(s[1], qf[2 * i], e4m3x2_to_f16x2(b2), e4m3x2_to_f16x2(b2 >> 16));
+      mma_f16_16816(s[1], qf[2 * i + 1], e4m3x2_to_f16x2(b3), e4m3x2_to_f16x2(b3 >> 16));
+    }
+  } else {
     const int tok = (lane & 7) + ((lane >> 4) << 3);
     const int csel = (lane >> 3) & 1;
 #pragma unroll
@@ -90,6 +171,9 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
   const float mn0 = fmaxf(st.m0, mx0), mn1 = fmaxf(st.m1, mx1);
   const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0, ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
   const float corr0 = exp2f(st.m0 - ms0), corr1 = exp2f(st.m1 - ms1);  // exp2(-inf) = 0 on first use
+  // in steady state the running maxima rarely move: then every correction factor is exactly 1 and the 64
+  // multiplies on the output accumulators can be skipped (warp-uniform decision)
+  const bool rescale = __any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f);
   st.m0 = mn0;
   st.m1 = mn1;
   float rs0 = 0.f, rs1 = 0.f;
@@ -110,11 +194,42 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
   st.l0 = st.l0 * corr0 + rs0;
   st.l1 = st.l1 * corr1 + rs1;
   uint32_t pf[4];
-  pf[0] = pack_bf16x2(s[0][0], s[0][1]);
-  pf[1] = pack_bf16x2(s[0][2], s[0][3]);
-  pf[2] = pack_bf16x2(s[1][0], s[1][1]);
-  pf[3] = pack_bf16x2(s[1][2], s[1][3]);
-  {
+  if constexpr (KV8) {
+    pf[0] = pack_f16x2(s[0][0], s[0][1]);
+    pf[1] = pack_f16x2(s[0][2], s[0][3]);
+    pf[2] = pack_f16x2(s[1][0], s[1][1]);
+    pf[3] = pack_f16x2(s[1][2], s[1][3]);
+  } else {
+    pf[0] = pack_bf16x2(s[0][0], s[0][1]);
+    pf[1] = pack_bf16x2(s[0][2], s[0][3]);
+    pf[2] = pack_bf16x2(s[1][0], s[1][1]);
+    pf[3] = pack_bf16x2(s[1][2], s[1][3]);
+  }
+  if constexpr (KV8) {
+    // V tile: [16 tokens][128 bytes]; a transposed 8x8 b16 matrix hands thread (g, t) the bytes
+    // {tok 2t: features 2g, 2g+1 | tok 2t+1: features 2g, 2g+1} of a 16-feature block: bytes 0,2 are the even-feature
+    // B fragment, bytes 1,3 the odd one. One x4 load = tokens 0-7 / 8-15 x blocks 2i, 2i+1.
+    const int tok = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int csel = lane >> 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = 2 * i + csel;
+      const uint32_t addr = v_smem + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t r0, r1, r2, r3;   // (tok 0-7, blk 2i), (tok 8-15, blk 2i), (tok 0-7, blk 2i+1), (tok 8-15, blk 2i+1)
+      ldsm_x4_t(addr, r0, r1, r2, r3);
+      if (rescale) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[4 * i + q4][e] *= (e < 2) ? corr0 : corr1;
+        }
+      }
+      mma_f16_16816(o[4 * i + 0], pf, e4m3x2_to_f16x2(__byte_perm(r0, 0u, 0x4420)), e4m3x2_to_f16x2(__byte_perm(r1, 0u, 0x4420)));
+      mma_f16_16816(o[4 * i + 1], pf, e4m3x2_to_f16x2(__byte_perm(r0, 0u, 0x4431)), e4m3x2_to_f16x2(__byte_perm(r1, 0u, 0x4431)));
+      mma_f16_16816(o[4 * i + 2], pf, e4m3x2_to_f16x2(__byte_perm(r2, 0u, 0x4420)), e4m3x2_to_f16x2(__byte_perm(r3, 0u, 0x4420)));
+      mma_f16_16816(o[4 * i + 3], pf, e4m3x2_to_f16x2(__byte_perm(r2, 0u, 0x4431)), e4m3x2_to_f16x2(__byte_perm(r3, 0u, 0x4431)));
+    }
+  } else {
     const int tok = (lane & 7) + (((lane >> 3) & 1) << 3);
     const int csel = lane >> 4;
 #pragma unroll
@@ -124,10 +239,12 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
       const uint32_t addr = v_smem + box * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4);
       uint32_t b0, b1, b2, b3;
       ldsm_x4_t(addr, b0, b1, b2, b3);
+      if (rescale) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        o[2 * j][e] *= (e < 2) ? corr0 : corr1;
-        o[2 * j + 1][e] *= (e < 2) ? corr0 : corr1;
+        for (int e = 0; e < 4; ++e) {
+          o[2 * j][e] *= (e < 2) ? corr0 : corr1;
+          o[2 * j + 1][e] *= (e < 2) ? corr0 : corr1;
+        }
       }
       mma_bf16_16816(o[2 * j], pf, b0, b1);
       mma_bf16_16816(o[2 * j + 1], pf, b2, b3);
@@ -135,15 +252,21 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
   }
 }
 
+template <bool KV8>
 __device__ __forceinline__ void load_page_kv(const CUtensorMap* tmap, uint8_t* dst, uint64_t* bar, int page,
                                              int n_kv_heads, int kvh) {
   const int krow = ((page * 2 + 0) * n_kv_heads + kvh) * kPage;
   const int vrow = ((page * 2 + 1) * n_kv_heads + kvh) * kPage;
-  mbar_expect_tx(bar, 2 * kPageBytes);
-  tma_load_2d(dst, tmap, bar, 0, krow);
-  tma_load_2d(dst + 2048, tmap, bar, 64, krow);
-  tma_load_2d(dst + 4096, tmap, bar, 0, vrow);
-  tma_load_2d(dst + 6144, tmap, bar, 64, vrow);
+  mbar_expect_tx(bar, 2 * KvFmt<KV8>::kBytes);
+  if constexpr (KV8) {   // one 16 x 128-byte box per tile
+    tma_load_2d(dst, tmap, bar, 0, krow);
+    tma_load_2d(dst + 2048, tmap, bar, 0, vrow);
+  } else {
+    tma_load_2d(dst, tmap, bar, 0, krow);
+    tma_load_2d(dst + 2048, tmap, bar, 64, krow);
+    tma_load_2d(dst + 4096, tmap, bar, 0, vrow);
+    tma_load_2d(dst + 6144, tmap, bar, 64, vrow);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -164,18 +287,24 @@ struct DecodeParams {
   int num_pages;
   int window;          // 0 = full attention
   const float* sinks;  // [Hq] learnable sink logits or null
+  float v_scale;       // fp8 cache: value = stored * scale (the K scale is folded into scale_log2)
   int* err;
 };
 
 constexpr int kDecWarps = 4;
 constexpr int kDecStages = 3;
 constexpr int kDecSmem = kDecWarps * kDecStages * 2 * kPageBytes + 1024 + 1024;
+// fp8 pages: half the ring (still larger than the 33 KB the cross-warp merge needs), so three CTAs fit per SM; the
+// extra warps hide the latency of the per-fragment conversions
+constexpr int kDecSmem8 = kDecWarps * kDecStages * 2 * (kPageBytes / 2) + 1024 + 1024;
 
-__global__ void __launch_bounds__(kDecWarps * 32)
+template <bool KV8>
+__global__ void __launch_bounds__(kDecWarps * 32, KV8 ? 3 : 2)
 paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeParams p) {
+  constexpr int kTile = KvFmt<KV8>::kBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecWarps * kDecStages * 2 * kPageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDecWarps * kDecStages * 2 * kTile);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kDecWarps * kDecStages);
   int* is_last = const_cast<int*>(abort_flag) + 1;
 
@@ -208,14 +337,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
     const __nv_bfloat16* qb = p.q + (static_cast<long long>(b) * p.n_q_heads + kvh * p.group) * kHD;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const int c = ks * 16 + (lane & 3) * 2;
-      qf[ks][0] = r0 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r0 * kHD + c) : 0u;
-      qf[ks][1] = r1 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r1 * kHD + c) : 0u;
-      qf[ks][2] = r0 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r0 * kHD + c + 8) : 0u;
-      qf[ks][3] = r1 < p.group ? *reinterpret_cast<const uint32_t*>(qb + r1 * kHD + c + 8) : 0u;
-    }
+    load_q_frags<KV8>(qb + r0 * kHD, qb + r1 * kHD, r0 < p.group, r1 < p.group, qf);
   }
 
   float o[16][4];
@@ -223,7 +345,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   SoftmaxState st{-INFINITY, -INFINITY, 0.f, 0.f};
 
-  uint8_t* my_ring = smem + warp * kDecStages * 2 * kPageBytes;
+  uint8_t* my_ring = smem + warp * kDecStages * 2 * kTile;
   uint64_t* my_bars = bars + warp * kDecStages;
   const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
   const int n_my = (p1 - p0 - warp + kDecWarps - 1) / kDecWarps;  // pages p0+warp, p0+warp+4, ...
@@ -236,7 +358,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
       page = 0;
     }
     const int stg = i % kDecStages;
-    load_page_kv(&tmap_kv, my_ring + stg * 2 * kPageBytes, &my_bars[stg], page, p.n_kv_heads, kvh);
+    load_page_kv<KV8>(&tmap_kv, my_ring + stg * 2 * kTile, &my_bars[stg], page, p.n_kv_heads, kvh);
   };
   if (lane == 0) {
     for (int i = 0; i < n_my && i < kDecStages; ++i) issue(i);
@@ -247,9 +369,9 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     // warp-uniform decision: the page body uses warp-synchronous instructions
     const bool got = mbar_wait(&my_bars[stg], (i / kDecStages) & 1, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL);
     if (!__all_sync(0xffffffffu, got)) break;
-    const uint32_t kaddr = smem_u32(my_ring + stg * 2 * kPageBytes);
+    const uint32_t kaddr = smem_u32(my_ring + stg * 2 * kTile);
     const int tok_base = (p0 + warp + i * kDecWarps) * kPage;
-    attend_page(qf, kaddr, kaddr + kPageBytes, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
+    attend_page<KV8>(qf, kaddr, kaddr + kTile, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
     __syncwarp();
     if (lane == 0 && i + kDecStages < n_my) {
       fence_proxy_async_smem();
@@ -266,13 +388,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     const int r0 = lane >> 2, r1 = r0 + 8;
 #pragma unroll
     for (int dt = 0; dt < 16; ++dt) {
-      const int c = dt * 8 + (lane & 3) * 2;
-      float* w0 = mo + (warp * 16 + r0) * kHD + c;
-      float* w1 = mo + (warp * 16 + r1) * kHD + c;
-      w0[0] = o[dt][0];
-      w0[1] = o[dt][1];
-      w1[0] = o[dt][2];
-      w1[1] = o[dt][3];
+      const int c0 = out_feature<KV8>(dt, 0), c1 = out_feature<KV8>(dt, 1);
+      float* w0 = mo + (warp * 16 + r0) * kHD;
+      float* w1 = mo + (warp * 16 + r1) * kHD;
+      w0[c0] = o[dt][0];
+      w0[c1] = o[dt][1];
+      w1[c0] = o[dt][2];
+      w1[c1] = o[dt][3];
     }
     if ((lane & 3) == 0) {
       mml[(warp * 16 + r0) * 2 + 0] = st.m0;
@@ -299,10 +421,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     const int qh = kvh * p.group + r;
     if (single) {
       if (p.sinks) L += exp2f(p.sinks[qh] * 1.4426950408889634f - M);
-      p.out[(static_cast<long long>(b) * p.n_q_heads + qh) * kHD + d] = __float2bfloat16_rn(acc / L);
+      p.out[(static_cast<long long>(b) * p.n_q_heads + qh) * kHD + d] = __float2bfloat16_rn(acc / L * (KV8 ? p.v_scale : 1.f));
     } else {
       const long long pi = (static_cast<long long>(b) * p.n_q_heads + qh) * p.max_splits + split;
-      p.part_o[pi * kHD + d] = acc / L;
+      p.part_o[pi * kHD + d] = acc / L * (KV8 ? p.v_scale : 1.f);
       if (d == 0) p.part_lse[pi] = M + log2f(L);
     }
   }
@@ -351,6 +473,7 @@ struct PrefillParams {
   int window;
   int causal;  // 0 = bidirectional over [0, ctx)
   const float* sinks;
+  float v_scale;   // fp8 cache: value = stored * scale (the K scale is folded into scale_log2)
   int* err;
 };
 
@@ -358,11 +481,13 @@ constexpr int kPfWarps = 4;
 constexpr int kPfRows = kPfWarps * 16;  // 64 query rows per CTA
 constexpr int kPfBlockPages = 4;        // 64 KV tokens per stage
 constexpr int kPfStages = 2;
-constexpr int kPfStageBytes = kPfBlockPages * 2 * kPageBytes;  // 32 KB
+constexpr int kPfStageBytes = kPfBlockPages * 2 * kPageBytes;  // 32 KB (the fp8 variant fills half of it)
 constexpr int kPfSmem = kPfStages * kPfStageBytes + 1024 + 1024;
 
+template <bool KV8>
 __global__ void __launch_bounds__(kPfWarps * 32)
 paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillParams p) {
+  constexpr int kTile = KvFmt<KV8>::kBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPfStages * kPfStageBytes);
@@ -391,14 +516,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
   {
     const __nv_bfloat16* q0 = p.q + (static_cast<long long>(qstart + row0) * p.n_q_heads + qh) * kHD;
     const __nv_bfloat16* q1 = p.q + (static_cast<long long>(qstart + row1) * p.n_q_heads + qh) * kHD;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const int c = ks * 16 + (lane & 3) * 2;
-      qf[ks][0] = row0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
-      qf[ks][1] = row1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
-      qf[ks][2] = row0 < qlen ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
-      qf[ks][3] = row1 < qlen ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
-    }
+    load_q_frags<KV8>(q0, q1, row0 < qlen, row1 < qlen, qf);
   }
   // allowed token ranges per row
   int hi0, hi1, lo0 = 0, lo1 = 0;
@@ -429,7 +547,7 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
     uint8_t* dst = smem + stg * kPfStageBytes;
     const int pg0 = page_lo + blk * kPfBlockPages;
     const int npg = min(kPfBlockPages, page_hi - pg0);
-    mbar_expect_tx(&bars[stg], npg * 2 * kPageBytes);
+    mbar_expect_tx(&bars[stg], npg * 2 * kTile);
     for (int j = 0; j < npg; ++j) {
       int page = bt[pg0 + j];
       if (page < 0 || page >= p.num_pages) {
@@ -438,11 +556,16 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
       }
       const int krow = ((page * 2 + 0) * p.n_kv_heads + kvh) * kPage;
       const int vrow = ((page * 2 + 1) * p.n_kv_heads + kvh) * kPage;
-      uint8_t* d = dst + j * 2 * kPageBytes;
-      tma_load_2d(d, &tmap_kv, &bars[stg], 0, krow);
-      tma_load_2d(d + 2048, &tmap_kv, &bars[stg], 64, krow);
-      tma_load_2d(d + 4096, &tmap_kv, &bars[stg], 0, vrow);
-      tma_load_2d(d + 6144, &tmap_kv, &bars[stg], 64, vrow);
+      uint8_t* d = dst + j * 2 * kTile;
+      if constexpr (KV8) {
+        tma_load_2d(d, &tmap_kv, &bars[stg], 0, krow);
+        tma_load_2d(d + 2048, &tmap_kv, &bars[stg], 0, vrow);
+      } else {
+        tma_load_2d(d, &tmap_kv, &bars[stg], 0, krow);
+        tma_load_2d(d + 2048, &tmap_kv, &bars[stg], 64, krow);
+        tma_load_2d(d + 4096, &tmap_kv, &bars[stg], 0, vrow);
+        tma_load_2d(d + 6144, &tmap_kv, &bars[stg], 64, vrow);
+      }
     }
   };
 
@@ -468,8 +591,8 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
     for (int j = 0; j < npg; ++j) {
       const int tok_base = (pg0 + j) * kPage;
       if (tok_base >= warp_hi) break;  // fully masked for every row of this warp
-      attend_page(qf, base + j * 2 * kPageBytes, base + j * 2 * kPageBytes + kPageBytes, tok_base, lo0, hi0, lo1,
-                  hi1, p.scale_log2, o, st);
+      attend_page<KV8>(qf, base + j * 2 * kTile, base + j * 2 * kTile + kTile, tok_base, lo0, hi0, lo1, hi1,
+                       p.scale_log2, o, st);
     }
     __syncthreads();
     if (threadIdx.x == 0 && blk + kPfStages < n_blocks) {
@@ -484,19 +607,42 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
     L0 += exp2f(sk - (st.m0 == -INFINITY ? 0.f : st.m0));
     L1 += exp2f(sk - (st.m1 == -INFINITY ? 0.f : st.m1));
   }
-  const float inv0 = L0 > 0.f ? 1.f / L0 : 0.f, inv1 = L1 > 0.f ? 1.f / L1 : 0.f;
+  const float vs = KV8 ? p.v_scale : 1.f;
+  const float inv0 = L0 > 0.f ? vs / L0 : 0.f, inv1 = L1 > 0.f ? vs / L1 : 0.f;
   __nv_bfloat16* o0 = p.out + (static_cast<long long>(qstart + row0) * p.n_q_heads + qh) * kHD;
   __nv_bfloat16* o1 = p.out + (static_cast<long long>(qstart + row1) * p.n_q_heads + qh) * kHD;
+  if constexpr (KV8) {
+    // n-tiles 2j / 2j+1 hold the even / odd features of block j: features 16j + 4t .. 4t+3 are
+    // (even[0], odd[0], even[1], odd[1])
 #pragma unroll
-  for (int dt = 0; dt < 16; ++dt) {
-    const int c = dt * 8 + (lane & 3) * 2;
-    if (row0 < qlen) *reinterpret_cast<uint32_t*>(o0 + c) = pack_bf16x2(o[dt][0] * inv0, o[dt][1] * inv0);
-    if (row1 < qlen) *reinterpret_cast<uint32_t*>(o1 + c) = pack_bf16x2(o[dt][2] * inv1, o[dt][3] * inv1);
+    for (int j = 0; j < 8; ++j) {
+      const int c = 16 * j + 4 * (lane & 3);
+      if (row0 < qlen) {
+        uint2 w;
+        w.x = pack_bf16x2(o[2 * j][0] * inv0, o[2 * j + 1][0] * inv0);
+        w.y = pack_bf16x2(o[2 * j][1] * inv0, o[2 * j + 1][1] * inv0);
+        *reinterpret_cast<uint2*>(o0 + c) = w;
+      }
+      if (row1 < qlen) {
+        uint2 w;
+        w.x = pack_bf16x2(o[2 * j][2] * inv1, o[2 * j + 1][2] * inv1);
+        w.y = pack_bf16x2(o[2 * j][3] * inv1, o[2 * j + 1][3] * inv1);
+        *reinterpret_cast<uint2*>(o1 + c) = w;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int dt = 0; dt < 16; ++dt) {
+      const int c = dt * 8 + (lane & 3) * 2;
+      if (row0 < qlen) *reinterpret_cast<uint32_t*>(o0 + c) = pack_bf16x2(o[dt][0] * inv0, o[dt][1] * inv0);
+      if (row1 < qlen) *reinterpret_cast<uint32_t*>(o1 + c) = pack_bf16x2(o[dt][2] * inv1, o[dt][3] * inv1);
+    }
   }
 }
 
-static int kv_tmap(CUtensorMap* t, const void* kv_cache, int num_pages, int n_kv_heads) {
+static int kv_tmap(CUtensorMap* t, const void* kv_cache, int num_pages, int n_kv_heads, bool fp8 = false) {
   const uint64_t rows = uint64_t(num_pages) * 2 * n_kv_heads * kPage;
+  if (fp8) return make_tmap_2d(t, kv_cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, kHD, kHD, kPage, 128);
   return make_tmap_2d(t, kv_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHD, kHD, kPage, 64);
 }
 
@@ -510,10 +656,12 @@ GLLM_API long long gllm_decode_scratch_floats(int batch, int n_q_heads, int max_
   return static_cast<long long>(batch) * n_q_heads * max_splits * (kHD + 1);
 }
 
-GLLM_API int gllm_paged_decode(const void* q, void* out, const void* kv_cache, int num_pages,
-                               const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
-                               int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
-                               float* scratch, int* counters, int window, const float* sinks, void* stream) {
+template <bool KV8>
+static int paged_decode_impl(const void* q, void* out, const void* kv_cache, int num_pages,
+                             const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
+                             int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
+                             float* scratch, int* counters, int window, const float* sinks, float kv_scale,
+                             void* stream) {
   if (n_q_heads % n_kv_heads != 0 || n_q_heads / n_kv_heads > 16) {
     set_last_error("paged_decode: group size %d/%d unsupported (must divide, <= 16)", n_q_heads, n_kv_heads);
     return -1;
@@ -523,13 +671,14 @@ GLLM_API int gllm_paged_decode(const void* q, void* out, const void* kv_cache, i
     return -1;
   }
   CUtensorMap t;
-  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads)) return -1;
+  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads, KV8)) return -1;
   DecodeParams p = {};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.out = static_cast<__nv_bfloat16*>(out);
   p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.max_blocks = max_blocks;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = scale * 1.4426950408889634f * (KV8 ? kv_scale : 1.f);
+  p.v_scale = KV8 ? kv_scale : 1.f;
   p.pages_per_split = pages_per_split > 0 ? pages_per_split : (1 << 30);
   p.max_splits = max_splits > 0 ? max_splits : 1;
   p.part_o = scratch;
@@ -538,14 +687,68 @@ GLLM_API int gllm_paged_decode(const void* q, void* out, const void* kv_cache, i
   p.err = gllm_error_word();
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         KV8 ? kDecSmem8 : kDecSmem);
     if (e != cudaSuccess) { set_last_error("paged_decode: %s", cudaGetErrorString(e)); return -1; }
     attr_set = true;
   }
   dim3 grid(p.max_splits, n_kv_heads, batch);
-  paged_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, (cudaStream_t)stream>>>(t, p);
+  paged_decode_kernel<KV8><<<grid, kDecWarps * 32, KV8 ? kDecSmem8 : kDecSmem, (cudaStream_t)stream>>>(t, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("paged_decode launch: %s", cudaGetErrorString(e)); return -1; }
+  return 0;
+}
+
+GLLM_API int gllm_paged_decode(const void* q, void* out, const void* kv_cache, int num_pages,
+                               const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
+                               int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
+                               float* scratch, int* counters, int window, const float* sinks, void* stream) {
+  return paged_decode_impl<false>(q, out, kv_cache, num_pages, block_tables, max_blocks, ctx_lens, batch, n_q_heads,
+                                  n_kv_heads, scale, pages_per_split, max_splits, scratch, counters, window, sinks,
+                                  1.f, stream);
+}
+// Same kernel over an fp8 (e4m3) cache of the same shape; cached value = stored byte * kv_scale.
+GLLM_API int gllm_paged_decode_fp8(const void* q, void* out, const void* kv_cache, int num_pages,
+                                   const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
+                                   int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
+                                   float* scratch, int* counters, int window, const float* sinks, float kv_scale,
+                                   void* stream) {
+  return paged_decode_impl<true>(q, out, kv_cache, num_pages, block_tables, max_blocks, ctx_lens, batch, n_q_heads,
+                                 n_kv_heads, scale, pages_per_split, max_splits, scratch, counters, window, sinks,
+                                 kv_scale, stream);
+}
+
+template <bool KV8>
+static int paged_prefill_impl(const void* q, void* out, const void* kv_cache, int num_pages,
+                              const int* block_tables, int max_blocks, const int* q_start, const int* q_len,
+                              const int* ctx_lens, int num_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
+                              float scale, int causal, int window, const float* sinks, float kv_scale, void* stream) {
+  if (n_q_heads % n_kv_heads != 0) {
+    set_last_error("paged_prefill: heads %d not divisible by kv heads %d", n_q_heads, n_kv_heads);
+    return -1;
+  }
+  CUtensorMap t;
+  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads, KV8)) return -1;
+  PrefillParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.q_start = q_start; p.q_len = q_len; p.ctx_lens = ctx_lens;
+  p.block_tables = block_tables; p.max_blocks = max_blocks;
+  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+  p.scale_log2 = scale * 1.4426950408889634f * (KV8 ? kv_scale : 1.f);
+  p.v_scale = KV8 ? kv_scale : 1.f;
+  p.num_pages = num_pages; p.window = window; p.causal = causal; p.sinks = sinks;
+  p.err = gllm_error_word();
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel<KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
+    if (e != cudaSuccess) { set_last_error("paged_prefill: %s", cudaGetErrorString(e)); return -1; }
+    attr_set = true;
+  }
+  dim3 grid((max_q_len + kPfRows - 1) / kPfRows, n_q_heads, num_seqs);
+  paged_prefill_kernel<KV8><<<grid, kPfWarps * 32, kPfSmem, (cudaStream_t)stream>>>(t, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
 
@@ -553,32 +756,17 @@ GLLM_API int gllm_paged_prefill(const void* q, void* out, const void* kv_cache, 
                                 const int* block_tables, int max_blocks, const int* q_start, const int* q_len,
                                 const int* ctx_lens, int num_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
                                 float scale, int causal, int window, const float* sinks, void* stream) {
-  if (n_q_heads % n_kv_heads != 0) {
-    set_last_error("paged_prefill: heads %d not divisible by kv heads %d", n_q_heads, n_kv_heads);
-    return -1;
-  }
-  CUtensorMap t;
-  if (kv_tmap(&t, kv_cache, num_pages, n_kv_heads)) return -1;
-  PrefillParams p = {};
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.q_start = q_start; p.q_len = q_len; p.ctx_lens = ctx_lens;
-  p.block_tables = block_tables; p.max_blocks = max_blocks;
-  p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  p.num_pages = num_pages; p.window = window; p.causal = causal; p.sinks = sinks;
-  p.err = gllm_error_word();
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
-    if (e != cudaSuccess) { set_last_error("paged_prefill: %s", cudaGetErrorString(e)); return -1; }
-    attr_set = true;
-  }
-  dim3 grid((max_q_len + kPfRows - 1) / kPfRows, n_q_heads, num_seqs);
-  paged_prefill_kernel<<<grid, kPfWarps * 32, kPfSmem, (cudaStream_t)stream>>>(t, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) { set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
-  return 0;
+  return paged_prefill_impl<false>(q, out, kv_cache, num_pages, block_tables, max_blocks, q_start, q_len, ctx_lens,
+                                   num_seqs, max_q_len, n_q_heads, n_kv_heads, scale, causal, window, sinks, 1.f, stream);
+}
+GLLM_API int gllm_paged_prefill_fp8(const void* q, void* out, const void* kv_cache, int num_pages,
+                                    const int* block_tables, int max_blocks, const int* q_start, const int* q_len,
+                                    const int* ctx_lens, int num_seqs, int max_q_len, int n_q_heads, int n_kv_heads,
+                                    float scale, int causal, int window, const float* sinks, float kv_scale,
+                                    void* stream) {
+  return paged_prefill_impl<true>(q, out, kv_cache, num_pages, block_tables, max_blocks, q_start, q_len, ctx_lens,
+                                  num_seqs, max_q_len, n_q_heads, n_kv_heads, scale, causal, window, sinks, kv_scale,
+                                  stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -639,7 +827,7 @@ GLLM_API int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.counters), g_noalloc_counters);
     if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.err), g_noalloc_err);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(paged_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+      e = cudaFuncSetAttribute(paged_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
     if (e != cudaSuccess) {
       set_last_error("paged_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
       return -1;
@@ -690,7 +878,7 @@ GLLM_API int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_
   p.counters = st.counters; p.num_pages = num_pages; p.window = window; p.sinks = sinks;
   p.err = st.err;
   dim3 grid(max_splits, n_kv_heads, batch);
-  paged_decode_kernel<<<grid, kDecWarps * 32, kDecSmem, s>>>(t, p);
+  paged_decode_kernel<false><<<grid, kDecWarps * 32, kDecSmem, s>>>(t, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("paged_decode_noalloc launch: %s", cudaGetErrorString(e));

@@ -29,6 +29,8 @@
 // `rowscale` is the RMSNorm-as-prologue trick: the norm weight is folded into B at load time and
 // the per-row rsqrt(mean(x²)+eps) is applied to the accumulator, using the partial sums of squares
 // that the producing kernel's epilogue left behind.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace gllm {
@@ -81,6 +83,8 @@ struct GemmParams {
   const float* q_norm_w;  // [128] or null
   const float* k_norm_w;  // [128] or null
   float qk_eps;
+  int kv_fp8;             // 1: kv_cache holds fp8 e4m3 bytes of the same shape, stored = value * kv_inv_scale (saturating)
+  float kv_inv_scale;
   // fused all-reduce (row-parallel GEMM across `ar_world` GPUs): every rank stores its bf16 partial
   // tiles in its own symmetric buffer as they retire; after the arrival barrier each rank pulls the
   // sum of all ranks' partials (multimem.ld_reduce through NVSwitch when a multicast mapping exists,
@@ -137,6 +141,21 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&
   }
 }
 
+// 32 floats -> 32 fp8 e4m3 bytes (saturating) at a 16-byte aligned address
+__device__ __forceinline__ void store_fp8x32(uint8_t* dst, const float (&v)[32], float inv_scale) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i] * inv_scale, v[4 * i + 1] * inv_scale),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2] * inv_scale, v[4 * i + 3] * inv_scale),
+                                                 __NV_SATFINITE, __NV_E4M3);
+    w[i] = lo | (hi << 16);
+  }
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Accumulator access for the epilogue: 32 consecutive fp32 columns of this thread's TMEM lane.
@@ -339,6 +358,7 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
         if (pos < 0 || pos >= p.max_pos) pos = 0;
         const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
         __nv_bfloat16* dst = nullptr;
+        uint8_t* dst8 = nullptr;     // fp8 cache row
         if (is_q) {
           dst = p.q_out + (static_cast<long long>(m) * p.n_q_heads + head) * 128;
         } else if (slot >= 0) {
@@ -348,10 +368,13 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
           } else {
             const int kvh = is_k ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads;
             const long long b2 = ((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh);
-            dst = p.kv_cache + (b2 * kPageTokens + off) * 128;
+            if (p.kv_fp8)
+              dst8 = reinterpret_cast<uint8_t*>(p.kv_cache) + (b2 * kPageTokens + off) * 128;
+            else
+              dst = p.kv_cache + (b2 * kPageTokens + off) * 128;
           }
         }
-        if (dst) {
+        if (dst || dst8) {
           float a[2], b[2];
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
@@ -365,8 +388,16 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
               b[j] = x1[j];
             }
           }
-          *reinterpret_cast<uint32_t*>(dst + lane * 2) = pack_bf16x2(a[0], a[1]);
-          *reinterpret_cast<uint32_t*>(dst + 64 + lane * 2) = pack_bf16x2(b[0], b[1]);
+          if (dst8) {
+            const float is = p.kv_inv_scale;
+            *reinterpret_cast<uint16_t*>(dst8 + lane * 2) = static_cast<uint16_t>(
+                __nv_cvt_float2_to_fp8x2(make_float2(a[0] * is, a[1] * is), __NV_SATFINITE, __NV_E4M3));
+            *reinterpret_cast<uint16_t*>(dst8 + 64 + lane * 2) = static_cast<uint16_t>(
+                __nv_cvt_float2_to_fp8x2(make_float2(b[0] * is, b[1] * is), __NV_SATFINITE, __NV_E4M3));
+          } else {
+            *reinterpret_cast<uint32_t*>(dst + lane * 2) = pack_bf16x2(a[0], a[1]);
+            *reinterpret_cast<uint32_t*>(dst + 64 + lane * 2) = pack_bf16x2(b[0], b[1]);
+          }
         }
       }
 }
@@ -1154,6 +1185,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (pos < 0 || pos >= p.max_pos) pos = 0;
             }
             __nv_bfloat16* dst = nullptr;
+            uint8_t* dst8 = nullptr;     // fp8 cache row
             if (row_ok) {
               if (is_q) {
                 dst = p.q_out + (static_cast<long long>(m) * p.n_q_heads + head) * 128;
@@ -1164,7 +1196,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 } else {
                   const int kvh = is_k ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads;
                   const long long base = ((static_cast<long long>(page) * 2 + (is_k ? 0 : 1)) * p.n_kv_heads + kvh);
-                  dst = p.kv_cache + (base * kPageTokens + off) * 128;
+                  if (p.kv_fp8)
+                    dst8 = reinterpret_cast<uint8_t*>(p.kv_cache) + (base * kPageTokens + off) * 128;
+                  else
+                    dst = p.kv_cache + (base * kPageTokens + off) * 128;
                 }
               }
             }
@@ -1182,12 +1217,20 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                   x0 += p.bias[head * 128 + c * 32 + j];
                   x1 += p.bias[head * 128 + 64 + c * 32 + j];
                 }
-                if (nw) {
-                  x0 *= inv_rms * nw[c * 32 + j];
-                  x1 *= inv_rms * nw[64 + c * 32 + j];
-                }
                 a[j] = x0;
                 b[j] = x1;
+              }
+              if (nw) {   // per-head norm weights as 16-byte loads (the same 128 floats for every row)
+                const float4* w0 = reinterpret_cast<const float4*>(nw + c * 32);
+                const float4* w1 = reinterpret_cast<const float4*>(nw + 64 + c * 32);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                  const float4 wa = __ldg(w0 + jj), wb = __ldg(w1 + jj);
+                  a[jj * 4 + 0] *= inv_rms * wa.x; a[jj * 4 + 1] *= inv_rms * wa.y;
+                  a[jj * 4 + 2] *= inv_rms * wa.z; a[jj * 4 + 3] *= inv_rms * wa.w;
+                  b[jj * 4 + 0] *= inv_rms * wb.x; b[jj * 4 + 1] *= inv_rms * wb.y;
+                  b[jj * 4 + 2] *= inv_rms * wb.z; b[jj * 4 + 3] *= inv_rms * wb.w;
+                }
               }
               if (is_q || is_k) {
                 // this row's 32 cos / sin values as 16-byte loads (table rows are 256 bytes, 128-byte aligned here)
@@ -1208,6 +1251,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               if (dst) {
                 store_bf16x32(dst + c * 32, a);
                 store_bf16x32(dst + 64 + c * 32, b);
+              } else if (dst8) {
+                store_fp8x32(dst8 + c * 32, a, p.kv_inv_scale);
+                store_fp8x32(dst8 + 64 + c * 32, b, p.kv_inv_scale);
               }
             }
           }
@@ -1823,12 +1869,19 @@ GLLM_API void gllm_gemm_set_trace_k(int k) { g_trace_k = k; }
 
 // Fused QKV projection for head_dim 128: rowscale -> per-head RMSNorm (optional) -> RoPE -> q buffer and
 // paged KV write.  B is [(Hq+2Hkv)*128, K] with q heads first, then k heads, then v heads.
-GLLM_API int gllm_gemm_bf16_qkv(const void* A, long long lda, const void* B, long long ldb, int M, int K,
-                                int n_q_heads, int n_kv_heads, void* q_out, void* kv_cache, int num_pages,
-                                const int* slot_mapping, const int* positions, const float* cos_table,
-                                const float* sin_table, int max_pos, const float* q_norm_w, const float* k_norm_w,
-                                float qk_eps, const float* row_ss_in, int ss_in_parts, float norm_inv_dim,
-                                float norm_eps, const float* bias, void* stream, int max_ctas, int force_splits) {
+static int gemm_qkv_impl(const void* A, long long lda, const void* B, long long ldb, int M, int K,
+                         int n_q_heads, int n_kv_heads, void* q_out, void* kv_cache, int num_pages,
+                         const int* slot_mapping, const int* positions, const float* cos_table,
+                         const float* sin_table, int max_pos, const float* q_norm_w, const float* k_norm_w,
+                         float qk_eps, const float* row_ss_in, int ss_in_parts, float norm_inv_dim,
+                         float norm_eps, const float* bias, float kv_inv_scale, void* stream, int max_ctas,
+                         int force_splits) {
+  // the epilogue reads the rope tables and the per-head norm weights with 16-byte loads
+  if (((reinterpret_cast<uintptr_t>(cos_table) | reinterpret_cast<uintptr_t>(sin_table) |
+        reinterpret_cast<uintptr_t>(q_norm_w) | reinterpret_cast<uintptr_t>(k_norm_w)) & 15) != 0) {
+    set_last_error("gemm_qkv: rope tables and q/k norm weights must be 16-byte aligned");
+    return -1;
+  }
   GemmParams p = {};
   p.M = M; p.N = (n_q_heads + 2 * n_kv_heads) * 128; p.K = K;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
@@ -1836,10 +1889,38 @@ GLLM_API int gllm_gemm_bf16_qkv(const void* A, long long lda, const void* B, lon
   p.num_pages = num_pages; p.slot_mapping = slot_mapping; p.positions = positions;
   p.cos_table = cos_table; p.sin_table = sin_table; p.max_pos = max_pos;
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.qk_eps = qk_eps;
+  p.kv_fp8 = kv_inv_scale > 0.f ? 1 : 0;
+  p.kv_inv_scale = kv_inv_scale;
   p.row_ss_in = row_ss_in; p.ss_in_parts = ss_in_parts; p.norm_inv_dim = norm_inv_dim; p.norm_eps = norm_eps;
   p.bias = bias;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_QKV, false>(A, lda, B, ldb, p.N, p, 128, (cudaStream_t)stream, max_ctas, force_splits);
+}
+GLLM_API int gllm_gemm_bf16_qkv(const void* A, long long lda, const void* B, long long ldb, int M, int K,
+                                int n_q_heads, int n_kv_heads, void* q_out, void* kv_cache, int num_pages,
+                                const int* slot_mapping, const int* positions, const float* cos_table,
+                                const float* sin_table, int max_pos, const float* q_norm_w, const float* k_norm_w,
+                                float qk_eps, const float* row_ss_in, int ss_in_parts, float norm_inv_dim,
+                                float norm_eps, const float* bias, void* stream, int max_ctas, int force_splits) {
+  return gemm_qkv_impl(A, lda, B, ldb, M, K, n_q_heads, n_kv_heads, q_out, kv_cache, num_pages, slot_mapping, positions,
+                       cos_table, sin_table, max_pos, q_norm_w, k_norm_w, qk_eps, row_ss_in, ss_in_parts, norm_inv_dim,
+                       norm_eps, bias, 0.f, stream, max_ctas, force_splits);
+}
+// Same with an fp8 (e4m3) KV cache of the same shape: K / V rows are stored as value / kv_scale (saturating).
+GLLM_API int gllm_gemm_bf16_qkv_fp8kv(const void* A, long long lda, const void* B, long long ldb, int M, int K,
+                                      int n_q_heads, int n_kv_heads, void* q_out, void* kv_cache, int num_pages,
+                                      const int* slot_mapping, const int* positions, const float* cos_table,
+                                      const float* sin_table, int max_pos, const float* q_norm_w, const float* k_norm_w,
+                                      float qk_eps, const float* row_ss_in, int ss_in_parts, float norm_inv_dim,
+                                      float norm_eps, const float* bias, float kv_scale, void* stream, int max_ctas,
+                                      int force_splits) {
+  if (!(kv_scale > 0.f)) {
+    set_last_error("gemm_qkv_fp8kv: kv_scale must be positive");
+    return -1;
+  }
+  return gemm_qkv_impl(A, lda, B, ldb, M, K, n_q_heads, n_kv_heads, q_out, kv_cache, num_pages, slot_mapping, positions,
+                       cos_table, sin_table, max_pos, q_norm_w, k_norm_w, qk_eps, row_ss_in, ss_in_parts, norm_inv_dim,
+                       norm_eps, bias, 1.0f / kv_scale, stream, max_ctas, force_splits);
 }
 
 // FP8 (e4m3) GEMM with per-row activation scale and per-column weight scale applied in the epilogue.

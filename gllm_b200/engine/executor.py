@@ -313,10 +313,14 @@ class LLMEngine:
                              max_q_len=int(plan.pf_q_len.max()), logits_rows=rows)
         self.stats["prefill_steps"] += 1
         self.stats["prefill_tokens"] += int(T)
-        if rows is None:
-            self.model.forward(batch, self.kv_caches, return_hidden=True)
-            return np.zeros(0, np.int32)
-        logits = self.model.forward(batch, self.kv_caches)
+        self.model.op_timer = getattr(self, "prefill_timer", None)   # utils.tracing.GraphTimer(eager=True) or None
+        try:
+            if rows is None:
+                self.model.forward(batch, self.kv_caches, return_hidden=True)
+                return np.zeros(0, np.int32)
+            logits = self.model.forward(batch, self.kv_caches)
+        finally:
+            self.model.op_timer = None
         self._all_greedy = bool((self.slot_params[last_slots, 0] <= 0).all())
         sl = torch.tensor(last_slots, dtype=torch.int64)
         params = torch.from_numpy(self.slot_params[last_slots]).to(dev)

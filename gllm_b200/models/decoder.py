@@ -68,8 +68,8 @@ class DecoderModel:
         self.last_stage = (cfg.num_layers - 1) in self.layer_ids
         self.kv_dtype = kv_dtype or dtype      # torch.float8_e4m3fn: half the cache bytes; value = stored * kv_scale
         self.kv_scale = float(kv_scale)
-        if self.kv_dtype == torch.float8_e4m3fn:
-            fused = False        # the fused QKV epilogue and the tensor-core attention kernels read / write bf16 pages
+        if self.kv_dtype == torch.float8_e4m3fn and cfg.head_dim != 128 and fused is None:
+            fused = False        # only the head_dim-128 kernels (fused QKV epilogue, TMA attention) have fp8-page variants
         self.weight_quant = weight_quant
         if weight_quant is not None:
             fused = False        # quantised linears run through the dequantising GEMM; epilogue fusions need bf16 weights
@@ -212,7 +212,7 @@ class DecoderModel:
                 ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
                              slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
                              sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
-                             row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias)
+                             row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 mark("qkv_gemm")
                 self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
                 mark("attention")

@@ -32,10 +32,13 @@ _SIGNATURES = {
     "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I, I]),
     "gllm_gemm_bf16_grouped": (I, [P, L, P, L, P, L, I, I, I, P, I, I, P, I]),
     "gllm_gemm_bf16_qkv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, P, I, I]),
+    "gllm_gemm_bf16_qkv_fp8kv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, F, P, I, I]),
     "gllm_gemm_fp8": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, P, I, I]),
     "gllm_decode_scratch_floats": (L, [I, I, I]),
     "gllm_paged_decode": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, P]),
     "gllm_paged_prefill": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, P]),
+    "gllm_paged_decode_fp8": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, F, P]),
+    "gllm_paged_prefill_fp8": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, F, P]),
     "gllm_embed_gather": (I, [P, P, I, I, F, P, P, I, P]),
     "gllm_rmsnorm": (I, [P, P, P, I, I, F, I, P, P, P, P]),
     "gllm_layernorm": (I, [P, P, P, P, I, I, F, P, P]),

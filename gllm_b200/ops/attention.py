@@ -89,11 +89,19 @@ def paged_decode(q, kv_cache, block_tables, ctx_lens, *, n_q, n_kv, scale=None, 
         out.copy_(attention_ref(q, _dequant_cache(kv_cache, kv_scale), block_tables, ar, ones, ctx_lens, n_q, n_kv, scale,
                                 True, window, sinks))
         return out
-    if D == 128 and kv_cache.dtype != torch.float8_e4m3fn:
+    if D == 128 and n_q // n_kv <= 16:
         max_blocks = block_tables.shape[1]
         if workspace is None:
             max_splits = max(1, (max_blocks + pages_per_split - 1) // pages_per_split)
             workspace = DecodeWorkspace(B, n_q, n_kv, max_splits, q.device)
+        if kv_cache.dtype == torch.float8_e4m3fn:     # same TMA / tensor-core kernel, fp8 pages converted in registers
+            rc = nv.lib().gllm_paged_decode_fp8(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
+                                                block_tables.data_ptr(), max_blocks, ctx_lens.data_ptr(), B, n_q, n_kv,
+                                                scale, pages_per_split, workspace.max_splits,
+                                                workspace.scratch.data_ptr(), workspace.counters.data_ptr(), window,
+                                                nv.ptr(sinks), float(kv_scale), nv.stream_ptr())
+            nv.check(rc, "paged_decode_fp8")
+            return out
         rc = nv.lib().gllm_paged_decode(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
                                         block_tables.data_ptr(), max_blocks, ctx_lens.data_ptr(), B, n_q, n_kv,
                                         scale, pages_per_split, workspace.max_splits, workspace.scratch.data_ptr(),
@@ -119,6 +127,13 @@ def paged_prefill(q, kv_cache, block_tables, q_start, q_len, ctx_lens, *, max_q_
                                 causal, window, sinks))
         return out
     S = q_len.shape[0]
+    if kv_cache.dtype == torch.float8_e4m3fn and D == 128:
+        rc = nv.lib().gllm_paged_prefill_fp8(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
+                                             block_tables.data_ptr(), block_tables.shape[1], q_start.data_ptr(),
+                                             q_len.data_ptr(), ctx_lens.data_ptr(), S, max_q_len, n_q, n_kv, scale,
+                                             1 if causal else 0, window, nv.ptr(sinks), float(kv_scale), nv.stream_ptr())
+        nv.check(rc, "paged_prefill_fp8")
+        return out
     if kv_cache.dtype == torch.float8_e4m3fn:
         if sinks is not None:
             raise NotImplementedError("attention sinks with an fp8 KV cache")

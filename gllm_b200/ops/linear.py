@@ -304,8 +304,10 @@ def kv_write_ref(kv_cache, k, v, slot_mapping, kv_scale: float = 1.0):
 
 
 def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, cos_t, sin_t, q_norm_w=None,
-             k_norm_w=None, qk_eps=1e-6, row_ss=None, norm_dim=0, eps=0.0, bias=None, max_ctas=0, splits=0):
-    """Fused QKV projection for head_dim 128. ``w_qkv`` rows: q heads, k heads, v heads."""
+             k_norm_w=None, qk_eps=1e-6, row_ss=None, norm_dim=0, eps=0.0, bias=None, max_ctas=0, splits=0,
+             kv_scale: float = 1.0):
+    """Fused QKV projection for head_dim 128. ``w_qkv`` rows: q heads, k heads, v heads. An fp8 (e4m3) ``kv_cache``
+    receives value / kv_scale."""
     M, K = a.shape
     D = 128
     if not a.is_cuda:
@@ -318,12 +320,20 @@ def gemm_qkv(a, w_qkv, *, n_q, n_kv, q_out, kv_cache, slot_mapping, positions, c
         q, k, v = qkv_post_ref(acc, n_q, n_kv, D, positions, cos_t, sin_t, q_norm_w, k_norm_w, qk_eps)
         q_out[:M].copy_(q.reshape(M, n_q * D).to(q_out.dtype))
         if slot_mapping is not None:
-            kv_write_ref(kv_cache, k, v, slot_mapping)
+            kv_write_ref(kv_cache, k, v, slot_mapping, kv_scale)
         return q_out
     _on_device(a, weight=w_qkv, q_out=q_out, kv_cache=kv_cache, slot_mapping=slot_mapping, positions=positions,
                cos=cos_t, sin=sin_t, q_norm=q_norm_w, k_norm=k_norm_w, row_ss=row_ss, bias=bias)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
     nv.ensure_splitk_workspace(a.device)
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        rc = nv.lib().gllm_gemm_bf16_qkv_fp8kv(
+            a.data_ptr(), a.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), M, K, n_q, n_kv, q_out.data_ptr(),
+            kv_cache.data_ptr(), kv_cache.shape[0], nv.ptr(slot_mapping), positions.data_ptr(), cos_t.data_ptr(),
+            sin_t.data_ptr(), cos_t.shape[0], nv.ptr(q_norm_w), nv.ptr(k_norm_w), qk_eps, nv.ptr(row_ss), parts,
+            1.0 / norm_dim if norm_dim else 0.0, eps, nv.ptr(bias), float(kv_scale), nv.stream_ptr(), max_ctas, splits)
+        nv.check(rc, "gemm_bf16_qkv_fp8kv")
+        return q_out
     rc = nv.lib().gllm_gemm_bf16_qkv(a.data_ptr(), a.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), M, K, n_q, n_kv,
                                      q_out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0], nv.ptr(slot_mapping),
                                      positions.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), cos_t.shape[0],

@@ -238,6 +238,9 @@ def run(op: str, iters: int):
             pps = int(os.environ.get("GLLM_ATTN_PPS", 1 << 20))
             pages = B * ctx // 16
             kv = torch.randn(pages, 2, nkv, 16, D, device=dev).to(torch.bfloat16)
+            fp8 = os.environ.get("GLLM_ATTN_FP8", "0") == "1"      # e4m3 cache, one byte per value
+            if fp8:
+                kv = (kv.float() / 0.05).to(torch.float8_e4m3fn)
             bt = torch.randperm(pages, device=dev).to(torch.int32).reshape(B, ctx // 16).contiguous()
             if os.environ.get("GLLM_ATTN_RAGGED", "0") == "1":
                 cl = torch.randint(128, ctx + 1, (B,), device=dev).to(torch.int32)
@@ -248,9 +251,9 @@ def run(op: str, iters: int):
             max_splits = max(1, -(-(ctx // 16) // pps))
             wsp = ops.DecodeWorkspace(B, nq, nkv, max_splits, dev)
             t = _time(lambda: ops.paged_decode(q, kv, bt, cl, n_q=nq, n_kv=nkv, out=o, workspace=wsp,
-                                               pages_per_split=pps), iters)
-            byts = int(cl.sum().item()) * 2 * nkv * D * 2
-            out.update(batch=B, ctx=ctx, n_q=nq, n_kv=nkv, pages_per_split=pps, us=t * 1e6, kv_gbs=byts / t / 1e9,
+                                               pages_per_split=pps, kv_scale=0.05), iters)
+            byts = int(cl.sum().item()) * 2 * nkv * D * kv.element_size()
+            out.update(batch=B, ctx=ctx, n_q=nq, n_kv=nkv, pages_per_split=pps, kv_dtype=str(kv.dtype).split(".")[-1], us=t * 1e6, kv_gbs=byts / t / 1e9,
                        frac_of_hbm_peak=byts / t / 1e9 / hbm)
         else:
             S, L = 8, 2048

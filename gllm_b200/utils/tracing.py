@@ -83,13 +83,17 @@ class GraphTimer:
     external event-record node when called during stream capture); ``results`` attributes the interval since the
     previous mark of the same capture to ``name``. Marks whose events did not fire in the last replay are skipped."""
 
-    def __init__(self):
+    def __init__(self, eager: bool = False):
         self.marks: List[tuple] = []
+        self.eager = eager      # also time eagerly launched steps (prefill chunks)
 
     def mark(self, name: str):
-        if not torch.cuda.is_available() or not torch.cuda.is_current_stream_capturing():
+        if not torch.cuda.is_available():
+            return
+        capturing = torch.cuda.is_current_stream_capturing()
+        if not capturing and not self.eager:
             return      # only the captured step is timed, not its eager warm-up
-        e = torch.cuda.Event(enable_timing=True, external=True)
+        e = torch.cuda.Event(enable_timing=True, external=capturing)
         e.record()
         self.marks.append((name, e))
 

@@ -94,3 +94,45 @@ def test_generic_attention_head_dim_64():
     out = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=33, n_q=n_q, n_kv=n_kv)
     ref = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5)
     _close(out, ref)
+
+
+def _fp8_cache(kv, scale):
+    """bf16 cache -> (fp8 cache, its dequantised fp32 values)."""
+    kv8 = (kv.float() / scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return kv8, kv8.float() * scale
+
+
+@pytest.mark.parametrize("n_q,n_kv,pps", [(8, 2, 32), (4, 1, 4), (32, 8, 8), (16, 1, 1000)])
+def test_paged_decode_fp8_cache(n_q, n_kv, pps):
+    """The TMA / tensor-core decode kernel over fp8 pages (fragments converted in registers) vs the reference run on the
+    dequantised cache."""
+    D = 128
+    ctx = [1, 16, 17, 100, 515, 2304, 33, 64]
+    kv, bt = _setup(ctx, n_kv, D, seed=3)
+    kv8, deq = _fp8_cache(kv, 0.05)
+    B = len(ctx)
+    q = torch.randn(B, n_q * D, device=DEV).to(torch.bfloat16)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    out = ops.paged_decode(q, kv8, bt, cl, n_q=n_q, n_kv=n_kv, pages_per_split=pps, kv_scale=0.05)
+    ar = torch.arange(B, dtype=torch.int32, device=DEV)
+    ref = ops.attention_ref(q, deq, bt, ar, torch.ones_like(cl), cl, n_q, n_kv, D ** -0.5)
+    _close(out, ref)
+    out2 = ops.paged_decode(q, kv8, bt, cl, n_q=n_q, n_kv=n_kv, pages_per_split=pps, kv_scale=0.05)
+    _close(out2, ref)
+
+
+@pytest.mark.parametrize("n_q,n_kv", [(8, 2), (4, 4)])
+def test_paged_prefill_fp8_cache(n_q, n_kv):
+    D = 128
+    ctx = [70, 200, 16, 333]
+    qlen = [70, 64, 16, 100]        # sequences 1 and 3 are later chunks over cached tokens
+    kv, bt = _setup(ctx, n_kv, D, seed=4)
+    kv8, deq = _fp8_cache(kv, 0.05)
+    T = sum(qlen)
+    q = torch.randn(T, n_q * D, device=DEV).to(torch.bfloat16)
+    qs = torch.tensor([0, 70, 134, 150], dtype=torch.int32, device=DEV)
+    ql = torch.tensor(qlen, dtype=torch.int32, device=DEV)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    out = ops.paged_prefill(q, kv8, bt, qs, ql, cl, max_q_len=max(qlen), n_q=n_q, n_kv=n_kv, kv_scale=0.05)
+    ref = ops.attention_ref(q, deq, bt, qs, ql, cl, n_q, n_kv, D ** -0.5)
+    _close(out, ref)

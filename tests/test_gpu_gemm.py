@@ -206,3 +206,34 @@ def test_large_m_kernels_with_and_without_cta_pairs():
             test_gemm_glu(3000, 1536, 1024, 256, 1, 0)
         finally:
             ops.set_pair_big_m(old)
+
+
+@pytest.mark.parametrize("M,splits", [(150, 0), (256, 3), (700, 0)])
+def test_gemm_qkv_fused_fp8_kv_cache(M, splits):
+    """The fused QKV epilogue writing an fp8 (e4m3) paged cache: value / kv_scale, saturating."""
+    torch.manual_seed(15)
+    K, n_q, n_kv, D = 1024, 8, 2, 128
+    pages, max_pos, kv_scale = 64, 512, 0.125
+    a = _rand(M, K)
+    w = _rand((n_q + 2 * n_kv) * D, K, scale=0.05)
+    ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+    qn, kn = torch.rand(D, device=DEV) + 0.5, torch.rand(D, device=DEV) + 0.5
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=DEV).double() / D))
+    ang = torch.arange(max_pos, device=DEV).double()[:, None] * inv[None]
+    cos_t, sin_t = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    positions = torch.randint(0, max_pos, (M,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * 16, device=DEV)[:M].to(torch.int32)
+    slots[3] = -1
+    kv = torch.zeros(pages, 2, n_kv, 16, D, device=DEV, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    q_out = torch.zeros(M, n_q * D, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_qkv(a, w, n_q=n_q, n_kv=n_kv, q_out=q_out, kv_cache=kv, slot_mapping=slots, positions=positions,
+                 cos_t=cos_t, sin_t=sin_t, q_norm_w=qn, k_norm_w=kn, qk_eps=1e-6, row_ss=ss, norm_dim=K, eps=1e-6,
+                 splits=splits, kv_scale=kv_scale)
+    acc = (a.float() @ w.float().t()) * torch.rsqrt(ss / K + 1e-6)
+    q, k, v = L.qkv_post_ref(acc, n_q, n_kv, D, positions, cos_t, sin_t, qn, kn, 1e-6)
+    _close(q_out, q.reshape(M, -1))
+    kv_ref = torch.zeros_like(kv)
+    L.kv_write_ref(kv_ref, k, v, slots, kv_scale)
+    got, ref = kv.float() * kv_scale, kv_ref.float() * kv_scale
+    assert (got - ref).abs().max().item() <= 0.13 * ref.abs().max().item()      # at most one e4m3 step apart
+    assert torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item() > 0.999
