@@ -148,20 +148,35 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
       mma_bf16_16816(s[1], qf[ks], b2, b3);
     }
   }
-  // mask + scale (log2 domain)
+  // mask + scale (log2 domain); pages that every row of the warp may attend in full skip the mask tests
   float mx0 = -INFINITY, mx1 = -INFINITY;
+  const bool whole = __all_sync(0xffffffffu, tok_base >= lo0 && tok_base >= lo1 && tok_base + kPage <= hi0 &&
+                                                 tok_base + kPage <= hi1);
+  if (whole) {
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int t = tok_base + nt * 8 + (lane & 3) * 2 + e;
-      float v0 = s[nt][e] * scale_log2, v1 = s[nt][2 + e] * scale_log2;
-      if (t < lo0 || t >= hi0) v0 = -INFINITY;
-      if (t < lo1 || t >= hi1) v1 = -INFINITY;
-      s[nt][e] = v0;
-      s[nt][2 + e] = v1;
-      mx0 = fmaxf(mx0, v0);
-      mx1 = fmaxf(mx1, v1);
+      for (int e = 0; e < 2; ++e) {
+        s[nt][e] *= scale_log2;
+        s[nt][2 + e] *= scale_log2;
+        mx0 = fmaxf(mx0, s[nt][e]);
+        mx1 = fmaxf(mx1, s[nt][2 + e]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int t = tok_base + nt * 8 + (lane & 3) * 2 + e;
+        float v0 = s[nt][e] * scale_log2, v1 = s[nt][2 + e] * scale_log2;
+        if (t < lo0 || t >= hi0) v0 = -INFINITY;
+        if (t < lo1 || t >= hi1) v1 = -INFINITY;
+        s[nt][e] = v0;
+        s[nt][2 + e] = v1;
+        mx0 = fmaxf(mx0, v0);
+        mx1 = fmaxf(mx1, v1);
+      }
     }
   }
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));

@@ -136,11 +136,15 @@ def run(op: str, iters: int):
         o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         i = [0]
         glu = os.environ.get("GLLM_DEC_EPI", "residual") == "glu"    # N counts gate + up rows then
+        store32 = os.environ.get("GLLM_DEC_EPI", "residual") == "store_f32"   # the lm_head: fp32 logits
         ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+        o32 = torch.empty(M, N, device=dev, dtype=torch.float32) if store32 else None
 
         def f():
             i[0] = (i[0] + 1) % 3
-            if glu:
+            if store32:
+                ops.gemm(a, ws[i[0]], out=o32, out_dtype=torch.float32, row_ss=ss, norm_dim=K, eps=1e-6, bn=bn, splits=sp)
+            elif glu:
                 ops.gemm_glu(a, ws[i[0]], out=o[:, :N // 2], row_ss=ss, norm_dim=K, eps=1e-6, bn=bn, splits=sp)
             else:
                 ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
