@@ -124,7 +124,25 @@ __device__ __forceinline__ float row_scale_of(const GemmParams& p, int m) {
   if (p.row_ss_in == nullptr) return 1.0f;
   float ss = 0.f;
   const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
-  for (int i = 0; i < p.ss_in_parts; ++i) ss += src[i];
+  if ((p.ss_in_parts & 3) == 0 && (reinterpret_cast<uintptr_t>(p.row_ss_in) & 15) == 0) {
+    for (int i = 0; i < p.ss_in_parts; i += 4) {   // 16-byte loads: a row has up to hidden/128 partial sums
+      const float4 f = *reinterpret_cast<const float4*>(src + i);
+      ss += (f.x + f.y) + (f.z + f.w);
+    }
+  } else {
+    for (int i = 0; i < p.ss_in_parts; ++i) ss += src[i];
+  }
+  return rsqrtf(ss * p.norm_inv_dim + p.norm_eps);
+}
+// The same for a whole warp working on one row: the partial sums are spread over the lanes (one load + a warp
+// reduction instead of up to 32 dependent loads per unit; measured: the QKV reduce phase of the serving step went
+// from 45.6 k clocks with 32 partials per row).
+__device__ __forceinline__ float row_scale_warp(const GemmParams& p, int m, int lane) {
+  if (p.row_ss_in == nullptr) return 1.0f;
+  const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
+  float ss = 0.f;
+  for (int i = lane; i < p.ss_in_parts; i += 32) ss += __ldg(src + i);
+  ss = warp_sum(ss);
   return rsqrtf(ss * p.norm_inv_dim + p.norm_eps);
 }
 
@@ -258,10 +276,30 @@ __device__ __forceinline__ float2 ldcg2(const float* p) { return __ldcg(reinterp
 
 // The fused epilogue of EPI for one (row m, n tile) unit whose summed accumulator values a lane holds in v
 // (lane -> column mapping as in splitk_reduce_phase). Shared by the global-memory and the cluster reduce phases.
+// Inputs of the QKV epilogue of one unit that the reduce phases fetch ahead of time for all the units they keep in
+// flight: position and cache slot of the row, and this lane's two cos / sin pairs. Without it every unit pays two
+// dependent L2 round trips (row -> position -> rope table) after its partial sums arrived, one unit after the other
+// (measured: 43 k clocks for the QKV reduce phase of the serving step against 9.6 k for the residual one).
+struct QkvPre {
+  int pos, slot;
+  float2 cs, sn;
+};
+__device__ __forceinline__ void qkv_pre_row(const GemmParams& p, int m, QkvPre& q) {
+  int pos = __ldg(p.positions + m);
+  if (pos < 0 || pos >= p.max_pos) pos = 0;
+  q.pos = pos;
+  q.slot = p.slot_mapping ? __ldg(p.slot_mapping + m) : -1;
+}
+__device__ __forceinline__ void qkv_pre_rope(const GemmParams& p, int lane, QkvPre& q) {
+  q.cs = __ldg(reinterpret_cast<const float2*>(p.cos_table + static_cast<long long>(q.pos) * 64 + lane * 2));
+  q.sn = __ldg(reinterpret_cast<const float2*>(p.sin_table + static_cast<long long>(q.pos) * 64 + lane * 2));
+}
+
 template <int BN, int EPI, int NV, int SEGW>
 __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, int n_blk, int lane, float (&v)[NV],
-                                                    const uint2* pre_residual = nullptr) {
-      float rs = row_scale_of(p, m);
+                                                    const uint2* pre_residual = nullptr,
+                                                    const QkvPre* qpre = nullptr) {
+      float rs = row_scale_warp(p, m, lane);   // every lane of the warp is here with the same row
       if (p.a_scale) rs *= p.a_scale[m];
       if constexpr (EPI == EPI_STORE || EPI == EPI_RESIDUAL) {
         const int n0 = n_blk * BN + lane * NV;
@@ -339,8 +377,8 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
         if (p.bias) {
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            x0[j] += p.bias[head * 128 + lane * 2 + j];
-            x1[j] += p.bias[head * 128 + 64 + lane * 2 + j];
+            x0[j] += __ldg(p.bias + head * 128 + lane * 2 + j);
+            x1[j] += __ldg(p.bias + head * 128 + 64 + lane * 2 + j);
           }
         }
         const float* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
@@ -350,13 +388,18 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
           const float inv_rms = rsqrtf(ss * (1.0f / 128.0f) + p.qk_eps);
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
-            x0[j] *= inv_rms * nw[lane * 2 + j];
-            x1[j] *= inv_rms * nw[64 + lane * 2 + j];
+            x0[j] *= inv_rms * __ldg(nw + lane * 2 + j);
+            x1[j] *= inv_rms * __ldg(nw + 64 + lane * 2 + j);
           }
         }
-        int pos = p.positions[m];
-        if (pos < 0 || pos >= p.max_pos) pos = 0;
-        const int slot = p.slot_mapping ? p.slot_mapping[m] : -1;
+        QkvPre qp;
+        if (qpre) {
+          qp = *qpre;
+        } else {
+          qkv_pre_row(p, m, qp);
+          qkv_pre_rope(p, lane, qp);
+        }
+        const int slot = qp.slot;
         __nv_bfloat16* dst = nullptr;
         uint8_t* dst8 = nullptr;     // fp8 cache row
         if (is_q) {
@@ -379,8 +422,8 @@ __device__ __forceinline__ void apply_unit_epilogue(const GemmParams& p, int m, 
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             if (is_q || is_k) {
-              const float cs = p.cos_table[static_cast<long long>(pos) * 64 + lane * 2 + j];
-              const float sn = p.sin_table[static_cast<long long>(pos) * 64 + lane * 2 + j];
+              const float cs = j == 0 ? qp.cs.x : qp.cs.y;
+              const float sn = j == 0 ? qp.sn.x : qp.sn.y;
               a[j] = x0[j] * cs - x1[j] * sn;
               b[j] = x1[j] * cs + x0[j] * sn;
             } else {
@@ -437,10 +480,20 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
        u0 += gridDim.x * warps_per_cta * U) {
     float acc[U][NV];
     float* base[U];
+    QkvPre qpre[kQkv ? U : 1];
+    constexpr bool kPreRes = (EPI == EPI_RESIDUAL && NV == 4);
+    uint2 pre_res[kPreRes ? U : 1];     // the residual values travel with the partial sums, not unit after unit
 #pragma unroll
     for (int k = 0; k < U; ++k) {
       const int u = min(u0 + k, units - 1);
       base[k] = src_base + static_cast<long long>(u / p.num_n) * n_pad + static_cast<long long>(u % p.num_n) * BN;
+      if constexpr (kQkv) qkv_pre_row(p, u / p.num_n, qpre[k]);   // in flight together with the partial sums
+      if constexpr (kPreRes) {
+        const int n0 = (u % p.num_n) * BN + lane * 4;
+        pre_res[k] = make_uint2(0u, 0u);
+        if (n0 < p.N)
+          pre_res[k] = *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(u / p.num_n) * p.ldr + n0);
+      }
 #pragma unroll
       for (int j = 0; j < NV; ++j) acc[k][j] = 0.f;
     }
@@ -463,6 +516,12 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
               tmp[ds][k][g * 2 + 0] = f.x; tmp[ds][k][g * 2 + 1] = f.y;
             }
           }
+        }
+      }
+      if constexpr (kQkv) {
+        if (s0 == 0) {   // the positions have arrived by now; the rope rows travel while the partial sums are added
+#pragma unroll
+          for (int k = 0; k < U; ++k) qkv_pre_rope(p, lane, qpre[k]);
         }
       }
 #pragma unroll
@@ -498,7 +557,8 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
       float v[NV];
 #pragma unroll
       for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
-      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v);
+      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v, kPreRes ? &pre_res[k] : nullptr,
+                                             kQkv ? &qpre[k] : nullptr);
     }
   }
 }
@@ -521,10 +581,14 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
        u0 += gridDim.x * warps_per_cta * U) {
     float acc[U][8];
     long long off[U];
+    uint4 res[U];     // residual rows: requested before the pull so that they do not cost a round trip per unit
 #pragma unroll
     for (int k = 0; k < U; ++k) {
       const int u = min(u0 + k, units - 1);
       off[k] = buf_off + static_cast<long long>(u / groups) * n_pad + static_cast<long long>(u % groups) * 256 + lane * 8;
+      const int n0 = (u % groups) * 256 + lane * 8;
+      res[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (n0 < p.N) res[k] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(u / groups) * p.ldr + n0);
     }
 #pragma unroll
     for (int k = 0; k < U; ++k)
@@ -599,7 +663,7 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
           v[j] = acc[k][j];
           if (p.bias) v[j] += p.bias[n0 + j];
         }
-        const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+        const uint4 rr = res[k];
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -709,6 +773,7 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
   for (int r0 = r_begin + warp; r0 < r_end; r0 += nwarps * U) {
     float acc[U][NV];
     uint2 pre[U];
+    QkvPre qpre[kQkv ? U : 1];
     const float* gbase[U];
 #pragma unroll
     for (int k = 0; k < U; ++k) {
@@ -718,6 +783,7 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
       const int r = min(r0 + k * nwarps, r_end - 1);
       const int m = min(m_row0 + r, p.M - 1);
       gbase[k] = p.sk_scratch + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN;
+      if constexpr (kQkv) qkv_pre_row(p, m, qpre[k]);
       if constexpr (EPI == EPI_RESIDUAL) {   // ask for the residual together with the partials
         const int n0 = n_blk * BN + lane * 4;
         if (n0 < p.N) pre[k] = *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
@@ -755,6 +821,12 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
           }
         }
       }
+      if constexpr (kQkv) {
+        if (s0 == 0) {
+#pragma unroll
+          for (int k = 0; k < U; ++k) qkv_pre_rope(p, lane, qpre[k]);
+        }
+      }
 #pragma unroll
       for (int ds = 0; ds < SU; ++ds) {
         if (s0 + ds < S) {
@@ -774,7 +846,8 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
       float v[NV];
 #pragma unroll
       for (int j = 0; j < NV; ++j) v[j] = acc[k][j];
-      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v, EPI == EPI_RESIDUAL ? &pre[k] : nullptr);
+      apply_unit_epilogue<BN, EPI, NV, SEGW>(p, m, n_blk, lane, v, EPI == EPI_RESIDUAL ? &pre[k] : nullptr,
+                                             kQkv ? &qpre[k] : nullptr);
     }
   }
 }
@@ -1359,6 +1432,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // ---------------------------------------------------------------------------------------------
 static long long* g_trace_ptr = nullptr;
 static int g_trace_k = 0;   // when non-zero only launches with this K are traced
+static int g_trace_n = 0;   // likewise for N
 
 struct SplitKWorkspace {
   float* scratch = nullptr;
@@ -1414,7 +1488,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     set_last_error("gemm: N=%d must be a multiple of 32 (pad the weight at load time)", p.N);
     return -1;
   }
-  p.trace = (g_trace_k == 0 || g_trace_k == p.K) ? g_trace_ptr : nullptr;
+  p.trace = ((g_trace_k == 0 || g_trace_k == p.K) && (g_trace_n == 0 || g_trace_n == p.N)) ? g_trace_ptr : nullptr;
   p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1575,7 +1649,7 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
     set_last_error("gemm (pair): bad problem M=%d N=%d K=%d", p.M, p.N, p.K);
     return -1;
   }
-  p.trace = (g_trace_k == 0 || g_trace_k == p.K) ? g_trace_ptr : nullptr;
+  p.trace = ((g_trace_k == 0 || g_trace_k == p.K) && (g_trace_n == 0 || g_trace_n == p.N)) ? g_trace_ptr : nullptr;
   p.num_m = (p.M + 2 * kBM - 1) / (2 * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1666,6 +1740,18 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
     bool use_pair = p.M > 128 && p.M <= pair_max_m && ((g_pair_epi_mask >> EPI) & 1) && p.mblk_group == nullptr &&
                     p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0;
     if (EPI == EPI_GLU && g_pair_epi_mask != 0xF && bn < 192) use_pair = false;   // narrow GLU tiles: single CTAs win
+    if (EPI == EPI_GLU && !use_pair && g_pair_max_m > 0 && p.M > 128 && p.M <= g_pair_max_m && bn >= 192 &&
+        p.mblk_group == nullptr && p.ar_world == 0 && max_ctas <= 0) {
+      // gate/up shards of a tensor-parallel rank: when all tiles fit in one round of CTA pairs the pairs win (64 tiles
+      // of 192 columns at two ranks: 51 vs 62 us per layer); with 128 tiles (one GPU) the single-CTA wave is ahead
+      static int sms = 0;
+      if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      }
+      if ((p.N + bn - 1) / bn <= sms / 2) use_pair = true;
+    }
     if (EPI != EPI_QKV && bn == 256 && g_pair_big_m > 0 && p.M >= g_pair_big_m && p.mblk_group == nullptr &&
         p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0)
       use_pair = true;
@@ -1866,6 +1952,7 @@ GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const 
 // done, main loop left, split-K barrier passed, exit. Pass null to switch it off.
 GLLM_API void gllm_gemm_set_trace(long long* buf) { g_trace_ptr = buf; }
 GLLM_API void gllm_gemm_set_trace_k(int k) { g_trace_k = k; }
+GLLM_API void gllm_gemm_set_trace_n(int n) { g_trace_n = n; }
 
 // Fused QKV projection for head_dim 128: rowscale -> per-head RMSNorm (optional) -> RoPE -> q buffer and
 // paged KV write.  B is [(Hq+2Hkv)*128, K] with q heads first, then k heads, then v heads.

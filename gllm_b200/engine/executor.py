@@ -181,7 +181,8 @@ class LLMEngine:
         key = (B, self._all_greedy)
         keep = self.graphs.get(key)
         self.model.op_timer = GraphTimer()
-        trace_k = int(os.environ.get("GLLM_TRACE_K", "0"))   # also stamp the phases of the GEMMs with this K
+        trace_k = int(os.environ.get("GLLM_TRACE_K", "0"))   # also stamp the phases of the GEMMs with this K (and N)
+        trace_n = int(os.environ.get("GLLM_TRACE_N", "0"))
         trace = None
         if trace_k:
             import ctypes
@@ -192,7 +193,10 @@ class LLMEngine:
             lib.gllm_gemm_set_trace_k.argtypes = [ctypes.c_int]
             lib.gllm_gemm_set_trace_k.restype = None
             trace = torch.zeros(9, dtype=torch.int64, device=self.device)
+            lib.gllm_gemm_set_trace_n.argtypes = [ctypes.c_int]
+            lib.gllm_gemm_set_trace_n.restype = None
             lib.gllm_gemm_set_trace_k(trace_k)
+            lib.gllm_gemm_set_trace_n(trace_n)
             lib.gllm_gemm_set_trace(trace.data_ptr())
         try:
             g = self._capture(B)
@@ -206,6 +210,7 @@ class LLMEngine:
             if trace is not None:
                 lib.gllm_gemm_set_trace(None)
                 lib.gllm_gemm_set_trace_k(0)
+                lib.gllm_gemm_set_trace_n(0)
             self.model.op_timer = None
             if keep is not None:
                 self.graphs[key] = keep
