@@ -94,8 +94,10 @@ struct GemmParams {
   __nv_bfloat16* ar_peer_buf[8];          // unicast addresses (index = rank); [ar_rank] is local
   unsigned long long* ar_mc_counter;      // multicast address of the arrival counter, or null
   unsigned long long* ar_peer_counter[8];
-  unsigned long long* ar_state;           // local {expected rank arrivals, launch index, CTA arrivals, expected CTA arrivals}
+  unsigned long long* ar_state;           // local {expected rank arrivals, launch index, CTA arrivals, expected CTA
+                                          // arrivals, expected rank arrivals of the second meeting}
   int ar_rank;
+  int ar_two_shot;                        // 1: reduce-scatter + broadcast through the result region at 2 * ar_buf_elems
   long long ar_buf_elems;                 // elements of one partial buffer (two alternate per launch)
   // row scatter (expert-parallel return path): output row m goes to scatter_peer[meta >> 24] + (meta & 0xFFFFFF) * ldo
   // where meta = scatter_meta[m]; a negative meta drops the row. The stores go straight into the token owner's
@@ -209,23 +211,28 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned 
 // every rank (one multimem.red, or one red per peer); everybody then waits until the own rank's counter has reached
 // `target`. Bounded; returns false on timeout.
 __device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long long target,
-                                           unsigned long long local_target) {
+                                           unsigned long long local_target, int word = 0) {
+  // `word` selects one of two adjacent arrival counters: the two-shot form meets twice per launch and keeps the
+  // rounds on separate words, so an early second-round arrival can never stand in for a late first-round one.
   __shared__ int ok_flag;
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    __threadfence();
+    if (word)
+      __threadfence_system();   // second meeting: this CTA's stores went to the other GPUs' memory
+    else
+      __threadfence();
     const unsigned long long prev = atomicAdd(p.ar_state + 2, 1ull);
     if (prev + 1ull == local_target) {
       __threadfence_system();
       if (p.ar_mc_counter) {
-        asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_mc_counter), "l"(1ull) : "memory");
+        asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_mc_counter + word), "l"(1ull) : "memory");
       } else {
         for (int r = 0; r < p.ar_world; ++r)
-          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_peer_counter[r]), "l"(1ull) : "memory");
+          asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p.ar_peer_counter[r] + word), "l"(1ull) : "memory");
       }
     }
-    const unsigned long long* mine = p.ar_peer_counter[p.ar_rank];
+    const unsigned long long* mine = p.ar_peer_counter[p.ar_rank] + word;
     const unsigned long long t0 = globaltimer_ns();
     unsigned int spins = 0;
     while (ld_acquire_sys_u64(mine) < target) {
@@ -504,6 +511,13 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
         const int s = min(s0 + ds, nsplits - 1);
 #pragma unroll
         for (int k = 0; k < U; ++k) {
+          if constexpr (kQkv) {
+            if (p.park) {   // parked tiles were published with the two 64-column halves interleaved per lane
+              const float4 f = ldcg4(base[k] + s * split_stride + lane * 4);
+              tmp[ds][k][0] = f.x; tmp[ds][k][1] = f.y; tmp[ds][k][2] = f.z; tmp[ds][k][3] = f.w;
+              continue;
+            }
+          }
 #pragma unroll
           for (int g = 0; g < NSEG; ++g) {
             const float* src = base[k] + s * split_stride + seg_off[g];
@@ -569,14 +583,24 @@ __device__ void splitk_reduce_phase(const GemmParams& p, float* src_base, int ns
 // the row statistics for the next norm.
 // When the rank split K locally (`nsplits` partial buffers, `split_elems` apart) every split is pulled and added in
 // split order, identically on every rank.
-template <int BN>
-__device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nsplits, long long split_elems) {
-  constexpr int U = 4;
+// Two-shot form (bcast_off >= 0): the call covers only rows [row_lo, row_hi), this rank's share, and every finished
+// 16-byte piece is also stored into the result region of every rank (one multimem.st, or one store per peer), from
+// where ar_gather_phase copies the other ranks' rows after a second barrier. Each rank then pulls 1/W of the output
+// instead of all of it (at eight ranks the one-shot pull reads 8 x 2 MB out of every GPU per GEMM).
+__device__ __forceinline__ void multimem_st_b128(__nv_bfloat16* mc, const uint4& w) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(w.x), "r"(w.y),
+               "r"(w.z), "r"(w.w)
+               : "memory");
+}
+template <int BN, int U>
+__device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nsplits, long long split_elems, int row_lo,
+                                int row_hi, long long bcast_off) {
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   const long long n_pad = static_cast<long long>(p.num_n) * BN;
   const int groups = static_cast<int>(n_pad / 256);
-  const int units = p.M * groups;
+  const int units = (row_hi - row_lo) * groups;
+  if (units <= 0) return;
   for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
        u0 += gridDim.x * warps_per_cta * U) {
     float acc[U][8];
@@ -585,10 +609,11 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
 #pragma unroll
     for (int k = 0; k < U; ++k) {
       const int u = min(u0 + k, units - 1);
-      off[k] = buf_off + static_cast<long long>(u / groups) * n_pad + static_cast<long long>(u % groups) * 256 + lane * 8;
+      const int mrow = row_lo + u / groups;
+      off[k] = buf_off + static_cast<long long>(mrow) * n_pad + static_cast<long long>(u % groups) * 256 + lane * 8;
       const int n0 = (u % groups) * 256 + lane * 8;
       res[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (n0 < p.N) res[k] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(u / groups) * p.ldr + n0);
+      if (n0 < p.N) res[k] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(mrow) * p.ldr + n0);
     }
 #pragma unroll
     for (int k = 0; k < U; ++k)
@@ -653,7 +678,7 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
     for (int k = 0; k < U; ++k) {
       const int u = u0 + k;
       if (u >= units) continue;
-      const int m = u / groups, grp = u % groups;
+      const int m = row_lo + u / groups, grp = u % groups;
       const int n0 = grp * 256 + lane * 8;
       float ss = 0.f;
       if (n0 < p.N) {
@@ -670,7 +695,7 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
           const float2 f = __bfloat1622float2(h[e]);
           v[2 * e] = bf16_round(v[2 * e] + f.x);
           v[2 * e + 1] = bf16_round(v[2 * e + 1] + f.y);
-          ss += v[2 * e] * v[2 * e] + v[2 * e + 1] * v[2 * e + 1];
+          ss = fmaf(v[2 * e], v[2 * e], fmaf(v[2 * e + 1], v[2 * e + 1], ss));   // same order in ar_gather_phase
         }
         uint4 w;
         w.x = pack_bf16x2(v[0], v[1]);
@@ -678,9 +703,66 @@ __device__ void ar_reduce_phase(const GemmParams& p, long long buf_off, int nspl
         w.z = pack_bf16x2(v[4], v[5]);
         w.w = pack_bf16x2(v[6], v[7]);
         *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0) = w;
+        if (bcast_off >= 0) {
+          const long long roff = bcast_off + static_cast<long long>(m) * n_pad + n0;
+          if (p.ar_mc_buf) {
+            multimem_st_b128(p.ar_mc_buf + roff, w);
+          } else {
+            for (int r = 0; r < p.ar_world; ++r)
+              if (r != p.ar_rank) *reinterpret_cast<uint4*>(p.ar_peer_buf[r] + roff) = w;
+          }
+        }
       }
       ss = warp_sum(ss);
       if (p.row_ss_out && lane == 0) p.row_ss_out[static_cast<long long>(m) * groups + grp] = ss;
+    }
+  }
+}
+
+// Second half of the two-shot form: rows finished by the other ranks are copied from this GPU's result region into
+// the output, with their row statistics (the same bf16 values, so every rank ends up with identical numbers).
+template <int BN>
+__device__ void ar_gather_phase(const GemmParams& p, long long bcast_off, int own_lo, int own_hi) {
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const int groups = static_cast<int>(n_pad / 256);
+  const int other_rows = p.M - (own_hi - own_lo);
+  const int units = other_rows * groups;
+  const __nv_bfloat16* src = p.ar_peer_buf[p.ar_rank] + bcast_off;
+  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
+       u0 += gridDim.x * warps_per_cta * U) {
+    uint4 w[U];
+    int mr[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      int m = u / groups;
+      if (m >= own_lo) m += own_hi - own_lo;     // skip this rank's own rows
+      mr[k] = m;
+      const int n0 = (u % groups) * 256 + lane * 8;
+      w[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (n0 < p.N) w[k] = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<long long>(m) * n_pad + n0));
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = u0 + k;
+      if (u >= units) continue;
+      const int grp = u % groups;
+      const int n0 = grp * 256 + lane * 8;
+      float ss = 0.f;
+      if (n0 < p.N) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+        }
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(mr[k]) * p.ldo + n0) = w[k];
+      }
+      ss = warp_sum(ss);
+      if (p.row_ss_out && lane == 0) p.row_ss_out[static_cast<long long>(mr[k]) * groups + grp] = ss;
     }
   }
 }
@@ -727,8 +809,10 @@ __device__ __forceinline__ void cluster_row_range(int rows, int S, int rank, int
 
 // part: this CTA's partial tile [rows][kClusterPartStride] fp32 in shared memory. Writes every row that another
 // member finishes to scratch[ks][m][n_pad] (one warp per row: 512 contiguous bytes per store instruction).
+// halves_interleaved: a lane's float4 holds columns (2l, 2l+1, 64+2l, 64+2l+1) instead of (4l .. 4l+3): the layout in
+// which the QKV reduce phase wants its RoPE pairs, so that it reads one 16-byte piece per lane instead of two 8-byte ones.
 __device__ void cluster_publish_partials(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int S,
-                                         int ks, bool skip_own = true) {
+                                         int ks, bool skip_own = true, bool halves_interleaved = false) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const long long n_pad = static_cast<long long>(p.num_n) * 128;
   int own_b = 0, own_e = 0;
@@ -738,7 +822,14 @@ __device__ void cluster_publish_partials(const GemmParams& p, const float* part,
     if (r >= own_b && r < own_e) continue;
     const int m = m_row0 + r;
     if (m >= p.M) continue;
-    const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    float4 v;
+    if (halves_interleaved) {
+      const float2 a = *reinterpret_cast<const float2*>(part + r * kClusterPartStride + lane * 2);
+      const float2 b = *reinterpret_cast<const float2*>(part + r * kClusterPartStride + 64 + lane * 2);
+      v = make_float4(a.x, a.y, b.x, b.y);
+    } else {
+      v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    }
     __stcg(reinterpret_cast<float4*>(dst_base + static_cast<long long>(m) * n_pad), v);
   }
 }
@@ -890,10 +981,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __shared__ unsigned long long ar_expected_s;
   __shared__ unsigned int ar_launch_s;
   __shared__ unsigned long long ar_local_base_s;
+  __shared__ unsigned long long ar_expected2_s;
   if (fused_ar && threadIdx.x == 0) {
     ar_expected_s = p.ar_state[0];
     ar_launch_s = static_cast<unsigned int>(p.ar_state[1]);
     ar_local_base_s = p.ar_state[3];
+    ar_expected2_s = p.ar_state[4];
   }
   const int num_items = p.num_m * p.num_n * splits;
 
@@ -1395,7 +1488,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       } else {
         if (has_item)
-          cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, /*S=*/1, /*ks=*/ks, /*skip_own=*/false);
+          cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, /*S=*/1, /*ks=*/ks, /*skip_own=*/false,
+                                   /*halves_interleaved=*/EPI == EPI_QKV);
       }
     }
   }
@@ -1406,16 +1500,30 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const unsigned long long local_target = ar_local_base_s + gridDim.x;
       const bool ar_ok = ar_barrier(p, target, local_target);
       if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
-      if (ar_ok) {
-        if constexpr (EPI == EPI_RESIDUAL)
-          ar_reduce_phase<BN>(p, static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems, splits,
-                              static_cast<long long>(p.M) * p.num_n * BN);
+      unsigned long long local_done = local_target;
+      if constexpr (EPI == EPI_RESIDUAL) {
+        const long long part_off = static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems;
+        const long long split_elems = static_cast<long long>(p.M) * p.num_n * BN;
+        if (p.ar_two_shot) {
+          // reduce-scatter by pull, broadcast by store, second meeting on the other counter word, local gather
+          const int rows_per = (p.M + p.ar_world - 1) / p.ar_world;
+          const int own_lo = min(p.M, p.ar_rank * rows_per), own_hi = min(p.M, own_lo + rows_per);
+          const long long bcast_off = 2 * p.ar_buf_elems;
+          if (ar_ok) ar_reduce_phase<BN, 1>(p, part_off, splits, split_elems, own_lo, own_hi, bcast_off);
+          local_done = local_target + gridDim.x;
+          const unsigned long long target2 = ar_expected2_s + static_cast<unsigned long long>(p.ar_world);
+          const bool ok2 = ar_barrier(p, target2, local_done, 1);
+          if (ar_ok && ok2) ar_gather_phase<BN>(p, bcast_off, own_lo, own_hi);
+          if (blockIdx.x == 0 && threadIdx.x == 0) p.ar_state[4] = target2;
+        } else if (ar_ok) {
+          ar_reduce_phase<BN, 4>(p, part_off, splits, split_elems, 0, p.M, -1);
+        }
       }
       // Safe to advance the launch state: every CTA of this rank read it before arriving at the barrier.
       if (blockIdx.x == 0 && threadIdx.x == 0) {
         p.ar_state[0] = target;
         p.ar_state[1] = static_cast<unsigned long long>(ar_launch_s) + 1ull;
-        p.ar_state[3] = local_target;
+        p.ar_state[3] = local_done;
       }
     } else if (splits > 1) {
       // every partial of every CTA must be visible before anyone reduces
@@ -1864,6 +1972,24 @@ GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
+// Form of the fused all-reduce: -1 = by rank count (two-shot from `kTwoShotMinWorld` ranks on), 0 = one-shot (every rank
+// pulls every row), 1 = two-shot (each rank pulls its 1/W of the rows and broadcasts them). Every rank must use the same
+// setting; the symmetric buffer must hold three regions of `buf_elems` (two partial buffers and the result region).
+constexpr int kTwoShotMinWorld = 8;
+static int g_ar_two_shot = -2;   // -2: not read yet
+static bool ar_two_shot_setting(int world) {
+  if (g_ar_two_shot == -2) {
+    const char* v = getenv("GLLM_AR_TWO_SHOT");
+    g_ar_two_shot = v ? atoi(v) : -1;
+  }
+  return g_ar_two_shot < 0 ? world >= kTwoShotMinWorld : g_ar_two_shot != 0;
+}
+GLLM_API int gllm_gemm_set_ar_two_shot(int mode) {
+  const int old = g_ar_two_shot == -2 ? -1 : g_ar_two_shot;
+  g_ar_two_shot = mode;
+  return old;
+}
+
 // Row-parallel GEMM fused with the tensor-parallel all-reduce: out = sum over ranks(A_r · B_rᵀ) (+bias)
 // + residual, with the next norm's row statistics [M, ceil(N/256)]. Each rank stores its bf16 partial tiles
 // in its own symmetric buffer as they retire; all CTAs of all ranks meet at an arrival counter (one
@@ -1894,6 +2020,7 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce(const void* A, long long lda, con
     p.ar_peer_counter[r] = peer_counter[r];
   }
   p.ar_state = state; p.ar_buf_elems = buf_elems;
+  p.ar_two_shot = (world >= 2 && ar_two_shot_setting(world)) ? 1 : 0;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }

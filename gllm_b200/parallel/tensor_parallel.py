@@ -53,7 +53,7 @@ class TPContext:
     # ------------------------------------------------------------------------------------------
     def _setup_symmetric(self, force_p2p: bool):
         import torch.distributed as dist
-        total = 2 * self.buf_elems + 64
+        total = 3 * self.buf_elems + 64     # two alternating partial buffers, the two-shot result region, counters
         if self.size == 1:
             buf = torch.zeros(total, dtype=torch.bfloat16, device=self.device)
             peer_ptrs, mc_ptr = [buf.data_ptr()], 0
@@ -69,13 +69,13 @@ class TPContext:
             mc_ptr = 0 if force_p2p else int(getattr(self._handle, "multicast_ptr", 0) or 0)
         self._symm = buf
         self.uses_multimem = mc_ptr != 0
-        counter_off = 2 * self.buf_elems * 2  # bytes; 8-byte aligned because buf_elems is a multiple of 256
+        counter_off = 3 * self.buf_elems * 2  # bytes; 8-byte aligned because buf_elems is a multiple of 256
         n = len(peer_ptrs)
         self._peer_acc = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
         self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
         self._mc_acc = mc_ptr or None
         self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
-        self._state = torch.zeros(4, dtype=torch.int64, device=self.device)
+        self._state = torch.zeros(8, dtype=torch.int64, device=self.device)
 
     # ------------------------------------------------------------------------------------------
     def gemm_allreduce_residual(self, a, w, x, ss_out, partial, *, bn: int = 256):

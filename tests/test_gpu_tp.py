@@ -36,7 +36,7 @@ def test_fused_allreduce_world1_protocol():
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("mode", ["fused_p2p", "fused", "nccl"])
+@pytest.mark.parametrize("mode", ["fused_p2p", "fused", "nccl", "fused_two_shot", "fused_p2p_two_shot"])
 def test_fused_allreduce_two_gpus(mode):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",

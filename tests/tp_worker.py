@@ -8,6 +8,11 @@ import torch.distributed as dist
 
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    if mode.endswith("_two_shot"):      # reduce-scatter by pull + broadcast by store instead of the one-shot pull
+        os.environ["GLLM_AR_TWO_SHOT"] = "1"
+        mode = mode[:-len("_two_shot")]
+    else:
+        os.environ["GLLM_AR_TWO_SHOT"] = "0"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
