@@ -265,7 +265,7 @@ def main():
             "metric": "decode tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, uniform-random token ids)",
-            "config": {"model": f"{args.model}-shape dense decoder", "global_batch": n_active,
+            "config": {"model": f"{args.model}-shape " + ("MoE decoder" if cfg.is_moe else "dense decoder"), "global_batch": n_active,
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {budget_tokens} out",
                        "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
