@@ -44,6 +44,10 @@ def parse_args():
     ap.add_argument("--op-breakdown", action="store_true",
                     help="after the timed regions, time every op of one captured decode step with in-graph events")
     ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 marks the result invalid")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the NCCL baseline arm (unfused GEMM + ncclAllReduce) that vs_baseline is measured against")
+    ap.add_argument("--no-tp1-check", action="store_true",
+                    help="skip the comparison of greedy tokens with a single-GPU run of the same model on rank 0")
     return ap.parse_args()
 
 
@@ -165,6 +169,26 @@ def main():
     engine = LLMEngine(model, ecfg)
     prompts = make_prompts(args.concurrency, args.min_prompt, args.max_prompt, args.shared_prefix, cfg.vocab_size)
 
+    # ---- phase 0 (N > 1): the tensor-parallel engine must produce the single-GPU model's tokens ----
+    tp1_check = None
+    if world > 1 and not args.no_tp1_check:
+        check_prompts = make_prompts(8, 24, 96, 16, cfg.vocab_size, seed=4321)
+        got = [r.token_ids for r in engine.generate_batch(check_prompts, max_tokens=8, temperature=0.0, eos_ids=[])]
+        if rank == 0:
+            ref_model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, max_positions=max_len, **kv_kw)
+            ref_engine = LLMEngine(ref_model, EngineConfig(max_num_seqs=8, max_model_len=256, max_batch_tokens=1024,
+                                                           prefill_chunk=1024, num_pages=8 * 16 + 8, use_cuda_graphs=False))
+            want = [r.token_ids for r in ref_engine.generate_batch(check_prompts, max_tokens=8, temperature=0.0, eos_ids=[])]
+            same = sum(int(a == b) for g, w_ in zip(got, want) for a, b in zip(g, w_))
+            first = sum(int(g[0] == w_[0]) for g, w_ in zip(got, want))
+            tp1_check = {"tokens_equal": same, "tokens_total": 64, "first_tokens_equal": first, "prompts": 8}
+            del ref_engine, ref_model
+            torch.cuda.empty_cache()
+        dist.barrier()
+        for k in engine.stats:          # the check's prefill / decode work is not part of the measured workload
+            engine.stats[k] = 0
+
+    prefix_hits0 = int(engine.batcher.prefix_hits)
     W, K = max(args.warmup, 3), args.steps
     # every request generates the configured number of tokens; the timed window sits in the middle of it
     budget_tokens = max(args.output_tokens, W + K + 4)
@@ -193,6 +217,8 @@ def main():
     ttft = sorted(first_token_at.values())
     prefill_s = time.perf_counter() - t_submit
     # ---- phase 2: warm-up decode steps through the public API (captures the graph) ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(W + center_steps):
         engine.step()
     err = nv.device_error()
@@ -200,8 +226,7 @@ def main():
         raise SystemExit(f"device error word {err} after warm-up")
 
     # ---- phase 3: e2e timed region: K engine steps incl. H2D of inputs and D2H of tokens ----
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.lines.clear()      # the sampler has been running since before the warm-up; keep the timed regions' samples
     h2d0, d2h0 = engine.stats["h2d_bytes"], engine.stats["d2h_bytes"]
     tok0 = engine.stats["decode_tokens"]
     barrier()
@@ -239,6 +264,31 @@ def main():
     if err:
         raise SystemExit(f"device error word {err} in the timed region")
 
+    # ---- phase 5 (N > 1): the baseline arm, same engine, same step, collectives on NCCL ----
+    # unfused row-parallel GEMM -> ncclAllReduce -> residual/norm-statistics kernel, captured as its own CUDA graph
+    nccl_ms = None
+    if world > 1 and tp is not None and tp.mode == "fused" and not args.no_baseline and graph is not None:
+        tp.baseline = True
+        keep = engine.graphs.pop((B, True))
+        try:
+            g2 = engine._capture(B)
+            for _ in range(3):
+                g2.replay()
+            barrier()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            for _ in range(K):
+                g2.replay()
+            b1.record()
+            torch.cuda.synchronize(dev)
+            nccl_ms = b0.elapsed_time(b1)
+        finally:
+            tp.baseline = False
+            engine.graphs[(B, True)] = keep
+        err = nv.device_error()
+        if err:
+            raise SystemExit(f"device error word {err} in the baseline arm")
+
     prefill_ops = None
     if args.op_breakdown:
         prefill_ops = {n: round(v, 1) for n, v in engine.prefill_timer.results().items()}
@@ -252,10 +302,11 @@ def main():
             dist.all_reduce(bt, op=dist.ReduceOp.MAX)
         breakdown = {n: round(float(v), 4) for n, v in zip(names, bt.tolist())}
 
-    t = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    t = torch.tensor([dev_ms, e2e_s * 1e3, nccl_ms or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
+    nccl_ms = float(t[2]) if nccl_ms is not None else None
     n_active = args.concurrency
     value = n_active * K / (dev_ms / 1e3)
     e2e_value = e2e_tokens / (e2e_ms / 1e3)
@@ -264,7 +315,7 @@ def main():
         out = {
             "metric": "decode tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random-init weights, uniform-random token ids)",
+            "vs_baseline": (round(nccl_ms / dev_ms, 4) if nccl_ms else None), "dtype": "bf16", "data": "synthetic (random-init weights, uniform-random token ids)",
             "config": {"model": f"{args.model}-shape " + ("MoE decoder" if cfg.is_moe else "dense decoder"), "global_batch": n_active,
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {budget_tokens} out",
                        "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
@@ -283,9 +334,17 @@ def main():
                                      "prefill_calls_wall": round(engine.stats.get("prefill_wall_ms", 0.0), 1),
                                      "prefill_calls_device": round(engine.stats.get("prefill_device_ms", 0.0), 1),
                                      "prefill_steps": engine.stats["prefill_steps"]},
-            "prefix_cache_hits": int(engine.batcher.prefix_hits),
+            "prefix_cache_hits": int(engine.batcher.prefix_hits) - prefix_hits0,
             "kv_pages": engine.num_pages,
         }
+        if nccl_ms is not None:
+            # the baseline BASELINE.md names: this engine with every collective on NCCL, measured in the same run
+            out["baseline"] = {"what": "same engine, unfused row-parallel GEMM + ncclAllReduce + norm kernel (CUDA graph)",
+                               "value": round(n_active * K / (nccl_ms / 1e3), 1), "unit": "tokens/s",
+                               "ms_per_step": round(nccl_ms / K, 4)}
+        if tp1_check is not None:
+            out["config"]["tokens_match_tp1"] = tp1_check["tokens_equal"] == tp1_check["tokens_total"]
+            out["config"]["tp1_check"] = tp1_check
         if breakdown is not None:
             out["decode_breakdown_ms"] = breakdown
         if prefill_ops is not None:

@@ -1,6 +1,7 @@
 // C ABI shim: embeds (or joins) the CPython runtime and drives gllm_b200.ffi_bridge.
 #include <Python.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -8,7 +9,7 @@
 
 #include "gllm.h"
 
-struct gllm_client {
+struct GllmContext {
   PyObject* obj;
 };
 
@@ -51,24 +52,39 @@ static char* dup_str(const std::string& s) {
   return p;
 }
 
+#define GLLM_EXPORT __attribute__((visibility("default")))
+
+static PyObject* call_generate(GllmContext* c, const char* prompt, uint32_t max_tokens, float temperature,
+                               uint32_t top_k, float top_p, int32_t thinking_budget) {
+  // -> (text, [token ids], prompt_tokens, finish_reason)
+  return PyObject_CallMethod(c->obj, "generate", "sIfIfi", prompt, static_cast<unsigned int>(max_tokens),
+                             double(temperature), static_cast<unsigned int>(top_k), double(top_p), int(thinking_budget));
+}
+
 extern "C" {
 
-__attribute__((visibility("default"))) const char* gllm_client_version(void) { return "gllm_b200 0.1.0"; }
-__attribute__((visibility("default"))) const char* gllm_last_init_error(void) { return g_init_error.c_str(); }
+GLLM_EXPORT const char* gllm_client_version(void) { return "gllm_b200 0.2.0"; }
+GLLM_EXPORT const char* gllm_last_init_error(void) { return g_init_error.c_str(); }
 
-__attribute__((visibility("default"))) gllm_client* gllm_init(const char* model_id, const char* options_json) {
+GLLM_EXPORT GllmContext* gllm_init_with_options(const char* model_id, uint32_t kind, const char* options_json) {
+  if (!model_id) {
+    g_init_error = "null model id";
+    return nullptr;
+  }
   ensure_python();
   PyGILState_STATE gil = PyGILState_Ensure();
-  gllm_client* out = nullptr;
+  GllmContext* out = nullptr;
   PyObject* mod = PyImport_ImportModule("gllm_b200.ffi_bridge");
   if (!mod) {
     g_init_error = "import gllm_b200.ffi_bridge failed: " + py_error();
   } else {
-    PyObject* obj = PyObject_CallMethod(mod, "create", "ss", model_id ? model_id : "", options_json ? options_json : "");
+    PyObject* obj = PyObject_CallMethod(mod, "create", "sIs", model_id, static_cast<unsigned int>(kind),
+                                        options_json ? options_json : "");
     if (!obj) {
       g_init_error = py_error();
+      fprintf(stderr, "[gllm FFI] init failed: %s\n", g_init_error.c_str());
     } else {
-      out = new gllm_client{obj};
+      out = new GllmContext{obj};
       g_init_error.clear();
     }
     Py_DECREF(mod);
@@ -77,7 +93,12 @@ __attribute__((visibility("default"))) gllm_client* gllm_init(const char* model_
   return out;
 }
 
-__attribute__((visibility("default"))) void gllm_destroy(gllm_client* c) {
+// Reference signature: the options come from GLLM_FFI_OPTIONS (JSON) when set.
+GLLM_EXPORT GllmContext* gllm_init(const char* model_id, uint32_t kind) {
+  return gllm_init_with_options(model_id, kind, std::getenv("GLLM_FFI_OPTIONS"));
+}
+
+GLLM_EXPORT void gllm_destroy(GllmContext* c) {
   if (!c) return;
   PyGILState_STATE gil = PyGILState_Ensure();
   PyObject* r = PyObject_CallMethod(c->obj, "close", nullptr);
@@ -88,23 +109,50 @@ __attribute__((visibility("default"))) void gllm_destroy(gllm_client* c) {
   delete c;
 }
 
-__attribute__((visibility("default"))) gllm_generate_result* gllm_generate(gllm_client* c, const char* prompt,
-                                                                            int max_tokens, float temperature,
-                                                                            int top_k, float top_p) {
-  auto* res = static_cast<gllm_generate_result*>(std::calloc(1, sizeof(gllm_generate_result)));
+GLLM_EXPORT GllmGenerateResult gllm_generate(GllmContext* c, const char* prompt, uint32_t max_tokens, float temperature,
+                                             uint32_t top_k, float top_p, int32_t thinking_budget) {
+  GllmGenerateResult res = {nullptr, nullptr};
+  if (!c || !prompt) {
+    res.error = dup_str("null pointer argument");
+    return res;
+  }
+  PyGILState_STATE gil = PyGILState_Ensure();
+  PyObject* r = call_generate(c, prompt, max_tokens, temperature, top_k, top_p, thinking_budget);
+  if (!r) {
+    res.error = dup_str(py_error());
+  } else {
+    PyObject* text = PyTuple_GetItem(r, 0);
+    const char* t = text ? PyUnicode_AsUTF8(text) : nullptr;
+    res.text = dup_str(t ? t : "");
+    Py_DECREF(r);
+  }
+  PyGILState_Release(gil);
+  return res;
+}
+
+GLLM_EXPORT void gllm_free_generate_result(GllmGenerateResult* r) {
+  if (!r) return;
+  std::free(r->text);
+  std::free(r->error);
+  r->text = nullptr;
+  r->error = nullptr;
+}
+
+GLLM_EXPORT GllmGenerateResultEx* gllm_generate_ex(GllmContext* c, const char* prompt, uint32_t max_tokens,
+                                                   float temperature, uint32_t top_k, float top_p,
+                                                   int32_t thinking_budget) {
+  auto* res = static_cast<GllmGenerateResultEx*>(std::calloc(1, sizeof(GllmGenerateResultEx)));
   if (!c || !prompt) {
     res->error = 1;
     res->error_message = dup_str("null client or prompt");
     return res;
   }
   PyGILState_STATE gil = PyGILState_Ensure();
-  PyObject* r = PyObject_CallMethod(c->obj, "generate", "sifif", prompt, max_tokens, double(temperature), top_k,
-                                    double(top_p));
+  PyObject* r = call_generate(c, prompt, max_tokens, temperature, top_k, top_p, thinking_budget);
   if (!r) {
     res->error = 2;
     res->error_message = dup_str(py_error());
   } else {
-    // (text, [token ids], prompt_tokens, finish_reason)
     PyObject* text = PyTuple_GetItem(r, 0);
     PyObject* ids = PyTuple_GetItem(r, 1);
     const char* t = text ? PyUnicode_AsUTF8(text) : nullptr;
@@ -121,12 +169,45 @@ __attribute__((visibility("default"))) gllm_generate_result* gllm_generate(gllm_
   return res;
 }
 
-__attribute__((visibility("default"))) void gllm_free_generate_result(gllm_generate_result* r) {
+GLLM_EXPORT void gllm_free_generate_result_ex(GllmGenerateResultEx* r) {
   if (!r) return;
   std::free(r->text);
   std::free(r->token_ids);
   std::free(r->error_message);
   std::free(r);
+}
+
+GLLM_EXPORT int gllm_embed(GllmContext* c, const char* text, float* out, int capacity) {
+  if (!c || !text || !out) return -1;
+  PyGILState_STATE gil = PyGILState_Ensure();
+  int dim = -1;
+  PyObject* r = PyObject_CallMethod(c->obj, "embed", "s", text);
+  if (!r) {
+    g_init_error = py_error();
+  } else {
+    const Py_ssize_t n = PyList_Size(r);
+    dim = static_cast<int>(n);
+    for (Py_ssize_t i = 0; i < n && i < capacity; ++i) out[i] = static_cast<float>(PyFloat_AsDouble(PyList_GetItem(r, i)));
+    Py_DECREF(r);
+  }
+  PyGILState_Release(gil);
+  return dim;
+}
+
+GLLM_EXPORT int gllm_rerank_score(GllmContext* c, const char* query, const char* document, float* score) {
+  if (!c || !query || !document || !score) return -1;
+  PyGILState_STATE gil = PyGILState_Ensure();
+  int rc = -1;
+  PyObject* r = PyObject_CallMethod(c->obj, "rerank_score", "ss", query, document);
+  if (!r) {
+    g_init_error = py_error();
+  } else {
+    *score = static_cast<float>(PyFloat_AsDouble(r));
+    rc = 0;
+    Py_DECREF(r);
+  }
+  PyGILState_Release(gil);
+  return rc;
 }
 
 }  // extern "C"

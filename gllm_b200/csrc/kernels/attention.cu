@@ -325,8 +325,14 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ctx = p.ctx_lens[b];
+  pdl_wait();                // q and the KV rows of this step come from the kernel before this one
+  pdl_launch_dependents();
+  int ctx = p.ctx_lens[b];
   if (ctx <= 0) return;
+  if (ctx > p.max_blocks * kPage) {   // a context longer than the block table: report it and attend what the table covers
+    if (p.err && threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_ARG);
+    ctx = p.max_blocks * kPage;
+  }
   const int n_pages = (ctx + kPage - 1) / kPage;
   const int first_tok = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;
   const int first_page = first_tok / kPage;
@@ -510,9 +516,15 @@ paged_prefill_kernel(const __grid_constant__ CUtensorMap tmap_kv, const PrefillP
 
   const int qblk = blockIdx.x, qh = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_wait();
+  pdl_launch_dependents();
   const int qlen = p.q_len[seq];
   if (qblk * kPfRows >= qlen) return;
-  const int ctx = p.ctx_lens[seq];
+  int ctx = p.ctx_lens[seq];
+  if (ctx > p.max_blocks * kPage) {   // longer than the block table: report, never index past the table
+    if (p.err && threadIdx.x == 0) atomicCAS(p.err, 0, ERR_BAD_ARG);
+    ctx = p.max_blocks * kPage;
+  }
   const int qstart = p.q_start[seq];
   const int kvh = qh / p.group;
   const int pos0 = ctx - qlen;  // position of query row 0 of this sequence
@@ -700,17 +712,19 @@ static int paged_decode_impl(const void* q, void* out, const void* kv_cache, int
   p.part_lse = scratch ? scratch + static_cast<long long>(batch) * n_q_heads * p.max_splits * kHD : nullptr;
   p.counters = counters; p.num_pages = num_pages; p.window = window; p.sinks = sinks;
   p.err = gllm_error_word();
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          KV8 ? kDecSmem8 : kDecSmem);
     if (e != cudaSuccess) { set_last_error("paged_decode: %s", cudaGetErrorString(e)); return -1; }
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
   dim3 grid(p.max_splits, n_kv_heads, batch);
-  paged_decode_kernel<KV8><<<grid, kDecWarps * 32, KV8 ? kDecSmem8 : kDecSmem, (cudaStream_t)stream>>>(t, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) { set_last_error("paged_decode launch: %s", cudaGetErrorString(e)); return -1; }
+  cudaError_t e = launch_kernel(paged_decode_kernel<KV8>, grid, dim3(kDecWarps * 32), KV8 ? kDecSmem8 : kDecSmem,
+                                (cudaStream_t)stream, true, 0, t, p);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); set_last_error("paged_decode launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
 
@@ -754,16 +768,18 @@ static int paged_prefill_impl(const void* q, void* out, const void* kv_cache, in
   p.v_scale = KV8 ? kv_scale : 1.f;
   p.num_pages = num_pages; p.window = window; p.causal = causal; p.sinks = sinks;
   p.err = gllm_error_word();
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel<KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem);
     if (e != cudaSuccess) { set_last_error("paged_prefill: %s", cudaGetErrorString(e)); return -1; }
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
   dim3 grid((max_q_len + kPfRows - 1) / kPfRows, n_q_heads, num_seqs);
-  paged_prefill_kernel<KV8><<<grid, kPfWarps * 32, kPfSmem, (cudaStream_t)stream>>>(t, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) { set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
+  cudaError_t e = launch_kernel(paged_prefill_kernel<KV8>, grid, dim3(kPfWarps * 32), kPfSmem, (cudaStream_t)stream,
+                                true, 0, t, p);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); set_last_error("paged_prefill launch: %s", cudaGetErrorString(e)); return -1; }
   return 0;
 }
 
@@ -792,6 +808,8 @@ GLLM_API int gllm_paged_prefill_fp8(const void* q, void* out, const void* kv_cac
 // latency-critical loop. The split-KV scratch is the
 // static array below; the caller still owns q, out, the KV cache and the index tensors.
 // ---------------------------------------------------------------------------------------------
+#include <mutex>
+
 #include "gllm_noalloc.h"
 
 namespace gllm {
@@ -807,7 +825,49 @@ struct NoAllocDeviceState {
   int* err = nullptr;
 };
 static NoAllocDeviceState g_noalloc_state[64];
+static std::mutex g_noalloc_mutex;   // the per-device set-up may be reached by several host threads at once
+
+// Resolves (once per device, under the mutex) the device addresses of the static arrays. Returns null on failure.
+static NoAllocDeviceState* noalloc_state_for_current_device(const char* who) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_error("%s: no current device", who);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDeviceState& st = g_noalloc_state[dev];
+  if (!st.ready) {
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.scratch), g_noalloc_scratch);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.counters), g_noalloc_counters);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.err), g_noalloc_err);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(paged_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+    if (e != cudaSuccess) {
+      set_last_error("%s: set-up failed: %s", who, cudaGetErrorString(e));
+      return nullptr;
+    }
+    st.ready = true;
+  }
+  return &st;
+}
 }  // namespace gllm
+
+// Status of the allocation-free path on the current device (see gllm_noalloc.h). Copies the 4-byte status word
+// to the host on `stream`, waits for that stream, and clears the word when it was non-zero. Allocates nothing.
+GLLM_API int gllm_paged_decode_noalloc_status(void* stream) {
+  NoAllocDeviceState* st = noalloc_state_for_current_device("paged_decode_noalloc_status");
+  if (!st) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int code = 0;
+  cudaError_t e = cudaMemcpyAsync(&code, st->err, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && code != 0) e = cudaMemsetAsync(st->err, 0, sizeof(int), s);
+  if (e != cudaSuccess) {
+    set_last_error("paged_decode_noalloc_status: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return code;
+}
 
 GLLM_API int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_cache, int num_pages,
                                        const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
@@ -830,25 +890,10 @@ GLLM_API int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_
                    static_cast<long long>(batch) * n_kv_heads, GLLM_NOALLOC_MAX_COUNTERS);
     return -1;
   }
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-    set_last_error("paged_decode_noalloc: no current device");
-    return -1;
-  }
-  NoAllocDeviceState& st = g_noalloc_state[dev];
-  if (!st.ready) {
-    // one-time set-up for this device (do it before any stream capture): resolve the device addresses
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.scratch), g_noalloc_scratch);
-    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.counters), g_noalloc_counters);
-    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&st.err), g_noalloc_err);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(paged_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-    if (e != cudaSuccess) {
-      set_last_error("paged_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
-      return -1;
-    }
-    st.ready = true;
-  }
+  // one-time set-up for this device (do it before any stream capture): resolve the device addresses
+  NoAllocDeviceState* stp = noalloc_state_for_current_device("paged_decode_noalloc");
+  if (!stp) return -1;
+  NoAllocDeviceState& st = *stp;
   // tensor map built on the stack (the cached encoder used elsewhere grows a host-side table)
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) {

@@ -29,8 +29,24 @@ enum : int {
   ERR_BAD_ARG = 9,
 };
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // 2 s for on-chip barriers
-constexpr unsigned long long kPeerWaitLimitNs = 8000000000ull;  // 8 s for another GPU
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // default: 2 s for on-chip barriers
+constexpr unsigned long long kPeerWaitLimitNs = 8000000000ull;  // default: 8 s for another GPU
+
+// Process-wide settings of the kernel library (host side). They are read at launch time and travel to the kernels
+// in their parameter structs, so a change applies to the next launch (and to graphs captured after it).
+struct RuntimeSettings {
+  unsigned long long wait_ns = kWaitLimitNs;            // limit of waits on barriers inside one GPU
+  unsigned long long peer_wait_ns = kPeerWaitLimitNs;   // limit of waits on a flag another GPU writes
+  int pdl = 1;             // launch with programmatic stream serialization (kernels call griddepcontrol.wait)
+  int park = 1;            // split-K / all-reduce tiles parked in shared memory and written row by row
+  int cluster_sk = 1;      // split-K inside a thread-block cluster when every cluster fits at once
+  int ar_split = 1;        // the fused all-reduce may split K inside a rank
+  int qkv_two_rows = 1;    // 256-row tiles for the QKV GEMM
+  int ar_drop_flags = 0;   // test hook: the push all-reduce leaves its tile flags unset, so its waits run out
+  int pair_max_m = 256, pair_epi_mask = 0, pair_big_m = 1024;   // where CTA pairs are used (see gemm_sm100.cu)
+  int ar_two_shot = -1;    // pull form of the fused all-reduce: -1 by rank count, 0 one-shot, 1 two-shot
+};
+RuntimeSettings& settings();
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -78,14 +94,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. Returns false if the wait was abandoned (this thread timed out, or another
 // thread of the CTA already raised `*abort_flag`). `err` is a global int; the first failure wins.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err,
-                                          int code) {
+                                          int code, unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if (((++spins) & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (err) atomicCAS(err, 0, code);
         return false;
@@ -94,6 +110,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return true;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs. `pdl_wait` blocks the calling thread until every prerequisite grid
+// has completed and its memory operations are visible; everything that reads or writes memory another kernel
+// touches comes after it. `pdl_launch_dependents` lets the next kernel's CTAs be scheduled as soon as every CTA of
+// this grid has executed it (they then sit in their own pdl_wait). Both are no-ops in a normal launch.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, no cluster fan-out anywhere in this code base)
@@ -294,6 +320,35 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
 
 const char* last_error();
 void set_last_error(const char* fmt, ...);
+
+// Kernel launch through cudaLaunchKernelEx: optional cluster width and, when the library's `pdl` setting is on and
+// `allow_pdl` is true, the programmatic-stream-serialization attribute (the kernel must call pdl_wait()).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool allow_pdl, int cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (allow_pdl && settings().pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 }  // namespace gllm
 

@@ -37,11 +37,26 @@ namespace gllm {
 
 enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_QKV = 3 };
 
+// Phase stamps of CTA 0 (SM clocks) exist only in builds with -DGLLM_TRACE (python -m gllm_b200.build --trace).
+#ifdef GLLM_TRACE
+#define GLLM_TRACE_DECL const bool tracing = p.trace != nullptr && blockIdx.x == 0
+#define GLLM_STAMP(cond, slot)                           \
+  do {                                                   \
+    if (tracing && (cond)) p.trace[slot] = clock64();    \
+  } while (0)
+#else
+#define GLLM_TRACE_DECL
+#define GLLM_STAMP(cond, slot) \
+  do {                         \
+  } while (0)
+#endif
+
 constexpr int kBM = 128;
 constexpr int kTileKBytes = 128;  // one swizzle row
 constexpr int kGemmThreads = 256;
 constexpr int kPageTokens = 16;
 constexpr int kMaxSplits = 16;
+constexpr int kClusterPartStride = 128 + 4;  // floats per row of a parked fp32 tile in shared memory (padded: no bank conflicts)
 
 struct GemmParams {
   int M, N, K;
@@ -107,7 +122,23 @@ struct GemmParams {
   int park;           // 1: one work item per CTA: the fp32 accumulator tile is parked in shared memory and written out
                       //    by all warps with row-contiguous stores (split-K scratch or the all-reduce buffer)
   int cluster_sk;     // 1: the splits of a tile form a thread-block cluster and reduce through distributed shared memory
-  long long* trace;   // debugging aid: when set, CTA 0 writes SM clock stamps of its phases here (9 slots)
+  // Push form of the fused all-reduce (ar_push == 1). Rank r owns output rows [r * rows_per, (r + 1) * rows_per),
+  // rows_per = ceil(M / world). As a tile retires its bf16 rows are stored straight into the row owner's receive
+  // slots [source][local row][column] (peer stores over NVLink, no atomics) and one flag per (source, m tile, n tile)
+  // is released with the launch epoch; the owner's warps wait on those flags tile by tile, add the sources in a fixed
+  // order, add the residual, and store the finished rows and their row statistics into `out` / `row_ss_out` of EVERY
+  // rank (one multimem.st per 16 bytes, or a store per peer): both must lie inside the symmetric region. A last
+  // meeting on per-rank "done" words ends the kernel. All regions are offsets from the symmetric base of each rank.
+  int ar_push;
+  long long ar_recv_off;      // bf16 elements from the base: receive slots
+  long long ar_out_off;       // bf16 elements from the base: `out` (== residual) rows
+  long long ar_ss_off;        // BYTES from the base: row statistics [M, n_pad / 256] fp32
+  long long ar_flag_off;      // BYTES from the base: tile flags (u32)
+  long long ar_done_off;      // BYTES from the base: done words (u64 per rank)
+  long long ar_flag_cap;      // number of u32 flags at ar_flag_off
+  int ar_drop_flags;          // test hook: leave the tile flags unset, so that the waits run out
+  unsigned long long wait_ns, peer_wait_ns;   // limits of the bounded waits
+  long long* trace;   // debugging aid (GLLM_TRACE builds): CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
 };
 
@@ -236,7 +267,7 @@ __device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long lo
     const unsigned long long t0 = globaltimer_ns();
     unsigned int spins = 0;
     while (ld_acquire_sys_u64(mine) < target) {
-      if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > kPeerWaitLimitNs) {
+      if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > p.peer_wait_ns) {
         if (p.err) atomicCAS(p.err, 0, ERR_TIMEOUT_PEER);
         ok = 0;
         break;
@@ -249,7 +280,8 @@ __device__ __forceinline__ bool ar_barrier(const GemmParams& p, unsigned long lo
 }
 
 // Sense-reversing grid barrier over {count, generation}; bounded. Returns false on timeout.
-__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num_ctas, int* err) {
+__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num_ctas, int* err,
+                                             unsigned long long limit_ns) {
   __shared__ int ok_flag;
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -264,7 +296,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int num
       const unsigned long long t0 = globaltimer_ns();
       unsigned int spins = 0;
       while (*reinterpret_cast<volatile unsigned int*>(bar + 1) == gen) {
-        if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > limit_ns) {
           if (err) atomicCAS(err, 0, ERR_TIMEOUT_GRID);
           ok = 0;
           break;
@@ -767,6 +799,247 @@ __device__ void ar_gather_phase(const GemmParams& p, long long bcast_off, int ow
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Push form of the fused all-reduce (GemmParams::ar_push): no meeting of all ranks before data moves. A producer
+// stores the bf16 rows of a retired tile straight into the receive slots of the rank that owns those rows and then
+// releases one flag per (source, m tile, n tile) with the launch epoch; the owner's warps wait for the flags of the
+// tiles their units need, add the sources in (split, rank) order, finish the rows (bias, residual, rounding, row
+// statistics) and store them into every rank's output. The flags carry values, not counts, so nothing is reset
+// between launches; every rank issues the same launches in the same order, so the epochs agree.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* ptr, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long* ptr, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(ptr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_relaxed_sys_u32(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void multimem_st_f32(float* mc, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
+}
+__device__ __forceinline__ int ar_rows_per(const GemmParams& p) { return (p.M + p.ar_world - 1) / p.ar_world; }
+__device__ __forceinline__ unsigned int* ar_flag_ptr(const GemmParams& p, int r) {
+  return reinterpret_cast<unsigned int*>(reinterpret_cast<char*>(p.ar_peer_buf[r]) + p.ar_flag_off);
+}
+__device__ __forceinline__ unsigned long long* ar_done_ptr(const GemmParams& p, int r) {
+  return reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.ar_peer_buf[r]) + p.ar_done_off);
+}
+// Receive slot of (source, output row m, column n) in the memory of the rank that owns row m.
+__device__ __forceinline__ __nv_bfloat16* ar_recv_slot(const GemmParams& p, int src, int m, long long n_pad, int n) {
+  const int rows_per = ar_rows_per(p);
+  const int owner = m / rows_per;
+  const int lrow = m - owner * rows_per;
+  return p.ar_peer_buf[owner] + p.ar_recv_off + (static_cast<long long>(src) * rows_per + lrow) * n_pad + n;
+}
+// After a barrier among all threads that stored tile (m_sup, n_blk) of source `src`: thread `tid` < world releases
+// the tile's flag on rank `tid` when the tile holds rows of that rank.
+__device__ __forceinline__ void ar_push_signal(const GemmParams& p, int tid, int src, int m_sup, int n_blk,
+                                               int tile_rows, unsigned int epoch) {
+  if (tid < p.ar_world && !p.ar_drop_flags) {
+    const int rows_per = ar_rows_per(p);
+    const int lo = tid * rows_per, hi = min(p.M, lo + rows_per);
+    const int t_lo = m_sup * tile_rows, t_hi = min(p.M, t_lo + tile_rows);
+    if (t_lo < hi && t_hi > lo) {
+      __threadfence_system();
+      st_release_sys_u32(ar_flag_ptr(p, tid) + (static_cast<long long>(src) * p.num_m + m_sup) * p.num_n + n_blk, epoch);
+    }
+  }
+}
+// The parked fp32 tile of this CTA (BN = 128) goes out row by row: a warp stores 256 contiguous bytes per row.
+__device__ void ar_push_parked(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int src) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * 128;
+  for (int r = warp; r < rows; r += nwarps) {
+    const int m = m_row0 + r;
+    if (m >= p.M) continue;
+    const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    uint2 w;
+    w.x = pack_bf16x2(v.x, v.y);
+    w.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(ar_recv_slot(p, src, m, n_pad, n_blk * 128 + lane * 4)) = w;
+  }
+}
+
+// The owner's side: a warp takes (row, 256-column group) units of this rank's rows, four at a time; a lane covers 8
+// columns. tile_rows: rows of one producer tile (the m index of the flags). abort: the CTA's shared abort word.
+template <int BN>
+__device__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile_rows, volatile int* abort) {
+  constexpr int U = 4;
+  constexpr int NB = 256 / BN;   // n tiles per 256-column group
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int W = p.ar_world, nsrc = W * p.splits;
+  const int rows_per = ar_rows_per(p);
+  const int own_lo = min(p.M, p.ar_rank * rows_per), own_hi = min(p.M, own_lo + rows_per);
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const int groups = static_cast<int>(n_pad / 256);
+  const int units = (own_hi - own_lo) * groups;
+  if (units <= 0) return;
+  const __nv_bfloat16* recv = p.ar_peer_buf[p.ar_rank] + p.ar_recv_off;
+  const unsigned int* flags = ar_flag_ptr(p, p.ar_rank);
+  const long long src_stride = static_cast<long long>(rows_per) * n_pad;
+  for (int u0 = (blockIdx.x * warps_per_cta + (threadIdx.x >> 5)) * U; u0 < units;
+       u0 += gridDim.x * warps_per_cta * U) {
+    // ---- wait (bounded) for the tiles these units are made of: one lane per (source, n tile) flag ----
+    bool ok = true;
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      const int m = own_lo + u / groups, grp = u % groups;
+      if (lane < nsrc * NB) {
+        const unsigned int* f = flags + (static_cast<long long>(lane / NB) * p.num_m + m / tile_rows) * p.num_n +
+                                grp * NB + (lane % NB);
+        if (ld_relaxed_sys_u32(f) != epoch) {
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned int spins = 0;
+          while (ld_relaxed_sys_u32(f) != epoch) {
+            if (((++spins) & 0x3F) == 0) {
+              if (*abort) { ok = false; break; }
+              if (globaltimer_ns() - t0 > p.peer_wait_ns) {
+                *abort = 1;
+                if (p.err) atomicCAS(p.err, 0, ERR_TIMEOUT_PEER);
+                ok = false;
+                break;
+              }
+            }
+          }
+        }
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    fence_acq_rel_sys();   // the rows stored before a flag was released are visible now
+    if (!ok) continue;
+    // ---- add the sources in (split, rank) order ----
+    float acc[U][8];
+    long long off[U];
+    uint4 res[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = min(u0 + k, units - 1);
+      const int lrow = u / groups, grp = u % groups;
+      off[k] = static_cast<long long>(lrow) * n_pad + static_cast<long long>(grp) * 256 + lane * 8;
+      const int n0 = grp * 256 + lane * 8;
+      res[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (n0 < p.N) res[k] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(own_lo + lrow) * p.ldr + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+    }
+    for (int s0 = 0; s0 < nsrc; s0 += 4) {
+      uint4 raw[4][U];
+#pragma unroll
+      for (int ds = 0; ds < 4; ++ds) {
+        const int sidx = min(s0 + ds, nsrc - 1);
+#pragma unroll
+        for (int k = 0; k < U; ++k) raw[ds][k] = __ldcg(reinterpret_cast<const uint4*>(recv + sidx * src_stride + off[k]));
+      }
+#pragma unroll
+      for (int ds = 0; ds < 4; ++ds) {
+        if (s0 + ds < nsrc) {
+#pragma unroll
+          for (int k = 0; k < U; ++k) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[ds][k]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h[e]);
+              acc[k][2 * e] += f.x;
+              acc[k][2 * e + 1] += f.y;
+            }
+          }
+        }
+      }
+    }
+    // ---- finish the rows and hand them to every rank ----
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int u = u0 + k;
+      if (u >= units) continue;
+      const int m = own_lo + u / groups, grp = u % groups;
+      const int n0 = grp * 256 + lane * 8;
+      float ss = 0.f;
+      if (n0 < p.N) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] = acc[k][j];
+          if (p.bias) v[j] += p.bias[n0 + j];
+        }
+        const uint4 rr = res[k];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[2 * e] = bf16_round(v[2 * e] + f.x);
+          v[2 * e + 1] = bf16_round(v[2 * e + 1] + f.y);
+          ss = fmaf(v[2 * e], v[2 * e], fmaf(v[2 * e + 1], v[2 * e + 1], ss));
+        }
+        uint4 w;
+        w.x = pack_bf16x2(v[0], v[1]);
+        w.y = pack_bf16x2(v[2], v[3]);
+        w.z = pack_bf16x2(v[4], v[5]);
+        w.w = pack_bf16x2(v[6], v[7]);
+        const long long o = p.ar_out_off + static_cast<long long>(m) * p.ldo + n0;
+        if (p.ar_mc_buf) {
+          multimem_st_b128(p.ar_mc_buf + o, w);
+        } else {
+          for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(p.ar_peer_buf[r] + o) = w;
+        }
+      }
+      ss = warp_sum(ss);
+      if (p.row_ss_out && lane == 0) {
+        const long long so = p.ar_ss_off + (static_cast<long long>(m) * groups + grp) * 4;
+        if (p.ar_mc_buf) {
+          multimem_st_f32(reinterpret_cast<float*>(reinterpret_cast<char*>(p.ar_mc_buf) + so), ss);
+        } else {
+          for (int r = 0; r < W; ++r) *reinterpret_cast<float*>(reinterpret_cast<char*>(p.ar_peer_buf[r]) + so) = ss;
+        }
+      }
+    }
+  }
+}
+
+// End of a push launch: the last CTA of this rank to get here tells every rank that this rank's rows are out, then
+// every CTA waits (bounded) until all ranks have said so. After that the outputs of all ranks are in local memory and
+// nobody still reads this rank's receive slots, so the next launch may overwrite them.
+__device__ __forceinline__ bool ar_push_finish(const GemmParams& p, unsigned long long epoch, unsigned long long launch) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();   // this CTA's stores went to the other GPUs' memory
+    const unsigned long long prev = atomicAdd(p.ar_state + 5, 1ull);
+    if (prev + 1ull == gridDim.x) {
+      p.ar_state[5] = 0ull;             // every CTA has arrived, so every CTA has read the launch index
+      p.ar_state[1] = launch + 1ull;
+      __threadfence_system();
+      for (int r = 0; r < p.ar_world; ++r) st_release_sys_u64(ar_done_ptr(p, r) + p.ar_rank, epoch);
+    }
+  }
+  if (threadIdx.x < 32) {
+    bool ok = true;
+    if (threadIdx.x < p.ar_world) {
+      const unsigned long long* d = ar_done_ptr(p, p.ar_rank) + threadIdx.x;
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned int spins = 0;
+      while (ld_acquire_sys_u64(d) != epoch) {
+        if (((++spins) & 0x3F) == 0 && globaltimer_ns() - t0 > p.peer_wait_ns) {
+          if (p.err) atomicCAS(p.err, 0, ERR_TIMEOUT_PEER);
+          ok = false;
+          break;
+        }
+      }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0) ok_flag = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // split-K inside a thread-block cluster: the S CTAs that share an output tile park their fp32 partial tiles in
 // their own shared memory, write the rows that OTHER members will finish to the global scratch with coalesced
@@ -799,7 +1072,6 @@ __device__ __forceinline__ float2 ld_dsmem_f2(uint32_t addr) {
   return v;
 }
 
-constexpr int kClusterPartStride = 128 + 4;  // floats per row of the shared-memory partial tile (padded: no bank conflicts)
 
 // Rows of the tile that cluster member `rank` finishes.
 __device__ __forceinline__ void cluster_row_range(int rows, int S, int rank, int& b, int& e) {
@@ -976,18 +1248,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int lane = threadIdx.x & 31;
   const int splits = p.splits;
   const bool fused_ar = p.ar_world > 0;
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
-  if (tracing && threadIdx.x == 0) p.trace[0] = clock64();
+  GLLM_TRACE_DECL;
+  GLLM_STAMP(threadIdx.x == 0, 0);
   __shared__ unsigned long long ar_expected_s;
-  __shared__ unsigned int ar_launch_s;
+  __shared__ unsigned long long ar_launch_s;
   __shared__ unsigned long long ar_local_base_s;
   __shared__ unsigned long long ar_expected2_s;
-  if (fused_ar && threadIdx.x == 0) {
-    ar_expected_s = p.ar_state[0];
-    ar_launch_s = static_cast<unsigned int>(p.ar_state[1]);
-    ar_local_base_s = p.ar_state[3];
-    ar_expected2_s = p.ar_state[4];
-  }
   const int num_items = p.num_m * p.num_n * splits;
 
   if (threadIdx.x == 0) {
@@ -1003,26 +1269,6 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_a);
-    tma_prefetch_desc(&tmap_b);
-  }
-  if (warp == 2) {
-    if constexpr (PAIR) {
-      tmem_alloc_pair(tmem_base_ptr, Cfg::kTmemCols);
-      tmem_relinquish_pair();
-    } else {
-      tmem_alloc(tmem_base_ptr, Cfg::kTmemCols);
-      tmem_relinquish();
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if constexpr (PAIR) cluster_barrier();   // the partner's barriers are initialised before anything signals them
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_base_ptr;
-  if (tracing && threadIdx.x == 0) p.trace[1] = clock64();
-
   // work item -> (k split, m super tile, n tile); the splits of one output tile are adjacent so
   // they run at the same time and the reduction does not wait long
   auto decode_item = [&](int t, int& ks, int& m_sup, int& n_blk, int& kb0, int& kb1) {
@@ -1033,6 +1279,51 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     kb0 = static_cast<int>(static_cast<long long>(ks) * p.num_kb / splits);
     kb1 = static_cast<int>(static_cast<long long>(ks + 1) * p.num_kb / splits);
   };
+  // Weight tiles do not depend on the kernel before this one: the producer thread requests the B halves of its
+  // first stages before it waits for that kernel (programmatic dependent launch), the A halves after.
+  int b_prefetched = 0;
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if constexpr (!PAIR) {
+      if (p.mblk_group == nullptr && work_id < num_items) {
+        int ks, m_sup, n_blk, kb0, kb1;
+        decode_item(work_id, ks, m_sup, n_blk, kb0, kb1);
+        const int n_pre = min(kStages, kb1 - kb0);
+        for (int i = 0; i < n_pre; ++i) {
+          mbar_expect_tx(&full_bar[i], kStageBytes);
+          tma_load_2d(tiles + i * kStageBytes + MT * kABytes, &tmap_b, &full_bar[i], (kb0 + i) * kElemsPerKB, n_blk * BN);
+        }
+        b_prefetched = n_pre;
+      }
+    }
+  }
+  if (warp == 2) {
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_base_ptr, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_ptr, Cfg::kTmemCols);
+      tmem_relinquish();
+    }
+  }
+  // From here on the kernel reads and writes memory that the kernel before it in the stream may still be using.
+  pdl_wait();
+  if (fused_ar && threadIdx.x == 0) {
+    ar_expected_s = p.ar_state[0];
+    ar_launch_s = p.ar_state[1];
+    ar_local_base_s = p.ar_state[3];
+    ar_expected2_s = p.ar_state[4];
+  }
+  tc_fence_before();
+  __syncthreads();
+  pdl_launch_dependents();   // the next kernel's CTAs may be scheduled (they wait for this grid in their own pdl_wait)
+  if constexpr (PAIR) cluster_barrier();   // the partner's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_ptr;
+  GLLM_STAMP(threadIdx.x == 0, 1);
+  // push all-reduce: epoch of this launch (never 0, the value of untouched flags) and this rank's source index base
+  const unsigned int ar_epoch = static_cast<unsigned int>(ar_launch_s & 0x7fffffffull) + 1u;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -1050,7 +1341,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           b_row += grp * p.group_rows;
         }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_SMEM_EMPTY)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_SMEM_EMPTY, p.wait_ns)) {
             ok = false;
             break;
           }
@@ -1063,11 +1354,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_load_2d_pair(sa, &tmap_a, bar0, kb * kElemsPerKB, (m_sup * 2 + static_cast<int>(crank)) * kBM);
             tma_load_2d_pair(sb, &tmap_b, bar0, kb * kElemsPerKB, b_row + static_cast<int>(crank) * (BN / 2));
           } else {
-            mbar_expect_tx(&full_bar[stage], kStageBytes);
+            const bool b_done = b_prefetched > 0;   // the first stages' weight halves were requested before pdl_wait
+            if (b_done) --b_prefetched;
+            else mbar_expect_tx(&full_bar[stage], kStageBytes);
 #pragma unroll
             for (int i = 0; i < MT; ++i)
               tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
+            if (!b_done) tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -1092,19 +1385,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int it_cur = it++;
         const int acc = it_cur % kAcc;
         const uint32_t acc_phase = (it_cur / kAcc) & 1;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_TMEM_EMPTY)) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TIMEOUT_TMEM_EMPTY, p.wait_ns)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * (MT * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL)) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_TIMEOUT_TMA_FULL, p.wait_ns)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (tracing && it_cur == 0 && kb == kb0) p.trace[2] = clock64();
+          GLLM_STAMP(it_cur == 0 && kb == kb0, 2);
           const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
           const uint64_t b_desc = umma_desc_sw128(sa + MT * kABytes);
 #pragma unroll
@@ -1140,7 +1433,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             umma_commit(&tmem_full[acc]);
           }
         }
-        if (tracing && it_cur == 0) p.trace[3] = clock64();
+        GLLM_STAMP(it_cur == 0, 3);
       }
     }
     __syncwarp();
@@ -1157,13 +1450,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int acc = it_cur % kAcc;
       const uint32_t acc_phase = (it_cur / kAcc) & 1;
       // warp-uniform decision: tcgen05.ld below is warp-collective
-      const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, ERR_TIMEOUT_TMEM_FULL);
+      const bool got = mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.err, ERR_TIMEOUT_TMEM_FULL, p.wait_ns);
       if (!__all_sync(0xffffffffu, got)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (tracing && it_cur == 0 && warp == 4 && lane == 0) p.trace[4] = clock64();
+      GLLM_STAMP(it_cur == 0 && warp == 4 && lane == 0, 4);
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * (MT * BN);
 
       // ---- split-K phase 1: dump this CTA's fp32 partial tile; the fused epilogue runs in phase 2 ----
@@ -1205,12 +1498,17 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tmem_ld_32x32(taddr0 + i * BN + c * 32, r);
             tmem_ld_wait();
             if (m < p.M && fused_ar) {
-              // this rank's bf16 partial tile, in its own symmetric buffer (peers pull it after the barrier)
-              const long long off = ar_off + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN + c * 32;
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-              store_bf16x32(p.ar_peer_buf[p.ar_rank] + off, v);
+              if (p.ar_push) {
+                // straight into the receive slots of the rank that owns this row (a peer store over NVLink)
+                store_bf16x32(ar_recv_slot(p, ks * p.ar_world + p.ar_rank, m, n_pad, n_blk * BN + c * 32), v);
+              } else {
+                // this rank's bf16 partial tile, in its own symmetric buffer (peers pull it after the barrier)
+                const long long off = ar_off + static_cast<long long>(m) * n_pad + static_cast<long long>(n_blk) * BN + c * 32;
+                store_bf16x32(p.ar_peer_buf[p.ar_rank] + off, v);
+              }
             } else if (m < p.M) {
               float4* d4 = reinterpret_cast<float4*>(dst + c * 32);
 #pragma unroll
@@ -1219,6 +1517,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                            __uint_as_float(r[j * 4 + 2]), __uint_as_float(r[j * 4 + 3])));
             }
           }
+        }
+        if (fused_ar && p.ar_push) {   // the four epilogue warps stored the tile: release its flags
+          epi_bar_sync();
+          ar_push_signal(p, static_cast<int>(threadIdx.x) - 128, ks * p.ar_world + p.ar_rank, m_sup, n_blk, MTE * kBM,
+                         ar_epoch);
         }
       }
 
@@ -1434,7 +1737,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         else
           mbar_arrive(&tmem_empty[acc]);
       }
-      if (tracing && it_cur == 0 && warp == 4 && lane == 0) p.trace[5] = clock64();
+      GLLM_STAMP(it_cur == 0 && warp == 4 && lane == 0, 5);
     }
   }
 
@@ -1449,7 +1752,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     else
       tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
-  if (tracing && threadIdx.x == 0) p.trace[6] = clock64();
+  GLLM_STAMP(threadIdx.x == 0, 6);
 
   if constexpr (BN == 128) {
     if (p.cluster_sk) {
@@ -1459,9 +1762,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float* part = reinterpret_cast<const float*>(tiles);
       cluster_publish_partials(p, part, MT * kBM, m_sup * MT * kBM, n_blk, splits, ks);
       cluster_barrier();   // release / acquire at cluster scope: the members' scratch rows are visible
-      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      GLLM_STAMP(threadIdx.x == 0, 7);
       cluster_reduce_phase<EPI>(p, part, MT * kBM, m_sup * MT * kBM, n_blk, splits, ks);
-      if (tracing && threadIdx.x == 0) p.trace[8] = clock64();
+      GLLM_STAMP(threadIdx.x == 0, 8);
       return;
     }
   }
@@ -1473,7 +1776,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool has_item = static_cast<int>(blockIdx.x) < num_items;   // the fused all-reduce launches every SM
       if (has_item) decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
       const float* part = reinterpret_cast<const float*>(tiles);
-      if (fused_ar) {
+      if (fused_ar && p.ar_push) {
+        if (has_item) ar_push_parked(p, part, MT * kBM, m_sup * MT * kBM, n_blk, ks * p.ar_world + p.ar_rank);
+        __syncthreads();
+        if (has_item) ar_push_signal(p, threadIdx.x, ks * p.ar_world + p.ar_rank, m_sup, n_blk, MT * kBM, ar_epoch);
+      } else if (fused_ar) {
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
         __nv_bfloat16* dst = p.ar_peer_buf[p.ar_rank] + static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems +
                              static_cast<long long>(ks) * p.M * n_pad + static_cast<long long>(n_blk) * BN + lane * 4;
@@ -1494,12 +1801,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
-    if (fused_ar) {
+    if (fused_ar && p.ar_push) {
+      if constexpr (EPI == EPI_RESIDUAL) {
+        GLLM_STAMP(threadIdx.x == 0, 7);
+        ar_push_reduce<BN>(p, ar_epoch, MTE * kBM, abort_flag);
+        ar_push_finish(p, static_cast<unsigned long long>(ar_epoch), ar_launch_s);
+      }
+    } else if (fused_ar) {
       // one arrival per rank once all of that rank's CTAs have published their tiles
       const unsigned long long target = ar_expected_s + static_cast<unsigned long long>(p.ar_world);
       const unsigned long long local_target = ar_local_base_s + gridDim.x;
       const bool ar_ok = ar_barrier(p, target, local_target);
-      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      GLLM_STAMP(threadIdx.x == 0, 7);
       unsigned long long local_done = local_target;
       if constexpr (EPI == EPI_RESIDUAL) {
         const long long part_off = static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems;
@@ -1527,12 +1840,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     } else if (splits > 1) {
       // every partial of every CTA must be visible before anyone reduces
-      const bool bar_ok = grid_barrier(p.sk_barrier, gridDim.x, p.err);
-      if (tracing && threadIdx.x == 0) p.trace[7] = clock64();
+      const bool bar_ok = grid_barrier(p.sk_barrier, gridDim.x, p.err, p.wait_ns);
+      GLLM_STAMP(threadIdx.x == 0, 7);
       if (bar_ok) splitk_reduce_phase<BN, EPI>(p, p.sk_scratch, splits, false);
     }
   }
-  if (tracing && threadIdx.x == 0) p.trace[8] = clock64();
+  GLLM_STAMP(threadIdx.x == 0, 8);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1597,24 +1910,27 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     return -1;
   }
   p.trace = ((g_trace_k == 0 || g_trace_k == p.K) && (g_trace_n == 0 || g_trace_n == p.N)) ? g_trace_ptr : nullptr;
+  const RuntimeSettings& rt = settings();
+  p.wait_ns = rt.wait_ns;
+  p.peer_wait_ns = rt.peer_wait_ns;
   p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
   CUtensorMap ta, tb;
   if (make_tmap_2d(&ta, A, dt, esz, uint64_t(p.M), uint64_t(p.K), uint64_t(lda), kBM, kElemsPerKB)) return -1;
   if (make_tmap_2d(&tb, B, dt, esz, uint64_t(b_rows), uint64_t(p.K), uint64_t(ldb), BN, kElemsPerKB)) return -1;
-  static bool attr_set = false;
+  static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
   auto kern = gemm_tn_kernel<BN, MT, EPI, FP8>;
-  if (!attr_set) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) {
       set_last_error("gemm: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
       return -1;
     }
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
-  int dev = 0;
-  cudaGetDevice(&dev);
   int sms = max_ctas;
   if (sms <= 0) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = p.num_m * p.num_n;
@@ -1623,36 +1939,48 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
   int splits = 1;
   if (p.mblk_group || BN % 128 != 0) force_splits = 1;  // grouped GEMMs have plenty of tiles
-  static const bool park_allowed = [] {
-    const char* v = getenv("GLLM_NO_PARK");
-    return !(v && v[0] == '1');
-  }();
+  const bool park_allowed = rt.park != 0;
   const bool part_fits = static_cast<long long>(MT) * kBM * kClusterPartStride * 4 <= static_cast<long long>(Cfg::kStages) * Cfg::kStageBytes;
   if (p.ar_world > 0) {
     // Fused all-reduce: a rank may split K locally when every work item gets its own CTA (the parked-tile path):
     // split s publishes its bf16 partial in buffer slice s and the pull adds the slices of every rank. Halves the
     // main loop of the decode-sized row-parallel GEMMs (64 tiles on 148 SMs).
     splits = 1;
-    static const bool ar_split_allowed = [] {
-      const char* v = getenv("GLLM_AR_SPLIT");
-      return !(v && v[0] == '0');
-    }();
-    // Only with two ranks: the pull moves (ranks x splits) partial buffers per output element, and from four ranks
-    // on that traffic (every rank reads every rank's buffer) costs more than the shorter main loop saves.
+    const bool ar_split_allowed = rt.ar_split != 0;
+    // Pull forms, only with two ranks: the pull moves (ranks x splits) partial buffers per output element, and from
+    // four ranks on that traffic (every rank reads every rank's buffer) costs more than the shorter main loop saves.
+    // Push form, any rank count: the extra partials travel while the main loops run and are added from local memory.
     if (BN == 128 && park_allowed && part_fits && ar_split_allowed && force_splits <= 0 && p.mblk_group == nullptr &&
-        p.ar_world <= 2) {
+        (p.ar_world <= 2 || p.ar_push)) {
       int sp = sms / (tiles > 0 ? tiles : 1);
       if (sp > 4) sp = 4;
       if (sp > p.num_kb / 8) sp = p.num_kb / 8;
-      while (sp > 1 && sp * out_floats > p.ar_buf_elems) --sp;
+      if (p.ar_push) {
+        // a warp waits with one lane per (source, n tile) flag; the receive slots hold (world x splits) sources
+        while (sp > 1 && p.ar_world * sp * (256 / BN) > 32) --sp;
+        const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
+        while (sp > 1 && static_cast<long long>(p.ar_world) * sp * rows_per * p.num_n * BN > p.ar_buf_elems) --sp;
+      } else {
+        while (sp > 1 && sp * out_floats > p.ar_buf_elems) --sp;
+      }
       if (sp >= 2) splits = sp;
     }
   } else if (force_splits > 0)
     splits = force_splits;
   else if (ws.scratch)
     splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats,
-                           BN == 128 && max_ctas <= 0 && !(getenv("GLLM_NO_CLUSTER_SK") && getenv("GLLM_NO_CLUSTER_SK")[0] == '1'));
-  if (p.ar_world > 0) {
+                           BN == 128 && max_ctas <= 0 && rt.cluster_sk != 0);
+  if (p.ar_world > 0 && p.ar_push) {
+    const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
+    const long long need = static_cast<long long>(p.ar_world) * splits * rows_per * p.num_n * BN;
+    const long long nflags = static_cast<long long>(p.ar_world) * splits * p.num_m * p.num_n;
+    if (need > p.ar_buf_elems || nflags > p.ar_flag_cap || (static_cast<long long>(p.num_n) * BN) % 256 != 0 ||
+        p.ar_world * splits * (256 / BN) > 32) {
+      set_last_error("fused all-reduce (push): needs %lld receive elements (have %lld) and %lld flags (have %lld), "
+                     "padded width %% 256", need, p.ar_buf_elems, nflags, p.ar_flag_cap);
+      return -1;
+    }
+  } else if (p.ar_world > 0) {
     if (splits * out_floats > p.ar_buf_elems || (static_cast<long long>(p.num_n) * BN) % 256 != 0) {
       set_last_error("fused all-reduce: output needs %lld elements per buffer (have %lld), padded width %% 256",
                      splits * out_floats, p.ar_buf_elems);
@@ -1673,10 +2001,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   const int grid = (p.ar_world > 0) ? sms : (items < sms ? items : sms);
   // Cluster split-K: the splits of a tile become one thread-block cluster (one work item per CTA) and reduce through
   // distributed shared memory instead of global scratch + grid barrier.
-  static const bool cluster_allowed = [] {
-    const char* v = getenv("GLLM_NO_CLUSTER_SK");
-    return !(v && v[0] == '1');
-  }();
+  const bool cluster_allowed = rt.cluster_sk != 0;
   if (BN == 128 && cluster_allowed && splits >= 2 && splits <= 8 && items <= sms && part_fits && p.ar_world == 0 &&
       p.mblk_group == nullptr && max_ctas <= 0) {
     p.cluster_sk = 1;
@@ -1685,11 +2010,13 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // Clusters are placed inside one GPC; when the GPC sizes do not let every cluster of this launch run at once the
@@ -1704,6 +2031,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
       max_clusters[splits] = n > 0 ? n : -1;
     }
     if (max_clusters[splits] >= tiles) {
+      cfg.numAttrs = rt.pdl ? 2 : 1;
       cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
       if (ce == cudaSuccess) return 0;
       (void)cudaGetLastError();   // this cluster shape cannot be scheduled here: fall back
@@ -1712,9 +2040,9 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   }
   p.park = (BN == 128 && park_allowed && (splits > 1 || p.ar_world > 0) && items <= grid && part_fits &&
             p.mblk_group == nullptr) ? 1 : 0;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, true, 0, ta, tb, p);
   if (e != cudaSuccess) {
+    (void)cudaGetLastError();
     set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
     return -1;
   }
@@ -1728,21 +2056,12 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
 // At prefill sizes (M = 8192) 256 x 256 pair tiles run 1.4-3.5 % faster than 256 x 256 single-CTA tiles (plain
 // 1333 vs 1288 TFLOP/s, residual 1324 vs 1292, gate/up 1340 vs 1321), so 256-wide launches with M >= g_pair_big_m
 // use them too; the one-head-per-tile QKV GEMM does not (729 vs 948 TFLOP/s).
-static int g_pair_max_m = -1;   // -1: not read yet
-static int g_pair_epi_mask = 0;
-static int g_pair_big_m = 1024;
-static int pair_max_m_setting() {
-  if (g_pair_max_m < 0) {
-    const char* on = getenv("GLLM_PAIR");          // "0": off; "1": every epilogue; unset: the default mask
-    const char* m = getenv("GLLM_PAIR_MAX_M");
-    g_pair_max_m = (on && on[0] == '0') ? 0 : (m ? atoi(m) : 256);
-    if (on && on[0] == '1') g_pair_epi_mask = 0xF;
-    const char* big = getenv("GLLM_PAIR_BIG_M");    // 0: no pairs at prefill sizes
-    if (big) g_pair_big_m = atoi(big);
-    if (on && on[0] == '0') g_pair_big_m = 0;
-  }
-  return g_pair_max_m;
-}
+// (settings pair_max_m / pair_epi_mask / pair_big_m of RuntimeSettings; the Python layer maps the GLLM_PAIR* environment
+// variables onto them when it loads the library)
+#define g_pair_max_m (settings().pair_max_m)
+#define g_pair_epi_mask (settings().pair_epi_mask)
+#define g_pair_big_m (settings().pair_big_m)
+static int pair_max_m_setting() { return settings().pair_max_m; }
 
 // CTA-pair launch (clusters of two, `tcgen05.mma.cta_group::2`): a work item is a 256-row x BN tile. Per 64-deep K
 // block each SM ingests 16 KB of A and BN/2 rows of B instead of 32 KB + BN rows for a 256-row single-CTA tile, and the
@@ -1758,6 +2077,9 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
     return -1;
   }
   p.trace = ((g_trace_k == 0 || g_trace_k == p.K) && (g_trace_n == 0 || g_trace_n == p.N)) ? g_trace_ptr : nullptr;
+  const RuntimeSettings& rt = settings();
+  p.wait_ns = rt.wait_ns;
+  p.peer_wait_ns = rt.peer_wait_ns;
   p.num_m = (p.M + 2 * kBM - 1) / (2 * kBM);
   p.num_n = (p.N + BN - 1) / BN;
   p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
@@ -1767,26 +2089,28 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
   if (make_tmap_2d(&ta, A, dt, 2, uint64_t(p.M), uint64_t(p.K), uint64_t(lda), kBM, kElemsPerKB)) return -1;
   if (make_tmap_2d(&tb, B, dt, 2, uint64_t(b_rows), uint64_t(p.K), uint64_t(ldb), BN / 2, kElemsPerKB)) return -1;
   auto kern = gemm_tn_kernel<BN, 1, EPI, false, true>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) {
       set_last_error("gemm (pair): cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
       return -1;
     }
-    attr_set = true;
+    attr_set[dev & 63] = true;
   }
-  int dev = 0;
-  cudaGetDevice(&dev);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   // how many pairs can be resident at once (the split-K grid barrier needs every CTA of the launch running)
@@ -1827,6 +2151,7 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
   const int items = tiles * splits;
   const int pairs = items < max_pairs ? items : max_pairs;
   cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.numAttrs = rt.pdl ? 2 : 1;
   cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
   if (ce != cudaSuccess) {
     (void)cudaGetLastError();
@@ -1878,11 +2203,7 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
   if constexpr (EPI == EPI_QKV) {
     // The QKV epilogue needs one head (128 columns) per tile, so its tiles cannot widen; 256 rows per CTA is what
     // lets a weight tile serve twice the MMAs at prefill sizes too.
-    static const bool wide = [] {
-      const char* v = getenv("GLLM_QKV_TWO_ROWS");
-      return !(v && v[0] == '0');
-    }();
-    if (wide && p.M > 128) two_rows = true;
+    if (settings().qkv_two_rows && p.M > 128) two_rows = true;
   }
   if constexpr (EPI == EPI_GLU) {
     // 192-wide tiles: 128 tiles for a 24576-row gate/up weight fill one wave of 148 SMs without splitting
@@ -1976,17 +2297,13 @@ GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B
 // pulls every row), 1 = two-shot (each rank pulls its 1/W of the rows and broadcasts them). Every rank must use the same
 // setting; the symmetric buffer must hold three regions of `buf_elems` (two partial buffers and the result region).
 constexpr int kTwoShotMinWorld = 8;
-static int g_ar_two_shot = -2;   // -2: not read yet
 static bool ar_two_shot_setting(int world) {
-  if (g_ar_two_shot == -2) {
-    const char* v = getenv("GLLM_AR_TWO_SHOT");
-    g_ar_two_shot = v ? atoi(v) : -1;
-  }
-  return g_ar_two_shot < 0 ? world >= kTwoShotMinWorld : g_ar_two_shot != 0;
+  const int v = settings().ar_two_shot;
+  return v < 0 ? world >= kTwoShotMinWorld : v != 0;
 }
 GLLM_API int gllm_gemm_set_ar_two_shot(int mode) {
-  const int old = g_ar_two_shot == -2 ? -1 : g_ar_two_shot;
-  g_ar_two_shot = mode;
+  const int old = settings().ar_two_shot;
+  settings().ar_two_shot = mode;
   return old;
 }
 
@@ -2023,6 +2340,55 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce(const void* A, long long lda, con
   p.ar_two_shot = (world >= 2 && ar_two_shot_setting(world)) ? 1 : 0;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
+}
+
+// Push form of the same fused op (see GemmParams::ar_push): no meeting before data moves. Each rank's symmetric
+// region (`peer_base[r]`, all mapped by every rank; `mc_base` its multicast alias or null) holds, at the given
+// offsets from its base: the receive slots (`recv_elems` bf16 at `recv_off` BYTES), the tile flags (`flag_count`
+// u32, zero at start, at `flag_off` bytes) and the done words (8 u64, zero at start, at `done_off` bytes). `out`
+// (which is also the residual: the op is x <- x + sum) and `row_ss_out` [M, ceil(N/256)] must themselves lie inside
+// this rank's region, at the same offset on every rank: the owner of a row stores the finished row and its
+// statistics into every rank's copy. `state`: 8 local u64, zero at start. Every rank issues the same calls in the
+// same order. Waits are bounded by the `peer_wait_ns` setting and report ERR_TIMEOUT_PEER in the status word.
+GLLM_API int gllm_gemm_bf16_residual_allreduce_push(const void* A, long long lda, const void* B, long long ldb,
+                                                    void* out, long long ldo, float* row_ss_out, int M, int N, int K,
+                                                    const float* bias, int bn, void* stream, int world, int rank,
+                                                    void* mc_base, void* const* peer_base, long long region_bytes,
+                                                    long long recv_off, long long recv_elems, long long flag_off,
+                                                    long long flag_count, long long done_off,
+                                                    unsigned long long* state) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !out) {
+    set_last_error("gemm_allreduce_push: bad world/rank/pointers (world %d rank %d)", world, rank);
+    return -1;
+  }
+  const char* base = static_cast<const char*>(peer_base[rank]);
+  const long long out_off = static_cast<const char*>(out) - base;
+  const long long ss_off = row_ss_out ? reinterpret_cast<const char*>(row_ss_out) - base : 0;
+  const long long groups = (N + 255) / 256;
+  if (out_off < 0 || out_off + (static_cast<long long>(M - 1) * ldo + N) * 2 > region_bytes || (out_off & 15) ||
+      (row_ss_out && (ss_off < 0 || ss_off + static_cast<long long>(M) * groups * 4 > region_bytes || (ss_off & 3)))) {
+    set_last_error("gemm_allreduce_push: out / row_ss_out must lie inside the symmetric region (16-byte aligned)");
+    return -1;
+  }
+  if ((recv_off & 15) || (flag_off & 3) || (done_off & 7) || recv_off + recv_elems * 2 > region_bytes ||
+      flag_off + flag_count * 4 > region_bytes || done_off + 64 > region_bytes) {
+    set_last_error("gemm_allreduce_push: bad region layout");
+    return -1;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(out); p.ldr = ldo; p.row_ss_out = row_ss_out;
+  p.ar_world = world; p.ar_rank = rank; p.ar_mc_buf = static_cast<__nv_bfloat16*>(mc_base);
+  for (int r = 0; r < world; ++r) p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(peer_base[r]);
+  p.ar_state = state;
+  p.ar_push = 1;
+  p.ar_recv_off = recv_off / 2; p.ar_buf_elems = recv_elems;
+  p.ar_out_off = out_off / 2; p.ar_ss_off = ss_off;
+  p.ar_flag_off = flag_off; p.ar_flag_cap = flag_count; p.ar_done_off = done_off;
+  p.ar_drop_flags = settings().ar_drop_flags;
+  p.err = gllm_error_word();
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, 0, 0);
 }
 
 // out[M,N/2] = act(rowscale*gate) * rowscale*up ; B is the tile-interleaved gate/up weight [N,K]:
@@ -2077,6 +2443,13 @@ GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const 
 // Debugging aid: CTA 0 of every following GEMM launch writes 9 SM-clock stamps to `buf` (device memory, 9 x int64):
 // entry, set-up done, first stage landed, MMAs of the first item issued, first accumulator ready, first epilogue
 // done, main loop left, split-K barrier passed, exit. Pass null to switch it off.
+GLLM_API int gllm_gemm_trace_enabled() {   // 1 when the library was built with -DGLLM_TRACE
+#ifdef GLLM_TRACE
+  return 1;
+#else
+  return 0;
+#endif
+}
 GLLM_API void gllm_gemm_set_trace(long long* buf) { g_trace_ptr = buf; }
 GLLM_API void gllm_gemm_set_trace_k(int k) { g_trace_k = k; }
 GLLM_API void gllm_gemm_set_trace_n(int n) { g_trace_n = n; }

@@ -32,6 +32,18 @@
  *   block_tables  [batch, max_blocks] int32, ctx_lens [batch] int32 (<= 0 marks an empty slot)
  *   sinks         [n_q_heads] fp32 or NULL; window 0 = full attention; stream is a cudaStream_t
  * Returns 0 on success.
+ *
+ * Errors found by the kernel itself (a block-table entry outside the pool is redirected to page 0, a
+ * context longer than the block table is cut to it, a page copy that never arrives is abandoned after a
+ * bounded wait) do not show in that return value: the launch is asynchronous. They are recorded in a
+ * status word of this path's own, separate from the one gllm_check_error() reads.
+ * gllm_paged_decode_noalloc_status(stream) copies that word to the host on `stream`, WAITS for the
+ * stream, and returns it (0 = no problem; otherwise one of the library's status codes: 1 page copy timed
+ * out, 6 page id outside the pool, 9 context longer than the block table; -1 if the read itself failed).
+ * A non-zero word is cleared by the read, so one bad call is reported once. It allocates nothing either.
+ * Call it after the calls you want checked, outside any stream capture.
+ *
+ * The first call on a device may come from any thread: the one-time set-up is guarded by a mutex.
  */
 #ifndef GLLM_NOALLOC_H_
 #define GLLM_NOALLOC_H_
@@ -47,6 +59,8 @@ int gllm_paged_decode_noalloc(const void* q, void* out, const void* kv_cache, in
                               const int* block_tables, int max_blocks, const int* ctx_lens, int batch,
                               int n_q_heads, int n_kv_heads, float scale, int pages_per_split, int max_splits,
                               int window, const float* sinks, void* stream);
+
+int gllm_paged_decode_noalloc_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -13,6 +13,11 @@ namespace gllm {
 
 static thread_local char g_last_error[512] = {0};
 
+RuntimeSettings& settings() {
+  static RuntimeSettings s;
+  return s;
+}
+
 const char* last_error() { return g_last_error; }
 
 void set_last_error(const char* fmt, ...) {
@@ -132,6 +137,16 @@ GLLM_API int* gllm_error_word() {
   return g_err_words[dev];
 }
 
+// Makes caller-owned device memory (at least 4 zeroed bytes, alive for the rest of the process) the error word of the
+// current device, so that a host runtime can copy it back together with its own results instead of paying a separate
+// synchronising read. Kernels launched (or graphs captured) before the call keep reporting to the old word.
+GLLM_API int gllm_set_error_word(int* word) {
+  int dev = 0;
+  if (!word || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  g_err_words[dev] = word;
+  return 0;
+}
+
 // Reads and clears the error word (synchronises the device).
 GLLM_API int gllm_check_error() {
   int* w = gllm_error_word();
@@ -153,4 +168,40 @@ GLLM_API int gllm_sm_count() {
   return g_sm_count[dev];
 }
 
-GLLM_API int gllm_kernels_abi_version() { return 1; }
+GLLM_API int gllm_kernels_abi_version() { return 2; }
+
+// Library settings by name (see RuntimeSettings in common.cuh). gllm_set_option returns the previous value, or
+// LLONG_MIN for an unknown name; a change applies to launches made after it.
+static long long* option_slot(const char* name, long long* tmp, int** as_int) {
+  RuntimeSettings& s = settings();
+  *as_int = nullptr;
+  if (!strcmp(name, "wait_ns")) return reinterpret_cast<long long*>(&s.wait_ns);
+  if (!strcmp(name, "peer_wait_ns")) return reinterpret_cast<long long*>(&s.peer_wait_ns);
+  struct { const char* n; int* v; } ints[] = {
+      {"pdl", &s.pdl}, {"park", &s.park}, {"cluster_sk", &s.cluster_sk}, {"ar_split", &s.ar_split},
+      {"qkv_two_rows", &s.qkv_two_rows}, {"ar_drop_flags", &s.ar_drop_flags}, {"pair_max_m", &s.pair_max_m},
+      {"pair_epi_mask", &s.pair_epi_mask}, {"pair_big_m", &s.pair_big_m}, {"ar_two_shot", &s.ar_two_shot}};
+  for (auto& e : ints)
+    if (!strcmp(name, e.n)) {
+      *as_int = e.v;
+      *tmp = *e.v;
+      return tmp;
+    }
+  return nullptr;
+}
+GLLM_API long long gllm_get_option(const char* name) {
+  long long tmp = 0;
+  int* as_int = nullptr;
+  long long* slot = name ? option_slot(name, &tmp, &as_int) : nullptr;
+  return slot ? *slot : (-0x7fffffffffffffffLL - 1);
+}
+GLLM_API long long gllm_set_option(const char* name, long long value) {
+  long long tmp = 0;
+  int* as_int = nullptr;
+  long long* slot = name ? option_slot(name, &tmp, &as_int) : nullptr;
+  if (!slot) return -0x7fffffffffffffffLL - 1;
+  const long long old = *slot;
+  if (as_int) *as_int = static_cast<int>(value);
+  else *slot = value;
+  return old;
+}

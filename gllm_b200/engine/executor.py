@@ -93,6 +93,14 @@ class LLMEngine:
         self.d_params = torch.zeros((self.ms, 4), dtype=torch.float32, device=dev)
         self.d_out = torch.zeros(self.ms, dtype=torch.int32, device=dev)
         self.d_offsets = torch.zeros(self.ms, dtype=torch.int64, device=dev)
+        # the kernels' status word (bounded-wait timeouts, bad page / expert ids): copied to pinned memory with every
+        # step's tokens and checked before the tokens are committed
+        self.d_status = None
+        self.h_status = torch.zeros(16, dtype=torch.int32, **pin)
+        if cuda:
+            from ..ops import _native as nv
+            self.d_status = nv.error_word_tensor(dev)
+        self.unhealthy: Optional[str] = None
         self.slot_params = np.zeros((self.ms, 4), dtype=np.float32)
         # Split the KV range of a sequence across CTAs only when (sequences x kv heads) alone cannot fill
         # the machine: an unsplit flash-decode CTA streams its pages at full speed, splits add a merge
@@ -252,8 +260,10 @@ class LLMEngine:
                 self._decode_body(B)
         else:
             self._decode_body(B)
+        if self.d_status is not None:
+            self.h_status.copy_(self.d_status, non_blocking=True)      # lands before the blocking copy below returns
         self.h_out.copy_(self.d_out, non_blocking=False)
-        self.stats["d2h_bytes"] += self.h_out.numel() * 4
+        self.stats["d2h_bytes"] += self.h_out.numel() * 4 + (64 if self.d_status is not None else 0)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += int(plan.num_decode)
         return self.h_out.numpy()
@@ -333,9 +343,37 @@ class LLMEngine:
         out = torch.empty(len(last_rows), dtype=torch.int32, device=dev)
         self._sample(logits, params, offs, out)
         self.d_offsets.index_add_(0, sl.to(dev), torch.ones(len(last_rows), dtype=torch.int64, device=dev))
+        if self.d_status is not None:
+            self.h_status.copy_(self.d_status, non_blocking=True)
         res = out.cpu().numpy()
         self.stats["d2h_bytes"] += res.size * 4
         return res
+
+    # ------------------------------------------------------------------------------------------
+    def _device_status(self) -> int:
+        """Status word as of the last step's download (0 = every kernel finished cleanly)."""
+        return int(self.h_status[0])
+
+    def _check_device_status(self, plan):
+        """A kernel that gave up a bounded wait (a peer rank that stalled) or met a bad page id leaves garbage behind.
+        Nothing of such a step is committed: the running requests fail, the engine is marked unhealthy (a tensor-
+        parallel rank must be re-synchronised with ``tp.reset()`` on every rank before it serves again) and the
+        caller gets an exception instead of tokens."""
+        code = self._device_status()
+        if code == 0:
+            return
+        from ..ops import _native as nv
+        if self.d_status is not None:
+            self.d_status.zero_()
+        self.h_status.zero_()
+        name = nv.ERROR_NAMES.get(code, "?")
+        self.unhealthy = f"device status {code} ({name})"
+        failed = list(self.reqs)          # waiting ones too: this rank serves nothing until it is re-synchronised
+        for rid in failed:
+            self._vetoed[rid] = f"error: rank unhealthy, {name}"
+        self._collect()
+        METRICS.inc("device_status_errors")
+        raise nv.DeviceStatusError(code, f"in engine step; {len(failed)} request(s) failed")
 
     # ------------------------------------------------------------------------------------------
     def step(self) -> List[GenerateResult]:
@@ -358,6 +396,7 @@ class LLMEngine:
         if plan.num_prefill_seqs > 0:
             with nvtx_range("prefill_chunk"):
                 pf_tokens = self._run_prefill(plan)
+        self._check_device_status(plan)
         METRICS.set("kv_free_pages", float(self.batcher.num_free_pages))
         METRICS.set("running_requests", float(len(self.reqs)))
         now = time.perf_counter()
@@ -433,6 +472,7 @@ class LLMEngine:
                 self._empty_prefill()
         if plan.idle:
             return self._collect()
+        self._check_device_status(plan)
         now = time.perf_counter()
         ids = plan.dec_seq_ids
         for sl in np.nonzero(ids >= 0)[0]:

@@ -38,7 +38,11 @@ class Workspace:
         T = max_tokens
         self.max_tokens = T
         H = c.hidden_size
-        self.x = torch.zeros((T, H), dtype=dt, device=dev)
+        # With the push form of the fused tensor-parallel all-reduce the row owner stores finished rows into every
+        # rank's residual stream, so `x` and the norm statistics live inside the symmetric region of the TP context.
+        sym = model.tp.workspace_buffers(T) if (model.tp is not None and hasattr(model.tp, "workspace_buffers")) else None
+        self.symmetric = sym is not None
+        self.x = sym["x"] if sym else torch.zeros((T, H), dtype=dt, device=dev)
         self.h = torch.zeros((T, H), dtype=dt, device=dev)
         self.q = torch.zeros((T, model.attn_width), dtype=dt, device=dev)
         self.attn = torch.zeros((T, model.attn_width), dtype=dt, device=dev)
@@ -49,8 +53,8 @@ class Workspace:
         self.gu = None if model.fused else torch.zeros((T, 2 * inter), dtype=dt, device=dev)
         self.parts = max(1, (H + 127) // 128)     # room for the narrowest tile width of the residual GEMMs
         self.ss0 = torch.zeros((T, 1), dtype=torch.float32, device=dev)
-        self.ss_a = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
-        self.ss_b = torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
+        self.ss_a = sym["ss_a"] if sym else torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
+        self.ss_b = sym["ss_b"] if sym else torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
         self.partial = torch.zeros((T, H), dtype=dt, device=dev) if model.tp_size > 1 else None
 
 
@@ -74,7 +78,9 @@ class DecoderModel:
         if weight_quant is not None:
             fused = False        # quantised linears run through the dequantising GEMM; epilogue fusions need bf16 weights
         self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and self.device.type == "cuda"
-        if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size):
+        if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size) or (
+                cfg.num_kv_heads < self.tp_size and self.tp_size % cfg.num_kv_heads):
+            # with fewer KV heads than ranks each KV head is replicated over tp / num_kv_heads ranks (pack_attention)
             raise ValueError(f"heads {cfg.num_heads}/{cfg.num_kv_heads} not divisible by tp={self.tp_size}")
         self.n_q_local = cfg.num_heads // self.tp_size
         self.n_kv_local = max(1, cfg.num_kv_heads // self.tp_size)

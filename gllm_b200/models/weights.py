@@ -105,6 +105,14 @@ class RandomWeights:
         if c.is_mla:
             table["o_proj"] = (H, c.num_heads * c.v_head_dim)
             table["q_proj"] = (c.num_heads * (c.qk_nope_head_dim + c.qk_rope_head_dim), H)
+        if c.norm_type == "layer" or c.kind != "chat":     # encoder checkpoints (BERT / XLM-R style) and their heads
+            I = c.intermediate_size
+            table.update({
+                "position_embeddings": (c.max_position_embeddings, H), "token_type_embeddings": (max(c.type_vocab_size, 1), H),
+                "embed_norm": (H,), "embed_norm_bias": (H,), "post_ffn_norm": (H,), "post_attn_norm_bias": (H,),
+                "post_ffn_norm_bias": (H,), "o_proj_bias": (H,), "up_proj_bias": (I,), "down_proj_bias": (H,),
+                "pooler": (H, H), "pooler_bias": (H,), "classifier": (max(getattr(c, "num_labels", 0) or 1, 1), H),
+                "classifier_bias": (max(getattr(c, "num_labels", 0) or 1, 1),)})
         if base in table:
             return table[base]
         inter = c.intermediate_size
@@ -139,6 +147,14 @@ class RandomWeights:
             return not c.tie_word_embeddings
         if base in ("q_norm", "k_norm"):
             return c.qk_norm
+        if base in ("classifier", "classifier_bias"):
+            return (getattr(c, "num_labels", 0) or 0) > 0
+        if base in ("token_type_embeddings",):
+            return c.type_vocab_size > 0
+        if base in ("up_proj_bias", "down_proj_bias"):
+            return bool(getattr(c, "mlp_bias", False))
+        if base.endswith("norm_bias"):
+            return c.norm_type == "layer"
         if base.endswith("_bias"):
             return c.attention_bias
         try:
@@ -216,14 +232,23 @@ def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: 
         return empty, None, None, None, wo.contiguous(), src.get(p + "input_norm").float().contiguous(), \
             cfg.num_heads // world, 0
     sh = lambda n: shard_tensor(n, src.get(p + n), rank, world, head_dim=D)
-    q, k, v = sh("q_proj"), sh("k_proj"), sh("v_proj")
+    if cfg.num_kv_heads < world:
+        # Fewer KV heads than ranks: a KV head is replicated over the world / num_kv_heads ranks whose query heads use
+        # it. Rank r holds query heads [r * Hq/world, ...), all of which belong to KV head r * Hkv // world.
+        if world % cfg.num_kv_heads:
+            raise ValueError(f"kv heads {cfg.num_kv_heads} must divide tp={world} to be replicated")
+        kvh = rank * cfg.num_kv_heads // world
+        kv_sh = lambda n: src.get(p + n)[kvh * D:(kvh + 1) * D].contiguous()
+    else:
+        kv_sh = sh
+    q, k, v = sh("q_proj"), kv_sh("k_proj"), kv_sh("v_proj")
     wqkv = torch.cat([q, k, v], 0)
     input_norm = src.get(p + "input_norm").float()
     if fused:
         wqkv = _fold(wqkv, input_norm, cfg.norm_one_plus_w)
     bias = None
     if cfg.attention_bias and src.has(p + "q_proj_bias"):
-        bias = torch.cat([sh("q_proj_bias"), sh("k_proj_bias"), sh("v_proj_bias")]).float().contiguous()
+        bias = torch.cat([sh("q_proj_bias"), kv_sh("k_proj_bias"), kv_sh("v_proj_bias")]).float().contiguous()
     qn = src.get(p + "q_norm").float().contiguous() if cfg.qk_norm else None
     kn = src.get(p + "k_norm").float().contiguous() if cfg.qk_norm else None
     wo = sh("o_proj")

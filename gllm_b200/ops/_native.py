@@ -20,6 +20,7 @@ P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
 _SIGNATURES = {
     "gllm_last_error": (ctypes.c_char_p, []),
     "gllm_error_word": (P, []),
+    "gllm_set_error_word": (I, [P]),
     "gllm_check_error": (I, []),
     "gllm_sm_count": (I, []),
     "gllm_kernels_abi_version": (I, []),
@@ -29,6 +30,10 @@ _SIGNATURES = {
     "gllm_gemm_set_pair": (I, [I, I]),
     "gllm_gemm_set_pair_big_m": (I, [I]),
     "gllm_gemm_bf16_residual_allreduce": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, I, I, P, P, P, P, P, L]),
+    "gllm_gemm_bf16_residual_allreduce_push": (I, [P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, P, P, L, L, L, L, L, L, P]),
+    "gllm_set_option": (L, [ctypes.c_char_p, L]),
+    "gllm_get_option": (L, [ctypes.c_char_p]),
+    "gllm_gemm_trace_enabled": (I, []),
     "gllm_gemm_bf16_glu": (I, [P, L, P, L, P, L, I, I, I, I, P, I, F, F, I, P, I, P, I, I]),
     "gllm_gemm_bf16_grouped": (I, [P, L, P, L, P, L, I, I, I, P, I, I, P, I]),
     "gllm_gemm_bf16_qkv": (I, [P, L, P, L, I, I, I, I, P, P, I, P, P, P, P, I, P, P, F, P, I, F, F, P, P, I, I]),
@@ -90,7 +95,60 @@ def lib():
             fn.restype = res
             fn.argtypes = args
         _lib = handle
+        _apply_env_options(handle)
     return _lib
+
+
+# Environment variables that map onto library settings (read once, when the library is loaded). The native code itself
+# reads no environment variable.
+_ENV_OPTIONS = (
+    ("GLLM_PDL", "pdl", int), ("GLLM_AR_SPLIT", "ar_split", int), ("GLLM_QKV_TWO_ROWS", "qkv_two_rows", int),
+    ("GLLM_AR_TWO_SHOT", "ar_two_shot", int), ("GLLM_PAIR_MAX_M", "pair_max_m", int), ("GLLM_PAIR_BIG_M", "pair_big_m", int),
+    ("GLLM_WAIT_NS", "wait_ns", int), ("GLLM_PEER_WAIT_NS", "peer_wait_ns", int),
+)
+
+
+def _apply_env_options(handle):
+    import os
+    env = os.environ
+    for var, name, conv in _ENV_OPTIONS:
+        if env.get(var, "") != "":
+            handle.gllm_set_option(name.encode(), conv(env[var]))
+    if env.get("GLLM_NO_PARK") == "1":
+        handle.gllm_set_option(b"park", 0)
+    if env.get("GLLM_NO_CLUSTER_SK") == "1":
+        handle.gllm_set_option(b"cluster_sk", 0)
+    pair = env.get("GLLM_PAIR")          # "0": no CTA pairs anywhere; "1": every epilogue at decode sizes
+    if pair == "0":
+        handle.gllm_set_option(b"pair_max_m", 0)
+        handle.gllm_set_option(b"pair_big_m", 0)
+    elif pair == "1":
+        handle.gllm_set_option(b"pair_epi_mask", 0xF)
+
+
+def set_option(name: str, value: int) -> int:
+    """Set a library setting (``RuntimeSettings`` in csrc/kernels/common.cuh); returns the previous value."""
+    old = int(lib().gllm_set_option(name.encode(), int(value)))
+    if old == -(1 << 63):
+        raise KeyError(f"unknown kernel-library option {name!r}")
+    return old
+
+
+def get_option(name: str) -> int:
+    v = int(lib().gllm_get_option(name.encode()))
+    if v == -(1 << 63):
+        raise KeyError(f"unknown kernel-library option {name!r}")
+    return v
+
+
+def set_wait_limits_ns(local_ns: int = None, peer_ns: int = None):
+    """Limits of the kernels' bounded waits (on-chip barriers / flags written by another GPU). Returns the old pair."""
+    old = (get_option("wait_ns"), get_option("peer_wait_ns"))
+    if local_ns is not None:
+        set_option("wait_ns", local_ns)
+    if peer_ns is not None:
+        set_option("peer_wait_ns", peer_ns)
+    return old
 
 
 def register(name, restype, argtypes, optional=False):
@@ -133,6 +191,33 @@ ERROR_NAMES = {
     5: "timeout waiting for a peer rank", 6: "page id outside the pool", 7: "expert id out of range",
     8: "timeout waiting for another CTA", 9: "bad argument",
 }
+
+
+_err_tensors = {}
+
+
+def error_word_tensor(device):
+    """The device's error word as a torch int32 tensor (allocated once per device and registered with the library),
+    so that an engine can copy it to pinned memory on its own stream next to the step's results. Call it before any
+    CUDA graph is captured: kernels captured earlier keep reporting to the previous word."""
+    import torch
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _err_tensors.get(idx)
+    if t is None:
+        with torch.cuda.device(idx):
+            t = torch.zeros(16, dtype=torch.int32, device=device)
+            if lib().gllm_set_error_word(t.data_ptr()) != 0:
+                raise RuntimeError("could not register the error word")
+        _err_tensors[idx] = t
+    return t
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel reported a bounded-wait timeout or a bad index through the device status word."""
+
+    def __init__(self, code: int, where: str = ""):
+        self.code = code
+        super().__init__(f"device kernel reported status {code} ({ERROR_NAMES.get(code, '?')}) {where}".rstrip())
 
 
 def raise_on_device_error(where: str = ""):

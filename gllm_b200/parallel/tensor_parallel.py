@@ -3,17 +3,26 @@
 
 The reference does every TP collective on host f32 slices through its NCCL wrapper
 (src/engine/coordinator/compute.rs:122-436: tp_all_reduce / tp_reduce_scatter / tp_all_gather,
-src/engine/distributed_config.rs:424-495). Here the row-parallel GEMM and its all-reduce are ONE kernel
-(``gllm_gemm_bf16_residual_allreduce``): each rank stores its bf16 partial tiles into its own symmetric
-buffer as the tcgen05 tiles retire, all CTAs of all ranks meet at an arrival counter, and every rank then
-pulls the sum of all partials — one ``multimem.ld_reduce`` per 16 bytes, added in fp32 inside NVSwitch, when
-the buffer has a multicast mapping, otherwise plain peer loads over NVLink — and finishes locally (residual
-add, bf16 store, next norm's row statistics). Bulk data never goes through atomics: accumulating partial
-tiles with ``red``/``multimem.red`` was measured at roughly 20x the time of this pull design. The NCCL path (unfused GEMM -> ncclAllReduce -> residual/norm-stat kernel) is kept as the
-selectable baseline.
+src/engine/distributed_config.rs:424-495). Here the row-parallel GEMM and its all-reduce are ONE kernel, in two
+forms:
 
-Modes: ``fused`` (multimem if available, else peer loads), ``fused_p2p`` (force peer loads), ``nccl``,
-``auto`` (fused when symmetric memory can be set up, else nccl).
+``push`` (default, ``gllm_gemm_bf16_residual_allreduce_push``): rank r owns the output rows
+[r * ceil(M/W), ...). As each tcgen05 tile retires, its bf16 rows are stored straight into the owner's receive
+slots with peer stores over NVLink and a per-tile flag is released; the owner's warps wait tile by tile (no meeting
+of all ranks before data moves), add the sources in a fixed order, add the residual and store the finished rows and
+their norm statistics into EVERY rank's activation buffer (one ``multimem.st`` per 16 bytes through NVSwitch, or a
+store per peer). The activation buffer ``x`` and the statistics therefore live inside the symmetric region
+(``workspace_buffers``); a caller's ordinary tensor is staged through it. The kernel ends with one exchange of
+per-rank "done" words.
+
+``pull`` (``gllm_gemm_bf16_residual_allreduce``): every rank stores its partial tiles in its own symmetric buffer,
+all ranks meet at an arrival counter, and every rank pulls the sum (``multimem.ld_reduce`` or peer loads), one-shot
+or two-shot. Kept for comparison.
+
+The NCCL path (unfused GEMM -> ncclAllReduce -> residual/norm-stat kernel) is the selectable baseline.
+
+Modes: ``auto`` (push when symmetric memory can be set up, else nccl), ``fused`` (push; multimem if available),
+``fused_p2p`` (push, peer stores only), ``pull`` / ``pull_p2p``, ``nccl``.
 """
 from __future__ import annotations
 
@@ -25,75 +34,158 @@ import torch
 from .. import ops
 from ..ops import _native as nv
 
+_FLAG_COUNT = 32768      # u32 tile flags of the push form
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
 
 class TPContext:
     def __init__(self, rank: int, size: int, device, *, mode: str = "auto", max_tokens: int = 1024, hidden: int = 4096,
-                 group=None, max_fused_tokens: int = 1024):
+                 group=None, max_fused_tokens: Optional[int] = None):
         self.rank, self.size, self.device = rank, size, torch.device(device)
         self.group = group
         self.requested_mode = mode
         self.mode = "nccl"
+        self.form = "none"            # "push" | "pull" once the fused kernel is set up
         self.uses_multimem = False
-        self.max_fused_tokens = min(max_fused_tokens, max_tokens)
+        self.max_tokens = max_tokens
+        self.hidden = hidden
+        # pull form: its three buffers are sized for decode batches only
+        self.max_fused_tokens = min(max_fused_tokens or (1024 if mode.startswith("pull") else max_tokens), max_tokens)
         self.fused_max_k = 1 << 30      # `auto` mode: longest local K that still takes the fused kernel
         self.n_pad = ((hidden + 255) // 256) * 256
         self.buf_elems = self.max_fused_tokens * self.n_pad
         self._symm = None
         self._handle = None
-        if mode in ("auto", "fused", "fused_p2p") and self.device.type == "cuda":
+        self.baseline = False           # True: run the NCCL path although the fused one is set up (bench baseline arm)
+        if mode in ("auto", "fused", "fused_p2p", "pull", "pull_p2p") and self.device.type == "cuda":
             try:
-                self._setup_symmetric(force_p2p=(mode == "fused_p2p"))
+                self.form = "pull" if mode.startswith("pull") else "push"
+                self._setup_symmetric(force_p2p=mode.endswith("_p2p"))
                 self.mode = "fused"
             except Exception as exc:  # no NVLink peer access / symmetric memory unavailable
                 if mode != "auto":
                     raise
                 self.setup_error = repr(exc)
-                self.mode = "nccl"
+                self.mode, self.form = "nccl", "none"
 
     # ------------------------------------------------------------------------------------------
+    def _layout(self):
+        """Byte offsets of the regions inside the symmetric allocation (identical on every rank)."""
+        T, W = self.max_tokens, self.size
+        parts = (self.hidden + 127) // 128
+        off, lay = 0, {}
+
+        def take(name, nbytes):
+            nonlocal off
+            lay[name] = (off, nbytes)
+            off = _align(off + nbytes)
+        if self.form == "push":
+            recv_rows = max(T + 8, min(4 * (T + 8), 4160))     # room for K splits inside a rank at decode sizes
+            take("recv", recv_rows * self.n_pad * 2)
+            take("x", T * self.hidden * 2)
+            for name in ("ss0", "ss_a", "ss_b", "ss_stage"):
+                take(name, T * parts * 4)
+            take("flags", _FLAG_COUNT * 4)
+            take("done", 64)
+        else:
+            take("pull", 3 * self.buf_elems * 2)
+            take("counters", 64)
+        lay["_total"] = (off, 0)
+        return lay
+
     def _setup_symmetric(self, force_p2p: bool):
         import torch.distributed as dist
-        total = 3 * self.buf_elems + 64     # two alternating partial buffers, the two-shot result region, counters
+        lay = self._layout()
+        total = lay["_total"][0]
         if self.size == 1:
-            buf = torch.zeros(total, dtype=torch.bfloat16, device=self.device)
+            buf = torch.zeros(total, dtype=torch.uint8, device=self.device)
             peer_ptrs, mc_ptr = [buf.data_ptr()], 0
         else:
             import torch.distributed._symmetric_memory as symm_mem
             group = self.group or dist.group.WORLD
-            buf = symm_mem.empty(total, dtype=torch.bfloat16, device=self.device)
+            buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
             self._handle = symm_mem.rendezvous(buf, group.group_name)
             buf.zero_()
             torch.cuda.synchronize(self.device)
             dist.barrier(group=group)
             peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
             mc_ptr = 0 if force_p2p else int(getattr(self._handle, "multicast_ptr", 0) or 0)
-        self._symm = buf
+        self._symm, self._lay, self._total = buf, lay, total
+        self._base = buf.data_ptr()
         self.uses_multimem = mc_ptr != 0
-        counter_off = 3 * self.buf_elems * 2  # bytes; 8-byte aligned because buf_elems is a multiple of 256
         n = len(peer_ptrs)
-        self._peer_acc = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
-        self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
-        self._mc_acc = mc_ptr or None
-        self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
+        self._mc_base = mc_ptr or None
+        self._peer_base = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
         self._state = torch.zeros(8, dtype=torch.int64, device=self.device)
+        if self.form == "pull":
+            off = lay["pull"][0]
+            counter_off = off + 3 * self.buf_elems * 2
+            self._peer_acc = (ctypes.c_void_p * 8)(*([p + off for p in peer_ptrs] + [None] * (8 - n)))
+            self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
+            self._mc_acc = (mc_ptr + off) if mc_ptr else None
+            self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
+
+    def _view(self, name, dtype, shape):
+        off, nbytes = self._lay[name]
+        n = 1
+        for d in shape:
+            n *= d
+        return self._symm[off:off + n * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(*shape)
+
+    def workspace_buffers(self, tokens: int):
+        """Activation buffer and norm-statistics buffers inside the symmetric region, for a model whose residual
+        stream the push kernel updates on every rank. None when the push form is not in use or ``tokens`` exceeds
+        what the region was sized for."""
+        if self.mode != "fused" or self.form != "push" or tokens > self.max_tokens:
+            return None
+        parts = (self.hidden + 127) // 128
+        return dict(x=self._view("x", torch.bfloat16, (self.max_tokens, self.hidden))[:tokens],
+                    ss0=self._view("ss0", torch.float32, (self.max_tokens, parts))[:tokens],
+                    ss_a=self._view("ss_a", torch.float32, (self.max_tokens, parts))[:tokens],
+                    ss_b=self._view("ss_b", torch.float32, (self.max_tokens, parts))[:tokens])
+
+    def _inside(self, t) -> bool:
+        return self._base <= t.data_ptr() and t.data_ptr() + t.numel() * t.element_size() <= self._base + self._total
 
     # ------------------------------------------------------------------------------------------
     def gemm_allreduce_residual(self, a, w, x, ss_out, partial, *, bn: int = 256):
         """x <- sum_ranks(a @ w.T) + x ; returns the tensor holding the row statistics of the new x."""
         M, K = a.shape
         N = w.shape[0]
-        # The fused kernel publishes one partial per tile (no split of K inside the rank). Measured on B200 at
-        # Qwen3-8B shapes, decode batch 256 (tokens/s fused vs unfused GEMM + NCCL all-reduce): 2 ranks 21.8k vs
-        # 20.1k, 4 ranks 28.5k vs 25.6k, 8 ranks 31.6k vs 27.8k: fused is ahead everywhere, so `auto` always takes
-        # it; `fused_max_k` stays as a knob.
         k_ok = self.requested_mode != "auto" or K <= self.fused_max_k
-        if self.mode == "fused" and k_ok and M <= self.max_fused_tokens and N <= self.n_pad:
+        fused = self.mode == "fused" and not self.baseline and k_ok and N <= self.n_pad
+        if fused and self.form == "push" and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:
             parts = (N + 255) // 256  # the fused kernel reports statistics per 256-column group
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
                 raise ValueError("row statistics buffer must be [tokens, parts] contiguous")
-            # few output tiles: prefer 128-wide tiles so more SMs stream weights (the pull phase works on
-            # 256-column groups either way)
+            staged = not (self._inside(x) and self._inside(ss))
+            xs, sss = x, ss
+            if staged:      # a caller's ordinary tensors: run on the symmetric staging buffers
+                xs = self._view("x", torch.bfloat16, (self.max_tokens, self.hidden))[:M, :N]
+                xs.copy_(x)
+                sss = self._view("ss_stage", torch.float32, (self.max_tokens * ((self.hidden + 127) // 128),))[:M * parts].view(M, parts)
+            # few output tiles: 128-wide tiles so that more SMs stream weights
+            tile_bn = 256 if (N // 256) * ((M + 127) // 128) >= 148 else 128
+            lay = self._lay
+            rc = nv.lib().gllm_gemm_bf16_residual_allreduce_push(
+                a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), xs.data_ptr(), xs.stride(0), sss.data_ptr(), M, N, K,
+                None, tile_bn, nv.stream_ptr(), self.size, self.rank, self._mc_base,
+                ctypes.cast(self._peer_base, ctypes.c_void_p), self._total, lay["recv"][0], lay["recv"][1] // 2,
+                lay["flags"][0], _FLAG_COUNT, lay["done"][0], self._state.data_ptr())
+            nv.check(rc, "gemm_bf16_residual_allreduce_push")
+            if staged:
+                x.copy_(xs)
+                ss.copy_(sss)
+            return ss
+        if fused and self.form == "pull" and M <= self.max_fused_tokens:
+            parts = (N + 255) // 256
+            ss = ss_out[:M, :parts]
+            if not ss.is_contiguous():
+                raise ValueError("row statistics buffer must be [tokens, parts] contiguous")
             tile_bn = 256 if (N // 256) * ((M + 127) // 128) >= 148 else 128
             rc = nv.lib().gllm_gemm_bf16_residual_allreduce(
                 a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), x.data_ptr(),
@@ -111,6 +203,22 @@ class TPContext:
         ss = ss_out.reshape(-1)[:M].view(M, 1)
         ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
         return ss
+
+    def reset(self):
+        """Clear the flags, done words and launch state after a failed launch (collective: every rank calls it)."""
+        import torch.distributed as dist
+        torch.cuda.synchronize(self.device)
+        if self.size > 1:
+            dist.barrier(group=self.group)
+        if self.mode == "fused":
+            for name in ("flags", "done", "counters"):
+                if name in self._lay:
+                    off, nbytes = self._lay[name]
+                    self._symm[off:off + nbytes].zero_()
+            self._state.zero_()
+        torch.cuda.synchronize(self.device)
+        if self.size > 1:
+            dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------------------------------
     def sample_vocab_parallel(self, logits, vocab_local, vocab_start, params, seed, offsets, out, vocab, greedy=True):
@@ -150,7 +258,8 @@ class TPContext:
         self._handle = None
 
 
-def single_gpu_context(device, hidden: int, max_tokens: int = 1024) -> TPContext:
-    """A world-size-1 context on ordinary device memory: exercises the fused kernel's protocol (alternating
-    buffers, arrival counter, launch state) on one GPU."""
-    return TPContext(0, 1, device, mode="fused_p2p", max_tokens=max_tokens, hidden=hidden)
+def single_gpu_context(device, hidden: int, max_tokens: int = 1024, mode: str = "fused_p2p") -> TPContext:
+    """A world-size-1 context on ordinary device memory: exercises the fused kernel's protocol (receive slots, tile
+    flags, done words, launch state; or, with ``mode="pull_p2p"``, alternating buffers and arrival counters) on one
+    GPU."""
+    return TPContext(0, 1, device, mode=mode, max_tokens=max_tokens, hidden=hidden)

@@ -120,3 +120,35 @@ def test_coordinators_and_backend_context():
     co.inference.drain()
     assert len(eng.results[rid].token_ids) == 3 and co.model_ctx.config is cfg
     assert co.kv.plan()["store_heads"] == list(range(cfg.num_kv_heads))
+
+
+def test_engine_step_raises_on_a_device_status_code_and_fails_the_requests():
+    """The serving path consults the kernels' status word every step: a non-zero code (injected on the host here) fails
+    the running requests instead of committing the step's tokens, and the engine says why."""
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.ops._native import DeviceStatusError
+    cfg = preset("tiny-qwen3")
+    model = DecoderModel(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=0), device="cpu", dtype=torch.float32,
+                         max_positions=128)
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=4, max_model_len=64, max_batch_tokens=64, prefill_chunk=64))
+    a = eng.add_request([5, 6, 7, 8], max_tokens=4, temperature=0.0, eos_ids=[])
+    b = eng.add_request([9, 10, 11], max_tokens=4, temperature=0.0, eos_ids=[])
+    eng.step()                                     # prefill
+    eng.step()                                     # one clean decode step
+    eng.h_status[0] = 5                            # what a timed-out wait for a peer rank leaves behind
+    real = eng._run_decode
+
+    def run_decode_keeping_status(plan):           # the download of a real step would overwrite the injected word
+        out = real(plan)
+        eng.h_status[0] = 5
+        return out
+    eng._run_decode = run_decode_keeping_status
+    with pytest.raises(DeviceStatusError, match="peer rank"):
+        eng.step()
+    assert eng.unhealthy and "5" in eng.unhealthy
+    assert not eng.reqs                            # nothing keeps running on a rank in this state
+    ra, rb = eng.results[a], eng.results[b]
+    assert ra.finish_reason.startswith("error: rank unhealthy") and rb.finish_reason.startswith("error")
+    assert len(ra.token_ids) <= 2                  # the faulty step's tokens were not committed

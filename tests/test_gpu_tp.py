@@ -14,11 +14,21 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_fused_allreduce_world1_protocol():
+def _rows_close(got, ref, what=""):
+    """Per-row relative check: an error confined to a few rows or one tile column must not hide behind the maximum."""
+    got, ref = got.float(), ref.float()
+    row_err = (got - ref).abs().amax(-1)
+    row_ref = ref.abs().amax(-1).clamp_min(1e-3)
+    bad = (row_err > 0.03 * row_ref + 0.02).nonzero().flatten()
+    assert bad.numel() == 0, f"{what}: rows {bad[:8].tolist()} off by {row_err[bad[:8]].tolist()}"
+
+
+@pytest.mark.parametrize("mode", ["fused_p2p", "pull_p2p"])
+def test_fused_allreduce_world1_protocol(mode):
     from gllm_b200.parallel.tensor_parallel import single_gpu_context
     dev = torch.device("cuda")
     H = 1024
-    tp = single_gpu_context(dev, hidden=H, max_tokens=512)
+    tp = single_gpu_context(dev, hidden=H, max_tokens=512, mode=mode)
     assert tp.mode == "fused" and not tp.uses_multimem
     torch.manual_seed(0)
     for it, (M, K) in enumerate([(256, 512), (100, 2048), (256, 512), (37, 1536), (512, 4096)]):
@@ -29,14 +39,69 @@ def test_fused_allreduce_world1_protocol():
         ss_buf = torch.zeros(512, H // 256, device=dev)
         part = torch.empty(512, H, device=dev, dtype=torch.bfloat16)
         ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, part, bn=256)
-        err = (x.float() - ref.float()).abs().max().item()
-        assert err < 0.05 * ref.float().abs().max().item(), (it, err)
+        _rows_close(x, ref, f"launch {it}")
         torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
     assert int(tp._state[1]) == 5  # five launches advanced the launch state five times
 
 
+def test_push_allreduce_in_place_on_symmetric_buffers():
+    """The serving path: x and the statistics live inside the symmetric region, nothing is staged."""
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H = 2048
+    tp = single_gpu_context(dev, hidden=H, max_tokens=1024)
+    bufs = tp.workspace_buffers(1024)
+    torch.manual_seed(1)
+    for M, K in [(256, 1024), (1024, 512), (33, 2048)]:
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(H, K, device=dev) * 0.05).to(torch.bfloat16)
+        x = bufs["x"][:M]
+        x.copy_(torch.randn(M, H, device=dev).to(torch.bfloat16))
+        ref = (a.float() @ w.float().t() + x.float()).to(torch.bfloat16)
+        ss = tp.gemm_allreduce_residual(a, w, x, bufs["ss_a"][:M].reshape(-1)[:M * (H // 256)].view(M, H // 256), None)
+        _rows_close(x, ref, f"M={M}")
+        torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+
+
+def test_push_allreduce_wait_runs_out_and_context_recovers():
+    """A wait on a flag that nothing sets ends after the configured limit with a status code, the host sees it, and
+    the next launch works (the permitted form of a failure test: nothing faults, traps or spins without a limit)."""
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H, M, K = 1024, 64, 512
+    tp = single_gpu_context(dev, hidden=H, max_tokens=256)
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(H, K, device=dev) * 0.05).to(torch.bfloat16)
+    x0 = torch.randn(M, H, device=dev).to(torch.bfloat16)
+    ss_buf = torch.zeros(256, H // 256, device=dev)
+    old = nv.set_wait_limits_ns(peer_ns=20_000_000)        # 20 ms
+    nv.set_option("ar_drop_flags", 1)                      # the producers leave their tile flags unset
+    try:
+        x = x0.clone()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        tp.gemm_allreduce_residual(a, w, x, ss_buf, None)
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 2000.0                # it returned, and soon
+        with pytest.raises(RuntimeError, match="timeout waiting for a peer"):
+            nv.raise_on_device_error("after the dropped flags")
+    finally:
+        nv.set_option("ar_drop_flags", 0)
+        nv.set_wait_limits_ns(*old)
+    tp.reset()
+    x = x0.clone()
+    ref = (a.float() @ w.float().t() + x0.float()).to(torch.bfloat16)
+    tp.gemm_allreduce_residual(a, w, x, ss_buf, None)
+    torch.cuda.synchronize()
+    _rows_close(x, ref, "after recovery")
+    assert nv.device_error() == 0
+
+
 @pytest.mark.multigpu
-@pytest.mark.parametrize("mode", ["fused_p2p", "fused", "nccl", "fused_two_shot", "fused_p2p_two_shot"])
+@pytest.mark.parametrize("mode", ["fused_p2p", "fused", "nccl", "pull", "pull_p2p", "pull_two_shot", "pull_p2p_two_shot"])
 def test_fused_allreduce_two_gpus(mode):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",

@@ -307,6 +307,17 @@ def test_tp_attention_with_expert_sharded_moe_matches_unsplit_model():
     assert r.stdout.count("TP_MOE_WORKER_OK") == 2
 
 
+@pytest.mark.parametrize("heads,kv", [(8, 2), (4, 4)])
+def test_tp4_dense_decoder_matches_unsplit_model_with_replicated_kv_heads(heads, kv):
+    """Four gloo ranks; with 2 KV heads each KV head is held by the two ranks whose query heads use it."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", str(29801 + kv), os.path.join(ROOT, "tests", "tp_dense_worker.py"), str(heads), str(kv)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_DENSE_WORKER_OK") == 4
+
+
 def test_lockstep_engines_with_expert_parallel_moe_match_unsplit_engine():
     """Two serving engines, each with its own requests, share the expert-parallel MoE; outputs equal the plain engine's."""
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")

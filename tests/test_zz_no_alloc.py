@@ -26,7 +26,14 @@ def _load():
     fn.restype = I
     fn.argtypes = [P, P, P, I, P, I, P, I, I, I, F, I, I, I, P, P]
     lib.gllm_last_error.restype = ctypes.c_char_p
+    lib.gllm_paged_decode_noalloc_status.restype = I
+    lib.gllm_paged_decode_noalloc_status.argtypes = [P]
     return lib, fn
+
+
+def _status(lib):
+    """The path's own status word (read-and-clear; waits for the stream)."""
+    return lib.gllm_paged_decode_noalloc_status(torch.cuda.current_stream().cuda_stream)
 
 
 def _case(seed, ctx, n_q, n_kv, dev):
@@ -67,6 +74,25 @@ def test_noalloc_decode_matches_regular_entry_point_twice():
         oracle = ops.attention_ref(q, kv, bt, torch.arange(len(ctx), dtype=torch.int32, device=dev),
                                    (cl > 0).int(), cl, n_q, n_kv, 128 ** -0.5)
         assert (out.float() - oracle.float()).abs().max().item() < 2e-2 * (oracle.float().abs().max().item() + 1e-6)
+        assert _status(lib) == 0, "the kernel recorded a problem on a well-formed call"
+
+
+def test_noalloc_status_reports_a_bad_page_once():
+    """A block-table entry outside the pool is redirected to page 0 and recorded in the path's status word; the read
+    clears it, and the regular status word (the one the other tests' fixture checks) stays untouched."""
+    from gllm_b200.ops import _native as nv
+    dev = torch.device("cuda")
+    lib, fn = _load()
+    q, kv, bt, cl = _case(9, [40, 20], 8, 2, dev)
+    bt[0, 1] = kv.shape[0] + 7          # outside the pool
+    out = torch.zeros_like(q)
+    rc = fn(q.data_ptr(), out.data_ptr(), kv.data_ptr(), kv.shape[0], bt.data_ptr(), bt.shape[1], cl.data_ptr(),
+            q.shape[0], 8, 2, 128 ** -0.5, 4, 1, 0, None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert _status(lib) == 6            # ERR_BAD_PAGE
+    assert _status(lib) == 0            # cleared by the read
+    assert torch.isfinite(out.float()).all()
+    assert nv.device_error() == 0
 
 
 def test_noalloc_decode_rejects_oversize():
