@@ -142,6 +142,13 @@ __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorM
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), credited to an mbarrier.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -191,6 +198,52 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// ---- block-scaled MMAs: every 32- (mxf8f6f4) or 16-element (mxf4nvf4, scale_vec::4X) slice along K of both operands is
+// multiplied by its scale factor inside the tensor core. The scale factors sit in tensor memory: for 128 rows, four
+// 32-bit columns; lane r % 32 of every 32-lane quarter holds, in column r / 32, the four consecutive scale bytes of
+// row r (the layout tcgen05.cp.32x128b.warpx4 produces from a 512-byte chunk whose byte
+// (r % 32) * 16 + (r / 32) * 4 + j is scale j of row r). mxf8f6f4 uses one byte per row and MMA: which one is the
+// "scale factor id" in the instruction descriptor (bits 4-5 for B, 29-30 for A). N = 256 reads eight columns.
+__device__ __forceinline__ void umma_mxf8_bs(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void umma_nvf4_bs(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(
+          d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// 512 contiguous bytes of shared memory (32 rows of 16 bytes) -> four tensor-memory columns, the same data in all
+// four 32-lane quarters.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Shared-memory descriptor of such a chunk: no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(16 >> 4) << 16;    // leading byte offset (one 16-byte column: not stepped over)
+  d |= static_cast<uint64_t>(128 >> 4) << 32;   // stride byte offset: next group of 8 rows
+  d |= static_cast<uint64_t>(1) << 46;          // descriptor version (sm_100)
+  return d;                                     // layout type 0: no swizzle
+}
+// Instruction descriptor of the block-scaled kinds: A and B K-major, fp32 accumulate (implied).
+// ab_fmt: mxf8f6f4 0 = e4m3; mxf4nvf4 1 = e2m1. sf_fmt: 0 = ue4m3, 1 = ue8m0. Scale-factor ids are or-ed in per MMA.
+__host__ __device__ constexpr uint32_t umma_idesc_bs(int m, int n, int ab_fmt, int sf_fmt) {
+  return (static_cast<uint32_t>(ab_fmt) << 7) | (static_cast<uint32_t>(ab_fmt) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(sf_fmt) << 23) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 // Arrive on an mbarrier once every previously issued tcgen05.mma of this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

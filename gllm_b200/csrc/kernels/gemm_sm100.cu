@@ -80,6 +80,11 @@ struct GemmParams {
   // per-row / per-column dequant scales (fp8 path), nullable
   const float* a_scale;
   const float* b_scale;
+  // block-scaled operands (OPM_MXFP8 / OPM_NVFP4): scale-factor chunks of A and B, and one factor for the whole
+  // product (NVFP4's per-tensor scales); out_scale == 0 means 1
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  float out_scale;
   // GLU
   int glu_act;  // 0 = silu, 1 = gelu_tanh
   // grouped GEMM: 128-row m-block -> group id; B rows of group g start at g * group_rows
@@ -142,19 +147,43 @@ struct GemmParams {
   int* err;
 };
 
-template <int BN, int MT, bool PAIR = false>
+// Operand modes of the kernel (template parameter OPM; the two first values are what `false` / `true` of the former
+// boolean meant):
+//   0  bf16 x bf16                      tcgen05.mma.kind::f16
+//   1  e4m3 x e4m3, scales in the epilogue (per row / per column)   kind::f8f6f4
+//   2  MXFP8: e4m3 x e4m3, one ue8m0 scale per 32 elements along K of both operands   kind::mxf8f6f4.block_scale
+//   3  NVFP4: e2m1 x e2m1 (two per byte), one ue4m3 scale per 16 elements             kind::mxf4nvf4.block_scale.scale_vec::4X
+// In modes 2 and 3 the scale factors of a (128 rows x one 128-byte K block) piece of an operand are one contiguous
+// chunk of global memory in the layout the tensor core wants (see sf_chunk_offset in the host code): the producer
+// brings the chunks into the stage with bulk copies, the MMA thread moves them to tensor memory with tcgen05.cp and
+// issues the block-scaled MMAs, which multiply every 32- (16-) element slice by its two scales in hardware.
+enum : int { OPM_BF16 = 0, OPM_FP8 = 1, OPM_MXFP8 = 2, OPM_NVFP4 = 3 };
+constexpr int kSfChunkBytes = 512;   // scale factors of 128 rows x 4 consecutive scale columns
+
+template <int BN, int MT, bool PAIR = false, int OPM = 0>
 struct GemmCfg {
+  static constexpr bool kBlockScaled = OPM >= OPM_MXFP8;
+  static constexpr int kSfChunks = OPM == OPM_MXFP8 ? 1 : (OPM == OPM_NVFP4 ? 4 : 0);   // chunks per 128 rows and stage
+  static constexpr int kSfABytes = MT * kSfChunks * kSfChunkBytes;
+  static constexpr int kSfBBytes = (BN / 128) * kSfChunks * kSfChunkBytes;
   // PAIR: each CTA of a pair stages its own 128 rows of A and half of the B tile's rows
-  static constexpr int kStageBytes = MT * kBM * kTileKBytes + (PAIR ? BN / 2 : BN) * kTileKBytes;
+  static constexpr int kTileBytes = MT * kBM * kTileKBytes + (PAIR ? BN / 2 : BN) * kTileKBytes;
+  static constexpr int kTxBytes = kTileBytes + kSfABytes + kSfBBytes;        // bytes that arrive per stage
+  static constexpr int kStageBytes = (kTxBytes + 1023) / 1024 * 1024;         // stages stay 1024-byte aligned (swizzle atoms)
   static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
-  static constexpr int kAccStages = (2 * MT * BN <= 512) ? 2 : 1;
-  static constexpr int kCols = kAccStages * MT * BN;
+  // tensor-memory columns of the scale factors: two buffers (stage parity) of [A: MT x chunks x 4 | B: BN/128 x chunks x 4]
+  static constexpr int kSfColsA = MT * kSfChunks * 4;
+  static constexpr int kSfColsB = (BN / 128) * kSfChunks * 4;
+  static constexpr int kSfCols = 2 * (kSfColsA + kSfColsB);
+  static constexpr int kAccStages = (2 * MT * BN + kSfCols <= 512) ? 2 : 1;
+  static_assert(!kBlockScaled || (MT * BN + kSfCols <= 512 && BN % 128 == 0 && !PAIR), "block-scaled tile does not fit tensor memory");
+  static constexpr int kCols = kAccStages * MT * BN + kSfCols;
   static constexpr int kTmemCols = kCols <= 32 ? 32 : (kCols <= 64 ? 64 : (kCols <= 128 ? 128 : (kCols <= 256 ? 256 : 512)));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*align slack*/;
 };
 
 __device__ __forceinline__ float row_scale_of(const GemmParams& p, int m) {
-  if (p.row_ss_in == nullptr) return 1.0f;
+  if (p.row_ss_in == nullptr) return p.out_scale != 0.f ? p.out_scale : 1.0f;
   float ss = 0.f;
   const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
   if ((p.ss_in_parts & 3) == 0 && (reinterpret_cast<uintptr_t>(p.row_ss_in) & 15) == 0) {
@@ -165,18 +194,18 @@ __device__ __forceinline__ float row_scale_of(const GemmParams& p, int m) {
   } else {
     for (int i = 0; i < p.ss_in_parts; ++i) ss += src[i];
   }
-  return rsqrtf(ss * p.norm_inv_dim + p.norm_eps);
+  return rsqrtf(ss * p.norm_inv_dim + p.norm_eps) * (p.out_scale != 0.f ? p.out_scale : 1.0f);
 }
 // The same for a whole warp working on one row: the partial sums are spread over the lanes (one load + a warp
 // reduction instead of up to 32 dependent loads per unit; measured: the QKV reduce phase of the serving step went
 // from 45.6 k clocks with 32 partials per row).
 __device__ __forceinline__ float row_scale_warp(const GemmParams& p, int m, int lane) {
-  if (p.row_ss_in == nullptr) return 1.0f;
+  if (p.row_ss_in == nullptr) return p.out_scale != 0.f ? p.out_scale : 1.0f;
   const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
   float ss = 0.f;
   for (int i = lane; i < p.ss_in_parts; i += 32) ss += __ldg(src + i);
   ss = warp_sum(ss);
-  return rsqrtf(ss * p.norm_inv_dim + p.norm_eps);
+  return rsqrtf(ss * p.norm_inv_dim + p.norm_eps) * (p.out_scale != 0.f ? p.out_scale : 1.0f);
 }
 
 __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32]) {
@@ -1215,12 +1244,16 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
   }
 }
 
-template <int BN, int MT, int EPI, bool FP8, bool PAIR = false>
+template <int BN, int MT, int EPI, int FP8 /* operand mode, OPM_* */, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
   static_assert(!PAIR || (MT == 1 && !FP8), "CTA pairs: one 128-row block per CTA, bf16");
-  using Cfg = GemmCfg<BN, MT, PAIR>;
+  using Cfg = GemmCfg<BN, MT, PAIR, FP8>;
+  constexpr bool kBS = Cfg::kBlockScaled;
+  constexpr int kTxBytes = Cfg::kTxBytes;
+  constexpr int kSfAOff = Cfg::kTileBytes;                       // scale chunks inside a stage: A's, then B's
+  constexpr int kSfBOff = Cfg::kTileBytes + Cfg::kSfABytes;
   // CTA pair (launched as clusters of two): one work item is a 256-row x BN tile; the even CTA issues the MMAs for
   // both, each CTA loads its own operand halves and finishes its own 128 accumulator rows.
   constexpr int MTE = PAIR ? 2 : MT;          // 128-row blocks per work item
@@ -1291,8 +1324,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         decode_item(work_id, ks, m_sup, n_blk, kb0, kb1);
         const int n_pre = min(kStages, kb1 - kb0);
         for (int i = 0; i < n_pre; ++i) {
-          mbar_expect_tx(&full_bar[i], kStageBytes);
+          mbar_expect_tx(&full_bar[i], kTxBytes);
           tma_load_2d(tiles + i * kStageBytes + MT * kABytes, &tmap_b, &full_bar[i], (kb0 + i) * kElemsPerKB, n_blk * BN);
+          if constexpr (kBS) {
+#pragma unroll
+            for (int blk = 0; blk < BN / 128; ++blk)
+              bulk_load(tiles + i * kStageBytes + kSfBOff + blk * Cfg::kSfChunks * kSfChunkBytes,
+                        p.sfb + (static_cast<long long>(n_blk * (BN / 128) + blk) * p.num_kb + (kb0 + i)) *
+                                    (Cfg::kSfChunks * kSfChunkBytes),
+                        Cfg::kSfChunks * kSfChunkBytes, &full_bar[i]);
+          }
         }
         b_prefetched = n_pre;
       }
@@ -1356,11 +1397,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else {
             const bool b_done = b_prefetched > 0;   // the first stages' weight halves were requested before pdl_wait
             if (b_done) --b_prefetched;
-            else mbar_expect_tx(&full_bar[stage], kStageBytes);
+            else mbar_expect_tx(&full_bar[stage], kTxBytes);
 #pragma unroll
             for (int i = 0; i < MT; ++i)
               tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
             if (!b_done) tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
+            if constexpr (kBS) {
+              constexpr int kChunkBytes = Cfg::kSfChunks * kSfChunkBytes;   // scale factors of 128 rows for this K block
+#pragma unroll
+              for (int i = 0; i < MT; ++i)
+                bulk_load(sa + kSfAOff + i * kChunkBytes,
+                          p.sfa + (static_cast<long long>(m_sup * MT + i) * p.num_kb + kb) * kChunkBytes, kChunkBytes,
+                          &full_bar[stage]);
+              if (!b_done) {
+#pragma unroll
+                for (int blk = 0; blk < BN / 128; ++blk)
+                  bulk_load(sa + kSfBOff + blk * kChunkBytes,
+                            p.sfb + (static_cast<long long>(b_row / 128 + blk) * p.num_kb + kb) * kChunkBytes, kChunkBytes,
+                            &full_bar[stage]);
+              }
+            }
           }
           if (++stage == kStages) {
             stage = 0;
@@ -1373,11 +1429,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = umma_idesc(PAIR ? 2 * kBM : kBM, BN, FP8 ? 0 : 1, FP8 ? 0 : 1);
+      constexpr uint32_t idesc = kBS ? umma_idesc_bs(kBM, BN, FP8 == OPM_NVFP4 ? 1 : 0, FP8 == OPM_MXFP8 ? 1 : 0)
+                                     : umma_idesc(PAIR ? 2 * kBM : kBM, BN, FP8 ? 0 : 1, FP8 ? 0 : 1);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      [[maybe_unused]] uint32_t sf_flip = 0;   // block-scaled modes: which of the two scale-factor column buffers is next
       for (int t = work_id; t < num_items && ok; t += work_stride) {
         int ks, m_sup, n_blk, kb0, kb1;
         decode_item(t, ks, m_sup, n_blk, kb0, kb1);
@@ -1400,6 +1458,42 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           GLLM_STAMP(it_cur == 0 && kb == kb0, 2);
           const uint32_t sa = smem_u32(tiles + stage * kStageBytes);
           const uint64_t b_desc = umma_desc_sw128(sa + MT * kABytes);
+          if constexpr (kBS) {
+            // scale factors: shared memory -> tensor memory (one of two column buffers, by stage parity), then the
+            // block-scaled MMAs; tcgen05.cp and tcgen05.mma of one thread run in issue order
+            constexpr int kCh = Cfg::kSfChunks;
+            const uint32_t sf_t = tmem_base + kAcc * (MT * BN) + (sf_flip & 1) * (Cfg::kSfColsA + Cfg::kSfColsB);
+            ++sf_flip;
+            const uint32_t sfb_t = sf_t + Cfg::kSfColsA;
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+              for (int j = 0; j < kCh; ++j)
+                tmem_cp_sf(sf_t + (i * kCh + j) * 4, umma_desc_sf(sa + kSfAOff + (i * kCh + j) * kSfChunkBytes));
+#pragma unroll
+            for (int blk = 0; blk < BN / 128; ++blk)
+#pragma unroll
+              for (int j = 0; j < kCh; ++j)
+                tmem_cp_sf(sfb_t + (j * (BN / 128) + blk) * 4, umma_desc_sf(sa + kSfBOff + (blk * kCh + j) * kSfChunkBytes));
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+              const uint64_t a_desc = umma_desc_sw128(sa + i * kABytes);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+                if constexpr (FP8 == OPM_MXFP8) {
+                  // one scale per row and MMA (32 elements): byte k of the 32-bit scale columns of this K block
+                  umma_mxf8_bs(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k,
+                               idesc | (static_cast<uint32_t>(k) << 4) | (static_cast<uint32_t>(k) << 29), accum,
+                               sf_t + i * 4, sfb_t);
+                } else {
+                  // four scales per row and MMA (64 elements in 16s): chunk k of this K block
+                  umma_nvf4_bs(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum, sf_t + (i * kCh + k) * 4,
+                               sfb_t + k * (BN / 128) * 4);
+                }
+              }
+            }
+          } else {
 #pragma unroll
           for (int i = 0; i < MT; ++i) {
             const uint64_t a_desc = umma_desc_sw128(sa + i * kABytes);
@@ -1413,6 +1507,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               else
                 umma_f16(d_tmem + i * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, accum);
             }
+          }
           }
           if constexpr (PAIR) {   // the stage is free in both CTAs once these MMAs retire
             umma_commit_pair(smem_u32(&empty_bar[stage]));
@@ -1894,10 +1989,10 @@ static int choose_splits(int tiles, int num_kb, int stage_bytes, long long tile_
   return best_s;
 }
 
-template <int BN, int MT, int EPI, bool FP8>
+template <int BN, int MT, int EPI, int FP8>
 static int launch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows, GemmParams p,
                        cudaStream_t stream, int max_ctas, int force_splits) {
-  using Cfg = GemmCfg<BN, MT>;
+  using Cfg = GemmCfg<BN, MT, false, FP8>;
   constexpr int kElemsPerKB = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -1915,10 +2010,20 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   p.peer_wait_ns = rt.peer_wait_ns;
   p.num_m = (p.M + MT * kBM - 1) / (MT * kBM);
   p.num_n = (p.N + BN - 1) / BN;
-  p.num_kb = (p.K + kElemsPerKB - 1) / kElemsPerKB;
+  // tensor-map columns: elements for bf16 / fp8, BYTES for the packed 4-bit operands (two elements per byte)
+  const int kcols = (FP8 == OPM_NVFP4) ? p.K / 2 : p.K;
+  p.num_kb = (kcols + kElemsPerKB - 1) / kElemsPerKB;
+  if (Cfg::kBlockScaled) {
+    if (!p.sfa || !p.sfb || kcols % 128 != 0 || ((reinterpret_cast<uintptr_t>(p.sfa) | reinterpret_cast<uintptr_t>(p.sfb)) & 15) ||
+        (p.mblk_group && p.group_rows % 128 != 0)) {
+      set_last_error("block-scaled gemm: needs 16-byte aligned scale chunks, K a multiple of %d, expert rows %% 128",
+                     FP8 == OPM_NVFP4 ? 256 : 128);
+      return -1;
+    }
+  }
   CUtensorMap ta, tb;
-  if (make_tmap_2d(&ta, A, dt, esz, uint64_t(p.M), uint64_t(p.K), uint64_t(lda), kBM, kElemsPerKB)) return -1;
-  if (make_tmap_2d(&tb, B, dt, esz, uint64_t(b_rows), uint64_t(p.K), uint64_t(ldb), BN, kElemsPerKB)) return -1;
+  if (make_tmap_2d(&ta, A, dt, esz, uint64_t(p.M), uint64_t(kcols), uint64_t(lda), kBM, kElemsPerKB)) return -1;
+  if (make_tmap_2d(&tb, B, dt, esz, uint64_t(b_rows), uint64_t(kcols), uint64_t(ldb), BN, kElemsPerKB)) return -1;
   static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
   auto kern = gemm_tn_kernel<BN, MT, EPI, FP8>;
   int dev = 0;
@@ -2164,9 +2269,24 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
 // Dispatch on (tile width, rows per CTA). Small M uses 256-row CTA tiles so a weight tile is pulled
 // into shared memory once for the whole batch; large M keeps 128 x 256 tiles with a double-buffered
 // accumulator so the epilogue overlaps the next main loop.
-template <int EPI, bool FP8>
+// Block-scaled operands: 128 x 128 and 256 x 128 (two accumulators share a weight tile) tiles, or 128 x 256 tiles at
+// prefill sizes (tensor memory holds the accumulators and the scale-factor columns).
+template <int EPI, int OPM>
+static int dispatch_gemm_bs(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
+                            const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
+  const bool rows2 = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr;
+  if constexpr (EPI != EPI_QKV) {
+    if (bn == 256 && !rows2) return launch_gemm<256, 1, EPI, OPM>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+  }
+  if (rows2 || (EPI == EPI_QKV && p.M > 128))
+    return launch_gemm<128, 2, EPI, OPM>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+  return launch_gemm<128, 1, EPI, OPM>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
+}
+
+template <int EPI, int FP8>
 static int dispatch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
                          const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
+  static_assert(FP8 < OPM_MXFP8, "block-scaled modes go through dispatch_gemm_bs");
   if constexpr (!FP8) {
     // decode-sized M: CTA pairs (gllm_gemm_set_pair / GLLM_PAIR / GLLM_PAIR_MAX_M choose where they are used)
     const int pair_max_m = pair_max_m_setting();
@@ -2438,6 +2558,87 @@ GLLM_API int gllm_gemm_bf16_grouped_scatter(const void* A, long long lda, const 
   p.err = gllm_error_word();
   const long long b_rows = static_cast<long long>(num_groups) * N;
   return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, b_rows, p, bn, (cudaStream_t)stream, max_ctas, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Block-scaled GEMMs (MXFP8 / NVFP4 operands on kind::mxf8f6f4 / kind::mxf4nvf4 with hardware scale factors).
+// One entry point with an argument block (the Python side fills a ctypes.Structure of the same layout); `epi`
+// selects the epilogue, and the fields of the other epilogues are ignored. Operands:
+//   a  [M, K] codes: e4m3 bytes (fmt 2) or packed e2m1, two per byte, low nibble first (fmt 3); lda / ldb in BYTES
+//   b  [N, K] (grouped: num_groups stacked) in the same format
+//   sfa / sfb  scale factors in 512-byte chunks: chunk (row block rb = row / 128, scale-column block cb) sits at
+//              (rb * chunks_per_row_block + cb) * 512 and holds scale (row r, column 4 * cb + j) at byte
+//              (r % 32) * 16 + ((r % 128) / 32) * 4 + j; rows padded to 128, K to 128 (fmt 2) / 256 (fmt 3) elements;
+//              fmt 2: ue8m0, one per 32 elements; fmt 3: ue4m3, one per 16 elements
+//   out_scale  factor for the whole product (NVFP4's per-tensor scales), 0 = 1
+// ---------------------------------------------------------------------------------------------
+struct GllmBsGemmArgs {
+  const void* a; long long lda; const void* sfa;
+  const void* b; long long ldb; const void* sfb;
+  void* out; long long ldo;
+  int M, N, K, fmt, epi, out_f32, bn, max_ctas, force_splits;
+  float out_scale;
+  const float* bias;
+  const float* row_ss_in; int ss_in_parts; float norm_inv_dim, norm_eps;
+  const void* residual; long long ldr; float* row_ss_out;          // EPI_RESIDUAL
+  int glu_act;                                                     // EPI_GLU
+  const int* mblk_group; int num_groups;                           // grouped (EPI_STORE / EPI_GLU)
+  int n_q_heads, n_kv_heads; void* q_out; void* kv_cache; int num_pages;   // EPI_QKV
+  const int* slot_mapping; const int* positions; const float* cos_table; const float* sin_table; int max_pos;
+  const float* q_norm_w; const float* k_norm_w; float qk_eps; float kv_inv_scale;
+  void* stream;
+};
+
+template <int OPM>
+static int bs_gemm_call(const GllmBsGemmArgs& a) {
+  GemmParams p = {};
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.out = a.out; p.ldo = a.ldo; p.out_f32 = a.out_f32; p.bias = a.bias;
+  p.sfa = static_cast<const uint8_t*>(a.sfa); p.sfb = static_cast<const uint8_t*>(a.sfb); p.out_scale = a.out_scale;
+  p.row_ss_in = a.row_ss_in; p.ss_in_parts = a.ss_in_parts; p.norm_inv_dim = a.norm_inv_dim; p.norm_eps = a.norm_eps;
+  p.mblk_group = a.mblk_group; p.group_rows = a.N;
+  p.err = gllm_error_word();
+  const long long b_rows = a.mblk_group ? static_cast<long long>(a.num_groups) * a.N : a.N;
+  const int fs = a.mblk_group ? 1 : a.force_splits;
+  cudaStream_t st = static_cast<cudaStream_t>(a.stream);
+  switch (a.epi) {
+    case EPI_STORE:
+      return dispatch_gemm_bs<EPI_STORE, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
+    case EPI_RESIDUAL:
+      p.residual = static_cast<const __nv_bfloat16*>(a.residual); p.ldr = a.ldr; p.row_ss_out = a.row_ss_out;
+      return dispatch_gemm_bs<EPI_RESIDUAL, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
+    case EPI_GLU:
+      p.glu_act = a.glu_act;
+      return dispatch_gemm_bs<EPI_GLU, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
+    case EPI_QKV: {
+      if (((reinterpret_cast<uintptr_t>(a.cos_table) | reinterpret_cast<uintptr_t>(a.sin_table) |
+            reinterpret_cast<uintptr_t>(a.q_norm_w) | reinterpret_cast<uintptr_t>(a.k_norm_w)) & 15) != 0) {
+        set_last_error("block-scaled qkv gemm: rope tables and q/k norm weights must be 16-byte aligned");
+        return -1;
+      }
+      p.N = (a.n_q_heads + 2 * a.n_kv_heads) * 128;
+      p.n_q_heads = a.n_q_heads; p.n_kv_heads = a.n_kv_heads;
+      p.q_out = static_cast<__nv_bfloat16*>(a.q_out); p.kv_cache = static_cast<__nv_bfloat16*>(a.kv_cache);
+      p.num_pages = a.num_pages; p.slot_mapping = a.slot_mapping; p.positions = a.positions;
+      p.cos_table = a.cos_table; p.sin_table = a.sin_table; p.max_pos = a.max_pos;
+      p.q_norm_w = a.q_norm_w; p.k_norm_w = a.k_norm_w; p.qk_eps = a.qk_eps;
+      p.kv_fp8 = a.kv_inv_scale > 0.f ? 1 : 0; p.kv_inv_scale = a.kv_inv_scale;
+      return dispatch_gemm_bs<EPI_QKV, OPM>(a.a, a.lda, a.b, a.ldb, p.N, p, 128, st, a.max_ctas, fs);
+    }
+  }
+  set_last_error("block-scaled gemm: unknown epilogue %d", a.epi);
+  return -1;
+}
+
+GLLM_API int gllm_gemm_blockscaled(const GllmBsGemmArgs* args) {
+  if (!args || !args->a || !args->b || !args->sfa || !args->sfb) {
+    set_last_error("block-scaled gemm: null operand");
+    return -1;
+  }
+  if (args->fmt == OPM_MXFP8) return bs_gemm_call<OPM_MXFP8>(*args);
+  if (args->fmt == OPM_NVFP4) return bs_gemm_call<OPM_NVFP4>(*args);
+  set_last_error("block-scaled gemm: fmt must be 2 (MXFP8) or 3 (NVFP4), got %d", args->fmt);
+  return -1;
 }
 
 // Debugging aid: CTA 0 of every following GEMM launch writes 9 SM-clock stamps to `buf` (device memory, 9 x int64):

@@ -61,7 +61,7 @@ class Workspace:
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
-                 quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0):
+                 quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0, expert_quant: Optional[str] = None):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
@@ -75,9 +75,16 @@ class DecoderModel:
         if self.kv_dtype == torch.float8_e4m3fn and cfg.head_dim != 128 and fused is None:
             fused = False        # only the head_dim-128 kernels (fused QKV epilogue, TMA attention) have fp8-page variants
         self.weight_quant = weight_quant
-        if weight_quant is not None:
-            fused = False        # quantised linears run through the dequantising GEMM; epilogue fusions need bf16 weights
-        self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and self.device.type == "cuda"
+        # "mxfp8" / "nvfp4": both GEMM operands block-scaled on the tensor cores (activations quantised on the device
+        # before each GEMM), every fused epilogue kept. Other modes: weight-only quantisation through the dequantising GEMM.
+        self.bs_fmt = weight_quant if weight_quant in ("mxfp8", "nvfp4") else None
+        self.act_tensor_scale = 1.0 / 64.0      # NVFP4 activations: static second-level scale (values up to 42 exact range)
+        if weight_quant is not None and self.bs_fmt is None:
+            fused = False        # the dequantising GEMM has no epilogue fusions
+        # the fused layer is the CUDA path; block-scaled models also run it on CPU tensors (every fused op has its fp32
+        # restatement), so that the CPU model quantises the same activations as the GPU one and can serve as its oracle
+        self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and (
+            self.device.type == "cuda" or self.bs_fmt is not None)
         if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size) or (
                 cfg.num_kv_heads < self.tp_size and self.tp_size % cfg.num_kv_heads):
             # with fewer KV heads than ranks each KV head is replicated over tp / num_kv_heads ranks (pack_attention)
@@ -112,7 +119,8 @@ class DecoderModel:
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
-                                        ep=ep if ep is not None else getattr(tp, "ep", None), fused=self.fused, tp=tp)
+                                        ep=ep if ep is not None else getattr(tp, "ep", None), fused=self.fused, tp=tp,
+                                        expert_quant=expert_quant or self.bs_fmt)
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
         self.lm_head = None
@@ -133,6 +141,16 @@ class DecoderModel:
         """Load-time quantisation of the dense projections of one layer into the canonical quantised form (a
         checkpoint that is already quantised arrives here as ``QuantWeight`` and is left alone)."""
         from ..ops.quant_gemm import QuantWeight, quantize
+        if self.bs_fmt is not None:
+            from ..ops import blockscale as B
+            mult = 128 if self.bs_fmt == "mxfp8" else 256
+            for name in ("wqkv", "wo", "w_gate_up", "w_down"):
+                w = getattr(lw, name, None)
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[0] > 0:
+                    if w.shape[1] % mult:
+                        raise ValueError(f"{name}: K = {w.shape[1]} must be a multiple of {mult} for {self.bs_fmt}")
+                    setattr(lw, name, B.quantize(w.float(), self.bs_fmt))
+            return
         for name in ("wqkv", "wo", "w_gate_up", "w_down"):
             w = getattr(lw, name, None)
             if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[0] > 0 and w.shape[1] % 64 == 0 and w.shape[1] % group == 0 \
@@ -140,11 +158,12 @@ class DecoderModel:
                 setattr(lw, name, quantize(w.float().cpu(), mode, group).to(self.device))
 
     def weight_bytes(self) -> int:
+        from ..ops.blockscale import BlockScaled
         from ..ops.quant_gemm import QuantWeight
         total = 0
         for lw in self.layers:
             for v in vars(lw).values():
-                if isinstance(v, QuantWeight):
+                if isinstance(v, (QuantWeight, BlockScaled)):
                     total += v.nbytes()
                 elif isinstance(v, torch.Tensor):
                     total += v.numel() * v.element_size()
@@ -178,8 +197,42 @@ class DecoderModel:
                                  max_q_len=batch.max_q_len, n_q=self.n_q_local, n_kv=self.n_kv_local, scale=self.scale,
                                  out=out, causal=batch.causal and self.cfg.causal, window=window, kv_scale=self.kv_scale)
 
+    def _act_q(self, a, T):
+        """Block-scaled copy of the activations ``a`` [T, K] (one reusable buffer per K)."""
+        from ..ops import blockscale as B
+        if not a.is_cuda:
+            return B.quantize_act(a, self.bs_fmt, tensor_scale=self.act_tensor_scale)
+        bufs = self.__dict__.setdefault("_actq", {})
+        K = a.shape[1]
+        buf = bufs.get(K)
+        if buf is None or buf.codes.shape[0] < T:
+            buf = bufs[K] = B.alloc_act(max(T, self._ws.max_tokens if self._ws else T), K, self.bs_fmt, self.device)
+        return B.quantize_act(a, self.bs_fmt, out=buf, tensor_scale=self.act_tensor_scale)
+
+    def _row_parallel_bs(self, a, w, x, ss_out, T):
+        """Row-parallel projection on block-scaled operands: x <- a @ w.T + x with the next norm's statistics."""
+        from ..ops import blockscale as B
+        N = w.rows
+        aq = self._act_q(a, T)
+        if self.tp_size == 1:
+            bn = 128 if T <= 1024 else self.res_bn
+            parts = (N + bn - 1) // bn
+            ss = ss_out.reshape(-1)[:T * parts].view(T, parts)
+            B.gemm_residual(aq, w, x, out=x, row_ss_out=ss, bn=bn)
+            return ss
+        # tensor parallel: partial products on the tensor cores, the sum over ranks on NCCL
+        import torch.distributed as dist
+        p = self._ws.partial[:T]
+        B.gemm(aq, w, out=p, bn=128 if T <= 1024 else 256)
+        dist.all_reduce(p, group=self.tp.group)
+        ss = ss_out.reshape(-1)[:T].view(T, 1)
+        ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
+        return ss
+
     def _row_parallel(self, a, w, x, ss_out, T):
         """x <- a @ w.T + x, row statistics into ss_out. With TP the partial sums are all-reduced."""
+        if self.bs_fmt is not None and not isinstance(w, torch.Tensor):
+            return self._row_parallel_bs(a, w, x, ss_out, T)
         N = w.shape[0]
         bn = self.res_bn
         if self.tp_size == 1 and T <= 256 and N % 128 == 0:
@@ -215,10 +268,17 @@ class DecoderModel:
         for li, lw in zip(self.layer_ids, self.layers):
             kv = kv_caches[li - self.layer_ids[0]]
             if self.fused:
-                ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
-                             slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
-                             sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
-                             row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
+                if self.bs_fmt is not None:
+                    from ..ops import blockscale as B
+                    B.gemm_qkv(self._act_q(x, T), lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
+                               slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
+                               sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
+                               row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
+                else:
+                    ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
+                                 slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
+                                 sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
+                                 row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 mark("qkv_gemm")
                 self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
                 mark("attention")
@@ -230,12 +290,21 @@ class DecoderModel:
                 else:
                     # the packing is tile-width independent: the width recorded with the weight fills one wave of SMs
                     # at decode sizes, prefill chunks take the widest tile (best tensor-core rate)
-                    glu_bn = 256 if (T > 1024 and lw.w_gate_up.shape[0] % 256 == 0) else lw.glu_bn
-                    ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
-                                 row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=glu_bn)
-                    mark("gate_up_gemm")
-                    ss_in = self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
-                    mark("down_proj")
+                    if self.bs_fmt is not None:
+                        from ..ops import blockscale as B
+                        inter = lw.w_down.k
+                        B.gemm_glu(self._act_q(x, T), lw.w_gate_up, act=self.act_id, out=ws.act[:T, :inter], row_ss=ss_mid,
+                                   norm_dim=H, eps=c.rms_norm_eps, bn=256 if (T > 1024 and lw.w_gate_up.rows % 256 == 0) else 128)
+                        mark("gate_up_gemm")
+                        ss_in = self._row_parallel(ws.act[:T, :inter], lw.w_down, x, ws.ss_a[:T], T)
+                        mark("down_proj")
+                    else:
+                        glu_bn = 256 if (T > 1024 and lw.w_gate_up.shape[0] % 256 == 0) else lw.glu_bn
+                        ops.gemm_glu(x, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :lw.w_down.shape[1]],
+                                     row_ss=ss_mid, norm_dim=H, eps=c.rms_norm_eps, bn=glu_bn)
+                        mark("gate_up_gemm")
+                        ss_in = self._row_parallel(ws.act[:T, :lw.w_down.shape[1]], lw.w_down, x, ws.ss_a[:T], T)
+                        mark("down_proj")
             else:
                 h = ws.h[:T]
                 ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w, out=h)

@@ -40,6 +40,8 @@ class MoeLayerWeights:
     fused: bool = True
     ep: Optional[object] = None
     tp_experts: Optional[object] = None  # tensor-parallel context when the experts are split over the TP ranks
+    bs_fmt: Optional[str] = None         # "mxfp8" / "nvfp4": the expert stacks are block-scaled operands (ops/blockscale.py)
+    act_tensor_scale: float = 1.0 / 64.0
     _ws: Optional[M.MoeWorkspace] = None
 
     # ------------------------------------------------------------------------------------------
@@ -54,6 +56,31 @@ class MoeLayerWeights:
             ws.logits = torch.zeros((max(T, 256), self.router.shape[0]), dtype=torch.float32, device=model.device)
             holder[key] = ws
         return ws
+
+    def _expert_ffn(self, model, src, ws, T, fused_norm: bool):
+        """The routed rows through their experts' SwiGLU FFNs: ws.y_perm <- down(glu(gate/up(rows))). ``src`` [T, H]
+        is what the experts read; the rows were bucketed by ``M.permute`` (ws.dest / blk_group / ss_perm)."""
+        c = self.cfg
+        H = c.hidden_size
+        rs = dict(row_ss=ws.ss_perm, norm_dim=H, eps=c.rms_norm_eps) if fused_norm else {}
+        if self.bs_fmt is None:
+            L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
+                       num_groups=self.e_local, **rs)
+            L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+            return
+        # block-scaled experts: the routed rows are quantised straight from the token rows into their expert blocks,
+        # the SwiGLU output is quantised again for the down projection (only the rows that exist: a device-side count)
+        from ..ops import blockscale as B
+        k = c.num_experts_per_tok
+        if getattr(ws, "aq", None) is None or ws.aq.fmt != B.FMT_NAMES[self.bs_fmt]:
+            ws.aq = B.alloc_act(ws.max_rows, H, self.bs_fmt, src.device)
+            ws.actq = B.alloc_act(ws.max_rows, self.inter, self.bs_fmt, src.device)
+        ts = self.act_tensor_scale
+        B.quantize_act_scatter(src, ws.dest, k, self.bs_fmt, ws.aq, ws.max_rows, tensor_scale=ts)
+        B.gemm_glu(ws.aq, self.w_gate_up, act=model.act_id, out=ws.act, bn=128, mblk_group=ws.blk_group,
+                   num_groups=self.e_local, **rs)
+        B.quantize_act_rows(ws.act, self.bs_fmt, ws.actq, ws.total_rows, tensor_scale=ts)
+        B.gemm(ws.actq, self.w_down, out=ws.y_perm, bn=128, mblk_group=ws.blk_group, num_groups=self.e_local)
 
     def _route(self, x, row_ss, ws, T, norm_dim, eps):
         c = self.cfg
@@ -76,9 +103,7 @@ class MoeLayerWeights:
         if self.tp_experts is not None:
             return self._forward_tp_experts(model, x, x, ss_in, ss_out, ids, w, ws, T, fused_norm=True)
         M.permute(x, ss_in, ids, ws, self.e0, self.e_local)
-        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, row_ss=ws.ss_perm, norm_dim=H,
-                   eps=c.rms_norm_eps, bn=self.glu_bn, mblk_group=ws.blk_group, num_groups=self.e_local)
-        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        self._expert_ffn(model, x, ws, T, fused_norm=True)
         shared = None
         if self.shared_gate_up is not None:
             sa = L.gemm_glu(x, self.shared_gate_up, act=model.act_id, row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps,
@@ -97,10 +122,7 @@ class MoeLayerWeights:
         c = self.cfg
         H = c.hidden_size
         M.permute(src, ss_in if fused_norm else None, ids, ws, self.e0, self.e_local)
-        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, row_ss=ws.ss_perm if fused_norm else None,
-                   norm_dim=H if fused_norm else 0, eps=c.rms_norm_eps if fused_norm else 0.0, bn=self.glu_bn,
-                   mblk_group=ws.blk_group, num_groups=self.e_local)
-        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        self._expert_ffn(model, src, ws, T, fused_norm)
         holder = model.__dict__.setdefault("_moe_partial", {})
         part = holder.get("buf")
         if part is None or part.shape[0] < T:
@@ -131,9 +153,7 @@ class MoeLayerWeights:
             self._forward_tp_experts(model, x, h, None, None, ids, w, ws, T, fused_norm=False)
             return
         M.permute(h, None, ids, ws, self.e0, self.e_local)
-        L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
-                   num_groups=self.e_local)
-        L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+        self._expert_ffn(model, h, ws, T, fused_norm=False)
         shared = None
         if self.shared_gate_up is not None:
             sa = L.gemm_glu(h, self.shared_gate_up, act=model.act_id, bn=self.shared_bn)
@@ -141,7 +161,8 @@ class MoeLayerWeights:
         M.combine(x, ws.y_perm, ws.dest, w, shared=shared)
 
 
-def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, device, dtype, ep=None, fused=True, tp=None):
+def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, device, dtype, ep=None, fused=True, tp=None,
+                   expert_quant: Optional[str] = None):
     """Experts are split over the expert-parallel group (``ep``), or kept whole when there is none; the shared
     expert and the router are replicated."""
     p = layer_prefix(i)
@@ -168,9 +189,18 @@ def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, de
         router = _fold(router, post, cfg.norm_one_plus_w)
     router = L.pad_rows(router, 128).contiguous()
     rb = src.get(p + "router_bias").float().to(device) if src.has(p + "router_bias") else None
-    lw = MoeLayerWeights(router=router, router_bias=rb, w_gate_up=torch.cat(gus, 0).contiguous(),
-                         w_down=torch.cat(downs, 0).contiguous(), glu_bn=bn, e0=e0, e_local=e1 - e0, inter=inter,
-                         cfg=cfg, fused=fused, ep=ep, tp_experts=tp_experts)
+    w_gu, w_dn = torch.cat(gus, 0).contiguous(), torch.cat(downs, 0).contiguous()
+    if expert_quant in ("mxfp8", "nvfp4"):
+        # expert stacks as block-scaled operands (MXFP8: e4m3 + ue8m0 per 32; NVFP4: e2m1 + ue4m3 per 16): the grouped
+        # GEMMs then run on the block-scaled tensor-core kinds and half / a quarter of the bytes cross HBM
+        from ..ops import blockscale as B
+        mult = 128 if expert_quant == "mxfp8" else 256
+        if cfg.hidden_size % mult or inter % mult or (2 * inter) % 128 or w_dn.shape[0] // max(e1 - e0, 1) % 128:
+            raise ValueError(f"{expert_quant} experts need hidden / intermediate sizes that are multiples of {mult}")
+        w_gu, w_dn = B.quantize(w_gu.float(), expert_quant), B.quantize(w_dn.float(), expert_quant)
+    lw = MoeLayerWeights(router=router, router_bias=rb, w_gate_up=w_gu, w_down=w_dn, glu_bn=bn, e0=e0, e_local=e1 - e0,
+                         inter=inter, cfg=cfg, fused=fused, ep=ep, tp_experts=tp_experts,
+                         bs_fmt=expert_quant if expert_quant in ("mxfp8", "nvfp4") else None)
     if cfg.num_shared_experts and src.has(p + "shared_expert.gate_proj"):
         g = src.get(p + "shared_expert.gate_proj").to(device, dtype)
         u = src.get(p + "shared_expert.up_proj").to(device, dtype)

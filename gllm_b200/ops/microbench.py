@@ -5,7 +5,7 @@ also be captured with ``ncu`` in a minute or two. Timing uses CUDA events on the
 warm-up; the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at the repository root if
 present) is printed as JSON.
 
-ops: gemm_prefill  gemm_prefill_glu  gemm_prefill_residual  gemm_prefill_qkv  gemm_decode  gemm_decode_trace  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
+ops: bsgemm_mxfp8  bsgemm_nvfp4  gemm_prefill  gemm_prefill_glu  gemm_prefill_residual  gemm_prefill_qkv  gemm_decode  gemm_decode_trace  gemm_glu  gemm_qkv  decode_attn  prefill_attn  sample  qgemm_fp8  qgemm_fp4  qgemm_int4
      mla_attn
 """
 from __future__ import annotations
@@ -212,6 +212,31 @@ def run(op: str, iters: int):
         out.update(shape=[M, N, K], mode=mode, group=group, us=t * 1e6, weight_bytes=byts, weight_gbs=byts / t / 1e9,
                    frac_of_hbm_peak=byts / t / 1e9 / hbm, bf16_equivalent_gbs=dense / t / 1e9,
                    tflops=2 * M * N * K / t / 1e12)
+    elif op.startswith("bsgemm_"):
+        # block-scaled tensor-core GEMM (both operands MXFP8 / NVFP4, hardware scale factors). Shape from GLLM_BS_SHAPE
+        # ("M,N,K"); default: the decode-sized gate/up projection. GLLM_BS_QUANT=1 adds the activation quantisation.
+        from . import blockscale as B
+        fmt = op.split("_", 1)[1]
+        M, N, K = [int(v) for v in os.environ.get("GLLM_BS_SHAPE", "256,12288,4096").split(",")]
+        bn = int(os.environ.get("GLLM_BS_BN", "128"))
+        nw = 3 if N * K <= (1 << 27) else 1
+        ws = [B.quantize(torch.randn(N, K) * 0.05, fmt).to(dev) for _ in range(nw)]
+        a = rnd(M, K)
+        aq = B.quantize_act(a, fmt, tensor_scale=0.02)
+        o = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        with_quant = os.environ.get("GLLM_BS_QUANT", "0") == "1"
+        i = [0]
+
+        def f():
+            i[0] = (i[0] + 1) % nw
+            if with_quant:
+                B.quantize_act(a, fmt, out=aq, tensor_scale=0.02)
+            B.gemm(aq, ws[i[0]], out=o, bn=bn)
+        t = _time(f, iters)
+        byts = ws[0].nbytes()
+        out.update(shape=[M, N, K], fmt=fmt, bn=bn, with_quant=with_quant, us=t * 1e6, weight_bytes=byts,
+                   weight_gbs=byts / t / 1e9, frac_of_hbm_peak=byts / t / 1e9 / hbm, tflops=2 * M * N * K / t / 1e12,
+                   frac_of_bf16_peak=2 * M * N * K / t / 1e12 / tf)
     elif op == "mla_attn":
         from . import mla as MLA
         nh, d_c, d_r = 16, 512, 64
