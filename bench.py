@@ -167,6 +167,7 @@ def main():
                         prefill_chunk=8192, use_cuda_graphs=not args.no_graphs)
     ecfg.num_pages = args.concurrency * ((max_len + 15) // 16) + 64
     engine = LLMEngine(model, ecfg)
+    engine.precapture()        # decode graphs for every batch bucket, as a server does at start-up (not part of TTFT)
     prompts = make_prompts(args.concurrency, args.min_prompt, args.max_prompt, args.shared_prefix, cfg.vocab_size)
 
     # ---- phase 0 (N > 1): the tensor-parallel engine must produce the single-GPU model's tokens ----

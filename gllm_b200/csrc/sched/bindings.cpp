@@ -83,6 +83,7 @@ PYBIND11_MODULE(_sched, m) {
       .def_readwrite("defrag_threshold", &PolicyConfig::defrag_threshold)
       .def_readwrite("watermark_pages", &PolicyConfig::watermark_pages)
       .def_readwrite("enable_prefix_cache", &PolicyConfig::enable_prefix_cache)
+      .def_readwrite("preempt_swap", &PolicyConfig::preempt_swap)
       .def_readwrite("phase_isolated", &PolicyConfig::phase_isolated)
       .def_readwrite("order", &PolicyConfig::order);
 
@@ -108,11 +109,18 @@ PYBIND11_MODULE(_sched, m) {
       .def_readonly("len", &PrefillItem::len)
       .def_readonly("last", &PrefillItem::last);
 
+  py::class_<SwapItem>(m, "SwapItem")
+      .def_readonly("seq_id", &SwapItem::seq_id)
+      .def_readonly("pages", &SwapItem::pages)
+      .def_readonly("num_tokens", &SwapItem::num_tokens);
+
   py::class_<StepPlan>(m, "StepPlan")
       .def_readonly("num_decode", &StepPlan::num_decode)
       .def_readonly("prefill", &StepPlan::prefill)
       .def_readonly("max_blocks", &StepPlan::max_blocks)
       .def_readonly("preempted", &StepPlan::preempted)
+      .def_readonly("swap_out", &StepPlan::swap_out)
+      .def_readonly("swap_in", &StepPlan::swap_in)
       .def_property_readonly("idle", &StepPlan::idle)
       .def_property_readonly("num_prefill_tokens", [](const StepPlan& p) { return p.pf_tokens.size(); })
       .def_property_readonly("num_prefill_seqs", [](const StepPlan& p) { return p.prefill.size(); })
@@ -147,6 +155,40 @@ PYBIND11_MODULE(_sched, m) {
              std::memcpy(d + n, p.dec_positions.data(), n * 4);
              std::memcpy(d + 2 * n, p.dec_slot_mapping.data(), n * 4);
              std::memcpy(d + 3 * n, p.dec_ctx_lens.data(), n * 4);
+           })
+      // packs the prefill side into caller-provided (pinned) buffers, no allocation:
+      //   pack = [tokens T | positions T | slot_mapping T | q_start S | q_len S | ctx_lens S | last_rows L | last_slots L]
+      //   bt   = [S, max_blocks]
+      // and returns (T, S, L, max_q_len); L = chunks that reach the end of their prompt (they sample a token)
+      .def("pack_prefill_into",
+           [](const StepPlan& p, py::array_t<int32_t, py::array::c_style> pack, py::array_t<int32_t, py::array::c_style> bt) {
+             const size_t T = p.pf_tokens.size(), S = p.prefill.size();
+             size_t L = 0;
+             for (auto& it : p.prefill) L += it.last ? 1 : 0;
+             if (static_cast<size_t>(pack.size()) < 3 * T + 3 * S + 2 * L ||
+                 static_cast<size_t>(bt.size()) < p.pf_block_tables.size())
+               throw std::invalid_argument("prefill staging buffers too small");
+             int32_t* d = pack.mutable_data();
+             std::memcpy(d, p.pf_tokens.data(), T * 4);
+             std::memcpy(d + T, p.pf_positions.data(), T * 4);
+             std::memcpy(d + 2 * T, p.pf_slot_mapping.data(), T * 4);
+             std::memcpy(d + 3 * T, p.pf_q_start.data(), S * 4);
+             std::memcpy(d + 3 * T + S, p.pf_q_len.data(), S * 4);
+             std::memcpy(d + 3 * T + 2 * S, p.pf_ctx_lens.data(), S * 4);
+             int32_t* rows = d + 3 * T + 3 * S;
+             int32_t* slots = rows + L;
+             size_t k = 0;
+             int max_q = 0;
+             for (size_t i = 0; i < S; ++i) {
+               max_q = std::max(max_q, p.pf_q_len[i]);
+               if (p.prefill[i].last) {
+                 rows[k] = p.pf_q_start[i] + p.prefill[i].len - 1;
+                 slots[k] = p.prefill[i].slot;
+                 ++k;
+               }
+             }
+             std::memcpy(bt.mutable_data(), p.pf_block_tables.data(), p.pf_block_tables.size() * 4);
+             return py::make_tuple(T, S, L, max_q);
            });
 
   py::class_<FinishedSeq>(m, "FinishedSeq")
@@ -214,6 +256,8 @@ PYBIND11_MODULE(_sched, m) {
       .def("lookup_prefix_pages", &ContinuousBatcher::lookup_prefix_pages)
       .def("import_prefix", &ContinuousBatcher::import_prefix)
       .def_property_readonly("num_waiting", &ContinuousBatcher::num_waiting)
+      .def_property_readonly("num_swapped", &ContinuousBatcher::num_swapped)
+      .def("set_victim_order", &ContinuousBatcher::set_victim_order)
       .def_property_readonly("num_running", &ContinuousBatcher::num_running)
       .def_property_readonly("num_free_pages", &ContinuousBatcher::num_free_pages)
       .def_property_readonly("num_total_pages", &ContinuousBatcher::num_total_pages)

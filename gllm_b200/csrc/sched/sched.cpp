@@ -321,6 +321,7 @@ bool ContinuousBatcher::abort(int64_t id) {
   if (it == seqs_.end()) return false;
   Sequence& s = *it->second;
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), id), waiting_.end());
+  swapped_.erase(std::remove(swapped_.begin(), swapped_.end(), id), swapped_.end());
   finish(s, FinishReason::Aborted);
   return true;
 }
@@ -331,13 +332,24 @@ bool ContinuousBatcher::abort(int64_t id) {
 bool ContinuousBatcher::preempt_one(int64_t protect_id) {
   if (running_.empty()) return false;
   int64_t victim = -1;
+  // the eviction policy's order first (best victim first) ...
+  for (int64_t id : victim_order_) {
+    if (id == protect_id) continue;
+    auto it = seqs_.find(id);
+    if (it == seqs_.end() || it->second->state != SeqState::Running) continue;
+    victim = id;
+    break;
+  }
+  // ... else the youngest running sequence
   uint64_t best = 0;
-  for (auto& kv : running_) {
-    Sequence& s = *seqs_[kv.second];
-    if (s.id == protect_id) continue;
-    if (victim < 0 || s.arrival >= best) {
-      victim = s.id;
-      best = s.arrival;
+  if (victim < 0) {
+    for (auto& kv : running_) {
+      Sequence& s = *seqs_[kv.second];
+      if (s.id == protect_id) continue;
+      if (victim < 0 || s.arrival >= best) {
+        victim = s.id;
+        best = s.arrival;
+      }
     }
   }
   if (victim < 0) return false;
@@ -347,10 +359,22 @@ bool ContinuousBatcher::preempt_one(int64_t protect_id) {
       running_.erase(it);
       break;
     }
+  ++v.preemptions;
+  if (cfg_.preempt_swap && v.state == SeqState::Running && v.num_computed > 0) {
+    // swap: the caller copies these pages to host memory before the step runs; the position is kept
+    SwapItem item;
+    item.seq_id = victim;
+    item.pages.assign(v.block_table.begin(), v.block_table.end());
+    item.num_tokens = v.num_computed;
+    pending_swap_out_.push_back(std::move(item));
+    free_sequence(v, false);
+    v.state = SeqState::Swapped;
+    swapped_.push_back(victim);
+    return true;
+  }
   free_sequence(v, true);
   v.state = SeqState::Paused;
   v.num_computed = 0;
-  ++v.preemptions;
   waiting_.push_front(victim);
   return true;
 }
@@ -505,7 +529,41 @@ StepPlan ContinuousBatcher::schedule() {
     add_chunk(*seqs_[id]);
   }
 
-  if (dec.admit_new_prefill) {
+  // ---- 2b. swapped-out sequences come back (oldest first) as soon as their pages and a slot are free; they take the
+  // pages now, the caller copies their KV back before the step runs, and they decode again from the next step on.
+  // Sequences still paying for this step's preemptions never return in the same step.
+  plan.swap_out = std::move(pending_swap_out_);
+  pending_swap_out_.clear();
+  while (!swapped_.empty() && plan.swap_out.empty()) {
+    const int64_t id = swapped_.front();
+    auto sit = seqs_.find(id);
+    if (sit == seqs_.end()) {   // aborted while swapped out
+      swapped_.pop_front();
+      continue;
+    }
+    Sequence& s = *sit->second;
+    const int need = (s.num_computed + 1 + page_size_ - 1) / page_size_;
+    const int reclaimable = alloc_.num_free() + prefix_.cached_pages();
+    if (free_slots_.empty() || need + cfg_.watermark_pages > reclaimable) break;
+    if (!ensure_pages(s, s.num_computed + 1)) break;
+    s.slot = free_slots_.back();
+    free_slots_.pop_back();
+    slot_owner_[s.slot] = s.id;
+    s.state = SeqState::Running;
+    const uint64_t key = static_cast<OrderPolicy>(cfg_.order) == OrderPolicy::StrictRequestId
+                             ? static_cast<uint64_t>(s.id)
+                             : s.arrival;
+    running_[static_cast<int64_t>(key)] = s.id;
+    write_slot_table(s);
+    SwapItem item;
+    item.seq_id = id;
+    item.pages.assign(s.block_table.begin(), s.block_table.end());
+    item.num_tokens = s.num_computed;
+    plan.swap_in.push_back(std::move(item));
+    swapped_.pop_front();
+  }
+
+  if (dec.admit_new_prefill && swapped_.empty()) {   // nobody new while a swapped-out sequence still waits
     if (static_cast<OrderPolicy>(cfg_.order) == OrderPolicy::StrictRequestId) {
       // paused sequences keep their place at the front; the rest is ordered by request id
       std::stable_sort(waiting_.begin(), waiting_.end(), [this](int64_t a, int64_t b) {

@@ -82,7 +82,7 @@ class PrefixIndex {
 };
 
 // ---------------------------------------------------------------------------------------------
-enum class SeqState : int { Waiting = 0, Prefilling = 1, Running = 2, Paused = 3, Finished = 4 };
+enum class SeqState : int { Waiting = 0, Prefilling = 1, Running = 2, Paused = 3, Finished = 4, Swapped = 5 };
 enum class FinishReason : int { None = 0, Eos = 1, Length = 2, Aborted = 3, Veto = 4 };
 enum class OrderPolicy : int { StrictRequestId = 0, Fifo = 1 };
 
@@ -123,6 +123,10 @@ struct PolicyConfig {
   bool enable_prefix_cache = true;
   bool phase_isolated = true;        // decode batch and prefill chunk are separate launches
   int order = 0;                     // OrderPolicy
+  // Preemption of a running (fully prefilled) sequence: false = recompute (pages go back, the sequence is prefilled
+  // again later); true = swap (the plan lists the victim's pages in `swap_out`, the caller copies them to host memory
+  // before the step runs, the sequence keeps its position and comes back through `swap_in` when pages are free).
+  bool preempt_swap = false;
 };
 
 struct SystemState {
@@ -137,6 +141,13 @@ struct PolicyDecision {
 };
 
 PolicyDecision policy_decide(const PolicyConfig& cfg, const SystemState& st);
+
+// A sequence leaving for / returning from host memory: its pages in logical order and the tokens they cover.
+struct SwapItem {
+  int64_t seq_id;
+  std::vector<int> pages;
+  int num_tokens;
+};
 
 // One prefill work item: a chunk of one sequence.
 struct PrefillItem {
@@ -159,7 +170,10 @@ struct StepPlan {
   std::vector<int32_t> pf_block_tables;  // [S, max_blocks]
   int max_blocks = 0;
   std::vector<int64_t> preempted;
-  bool idle() const { return num_decode == 0 && prefill.empty(); }
+  // swap-style preemption (PolicyConfig::preempt_swap): copy these pages out BEFORE, these in BEFORE the step's
+  // kernels run (pages of a swapped-out sequence may already belong to another sequence of this same plan)
+  std::vector<SwapItem> swap_out, swap_in;
+  bool idle() const { return num_decode == 0 && prefill.empty() && swap_out.empty() && swap_in.empty(); }
 };
 
 struct FinishedSeq {
@@ -194,6 +208,10 @@ class ContinuousBatcher {
   // dense [max_slots, max_blocks] table of the running sequences (row = slot)
   const std::vector<int32_t>& slot_block_tables() const { return slot_tables_; }
   int num_waiting() const { return static_cast<int>(waiting_.size()); }
+  int num_swapped() const { return static_cast<int>(swapped_.size()); }
+  // Preferred victims of the next preemptions, best victim first (an eviction policy such as HGAL supplies it);
+  // ids that are not running are skipped, and when the list runs out the youngest running sequence is taken.
+  void set_victim_order(const std::vector<int64_t>& ids) { victim_order_ = ids; }
   int num_running() const { return static_cast<int>(running_.size()); }
   int num_free_pages() const { return alloc_.num_free(); }
   int num_total_pages() const { return alloc_.num_total(); }
@@ -234,6 +252,9 @@ class ContinuousBatcher {
   SystemState sys_;
   uint64_t arrivals_ = 0;
   std::deque<int64_t> waiting_;
+  std::deque<int64_t> swapped_;               // swapped-out sequences, oldest first
+  std::vector<SwapItem> pending_swap_out_;    // filled by preempt_one during schedule()
+  std::vector<int64_t> victim_order_;
   std::map<int64_t, int64_t> running_;  // order key -> id
   std::unordered_map<int64_t, std::unique_ptr<Sequence>> seqs_;
   std::vector<int64_t> slot_owner_;

@@ -46,6 +46,17 @@ class EngineConfig:
     pages_per_split: int = 32
     seed: int = 0
     order: int = S.ORDER_STRICT_REQUEST_ID
+    # swap tier: > 0 turns preemption from "recompute later" into "copy the victim's KV pages to pinned host memory and
+    # bring them back when pages are free" (victims chosen by the HGAL policy); overflow goes to the NVMe file
+    swap_space_pages: int = 0
+    swap_path: Optional[str] = None
+    swap_nvme_pages: int = 0
+    # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
+    speculative_tokens: int = 0
+    speculative_ngram: int = 3
+    # role of this engine in a prefill / decode disaggregated deployment (parallel/pd.py): "collocated",
+    # "prefill_only" (finished prefills are handed to `pd_link` with their KV pages) or "decode_only"
+    pd_role: str = "collocated"
 
 
 @dataclass
@@ -78,7 +89,13 @@ class LLMEngine:
         pc.prefill_chunk = ec.prefill_chunk
         pc.enable_prefix_cache = ec.enable_prefix_cache
         pc.order = ec.order
+        pc.preempt_swap = ec.swap_space_pages > 0
         self.batcher = S.ContinuousBatcher(self.num_pages, 16, ec.max_num_seqs, self.max_blocks, pc)
+        self.kv_swap = None
+        if ec.swap_space_pages > 0:
+            from .kv_swap import KvSwapManager
+            self.kv_swap = KvSwapManager(self.kv_caches, ec.swap_space_pages, swap_path=ec.swap_path,
+                                         nvme_pages=ec.swap_nvme_pages)
         self.ms = ec.max_num_seqs
         dev = self.device
         cuda = dev.type == "cuda"
@@ -102,6 +119,16 @@ class LLMEngine:
             self.d_status = nv.error_word_tensor(dev)
         self.unhealthy: Optional[str] = None
         self.slot_params = np.zeros((self.ms, 4), dtype=np.float32)
+        # prefill staging (allocated once: no per-step pinned allocation, concatenation or tensor construction)
+        pf_ints = 3 * ec.max_batch_tokens + 5 * self.ms + 64
+        self.h_pf = torch.zeros(pf_ints, dtype=torch.int32, **pin)
+        self.d_pf = torch.zeros(pf_ints, dtype=torch.int32, device=dev)
+        self.h_pf_bt = torch.zeros((self.ms, self.max_blocks), dtype=torch.int32, **pin)
+        self.d_pf_bt = torch.zeros((self.ms, self.max_blocks), dtype=torch.int32, device=dev)
+        self.h_pf_params = torch.zeros((self.ms, 4), dtype=torch.float32, **pin)
+        self.d_pf_params = torch.zeros((self.ms, 4), dtype=torch.float32, device=dev)
+        self.h_pf_out = torch.zeros(self.ms, dtype=torch.int32, **pin)
+        self.d_pf_out = torch.zeros(self.ms, dtype=torch.int32, device=dev)
         # Split the KV range of a sequence across CTAs only when (sequences x kv heads) alone cannot fill
         # the machine: an unsplit flash-decode CTA streams its pages at full speed, splits add a merge
         # (measured at 256 sequences x 1 kv head, ragged contexts: unsplit 39.9 us, 3 splits 42.1 us).
@@ -303,29 +330,19 @@ class LLMEngine:
 
     def _run_prefill_inner(self, plan) -> np.ndarray:
         dev = self.device
-        T = plan.num_prefill_tokens
-        S_ = plan.num_prefill_seqs
-        t = lambda a: torch.from_numpy(a)
-        pack = np.concatenate([plan.pf_tokens, plan.pf_positions, plan.pf_slot_mapping, plan.pf_q_start,
-                               plan.pf_q_len, plan.pf_ctx_lens]).astype(np.int32)
-        hp = t(pack)
-        hb = t(plan.pf_block_tables)
-        if dev.type == "cuda":
-            hp, hb = hp.pin_memory(), hb.pin_memory()
-        dp = hp.to(dev, non_blocking=True)
-        db = hb.to(dev, non_blocking=True)
-        self.stats["h2d_bytes"] += hp.numel() * 4 + hb.numel() * 4
-        items = plan.prefill
-        last_rows, last_slots = [], []
-        for i, it in enumerate(items):
-            if it.last:
-                last_rows.append(int(plan.pf_q_start[i]) + it.len - 1)
-                last_slots.append(it.slot)
-        rows = torch.tensor(last_rows, dtype=torch.int64, device=dev) if last_rows else None
+        cuda = dev.type == "cuda"
+        T, S_, n_last, max_q = plan.pack_prefill_into(self.h_pf.numpy(), self.h_pf_bt.numpy().reshape(-1))
+        used = 3 * T + 3 * S_ + 2 * n_last
+        self.d_pf[:used].copy_(self.h_pf[:used], non_blocking=cuda)
+        self.d_pf_bt[:S_].copy_(self.h_pf_bt[:S_], non_blocking=cuda)
+        self.stats["h2d_bytes"] += used * 4 + S_ * self.max_blocks * 4
+        dp = self.d_pf
+        o = 3 * T + 3 * S_
+        rows = dp[o:o + n_last] if n_last else None
         batch = ForwardBatch(token_ids=dp[0:T], positions=dp[T:2 * T], slot_mapping=dp[2 * T:3 * T],
-                             block_tables=db, ctx_lens=dp[3 * T + 2 * S_:3 * T + 3 * S_], is_decode=False,
+                             block_tables=self.d_pf_bt[:S_], ctx_lens=dp[3 * T + 2 * S_:3 * T + 3 * S_], is_decode=False,
                              q_start=dp[3 * T:3 * T + S_], q_len=dp[3 * T + S_:3 * T + 2 * S_],
-                             max_q_len=int(plan.pf_q_len.max()), logits_rows=rows)
+                             max_q_len=int(max_q), logits_rows=rows)
         self.stats["prefill_steps"] += 1
         self.stats["prefill_tokens"] += int(T)
         self.model.op_timer = getattr(self, "prefill_timer", None)   # utils.tracing.GraphTimer(eager=True) or None
@@ -336,18 +353,20 @@ class LLMEngine:
             logits = self.model.forward(batch, self.kv_caches)
         finally:
             self.model.op_timer = None
+        last_slots = self.h_pf.numpy()[o + n_last:o + 2 * n_last]
         self._all_greedy = bool((self.slot_params[last_slots, 0] <= 0).all())
-        sl = torch.tensor(last_slots, dtype=torch.int64)
-        params = torch.from_numpy(self.slot_params[last_slots]).to(dev)
-        offs = self.d_offsets.index_select(0, sl.to(dev))
-        out = torch.empty(len(last_rows), dtype=torch.int32, device=dev)
-        self._sample(logits, params, offs, out)
-        self.d_offsets.index_add_(0, sl.to(dev), torch.ones(len(last_rows), dtype=torch.int64, device=dev))
+        self.h_pf_params.numpy()[:n_last] = self.slot_params[last_slots]
+        self.d_pf_params[:n_last].copy_(self.h_pf_params[:n_last], non_blocking=cuda)
+        sl = dp[o + n_last:o + 2 * n_last]
+        offs = self.d_offsets.index_select(0, sl)
+        out = self.d_pf_out[:n_last]
+        self._sample(logits, self.d_pf_params[:n_last], offs, out)
+        self.d_offsets.index_add_(0, sl, torch.ones(n_last, dtype=torch.int64, device=dev))
         if self.d_status is not None:
             self.h_status.copy_(self.d_status, non_blocking=True)
-        res = out.cpu().numpy()
-        self.stats["d2h_bytes"] += res.size * 4
-        return res
+        self.h_pf_out[:n_last].copy_(out, non_blocking=False)     # the only wait of the step: the sampled tokens
+        self.stats["d2h_bytes"] += n_last * 4
+        return self.h_pf_out.numpy()[:n_last].copy()
 
     # ------------------------------------------------------------------------------------------
     def _device_status(self) -> int:
@@ -378,8 +397,21 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------
     def step(self) -> List[GenerateResult]:
         """One scheduler iteration: decode replay for the running set, then one prefill chunk batch."""
+        if self.kv_swap is not None and self.batcher.num_free_pages < max(8, self.num_pages // 16):
+            # memory is tight: the batcher's next victims follow the eviction policy, not "youngest first"
+            running = [rid for rid in self.reqs if rid not in self.kv_swap.keys]
+            self.batcher.set_victim_order(self.kv_swap.victim_order(running))
         plan = self.batcher.schedule()
         self.stats["preemptions"] += len(plan.preempted)
+        if self.kv_swap is not None:
+            # before any kernel of this step runs: the victims' pages may already belong to someone else in this plan
+            for it in plan.swap_out:
+                self.kv_swap.swap_out(it)
+            for it in plan.swap_in:
+                self.kv_swap.swap_in(it)
+            self.stats["swap_outs"] = self.stats.get("swap_outs", 0) + len(plan.swap_out)
+            self.stats["swap_ins"] = self.stats.get("swap_ins", 0) + len(plan.swap_in)
+            self.kv_swap.touch(int(i) for i in plan.dec_seq_ids if i >= 0)
         if self.lockstep is not None:
             return self._step_lockstep(plan)
         if plan.idle:
@@ -446,6 +478,11 @@ class LLMEngine:
         a capture's warm-up run executes the collective kernels, so it cannot happen on one rank alone later."""
         if self.device.type != "cuda" or not self.cfg.use_cuda_graphs:
             return
+        if not self.reqs:        # nothing is running: capture on an empty step (no KV write, zero-length contexts)
+            ms = self.ms
+            self.h_dec.zero_()
+            self.h_dec[2 * ms:3 * ms] = -1
+            self.d_dec.copy_(self.h_dec, non_blocking=True)
         for B in (buckets or [b for b in DECODE_BUCKETS if b <= self.ms]):
             self._all_greedy = True
             if (B, True) not in self.graphs:
@@ -509,6 +546,9 @@ class LLMEngine:
         for rid in list(vetoed):
             self.batcher.abort(rid)
         for f in self.batcher.pop_finished():
+            if self.kv_swap is not None:
+                self.kv_swap.forget(f.id)
+                self.kv_swap.drop(f.id)
             st = self.reqs.pop(f.id, None)
             self._req_params.pop(f.id, None)
             toks = [int(t) for t in f.tokens]

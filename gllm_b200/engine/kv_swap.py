@@ -1,0 +1,135 @@
+"""Swap tier of the serving engine: sequences preempted under memory pressure leave for pinned host memory (and,
+when that fills up, for the NVMe file) instead of being recomputed, and come back when pages are free.
+
+The C++ batcher decides WHEN (``PolicyConfig.preempt_swap``: its plans list ``swap_out`` / ``swap_in`` items), this
+module decides WHO (``Hgal``: gang-aware eviction order over the running sequences, handed to the batcher as its
+victim order) and moves the bytes (``ThreeTierSwap`` over a ``LayeredPool`` view of the per-layer KV caches: one page
+of the pool is the same page index in every layer).
+
+Reference parity: ``reclaim_memory`` / ``ensure_pages_resident`` / ``check_memory_pressure``
+(src/engine/executor.rs:736-1050) on top of ``ThreeTierSwapCoordinator`` (src/scheduler/three_tier_swap.rs) with
+``HGALScheduler::select_victims`` choosing whole sequence groups (src/scheduler/hgal.rs:111-156,306-331).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kv_cache.header import StorageTier
+from ..scheduler.hgal import Hgal, HgalConfig
+from ..scheduler.swap import DmaCommand, LayeredPool, SwapPolicy, ThreeTierSwap
+from ..scheduler.types import PayloadKind, UnifiedVirtualPage
+
+
+class KvSwapManager:
+    def __init__(self, kv_caches: List[torch.Tensor], host_pages: int, *, swap_path: Optional[str] = None,
+                 nvme_pages: int = 0, hgal: Optional[HgalConfig] = None):
+        layers = [t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in kv_caches]
+        self.swap = ThreeTierSwap(LayeredPool(layers), host_pages, swap_path=swap_path, nvme_slots=nvme_pages,
+                                  policy=SwapPolicy())
+        # victims must be allowed right away in a serving step: the warm-up window only protects pages from the
+        # background eviction passes of the reference, not from the batcher's own out-of-memory handling
+        self.hgal = Hgal(hgal or HgalConfig(warmup_ms=0.0))
+        self.keys: Dict[int, List[int]] = {}       # swapped-out sequence -> its page keys, logical order
+        self._next_key = 1
+        self.stats = {"swapped_out_seqs": 0, "swapped_in_seqs": 0, "pages_out": 0, "pages_in": 0, "to_nvme": 0}
+
+    # ---- who leaves ----------------------------------------------------------------------------------
+    def _now_ms(self) -> float:
+        return time.perf_counter() * 1e3
+
+    def track(self, seq_id: int, pinned: bool = False):
+        """A sequence entered the running set: one eviction group (a sequence's pages leave together)."""
+        if seq_id in self.hgal.groups:
+            return
+        page = UnifiedVirtualPage(vpid=seq_id, kind=PayloadKind.KV, owner=seq_id)
+        page.pinned = pinned
+        self.hgal.add_page(page, group=seq_id, now_ms=self._now_ms())
+
+    def touch(self, seq_ids):
+        now = self._now_ms()
+        for sid in seq_ids:
+            if sid in self.hgal.groups:
+                self.hgal.touch_group(sid, now)
+
+    def forget(self, seq_id: int):
+        self.hgal.remove_group(seq_id)
+
+    def victim_order(self, running_ids) -> List[int]:
+        """Running sequences, best victim first (idle, rarely touched, unpinned groups go first)."""
+        now = self._now_ms()
+        for sid in running_ids:
+            self.track(sid)
+        order = self.hgal.select_victims(1 << 30, now)
+        live = set(running_ids)
+        return [g for g in order if g in live]
+
+    # ---- moving the bytes ----------------------------------------------------------------------------
+    def _make_room_on_host(self, need: int):
+        """Pinned host memory is the second tier: when it cannot take ``need`` more pages, the pages that have been
+        there longest go down to the NVMe file (compressed, CRC-checked), as the reference's eviction worker does."""
+        sw = self.swap
+        if len(sw.host_free) >= need:
+            return
+        if sw.nvme is None:
+            raise MemoryError(f"host swap space exhausted ({sw.host_pool.shape[0]} pages) and no NVMe tier configured")
+        in_dram = sorted(((r.age, k) for k, r in sw.records.items() if r.tier == StorageTier.DRAM), reverse=True)
+        for _, key in in_dram:
+            if len(sw.host_free) >= need:
+                break
+            sw.execute(DmaCommand.EVICT_TO_NVME, key)
+            self.stats["to_nvme"] += 1
+        if len(sw.host_free) < need:
+            raise MemoryError("swap space exhausted on both the host and the NVMe tier")
+
+    def swap_out(self, item):
+        """Copy the pages of a preempted sequence to the host (before the step's kernels may reuse them)."""
+        self._make_room_on_host(len(item.pages))
+        keys = []
+        for page in item.pages:
+            key = self._next_key
+            self._next_key += 1
+            self.swap.register(key, int(page))
+            self.swap.execute(DmaCommand.EVICT_TO_DRAM, key)
+            keys.append(key)
+        self.swap.tick()
+        self.keys[int(item.seq_id)] = keys
+        self.forget(int(item.seq_id))
+        self.stats["swapped_out_seqs"] += 1
+        self.stats["pages_out"] += len(keys)
+
+    def swap_in(self, item):
+        """Bring a sequence back into the pages the batcher just gave it (the last page may be a fresh, empty one)."""
+        keys = self.keys.pop(int(item.seq_id), [])
+        pairs = list(zip(keys, item.pages))
+        # pages still in host memory first (each frees a host slot), then the ones that went down to the file tier:
+        # those come up in two hops and need one free host slot on their way
+        for tier in (StorageTier.DRAM, StorageTier.NVME):
+            for key, page in pairs:
+                if self.swap.records[key].tier != tier:
+                    continue
+                if tier == StorageTier.NVME:
+                    self._make_room_on_host(1)
+                self.swap.execute(DmaCommand.PROMOTE_TO_HBM, key, dev_page=int(page))
+        for key in keys:
+            del self.swap.records[key]
+        self.swap.dev_free.clear()          # device pages belong to the batcher's allocator, not to the swap tier
+        self.track(int(item.seq_id))
+        self.stats["swapped_in_seqs"] += 1
+        self.stats["pages_in"] += len(keys)
+
+    def drop(self, seq_id: int):
+        """A swapped-out sequence was aborted: release its copies."""
+        for key in self.keys.pop(int(seq_id), []):
+            r = self.swap.records.pop(key, None)
+            if r is None:
+                continue
+            if r.tier == StorageTier.DRAM:
+                self.swap.host_free.append(r.location)
+            elif r.tier == StorageTier.NVME and self.swap.nvme is not None:
+                self.swap.nvme.free.append(r.location)
+
+    def close(self):
+        self.swap.close()

@@ -94,6 +94,37 @@ def decompress(data: bytes, codec: CompressionCodec) -> bytes:
 # ------------------------------------------------------------------------------------------------
 # DMA backends
 # ------------------------------------------------------------------------------------------------
+class LayeredPool:
+    """The serving engine's KV cache: one device tensor [pages, ...] per layer. A "page" of this pool is the same
+    page index in every layer, and its host image is [layers, ...]. Indexing and ``copy_`` are what the DMA
+    backends use, so the pool stands in for a single stacked tensor without the cache having to be one allocation."""
+
+    class _Page:
+        def __init__(self, layers, page):
+            self.layers, self.page = layers, page
+
+        def copy_(self, host_page, non_blocking=False):          # host image -> device page
+            for l, t in enumerate(self.layers):
+                t[self.page].copy_(host_page[l], non_blocking=non_blocking)
+
+    def __init__(self, layers: List[torch.Tensor]):
+        self.layers = list(layers)
+        t = self.layers[0]
+        self.shape = (t.shape[0], len(self.layers)) + tuple(t.shape[1:])
+        self.dtype, self.device, self.is_cuda = t.dtype, t.device, t.is_cuda
+
+    def __getitem__(self, page: int):
+        return LayeredPool._Page(self.layers, page)
+
+
+def _copy_page_to_host(host_page: torch.Tensor, dev_page, non_blocking=False):
+    if isinstance(dev_page, LayeredPool._Page):
+        for l, t in enumerate(dev_page.layers):
+            host_page[l].copy_(t[dev_page.page], non_blocking=non_blocking)
+    else:
+        host_page.copy_(dev_page, non_blocking=non_blocking)
+
+
 class DmaBackend:
     def d2h(self, dev_pool: torch.Tensor, page: int, host_pool: torch.Tensor, slot: int):
         raise NotImplementedError
@@ -107,7 +138,7 @@ class DmaBackend:
 
 class MemcpyDma(DmaBackend):
     def d2h(self, dev_pool, page, host_pool, slot):
-        host_pool[slot].copy_(dev_pool[page])
+        _copy_page_to_host(host_pool[slot], dev_pool[page])
 
     def h2d(self, host_pool, slot, dev_pool, page):
         dev_pool[page].copy_(host_pool[slot])
@@ -122,7 +153,7 @@ class CudaStreamDma(DmaBackend):
     def d2h(self, dev_pool, page, host_pool, slot):
         self.stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.stream):
-            host_pool[slot].copy_(dev_pool[page], non_blocking=True)
+            _copy_page_to_host(host_pool[slot], dev_pool[page], non_blocking=True)
 
     def h2d(self, host_pool, slot, dev_pool, page):
         with torch.cuda.stream(self.stream):
@@ -202,14 +233,15 @@ class SwapPolicy:
 
 
 class ThreeTierSwap:
-    """Coordinator. ``dev_pool`` [pages, ...] is the device KV pool (all layers of a page may be stacked by the
-    caller), ``host_slots`` pinned host pages of the same shape."""
+    """Coordinator. ``dev_pool`` [pages, ...] is the device KV pool (one stacked tensor, or a ``LayeredPool`` over the
+    per-layer caches of the serving engine), ``host_slots`` pinned host pages of one page's shape."""
 
-    def __init__(self, dev_pool: torch.Tensor, host_slots: int, swap_path: Optional[str] = None, nvme_slots: int = 0,
+    def __init__(self, dev_pool, host_slots: int, swap_path: Optional[str] = None, nvme_slots: int = 0,
                  policy: SwapPolicy = SwapPolicy(), dma: Optional[DmaBackend] = None):
         self.dev_pool = dev_pool
         pin = dev_pool.is_cuda
-        self.host_pool = torch.zeros((host_slots,) + tuple(dev_pool.shape[1:]), dtype=dev_pool.dtype, pin_memory=pin)
+        hdt = torch.uint8 if dev_pool.dtype == torch.float8_e4m3fn else dev_pool.dtype
+        self.host_pool = torch.zeros((host_slots,) + tuple(dev_pool.shape[1:]), dtype=hdt, pin_memory=pin)
         self.host_free = list(range(host_slots - 1, -1, -1))
         self.dev_free: List[int] = []
         self.policy = policy

@@ -152,3 +152,34 @@ def test_engine_step_raises_on_a_device_status_code_and_fails_the_requests():
     ra, rb = eng.results[a], eng.results[b]
     assert ra.finish_reason.startswith("error: rank unhealthy") and rb.finish_reason.startswith("error")
     assert len(ra.token_ids) <= 2                  # the faulty step's tokens were not committed
+
+
+def _tiny_engine(**kw):
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    model = DecoderModel(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=0), device="cpu", dtype=torch.float32,
+                         max_positions=256)
+    base = dict(max_num_seqs=6, max_model_len=160, max_batch_tokens=256, prefill_chunk=128, enable_prefix_cache=False)
+    base.update(kw)
+    return LLMEngine(model, EngineConfig(**base))
+
+
+def test_swap_tier_under_memory_pressure_gives_the_unconstrained_tokens(tmp_path):
+    """A KV pool smaller than the working set: sequences chosen by the eviction policy leave for pinned host memory
+    (and, beyond its size, for the NVMe file) and come back later; the tokens equal those of a run with enough pages."""
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 33, 48, 37, 45, 30)]
+    want = [r.token_ids for r in _tiny_engine(num_pages=128).generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])]
+    eng = _tiny_engine(num_pages=22, swap_space_pages=12, swap_path=str(tmp_path / "kv.swap"), swap_nvme_pages=64)
+    got = [r.token_ids for r in eng.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])]
+    assert got == want
+    assert eng.stats["swap_outs"] > 0 and eng.stats["swap_ins"] == eng.stats["swap_outs"]
+    assert eng.kv_swap.stats["pages_out"] == eng.kv_swap.stats["pages_in"] > 0
+    assert eng.kv_swap.stats["to_nvme"] > 0              # host space (12 pages) overflowed into the file tier
+    assert not eng.kv_swap.keys and not eng.kv_swap.swap.records
+    # the same pool without a swap tier falls back to recompute-style preemption, also with the right tokens
+    rec = _tiny_engine(num_pages=22)
+    assert [r.token_ids for r in rec.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])] == want
+    assert rec.stats["preemptions"] > 0 and rec.stats.get("swap_outs", 0) == 0
