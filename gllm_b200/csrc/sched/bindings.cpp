@@ -242,6 +242,8 @@ PYBIND11_MODULE(_sched, m) {
              d["cached_prefix"] = s->num_cached_prefix;
              d["pages"] = s->block_table.size();
              d["preemptions"] = s->preemptions;
+             d["num_generated"] = s->num_generated();
+             d["max_new_tokens"] = s->sp.max_new_tokens;
              return d;
            })
       .def("tokens_of",
@@ -258,6 +260,8 @@ PYBIND11_MODULE(_sched, m) {
       .def_property_readonly("num_waiting", &ContinuousBatcher::num_waiting)
       .def_property_readonly("num_swapped", &ContinuousBatcher::num_swapped)
       .def("set_victim_order", &ContinuousBatcher::set_victim_order)
+      .def("reserve_tokens", &ContinuousBatcher::reserve_tokens)
+      .def("commit_tokens", &ContinuousBatcher::commit_tokens)
       .def_property_readonly("num_running", &ContinuousBatcher::num_running)
       .def_property_readonly("num_free_pages", &ContinuousBatcher::num_free_pages)
       .def_property_readonly("num_total_pages", &ContinuousBatcher::num_total_pages)

@@ -708,6 +708,36 @@ bool ContinuousBatcher::append_tokens(int64_t id, const std::vector<int32_t>& to
   return true;
 }
 
+bool ContinuousBatcher::reserve_tokens(int64_t id, int n_tokens) {
+  auto it = seqs_.find(id);
+  if (it == seqs_.end() || n_tokens <= 0) return false;
+  Sequence& s = *it->second;
+  if (s.state != SeqState::Running) return false;
+  if (!ensure_pages(s, s.num_computed + n_tokens)) return false;
+  write_slot_table(s);
+  return true;
+}
+
+bool ContinuousBatcher::commit_tokens(int64_t id, const std::vector<int32_t>& toks) {
+  auto it = seqs_.find(id);
+  if (it == seqs_.end()) return false;
+  Sequence& s = *it->second;
+  if (s.state != SeqState::Running) return false;
+  for (int32_t t : toks) {
+    s.num_computed += 1;       // the KV of the token before this one is in the cache
+    s.tokens.push_back(t);
+    if (is_eos(s, t)) {
+      finish(s, FinishReason::Eos);
+      return true;
+    }
+    if (s.num_generated() >= s.sp.max_new_tokens) {
+      finish(s, FinishReason::Length);
+      return true;
+    }
+  }
+  return true;
+}
+
 const Sequence* ContinuousBatcher::find(int64_t id) const {
   auto it = seqs_.find(id);
   return it == seqs_.end() ? nullptr : it->second.get();

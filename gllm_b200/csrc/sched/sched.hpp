@@ -202,6 +202,11 @@ class ContinuousBatcher {
   bool rollback(int64_t id, int n_tokens);
   // append externally verified tokens to a running sequence (speculative accept)
   bool append_tokens(int64_t id, const std::vector<int32_t>& toks);
+  // speculative decoding: make sure a running sequence owns pages for its next `n_tokens` positions (no preemption;
+  // false when the pool cannot give them), and commit tokens whose predecessors' KV a verify forward already wrote:
+  // every committed token advances the computed position by one. Stops at EOS / the length limit.
+  bool reserve_tokens(int64_t id, int n_tokens);
+  bool commit_tokens(int64_t id, const std::vector<int32_t>& toks);
 
   const Sequence* find(int64_t id) const;
   std::vector<int32_t> block_table_of(int64_t id) const;

@@ -27,6 +27,7 @@ class ForwardBatch:
     logits_rows: Optional[torch.Tensor] = None  # [R] int64 rows that need logits; None = all rows
     token_type_ids: Optional[torch.Tensor] = None
     causal: bool = True
+    want_mtp: bool = False           # also run the model's multi-token-prediction heads on the logits rows
 
     @property
     def num_tokens(self) -> int:

@@ -54,6 +54,9 @@ class EngineConfig:
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
+    # multi-token prediction: use the model's MTP heads (when the checkpoint has them) as the draft source; every step
+    # verifies the previous step's candidates (0 = off)
+    mtp_depth: int = 0
     # role of this engine in a prefill / decode disaggregated deployment (parallel/pd.py): "collocated",
     # "prefill_only" (finished prefills are handed to `pd_link` with their KV pages) or "decode_only"
     pd_role: str = "collocated"
@@ -70,12 +73,14 @@ class _ReqState:
 
 
 class LLMEngine:
-    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None, lockstep_group=None):
+    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None, lockstep_group=None, pd_link=None):
         """``lockstep_group``: a process group whose ranks serve DIFFERENT requests but share collective kernels
         inside the model (data-parallel attention + expert-parallel MoE). Every rank then runs the same sequence of
         forwards per step (a rank without work runs an empty one), agreed on by one tiny all-reduce per step."""
         self.model, self.cfg, self.tokenizer = model, cfg or EngineConfig(), tokenizer
         self.lockstep = lockstep_group
+        self.pd_link = pd_link                 # engine/pd.py link: where a prefill_only engine sends, a decode_only one polls
+        self._pd_prompts: Dict[int, List[int]] = {}
         self.mc: ModelConfig = model.cfg
         self.device = model.device
         ec = self.cfg
@@ -153,6 +158,13 @@ class LLMEngine:
         self._all_greedy = True
         self._req_params: Dict[int, tuple] = {}
         self._vetoed: Dict[int, str] = {}
+        self._spec_idx: Dict[int, object] = {}      # request -> n-gram index of its prompt + generated tokens
+        self.spec_stats = dict(steps=0, drafted=0, accepted=0, emitted=0)
+        self.mtp = None                             # MtpExecutor: candidates of the model's own heads as drafts
+        self._mtp_cand: Dict[int, List[int]] = {}
+        if ec.mtp_depth > 0 and getattr(model, "mtp_heads", None):
+            from ..speculative.mtp_executor import MtpExecutor
+            self.mtp = MtpExecutor(min(ec.mtp_depth, len(model.mtp_heads)))
 
     # ------------------------------------------------------------------------------------------
     def _auto_pages(self) -> int:
@@ -180,6 +192,17 @@ class LLMEngine:
                               max_new_tokens=int(max_tokens), eos_ids=eos)
         self.batcher.add_request(rid, [int(t) for t in prompt_ids], sp, session_id or "")
         self.reqs[rid] = _ReqState(t_submit=time.perf_counter(), hook=hook, stream=stream)
+        if self.cfg.pd_role == "prefill_only":
+            self._pd_prompts[rid] = [int(t) for t in prompt_ids]
+            self._req_params[rid] = (float(temperature), int(top_k), float(top_p))
+            self._pd_meta = getattr(self, "_pd_meta", {})
+            self._pd_meta[rid] = dict(max_tokens=int(max_tokens), temperature=float(temperature), top_k=int(top_k),
+                                      top_p=float(top_p), eos_ids=eos)
+        if self.cfg.speculative_tokens > 0:
+            from ..speculative.tree import NgramIndex
+            idx = NgramIndex(min_n=2, max_n=max(2, self.cfg.speculative_ngram))
+            idx.extend(prompt_ids)
+            self._spec_idx[rid] = idx
         self._req_params[rid] = (float(temperature), int(top_k), float(top_p))
         return rid
 
@@ -295,6 +318,140 @@ class LLMEngine:
         self.stats["decode_tokens"] += int(plan.num_decode)
         return self.h_out.numpy()
 
+    # ---- speculative decoding (prompt lookup) ---------------------------------------------------------
+    def _run_speculative_decode(self, plan):
+        """One verify forward over [last token, draft...] of every running sequence instead of a one-token decode step.
+        Drafts come from each request's own history (the continuation that followed the same n-gram earlier: prompt
+        lookup); the target's greedy choices decide how many are kept, so the output equals plain greedy decoding.
+        Returns (first new token per slot, {request: the further tokens}) or None when nobody had a draft.
+
+        Reference parity: ``draft_phase`` / ``verify_phase`` (src/speculative/engine.rs:310-420), PLD spine and n-gram
+        index (src/speculative/tree.rs:93-340,394-452), KV rollback by position (src/engine/mtp_executor.rs)."""
+        from ..speculative.verify import verify_greedy
+        k = self.cfg.speculative_tokens
+        ids = plan.dec_seq_ids
+        slots = [int(sl) for sl in np.nonzero(ids >= 0)[0]]
+        drafts, from_mtp = {}, {}
+        for sl in slots:
+            rid = int(ids[sl])
+            d = []
+            if self.mtp is not None:        # the model's own candidates from the step before (depth set by the controller)
+                d = self._mtp_cand.pop(rid, [])[:self.mtp.active_depth()]
+                from_mtp[sl] = bool(d)
+            if not d and k > 0:
+                idx = self._spec_idx.get(rid)
+                cand = idx.lookup(k) if idx is not None else []
+                d = [int(t) for t in cand[0][:k]] if cand else []
+            left = self._remaining_tokens(rid)
+            d = d[:max(0, left - 1)]            # never draft past the request's length limit
+            if d and not self.batcher.reserve_tokens(rid, 1 + len(d)):
+                d = []
+            drafts[sl] = d
+        if not any(drafts.values()) and (self.mtp is None or self.mtp.active_depth() == 0):
+            return None      # nothing to verify (and no candidates wanted): the captured one-token decode step runs
+        self.batcher.copy_slot_block_tables_into(self.h_bt.numpy().reshape(-1))
+        bt = self.h_bt.numpy()
+        toks, pos, slotmap, q_start, q_len, ctx = [], [], [], [], [], []
+        for sl in slots:
+            d = drafts[sl]
+            p0 = int(plan.dec_positions[sl])
+            q_start.append(len(toks))
+            q_len.append(1 + len(d))
+            ctx.append(p0 + 1 + len(d))
+            for i, t in enumerate([int(plan.dec_tokens[sl])] + d):
+                toks.append(t)
+                pos.append(p0 + i)
+                slotmap.append(int(bt[sl, (p0 + i) // 16]) * 16 + (p0 + i) % 16)
+        dev = self.device
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        T = len(toks)
+        batch = ForwardBatch(token_ids=i32(toks), positions=i32(pos), slot_mapping=i32(slotmap),
+                             block_tables=torch.from_numpy(bt[slots]).to(dev), ctx_lens=i32(ctx), is_decode=False,
+                             q_start=i32(q_start), q_len=i32(q_len), max_q_len=max(q_len), want_mtp=self.mtp is not None)
+        self.stats["h2d_bytes"] += 4 * (3 * T + 3 * len(slots)) + bt[slots].nbytes
+        logits = self.model.forward(batch, self.kv_caches)
+        out = torch.empty(T, dtype=torch.int32, device=dev)
+        greedy = torch.zeros((T, 4), dtype=torch.float32, device=dev)
+        zeros = torch.zeros(T, dtype=torch.int64, device=dev)
+        keep = self._all_greedy
+        self._all_greedy = True
+        self._sample(logits, greedy, zeros, out)
+        mtp_choice = []
+        if self.mtp is not None:      # every row's candidates; the row of the last accepted token is picked below
+            for lg in self.model.last_mtp_logits[:self.mtp.depth]:
+                o = torch.empty(T, dtype=torch.int32, device=dev)
+                self._sample(lg, greedy, zeros, o)
+                mtp_choice.append(o.cpu().numpy())
+        self._all_greedy = keep
+        if self.d_status is not None:
+            self.h_status.copy_(self.d_status, non_blocking=True)
+        choice = out.cpu().numpy()
+        self.stats["d2h_bytes"] += T * 4
+        self.stats["decode_steps"] += 1
+        first = np.zeros(self.ms, np.int32)
+        extra = {}
+        st = self.spec_stats
+        st["steps"] += 1
+        for j, sl in enumerate(slots):
+            d = drafts[sl]
+            seg = choice[q_start[j]:q_start[j] + q_len[j]]
+            n_acc, nxt = verify_greedy(d, seg)
+            new = d[:n_acc] + [nxt]
+            first[sl] = new[0]
+            if len(new) > 1:
+                extra[int(ids[sl])] = new[1:]
+            st["drafted"] += len(d)
+            st["accepted"] += n_acc
+            st["emitted"] += len(new)
+            self.stats["decode_tokens"] += len(new)
+            if self.mtp is not None:
+                if from_mtp.get(sl):
+                    self.mtp.controller.update(n_acc, len(d))
+                row = q_start[j] + n_acc         # the hidden state behind the last token that stays
+                self._mtp_cand[int(ids[sl])] = [int(c[row]) for c in mtp_choice]
+        return first, extra
+
+    # ---- prefill / decode disaggregation (engine/pd.py) ------------------------------------------------
+    def _export_handoff(self, rid: int, first_token: int):
+        """Prefill-only role: ship the request with the KV of its prompt's full pages."""
+        from .pd import PdHandoff
+        prompt = self._pd_prompts.pop(rid)
+        n_full = len(prompt) // 16
+        pages = None
+        if n_full:
+            idx = torch.as_tensor(self.batcher.block_table_of(rid)[:n_full], dtype=torch.long, device=self.device)
+            pages = torch.stack([(c.view(torch.uint8) if c.dtype == torch.float8_e4m3fn else c).index_select(0, idx)
+                                 for c in self.kv_caches]).contiguous()
+        meta = getattr(self, "_pd_meta", {}).pop(rid, dict(max_tokens=256, temperature=0.0, top_k=0, top_p=1.0, eos_ids=[]))
+        self.stats["pd_exported"] = self.stats.get("pd_exported", 0) + 1
+        if self.pd_link is not None:
+            self.pd_link.send(PdHandoff(rid, prompt, first_token, meta, pages))
+
+    def import_handoff(self, h) -> int:
+        """Decode-only role: the prompt's full pages become cached prefix pages of this pool, then the request is
+        admitted; its admission finds them and computes only the partial last page before decoding."""
+        n_full = len(h.prompt) // 16
+        if n_full and h.pages is not None:
+            dst = self.batcher.import_prefix(h.prompt[:n_full * 16], "")
+            sel = [i for i, p in enumerate(dst) if p >= 0]          # -1: that page is already cached here
+            if sel:
+                src_idx = torch.as_tensor(sel, dtype=torch.long, device=self.device)
+                dst_idx = torch.as_tensor([dst[i] for i in sel], dtype=torch.long, device=self.device)
+                pages = h.pages.to(self.device)
+                for l, c in enumerate(self.kv_caches):
+                    tgt = c.view(torch.uint8) if c.dtype == torch.float8_e4m3fn else c
+                    tgt.index_copy_(0, dst_idx, pages[l].index_select(0, src_idx))
+        self.stats["pd_imported"] = self.stats.get("pd_imported", 0) + 1
+        p = h.params
+        return self.add_request(h.prompt, max_tokens=p["max_tokens"], temperature=p["temperature"], top_k=p["top_k"],
+                                top_p=p["top_p"], eos_ids=p["eos_ids"], request_id=h.request_id)
+
+    def _remaining_tokens(self, rid: int) -> int:
+        st = self.batcher.state_of(rid)
+        if st is None:
+            return 0
+        return int(st.get("max_new_tokens", 1 << 30)) - int(st.get("num_generated", 0))
+
     def _capture(self, B: int):
         # warm up outside capture so lazy initialisation (attribute setting, descriptor cache) is done
         s = torch.cuda.Stream(device=self.device)
@@ -342,7 +499,7 @@ class LLMEngine:
         batch = ForwardBatch(token_ids=dp[0:T], positions=dp[T:2 * T], slot_mapping=dp[2 * T:3 * T],
                              block_tables=self.d_pf_bt[:S_], ctx_lens=dp[3 * T + 2 * S_:3 * T + 3 * S_], is_decode=False,
                              q_start=dp[3 * T:3 * T + S_], q_len=dp[3 * T + S_:3 * T + 2 * S_],
-                             max_q_len=int(max_q), logits_rows=rows)
+                             max_q_len=int(max_q), logits_rows=rows, want_mtp=self.mtp is not None)
         self.stats["prefill_steps"] += 1
         self.stats["prefill_tokens"] += int(T)
         self.model.op_timer = getattr(self, "prefill_timer", None)   # utils.tracing.GraphTimer(eager=True) or None
@@ -362,6 +519,20 @@ class LLMEngine:
         out = self.d_pf_out[:n_last]
         self._sample(logits, self.d_pf_params[:n_last], offs, out)
         self.d_offsets.index_add_(0, sl, torch.ones(n_last, dtype=torch.int64, device=dev))
+        if self.mtp is not None and self.model.last_mtp_logits:
+            # the heads' candidates behind each finished prompt: the first decode step of the request verifies them
+            greedy = torch.zeros((n_last, 4), dtype=torch.float32, device=dev)
+            zeros = torch.zeros(n_last, dtype=torch.int64, device=dev)
+            keep, self._all_greedy = self._all_greedy, True
+            cands = []
+            for lg in self.model.last_mtp_logits[:self.mtp.depth]:
+                o = torch.empty(n_last, dtype=torch.int32, device=dev)
+                self._sample(lg, greedy, zeros, o)
+                cands.append(o.cpu().numpy())
+            self._all_greedy = keep
+            rids = [int(it.seq_id) for it in plan.prefill if it.last]
+            for j, rid in enumerate(rids):
+                self._mtp_cand[rid] = [int(c[j]) for c in cands]
         if self.d_status is not None:
             self.h_status.copy_(self.d_status, non_blocking=True)
         self.h_pf_out[:n_last].copy_(out, non_blocking=False)     # the only wait of the step: the sampled tokens
@@ -397,6 +568,9 @@ class LLMEngine:
     # ------------------------------------------------------------------------------------------
     def step(self) -> List[GenerateResult]:
         """One scheduler iteration: decode replay for the running set, then one prefill chunk batch."""
+        if self.cfg.pd_role == "decode_only" and getattr(self.pd_link, "nonblocking", False):
+            for h in self.pd_link.poll():      # a link that never blocks: take what the prefill side has finished
+                self.import_handoff(h)
         if self.kv_swap is not None and self.batcher.num_free_pages < max(8, self.num_pages // 16):
             # memory is tight: the batcher's next victims follow the eviction policy, not "youngest first"
             running = [rid for rid in self.reqs if rid not in self.kv_swap.keys]
@@ -422,9 +596,17 @@ class LLMEngine:
                 self.slot_params[it.slot] = (sp[0], sp[1], sp[2], float(it.seq_id))
         dec_tokens = np.zeros(self.ms, np.int32)
         pf_tokens = np.zeros(0, np.int32)
+        spec_extra = {}
         if plan.num_decode > 0:
-            with nvtx_range("decode_step"):
-                dec_tokens = self._run_decode(plan).copy()
+            spec = None
+            if (self.cfg.speculative_tokens > 0 or self.mtp is not None) and bool((self.slot_params[:, 0] <= 0).all()):
+                with nvtx_range("speculative_step"):
+                    spec = self._run_speculative_decode(plan)
+            if spec is not None:
+                dec_tokens, spec_extra = spec
+            else:
+                with nvtx_range("decode_step"):
+                    dec_tokens = self._run_decode(plan).copy()
         if plan.num_prefill_seqs > 0:
             with nvtx_range("prefill_chunk"):
                 pf_tokens = self._run_prefill(plan)
@@ -437,11 +619,22 @@ class LLMEngine:
         for sl in np.nonzero(ids >= 0)[0]:
             self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
         k = 0
+        handoff = []
         for it in plan.prefill:
             if it.last:
                 self._observe(int(it.seq_id), int(pf_tokens[k]), now)
+                if self.cfg.pd_role == "prefill_only":
+                    handoff.append((int(it.seq_id), int(pf_tokens[k])))
                 k += 1
+        for rid, tok in handoff:               # before the commit: the sequence still owns its pages
+            self._export_handoff(rid, tok)
         self.batcher.commit(plan, dec_tokens, pf_tokens)
+        for rid, _ in handoff:                 # the decode side continues the request; it ends here
+            self._vetoed[rid] = "handoff"
+        for rid, toks in spec_extra.items():       # the accepted drafts beyond the first token, and the bonus token
+            for t in toks:
+                self._observe(rid, int(t), now)
+            self.batcher.commit_tokens(rid, [int(t) for t in toks])
         return self._collect()
 
     # ---- lockstep (data-parallel attention + expert parallelism) -----------------------------------
@@ -533,6 +726,9 @@ class LLMEngine:
             st.t_first = now
         st.t_last = now
         st.n_out += 1
+        idx = self._spec_idx.get(rid)
+        if idx is not None:
+            idx.extend([tok])
         if st.stream is not None:
             st.stream(rid, tok)
         if st.hook is not None:
@@ -551,6 +747,8 @@ class LLMEngine:
                 self.kv_swap.drop(f.id)
             st = self.reqs.pop(f.id, None)
             self._req_params.pop(f.id, None)
+            self._spec_idx.pop(f.id, None)
+            self._mtp_cand.pop(f.id, None)
             toks = [int(t) for t in f.tokens]
             reason = S.FINISH_REASONS.get(f.finish, "length")
             if f.id in vetoed:

@@ -134,6 +134,18 @@ class DecoderModel:
             if self.fused:
                 head = _fold(head, self.final_norm, cfg.norm_one_plus_w)
             self.lm_head = L.pad_rows(head, 256).contiguous()
+        # Multi-token-prediction heads: ``mtp_proj.{d}`` [vocab, hidden] reads the final-normed hidden state and proposes
+        # the token d + 1 positions after the one the main head samples (the reference's graph tail:
+        # src/arch/auto_graph_fragments/build_graph.inc.rs:2615-2655). Sharded over the vocabulary like lm_head.
+        self.mtp_heads: List[torch.Tensor] = []
+        self.last_mtp_logits: List[torch.Tensor] = []
+        d = 0
+        while self.last_stage and src.has(f"mtp_proj.{d}"):
+            w = src.get(f"mtp_proj.{d}")[self.vocab_start:self.vocab_start + self.vocab_local].to(self.device, dtype)
+            if self.fused:
+                w = _fold(w, self.final_norm, cfg.norm_one_plus_w)
+            self.mtp_heads.append(L.pad_rows(w, 256).contiguous())
+            d += 1
         self._ws: Optional[Workspace] = None
 
     # ------------------------------------------------------------------------------------------
@@ -343,6 +355,14 @@ class DecoderModel:
             hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
             logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256)
         mark("lm_head")
+        self.last_mtp_logits = []
+        if self.mtp_heads and getattr(batch, "want_mtp", False):
+            for w in self.mtp_heads:      # same rows, same norm handling as the main head
+                if self.fused:
+                    self.last_mtp_logits.append(ops.gemm(xr, w, out_dtype=torch.float32, row_ss=sr, norm_dim=H,
+                                                         eps=c.rms_norm_eps, bn=256))
+                else:
+                    self.last_mtp_logits.append(ops.gemm(hn, w, out_dtype=torch.float32, bn=256))
         if c.logit_softcap:
             logits = torch.tanh(logits / c.logit_softcap) * c.logit_softcap
         return logits

@@ -183,3 +183,87 @@ def test_swap_tier_under_memory_pressure_gives_the_unconstrained_tokens(tmp_path
     rec = _tiny_engine(num_pages=22)
     assert [r.token_ids for r in rec.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])] == want
     assert rec.stats["preemptions"] > 0 and rec.stats.get("swap_outs", 0) == 0
+
+
+def test_speculative_decoding_in_the_engine_equals_plain_greedy():
+    """Prompt-lookup drafts verified by one forward per step: the same tokens as plain greedy decoding, in fewer steps
+    whenever drafts are accepted; acceptance statistics are kept."""
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(0, 1000, (12,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, 1000, (25,), generator=g).tolist(), (base[:5] * 6)[:29]]
+    plain = _tiny_engine(num_pages=128)
+    want = [r.token_ids for r in plain.generate_batch(prompts, max_tokens=48, temperature=0.0, eos_ids=[])]
+    spec = _tiny_engine(num_pages=128, speculative_tokens=4)
+    got = [r.token_ids for r in spec.generate_batch(prompts, max_tokens=48, temperature=0.0, eos_ids=[])]
+    assert got == want
+    st = spec.spec_stats
+    assert st["steps"] > 0 and st["drafted"] > 0 and 0 <= st["accepted"] <= st["drafted"]
+    assert st["emitted"] >= st["steps"]
+    if st["accepted"]:
+        assert spec.stats["decode_steps"] < plain.stats["decode_steps"]
+    # sampling requests never speculate (the verify rule here is the greedy one)
+    hot = _tiny_engine(num_pages=128, speculative_tokens=4)
+    hot.generate_batch(prompts[:1], max_tokens=8, temperature=0.8, eos_ids=[])
+    assert hot.spec_stats["steps"] == 0
+
+
+def test_mtp_heads_in_the_model_feed_the_verify_step():
+    """``mtp_proj.{d}`` heads in the checkpoint: the model emits candidates next to its main token, the next step
+    verifies them in one forward, the acceptance controller adapts the depth; tokens equal plain greedy decoding."""
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    base = RandomWeights(cfg, "cpu", torch.float32, seed=0)
+
+    class WithMtp:           # two heads that are copies of the output head: right whenever the output repeats itself
+        def has(self, n):
+            return n in ("mtp_proj.0", "mtp_proj.1") or base.has(n)
+
+        def get(self, n):
+            if n.startswith("mtp_proj."):
+                return base.get("lm_head") if base.has("lm_head") else base.get("embed_tokens")
+            return base.get(n)
+    model = DecoderModel(cfg, WithMtp(), device="cpu", dtype=torch.float32, max_positions=256)
+    assert len(model.mtp_heads) == 2
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (36, 25, 29)]
+    ec = dict(max_num_seqs=6, max_model_len=160, max_batch_tokens=256, prefill_chunk=128, num_pages=128)
+    want = [r.token_ids for r in LLMEngine(model, EngineConfig(**ec)).generate_batch(prompts, max_tokens=48, temperature=0.0, eos_ids=[])]
+    eng = LLMEngine(model, EngineConfig(mtp_depth=2, **ec))
+    assert eng.mtp is not None and eng.mtp.depth == 2
+    got = [r.token_ids for r in eng.generate_batch(prompts, max_tokens=48, temperature=0.0, eos_ids=[])]
+    assert got == want
+    assert eng.spec_stats["drafted"] > 0 and 0.0 <= eng.mtp.controller.ema <= 1.0
+
+
+def test_prefill_and_decode_roles_hand_requests_over_with_their_kv_pages():
+    """A prefill_only engine and a decode_only engine joined by a link produce what one collocated engine produces;
+    the decode side computes only the partial last page of each prompt."""
+    from gllm_b200.engine.pd import InProcessPdLink
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (50, 33, 64, 19)]
+    want = [r.token_ids for r in _tiny_engine(num_pages=128).generate_batch(prompts, max_tokens=12, temperature=0.0, eos_ids=[])]
+    link = InProcessPdLink()
+    pre = _tiny_engine(num_pages=128, pd_role="prefill_only", enable_prefix_cache=True)
+    dec = _tiny_engine(num_pages=128, pd_role="decode_only", enable_prefix_cache=True)
+    pre.pd_link, dec.pd_link = link, link
+    ids = [pre.add_request(p, max_tokens=12, temperature=0.0, eos_ids=[]) for p in prompts]
+    first = {}
+    while pre.has_work():
+        for r in pre.step():
+            assert r.finish_reason == "handoff" and len(r.token_ids) == 1
+            first[r.request_id] = r.token_ids[0]
+    assert pre.stats["decode_steps"] == 0 and pre.stats["pd_exported"] == 4
+    done = {}
+    for _ in range(200):
+        for r in dec.step():
+            done[r.request_id] = r
+        if len(done) == 4:
+            break
+    assert [done[i].token_ids for i in ids] == want
+    assert all(first[i] == want[j][0] for j, i in enumerate(ids))      # the prefill side's first token is the same one
+    assert dec.stats["pd_imported"] == 4
+    # 50 -> 3 cached pages (48), 33 -> 32, 64 -> 48 (one token is always left to compute), 19 -> 16
+    assert [done[i].telemetry.cached_prefix_tokens for i in ids] == [48, 32, 48, 16]
+    assert dec.stats["prefill_tokens"] == sum(len(p) for p in prompts) - (48 + 32 + 48 + 16)
