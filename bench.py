@@ -37,7 +37,13 @@ def parse_args():
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--shared-prefix", type=int, default=512)
-    ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "fused_p2p", "pull", "nccl"])
+    ap.add_argument("--parallel", default="tp",
+                    help="tp (tensor parallel over all GPUs, the headline), ep (data-parallel attention + expert-parallel "
+                         "MoE, engines in lockstep), or tpXppY (X-way tensor parallel stages of a Y-stage pipeline)")
+    ap.add_argument("--weight-quant", default=None, choices=[None, "mxfp8", "nvfp4"],
+                    help="linear weights (and activations) block-scaled on the tensor cores")
+    ap.add_argument("--expert-quant", default=None, choices=[None, "mxfp8", "nvfp4"], help="MoE expert weights block-scaled")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"],
                     help="fp8: e4m3 KV cache (half the KV bytes); not the headline configuration, reported as invalid for it")
@@ -155,24 +161,65 @@ def main():
     cfg = preset(args.model)
     if args.layers:
         cfg.num_layers = args.layers
-    tp = None
-    if world > 1:
-        from gllm_b200.parallel.tensor_parallel import TPContext
-        tp = TPContext(rank, world, dev, mode=args.tp_mode, max_tokens=8192, hidden=cfg.hidden_size)
+    # ---- parallel layout: ranks = pipeline stage * tp + tensor-parallel index ----
+    import re
+    par = args.parallel.lower()
+    tp_size, pp_size, ep_mode = world, 1, False
+    if par == "ep":
+        tp_size, ep_mode = 1, world > 1
+    elif par != "tp":
+        m = re.fullmatch(r"tp(\d+)(?:pp(\d+))?", par)
+        if not m:
+            raise SystemExit(f"--parallel {args.parallel!r}: expected tp, ep or tpXppY")
+        tp_size, pp_size = int(m.group(1)), int(m.group(2) or 1)
+        if tp_size * pp_size != world:
+            raise SystemExit(f"--parallel {args.parallel}: {tp_size} x {pp_size} != {world} GPUs")
+    stage, tpi = rank // tp_size, rank % tp_size
     max_len = args.max_prompt + args.output_tokens + 16
+    tp = ep = pp_ctx = None
+    lockstep = None
+    if tp_size > 1:
+        from gllm_b200.parallel.tensor_parallel import TPContext
+        tp_group = None
+        if pp_size > 1:      # one tensor-parallel group per pipeline stage (creating a group is collective over the world)
+            for st in range(pp_size):
+                g = dist.new_group(list(range(st * tp_size, (st + 1) * tp_size)))
+                if st == stage:
+                    tp_group = g
+        tp = TPContext(tpi, tp_size, dev, mode=args.tp_mode, max_tokens=8192, hidden=cfg.hidden_size, group=tp_group)
+    if pp_size > 1:
+        from gllm_b200.engine.pp import build_pipeline
+        from gllm_b200.parallel.comm import CommHandle
+        pp_ctx = build_pipeline(CommHandle.from_env("nccl", device=dev), pp=pp_size, tp=tp_size)
+    if ep_mode:
+        from gllm_b200.parallel.expert_parallel import EPContext
+        ep = EPContext(rank, world, dev, num_experts=cfg.num_experts, hidden=cfg.hidden_size,
+                       top_k=cfg.num_experts_per_tok, max_tokens=8192, mode="fused")
+        lockstep = dist.group.WORLD
+    layers = None
+    if pp_size > 1:
+        from gllm_b200.parallel.pipeline import PipelineConfig
+        layers = PipelineConfig(num_layers=cfg.num_layers, num_stages=pp_size).stage_ranges()[stage]
     src = RandomWeights(cfg, dev, torch.bfloat16, seed=0)
     kv_kw = dict(kv_dtype=torch.float8_e4m3fn, kv_scale=0.05) if args.kv_dtype == "fp8" else {}
-    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len, **kv_kw)
+    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len, layers=layers, ep=ep,
+                         weight_quant=args.weight_quant, expert_quant=args.expert_quant, **kv_kw)
+    # data-parallel attention: every rank serves its own share of the requests
+    conc_total = args.concurrency
+    if ep_mode:
+        args.concurrency = max(1, args.concurrency // world)
     ecfg = EngineConfig(max_num_seqs=args.concurrency, max_model_len=max_len, max_batch_tokens=8192,
                         prefill_chunk=8192, use_cuda_graphs=not args.no_graphs)
     ecfg.num_pages = args.concurrency * ((max_len + 15) // 16) + 64
-    engine = LLMEngine(model, ecfg)
+    engine = LLMEngine(model, ecfg, lockstep_group=lockstep, pp=pp_ctx)
     engine.precapture()        # decode graphs for every batch bucket, as a server does at start-up (not part of TTFT)
-    prompts = make_prompts(args.concurrency, args.min_prompt, args.max_prompt, args.shared_prefix, cfg.vocab_size)
+    prompts = make_prompts(conc_total, args.min_prompt, args.max_prompt, args.shared_prefix, cfg.vocab_size)
+    if ep_mode:
+        prompts = prompts[rank::world]
 
     # ---- phase 0 (N > 1): the tensor-parallel engine must produce the single-GPU model's tokens ----
     tp1_check = None
-    if world > 1 and not args.no_tp1_check:
+    if world > 1 and par == "tp" and not args.no_tp1_check:
         check_prompts = make_prompts(8, 24, 96, 16, cfg.vocab_size, seed=4321)
         got = [r.token_ids for r in engine.generate_batch(check_prompts, max_tokens=8, temperature=0.0, eos_ids=[])]
         if rank == 0:
@@ -208,7 +255,15 @@ def main():
     ids = [engine.add_request(p, max_tokens=budget_tokens, temperature=0.0, eos_ids=[]) for p in prompts]
     first_token_at = {}
     guard = 0
-    while engine.batcher.num_running < args.concurrency and guard < 10000:
+    def prefilling():
+        mine = 1 if engine.batcher.num_running < len(prompts) else 0
+        if lockstep is None:
+            return bool(mine)
+        f = torch.tensor([mine], dtype=torch.int32, device=dev)      # lockstep engines step together until all are done
+        dist.all_reduce(f, op=dist.ReduceOp.MAX)
+        return bool(int(f[0]))
+
+    while prefilling() and guard < 10000:
         engine.step()
         now = time.perf_counter()
         for rid, st in engine.reqs.items():
@@ -268,7 +323,7 @@ def main():
     # ---- phase 5 (N > 1): the baseline arm, same engine, same step, collectives on NCCL ----
     # unfused row-parallel GEMM -> ncclAllReduce -> residual/norm-statistics kernel, captured as its own CUDA graph
     nccl_ms = None
-    if world > 1 and tp is not None and tp.mode == "fused" and not args.no_baseline and graph is not None:
+    if world > 1 and par == "tp" and tp is not None and tp.mode == "fused" and not args.no_baseline and graph is not None:
         tp.baseline = True
         keep = engine.graphs.pop((B, True))
         try:
@@ -304,11 +359,15 @@ def main():
         breakdown = {n: round(float(v), 4) for n, v in zip(names, bt.tolist())}
 
     t = torch.tensor([dev_ms, e2e_s * 1e3, nccl_ms or 0.0], dtype=torch.float64, device=dev)
+    cnt = torch.tensor([float(e2e_tokens)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if ep_mode:
+            dist.all_reduce(cnt, op=dist.ReduceOp.SUM)      # every rank served its own requests
     dev_ms, e2e_ms = float(t[0]), float(t[1])
     nccl_ms = float(t[2]) if nccl_ms is not None else None
-    n_active = args.concurrency
+    e2e_tokens = float(cnt[0])
+    n_active = conc_total
     value = n_active * K / (dev_ms / 1e3)
     e2e_value = e2e_tokens / (e2e_ms / 1e3)
     if rank == 0:
@@ -319,11 +378,13 @@ def main():
             "vs_baseline": (round(nccl_ms / dev_ms, 4) if nccl_ms else None), "dtype": "bf16", "data": "synthetic (random-init weights, uniform-random token ids)",
             "config": {"model": f"{args.model}-shape " + ("MoE decoder" if cfg.is_moe else "dense decoder"), "global_batch": n_active,
                        "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {budget_tokens} out",
-                       "parallelism": f"tp{world}", "kv_page": 16, "shared_prefix": args.shared_prefix,
+                       "parallelism": (f"ep{world} experts + data-parallel attention" if ep_mode else
+                                       f"tp{tp_size}" + (f"pp{pp_size}" if pp_size > 1 else "")), "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
                        "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
                        "layers": cfg.num_layers, "kv_dtype": args.kv_dtype,
-                       "valid": args.layers == 0 and args.kv_dtype == "bf16"},
+                       "weight_quant": args.weight_quant, "expert_quant": args.expert_quant,
+                       "valid": args.layers == 0 and (args.kv_dtype == "bf16" or args.model != "qwen3-8b")},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms / K, 4)},
             "gpu_launches": int(launches_per_step * K),

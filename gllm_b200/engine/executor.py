@@ -60,6 +60,12 @@ class EngineConfig:
     # role of this engine in a prefill / decode disaggregated deployment (parallel/pd.py): "collocated",
     # "prefill_only" (finished prefills are handed to `pd_link` with their KV pages) or "decode_only"
     pd_role: str = "collocated"
+    # runtime heuristics: decode batch buckets follow the observed batch sizes (runtime/buckets.py), captured graphs
+    # live in a budgeted registry (runtime/variants.py), and a background director (runtime/director.py) turns
+    # sustained drift of the batch size into a re-derivation of the buckets
+    adaptive_buckets: bool = False
+    graph_budget_bytes: int = 8 << 30
+    director: bool = False
 
 
 @dataclass
@@ -73,12 +79,14 @@ class _ReqState:
 
 
 class LLMEngine:
-    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None, lockstep_group=None, pd_link=None):
+    def __init__(self, model: DecoderModel, cfg: EngineConfig = None, tokenizer=None, lockstep_group=None, pd_link=None,
+                 pp=None):
         """``lockstep_group``: a process group whose ranks serve DIFFERENT requests but share collective kernels
         inside the model (data-parallel attention + expert-parallel MoE). Every rank then runs the same sequence of
         forwards per step (a rank without work runs an empty one), agreed on by one tiny all-reduce per step."""
         self.model, self.cfg, self.tokenizer = model, cfg or EngineConfig(), tokenizer
         self.lockstep = lockstep_group
+        self.pp = pp                           # engine/pp.py PipelineContext: this engine runs one pipeline stage
         self.pd_link = pd_link                 # engine/pd.py link: where a prefill_only engine sends, a decode_only one polls
         self._pd_prompts: Dict[int, List[int]] = {}
         self.mc: ModelConfig = model.cfg
@@ -147,7 +155,21 @@ class LLMEngine:
         if self.decode_ws is not None:
             self.decode_ws.pages_per_split = pps
         model.workspace(max(ec.max_batch_tokens, self.ms))
+        if pp is not None:
+            self.pp_hidden = torch.zeros((max(ec.max_batch_tokens, self.ms), self.mc.hidden_size), dtype=model.dtype, device=dev)
+            ec.use_cuda_graphs = False      # the stage-to-stage transfers run as ordinary p2p calls between the launches
         self.graphs: Dict[int, "torch.cuda.CUDAGraph"] = {}
+        from ..runtime.buckets import GoldenBuckets
+        from ..runtime.director import Director, DirectorSharedState
+        from ..runtime.variants import VariantRegistry
+        sizes = sorted({min(b, self.ms) for b in DECODE_BUCKETS})
+        self.buckets = GoldenBuckets(buckets=sizes, max_buckets=max(12, len(sizes)))
+        self.variants = VariantRegistry(ec.graph_budget_bytes)
+        self.director_state = DirectorSharedState()
+        self.director = None
+        self._evolve_pending = False
+        if ec.director:
+            self.director = Director(self.director_state, on_event=self._on_director_event, interval_s=1.0).spawn()
         self.reqs: Dict[int, _ReqState] = {}
         self.results: Dict[int, GenerateResult] = {}
         self._next_id = 0
@@ -213,10 +235,21 @@ class LLMEngine:
 
     # ------------------------------------------------------------------------------------------
     def _bucket(self, n: int) -> int:
-        for b in DECODE_BUCKETS:
-            if b >= n:
-                return min(b, self.ms)
-        return self.ms
+        return min(self.buckets.bucket_for(n), self.ms)
+
+    def _on_director_event(self, ev):
+        """Director thread: the batch size has drifted for several windows in a row -> re-derive the buckets at the next
+        step (on the serving thread: graph capture is not thread-safe)."""
+        if ev.kind == "bucket_drift":
+            self._evolve_pending = True
+
+    def evolve_buckets(self):
+        """Re-derive the decode buckets from the observed batch sizes; graphs of new buckets are captured on first use,
+        graphs of dropped buckets leave the registry when its budget needs the room."""
+        before = list(self.buckets.buckets)
+        after = self.buckets.evolve()
+        self._evolve_pending = False
+        return before, list(after)
 
     def _decode_batch(self, B: int) -> ForwardBatch:
         ms = self.ms
@@ -224,7 +257,27 @@ class LLMEngine:
                             slot_mapping=self.d_dec[2 * ms:2 * ms + B], block_tables=self.d_bt[:B],
                             ctx_lens=self.d_dec[3 * ms:3 * ms + B], is_decode=True)
 
+    def _pp_forward(self, batch, T: int, **kw):
+        """One pipeline stage of a forward over ``T`` tokens: hidden states in from the previous stage, out to the
+        next; only the last stage returns logits (the others return None)."""
+        pp = self.pp
+        hidden_in = None
+        if not pp.is_first:
+            hidden_in = pp.recv_hidden(self.pp_hidden[:T])
+        out = self.model.forward(batch, self.kv_caches, hidden_in=hidden_in, **kw)
+        if not pp.is_last:
+            pp.send_hidden(out[:T])
+            return None
+        return out
+
     def _decode_body(self, B: int):
+        if self.pp is not None:
+            logits = self._pp_forward(self._decode_batch(B), B, decode_ws=self.decode_ws)
+            if logits is not None:
+                self._sample(logits, self.d_params[:B], self.d_offsets[:B], self.d_out[:B])
+            self.pp.share_tokens(self.d_out[:B])
+            self.d_offsets[:B] += 1
+            return
         logits = self.model.forward(self._decode_batch(B), self.kv_caches, decode_ws=self.decode_ws)
         self._sample(logits, self.d_params[:B], self.d_offsets[:B], self.d_out[:B])
         self.d_offsets[:B] += 1
@@ -291,7 +344,13 @@ class LLMEngine:
         self.batcher.copy_slot_block_tables_into(self.h_bt.numpy().reshape(-1))
         ids = plan.dec_seq_ids
         active = np.nonzero(ids >= 0)[0]
-        B = self._bucket(int(active[-1]) + 1)
+        n_slots = int(active[-1]) + 1
+        self.buckets.observe(n_slots)
+        with self.director_state.lock:
+            self.director_state.batch_sizes.add(float(n_slots))
+        if self.cfg.adaptive_buckets and (self._evolve_pending or (self.stats["decode_steps"] + 1) % 512 == 0):
+            self.evolve_buckets()
+        B = self._bucket(n_slots)
         self.h_params.numpy()[:] = self.slot_params
         cuda = self.device.type == "cuda"
         self.d_dec.copy_(self.h_dec, non_blocking=cuda)
@@ -305,6 +364,7 @@ class LLMEngine:
             if g is None and self.lockstep is None:
                 g = self._capture(B)
             if g is not None:
+                self._note_variant_hit(key)
                 g.replay()
             else:     # lockstep: a capture (with its warm-up run) cannot happen on one rank alone; see precapture()
                 self._decode_body(B)
@@ -468,7 +528,31 @@ class LLMEngine:
             self._decode_body(B)
         self.launches_per_graph[B] = nv.CALLS[0] - n0
         self.graphs[(B, self._all_greedy)] = g
+        self._register_variant((B, self._all_greedy), g)
         return g
+
+    def _variant_key(self, key):
+        from ..runtime.variants import MechanismId, VariantKey
+        mech = (MechanismId.DENSE,) if key[1] else (MechanismId.DENSE, MechanismId.SAMPLED)
+        if self.mc.is_moe:
+            mech = mech + (MechanismId.MOE_EP,) if getattr(self.model, "ep", None) is not None else mech
+        return VariantKey(int(key[0]), mech)
+
+    def _register_variant(self, key, graph):
+        """Captured graphs are budgeted: a graph pins its private memory pool, so cold ones leave when a new one
+        would exceed the budget (the reference budgets JIT code in the instruction cache the same way)."""
+        from ..runtime.variants import CompiledVariant
+        est = int(key[0]) * self.mc.hidden_size * 64 + (8 << 20)      # activations a graph's pool keeps alive
+        vk = self._variant_key(key)
+        self.variants.register(CompiledVariant(vk, graph, bytes=est))
+        live = {v.key for v in self.variants.variants.values()}
+        for k in [k for k in self.graphs if self._variant_key(k) not in live]:
+            del self.graphs[k]                                         # evicted by the registry: drop the graph
+
+    def _note_variant_hit(self, key):
+        v = self.variants.variants.get(self._variant_key(key))
+        if v is not None:
+            v.hits += 1
 
     def _run_prefill(self, plan) -> np.ndarray:
         t_host0 = time.perf_counter()
@@ -504,10 +588,15 @@ class LLMEngine:
         self.stats["prefill_tokens"] += int(T)
         self.model.op_timer = getattr(self, "prefill_timer", None)   # utils.tracing.GraphTimer(eager=True) or None
         try:
-            if rows is None:
+            if self.pp is not None:
+                logits = self._pp_forward(batch, T, return_hidden=rows is None)
+                if rows is None:
+                    return np.zeros(0, np.int32)
+            elif rows is None:
                 self.model.forward(batch, self.kv_caches, return_hidden=True)
                 return np.zeros(0, np.int32)
-            logits = self.model.forward(batch, self.kv_caches)
+            else:
+                logits = self.model.forward(batch, self.kv_caches)
         finally:
             self.model.op_timer = None
         last_slots = self.h_pf.numpy()[o + n_last:o + 2 * n_last]
@@ -517,7 +606,10 @@ class LLMEngine:
         sl = dp[o + n_last:o + 2 * n_last]
         offs = self.d_offsets.index_select(0, sl)
         out = self.d_pf_out[:n_last]
-        self._sample(logits, self.d_pf_params[:n_last], offs, out)
+        if logits is not None:
+            self._sample(logits, self.d_pf_params[:n_last], offs, out)
+        if self.pp is not None:
+            self.pp.share_tokens(out)
         self.d_offsets.index_add_(0, sl, torch.ones(n_last, dtype=torch.int64, device=dev))
         if self.mtp is not None and self.model.last_mtp_logits:
             # the heads' candidates behind each finished prompt: the first decode step of the request verifies them

@@ -267,3 +267,18 @@ def test_prefill_and_decode_roles_hand_requests_over_with_their_kv_pages():
     # 50 -> 3 cached pages (48), 33 -> 32, 64 -> 48 (one token is always left to compute), 19 -> 16
     assert [done[i].telemetry.cached_prefix_tokens for i in ids] == [48, 32, 48, 16]
     assert dec.stats["prefill_tokens"] == sum(len(p) for p in prompts) - (48 + 32 + 48 + 16)
+
+
+def test_engine_buckets_follow_the_observed_batch_sizes_and_the_director():
+    from gllm_b200.runtime.director import ConsensusEvent
+    eng = _tiny_engine(num_pages=128, max_num_seqs=6, adaptive_buckets=True)
+    assert eng._bucket(3) == 4 and eng._bucket(6) == 6 and eng.buckets.buckets[-1] == 6
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1000, (12,), generator=g).tolist() for _ in range(3)]
+    eng.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])
+    assert eng.buckets.hist.total >= 39 and eng.director_state.batch_sizes.mean() > 0
+    eng._on_director_event(ConsensusEvent("bucket_drift", 0, 0.9))
+    assert eng._evolve_pending
+    before, after = eng.evolve_buckets()
+    assert after[-1] == 6 and 3 in after or 4 in after       # three running sequences: a bucket near 3, capacity kept
+    assert not eng._evolve_pending

@@ -298,6 +298,17 @@ def test_pipeline_parallel_generation_matches_single_process(world):
     assert r.stdout.count("PP_WORKER_OK") == world
 
 
+@pytest.mark.parametrize("world", [2])
+def test_serving_engine_as_pipeline_stages_matches_single_process(world):
+    """The real LLMEngine (C++ batcher, paged KV, chunked prefill) run as pipeline stages over gloo."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29820 + world), os.path.join(ROOT, "tests", "pp_engine_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("PP_ENGINE_WORKER_OK") == world
+
+
 def test_tp_attention_with_expert_sharded_moe_matches_unsplit_model():
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
