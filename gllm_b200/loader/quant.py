@@ -33,7 +33,8 @@ _T = [
     QuantType(9, "Q8_1", 32, 36), QuantType(10, "Q2_K", 256, 84), QuantType(11, "Q3_K", 256, 110),
     QuantType(12, "Q4_K", 256, 144), QuantType(13, "Q5_K", 256, 176), QuantType(14, "Q6_K", 256, 210),
     QuantType(15, "Q8_K", 256, 292),
-    # codebook formats: geometry known, grids not shipped -> metadata only
+    # codebook formats (lattice grids): decoded through the ``gguf`` package's tables when that package is importable
+    # (it ships the grids of every IQ type), metadata only otherwise
     QuantType(16, "IQ2_XXS", 256, 66, False), QuantType(17, "IQ2_XS", 256, 74, False),
     QuantType(18, "IQ3_XXS", 256, 98, False), QuantType(19, "IQ1_S", 256, 50, False),
     QuantType(20, "IQ4_NL", 32, 18), QuantType(21, "IQ3_S", 256, 110, False), QuantType(22, "IQ2_S", 256, 82, False),
@@ -75,7 +76,7 @@ def dequantize(type_id: int, raw, n_elems: int) -> torch.Tensor:
     if t is None:
         raise ValueError(f"unknown quant type id {type_id}")
     if not t.supported:
-        raise NotImplementedError(f"{t.name} needs codebook grids that are not shipped; convert the checkpoint")
+        return _dequantize_codebook(t, raw, n_elems)
     if t.name in ("I8", "I16", "I32", "I64", "F64"):
         dt = {"I8": np.int8, "I16": np.int16, "I32": np.int32, "I64": np.int64, "F64": np.float64}[t.name]
         return torch.from_numpy(np.frombuffer(raw, dtype=dt, count=n_elems).astype(np.float32))
@@ -85,6 +86,33 @@ def dequantize(type_id: int, raw, n_elems: int) -> torch.Tensor:
     if rc != 0:
         raise RuntimeError(f"dequantize({t.name}) failed")
     return torch.from_numpy(out)
+
+
+def codebook_backend_available() -> bool:
+    try:
+        import gguf.quants  # noqa: F401
+        return True
+    except Exception:
+        return False
+
+
+def _dequantize_codebook(t: QuantType, raw, n_elems: int) -> torch.Tensor:
+    """IQ1 / IQ2 / IQ3 blocks index lattice codebooks of a few thousand entries. Those tables are data of the GGML
+    format, not of this engine: when the ``gguf`` package (the format's own Python library) is installed its tables
+    decode the blocks; without it the type stays metadata-only and the loader says so."""
+    try:
+        import gguf
+        from gguf import quants as gq
+    except Exception as exc:
+        raise NotImplementedError(
+            f"{t.name} needs the codebook grids of the GGML format; install the `gguf` package or convert the checkpoint") from exc
+    qt = getattr(gguf.GGMLQuantizationType, t.name, None)
+    if qt is None:
+        raise NotImplementedError(f"the installed gguf package does not know {t.name}")
+    n_bytes = nbytes(t.id, n_elems)
+    buf = np.frombuffer(raw, dtype=np.uint8, count=n_bytes).reshape(n_elems // t.block_elems, t.block_bytes)
+    out = gq.dequantize(buf, qt)
+    return torch.from_numpy(np.ascontiguousarray(out, dtype=np.float32).reshape(-1))
 
 
 # ------------------------------------------------------------------------------------------------

@@ -102,8 +102,13 @@ def test_every_supported_type_decodes_whole_blocks():
         raw = bytearray(rng.randint(0, 256, size=t.block_bytes * 2, dtype=np.uint8).tobytes())
         y = quant.dequantize(t.id, bytes(raw), t.block_elems * 2)
         assert y.shape == (t.block_elems * 2,)
-    with pytest.raises(NotImplementedError):
-        quant.dequantize(quant.BY_NAME["IQ2_XXS"].id, b"\0" * 66, 256)
+    if quant.codebook_backend_available():      # lattice-codebook types decode through the gguf package's tables
+        assert quant.dequantize(quant.BY_NAME["IQ2_XXS"].id, b"\0" * 66, 256).shape == (256,)
+    else:
+        with pytest.raises(NotImplementedError):
+            quant.dequantize(quant.BY_NAME["IQ2_XXS"].id, b"\0" * 66, 256)
+    with pytest.raises(NotImplementedError):     # a format nobody can decode stays an explicit error
+        quant.dequantize(quant.BY_NAME["SQUEEZE"].id, b"\0" * 72, 128)
     # hand-built classic blocks (split nibbles: low nibble -> element j, high -> element j+16)
     blk = np.float16(0.5).tobytes() + bytes([0x1F] * 16)
     y = quant.dequantize(2, blk, 32).numpy()
@@ -344,3 +349,103 @@ def test_onnx_initializers(tmp_path):
     tensors, nodes = read_onnx(tmp_path / "m.onnx")
     assert np.array_equal(tensors["encoder.layer.0.attention.self.query.weight"].numpy(), w)
     assert [n["op_type"] for n in nodes] == ["MatMul", "Add"] and fused_patterns(nodes)["linear"] == 1
+
+
+def test_codebook_gguf_types_decode_through_the_format_library():
+    """IQ1 / IQ2 / IQ3 blocks (lattice codebooks) decode through the tables of the ``gguf`` package when it is there;
+    the block geometry is ours. The block scale is linear: doubling the fp16 ``d`` field doubles every value."""
+    import numpy as np
+    from gllm_b200.loader import quant as Q
+    if not Q.codebook_backend_available():
+        import pytest
+        pytest.skip("gguf package not installed")
+    rng = np.random.RandomState(0)
+    for name in ("IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S"):
+        t = Q.BY_NAME[name]
+        raw = rng.randint(0, 256, size=(3, t.block_bytes), dtype=np.uint8)
+        raw[:, 0:2] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
+        a = Q.dequantize(t.id, raw.tobytes(), 3 * t.block_elems)
+        raw[:, 0:2] = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
+        b = Q.dequantize(t.id, raw.tobytes(), 3 * t.block_elems)
+        assert a.shape == (3 * t.block_elems,) and torch.isfinite(a).all() and a.abs().max() > 0
+        torch.testing.assert_close(b, 2 * a)
+    m = Q.BY_NAME["IQ1_M"]
+    out = Q.dequantize(m.id, rng.randint(0, 256, size=(2, m.block_bytes), dtype=np.uint8).tobytes(), 2 * m.block_elems)
+    assert out.shape == (512,)
+
+
+def test_onnx_graph_import_recovers_fused_ops_and_names_anonymous_weights(tmp_path):
+    """A one-layer BERT-style export written node by node, with initializer names that say nothing
+    (``onnx::MatMul_7``): decomposed LayerNorm, erf-GELU, MatMul+Add and the softmax attention core are recovered as
+    fused ops and the structure alone names every weight."""
+    from gllm_b200.loader.onnx import OnnxProvider, import_graph
+
+    def vi(n):
+        out = b""
+        while True:
+            b7 = n & 0x7F
+            n >>= 7
+            out += bytes([b7 | (0x80 if n else 0)])
+            if not n:
+                return out
+    ld = lambda fn, payload: vi((fn << 3) | 2) + vi(len(payload)) + payload
+
+    def tensor(name, arr):
+        b = b"".join(vi((1 << 3) | 0) + vi(d) for d in arr.shape) + vi((2 << 3) | 0) + vi(1)
+        return b + ld(8, name.encode()) + ld(9, arr.astype("<f4").tobytes())
+    node = lambda op, ins, outs: b"".join(ld(1, i.encode()) for i in ins) + b"".join(ld(2, o.encode()) for o in outs) + ld(4, op.encode())
+    H = 8
+    rng = np.random.RandomState(0)
+    inits, nodes, k = {}, [], [0]
+
+    def w(shape):
+        k[0] += 1
+        name = f"onnx::MatMul_{k[0]}"
+        inits[name] = np.asarray(rng.randn(*shape), dtype=np.float32)
+        return name
+
+    def layernorm(x, out):
+        g, b, eps, two = w((H,)), w((H,)), w(()), w(())
+        nodes.extend([("ReduceMean", [x], [out + "_m"]), ("Sub", [x, out + "_m"], [out + "_c"]),
+                      ("Pow", [out + "_c", two], [out + "_p"]), ("ReduceMean", [out + "_p"], [out + "_v"]),
+                      ("Add", [out + "_v", eps], [out + "_e"]), ("Sqrt", [out + "_e"], [out + "_s"]),
+                      ("Div", [out + "_c", out + "_s"], [out + "_n"]), ("Mul", [out + "_n", g], [out + "_g"]),
+                      ("Add", [out + "_g", b], [out])])
+        return g, b
+
+    def linear(x, out, n_in, n_out):
+        wt, bs = w((n_in, n_out)), w((n_out,))
+        nodes.extend([("MatMul", [x, wt], [out + "_mm"]), ("Add", [out + "_mm", bs], [out])])
+        return wt, bs
+    table = w((30, H))
+    nodes.append(("Gather", [table, "input_ids"], ["emb"]))
+    g0, _ = layernorm("emb", "h0")
+    q, _ = linear("h0", "q", H, H)
+    kk, _ = linear("h0", "k", H, H)
+    v, _ = linear("h0", "v", H, H)
+    sc = w(())
+    nodes.extend([("Transpose", ["k"], ["kt"]), ("MatMul", ["q", "kt"], ["s"]), ("Div", ["s", sc], ["ss"]),
+                  ("Add", ["ss", "mask"], ["sm"]), ("Softmax", ["sm"], ["p"]), ("MatMul", ["p", "v"], ["ctx"])])
+    o, _ = linear("ctx", "ao", H, H)
+    nodes.append(("Add", ["ao", "h0"], ["r1"]))
+    g1, _ = layernorm("r1", "h1")
+    up, _ = linear("h1", "u", H, 4 * H)
+    c2, c1, ch = w(()), w(()), w(())
+    nodes.extend([("Div", ["u", c2], ["u_d"]), ("Erf", ["u_d"], ["u_e"]), ("Add", ["u_e", c1], ["u_a"]),
+                  ("Mul", ["u", "u_a"], ["u_m"]), ("Mul", ["u_m", ch], ["act"])])
+    dn, _ = linear("act", "d", 4 * H, H)
+    nodes.append(("Add", ["d", "h1"], ["r2"]))
+    g2, _ = layernorm("r2", "h2")
+    graph = b"".join(ld(1, node(*n)) for n in nodes) + b"".join(ld(5, tensor(n, a)) for n, a in inits.items())
+    (tmp_path / "enc.onnx").write_bytes(ld(7, graph))
+    tensors, ops, names = import_graph(tmp_path / "enc.onnx")
+    kinds = [o.kind for o in ops if o.kind != "other"]
+    assert kinds == ["embedding", "layernorm", "linear", "linear", "linear", "attention", "linear", "add", "layernorm",
+                     "linear", "gelu", "linear", "add", "layernorm"]
+    assert sum(len(o.nodes) for o in ops) == len(nodes)                  # every node belongs to exactly one op
+    want = {"embed_tokens": table, "embed_norm": g0, "L0.q_proj": q, "L0.k_proj": kk, "L0.v_proj": v, "L0.o_proj": o,
+            "L0.post_attn_norm": g1, "L0.up_proj": up, "L0.down_proj": dn, "L0.post_ffn_norm": g2}
+    assert {k_: names[k_] for k_ in want} == want and "L0.q_proj_bias" in names and "L0.post_ffn_norm_bias" in names
+    prov = OnnxProvider(tmp_path / "enc.onnx", dtype=torch.float32)
+    # MatMul weights are stored [in, out] in the export; the provider hands out [out, in]
+    assert torch.equal(prov.get("L0.up_proj"), torch.from_numpy(inits[up]).t())
