@@ -57,20 +57,24 @@ def _run(cmd, verbose=False):
     return r
 
 
-def build_kernels(force=False, verbose=False) -> Path:
-    """nvcc -> libgllm_kernels.so (all .cu files under csrc/kernels)."""
+def build_kernels(force=False, verbose=False, trace=False) -> Path:
+    """nvcc -> libgllm_kernels.so (all .cu files under csrc/kernels). ``trace``: a second library,
+    libgllm_kernels_trace.so, compiled with -DGLLM_TRACE (phase stamps in the GEMM kernel; loaded instead of the regular
+    one when GLLM_TRACE_LIB=1)."""
     LIB.mkdir(exist_ok=True)
-    OBJ.mkdir(exist_ok=True)
-    out = LIB / "libgllm_kernels.so"
+    obj_dir = LIB / ("obj_trace" if trace else "obj")
+    obj_dir.mkdir(exist_ok=True)
+    out = LIB / ("libgllm_kernels_trace.so" if trace else "libgllm_kernels.so")
     srcs = sorted((CSRC / "kernels").glob("*.cu"))
     hdrs = sorted((CSRC / "kernels").glob("*.cuh")) + sorted((CSRC / "kernels").glob("*.h"))
     nvcc = _nvcc()
     objs, jobs = [], []
     for s in srcs:
-        o = OBJ / (s.stem + ".o")
+        o = obj_dir / (s.stem + ".o")
         objs.append(o)
         if force or _newer([s] + hdrs, o):
-            jobs.append([nvcc, *NVCC_FLAGS] + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o])
+            jobs.append([nvcc, *NVCC_FLAGS] + (["-DGLLM_TRACE"] if trace else []) + (["-Xptxas", "-v"] if verbose else [])
+                        + ["-c", s, "-o", o])
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(lambda c: _run(c, verbose), jobs))
@@ -124,3 +128,5 @@ if __name__ == "__main__":
     verbose = "--verbose" in sys.argv
     for o in build_all(force, verbose):
         print("built", o)
+    if "--trace" in sys.argv:
+        print("built", build_kernels(force, verbose, trace=True))

@@ -897,9 +897,15 @@ __device__ void ar_push_parked(const GemmParams& p, const float* part, int rows,
 
 // The owner's side: a warp takes (row, 256-column group) units of this rank's rows, four at a time; a lane covers 8
 // columns. tile_rows: rows of one producer tile (the m index of the flags). abort: the CTA's shared abort word.
-template <int BN>
-__device__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile_rows, volatile int* abort) {
-  constexpr int U = 4;
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// U: units a warp keeps in flight. Decode-sized launches have fewer units than the grid has warps, so they run with
+// U = 1 (every warp that has a unit works on it at once); large M uses 4 for memory-level parallelism.
+template <int BN, int U>
+__device__ void ar_push_reduce_u(const GemmParams& p, unsigned int epoch, int tile_rows, volatile int* abort) {
   constexpr int NB = 256 / BN;   // n tiles per 256-column group
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
@@ -924,10 +930,12 @@ __device__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile
       if (lane < nsrc * NB) {
         const unsigned int* f = flags + (static_cast<long long>(lane / NB) * p.num_m + m / tile_rows) * p.num_n +
                                 grp * NB + (lane % NB);
-        if (ld_relaxed_sys_u32(f) != epoch) {
+        // acquire loads: the tile's rows, stored before its flag was released, are visible to this lane afterwards and,
+        // through the warp-level meeting below, to the whole warp
+        if (ld_acquire_sys_u32(f) != epoch) {
           const unsigned long long t0 = globaltimer_ns();
           unsigned int spins = 0;
-          while (ld_relaxed_sys_u32(f) != epoch) {
+          while (ld_acquire_sys_u32(f) != epoch) {
             if (((++spins) & 0x3F) == 0) {
               if (*abort) { ok = false; break; }
               if (globaltimer_ns() - t0 > p.peer_wait_ns) {
@@ -942,7 +950,6 @@ __device__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile
       }
     }
     ok = __all_sync(0xffffffffu, ok);
-    fence_acq_rel_sys();   // the rows stored before a flag was released are visible now
     if (!ok) continue;
     // ---- add the sources in (split, rank) order ----
     float acc[U][8];
@@ -1030,6 +1037,17 @@ __device__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile
       }
     }
   }
+}
+
+template <int BN>
+__device__ __forceinline__ void ar_push_reduce(const GemmParams& p, unsigned int epoch, int tile_rows, volatile int* abort) {
+  const int rows_per = ar_rows_per(p);
+  const int own = max(0, min(p.M, (p.ar_rank + 1) * rows_per) - min(p.M, p.ar_rank * rows_per));
+  const long long units = static_cast<long long>(own) * (static_cast<long long>(p.num_n) * BN / 256);
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  if (units <= warps) ar_push_reduce_u<BN, 1>(p, epoch, tile_rows, abort);
+  else if (units <= 2 * warps) ar_push_reduce_u<BN, 2>(p, epoch, tile_rows, abort);
+  else ar_push_reduce_u<BN, 4>(p, epoch, tile_rows, abort);
 }
 
 // End of a push launch: the last CTA of this rank to get here tells every rank that this rank's rows are out, then
@@ -1898,8 +1916,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
     if (fused_ar && p.ar_push) {
       if constexpr (EPI == EPI_RESIDUAL) {
-        GLLM_STAMP(threadIdx.x == 0, 7);
+        GLLM_STAMP(threadIdx.x == 0, 7);     // tiles pushed, flags released
         ar_push_reduce<BN>(p, ar_epoch, MTE * kBM, abort_flag);
+        GLLM_STAMP(threadIdx.x == 0, 9);     // this CTA's share of the rows reduced and stored to every rank
         ar_push_finish(p, static_cast<unsigned long long>(ar_epoch), ar_launch_s);
       }
     } else if (fused_ar) {
@@ -2641,7 +2660,8 @@ GLLM_API int gllm_gemm_blockscaled(const GllmBsGemmArgs* args) {
   return -1;
 }
 
-// Debugging aid: CTA 0 of every following GEMM launch writes 9 SM-clock stamps to `buf` (device memory, 9 x int64):
+// Debugging aid (trace builds): CTA 0 of every following GEMM launch writes SM-clock stamps to `buf` (device memory,
+// 12 x int64; slot 9 = push all-reduce: this CTA's rows reduced):
 // entry, set-up done, first stage landed, MMAs of the first item issued, first accumulator ready, first epilogue
 // done, main loop left, split-K barrier passed, exit. Pass null to switch it off.
 GLLM_API int gllm_gemm_trace_enabled() {   // 1 when the library was built with -DGLLM_TRACE

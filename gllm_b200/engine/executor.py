@@ -299,11 +299,14 @@ class LLMEngine:
             import ctypes
             from ..ops import _native as nv
             lib = nv.lib()
+            if not lib.gllm_gemm_trace_enabled():
+                raise RuntimeError("phase stamps need the trace build of the kernel library: python -m gllm_b200.build "
+                                   "--trace, then GLLM_TRACE_LIB=1")
             lib.gllm_gemm_set_trace.argtypes = [ctypes.c_void_p]
             lib.gllm_gemm_set_trace.restype = None
             lib.gllm_gemm_set_trace_k.argtypes = [ctypes.c_int]
             lib.gllm_gemm_set_trace_k.restype = None
-            trace = torch.zeros(9, dtype=torch.int64, device=self.device)
+            trace = torch.zeros(12, dtype=torch.int64, device=self.device)
             lib.gllm_gemm_set_trace_n.argtypes = [ctypes.c_int]
             lib.gllm_gemm_set_trace_n.restype = None
             lib.gllm_gemm_set_trace_k(trace_k)
@@ -317,6 +320,8 @@ class LLMEngine:
             if trace is not None:
                 st = trace.tolist()
                 res.update({f"_clk{j}": float(st[j + 1] - st[j]) if st[j + 1] and st[j] else 0.0 for j in range(8)})
+                if st[9]:       # push all-reduce: flags released -> rows reduced -> all ranks done
+                    res.update({"_clk_push_reduce": float(st[9] - st[7]), "_clk_push_finish": float(st[8] - st[9])})
         finally:
             if trace is not None:
                 lib.gllm_gemm_set_trace(None)

@@ -65,6 +65,9 @@ class NativeLibraryError(RuntimeError):
 
 
 def lib_path() -> Path:
+    import os
+    if os.environ.get("GLLM_TRACE_LIB") == "1":      # the -DGLLM_TRACE build (python -m gllm_b200.build --trace)
+        return _LIB_DIR / "libgllm_kernels_trace.so"
     return _LIB_DIR / "libgllm_kernels.so"
 
 

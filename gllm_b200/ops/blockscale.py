@@ -50,8 +50,10 @@ def sf_swizzle(sf: torch.Tensor) -> torch.Tensor:
 
 
 def sf_unswizzle(buf: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    """The first ``rows`` rows of the scale matrix stored in ``buf`` (which may cover more row blocks than that)."""
     Rp, Cp = (rows + 127) // 128 * 128, (cols + 3) // 4 * 4
-    t = buf.view(Rp // 128, Cp // 4, 32, 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(Rp, Cp)
+    need = (Rp // 128) * (Cp // 4) * 512
+    t = buf[:need].view(Rp // 128, Cp // 4, 32, 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(Rp, Cp)
     return t[:rows, :cols]
 
 
@@ -167,16 +169,21 @@ def quantize_mxfp8(x: torch.Tensor) -> BlockScaled:
 
 
 def quantize_nvfp4(x: torch.Tensor, tensor_scale: Optional[float] = None) -> BlockScaled:
-    """[rows, K] -> NVFP4 (K padded to 256). tensor_scale defaults to amax / (6 * 448), the usual two-level recipe."""
+    """[rows, K] -> NVFP4 (K padded to 256). tensor_scale defaults to amax / (6 * 448), the usual two-level recipe.
+    The arithmetic (reciprocal multiplies in fp32, block scale rounded to ue4m3 before the codes are taken against it)
+    is the device kernel's, operation for operation, so both produce the same bytes."""
+    import numpy as np
     x = _pad_k(x.float(), 256)
     R, K = x.shape
     if tensor_scale is None:
         tensor_scale = max(float(x.abs().max()) / (6.0 * 448.0), 1e-12)
-    blk = x.view(R, K // 16, 16) / tensor_scale
-    s = e4m3_decode(e4m3_encode(blk.abs().amax(-1) / 6.0))              # ue4m3: the positive half of e4m3
-    s_safe = torch.where(s > 0, s, torch.ones_like(s))
-    codes = e2m1_encode(blk / s_safe[..., None]).view(R, K)
-    return BlockScaled(NVFP4, R, K, pack_nibbles(codes), sf_swizzle(e4m3_encode(s)), float(tensor_scale))
+    inv_ts = float(np.float32(1.0) / np.float32(tensor_scale))
+    sixth = float(np.float32(1.0) / np.float32(6.0))
+    blk = x.view(R, K // 16, 16) * inv_ts
+    s = e4m3_decode(e4m3_encode(blk.abs().amax(-1) * sixth))            # ue4m3: the positive half of e4m3
+    inv = torch.where(s > 0, 1.0 / s, torch.zeros_like(s))
+    codes = e2m1_encode(blk * inv[..., None]).view(R, K)
+    return BlockScaled(NVFP4, R, K, pack_nibbles(codes), sf_swizzle(e4m3_encode(s)), float(np.float32(tensor_scale)))
 
 
 def quantize(x: torch.Tensor, fmt) -> BlockScaled:

@@ -150,7 +150,7 @@ def run(op: str, iters: int):
                 ops.gemm_residual(a, ws[i[0]], r, out=o, bn=bn, splits=sp)
         os.environ["GLLM_BENCH_GRAPH"] = "1"
         t = _time(f, iters)
-        tr = torch.zeros(9, dtype=torch.int64, device=dev)
+        tr = torch.zeros(12, dtype=torch.int64, device=dev)
         lib.gllm_gemm_set_trace(tr.data_ptr())
         f()
         torch.cuda.synchronize()
