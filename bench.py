@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--output-tokens", type=int, default=256)
     ap.add_argument("--shared-prefix", type=int, default=512)
-    ap.add_argument("--tp-mode", default="auto", choices=["auto", "fused", "fused_p2p", "pull", "nccl"])
+    ap.add_argument("--tp-mode", default="auto", choices=["auto", "ll", "ll_p2p", "fused", "fused_p2p", "pull", "nccl"])
     ap.add_argument("--parallel", default="tp",
                     help="tp (tensor parallel over all GPUs, the headline), ep (data-parallel attention + expert-parallel "
                          "MoE, engines in lockstep), or tpXppY (X-way tensor parallel stages of a Y-stage pipeline)")
@@ -381,7 +381,7 @@ def main():
                        "parallelism": (f"ep{world} experts + data-parallel attention" if ep_mode else
                                        f"tp{tp_size}" + (f"pp{pp_size}" if pp_size > 1 else "")), "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
-                       "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
+                       "tp_form": getattr(tp, "form", "none"), "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
                        "layers": cfg.num_layers, "kv_dtype": args.kv_dtype,
                        "weight_quant": args.weight_quant, "expert_quant": args.expert_quant,
                        "valid": args.layers == 0 and (args.kv_dtype == "bf16" or args.model != "qwen3-8b")},

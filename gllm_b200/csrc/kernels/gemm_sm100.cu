@@ -141,7 +141,17 @@ struct GemmParams {
   long long ar_flag_off;      // BYTES from the base: tile flags (u32)
   long long ar_done_off;      // BYTES from the base: done words (u64 per rank)
   long long ar_flag_cap;      // number of u32 flags at ar_flag_off
-  int ar_drop_flags;          // test hook: leave the tile flags unset, so that the waits run out
+  // Low-latency form (ar_ll == 1, decode-sized M): no flags, no fences, no meeting. Every 32-bit word of the receive
+  // and result slots holds either the sentinel 0x80008000 (two bf16 negative zeros, which the writers never store:
+  // they write +0 instead) or data; a reader polls the data words themselves until none is the sentinel and puts the
+  // sentinel back after reading, so the slots clean themselves. Two parity sets of slots alternate between launches.
+  // Producers store bf16 partial rows into the owner's receive slots, the owner adds them and stores the finished rows
+  // into the result slots of EVERY rank, and every rank copies all rows from its own result slots into `out` (plain
+  // local memory) with their row statistics.
+  int ar_ll;
+  long long ar_ll_recv_off, ar_ll_recv_bytes;   // BYTES from the base / bytes of one parity set of receive slots
+  long long ar_ll_res_off, ar_ll_res_bytes;     // same for the result slots ([M][n_pad] bf16)
+  int ar_drop_flags;          // test hook: leave the tile flags unset (push) / the tiles unsent (ll): the waits run out
   unsigned long long wait_ns, peer_wait_ns;   // limits of the bounded waits
   long long* trace;   // debugging aid (GLLM_TRACE builds): CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
@@ -1088,6 +1098,160 @@ __device__ __forceinline__ bool ar_push_finish(const GemmParams& p, unsigned lon
 }
 
 // ---------------------------------------------------------------------------------------------
+// Low-latency (self-validating data) form of the fused all-reduce, see GemmParams::ar_ll.
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned int kLlSentinel = 0x80008000u;   // bf16x2 (-0, -0): never stored as data
+__device__ __forceinline__ unsigned int ll_word(unsigned int w) { return w == kLlSentinel ? 0u : w; }
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_u4(void* ptr, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_volatile_u2(void* ptr, unsigned int a, unsigned int b) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(ptr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ bool ll_valid(const uint4& v) {
+  return v.x != kLlSentinel && v.y != kLlSentinel && v.z != kLlSentinel && v.w != kLlSentinel;
+}
+__device__ __forceinline__ __nv_bfloat16* ar_ll_recv(const GemmParams& p, int r, int parity) {
+  return reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.ar_peer_buf[r]) + p.ar_ll_recv_off + parity * p.ar_ll_recv_bytes);
+}
+__device__ __forceinline__ __nv_bfloat16* ar_ll_res(const GemmParams& p, int r, int parity) {
+  return reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.ar_peer_buf[r]) + p.ar_ll_res_off + parity * p.ar_ll_res_bytes);
+}
+// Bounded poll of one 16-byte slot piece; puts the sentinel back once the data has been taken.
+__device__ __forceinline__ bool ll_take(__nv_bfloat16* slot, uint4& v, const GemmParams& p, volatile int* abort) {
+  v = ld_volatile_u4(slot);
+  if (!ll_valid(v)) {
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned int spins = 0;
+    do {
+      if (((++spins) & 0x3F) == 0) {
+        if (*abort) return false;
+        if (globaltimer_ns() - t0 > p.peer_wait_ns) {
+          *abort = 1;
+          if (p.err) atomicCAS(p.err, 0, ERR_TIMEOUT_PEER);
+          return false;
+        }
+      }
+      v = ld_volatile_u4(slot);
+    } while (!ll_valid(v));
+  }
+  st_volatile_u4(slot, make_uint4(kLlSentinel, kLlSentinel, kLlSentinel, kLlSentinel));
+  return true;
+}
+// The parked fp32 tile (BN = 128) of this CTA -> bf16 rows in the receive slots of the rows' owners.
+__device__ void ar_ll_push_parked(const GemmParams& p, const float* part, int rows, int m_row0, int n_blk, int src, int parity) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * 128;
+  const int rows_per = ar_rows_per(p);
+  for (int r = warp; r < rows; r += nwarps) {
+    const int m = m_row0 + r;
+    if (m >= p.M) continue;
+    const int owner = m / rows_per, lrow = m - owner * rows_per;
+    const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    __nv_bfloat16* dst = ar_ll_recv(p, owner, parity) + (static_cast<long long>(src) * rows_per + lrow) * n_pad + n_blk * 128 + lane * 4;
+    st_volatile_u2(dst, ll_word(pack_bf16x2(v.x, v.y)), ll_word(pack_bf16x2(v.z, v.w)));
+  }
+}
+// Owner: add the sources of this rank's rows, finish them, store them into every rank's result slots.
+template <int BN>
+__device__ void ar_ll_reduce(const GemmParams& p, int parity, volatile int* abort) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int W = p.ar_world, nsrc = W * p.splits;
+  const int rows_per = ar_rows_per(p);
+  const int own_lo = min(p.M, p.ar_rank * rows_per), own_hi = min(p.M, own_lo + rows_per);
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const int groups = static_cast<int>(n_pad / 256);
+  const int units = (own_hi - own_lo) * groups;
+  __nv_bfloat16* recv = ar_ll_recv(p, p.ar_rank, parity);
+  const long long src_stride = static_cast<long long>(rows_per) * n_pad;
+  for (int u = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); u < units; u += gridDim.x * warps_per_cta) {
+    const int lrow = u / groups, grp = u % groups, m = own_lo + lrow;
+    const int n0 = grp * 256 + lane * 8;
+    const long long off = static_cast<long long>(lrow) * n_pad + n0;
+    uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+    if (n0 < p.N) rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    bool ok = true;
+    for (int s0 = 0; s0 < nsrc && ok; ++s0) {   // (split, rank) order; the polls of later sources overlap the earlier adds
+      uint4 raw;
+      ok = ll_take(recv + s0 * src_stride + off, raw, p, abort);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+    if (!__all_sync(0xffffffffu, ok)) continue;
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (n0 < p.N) {
+      float v[8];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        v[2 * e] = acc[2 * e] + (p.bias ? p.bias[n0 + 2 * e] : 0.f) + f.x;
+        v[2 * e + 1] = acc[2 * e + 1] + (p.bias ? p.bias[n0 + 2 * e + 1] : 0.f) + f.y;
+      }
+      w.x = ll_word(pack_bf16x2(v[0], v[1]));
+      w.y = ll_word(pack_bf16x2(v[2], v[3]));
+      w.z = ll_word(pack_bf16x2(v[4], v[5]));
+      w.w = ll_word(pack_bf16x2(v[6], v[7]));
+    }
+    const long long ro = static_cast<long long>(m) * n_pad + n0;
+    for (int r = 0; r < W; ++r) st_volatile_u4(ar_ll_res(p, r, parity) + ro, w);
+  }
+}
+// Every rank: all rows from the own result slots into `out`, with the row statistics of the next norm.
+template <int BN>
+__device__ void ar_ll_gather(const GemmParams& p, int parity, volatile int* abort) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const long long n_pad = static_cast<long long>(p.num_n) * BN;
+  const int groups = static_cast<int>(n_pad / 256);
+  const int units = p.M * groups;
+  __nv_bfloat16* res = ar_ll_res(p, p.ar_rank, parity);
+  for (int u = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); u < units; u += gridDim.x * warps_per_cta) {
+    const int m = u / groups, grp = u % groups;
+    const int n0 = grp * 256 + lane * 8;
+    uint4 w;
+    const bool ok = ll_take(res + static_cast<long long>(m) * n_pad + n0, w, p, abort);
+    if (!__all_sync(0xffffffffu, ok)) continue;
+    float ss = 0.f;
+    if (n0 < p.N) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+      }
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(m) * p.ldo + n0) = w;
+    }
+    ss = warp_sum(ss);
+    if (p.row_ss_out && lane == 0) p.row_ss_out[static_cast<long long>(m) * groups + grp] = ss;
+  }
+}
+// The launch index advances once per launch: the last CTA to pass here does it (a local, relaxed counter).
+__device__ __forceinline__ void ar_ll_advance(const GemmParams& p, unsigned long long launch) {
+  if (threadIdx.x == 0) {
+    const unsigned long long prev = atomicAdd(p.ar_state + 5, 1ull);
+    if (prev + 1ull == gridDim.x) {
+      p.ar_state[5] = 0ull;
+      p.ar_state[1] = launch + 1ull;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // split-K inside a thread-block cluster: the S CTAs that share an output tile park their fp32 partial tiles in
 // their own shared memory, write the rows that OTHER members will finish to the global scratch with coalesced
 // stores, meet at one cluster barrier (instead of a grid-wide one) and each finishes 1/S of the rows: its own
@@ -1889,7 +2053,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool has_item = static_cast<int>(blockIdx.x) < num_items;   // the fused all-reduce launches every SM
       if (has_item) decode_item(blockIdx.x, ks, m_sup, n_blk, kb0, kb1);
       const float* part = reinterpret_cast<const float*>(tiles);
-      if (fused_ar && p.ar_push) {
+      if (fused_ar && p.ar_ll) {
+        if (has_item && !p.ar_drop_flags)
+          ar_ll_push_parked(p, part, MT * kBM, m_sup * MT * kBM, n_blk, ks * p.ar_world + p.ar_rank,
+                            static_cast<int>(ar_launch_s & 1ull));
+      } else if (fused_ar && p.ar_push) {
         if (has_item) ar_push_parked(p, part, MT * kBM, m_sup * MT * kBM, n_blk, ks * p.ar_world + p.ar_rank);
         __syncthreads();
         if (has_item) ar_push_signal(p, threadIdx.x, ks * p.ar_world + p.ar_rank, m_sup, n_blk, MT * kBM, ar_epoch);
@@ -1914,7 +2082,16 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
-    if (fused_ar && p.ar_push) {
+    if (fused_ar && p.ar_ll) {
+      if constexpr (EPI == EPI_RESIDUAL && BN == 128) {
+        GLLM_STAMP(threadIdx.x == 0, 7);     // tile sent
+        const int parity = static_cast<int>(ar_launch_s & 1ull);
+        ar_ll_reduce<BN>(p, parity, abort_flag);
+        GLLM_STAMP(threadIdx.x == 0, 9);     // this CTA's share of the owned rows reduced and sent to every rank
+        ar_ll_gather<BN>(p, parity, abort_flag);
+        ar_ll_advance(p, ar_launch_s);
+      }
+    } else if (fused_ar && p.ar_push) {
       if constexpr (EPI == EPI_RESIDUAL) {
         GLLM_STAMP(threadIdx.x == 0, 7);     // tiles pushed, flags released
         ar_push_reduce<BN>(p, ar_epoch, MTE * kBM, abort_flag);
@@ -2075,11 +2252,14 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     // four ranks on that traffic (every rank reads every rank's buffer) costs more than the shorter main loop saves.
     // Push form, any rank count: the extra partials travel while the main loops run and are added from local memory.
     if (BN == 128 && park_allowed && part_fits && ar_split_allowed && force_splits <= 0 && p.mblk_group == nullptr &&
-        (p.ar_world <= 2 || p.ar_push)) {
+        (p.ar_world <= 2 || p.ar_push || p.ar_ll)) {
       int sp = sms / (tiles > 0 ? tiles : 1);
       if (sp > 4) sp = 4;
       if (sp > p.num_kb / 8) sp = p.num_kb / 8;
-      if (p.ar_push) {
+      if (p.ar_ll) {
+        const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
+        while (sp > 1 && static_cast<long long>(p.ar_world) * sp * rows_per * p.num_n * BN * 2 > p.ar_ll_recv_bytes) --sp;
+      } else if (p.ar_push) {
         // a warp waits with one lane per (source, n tile) flag; the receive slots hold (world x splits) sources
         while (sp > 1 && p.ar_world * sp * (256 / BN) > 32) --sp;
         const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
@@ -2094,7 +2274,19 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   else if (ws.scratch)
     splits = choose_splits(tiles, p.num_kb, Cfg::kStageBytes, tile_floats, out_floats, sms, ws.scratch_floats,
                            BN == 128 && max_ctas <= 0 && rt.cluster_sk != 0);
-  if (p.ar_world > 0 && p.ar_push) {
+  if (p.ar_world > 0 && p.ar_ll) {
+    const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
+    const long long n_pad = static_cast<long long>(p.num_n) * BN;
+    const long long need = static_cast<long long>(p.ar_world) * splits * rows_per * n_pad * 2;
+    const long long need_res = static_cast<long long>(p.M) * n_pad * 2;
+    const bool parks = BN == 128 && park_allowed && part_fits && tiles * splits <= sms && p.mblk_group == nullptr;
+    if (!parks || need > p.ar_ll_recv_bytes || need_res > p.ar_ll_res_bytes || n_pad % 256 != 0) {
+      set_last_error("fused all-reduce (low latency): one 128-wide tile per CTA (%d tiles x %d splits on %d SMs), %lld "
+                     "receive bytes (have %lld), %lld result bytes (have %lld), padded width %% 256",
+                     tiles, splits, sms, need, p.ar_ll_recv_bytes, need_res, p.ar_ll_res_bytes);
+      return -1;
+    }
+  } else if (p.ar_world > 0 && p.ar_push) {
     const long long rows_per = (p.M + p.ar_world - 1) / p.ar_world;
     const long long need = static_cast<long long>(p.ar_world) * splits * rows_per * p.num_n * BN;
     const long long nflags = static_cast<long long>(p.ar_world) * splits * p.num_m * p.num_n;
@@ -2528,6 +2720,39 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_push(const void* A, long long lda
   p.ar_drop_flags = settings().ar_drop_flags;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, 0, 0);
+}
+
+// Low-latency form of the fused all-reduce (GemmParams::ar_ll): `out` is plain local memory and holds the residual
+// on entry; the receive and result slots ([2 parities] each) live in the symmetric region and hold the sentinel
+// 0x80008000 in every word between launches (the caller fills them once, and again after a launch that timed out).
+GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, const void* B, long long ldb, void* out,
+                                                  long long ldo, float* row_ss_out, int M, int N, int K,
+                                                  const float* bias, void* stream, int world, int rank,
+                                                  void* const* peer_base, long long region_bytes, long long recv_off,
+                                                  long long recv_bytes, long long res_off, long long res_bytes,
+                                                  unsigned long long* state) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !out) {
+    set_last_error("gemm_allreduce_ll: bad world/rank/pointers (world %d rank %d)", world, rank);
+    return -1;
+  }
+  if ((recv_off & 15) || (res_off & 15) || (recv_bytes & 15) || (res_bytes & 15) || recv_off < 0 || res_off < 0 ||
+      recv_off + 2 * recv_bytes > region_bytes || res_off + 2 * res_bytes > region_bytes) {
+    set_last_error("gemm_allreduce_ll: bad region layout");
+    return -1;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(out); p.ldr = ldo; p.row_ss_out = row_ss_out;
+  p.ar_world = world; p.ar_rank = rank;
+  for (int r = 0; r < world; ++r) p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(peer_base[r]);
+  p.ar_state = state;
+  p.ar_ll = 1;
+  p.ar_ll_recv_off = recv_off; p.ar_ll_recv_bytes = recv_bytes;
+  p.ar_ll_res_off = res_off; p.ar_ll_res_bytes = res_bytes;
+  p.ar_drop_flags = settings().ar_drop_flags;
+  p.err = gllm_error_word();
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, 128, (cudaStream_t)stream, 0, 0);
 }
 
 // out[M,N/2] = act(rowscale*gate) * rowscale*up ; B is the tile-interleaved gate/up weight [N,K]:

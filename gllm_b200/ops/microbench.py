@@ -212,6 +212,25 @@ def run(op: str, iters: int):
         out.update(shape=[M, N, K], mode=mode, group=group, us=t * 1e6, weight_bytes=byts, weight_gbs=byts / t / 1e9,
                    frac_of_hbm_peak=byts / t / 1e9 / hbm, bf16_equivalent_gbs=dense / t / 1e9,
                    tflops=2 * M * N * K / t / 1e12)
+    elif op in ("ar_ll_world1", "ar_push_world1", "ar_pull_world1"):
+        # the fused row-parallel GEMM + all-reduce kernel on ONE GPU (world size 1, ordinary device memory): the whole
+        # protocol runs (self-validating slots, receive slots / tile flags / done words, or buffers / arrival counters) without a peer, which
+        # is the form that can sit under a profiler. Decode-sized o_proj of a TP-8 shard by default.
+        from ..parallel.tensor_parallel import single_gpu_context
+        M, N, K = [int(v) for v in os.environ.get("GLLM_AR_SHAPE", "256,4096,512").split(",")]
+        tp = single_gpu_context(dev, hidden=N, max_tokens=max(M, 256), mode={"ar_ll_world1": "ll_p2p", "ar_push_world1": "fused_p2p"}.get(op, "pull_p2p"))
+        ws = [rnd(N, K, scale=0.05) for _ in range(8)]
+        a = rnd(M, K)
+        bufs = tp.workspace_buffers(M) if op == "ar_push_world1" else None
+        x = bufs["x"] if bufs else rnd(M, N)
+        ss = (bufs["ss_a"].reshape(-1)[:M * (N // 256)].view(M, N // 256) if bufs else torch.zeros(M, N // 256, device=dev))
+        i = [0]
+
+        def f():
+            i[0] = (i[0] + 1) % 8
+            tp.gemm_allreduce_residual(a, ws[i[0]], x, ss, None)
+        t = _time(f, iters)
+        out.update(shape=[M, N, K], form=tp.form, us=t * 1e6, weight_gbs=N * K * 2 / t / 1e9)
     elif op.startswith("bsgemm_"):
         # block-scaled tensor-core GEMM (both operands MXFP8 / NVFP4, hardware scale factors). Shape from GLLM_BS_SHAPE
         # ("M,N,K"); default: the decode-sized gate/up projection. GLLM_BS_QUANT=1 adds the activation quantisation.

@@ -15,14 +15,22 @@ store per peer). The activation buffer ``x`` and the statistics therefore live i
 (``workspace_buffers``); a caller's ordinary tensor is staged through it. The kernel ends with one exchange of
 per-rank "done" words.
 
+``ll`` (``gllm_gemm_bf16_residual_allreduce_ll``, decode-sized M): the same ownership of rows, but no flags, fences
+or meetings at all. Every 32-bit word of the receive and result slots is either the sentinel 0x80008000 (a pair of
+bf16 negative zeros, which the writers replace by +0) or data; readers poll the data words themselves and put the
+sentinel back after reading, and two parity sets of slots alternate between launches. The finished rows go into
+every rank's result slots and each rank copies them into its ordinary activation tensor, computing the norm
+statistics on the way. Larger M (prefill) takes the push kernel.
+
 ``pull`` (``gllm_gemm_bf16_residual_allreduce``): every rank stores its partial tiles in its own symmetric buffer,
 all ranks meet at an arrival counter, and every rank pulls the sum (``multimem.ld_reduce`` or peer loads), one-shot
 or two-shot. Kept for comparison.
 
 The NCCL path (unfused GEMM -> ncclAllReduce -> residual/norm-stat kernel) is the selectable baseline.
 
-Modes: ``auto`` (push when symmetric memory can be set up, else nccl), ``fused`` (push; multimem if available),
-``fused_p2p`` (push, peer stores only), ``pull`` / ``pull_p2p``, ``nccl``.
+Modes: ``auto`` (the fused form that measured fastest when symmetric memory can be set up, else nccl), ``ll`` /
+``ll_p2p`` (low-latency form at decode sizes, push above), ``fused`` (push; multimem if available), ``fused_p2p``
+(push, peer stores only), ``pull`` / ``pull_p2p``, ``nccl``.
 """
 from __future__ import annotations
 
@@ -35,6 +43,8 @@ from .. import ops
 from ..ops import _native as nv
 
 _FLAG_COUNT = 32768      # u32 tile flags of the push form
+_LL_SENTINEL = -2147450880   # 0x80008000 as int32: "no data yet" in the slots of the low-latency form
+_AUTO_FORM = "ll"
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -48,7 +58,8 @@ class TPContext:
         self.group = group
         self.requested_mode = mode
         self.mode = "nccl"
-        self.form = "none"            # "push" | "pull" once the fused kernel is set up
+        self.form = "none"            # "ll" | "push" | "pull" once the fused kernel is set up
+        self.ll_max_tokens = min(1024, max_tokens)
         self.uses_multimem = False
         self.max_tokens = max_tokens
         self.hidden = hidden
@@ -60,9 +71,10 @@ class TPContext:
         self._symm = None
         self._handle = None
         self.baseline = False           # True: run the NCCL path although the fused one is set up (bench baseline arm)
-        if mode in ("auto", "fused", "fused_p2p", "pull", "pull_p2p") and self.device.type == "cuda":
+        if mode in ("auto", "ll", "ll_p2p", "fused", "fused_p2p", "pull", "pull_p2p") and self.device.type == "cuda":
             try:
-                self.form = "pull" if mode.startswith("pull") else "push"
+                self.form = ("pull" if mode.startswith("pull") else "ll" if mode.startswith("ll") else
+                             _AUTO_FORM if mode == "auto" else "push")
                 self._setup_symmetric(force_p2p=mode.endswith("_p2p"))
                 self.mode = "fused"
             except Exception as exc:  # no NVLink peer access / symmetric memory unavailable
@@ -82,7 +94,7 @@ class TPContext:
             nonlocal off
             lay[name] = (off, nbytes)
             off = _align(off + nbytes)
-        if self.form == "push":
+        if self.form in ("push", "ll"):
             recv_rows = max(T + 8, min(4 * (T + 8), 4160))     # room for K splits inside a rank at decode sizes
             take("recv", recv_rows * self.n_pad * 2)
             take("x", T * self.hidden * 2)
@@ -90,6 +102,12 @@ class TPContext:
                 take(name, T * parts * 4)
             take("flags", _FLAG_COUNT * 4)
             take("done", 64)
+            if self.form == "ll":
+                # one parity set: up to four K splits of every rank's partial rows / all finished rows
+                self._ll_recv_bytes = _align(4 * (self.ll_max_tokens + 8) * self.n_pad * 2)
+                self._ll_res_bytes = _align(self.ll_max_tokens * self.n_pad * 2)
+                take("ll_recv", 2 * self._ll_recv_bytes)
+                take("ll_res", 2 * self._ll_res_bytes)
         else:
             take("pull", 3 * self.buf_elems * 2)
             take("counters", 64)
@@ -102,6 +120,8 @@ class TPContext:
         total = lay["_total"][0]
         if self.size == 1:
             buf = torch.zeros(total, dtype=torch.uint8, device=self.device)
+            self._symm, self._lay = buf, lay
+            self._fill_sentinel()
             peer_ptrs, mc_ptr = [buf.data_ptr()], 0
         else:
             import torch.distributed._symmetric_memory as symm_mem
@@ -109,6 +129,8 @@ class TPContext:
             buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
             self._handle = symm_mem.rendezvous(buf, group.group_name)
             buf.zero_()
+            self._symm, self._lay = buf, lay
+            self._fill_sentinel()
             torch.cuda.synchronize(self.device)
             dist.barrier(group=group)
             peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
@@ -120,6 +142,7 @@ class TPContext:
         self._mc_base = mc_ptr or None
         self._peer_base = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
         self._state = torch.zeros(8, dtype=torch.int64, device=self.device)
+        self._sms = int(nv.lib().gllm_sm_count())
         if self.form == "pull":
             off = lay["pull"][0]
             counter_off = off + 3 * self.buf_elems * 2
@@ -127,6 +150,12 @@ class TPContext:
             self._peer_cnt = (ctypes.c_void_p * 8)(*([p + counter_off for p in peer_ptrs] + [None] * (8 - n)))
             self._mc_acc = (mc_ptr + off) if mc_ptr else None
             self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
+
+    def _fill_sentinel(self):
+        for name in ("ll_recv", "ll_res"):
+            if name in self._lay:
+                off, nbytes = self._lay[name]
+                self._symm[off:off + nbytes].view(torch.int32).fill_(_LL_SENTINEL)
 
     def _view(self, name, dtype, shape):
         off, nbytes = self._lay[name]
@@ -139,7 +168,7 @@ class TPContext:
         """Activation buffer and norm-statistics buffers inside the symmetric region, for a model whose residual
         stream the push kernel updates on every rank. None when the push form is not in use or ``tokens`` exceeds
         what the region was sized for."""
-        if self.mode != "fused" or self.form != "push" or tokens > self.max_tokens:
+        if self.mode != "fused" or self.form not in ("push", "ll") or tokens > self.max_tokens:
             return None
         parts = (self.hidden + 127) // 128
         return dict(x=self._view("x", torch.bfloat16, (self.max_tokens, self.hidden))[:tokens],
@@ -157,7 +186,20 @@ class TPContext:
         N = w.shape[0]
         k_ok = self.requested_mode != "auto" or K <= self.fused_max_k
         fused = self.mode == "fused" and not self.baseline and k_ok and N <= self.n_pad
-        if fused and self.form == "push" and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:
+        if fused and self.form == "ll" and M <= self.ll_max_tokens and x.stride(0) * 2 % 16 == 0 and \
+                ((M + 127) // 128) * (self.n_pad // 128) <= self._sms:
+            parts = (N + 255) // 256
+            ss = ss_out[:M, :parts]
+            if not ss.is_contiguous():
+                raise ValueError("row statistics buffer must be [tokens, parts] contiguous")
+            lay = self._lay
+            rc = nv.lib().gllm_gemm_bf16_residual_allreduce_ll(
+                a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), ss.data_ptr(), M, N, K,
+                None, nv.stream_ptr(), self.size, self.rank, ctypes.cast(self._peer_base, ctypes.c_void_p), self._total,
+                lay["ll_recv"][0], self._ll_recv_bytes, lay["ll_res"][0], self._ll_res_bytes, self._state.data_ptr())
+            nv.check(rc, "gemm_bf16_residual_allreduce_ll")
+            return ss
+        if fused and self.form in ("push", "ll") and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:
             parts = (N + 255) // 256  # the fused kernel reports statistics per 256-column group
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
@@ -215,6 +257,7 @@ class TPContext:
                 if name in self._lay:
                     off, nbytes = self._lay[name]
                     self._symm[off:off + nbytes].zero_()
+            self._fill_sentinel()
             self._state.zero_()
         torch.cuda.synchronize(self.device)
         if self.size > 1:
@@ -260,6 +303,6 @@ class TPContext:
 
 def single_gpu_context(device, hidden: int, max_tokens: int = 1024, mode: str = "fused_p2p") -> TPContext:
     """A world-size-1 context on ordinary device memory: exercises the fused kernel's protocol (receive slots, tile
-    flags, done words, launch state; or, with ``mode="pull_p2p"``, alternating buffers and arrival counters) on one
-    GPU."""
+    flags, done words, launch state; with ``mode="ll_p2p"`` the self-validating slots; with ``mode="pull_p2p"``
+    alternating buffers and arrival counters) on one GPU."""
     return TPContext(0, 1, device, mode=mode, max_tokens=max_tokens, hidden=hidden)

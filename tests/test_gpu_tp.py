@@ -23,7 +23,7 @@ def _rows_close(got, ref, what=""):
     assert bad.numel() == 0, f"{what}: rows {bad[:8].tolist()} off by {row_err[bad[:8]].tolist()}"
 
 
-@pytest.mark.parametrize("mode", ["fused_p2p", "pull_p2p"])
+@pytest.mark.parametrize("mode", ["ll_p2p", "fused_p2p", "pull_p2p"])
 def test_fused_allreduce_world1_protocol(mode):
     from gllm_b200.parallel.tensor_parallel import single_gpu_context
     dev = torch.device("cuda")
@@ -63,14 +63,16 @@ def test_push_allreduce_in_place_on_symmetric_buffers():
         torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
 
 
-def test_push_allreduce_wait_runs_out_and_context_recovers():
-    """A wait on a flag that nothing sets ends after the configured limit with a status code, the host sees it, and
-    the next launch works (the permitted form of a failure test: nothing faults, traps or spins without a limit)."""
+@pytest.mark.parametrize("mode", ["ll_p2p", "fused_p2p"])
+def test_push_allreduce_wait_runs_out_and_context_recovers(mode):
+    """A wait on a flag (push form) or a data word (low-latency form) that nothing writes ends after the configured
+    limit with a status code, the host sees it, and the next launch works (the permitted form of a failure test:
+    nothing faults, traps or spins without a limit)."""
     from gllm_b200.ops import _native as nv
     from gllm_b200.parallel.tensor_parallel import single_gpu_context
     dev = torch.device("cuda")
     H, M, K = 1024, 64, 512
-    tp = single_gpu_context(dev, hidden=H, max_tokens=256)
+    tp = single_gpu_context(dev, hidden=H, max_tokens=256, mode=mode)
     torch.manual_seed(2)
     a = torch.randn(M, K, device=dev).to(torch.bfloat16)
     w = (torch.randn(H, K, device=dev) * 0.05).to(torch.bfloat16)
@@ -101,7 +103,7 @@ def test_push_allreduce_wait_runs_out_and_context_recovers():
 
 
 @pytest.mark.multigpu
-@pytest.mark.parametrize("mode", ["fused_p2p", "fused", "nccl", "pull", "pull_p2p", "pull_two_shot", "pull_p2p_two_shot"])
+@pytest.mark.parametrize("mode", ["ll", "fused_p2p", "fused", "nccl", "pull", "pull_p2p", "pull_two_shot", "pull_p2p_two_shot"])
 def test_fused_allreduce_two_gpus(mode):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
