@@ -371,18 +371,31 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   const int* bt = p.block_tables + static_cast<long long>(b) * p.max_blocks;
   const int n_my = (p1 - p0 - warp + kDecWarps - 1) / kDecWarps;  // pages p0+warp, p0+warp+4, ...
 
-  auto issue = [&](int i) {
-    const int pg_idx = p0 + warp + i * kDecWarps;
-    int page = bt[pg_idx];
-    if (page < 0 || page >= p.num_pages) {
-      if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
-      page = 0;
+  // The page ids of this warp's pages are fetched 32 at a time, one per lane, ahead of their use: a load of the block
+  // table in front of every TMA issue would put an L2 round trip into each page's critical path (at one KV head per
+  // rank, with few warps per SM to hide it, that round trip was most of the kernel's time).
+  auto fetch_ids = [&](int base) {
+    const int i = base + lane;
+    int page = 0;
+    if (i < n_my) {
+      page = bt[p0 + warp + i * kDecWarps];
+      if (page < 0 || page >= p.num_pages) {
+        if (p.err) atomicCAS(p.err, 0, ERR_BAD_PAGE);
+        page = 0;
+      }
     }
+    return page;
+  };
+  int ids = fetch_ids(0);        // pages [0, 32) of this warp
+  int ids_next = 0;              // pages [32 * c + 32, 32 * c + 64): fetched one chunk ahead
+  if (n_my > 32) ids_next = fetch_ids(32);
+  auto issue = [&](int i, int page) {   // lane 0 only
     const int stg = i % kDecStages;
     load_page_kv<KV8>(&tmap_kv, my_ring + stg * 2 * kTile, &my_bars[stg], page, p.n_kv_heads, kvh);
   };
-  if (lane == 0) {
-    for (int i = 0; i < n_my && i < kDecStages; ++i) issue(i);
+  for (int i = 0; i < n_my && i < kDecStages; ++i) {
+    const int page = __shfl_sync(0xffffffffu, ids, i);
+    if (lane == 0) issue(i, page);
   }
   __syncwarp();
   for (int i = 0; i < n_my; ++i) {
@@ -394,9 +407,17 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     const int tok_base = (p0 + warp + i * kDecWarps) * kPage;
     attend_page<KV8>(qf, kaddr, kaddr + kTile, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
     __syncwarp();
-    if (lane == 0 && i + kDecStages < n_my) {
-      fence_proxy_async_smem();
-      issue(i + kDecStages);
+    const int nxt = i + kDecStages;
+    if ((nxt & 31) == 0 && nxt < n_my) {   // the next issue opens a new chunk of 32 page ids
+      ids = ids_next;
+      if (nxt + 32 < n_my) ids_next = fetch_ids(nxt + 32);
+    }
+    if (nxt < n_my) {
+      const int page = __shfl_sync(0xffffffffu, ids, nxt & 31);
+      if (lane == 0) {
+        fence_proxy_async_smem();
+        issue(nxt, page);
+      }
     }
   }
   // every issued copy has been waited for above (or the wait was abandoned after the limit)

@@ -2831,6 +2831,7 @@ struct GllmBsGemmArgs {
   const int* slot_mapping; const int* positions; const float* cos_table; const float* sin_table; int max_pos;
   const float* q_norm_w; const float* k_norm_w; float qk_eps; float kv_inv_scale;
   void* stream;
+  const int* scatter_meta; void* const* scatter_peer; int scatter_world;   // EPI_STORE: rows scattered into peers
 };
 
 template <int OPM>
@@ -2847,6 +2848,15 @@ static int bs_gemm_call(const GllmBsGemmArgs& a) {
   cudaStream_t st = static_cast<cudaStream_t>(a.stream);
   switch (a.epi) {
     case EPI_STORE:
+      if (a.scatter_meta) {
+        if (a.scatter_world < 1 || a.scatter_world > 8 || !a.scatter_peer) {
+          set_last_error("gemm_blockscaled: bad scatter world %d", a.scatter_world);
+          return -1;
+        }
+        p.scatter_meta = a.scatter_meta;
+        for (int r = 0; r < a.scatter_world; ++r) p.scatter_peer[r] = static_cast<__nv_bfloat16*>(a.scatter_peer[r]);
+        p.out = a.scatter_peer[0];
+      }
       return dispatch_gemm_bs<EPI_STORE, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
     case EPI_RESIDUAL:
       p.residual = static_cast<const __nv_bfloat16*>(a.residual); p.ldr = a.ldr; p.row_ss_out = a.row_ss_out;

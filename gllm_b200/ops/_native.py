@@ -43,6 +43,7 @@ _SIGNATURES = {
     "gllm_decode_scratch_floats": (L, [I, I, I]),
     "gllm_paged_decode": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, P]),
     "gllm_paged_prefill": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, P]),
+    "gllm_paged_prefill_tc": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, P, P]),
     "gllm_paged_decode_fp8": (I, [P, P, P, I, P, I, P, I, I, I, F, I, I, P, P, I, P, F, P]),
     "gllm_paged_prefill_fp8": (I, [P, P, P, I, P, I, P, P, P, I, I, I, I, F, I, I, P, F, P]),
     "gllm_embed_gather": (I, [P, P, I, I, F, P, P, I, P]),
@@ -106,7 +107,7 @@ def lib():
 # Environment variables that map onto library settings (read once, when the library is loaded). The native code itself
 # reads no environment variable.
 _ENV_OPTIONS = (
-    ("GLLM_PDL", "pdl", int), ("GLLM_AR_SPLIT", "ar_split", int), ("GLLM_QKV_TWO_ROWS", "qkv_two_rows", int),
+    ("GLLM_PDL", "pdl", int), ("GLLM_AR_SPLIT", "ar_split", int), ("GLLM_QKV_TWO_ROWS", "qkv_two_rows", int), ("GLLM_PREFILL_TC", "prefill_tc", int),
     ("GLLM_AR_TWO_SHOT", "ar_two_shot", int), ("GLLM_PAIR_MAX_M", "pair_max_m", int), ("GLLM_PAIR_BIG_M", "pair_big_m", int),
     ("GLLM_WAIT_NS", "wait_ns", int), ("GLLM_PEER_WAIT_NS", "peer_wait_ns", int),
 )

@@ -143,7 +143,14 @@ def paged_prefill(q, kv_cache, block_tables, q_start, q_len, ctx_lens, *, max_q_
                                                  1 if causal else 0, window, float(kv_scale), nv.stream_ptr())
         nv.check(rc, "paged_attention_fp8kv")
         return out
-    if D == 128:
+    if D == 128 and nv.get_option("prefill_tc") != 0 and q.is_contiguous() and out.is_contiguous():
+        # tcgen05 flash attention (S and O accumulators in tensor memory)
+        rc = nv.lib().gllm_paged_prefill_tc(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
+                                            block_tables.data_ptr(), block_tables.shape[1], q_start.data_ptr(),
+                                            q_len.data_ptr(), ctx_lens.data_ptr(), S, max_q_len, q.shape[0], n_q, n_kv,
+                                            scale, 1 if causal else 0, window, nv.ptr(sinks), nv.stream_ptr())
+        nv.check(rc, "paged_prefill_tc")
+    elif D == 128:
         rc = nv.lib().gllm_paged_prefill(q.data_ptr(), out.data_ptr(), kv_cache.data_ptr(), kv_cache.shape[0],
                                          block_tables.data_ptr(), block_tables.shape[1], q_start.data_ptr(),
                                          q_len.data_ptr(), ctx_lens.data_ptr(), S, max_q_len, n_q, n_kv, scale,

@@ -314,7 +314,8 @@ class _Args(ctypes.Structure):
                 ("mblk_group", nv.P), ("num_groups", nv.I),
                 ("n_q_heads", nv.I), ("n_kv_heads", nv.I), ("q_out", nv.P), ("kv_cache", nv.P), ("num_pages", nv.I),
                 ("slot_mapping", nv.P), ("positions", nv.P), ("cos_table", nv.P), ("sin_table", nv.P), ("max_pos", nv.I),
-                ("q_norm_w", nv.P), ("k_norm_w", nv.P), ("qk_eps", nv.F), ("kv_inv_scale", nv.F), ("stream", nv.P)]
+                ("q_norm_w", nv.P), ("k_norm_w", nv.P), ("qk_eps", nv.F), ("kv_inv_scale", nv.F), ("stream", nv.P),
+                ("scatter_meta", nv.P), ("scatter_peer", nv.P), ("scatter_world", nv.I)]
 
 
 nv.register("gllm_gemm_blockscaled", ctypes.c_int, [ctypes.POINTER(_Args)])
@@ -379,6 +380,21 @@ def gemm(a: BlockScaled, w: BlockScaled, *, out=None, out_dtype=torch.bfloat16, 
         g.mblk_group, g.num_groups = mblk_group.data_ptr(), num_groups
     nv.check(nv.lib().gllm_gemm_blockscaled(ctypes.byref(g)), "gemm_blockscaled")
     return out
+
+
+def gemm_grouped_scatter(a: BlockScaled, w: BlockScaled, mblk_group, num_groups: int, *, ldo: int, scatter_meta,
+                         scatter_peers, world: int, bn: int = 128):
+    """Grouped GEMM (row block i of A times expert ``mblk_group[i]``) whose output rows go straight into up to eight
+    ranks' buffers: ``scatter_meta`` holds (rank, row) per input row, ``scatter_peers`` is a ctypes array of the
+    ranks' base pointers, ``ldo`` the row pitch of those buffers in elements. CUDA only (the expert-parallel path)."""
+    M = a.rows
+    N = w.rows // num_groups
+    nv.ensure_splitk_workspace(a.device)
+    g = _base_args(a, w, M, N, EPI_STORE, bn, 1, 0)
+    g.ldo = ldo
+    g.mblk_group, g.num_groups = mblk_group.data_ptr(), num_groups
+    g.scatter_meta, g.scatter_peer, g.scatter_world = scatter_meta.data_ptr(), ctypes.cast(scatter_peers, ctypes.c_void_p), world
+    nv.check(nv.lib().gllm_gemm_blockscaled(ctypes.byref(g)), "gemm_blockscaled (scatter)")
 
 
 def gemm_residual(a: BlockScaled, w: BlockScaled, residual, *, out=None, row_ss_out=None, bias=None, bn: int = 128,

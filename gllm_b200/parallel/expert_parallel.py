@@ -167,15 +167,44 @@ class EPContext:
         self.dispatch(src, ss_in if fused_norm else None, ids, T)
         rows = self.rows_bound()
         act = self.act_buffer(layer.inter)
-        L.gemm_glu(self.x_recv[:rows], layer.w_gate_up, act=model.act_id, out=act[:rows],
-                   row_ss=self.ss_recv[:rows] if fused_norm else None, norm_dim=H if fused_norm else 0,
-                   eps=c.rms_norm_eps if fused_norm else 0.0, bn=layer.glu_bn, mblk_group=self.blk_group,
-                   num_groups=self.e_local)
-        self.grouped_scatter(act, layer.w_down, rows)
+        if getattr(layer, "bs_fmt", None) is None:
+            L.gemm_glu(self.x_recv[:rows], layer.w_gate_up, act=model.act_id, out=act[:rows],
+                       row_ss=self.ss_recv[:rows] if fused_norm else None, norm_dim=H if fused_norm else 0,
+                       eps=c.rms_norm_eps if fused_norm else 0.0, bn=layer.glu_bn, mblk_group=self.blk_group,
+                       num_groups=self.e_local)
+            self.grouped_scatter(act, layer.w_down, rows)
+        else:
+            self._bs_experts(layer, model, act, rows, fused_norm, H)
         if layer.shared_gate_up is not None:
             shared = self._shared(layer, model, src, ss_in if fused_norm else None, H)
         self.combine(x, w, T, shared, ss)
         return ss
+
+    def _bs_experts(self, layer, model, act, rows, fused_norm, H):
+        """Block-scaled experts: the received rows (bf16, as the peers stored them) are quantised in place of the bf16
+        A operand, only as many as arrived (a count on the device); the SwiGLU output likewise; the second GEMM's
+        epilogue scatters its rows back to their source ranks as the bf16 path does."""
+        from ..ops import blockscale as B
+        c = layer.cfg
+        fmt = layer.bs_fmt
+        key = (fmt, layer.inter)
+        q = self._bsq.get(key) if hasattr(self, "_bsq") else None
+        if q is None:
+            if not hasattr(self, "_bsq"):
+                self._bsq = {}
+            q = self._bsq[key] = (B.alloc_act(self.max_rows, H, fmt, self.device),
+                                  B.alloc_act(self.max_rows, layer.inter, fmt, self.device))
+        xq, aq = q
+        ts = layer.act_tensor_scale
+        B.quantize_act_rows(self.x_recv, fmt, xq, self.total_rows, tensor_scale=ts)
+        xq.rows = rows
+        rs = dict(row_ss=self.ss_recv[:rows], norm_dim=H, eps=c.rms_norm_eps) if fused_norm else {}
+        B.gemm_glu(xq, layer.w_gate_up, act=model.act_id, out=act[:rows], bn=128, mblk_group=self.blk_group,
+                   num_groups=self.e_local, **rs)
+        B.quantize_act_rows(act, fmt, aq, self.total_rows, tensor_scale=ts)
+        aq.rows = rows
+        B.gemm_grouped_scatter(aq, layer.w_down, self.blk_group, self.e_local, ldo=self.hidden, scatter_meta=self.meta,
+                               scatter_peers=self._y_peers, world=self.size)
 
     @staticmethod
     def _shared(layer, model, src, ss_in, H):

@@ -83,6 +83,45 @@ def test_paged_prefill(n_q, n_kv):
     _close(out_w, ref_w)
 
 
+def _rows_close(got, ref, what=""):
+    got, ref = got.float(), ref.float()
+    row_err = (got - ref).abs().amax(-1)
+    row_ref = ref.abs().amax(-1).clamp_min(1e-3)
+    bad = (row_err > 0.03 * row_ref + 0.01).nonzero().flatten()
+    assert bad.numel() == 0, f"{what}: rows {bad[:8].tolist()} off by {row_err[bad[:8]].tolist()}"
+
+
+@pytest.mark.parametrize("n_q,n_kv", [(8, 2), (6, 2), (2, 2), (32, 8)])
+def test_paged_prefill_tensor_memory_kernel(n_q, n_kv):
+    """The tcgen05 prefill kernel (two query tiles per CTA: head pairs when the group size is even, row-block pairs
+    otherwise) against the fp32 reference, row by row, and against the mma.sync kernel: long causal ranges, chunks
+    over cached prefixes, ragged tails, sliding window, sinks."""
+    from gllm_b200.ops import _native as nv
+    D = 128
+    q_len = [384, 1, 129, 700, 64, 256]
+    ctx = [384, 300, 129, 1500, 64, 2000]
+    kv, bt = _setup(ctx, n_kv, D, seed=5)
+    T = sum(q_len)
+    q = torch.randn(T, n_q * D, device=DEV).to(torch.bfloat16)
+    qs = torch.tensor([sum(q_len[:i]) for i in range(len(q_len))], dtype=torch.int32, device=DEV)
+    ql = torch.tensor(q_len, dtype=torch.int32, device=DEV)
+    cl = torch.tensor(ctx, dtype=torch.int32, device=DEV)
+    sinks = torch.randn(n_q, device=DEV)
+    assert nv.get_option("prefill_tc") == 1
+    for kw in (dict(), dict(causal=False), dict(window=100), dict(sinks=sinks), dict(window=700, sinks=sinks)):
+        out = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=max(q_len), n_q=n_q, n_kv=n_kv, **kw)
+        ref = ops.attention_ref(q, kv, bt, qs, ql, cl, n_q, n_kv, D ** -0.5, kw.get("causal", True), kw.get("window", 0),
+                                kw.get("sinks"))
+        _rows_close(out.view(T * n_q, D), ref.view(T * n_q, D), f"tensor-memory kernel {kw.keys()}")
+        nv.set_option("prefill_tc", 0)
+        try:
+            old = ops.paged_prefill(q, kv, bt, qs, ql, cl, max_q_len=max(q_len), n_q=n_q, n_kv=n_kv, **kw)
+        finally:
+            nv.set_option("prefill_tc", 1)
+        _rows_close(out.view(T * n_q, D), old.view(T * n_q, D), f"vs mma.sync kernel {kw.keys()}")
+    assert nv.device_error() == 0
+
+
 def test_generic_attention_head_dim_64():
     D, n_q, n_kv = 64, 9, 3
     q_len, ctx = [7, 33], [7, 50]
