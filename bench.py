@@ -217,20 +217,46 @@ def main():
     if ep_mode:
         prompts = prompts[rank::world]
 
-    # ---- phase 0 (N > 1): the tensor-parallel engine must produce the single-GPU model's tokens ----
+    # ---- phase 0 (N > 1): the tensor-parallel engine against the single-GPU model ----
+    # The TP engine generates 8 greedy tokens for 8 prompts. The single-GPU model of the same weights then scores the
+    # same sequences teacher-forced (one forward over prompt + generated tokens, logits at the 64 generated positions),
+    # so a token that flipped between two near-equal logits does not compound. With random-init weights the logits
+    # are close to flat (the gap between the two largest of 150 k is about 0.2 standard deviations), so the check is on
+    # the GAP: every token the TP engine chose must lie within 0.25 standard deviations of the single-GPU maximum
+    # (a wrong kernel picks tokens about 4-5 standard deviations below it) and most must be the exact argmax.
     tp1_check = None
     if world > 1 and par == "tp" and not args.no_tp1_check:
+        from gllm_b200.engine.batch import ForwardBatch
         check_prompts = make_prompts(8, 24, 96, 16, cfg.vocab_size, seed=4321)
         got = [r.token_ids for r in engine.generate_batch(check_prompts, max_tokens=8, temperature=0.0, eos_ids=[])]
         if rank == 0:
             ref_model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, max_positions=max_len, **kv_kw)
-            ref_engine = LLMEngine(ref_model, EngineConfig(max_num_seqs=8, max_model_len=256, max_batch_tokens=1024,
-                                                           prefill_chunk=1024, num_pages=8 * 16 + 8, use_cuda_graphs=False))
-            want = [r.token_ids for r in ref_engine.generate_batch(check_prompts, max_tokens=8, temperature=0.0, eos_ids=[])]
-            same = sum(int(a == b) for g, w_ in zip(got, want) for a, b in zip(g, w_))
-            first = sum(int(g[0] == w_[0]) for g, w_ in zip(got, want))
-            tp1_check = {"tokens_equal": same, "tokens_total": 64, "first_tokens_equal": first, "prompts": 8}
-            del ref_engine, ref_model
+            exact = first = 0
+            gaps = []
+            for pr, g in zip(check_prompts, got):
+                ids = list(pr) + list(g[:-1])
+                n = len(ids)
+                rows = [len(pr) - 1 + i for i in range(len(g))]
+                kv = ref_model.alloc_kv_cache((n + 15) // 16 + 1)
+                i32 = dict(dtype=torch.int32, device=dev)
+                fb = ForwardBatch(token_ids=torch.tensor(ids, **i32), positions=torch.arange(n, **i32),
+                                  slot_mapping=torch.arange(n, **i32),
+                                  block_tables=torch.arange((n + 15) // 16, **i32)[None],
+                                  ctx_lens=torch.tensor([n], **i32), q_start=torch.tensor([0], **i32),
+                                  q_len=torch.tensor([n], **i32), max_q_len=n,
+                                  logits_rows=torch.tensor(rows, dtype=torch.int64, device=dev))
+                lg = ref_model.forward(fb, kv).float()[:, :cfg.vocab_size]
+                for i, tok in enumerate(g):
+                    row = lg[i]
+                    gaps.append(float((row.max() - row[int(tok)]) / row.std()))
+                    hit = int(int(row.argmax()) == int(tok))
+                    exact += hit
+                    first += hit if i == 0 else 0
+                del kv
+            tp1_check = {"method": "teacher-forced single-GPU logits at the generated positions",
+                         "tokens_equal": exact, "tokens_total": len(gaps), "first_tokens_equal": first, "prompts": 8,
+                         "max_gap_sigma": round(max(gaps), 4), "mean_gap_sigma": round(sum(gaps) / len(gaps), 5)}
+            del ref_model
             torch.cuda.empty_cache()
         dist.barrier()
         for k in engine.stats:          # the check's prefill / decode work is not part of the measured workload
@@ -405,10 +431,9 @@ def main():
                                "value": round(n_active * K / (nccl_ms / 1e3), 1), "unit": "tokens/s",
                                "ms_per_step": round(nccl_ms / K, 4)}
         if tp1_check is not None:
-            # random-init logits are nearly flat, so bf16 rounding (a different summation order across ranks) flips an
-            # argmax somewhere along a 8-token continuation and the rest of that continuation differs; the first token
-            # of every prompt (prefill logits) and most of the tokens must agree
-            out["config"]["tokens_match_tp1"] = (tp1_check["first_tokens_equal"] == tp1_check["prompts"] and
+            # see phase 0: every chosen token within 0.25 standard deviations of the single-GPU maximum, and most of
+            # them the exact single-GPU argmax
+            out["config"]["tokens_match_tp1"] = (tp1_check["max_gap_sigma"] < 0.25 and
                                                  tp1_check["tokens_equal"] >= 0.6 * tp1_check["tokens_total"])
             out["config"]["tp1_check"] = tp1_check
         if breakdown is not None:

@@ -115,6 +115,8 @@ def _python_embed_flags():
 
 def build_all(force=False, verbose=False):
     outs = [build_kernels(force, verbose)]
+    if (LIB / "libgllm_kernels_trace.so").exists():     # keep an existing trace build in step with the sources
+        outs.append(build_kernels(force, verbose, trace=True))
     for name, sub, pyb, extra in (("_sched", "sched", True, ()), ("libgllm_cpuref", "ref", False, ("-fopenmp",)),
                                   ("libgllm_loader", "loader", False, ("-fopenmp",)),
                                   ("libgllm_ffi", "ffi", False, _python_embed_flags())):

@@ -42,6 +42,7 @@ struct RuntimeSettings {
   int cluster_sk = 1;      // split-K inside a thread-block cluster when every cluster fits at once
   int ar_split = 1;        // the fused all-reduce may split K inside a rank
   int qkv_two_rows = 1;    // 256-row tiles for the QKV GEMM
+  int dec_tiles = 8;       // bit per epilogue (store 1, residual 2, GLU 4, QKV 8): decode-sized GEMMs unsplit on 128-row tiles
   int prefill_tc = 1;      // prefill attention on the tcgen05 kernel (0: the mma.sync kernel)
   int ar_drop_flags = 0;   // test hook: the push all-reduce leaves its tile flags unset, so its waits run out
   int pair_max_m = 256, pair_epi_mask = 0, pair_big_m = 1024;   // where CTA pairs are used (see gemm_sm100.cu)

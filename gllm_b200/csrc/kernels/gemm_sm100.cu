@@ -33,6 +33,8 @@
 
 #include "common.cuh"
 
+extern "C" int gllm_sm_count();
+
 namespace gllm {
 
 enum : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_QKV = 3 };
@@ -2535,6 +2537,21 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
     // The QKV epilogue needs one head (128 columns) per tile, so its tiles cannot widen; 256 rows per CTA is what
     // lets a weight tile serve twice the MMAs at prefill sizes too.
     if (settings().qkv_two_rows && p.M > 128) two_rows = true;
+  }
+  // Decode-sized M without a K split (setting dec_tiles, one bit per epilogue): 128-row tiles, every tile streams its
+  // whole K range. A CTA then pulls more bytes through its L2 port (all of A's rows for its tile), but nothing is
+  // dumped, met at a barrier or reduced.
+  // Measured in the serving step (M = 256, one GPU): QKV 49 -> 37 us per layer unsplit (its reduce phase was the slow
+  // part); the residual GEMMs and gate/up get slower (down 43 -> 72 us), so only the QKV bit is on by default, and only
+  // while the unsplit tiles fill at least half of the SMs (a tensor-parallel shard with few tiles keeps the split).
+  if (p.M > 128 && p.M <= 256 && p.mblk_group == nullptr && p.ar_world == 0 && max_ctas <= 0 && force_splits <= 0 &&
+      ((settings().dec_tiles >> EPI) & 1) && 2 * 2 * ((p.N + 127) / 128) >= gllm_sm_count()) {
+    two_rows = false;
+    force_splits = 1;
+  }
+  if constexpr (!FP8 && (EPI == EPI_STORE || EPI == EPI_RESIDUAL)) {
+    // 64-wide tiles: twice the tiles of a narrow output (N = 4096 gives 128 tiles of 128 rows), never split
+    if (bn == 64) return launch_gemm<64, 1, EPI, FP8>(A, lda, B, ldb, b_rows, p, stream, max_ctas, 1);
   }
   if constexpr (EPI == EPI_GLU) {
     // 192-wide tiles: 128 tiles for a 24576-row gate/up weight fill one wave of 148 SMs without splitting

@@ -179,7 +179,7 @@ static long long* option_slot(const char* name, long long* tmp, int** as_int) {
   if (!strcmp(name, "peer_wait_ns")) return reinterpret_cast<long long*>(&s.peer_wait_ns);
   struct { const char* n; int* v; } ints[] = {
       {"pdl", &s.pdl}, {"park", &s.park}, {"cluster_sk", &s.cluster_sk}, {"ar_split", &s.ar_split},
-      {"qkv_two_rows", &s.qkv_two_rows}, {"prefill_tc", &s.prefill_tc}, {"ar_drop_flags", &s.ar_drop_flags}, {"pair_max_m", &s.pair_max_m},
+      {"qkv_two_rows", &s.qkv_two_rows}, {"prefill_tc", &s.prefill_tc}, {"dec_tiles", &s.dec_tiles}, {"ar_drop_flags", &s.ar_drop_flags}, {"pair_max_m", &s.pair_max_m},
       {"pair_epi_mask", &s.pair_epi_mask}, {"pair_big_m", &s.pair_big_m}, {"ar_two_shot", &s.ar_two_shot}};
   for (auto& e : ints)
     if (!strcmp(name, e.n)) {

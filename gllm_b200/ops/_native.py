@@ -107,7 +107,7 @@ def lib():
 # Environment variables that map onto library settings (read once, when the library is loaded). The native code itself
 # reads no environment variable.
 _ENV_OPTIONS = (
-    ("GLLM_PDL", "pdl", int), ("GLLM_AR_SPLIT", "ar_split", int), ("GLLM_QKV_TWO_ROWS", "qkv_two_rows", int), ("GLLM_PREFILL_TC", "prefill_tc", int),
+    ("GLLM_PDL", "pdl", int), ("GLLM_AR_SPLIT", "ar_split", int), ("GLLM_QKV_TWO_ROWS", "qkv_two_rows", int), ("GLLM_PREFILL_TC", "prefill_tc", int), ("GLLM_DEC_TILES", "dec_tiles", int),
     ("GLLM_AR_TWO_SHOT", "ar_two_shot", int), ("GLLM_PAIR_MAX_M", "pair_max_m", int), ("GLLM_PAIR_BIG_M", "pair_big_m", int),
     ("GLLM_WAIT_NS", "wait_ns", int), ("GLLM_PEER_WAIT_NS", "peer_wait_ns", int),
 )
