@@ -154,6 +154,7 @@ struct GemmParams {
   long long ar_ll_recv_off, ar_ll_recv_bytes;   // BYTES from the base / bytes of one parity set of receive slots
   long long ar_ll_res_off, ar_ll_res_bytes;     // same for the result slots ([M][n_pad] bf16)
   int ar_drop_flags;          // test hook: leave the tile flags unset (push) / the tiles unsent (ll): the waits run out
+  float softcap;              // EPI_STORE, unsplit launches only: out = softcap * tanh(out / softcap) (0 = off)
   unsigned long long wait_ns, peer_wait_ns;   // limits of the bounded waits
   long long* trace;   // debugging aid (GLLM_TRACE builds): CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
@@ -1210,7 +1211,12 @@ __device__ void ar_ll_reduce(const GemmParams& p, int parity, volatile int* abor
       w.w = ll_word(pack_bf16x2(v[6], v[7]));
     }
     const long long ro = static_cast<long long>(m) * n_pad + n0;
-    for (int r = 0; r < W; ++r) st_volatile_u4(ar_ll_res(p, r, parity) + ro, w);
+    if (p.ar_mc_buf) {   // one store, replicated to every rank's result slots by the switch
+      multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.ar_mc_buf) + p.ar_ll_res_off +
+                                                        parity * p.ar_ll_res_bytes) + ro, w);
+    } else {
+      for (int r = 0; r < W; ++r) st_volatile_u4(ar_ll_res(p, r, parity) + ro, w);
+    }
   }
 }
 // Every rank: all rows from the own result slots into `out`, with the row statistics of the next norm.
@@ -1853,6 +1859,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < 32; ++j) {
                   v[j] = bf16_round(v[j]);
                   ss += v[j] * v[j];
+                }
+              }
+              if constexpr (EPI == EPI_STORE) {
+                if (p.softcap != 0.f) {   // final-logit soft cap: cap * tanh(x / cap)
+                  const float inv_cap = 1.f / p.softcap;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] = p.softcap * tanhf(v[j] * inv_cap);
                 }
               }
               if (p.scatter_meta) {
@@ -2628,6 +2641,20 @@ GLLM_API int gllm_gemm_bf16(const void* A, long long lda, const void* B, long lo
   return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, max_ctas, force_splits);
 }
 
+// gllm_gemm_bf16 with the final-logit soft cap in the epilogue (never split along K: the cap is not linear).
+GLLM_API int gllm_gemm_bf16_softcap(const void* A, long long lda, const void* B, long long ldb, void* out, long long ldo,
+                                    int M, int N, int K, int out_f32, const float* bias, const float* row_ss_in,
+                                    int ss_in_parts, float norm_inv_dim, float norm_eps, int bn, void* stream,
+                                    float softcap) {
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_f32 = out_f32; p.bias = bias;
+  p.row_ss_in = row_ss_in; p.ss_in_parts = ss_in_parts; p.norm_inv_dim = norm_inv_dim; p.norm_eps = norm_eps;
+  p.softcap = softcap;
+  p.err = gllm_error_word();
+  return dispatch_gemm<EPI_STORE, false>(A, lda, B, ldb, N, p, bn, (cudaStream_t)stream, 0, 1);
+}
+
 // out[M,N] = A · Bᵀ (+bias) + residual ; row_ss_out[M, ceil(N/bn)] receives per-tile sums of squares.
 GLLM_API int gllm_gemm_bf16_residual(const void* A, long long lda, const void* B, long long ldb, void* out,
                                      long long ldo, const void* residual, long long ldr, float* row_ss_out, int M,
@@ -2745,7 +2772,7 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_push(const void* A, long long lda
 GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, const void* B, long long ldb, void* out,
                                                   long long ldo, float* row_ss_out, int M, int N, int K,
                                                   const float* bias, void* stream, int world, int rank,
-                                                  void* const* peer_base, long long region_bytes, long long recv_off,
+                                                  void* mc_base, void* const* peer_base, long long region_bytes, long long recv_off,
                                                   long long recv_bytes, long long res_off, long long res_bytes,
                                                   unsigned long long* state) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !out) {
@@ -2761,7 +2788,7 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, 
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.bias = bias;
   p.residual = static_cast<const __nv_bfloat16*>(out); p.ldr = ldo; p.row_ss_out = row_ss_out;
-  p.ar_world = world; p.ar_rank = rank;
+  p.ar_world = world; p.ar_rank = rank; p.ar_mc_buf = static_cast<__nv_bfloat16*>(mc_base);
   for (int r = 0; r < world; ++r) p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(peer_base[r]);
   p.ar_state = state;
   p.ar_ll = 1;

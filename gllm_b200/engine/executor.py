@@ -270,7 +270,16 @@ class LLMEngine:
             return None
         return out
 
+    def _ep_bound(self, decode: bool):
+        """Expert parallelism: how many tokens ANY rank may route in this kind of step (the same number on every rank:
+        it sizes the grouped-GEMM grids over the rows a rank receives). Decode steps are bounded by the slot count,
+        prefill steps by the token budget; without this the GEMMs would scan the row blocks of the largest prefill."""
+        ep = getattr(self.model, "ep", None)
+        if ep is not None:
+            ep.token_bound = min(ep.max_tokens, self.ms if decode else max(self.cfg.max_batch_tokens, self.ms))
+
     def _decode_body(self, B: int):
+        self._ep_bound(True)
         if self.pp is not None:
             logits = self._pp_forward(self._decode_batch(B), B, decode_ws=self.decode_ws)
             if logits is not None:
@@ -434,6 +443,7 @@ class LLMEngine:
                              block_tables=torch.from_numpy(bt[slots]).to(dev), ctx_lens=i32(ctx), is_decode=False,
                              q_start=i32(q_start), q_len=i32(q_len), max_q_len=max(q_len), want_mtp=self.mtp is not None)
         self.stats["h2d_bytes"] += 4 * (3 * T + 3 * len(slots)) + bt[slots].nbytes
+        self._ep_bound(False)
         logits = self.model.forward(batch, self.kv_caches)
         out = torch.empty(T, dtype=torch.int32, device=dev)
         greedy = torch.zeros((T, 4), dtype=torch.float32, device=dev)
@@ -592,6 +602,7 @@ class LLMEngine:
         self.stats["prefill_steps"] += 1
         self.stats["prefill_tokens"] += int(T)
         self.model.op_timer = getattr(self, "prefill_timer", None)   # utils.tracing.GraphTimer(eager=True) or None
+        self._ep_bound(False)
         try:
             if self.pp is not None:
                 logits = self._pp_forward(batch, T, return_hidden=rows is None)
@@ -761,6 +772,7 @@ class LLMEngine:
         batch = ForwardBatch(token_ids=i32([0]), positions=i32([0]), slot_mapping=i32([-1]),
                              block_tables=torch.zeros((1, self.max_blocks), dtype=torch.int32, device=dev),
                              ctx_lens=i32([1]), is_decode=False, q_start=i32([0]), q_len=i32([1]), max_q_len=1)
+        self._ep_bound(False)
         self.model.forward(batch, self.kv_caches, return_hidden=True)
 
     def precapture(self, buckets=None):

@@ -118,12 +118,15 @@ class DecoderModel:
                 self._quantize_layer(lw, weight_quant, quant_group)
             if cfg.layer_is_moe(i):
                 from .moe import pack_moe_layer
+                self.ep = ep if ep is not None else getattr(tp, "ep", None)
                 lw.moe = pack_moe_layer(cfg, src, i, self.tp_rank, self.tp_size, self.device, dtype,
                                         ep=ep if ep is not None else getattr(tp, "ep", None), fused=self.fused, tp=tp,
                                         expert_quant=expert_quant or self.bs_fmt)
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
         self.lm_head = None
+        if not hasattr(self, "ep"):
+            self.ep = None
         self.vocab_local = cfg.vocab_size
         self.vocab_start = 0
         if self.last_stage:
@@ -346,14 +349,15 @@ class DecoderModel:
         if not self.last_stage or return_hidden:
             return x
         rows = batch.logits_rows
+        cap = float(c.logit_softcap or 0.0)       # final-logit soft cap: applied in the lm_head GEMM's epilogue
         if self.fused:
             xr, sr = (x, ss_in) if rows is None else (x.index_select(0, rows), ss_in.index_select(0, rows))
             logits = ops.gemm(xr, self.lm_head, out_dtype=torch.float32, row_ss=sr, norm_dim=H, eps=c.rms_norm_eps,
-                              bn=256)
+                              bn=256, softcap=cap)
         else:
             xr = x if rows is None else x.index_select(0, rows)
             hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
-            logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256)
+            logits = ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256, softcap=cap)
         mark("lm_head")
         self.last_mtp_logits = []
         if self.mtp_heads and getattr(batch, "want_mtp", False):
@@ -363,8 +367,6 @@ class DecoderModel:
                                                          eps=c.rms_norm_eps, bn=256))
                 else:
                     self.last_mtp_logits.append(ops.gemm(hn, w, out_dtype=torch.float32, bn=256))
-        if c.logit_softcap:
-            logits = torch.tanh(logits / c.logit_softcap) * c.logit_softcap
         return logits
 
     # ------------------------------------------------------------------------------------------

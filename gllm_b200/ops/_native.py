@@ -25,13 +25,14 @@ _SIGNATURES = {
     "gllm_sm_count": (I, []),
     "gllm_kernels_abi_version": (I, []),
     "gllm_gemm_bf16": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, I, I]),
+    "gllm_gemm_bf16_softcap": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, F]),
     "gllm_gemm_set_splitk_workspace": (I, [P, L, P, I]),
     "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I]),
     "gllm_gemm_set_pair": (I, [I, I]),
     "gllm_gemm_set_pair_big_m": (I, [I]),
     "gllm_gemm_bf16_residual_allreduce": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, I, I, P, P, P, P, P, L]),
     "gllm_gemm_bf16_residual_allreduce_push": (I, [P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, P, P, L, L, L, L, L, L, P]),
-    "gllm_gemm_bf16_residual_allreduce_ll": (I, [P, L, P, L, P, L, P, I, I, I, P, P, I, I, P, L, L, L, L, L, P]),
+    "gllm_gemm_bf16_residual_allreduce_ll": (I, [P, L, P, L, P, L, P, I, I, I, P, P, I, I, P, P, L, L, L, L, L, P]),
     "gllm_set_option": (L, [ctypes.c_char_p, L]),
     "gllm_get_option": (L, [ctypes.c_char_p]),
     "gllm_gemm_trace_enabled": (I, []),

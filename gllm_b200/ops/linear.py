@@ -77,15 +77,19 @@ def row_scale_ref(row_ss, norm_dim, eps):
 # plain GEMM (+ RMSNorm-as-row-scale prologue, + bias)
 # --------------------------------------------------------------------------------------------
 def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, norm_dim=0, eps=0.0,
-         bn=None, max_ctas=0, splits=0):
+         bn=None, max_ctas=0, splits=0, softcap: float = 0.0):
     """out[M,N] = rowscale(a) @ w.T (+ bias). ``row_ss`` [M, parts] are partial sums of squares of ``a``'s
     rows; when given, each output row is scaled by rsqrt(sum/norm_dim + eps) (the norm weight must
-    already be folded into ``w``)."""
+    already be folded into ``w``). ``softcap`` > 0 applies cap * tanh(x / cap) to the result (final-logit soft
+    capping) in the GEMM epilogue."""
     from .quant_gemm import QuantWeight, qgemm
     if isinstance(w, QuantWeight):      # quantised weight: dequantisation fused into the GEMM main loop
         y = qgemm(a, w, row_ss=row_ss, norm_dim=norm_dim, eps=eps)
-        if bias is not None or out_dtype != y.dtype:
-            y = (y.float() + bias.float() if bias is not None else y.float()).to(out_dtype)
+        if bias is not None or out_dtype != y.dtype or softcap:
+            y = y.float() + bias.float() if bias is not None else y.float()
+            if softcap:
+                y = torch.tanh(y / softcap) * softcap
+            y = y.to(out_dtype)
         if out is not None:
             out.copy_(y)
             return out
@@ -99,6 +103,8 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
             acc = acc * rs[:, None]
         if bias is not None:
             acc = acc + bias.float()
+        if softcap:
+            acc = torch.tanh(acc / softcap) * softcap
         res = acc.to(out.dtype if out is not None else out_dtype)
         if out is not None:
             out.copy_(res)
@@ -112,6 +118,13 @@ def gemm(a, w, *, out=None, out_dtype=torch.bfloat16, bias=None, row_ss=None, no
     bn = bn or _bn_for(N, M)
     nv.ensure_splitk_workspace(a.device)
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
+    if softcap:
+        rc = nv.lib().gllm_gemm_bf16_softcap(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                             out.stride(0), M, N, K, 1 if out.dtype == torch.float32 else 0, nv.ptr(bias),
+                                             nv.ptr(row_ss), parts, 1.0 / norm_dim if norm_dim else 0.0, eps, bn,
+                                             nv.stream_ptr(), float(softcap))
+        nv.check(rc, "gemm_bf16_softcap")
+        return out
     rc = nv.lib().gllm_gemm_bf16(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
                                  M, N, K, 1 if out.dtype == torch.float32 else 0, nv.ptr(bias), nv.ptr(row_ss),
                                  parts, 1.0 / norm_dim if norm_dim else 0.0, eps, bn, nv.stream_ptr(), max_ctas,

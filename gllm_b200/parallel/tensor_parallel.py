@@ -195,8 +195,8 @@ class TPContext:
             lay = self._lay
             rc = nv.lib().gllm_gemm_bf16_residual_allreduce_ll(
                 a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), ss.data_ptr(), M, N, K,
-                None, nv.stream_ptr(), self.size, self.rank, ctypes.cast(self._peer_base, ctypes.c_void_p), self._total,
-                lay["ll_recv"][0], self._ll_recv_bytes, lay["ll_res"][0], self._ll_res_bytes, self._state.data_ptr())
+                None, nv.stream_ptr(), self.size, self.rank, self._mc_base, ctypes.cast(self._peer_base, ctypes.c_void_p),
+                self._total, lay["ll_recv"][0], self._ll_recv_bytes, lay["ll_res"][0], self._ll_res_bytes, self._state.data_ptr())
             nv.check(rc, "gemm_bf16_residual_allreduce_ll")
             return ss
         if fused and self.form in ("push", "ll") and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:

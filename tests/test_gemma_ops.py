@@ -43,3 +43,15 @@ def test_laurel_altup_and_ple():
     torch.testing.assert_close(e, table[[2, 7], 4:8] * 2.0)
     inj = G.altup_inject(cor, e.new_ones(T, H), w)
     torch.testing.assert_close(inj[0], cor[0]); torch.testing.assert_close(inj[1], cor[1] + 1.0)
+
+
+def test_logit_softcap_in_the_gemm_op_cpu():
+    """ops.gemm(softcap=c) == c * tanh(x / c) on the CPU oracle path (the CUDA path does it in the GEMM epilogue)."""
+    import torch
+    from gllm_b200 import ops
+    torch.manual_seed(0)
+    a = torch.randn(5, 64).to(torch.bfloat16)
+    w = torch.randn(32, 64).to(torch.bfloat16)
+    got = ops.gemm(a, w, out_dtype=torch.float32, softcap=7.0)
+    x = a.float() @ w.float().t()
+    torch.testing.assert_close(got, torch.tanh(x / 7.0) * 7.0)

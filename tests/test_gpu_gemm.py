@@ -20,6 +20,12 @@ def _close(got, ref, tol=2e-2):
     assert err / denom < tol, f"max abs err {err} vs ref max {denom}"
     cos = torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item()
     assert cos > 0.9995, f"cosine {cos}"
+    # row by row: an error confined to a few rows or one tile column must not hide behind the global maximum
+    g2, r2 = got.reshape(-1, got.shape[-1]), ref.reshape(-1, ref.shape[-1])
+    row_err = (g2 - r2).abs().amax(-1)
+    row_ref = r2.abs().amax(-1)
+    bad = (row_err > 2 * tol * row_ref + 0.002 * denom).nonzero().flatten()
+    assert bad.numel() == 0, f"rows {bad[:8].tolist()} off by {row_err[bad[:8]].tolist()} (row max {row_ref[bad[:8]].tolist()})"
 
 
 @pytest.mark.parametrize("M,N,K,bn", [
@@ -32,6 +38,24 @@ def test_gemm_plain(M, N, K, bn):
     a, w = _rand(M, K), _rand(N, K, scale=0.05)
     out = ops.gemm(a, w, bn=bn)
     _close(out, a.float() @ w.float().t())
+
+
+def test_gemm_softcap_epilogue_and_narrow_tiles():
+    """Final-logit soft cap inside the store epilogue (fp32 logits, fused norm scale), and the 64-wide residual tiles."""
+    torch.manual_seed(3)
+    M, N, K = 200, 2048, 1024
+    a, w = _rand(M, K), _rand(N, K, scale=0.2)
+    ss = a.float().pow(2).sum(-1, keepdim=True).contiguous()
+    out = ops.gemm(a, w, out_dtype=torch.float32, row_ss=ss, norm_dim=K, eps=1e-6, bn=256, softcap=30.0)
+    x = (a.float() * torch.rsqrt(ss / K + 1e-6)) @ w.float().t()
+    ref = torch.tanh(x / 30.0) * 30.0
+    assert x.abs().max() > 20.0          # the cap actually bends some values
+    _close(out, ref)
+    r = _rand(M, N)
+    o, ss_out = ops.gemm_residual(a, w, r, bn=64)
+    want = (a.float() @ w.float().t() + r.float())
+    _close(o, want)
+    torch.testing.assert_close(ss_out[:M, :N // 64].sum(-1), o.float().pow(2).sum(-1), rtol=2e-3, atol=2e-3)
 
 
 @pytest.mark.parametrize("M,N,K,bn,splits", [

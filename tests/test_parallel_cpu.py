@@ -337,3 +337,31 @@ def test_lockstep_engines_with_expert_parallel_moe_match_unsplit_engine():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("EP_ENGINE_WORKER_OK") == 2
+
+
+def test_nvlink_counter_reader_against_a_fake_nvml(monkeypatch):
+    """The NVLink byte probe only READS the driver's throughput counters; here against a fake NVML."""
+    import types
+    import pynvml
+    from gllm_b200.parallel import nvlink_probe as P
+
+    calls = []
+
+    def fake_get(handle, fields):
+        calls.append(list(fields))
+        vals = []
+        for fid, scope in fields:
+            v = types.SimpleNamespace(nvmlReturn=0, value=types.SimpleNamespace(ullVal=1000 * fid + 7))
+            vals.append(v)
+        return vals
+
+    monkeypatch.setattr(pynvml, "nvmlDeviceGetFieldValues", fake_get)
+    tx, rx = P.read_nvlink_kib(object())
+    assert (tx, rx) == (138007, 139007)
+    assert calls == [[(138, 0xFFFFFFFF), (139, 0xFFFFFFFF)]]
+
+    def failing(handle, fields):
+        return [types.SimpleNamespace(nvmlReturn=3, value=types.SimpleNamespace(ullVal=0)) for _ in fields]
+
+    monkeypatch.setattr(pynvml, "nvmlDeviceGetFieldValues", failing)
+    assert P.read_nvlink_kib(object()) is None
