@@ -58,6 +58,7 @@ class ModelConfig:
     mlp_bias: bool = False
     hidden_act: str = "silu"
     sliding_window: int = 0
+    num_kv_shared_layers: int = 0      # trailing layers that reuse an earlier layer's KV cache (see kv_donor)
     attention_pattern: Optional[List[int]] = None  # per layer: 1 = sliding, 0 = global
     attention_sinks: bool = False
     embedding_scale: float = 1.0
@@ -141,6 +142,20 @@ class ModelConfig:
         return self.is_moe and layer >= self.first_k_dense and (layer % max(self.moe_layer_freq, 1) == 0
                                                                  or self.moe_layer_freq <= 1)
 
+    def kv_donor(self, layer: int):
+        """Shared-KV layers (the last ``num_kv_shared_layers`` of the stack) project no keys or values of their own:
+        they attend over the cache of the last earlier layer of the same attention kind (sliding-window or global).
+        Returns that layer's index, or None for a layer that owns its cache (src/arch/resolve.rs:16-455 resolves the
+        same donor map)."""
+        first_shared = self.num_layers - int(self.num_kv_shared_layers or 0)
+        if self.num_kv_shared_layers <= 0 or layer < first_shared:
+            return None
+        kind = self.layer_window(layer) > 0
+        for d in range(first_shared - 1, -1, -1):
+            if (self.layer_window(d) > 0) == kind:
+                return d
+        return first_shared - 1
+
     def layer_window(self, layer: int) -> int:
         if not self.sliding_window:
             return 0
@@ -212,6 +227,7 @@ class ModelConfig:
             mlp_bias=bool(g("mlp_bias", default=False)),
             hidden_act=str(g("hidden_act", "hidden_activation", "activation_function", default="silu")),
             sliding_window=int(g("sliding_window", default=0) or 0) if g("use_sliding_window", default=True) else 0,
+            num_kv_shared_layers=int(g("num_kv_shared_layers", default=0) or 0),
             num_experts=int(g("num_experts", "num_local_experts", "n_routed_experts", default=0) or 0),
             num_experts_per_tok=int(g("num_experts_per_tok", default=0) or 0),
             moe_intermediate_size=int(g("moe_intermediate_size", default=0) or 0),

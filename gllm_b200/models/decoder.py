@@ -190,11 +190,16 @@ class DecoderModel:
         return (num_pages, 2, self.n_kv_local, 16, self.cfg.head_dim)
 
     def alloc_kv_cache(self, num_pages: int) -> List[torch.Tensor]:
-        if self.kv_dtype == torch.float8_e4m3fn:
-            return [torch.zeros(self.kv_cache_shape(num_pages), dtype=torch.uint8, device=self.device).view(torch.float8_e4m3fn)
-                    for _ in self.layer_ids]
-        return [torch.zeros(self.kv_cache_shape(num_pages), dtype=self.dtype, device=self.device)
-                for _ in self.layer_ids]
+        """One cache per layer of this stage; a shared-KV layer's entry is its donor's tensor (no memory of its own)."""
+        def one():
+            if self.kv_dtype == torch.float8_e4m3fn:
+                return torch.zeros(self.kv_cache_shape(num_pages), dtype=torch.uint8, device=self.device).view(torch.float8_e4m3fn)
+            return torch.zeros(self.kv_cache_shape(num_pages), dtype=self.dtype, device=self.device)
+        caches: List[torch.Tensor] = []
+        for li, lw in zip(self.layer_ids, self.layers):
+            donor = getattr(lw, "kv_donor", None)
+            caches.append(caches[donor - self.layer_ids[0]] if donor is not None else one())
+        return caches
 
     def workspace(self, tokens: int) -> Workspace:
         if self._ws is None or self._ws.max_tokens < tokens:
@@ -281,17 +286,21 @@ class DecoderModel:
                 ops.rmsnorm(x, None, c.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)
         ss_in = ws.ss0[:T]
         for li, lw in zip(self.layer_ids, self.layers):
-            kv = kv_caches[li - self.layer_ids[0]]
+            # a shared-KV layer projects queries only (n_kv = 0: no K / V tiles, nothing written) and attends over its
+            # donor's pages
+            shared = lw.kv_donor is not None
+            kv = kv_caches[(lw.kv_donor if shared else li) - self.layer_ids[0]]
+            slots = None if shared else batch.slot_mapping
             if self.fused:
                 if self.bs_fmt is not None:
                     from ..ops import blockscale as B
                     B.gemm_qkv(self._act_q(x, T), lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
-                               slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
+                               slot_mapping=slots, positions=batch.positions, cos_t=self.cos,
                                sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                                row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 else:
                     ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
-                                 slot_mapping=batch.slot_mapping, positions=batch.positions, cos_t=self.cos,
+                                 slot_mapping=slots, positions=batch.positions, cos_t=self.cos,
                                  sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                                  row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 mark("qkv_gemm")
@@ -328,9 +337,9 @@ class DecoderModel:
                     attn = mla_attention(self, lw.mla, h, batch, kv, ws.attn[:T])
                     self._row_parallel(attn, lw.wo, x, ws.ss_b[:T], T)
                 else:
-                    qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
+                    qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T, :lw.wqkv.shape[0]], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
                     ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
-                                      positions=batch.positions, slot_mapping=batch.slot_mapping, cos_t=self.cos,
+                                      positions=batch.positions, slot_mapping=slots, cos_t=self.cos,
                                       sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
                                       k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, kv_scale=self.kv_scale)
                     self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)

@@ -207,6 +207,7 @@ class DenseLayerWeights:
     n_kv: int = 0
     moe: Optional[object] = None
     mla: Optional[object] = None
+    kv_donor: Optional[int] = None           # shared-KV layer: attends over this earlier layer's cache, writes none
     extra: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
@@ -223,7 +224,8 @@ def can_fuse(cfg: ModelConfig, tp: int = 1) -> bool:
             and cfg.hidden_act in L.ACT_IDS and cfg.hidden_size % 8 == 0)
 
 
-def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: bool):
+def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: bool, q_only: bool = False):
+    """``q_only``: a shared-KV layer (ModelConfig.kv_donor): only the query projection is packed, n_kv is 0."""
     p = layer_prefix(i)
     D = cfg.head_dim
     if cfg.is_mla:   # projections live in models/mla.py; only o_proj (row-parallel over heads * v) is packed here
@@ -241,16 +243,18 @@ def pack_attention(cfg: ModelConfig, src, i: int, rank: int, world: int, fused: 
         kv_sh = lambda n: src.get(p + n)[kvh * D:(kvh + 1) * D].contiguous()
     else:
         kv_sh = sh
-    q, k, v = sh("q_proj"), kv_sh("k_proj"), kv_sh("v_proj")
+    q = sh("q_proj")
+    k, v = (q[:0], q[:0]) if q_only else (kv_sh("k_proj"), kv_sh("v_proj"))
     wqkv = torch.cat([q, k, v], 0)
     input_norm = src.get(p + "input_norm").float()
     if fused:
         wqkv = _fold(wqkv, input_norm, cfg.norm_one_plus_w)
     bias = None
     if cfg.attention_bias and src.has(p + "q_proj_bias"):
-        bias = torch.cat([sh("q_proj_bias"), kv_sh("k_proj_bias"), kv_sh("v_proj_bias")]).float().contiguous()
+        parts = [sh("q_proj_bias")] + ([] if q_only else [kv_sh("k_proj_bias"), kv_sh("v_proj_bias")])
+        bias = torch.cat(parts).float().contiguous()
     qn = src.get(p + "q_norm").float().contiguous() if cfg.qk_norm else None
-    kn = src.get(p + "k_norm").float().contiguous() if cfg.qk_norm else None
+    kn = src.get(p + "k_norm").float().contiguous() if cfg.qk_norm and not q_only else None
     wo = sh("o_proj")
     return wqkv.contiguous(), bias, qn, kn, wo.contiguous(), input_norm.contiguous(), q.shape[0] // D, k.shape[0] // D
 
@@ -285,10 +289,12 @@ def pack_mlp(cfg: ModelConfig, src, prefix: str, rank: int, world: int, fused: b
 def pack_dense_layer(cfg: ModelConfig, src, i: int, rank: int = 0, world: int = 1, fused: Optional[bool] = None):
     fused = can_fuse(cfg, world) if fused is None else fused
     p = layer_prefix(i)
-    wqkv, bias, qn, kn, wo, input_norm, n_q, n_kv = pack_attention(cfg, src, i, rank, world, fused)
+    donor = cfg.kv_donor(i) if not cfg.is_mla else None
+    wqkv, bias, qn, kn, wo, input_norm, n_q, n_kv = pack_attention(cfg, src, i, rank, world, fused, q_only=donor is not None)
     post = src.get(p + "post_attn_norm").float().contiguous()
     lw = DenseLayerWeights(fused=fused, wqkv=wqkv, qkv_bias=bias, q_norm=qn, k_norm=kn, wo=wo, w_gate_up=None,
                            w_down=None, input_norm=input_norm, post_attn_norm=post, n_q=n_q, n_kv=n_kv)
+    lw.kv_donor = donor
     if not cfg.layer_is_moe(i):
         lw.w_gate_up, lw.w_down, lw.glu_bn = pack_mlp(cfg, src, p, rank, world, fused, post if fused else None)
     return lw

@@ -109,7 +109,7 @@ def main():
         x = torch.randn(M, N, device=dev).to(torch.bfloat16)
         act = torch.randn(M, K, device=dev).to(torch.bfloat16)
         ws = [(torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(per_graph)]
-        ss = torch.zeros(M, N // 128, device=dev)
+        ss = torch.zeros(M, N // 256, device=dev)      # the fused kernels report statistics per 256 columns
         part = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         bufs = tp.workspace_buffers(M) if tp.form == "push" else None
         if bufs is not None:

@@ -55,3 +55,61 @@ def test_logit_softcap_in_the_gemm_op_cpu():
     got = ops.gemm(a, w, out_dtype=torch.float32, softcap=7.0)
     x = a.float() @ w.float().t()
     torch.testing.assert_close(got, torch.tanh(x / 7.0) * 7.0)
+
+
+def _tiny_shared_kv_model(fused, seed=0, perturb=False):
+    import torch
+    from gllm_b200.models.config import ModelConfig
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = ModelConfig(arch="llama", hidden_size=256, num_layers=4, num_heads=2, num_kv_heads=1, head_dim=128,
+                      intermediate_size=512, vocab_size=300, max_position_embeddings=128, rms_norm_eps=1e-6,
+                      num_kv_shared_layers=2)
+    src = RandomWeights(cfg, "cpu", torch.bfloat16, seed=seed, std=0.05)
+    if perturb:           # other keys / values for the shared layers: they must not matter
+        base_get = src.get
+
+        def get(name):
+            t = base_get(name)
+            if name.startswith(("L2.", "L3.")) and name.rsplit(".", 1)[-1] in ("k_proj", "v_proj"):
+                return t + 1.0
+            return t
+        src.get = get
+    return cfg, DecoderModel(cfg, src, device="cpu", dtype=torch.bfloat16, fused=fused, max_positions=128)
+
+
+def _run_tokens(model, ids, kv=None, start=0):
+    import torch
+    from gllm_b200.engine.batch import ForwardBatch
+    n = len(ids)
+    total = start + n
+    kv = kv or model.alloc_kv_cache(8)
+    i32 = dict(dtype=torch.int32)
+    fb = ForwardBatch(token_ids=torch.tensor(ids, **i32), positions=torch.arange(start, total, **i32),
+                      slot_mapping=torch.arange(start, total, **i32), block_tables=torch.arange(8, **i32)[None],
+                      ctx_lens=torch.tensor([total], **i32), q_start=torch.tensor([0], **i32),
+                      q_len=torch.tensor([n], **i32), max_q_len=n, logits_rows=torch.tensor([n - 1]))
+    return model.forward(fb, kv).float()[0, :300], kv
+
+
+def test_shared_kv_donor_layers():
+    """The last two layers of a four-layer model project no keys / values and attend over layer 1's cache: the donor
+    map, the aliasing of the caches, independence from the shared layers' own K / V weights, fused and unfused paths
+    agreeing, and prefill + one more token matching a single longer prefill."""
+    import torch
+    cfg, m = _tiny_shared_kv_model(fused=True)
+    assert [cfg.kv_donor(i) for i in range(4)] == [None, None, 1, 1]
+    assert m.layers[2].n_kv == 0 and m.layers[2].wqkv.shape[0] == 2 * 128
+    kv = m.alloc_kv_cache(8)
+    assert kv[2] is kv[1] and kv[3] is kv[1] and kv[0] is not kv[1]
+    ids = [5, 17, 250, 3, 99, 42, 7]
+    ref, _ = _run_tokens(m, ids)
+    _, m2 = _tiny_shared_kv_model(fused=True, perturb=True)
+    got, _ = _run_tokens(m2, ids)
+    torch.testing.assert_close(got, ref)
+    _, mu = _tiny_shared_kv_model(fused=False)
+    got_u, _ = _run_tokens(mu, ids)
+    assert torch.nn.functional.cosine_similarity(got_u, ref, dim=0) > 0.995
+    _, kv = _run_tokens(m, ids[:-1])
+    step, _ = _run_tokens(m, ids[-1:], kv=kv, start=len(ids) - 1)
+    assert torch.nn.functional.cosine_similarity(step, ref, dim=0) > 0.999

@@ -100,3 +100,42 @@ def test_pool():
     torch.testing.assert_close(out[1], h[10:30].float().mean(0), rtol=1e-3, atol=1e-3)
     assert torch.equal(ops.pool(h, st, ln, "cls")[1], h[10].float())
     assert torch.equal(ops.pool(h, st, ln, "last")[0], h[9].float())
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_shared_kv_donor_layers_on_the_gpu(fused):
+    """A model whose last two layers reuse layer 1's KV pages (query-only QKV GEMM, n_kv = 0) gives the CPU oracle's
+    logits, for a prefill and for a decode step over the aliased caches."""
+    from gllm_b200.engine.batch import ForwardBatch
+    from gllm_b200.models.config import ModelConfig
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = ModelConfig(arch="llama", hidden_size=256, num_layers=4, num_heads=2, num_kv_heads=1, head_dim=128,
+                      intermediate_size=512, vocab_size=300, max_position_embeddings=128, rms_norm_eps=1e-6,
+                      num_kv_shared_layers=2)
+    models = {}
+    for dev in ("cpu", "cuda"):
+        src = RandomWeights(cfg, "cpu", torch.bfloat16, seed=0, std=0.05)
+        models[dev] = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, fused=fused, max_positions=128)
+    ids = [5, 17, 250, 3, 99, 42, 7, 11, 200]
+
+    def run(m, toks, kv, start, decode):
+        dev = m.device
+        n, total = len(toks), start + len(toks)
+        i32 = dict(dtype=torch.int32, device=dev)
+        fb = ForwardBatch(token_ids=torch.tensor(toks, **i32), positions=torch.arange(start, total, **i32),
+                          slot_mapping=torch.arange(start, total, **i32), block_tables=torch.arange(8, **i32)[None],
+                          ctx_lens=torch.tensor([total], **i32), is_decode=decode, q_start=torch.tensor([0], **i32),
+                          q_len=torch.tensor([n], **i32), max_q_len=n,
+                          logits_rows=torch.tensor([n - 1], dtype=torch.int64, device=dev))
+        return m.forward(fb, kv).float()[0, :300].cpu()
+
+    out = {}
+    for dev, m in models.items():
+        kv = m.alloc_kv_cache(8)
+        assert kv[2] is kv[1]
+        pre = run(m, ids[:-1], kv, 0, False)
+        dec = run(m, ids[-1:], kv, len(ids) - 1, True)
+        out[dev] = (pre, dec)
+    for a, b in zip(out["cuda"], out["cpu"]):
+        assert torch.nn.functional.cosine_similarity(a, b, dim=0) > 0.995
