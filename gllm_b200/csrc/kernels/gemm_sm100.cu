@@ -155,6 +155,20 @@ struct GemmParams {
   long long ar_ll_res_off, ar_ll_res_bytes;     // same for the result slots ([M][n_pad] bf16)
   int ar_drop_flags;          // test hook: leave the tile flags unset (push) / the tiles unsent (ll): the waits run out
   float softcap;              // EPI_STORE, unsplit launches only: out = softcap * tanh(out / softcap) (0 = off)
+  // Reduce-scatter output of the low-latency form (ar_rs_only == 1): rank r keeps the finished rows [r * ceil(M / W), ...)
+  // in `out` / `residual` / `row_ss_out`, which then are SHARDS indexed by the local row; nothing is broadcast.
+  int ar_rs_only;
+  // All-gather of the A operand before the main loop (ag_world > 0): every rank holds rows [r * ceil(M / W), ...) of A in
+  // `ag_src`; the kernel stores them into every rank's slots (self-validating words as in the low-latency all-reduce:
+  // sentinel 0x80008000, two parity sets), copies all rows from its own slots into `ag_dst` (the tensor the A tensor
+  // map describes, local memory), meets the other CTAs of the grid and only then starts the A loads. The weight tiles
+  // of the first stages are requested before that, so they travel while the rows are exchanged.
+  int ag_world, ag_rank;
+  const __nv_bfloat16* ag_src; long long ag_src_ld;
+  __nv_bfloat16* ag_dst; long long ag_dst_ld;
+  char* ag_peer[8]; char* ag_mc;            // symmetric region bases (and the multicast mapping or null)
+  long long ag_slot_off, ag_slot_bytes;     // bytes: offset of the slots in the region, size of one parity set
+  unsigned long long* ag_state;             // local: [0] launch index (parity)
   unsigned long long wait_ns, peer_wait_ns;   // limits of the bounded waits
   long long* trace;   // debugging aid (GLLM_TRACE builds): CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
@@ -1178,7 +1192,8 @@ __device__ void ar_ll_reduce(const GemmParams& p, int parity, volatile int* abor
     const int n0 = grp * 256 + lane * 8;
     const long long off = static_cast<long long>(lrow) * n_pad + n0;
     uint4 rr = make_uint4(0u, 0u, 0u, 0u);
-    if (n0 < p.N) rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(m) * p.ldr + n0);
+    const long long rrow = p.ar_rs_only ? lrow : m;    // reduce-scatter output: residual / out / statistics are shards
+    if (n0 < p.N) rr = *reinterpret_cast<const uint4*>(p.residual + rrow * p.ldr + n0);
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -1209,6 +1224,21 @@ __device__ void ar_ll_reduce(const GemmParams& p, int parity, volatile int* abor
       w.y = ll_word(pack_bf16x2(v[2], v[3]));
       w.z = ll_word(pack_bf16x2(v[4], v[5]));
       w.w = ll_word(pack_bf16x2(v[6], v[7]));
+    }
+    if (p.ar_rs_only) {
+      float ss = 0.f;
+      if (n0 < p.N) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+        }
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + rrow * p.ldo + n0) = w;
+      }
+      ss = warp_sum(ss);
+      if (p.row_ss_out && lane == 0) p.row_ss_out[rrow * groups + grp] = ss;
+      continue;
     }
     const long long ro = static_cast<long long>(m) * n_pad + n0;
     if (p.ar_mc_buf) {   // one store, replicated to every rank's result slots by the switch
@@ -1257,6 +1287,48 @@ __device__ __forceinline__ void ar_ll_advance(const GemmParams& p, unsigned long
       p.ar_state[1] = launch + 1ull;
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------------
+// All-gather of the A rows in front of the main loop, see GemmParams::ag_world.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ bool ag_ll_phase(const GemmParams& p, int parity, volatile int* abort) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
+  const int W = p.ag_world;
+  const int rows_per = (p.M + W - 1) / W;
+  const int own_lo = min(p.M, p.ag_rank * rows_per), own_hi = min(p.M, own_lo + rows_per);
+  const int groups = p.K / 256;
+  const long long set_off = p.ag_slot_off + parity * p.ag_slot_bytes;
+  // this rank's rows -> every rank's slots
+  for (int u = blockIdx.x * wpc + warp; u < (own_hi - own_lo) * groups; u += gridDim.x * wpc) {
+    const int lrow = u / groups, grp = u % groups;
+    const int c0 = grp * 256 + lane * 8;
+    uint4 v = *reinterpret_cast<const uint4*>(p.ag_src + static_cast<long long>(lrow) * p.ag_src_ld + c0);
+    v.x = ll_word(v.x); v.y = ll_word(v.y); v.z = ll_word(v.z); v.w = ll_word(v.w);
+    const long long off = (static_cast<long long>(own_lo + lrow) * p.K + c0) * 2;
+    if (p.ag_mc) {
+      multimem_st_b128(reinterpret_cast<__nv_bfloat16*>(p.ag_mc + set_off + off), v);
+    } else {
+      for (int r = 0; r < W; ++r) st_volatile_u4(p.ag_peer[r] + set_off + off, v);
+    }
+  }
+  // all rows: own slots -> the A tensor
+  bool all_ok = true;
+  for (int u = blockIdx.x * wpc + warp; u < p.M * groups; u += gridDim.x * wpc) {
+    const int m = u / groups, grp = u % groups;
+    const int c0 = grp * 256 + lane * 8;
+    uint4 v;
+    const bool ok = ll_take(reinterpret_cast<__nv_bfloat16*>(p.ag_peer[p.ag_rank] + set_off) + static_cast<long long>(m) * p.K + c0,
+                            v, p, abort);
+    if (!__all_sync(0xffffffffu, ok)) {
+      all_ok = false;
+      break;
+    }
+    *reinterpret_cast<uint4*>(p.ag_dst + static_cast<long long>(m) * p.ag_dst_ld + c0) = v;
+  }
+  fence_proxy_async_global();   // the rows were written by ordinary stores and are read by TMA
+  return all_ok;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1548,6 +1620,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (!PAIR && FP8 == 0) {
+    if (p.ag_world > 0) {
+      // the A rows of the other ranks arrive before any A tile is loaded; every CTA of the (co-resident) grid helps
+      const unsigned long long ag_launch = p.ag_state[0];
+      const bool ag_ok = ag_ll_phase(p, static_cast<int>(ag_launch & 1ull), abort_flag);
+      const bool bar_ok = grid_barrier(p.sk_barrier, gridDim.x, p.err, p.wait_ns);
+      if (blockIdx.x == 0 && threadIdx.x == 0) p.ag_state[0] = ag_launch + 1ull;   // every CTA read it before the barrier
+      if (!ag_ok || !bar_ok) *abort_flag = 1;
+      fence_proxy_async_global();
+      __syncthreads();
+    }
+  }
   pdl_launch_dependents();   // the next kernel's CTAs may be scheduled (they wait for this grid in their own pdl_wait)
   if constexpr (PAIR) cluster_barrier();   // the partner's barriers are initialised before anything signals them
   tc_fence_after();
@@ -2103,7 +2187,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int parity = static_cast<int>(ar_launch_s & 1ull);
         ar_ll_reduce<BN>(p, parity, abort_flag);
         GLLM_STAMP(threadIdx.x == 0, 9);     // this CTA's share of the owned rows reduced and sent to every rank
-        ar_ll_gather<BN>(p, parity, abort_flag);
+        if (!p.ar_rs_only) ar_ll_gather<BN>(p, parity, abort_flag);
         ar_ll_advance(p, ar_launch_s);
       }
     } else if (fused_ar && p.ar_push) {
@@ -2200,10 +2284,39 @@ static int choose_splits(int tiles, int num_kb, int stage_bytes, long long tile_
   return best_s;
 }
 
+// The all-gather descriptor of the NEXT single-CTA bf16 GEMM launched by this thread (gllm_gemm_set_allgather_input).
+struct PendingAllGather {
+  bool active = false;
+  int world = 0, rank = 0;
+  const void* src = nullptr; long long src_ld = 0;
+  void* dst = nullptr; long long dst_ld = 0;
+  void* peer[8] = {}; void* mc = nullptr;
+  long long slot_off = 0, slot_bytes = 0;
+  unsigned long long* state = nullptr;
+};
+static thread_local PendingAllGather g_pending_ag;
+
 template <int BN, int MT, int EPI, int FP8>
 static int launch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows, GemmParams p,
                        cudaStream_t stream, int max_ctas, int force_splits) {
   using Cfg = GemmCfg<BN, MT, false, FP8>;
+  if (g_pending_ag.active) {
+    PendingAllGather ag = g_pending_ag;
+    g_pending_ag.active = false;
+    if (FP8 != 0 || p.mblk_group != nullptr || p.K % 256 != 0 || A != ag.dst || lda != ag.dst_ld || p.ar_world > 0 ||
+        static_cast<long long>(p.M) * p.K * 2 > ag.slot_bytes) {
+      set_last_error("gemm with all-gathered A: needs a bf16, ungrouped GEMM whose A is the gather destination, K %% 256 "
+                     "== 0 and %lld slot bytes (have %lld)", static_cast<long long>(p.M) * p.K * 2, ag.slot_bytes);
+      return -1;
+    }
+    p.ag_world = ag.world; p.ag_rank = ag.rank;
+    p.ag_src = static_cast<const __nv_bfloat16*>(ag.src); p.ag_src_ld = ag.src_ld;
+    p.ag_dst = static_cast<__nv_bfloat16*>(ag.dst); p.ag_dst_ld = ag.dst_ld;
+    for (int r = 0; r < ag.world; ++r) p.ag_peer[r] = static_cast<char*>(ag.peer[r]);
+    p.ag_mc = static_cast<char*>(ag.mc);
+    p.ag_slot_off = ag.slot_off; p.ag_slot_bytes = ag.slot_bytes; p.ag_state = ag.state;
+    p.peer_wait_ns = static_cast<unsigned long long>(settings().peer_wait_ns);
+  }
   constexpr int kElemsPerKB = FP8 ? 128 : 64;
   const int esz = FP8 ? 1 : 2;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -2334,6 +2447,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   // distributed shared memory instead of global scratch + grid barrier.
   const bool cluster_allowed = rt.cluster_sk != 0;
   if (BN == 128 && cluster_allowed && splits >= 2 && splits <= 8 && items <= sms && part_fits && p.ar_world == 0 &&
+      p.ag_world == 0 &&
       p.mblk_group == nullptr && max_ctas <= 0) {
     p.cluster_sk = 1;
     cudaLaunchConfig_t cfg = {};
@@ -2797,6 +2911,62 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, 
   p.ar_drop_flags = settings().ar_drop_flags;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, 128, (cudaStream_t)stream, 0, 0);
+}
+
+// Reduce-scatter form of the low-latency fused kernel: out_shard[lrow] = sum_ranks(A @ B^T)[rank * ceil(M / W) + lrow]
+// + out_shard[lrow] for the rows this rank owns (`out_shard` holds the residual shard on entry, `row_ss_out` the
+// statistics of the shard's rows per 256 columns); no rank receives the other rows. The sequence-parallel counterpart
+// of gllm_gemm_bf16_residual_allreduce_ll: same receive slots, no result slots.
+GLLM_API int gllm_gemm_bf16_residual_reduce_scatter(const void* A, long long lda, const void* B, long long ldb,
+                                                    void* out_shard, long long ldo, float* row_ss_out, int M, int N,
+                                                    int K, const float* bias, void* stream, int world, int rank,
+                                                    void* const* peer_base, long long region_bytes, long long recv_off,
+                                                    long long recv_bytes, unsigned long long* state) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !out_shard) {
+    set_last_error("gemm_reduce_scatter: bad world/rank/pointers (world %d rank %d)", world, rank);
+    return -1;
+  }
+  if ((recv_off & 15) || (recv_bytes & 15) || recv_off < 0 || recv_off + 2 * recv_bytes > region_bytes) {
+    set_last_error("gemm_reduce_scatter: bad region layout");
+    return -1;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out_shard; p.ldo = ldo; p.bias = bias;
+  p.residual = static_cast<const __nv_bfloat16*>(out_shard); p.ldr = ldo; p.row_ss_out = row_ss_out;
+  p.ar_world = world; p.ar_rank = rank;
+  for (int r = 0; r < world; ++r) p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(peer_base[r]);
+  p.ar_state = state;
+  p.ar_ll = 1; p.ar_rs_only = 1;
+  p.ar_ll_recv_off = recv_off; p.ar_ll_recv_bytes = recv_bytes;
+  p.ar_ll_res_off = recv_off; p.ar_ll_res_bytes = 1ll << 40;   // result slots are not used by this form
+  p.ar_drop_flags = settings().ar_drop_flags;
+  p.err = gllm_error_word();
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, 128, (cudaStream_t)stream, 0, 0);
+}
+
+// The NEXT bf16 GEMM this thread launches (plain, residual, GLU or QKV epilogue; not grouped, not a CTA-pair launch)
+// first all-gathers its A operand: `src` holds this rank's rows [rank * ceil(M / W), ...) of A, `dst` is the [M, K]
+// tensor passed as A to that GEMM (local memory, filled by the kernel), the slots ([2 parities][M][K] bf16, every word
+// the sentinel 0x80008000 between launches) live at `slot_off` of the symmetric region. `state`: one local 64-bit
+// launch counter owned by this all-gather site. The descriptor is consumed by the next launch, whatever its outcome.
+GLLM_API int gllm_gemm_set_allgather_input(const void* src, long long src_ld, void* dst, long long dst_ld, int world,
+                                           int rank, void* mc_base, void* const* peer_base, long long region_bytes,
+                                           long long slot_off, long long slot_bytes, unsigned long long* state) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !src || !dst ||
+      (slot_off & 15) || (slot_bytes & 15) || slot_off < 0 || slot_off + 2 * slot_bytes > region_bytes ||
+      (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || (src_ld & 7) || (dst_ld & 7)) {
+    set_last_error("gemm_set_allgather_input: bad arguments (world %d rank %d)", world, rank);
+    return -1;
+  }
+  PendingAllGather& ag = g_pending_ag;
+  ag.active = true;
+  ag.world = world; ag.rank = rank;
+  ag.src = src; ag.src_ld = src_ld; ag.dst = dst; ag.dst_ld = dst_ld;
+  for (int r = 0; r < world; ++r) ag.peer[r] = peer_base[r];
+  ag.mc = mc_base;
+  ag.slot_off = slot_off; ag.slot_bytes = slot_bytes; ag.state = state;
+  return 0;
 }
 
 // out[M,N/2] = act(rowscale*gate) * rowscale*up ; B is the tile-interleaved gate/up weight [N,K]:

@@ -61,7 +61,8 @@ class Workspace:
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
-                 quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0, expert_quant: Optional[str] = None):
+                 quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0, expert_quant: Optional[str] = None,
+                 weight_blob: Optional[bool] = None):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
@@ -150,6 +151,42 @@ class DecoderModel:
             self.mtp_heads.append(L.pad_rows(w, 256).contiguous())
             d += 1
         self._ws: Optional[Workspace] = None
+        self.blob = None
+        if weight_blob if weight_blob is not None else self.device.type == "cuda":
+            self._pack_blob()
+
+    def _pack_blob(self):
+        """Re-home the packed dense tensors (per-layer projections and norms, embedding, heads) in ONE contiguous,
+        256-byte-aligned allocation with an offset table (engine/weight_blob.py): one upload / one mapping for the
+        whole stage, constant per-layer strides for homogeneous layers. Skipped when the device cannot hold the
+        second copy that exists while the blob is filled."""
+        from ..engine.weight_blob import WeightBlob
+        tensors = {}
+        for li, lw in zip(self.layer_ids, self.layers):
+            for name, val in vars(lw).items():
+                if isinstance(val, torch.Tensor) and val.numel() > 0:
+                    tensors[f"L{li}.{name}"] = val
+        for name in ("embed", "lm_head", "final_norm"):
+            val = getattr(self, name, None)
+            if isinstance(val, torch.Tensor) and val.numel() > 0:
+                tensors[name] = val
+        for d, w in enumerate(self.mtp_heads):
+            tensors[f"mtp_head.{d}"] = w
+        need = sum((t.numel() * t.element_size() + 255) // 256 * 256 for t in tensors.values())
+        if self.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.device)
+            if need + (1 << 30) > free:
+                return
+        blob = WeightBlob.pack(tensors, device=self.device)
+        for li, lw in zip(self.layer_ids, self.layers):
+            for name, val in list(vars(lw).items()):
+                if f"L{li}.{name}" in blob.entries:
+                    setattr(lw, name, blob.view(f"L{li}.{name}"))
+        for name in ("embed", "lm_head", "final_norm"):
+            if name in blob.entries:
+                setattr(self, name, blob.view(name))
+        self.mtp_heads = [blob.view(f"mtp_head.{d}") for d in range(len(self.mtp_heads))]
+        self.blob = blob
 
     # ------------------------------------------------------------------------------------------
     def _quantize_layer(self, lw, mode: str, group: int):

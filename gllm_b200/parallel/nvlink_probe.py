@@ -28,18 +28,26 @@ import torch.distributed as dist
 _TX, _RX = 138, 139      # NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX / _RX (KiB since the driver loaded)
 
 
+LAST_NVML_STATUS = "ok"
+
+
 def read_nvlink_kib(handle):
-    """(tx_kib, rx_kib) summed over all links (scope id 0xFFFFFFFF), or None when the driver does not report them."""
+    """(tx_kib, rx_kib) summed over all links (scope id 0xFFFFFFFF), or None when the driver does not report them
+    (``LAST_NVML_STATUS`` then says what NVML answered)."""
+    global LAST_NVML_STATUS
     import pynvml
     try:
         vals = pynvml.nvmlDeviceGetFieldValues(handle, [(_TX, 0xFFFFFFFF), (_RX, 0xFFFFFFFF)])
-    except pynvml.NVMLError:
+    except pynvml.NVMLError as exc:
+        LAST_NVML_STATUS = f"nvmlDeviceGetFieldValues raised {exc!r}"
         return None
     out = []
     for v in vals:
         if v.nvmlReturn != 0:
+            LAST_NVML_STATUS = f"field {getattr(v, 'fieldId', '?')}: nvmlReturn {v.nvmlReturn}"
             return None
         out.append(int(v.value.ullVal))
+    LAST_NVML_STATUS = "ok"
     return tuple(out)
 
 
@@ -134,7 +142,7 @@ def main():
             res.update(tx_bytes_per_launch=tx // launches, rx_bytes_per_launch=rx // launches,
                        tx_over_algorithmic=round(tx / launches / algo, 3), rx_over_algorithmic=round(rx / launches / algo, 3))
         else:
-            res["counters_unavailable"] = True
+            res["counters_unavailable"] = LAST_NVML_STATUS
         res["device_error"] = nv.device_error()
         out["gemm_allreduce"] = res
         tp.close()
@@ -171,7 +179,7 @@ def main():
             res.update(tx_bytes_per_layer=tx // launches, rx_bytes_per_layer=rx // launches,
                        tx_over_algorithmic=round(tx / launches / algo, 3))
         else:
-            res["counters_unavailable"] = True
+            res["counters_unavailable"] = LAST_NVML_STATUS
         res["device_error"] = nv.device_error()
         out["ep_layer"] = res
         ep.close()

@@ -108,6 +108,9 @@ class TPContext:
                 self._ll_res_bytes = _align(self.ll_max_tokens * self.n_pad * 2)
                 take("ll_recv", 2 * self._ll_recv_bytes)
                 take("ll_res", 2 * self._ll_res_bytes)
+                # slots of the all-gather in front of a column-parallel GEMM (sequence-parallel activations)
+                self._ag_bytes = _align(self.ll_max_tokens * self.n_pad * 2)
+                take("ag_slots", 2 * self._ag_bytes)
         else:
             take("pull", 3 * self.buf_elems * 2)
             take("counters", 64)
@@ -142,6 +145,7 @@ class TPContext:
         self._mc_base = mc_ptr or None
         self._peer_base = (ctypes.c_void_p * 8)(*([p for p in peer_ptrs] + [None] * (8 - n)))
         self._state = torch.zeros(8, dtype=torch.int64, device=self.device)
+        self._ag_state = torch.zeros(8, dtype=torch.int64, device=self.device)
         self._sms = int(nv.lib().gllm_sm_count())
         if self.form == "pull":
             off = lay["pull"][0]
@@ -152,7 +156,7 @@ class TPContext:
             self._mc_cnt = (mc_ptr + counter_off) if mc_ptr else None
 
     def _fill_sentinel(self):
-        for name in ("ll_recv", "ll_res"):
+        for name in ("ll_recv", "ll_res", "ag_slots"):
             if name in self._lay:
                 off, nbytes = self._lay[name]
                 self._symm[off:off + nbytes].view(torch.int32).fill_(_LL_SENTINEL)
@@ -246,6 +250,75 @@ class TPContext:
         ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
         return ss
 
+    # ---- sequence-parallel forms: rows of the activations sharded over the ranks ----------------------------
+    def shard_rows(self, M: int):
+        """(first row, row count) of this rank's shard of an [M, ...] activation: rows [r * ceil(M / W), ...)."""
+        per = (M + self.size - 1) // self.size
+        lo = min(M, self.rank * per)
+        return lo, min(M, lo + per) - lo
+
+    def gemm_reduce_scatter_residual(self, a, w, x_shard, ss_out, M: int):
+        """Row-parallel GEMM whose sum over ranks stays sharded by rows (reduce-scatter instead of all-reduce):
+        x_shard <- rows of sum_ranks(a @ w.T) owned by this rank + x_shard. ``a`` [M, K_local], ``x_shard``
+        [ceil(M / W), N] (the first ``shard_rows(M)[1]`` rows are used). One kernel in the low-latency form; unfused
+        GEMM + all-reduce + slice otherwise. Reference: tp_reduce_scatter (src/engine/coordinator/compute.rs:148-164)."""
+        K = a.shape[1]
+        N = w.shape[0]
+        lo, n_own = self.shard_rows(M)
+        parts = (N + 255) // 256
+        ss = ss_out[:max(n_own, 1), :parts]
+        fused = (self.mode == "fused" and self.form == "ll" and not self.baseline and M <= self.ll_max_tokens and
+                 N <= self.n_pad and ((M + 127) // 128) * (self.n_pad // 128) <= self._sms and ss.is_contiguous())
+        if fused:
+            lay = self._lay
+            rc = nv.lib().gllm_gemm_bf16_residual_reduce_scatter(
+                a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x_shard.data_ptr(), x_shard.stride(0), ss.data_ptr(),
+                M, N, K, None, nv.stream_ptr(), self.size, self.rank, ctypes.cast(self._peer_base, ctypes.c_void_p),
+                self._total, lay["ll_recv"][0], self._ll_recv_bytes, self._state.data_ptr())
+            nv.check(rc, "gemm_bf16_residual_reduce_scatter")
+            return ss
+        import torch.distributed as dist
+        full = ops.gemm(a, w, out_dtype=torch.float32)
+        if self.size > 1:
+            dist.all_reduce(full, group=self.group)
+        mine = (full[lo:lo + n_own] + x_shard[:n_own].float()).to(x_shard.dtype)
+        x_shard[:n_own].copy_(mine)
+        pad = parts * 256 - N
+        sq = mine.float().pow(2)
+        if pad:
+            sq = torch.nn.functional.pad(sq, (0, pad))
+        ss[:n_own].copy_(sq.reshape(n_own, parts, 256).sum(-1))
+        return ss
+
+    def allgather_input(self, a_shard, a_full):
+        """Column-parallel GEMM over sequence-parallel activations: the NEXT GEMM op called with ``a_full`` ([M, K]
+        local tensor) as its A operand first gathers the ranks' row shards (``a_shard``: this rank's
+        ``shard_rows(M)`` rows) into it, inside the same kernel, while its first weight tiles are already in flight.
+        Without the fused form the rows are gathered here with an ordinary all-gather. Reference:
+        tp_column_parallel_all_gather (src/engine/coordinator/compute.rs:246-271)."""
+        M, K = a_full.shape
+        lo, n_own = self.shard_rows(M)
+        fused = (self.mode == "fused" and self.form == "ll" and not self.baseline and a_full.is_cuda and
+                 M * K * 2 <= self._ag_bytes and K % 256 == 0 and a_full.dtype == torch.bfloat16)
+        if fused:
+            rc = nv.lib().gllm_gemm_set_allgather_input(
+                a_shard.data_ptr(), a_shard.stride(0), a_full.data_ptr(), a_full.stride(0), self.size, self.rank,
+                self._mc_base, ctypes.cast(self._peer_base, ctypes.c_void_p), self._total, self._lay["ag_slots"][0],
+                self._ag_bytes, self._ag_state.data_ptr())
+            nv.check(rc, "gemm_set_allgather_input")
+            return a_full
+        import torch.distributed as dist
+        if self.size == 1:
+            a_full[:n_own].copy_(a_shard[:n_own])
+            return a_full
+        per = (M + self.size - 1) // self.size
+        buf = torch.zeros((self.size * per, K), dtype=a_full.dtype, device=a_full.device)
+        mine = torch.zeros((per, K), dtype=a_full.dtype, device=a_full.device)
+        mine[:n_own].copy_(a_shard[:n_own])
+        dist.all_gather_into_tensor(buf, mine, group=self.group)
+        a_full.copy_(buf[:M])
+        return a_full
+
     def reset(self):
         """Clear the flags, done words and launch state after a failed launch (collective: every rank calls it)."""
         import torch.distributed as dist
@@ -259,6 +332,7 @@ class TPContext:
                     self._symm[off:off + nbytes].zero_()
             self._fill_sentinel()
             self._state.zero_()
+            self._ag_state.zero_()
         torch.cuda.synchronize(self.device)
         if self.size > 1:
             dist.barrier(group=self.group)

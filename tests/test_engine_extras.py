@@ -282,3 +282,32 @@ def test_engine_buckets_follow_the_observed_batch_sizes_and_the_director():
     before, after = eng.evolve_buckets()
     assert after[-1] == 6 and 3 in after or 4 in after       # three running sequences: a bucket near 3, capacity kept
     assert not eng._evolve_pending
+
+
+def test_decoder_weights_live_in_one_blob():
+    """With ``weight_blob=True`` the packed dense tensors of a decoder are views into one contiguous allocation with an
+    offset table and a constant per-layer stride, and the model computes the same logits as without it."""
+    import torch
+    from gllm_b200.engine.batch import ForwardBatch
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    a = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, weight_blob=False, max_positions=64)
+    b = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, weight_blob=True, max_positions=64)
+    assert a.blob is None and b.blob is not None
+    base = b.blob.data.data_ptr()
+    for lw in b.layers:
+        assert base <= lw.wqkv.data_ptr() < base + b.blob.total_bytes()
+        assert (lw.wqkv.data_ptr() - base) % 256 == 0
+    assert b.blob.layer_stride("L0.", "L1.") > 0          # homogeneous layers: one byte distance for every tensor
+    T = 9
+    i32 = dict(dtype=torch.int32)
+    fb = lambda: ForwardBatch(token_ids=torch.arange(T, **i32) + 3, positions=torch.arange(T, **i32),
+                              slot_mapping=torch.arange(T, **i32), block_tables=torch.arange(2, **i32)[None],
+                              ctx_lens=torch.tensor([T], **i32), q_start=torch.tensor([0], **i32),
+                              q_len=torch.tensor([T], **i32), max_q_len=T)
+    la = a.forward(fb(), a.alloc_kv_cache(2))
+    lb = b.forward(fb(), b.alloc_kv_cache(2))
+    torch.testing.assert_close(la, lb)

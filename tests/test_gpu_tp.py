@@ -102,6 +102,42 @@ def test_push_allreduce_wait_runs_out_and_context_recovers(mode):
     assert nv.device_error() == 0
 
 
+def test_sequence_parallel_forms_world1_protocol():
+    """All-gather in front of a GEMM and reduce-scatter behind one, world size 1 on ordinary memory: the slots, the
+    parity sets and the launch counters of both forms over several launches, against fp32."""
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H = 1024
+    tp = single_gpu_context(dev, hidden=H, max_tokens=256, mode="ll_p2p")
+    torch.manual_seed(4)
+    for it, M in enumerate([256, 100, 256, 37]):
+        x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+        w1 = (torch.randn(768, H, device=dev) * 0.05).to(torch.bfloat16)
+        w2 = (torch.randn(H, 768, device=dev) * 0.05).to(torch.bfloat16)
+        a_full = torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
+        tp.allgather_input(x, a_full)
+        mid = ops.gemm(a_full, w1, bn=128)
+        assert torch.equal(a_full, x), f"launch {it}: gathered rows differ"
+        _rows_close(mid, x.float() @ w1.float().t(), f"all-gather GEMM, launch {it}")
+        res = x.clone()
+        ss = torch.zeros(M, H // 256, device=dev)
+        tp.gemm_reduce_scatter_residual(mid, w2, res, ss, M)
+        _rows_close(res, mid.float() @ w2.float().t() + x.float(), f"reduce-scatter GEMM, launch {it}")
+        torch.testing.assert_close(ss.sum(-1), res.float().pow(2).sum(-1), rtol=2e-3, atol=2e-3)
+    assert int(tp._ag_state[0]) == 4 and int(tp._state[1]) == 4
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("mode", ["ll", "ll_p2p", "nccl"])
+def test_sequence_parallel_block_two_gpus(mode):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29911 + hash(mode) % 50), os.path.join(ROOT, "tests", "sp_worker.py"), mode]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_WORKER_OK") == 2
+
+
 @pytest.mark.multigpu
 @pytest.mark.parametrize("mode", ["ll", "fused_p2p", "fused", "nccl", "pull", "pull_p2p", "pull_two_shot", "pull_p2p_two_shot"])
 def test_fused_allreduce_two_gpus(mode):

@@ -365,3 +365,15 @@ def test_nvlink_counter_reader_against_a_fake_nvml(monkeypatch):
 
     monkeypatch.setattr(pynvml, "nvmlDeviceGetFieldValues", failing)
     assert P.read_nvlink_kib(object()) is None
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_block_allgather_gemm_reduce_scatter_on_gloo(world):
+    """Row-sharded activations: all-gather -> column-parallel GEMM -> row-parallel GEMM -> reduce-scatter (the unfused
+    forms on gloo ranks; the fused kernels run the same worker on GPUs)."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29860 + world), os.path.join(ROOT, "tests", "sp_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_WORKER_OK") == world
