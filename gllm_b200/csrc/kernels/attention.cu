@@ -267,6 +267,108 @@ __device__ __forceinline__ void attend_page(const uint32_t (&qf)[8][4], uint32_t
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Decode with the roles of the operands swapped (bf16 pages): S^T = K Q^T and O^T = V^T P^T. The 16 tokens of a page
+// are the M rows of the MMA tile and the query heads of the group (at most 8) are its 8 columns, so a page costs 8 + 8
+// MMAs instead of 16 + 16, four exponentials per thread instead of eight, and the output accumulators are 32 registers
+// instead of 64. (With the queries as rows, a group of 4 heads fills 4 of 16 rows and the kernel is bound by its own
+// instruction stream, not by HBM, whenever few warps share an SM: one KV head per rank under tensor parallelism.)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+// B fragments of Q^T: thread (g = lane / 4, t = lane % 4) holds Q[head g][16 ks + 2t, +1] and [.. + 8 + 2t, +1].
+__device__ __forceinline__ void load_qT_frags(const __nv_bfloat16* qb, int group, uint32_t (&qt)[8][2]) {
+  const int g = (threadIdx.x & 31) >> 2, t = threadIdx.x & 3;
+  const __nv_bfloat16* row = qb + g * kHD;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const int c = ks * 16 + t * 2;
+    qt[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(row + c) : 0u;
+    qt[ks][1] = g < group ? *reinterpret_cast<const uint32_t*>(row + c + 8) : 0u;
+  }
+}
+// Softmax state per thread: the two query heads 2t and 2t + 1 (the same values in the eight threads that share t).
+struct SoftmaxStateT {
+  float mA, mB, lA, lB;
+};
+// One page: tokens [tok_base, tok_base + 16) of which [lo, hi) may be attended (the same range for every head).
+__device__ __forceinline__ void attend_page_t(const uint32_t (&qt)[8][2], uint32_t k_smem, uint32_t v_smem, int tok_base,
+                                              int lo, int hi, float scale_log2, float (&o)[8][4], SoftmaxStateT& st) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};   // two accumulation chains over the 8 k-steps
+  {
+    // A = K: matrices (tokens 0-7 | 8-15) x (chunk 2 ks | 2 ks + 1)
+    const int tok = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int csel = lane >> 4;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int chunk = (ks & 3) * 2 + csel;
+      const uint32_t addr = k_smem + (ks >> 2) * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t a[4];
+      ldsm_x4(addr, a[0], a[1], a[2], a[3]);
+      if (ks & 1) mma_bf16_16816(sb, a, qt[ks][0], qt[ks][1]);
+      else mma_bf16_16816(sa, a, qt[ks][0], qt[ks][1]);
+    }
+  }
+  // c0: (token g, head 2t)  c1: (token g, head 2t + 1)  c2, c3: token g + 8
+  float s0 = (sa[0] + sb[0]) * scale_log2, s1 = (sa[1] + sb[1]) * scale_log2;
+  float s2 = (sa[2] + sb[2]) * scale_log2, s3 = (sa[3] + sb[3]) * scale_log2;
+  const int t0 = tok_base + g, t1 = t0 + 8;
+  if (t0 < lo || t0 >= hi) s0 = s1 = -INFINITY;
+  if (t1 < lo || t1 >= hi) s2 = s3 = -INFINITY;
+  float mxA = fmaxf(s0, s2), mxB = fmaxf(s1, s3);
+#pragma unroll
+  for (int d = 4; d <= 16; d <<= 1) {
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, d));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, d));
+  }
+  const float mnA = fmaxf(st.mA, mxA), mnB = fmaxf(st.mB, mxB);
+  const float msA = (mnA == -INFINITY) ? 0.f : mnA, msB = (mnB == -INFINITY) ? 0.f : mnB;
+  const float corrA = exp2f(st.mA - msA), corrB = exp2f(st.mB - msB);
+  const bool rescale = __any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f);
+  st.mA = mnA;
+  st.mB = mnB;
+  s0 = exp2f(s0 - msA);
+  s1 = exp2f(s1 - msB);
+  s2 = exp2f(s2 - msA);
+  s3 = exp2f(s3 - msB);
+  float rsA = s0 + s2, rsB = s1 + s3;
+#pragma unroll
+  for (int d = 4; d <= 16; d <<= 1) {
+    rsA += __shfl_xor_sync(0xffffffffu, rsA, d);
+    rsB += __shfl_xor_sync(0xffffffffu, rsB, d);
+  }
+  st.lA = st.lA * corrA + rsA;
+  st.lB = st.lB * corrB + rsB;
+  // P^T as the B operand (k = token, n = head): the accumulator layout transposed 8 x 8 at a time
+  const uint32_t pb0 = movmatrix_trans(pack_bf16x2(s0, s1));
+  const uint32_t pb1 = movmatrix_trans(pack_bf16x2(s2, s3));
+  {
+    // A = V^T: transposed loads of (tokens 0-7 | 8-15) x (chunk 2 mt | 2 mt + 1)
+    const int tok = (lane & 7) + ((lane >> 4) << 3);
+    const int csel = (lane >> 3) & 1;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      const int chunk = (mt & 3) * 2 + csel;
+      const uint32_t addr = v_smem + (mt >> 2) * 2048 + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t a[4];
+      ldsm_x4_t(addr, a[0], a[1], a[2], a[3]);
+      if (rescale) {
+        o[mt][0] *= corrA;
+        o[mt][1] *= corrB;
+        o[mt][2] *= corrA;
+        o[mt][3] *= corrB;
+      }
+      mma_bf16_16816(o[mt], a, pb0, pb1);
+    }
+  }
+}
+
 template <bool KV8>
 __device__ __forceinline__ void load_page_kv(const CUtensorMap* tmap, uint8_t* dst, uint64_t* bar, int page,
                                              int n_kv_heads, int kvh) {
@@ -353,18 +455,28 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   }
   __syncthreads();
 
+  // bf16 pages with at most 8 heads per group take the swapped form (tokens as MMA rows, heads as columns); fp8
+  // pages and larger groups keep the heads as rows
+  constexpr bool kSwapOk = !KV8;
+  const bool swapped = kSwapOk && p.group <= 8;
   // Q fragments: rows = the `group` q heads of this kv head (rows >= group are zero)
   uint32_t qf[8][4];
+  [[maybe_unused]] uint32_t qt[8][2];
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
     const __nv_bfloat16* qb = p.q + (static_cast<long long>(b) * p.n_q_heads + kvh * p.group) * kHD;
-    load_q_frags<KV8>(qb + r0 * kHD, qb + r1 * kHD, r0 < p.group, r1 < p.group, qf);
+    if (swapped) {
+      if constexpr (kSwapOk) load_qT_frags(qb, p.group, qt);
+    } else {
+      load_q_frags<KV8>(qb + r0 * kHD, qb + r1 * kHD, r0 < p.group, r1 < p.group, qf);
+    }
   }
 
   float o[16][4];
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   SoftmaxState st{-INFINITY, -INFINITY, 0.f, 0.f};
+  [[maybe_unused]] SoftmaxStateT stt{-INFINITY, -INFINITY, 0.f, 0.f};
 
   uint8_t* my_ring = smem + warp * kDecStages * 2 * kTile;
   uint64_t* my_bars = bars + warp * kDecStages;
@@ -405,7 +517,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     if (!__all_sync(0xffffffffu, got)) break;
     const uint32_t kaddr = smem_u32(my_ring + stg * 2 * kTile);
     const int tok_base = (p0 + warp + i * kDecWarps) * kPage;
-    attend_page<KV8>(qf, kaddr, kaddr + kTile, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
+    if (swapped) {
+      if constexpr (kSwapOk)
+        attend_page_t(qt, kaddr, kaddr + kTile, tok_base, first_tok, ctx, p.scale_log2,
+                      *reinterpret_cast<float(*)[8][4]>(&o[0][0]), stt);
+    } else {
+      attend_page<KV8>(qf, kaddr, kaddr + kTile, tok_base, first_tok, ctx, first_tok, ctx, p.scale_log2, o, st);
+    }
     __syncwarp();
     const int nxt = i + kDecStages;
     if ((nxt & 31) == 0 && nxt < n_my) {   // the next issue opens a new chunk of 32 page ids
@@ -426,7 +544,25 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   // cross-warp merge through shared memory (the rings are idle now)
   float* mo = reinterpret_cast<float*>(smem);            // [warp][16][128]
   float* mml = mo + kDecWarps * 16 * kHD;                // [warp][16][2]
-  {
+  if (swapped) {
+    // swapped form: o[mt] = (feature 16 mt + g | + 8, head 2t | 2t + 1)
+    const int g = lane >> 2, t = lane & 3;
+    float* wA = mo + (warp * 16 + 2 * t) * kHD;
+    float* wB = wA + kHD;
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+      wA[mt * 16 + g] = o[mt][0];
+      wB[mt * 16 + g] = o[mt][1];
+      wA[mt * 16 + g + 8] = o[mt][2];
+      wB[mt * 16 + g + 8] = o[mt][3];
+    }
+    if (g == 0) {
+      mml[(warp * 16 + 2 * t) * 2 + 0] = stt.mA;
+      mml[(warp * 16 + 2 * t) * 2 + 1] = stt.lA;
+      mml[(warp * 16 + 2 * t + 1) * 2 + 0] = stt.mB;
+      mml[(warp * 16 + 2 * t + 1) * 2 + 1] = stt.lB;
+    }
+  } else {
     const int r0 = lane >> 2, r1 = r0 + 8;
 #pragma unroll
     for (int dt = 0; dt < 16; ++dt) {
