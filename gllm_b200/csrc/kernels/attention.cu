@@ -291,10 +291,18 @@ __device__ __forceinline__ void load_qT_frags(const __nv_bfloat16* qb, int group
     qt[ks][1] = g < group ? *reinterpret_cast<const uint32_t*>(row + c + 8) : 0u;
   }
 }
-// Softmax state per thread: the two query heads 2t and 2t + 1 (the same values in the eight threads that share t).
+// Softmax state per thread: the two query heads 2t and 2t + 1. The maxima are the same in the eight threads that share
+// t; the sums are partial (this thread's tokens) until `softmax_t_finish`.
 struct SoftmaxStateT {
   float mA, mB, lA, lB;
 };
+__device__ __forceinline__ void softmax_t_finish(SoftmaxStateT& st) {
+#pragma unroll
+  for (int d = 4; d <= 16; d <<= 1) {
+    st.lA += __shfl_xor_sync(0xffffffffu, st.lA, d);
+    st.lB += __shfl_xor_sync(0xffffffffu, st.lB, d);
+  }
+}
 // One page: tokens [tok_base, tok_base + 16) of which [lo, hi) may be attended (the same range for every head).
 __device__ __forceinline__ void attend_page_t(const uint32_t (&qt)[8][2], uint32_t k_smem, uint32_t v_smem, int tok_base,
                                               int lo, int hi, float scale_log2, float (&o)[8][4], SoftmaxStateT& st) {
@@ -337,14 +345,10 @@ __device__ __forceinline__ void attend_page_t(const uint32_t (&qt)[8][2], uint32
   s1 = exp2f(s1 - msB);
   s2 = exp2f(s2 - msA);
   s3 = exp2f(s3 - msB);
-  float rsA = s0 + s2, rsB = s1 + s3;
-#pragma unroll
-  for (int d = 4; d <= 16; d <<= 1) {
-    rsA += __shfl_xor_sync(0xffffffffu, rsA, d);
-    rsB += __shfl_xor_sync(0xffffffffu, rsB, d);
-  }
-  st.lA = st.lA * corrA + rsA;
-  st.lB = st.lB * corrB + rsB;
+  // the row sums stay per thread (its own two tokens of every page): the correction factors are the same in the eight
+  // threads of a head pair, so the sum over those threads can wait until the last page
+  st.lA = st.lA * corrA + (s0 + s2);
+  st.lB = st.lB * corrB + (s1 + s3);
   // P^T as the B operand (k = token, n = head): the accumulator layout transposed 8 x 8 at a time
   const uint32_t pb0 = movmatrix_trans(pack_bf16x2(s0, s1));
   const uint32_t pb1 = movmatrix_trans(pack_bf16x2(s2, s3));
@@ -547,6 +551,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
   if (swapped) {
     // swapped form: o[mt] = (feature 16 mt + g | + 8, head 2t | 2t + 1)
     const int g = lane >> 2, t = lane & 3;
+    if constexpr (kSwapOk) softmax_t_finish(stt);
     float* wA = mo + (warp * 16 + 2 * t) * kHD;
     float* wB = wA + kHD;
 #pragma unroll
