@@ -57,7 +57,7 @@ class MoeLayerWeights:
             holder[key] = ws
         return ws
 
-    def _expert_ffn(self, model, src, ws, T, fused_norm: bool):
+    def _expert_ffn(self, model, src, ws, T, fused_norm: bool, mark=lambda name: None):
         """The routed rows through their experts' SwiGLU FFNs: ws.y_perm <- down(glu(gate/up(rows))). ``src`` [T, H]
         is what the experts read; the rows were bucketed by ``M.permute`` (ws.dest / blk_group / ss_perm)."""
         c = self.cfg
@@ -66,7 +66,9 @@ class MoeLayerWeights:
         if self.bs_fmt is None:
             L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
                        num_groups=self.e_local, **rs)
+            mark("moe_gate_up")
             L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+            mark("moe_down")
             return
         # block-scaled experts: the routed rows are quantised straight from the token rows into their expert blocks,
         # the SwiGLU output is quantised again for the down projection (only the rows that exist: a device-side count)
@@ -77,10 +79,14 @@ class MoeLayerWeights:
             ws.actq = B.alloc_act(ws.max_rows, self.inter, self.bs_fmt, src.device)
         ts = self.act_tensor_scale
         B.quantize_act_scatter(src, ws.dest, k, self.bs_fmt, ws.aq, ws.max_rows, tensor_scale=ts)
+        mark("moe_quant_in")
         B.gemm_glu(ws.aq, self.w_gate_up, act=model.act_id, out=ws.act, bn=128, mblk_group=ws.blk_group,
                    num_groups=self.e_local, **rs)
+        mark("moe_gate_up")
         B.quantize_act_rows(ws.act, self.bs_fmt, ws.actq, ws.total_rows, tensor_scale=ts)
+        mark("moe_quant_mid")
         B.gemm(ws.actq, self.w_down, out=ws.y_perm, bn=128, mblk_group=ws.blk_group, num_groups=self.e_local)
+        mark("moe_down")
 
     def _route(self, x, row_ss, ws, T, norm_dim, eps):
         c = self.cfg
@@ -97,13 +103,17 @@ class MoeLayerWeights:
         c = self.cfg
         H = c.hidden_size
         ws = self.workspace(model, T)
+        tm = getattr(model, "op_timer", None)      # per-op device time inside a CUDA graph (bench --op-breakdown)
+        mark = tm.mark if tm is not None else (lambda name: None)
         ids, w = self._route(x, ss_in, ws, T, H, c.rms_norm_eps)
+        mark("moe_route")
         if self.ep is not None:
             return self.ep.moe_forward(self, model, x, ss_in, ss_out, ids, w, ws, T)
         if self.tp_experts is not None:
             return self._forward_tp_experts(model, x, x, ss_in, ss_out, ids, w, ws, T, fused_norm=True)
         M.permute(x, ss_in, ids, ws, self.e0, self.e_local)
-        self._expert_ffn(model, x, ws, T, fused_norm=True)
+        mark("moe_permute")
+        self._expert_ffn(model, x, ws, T, fused_norm=True, mark=mark)
         shared = None
         if self.shared_gate_up is not None:
             sa = L.gemm_glu(x, self.shared_gate_up, act=model.act_id, row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps,
@@ -111,6 +121,7 @@ class MoeLayerWeights:
             shared = ops.gemm(sa, self.shared_down, bn=128)
         ss = ss_out.reshape(-1)[:T].view(T, 1)
         M.combine(x, ws.y_perm, ws.dest, w, shared=shared, ss_out=ss)
+        mark("moe_combine")
         return ss
 
     def _forward_tp_experts(self, model, x, src, ss_in, ss_out, ids, w, ws, T, fused_norm: bool):
