@@ -159,7 +159,10 @@ __global__ void __launch_bounds__(256) ep_recv_plan_kernel(EpComm c, int* blk_gr
   const unsigned long long epoch = c.state[0];
   const bool ok = ep_wait(c.flags[c.rank] + 1, epoch * c.world, c.err);
   if (!ok) {  // nothing trustworthy arrived: make the GEMMs skip every block
-    for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) blk_group[b] = -1;
+    for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) {
+      blk_group[b] = -1;
+      blk_group[max_blocks + b] = 0;
+    }
     if (threadIdx.x == 0) *total_rows = 0;
     return;
   }
@@ -196,6 +199,8 @@ __global__ void __launch_bounds__(256) ep_recv_plan_kernel(EpComm c, int* blk_gr
       g = lo;
     }
     blk_group[b] = g;
+    // second half of the table: received rows in this block (the rest is padding), for the grouped GEMMs
+    blk_group[max_blocks + b] = g < 0 ? 0 : min(kEpBlockRows, s_tot[g] - (row - s_off[g]));
   }
   // padding rows of every block: no return address, benign statistic
   int* meta = c.meta[c.rank];
@@ -304,7 +309,8 @@ static int ep_make(const GllmEpDesc* d, EpComm& c) {
 
 // Steps 1-3 for T tokens with k routed experts each. x [T, hidden] bf16, row_ss [T, ss_parts] or null,
 // ids [T, k]. cursors: local int[num_experts] scratch. After it returns (stream order) this rank's x / ss / meta
-// buffers hold the rows routed to its experts and blk_group / total_rows describe them.
+// buffers hold the rows routed to its experts and blk_group (2 * max_blocks ints: the expert of every 128-row block, then
+// the received rows in every block) / total_rows describe them.
 GLLM_API int gllm_ep_dispatch(const GllmEpDesc* desc, const void* x, const float* row_ss, int ss_parts, const int* ids,
                               int T, int k, int* cursors, int* blk_group, int max_blocks, int* total_rows,
                               void* stream) {

@@ -155,6 +155,10 @@ struct GemmParams {
   long long ar_ll_res_off, ar_ll_res_bytes;     // same for the result slots ([M][n_pad] bf16)
   int ar_drop_flags;          // test hook: leave the tile flags unset (push) / the tiles unsent (ll): the waits run out
   float softcap;              // EPI_STORE, unsplit launches only: out = softcap * tanh(out / softcap) (0 = off)
+  // Grouped GEMMs: rows that exist in every 128-row block (the rest of a block is padding: a block of an expert with
+  // 16 routed rows has 112 of them). When given, the producer loads only ceil(rows / 32) * 32 rows of the A tile
+  // (32-row boxes through the third tensor map) and the epilogue neither reads nor stores the padding rows.
+  const int* mblk_rows;
   // Reduce-scatter output of the low-latency form (ar_rs_only == 1): rank r keeps the finished rows [r * ceil(M / W), ...)
   // in `out` / `residual` / `row_ss_out`, which then are SHARDS indexed by the local row; nothing is broadcast.
   int ar_rs_only;
@@ -1509,7 +1513,7 @@ __device__ void cluster_reduce_phase(const GemmParams& p, const float* part, int
 template <int BN, int MT, int EPI, int FP8 /* operand mode, OPM_* */, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_a32, const GemmParams p) {
   static_assert(!PAIR || (MT == 1 && !FP8), "CTA pairs: one 128-row block per CTA, bf16");
   using Cfg = GemmCfg<BN, MT, PAIR, FP8>;
   constexpr bool kBS = Cfg::kBlockScaled;
@@ -1670,11 +1674,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_load_2d_pair(sb, &tmap_b, bar0, kb * kElemsPerKB, b_row + static_cast<int>(crank) * (BN / 2));
           } else {
             const bool b_done = b_prefetched > 0;   // the first stages' weight halves were requested before pdl_wait
+            // grouped GEMM with row counts: only the 32-row pieces of the A tile that hold routed rows travel
+            int a_pieces = 4;
+            if constexpr (MT == 1) {
+              if (p.mblk_rows) a_pieces = min(4, max(1, (p.mblk_rows[m_sup] + 31) >> 5));
+            }
             if (b_done) --b_prefetched;
-            else mbar_expect_tx(&full_bar[stage], kTxBytes);
+            else mbar_expect_tx(&full_bar[stage], kTxBytes - (4 - a_pieces) * (kABytes / 4));
+            if (a_pieces < 4) {
+              for (int pc = 0; pc < a_pieces; ++pc)
+                tma_load_2d(sa + pc * (kABytes / 4), &tmap_a32, &full_bar[stage], kb * kElemsPerKB, m_sup * kBM + pc * 32);
+            } else {
 #pragma unroll
-            for (int i = 0; i < MT; ++i)
-              tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
+              for (int i = 0; i < MT; ++i)
+                tma_load_2d(sa + i * kABytes, &tmap_a, &full_bar[stage], kb * kElemsPerKB, (m_sup * MT + i) * kBM);
+            }
             if (!b_done) tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * kElemsPerKB, b_row);
             if constexpr (kBS) {
               constexpr int kChunkBytes = Cfg::kSfChunks * kSfChunkBytes;   // scale factors of 128 rows for this K block
@@ -1898,7 +1912,14 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll 1
         for (int i = 0; i < MT; ++i) {
           const int m = (m_sup * MTE + (PAIR ? static_cast<int>(crank) : i)) * kBM + q * 32 + lane;
-          const bool row_ok = m < p.M;
+          bool row_ok = m < p.M;
+          if constexpr (MT == 1 && !PAIR) {
+            if (p.mblk_rows) {   // padding rows of a grouped block: nothing to read or store
+              const int blk_rows = p.mblk_rows[m_sup];
+              if (q * 32 >= blk_rows) continue;     // warp-uniform: the whole quarter is padding
+              row_ok = row_ok && (q * 32 + lane) < blk_rows;
+            }
+          }
           const int mm = row_ok ? m : (p.M - 1);
           float rs = row_scale_of(p, mm);
           if (p.a_scale) rs *= p.a_scale[mm];
@@ -2295,6 +2316,7 @@ struct PendingAllGather {
   unsigned long long* state = nullptr;
 };
 static thread_local PendingAllGather g_pending_ag;
+static thread_local const int* g_pending_block_rows = nullptr;
 
 template <int BN, int MT, int EPI, int FP8>
 static int launch_gemm(const void* A, long long lda, const void* B, long long ldb, long long b_rows, GemmParams p,
@@ -2345,9 +2367,14 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
       return -1;
     }
   }
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, ta32;
   if (make_tmap_2d(&ta, A, dt, esz, uint64_t(p.M), uint64_t(kcols), uint64_t(lda), kBM, kElemsPerKB)) return -1;
   if (make_tmap_2d(&tb, B, dt, esz, uint64_t(b_rows), uint64_t(kcols), uint64_t(ldb), BN, kElemsPerKB)) return -1;
+  if (make_tmap_2d(&ta32, A, dt, esz, uint64_t(p.M), uint64_t(kcols), uint64_t(lda), 32, kElemsPerKB)) return -1;
+  if (g_pending_block_rows) {      // set for the next grouped launch of this thread (gllm_gemm_set_block_rows)
+    if (p.mblk_group && MT == 1) p.mblk_rows = g_pending_block_rows;
+    g_pending_block_rows = nullptr;
+  }
   static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
   auto kern = gemm_tn_kernel<BN, MT, EPI, FP8>;
   int dev = 0;
@@ -2477,7 +2504,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     }
     if (max_clusters[splits] >= tiles) {
       cfg.numAttrs = rt.pdl ? 2 : 1;
-      cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+      cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, ta32, p);
       if (ce == cudaSuccess) return 0;
       (void)cudaGetLastError();   // this cluster shape cannot be scheduled here: fall back
     }
@@ -2485,7 +2512,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   }
   p.park = (BN == 128 && park_allowed && (splits > 1 || p.ar_world > 0) && items <= grid && part_fits &&
             p.mblk_group == nullptr) ? 1 : 0;
-  cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, true, 0, ta, tb, p);
+  cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, true, 0, ta, tb, ta32, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -2597,7 +2624,7 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
   const int pairs = items < max_pairs ? items : max_pairs;
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.numAttrs = rt.pdl ? 2 : 1;
-  cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, ta, tb, ta, p);
   if (ce != cudaSuccess) {
     (void)cudaGetLastError();
     set_last_error("gemm (pair) launch failed: %s", cudaGetErrorString(ce));
@@ -2943,6 +2970,13 @@ GLLM_API int gllm_gemm_bf16_residual_reduce_scatter(const void* A, long long lda
   p.ar_drop_flags = settings().ar_drop_flags;
   p.err = gllm_error_word();
   return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, 128, (cudaStream_t)stream, 0, 0);
+}
+
+// Row counts of the 128-row blocks of the NEXT grouped GEMM this thread launches (GemmParams::mblk_rows): one int per
+// block, on the device. Consumed by that launch; launches that are not grouped ignore and clear it.
+GLLM_API int gllm_gemm_set_block_rows(const int* rows) {
+  g_pending_block_rows = rows;
+  return 0;
 }
 
 // The NEXT bf16 GEMM this thread launches (plain, residual, GLU or QKV epilogue; not grouped, not a CTA-pair launch)

@@ -111,7 +111,9 @@ __global__ void moe_count_kernel(const int* ids, int n, int e0, int e_local, int
   if (e >= 0 && e < e_local) atomicAdd(&counts[e], 1);
 }
 
-// Single block: padded bucket offsets, block -> expert map, cursors reset. max_blocks bounds blk_group.
+// Single block: padded bucket offsets, block -> expert map, cursors reset. blk_group holds 2 * max_blocks ints: the
+// expert of every 128-row block (-1: inactive), then the number of routed rows in every block (the rest is padding),
+// which lets the grouped GEMMs load and store only the rows that exist.
 __global__ void moe_plan_kernel(const int* counts, int e_local, int* offsets, int* cursors, int* blk_group,
                                 int max_blocks, int* total_rows) {
   __shared__ int s_off[513];
@@ -141,6 +143,7 @@ __global__ void moe_plan_kernel(const int* counts, int e_local, int* offsets, in
       g = lo;
     }
     blk_group[b] = g;
+    blk_group[max_blocks + b] = g < 0 ? 0 : min(kMoeBlockRows, counts[g] - (row - s_off[g]));
   }
 }
 
@@ -238,7 +241,7 @@ GLLM_API int gllm_moe_route(const float* logits, long long ld, int T, int E, int
 }
 
 // Buckets the T*k routed (token, slot) pairs of local experts [e0, e0+e_local) into 128-row blocks.
-// counts / offsets (e_local+1) / cursors / blk_group (max_blocks) / total_rows (1) are int32 device
+// counts / offsets (e_local+1) / cursors / blk_group (2 * max_blocks: experts, then row counts) / total_rows (1) are int32 device
 // buffers; counts must be zero on entry (the call re-zeroes nothing: the caller owns them).
 GLLM_API int gllm_moe_permute(const void* x, const float* row_ss, int ss_parts, const int* ids, int T, int k,
                               int hidden, int e0, int e_local, int* counts, int* offsets, int* cursors,

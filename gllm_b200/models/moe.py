@@ -64,9 +64,12 @@ class MoeLayerWeights:
         H = c.hidden_size
         rs = dict(row_ss=ws.ss_perm, norm_dim=H, eps=c.rms_norm_eps) if fused_norm else {}
         if self.bs_fmt is None:
+            rows = getattr(ws, "blk_rows", None)      # routed rows per block: padding rows are neither loaded nor stored
+            L.set_block_rows(rows)
             L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
                        num_groups=self.e_local, **rs)
             mark("moe_gate_up")
+            L.set_block_rows(rows)
             L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
             mark("moe_down")
             return
@@ -80,11 +83,14 @@ class MoeLayerWeights:
         ts = self.act_tensor_scale
         B.quantize_act_scatter(src, ws.dest, k, self.bs_fmt, ws.aq, ws.max_rows, tensor_scale=ts)
         mark("moe_quant_in")
+        rows = getattr(ws, "blk_rows", None)
+        L.set_block_rows(rows)
         B.gemm_glu(ws.aq, self.w_gate_up, act=model.act_id, out=ws.act, bn=128, mblk_group=ws.blk_group,
                    num_groups=self.e_local, **rs)
         mark("moe_gate_up")
         B.quantize_act_rows(ws.act, self.bs_fmt, ws.actq, ws.total_rows, tensor_scale=ts)
         mark("moe_quant_mid")
+        L.set_block_rows(rows)
         B.gemm(ws.actq, self.w_down, out=ws.y_perm, bn=128, mblk_group=ws.blk_group, num_groups=self.e_local)
         mark("moe_down")
 

@@ -250,6 +250,13 @@ def gemm_glu(a, w_packed, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, 
     return out
 
 
+def set_block_rows(rows):
+    """Row counts of the 128-row blocks of the NEXT grouped GEMM launched by this thread (``MoeWorkspace.blk_rows``):
+    the kernel then loads and stores only the rows that exist. No-op for CPU tensors."""
+    if rows is not None and rows.is_cuda:
+        nv.check(nv.lib().gllm_gemm_set_block_rows(rows.data_ptr()), "gemm_set_block_rows")
+
+
 def gemm_grouped(a, w_stack, mblk_group, num_groups, *, out=None, bn=128, max_ctas=0):
     """Grouped GEMM: rows [128i, 128i+128) of ``a`` multiply expert ``mblk_group[i]``'s [N,K] weight."""
     M, K = a.shape

@@ -52,7 +52,9 @@ class MoeWorkspace:
         self.max_blocks = self.max_rows // BLOCK
         z = lambda *s, dt=torch.int32: torch.zeros(*s, dtype=dt, device=device)
         self.counts, self.offsets, self.cursors = z(e_local), z(e_local + 1), z(e_local)
-        self.blk_group, self.total_rows = z(self.max_blocks), z(1)
+        self._blk, self.total_rows = z(2 * self.max_blocks), z(1)
+        self.blk_group = self._blk[:self.max_blocks]       # expert of every 128-row block (-1: inactive)
+        self.blk_rows = self._blk[self.max_blocks:]        # routed rows in every block (the rest of the block is padding)
         self.a_perm = torch.zeros((self.max_rows, hidden), dtype=dtype, device=device)
         self.ss_perm = torch.ones(self.max_rows, 1, dtype=torch.float32, device=device)
         self.act = torch.zeros((self.max_rows, inter), dtype=dtype, device=device)
@@ -88,11 +90,15 @@ def permute(x, row_ss, ids, ws: MoeWorkspace, e0=0, e_local=None):
                 if row_ss is not None:
                     ws.ss_perm[d, 0] = row_ss[i // k].float().sum()
         blk = torch.full((ws.max_blocks,), -1, dtype=torch.int32)
+        rows = torch.zeros(ws.max_blocks, dtype=torch.int32)
         for b in range(ws.max_blocks):
             r = b * BLOCK
             if r < int(offs[-1]):
-                blk[b] = int(torch.searchsorted(offs, torch.tensor(r), right=True)) - 1
+                e = int(torch.searchsorted(offs, torch.tensor(r), right=True)) - 1
+                blk[b] = e
+                rows[b] = min(BLOCK, int(counts[e]) - (r - int(offs[e])))
         ws.blk_group.copy_(blk)
+        ws.blk_rows.copy_(rows)
         return
     parts = 0 if row_ss is None else (row_ss.shape[1] if row_ss.dim() > 1 else 1)
     rc = nv.lib().gllm_moe_permute(x.data_ptr(), nv.ptr(row_ss), parts, ids.data_ptr(), T, k, H, e0, e_local,

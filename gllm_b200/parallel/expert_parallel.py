@@ -104,7 +104,9 @@ class EPContext:
         self.ss_recv.fill_(1.0)
         z = lambda n, dt=torch.int32: torch.zeros(n, dtype=dt, device=self.device)
         self.state, self.cta_done, self.cursors = z(1, torch.int64), z(1), z(E)
-        self.blk_group, self.total_rows = torch.full((self.max_blocks,), -1, dtype=torch.int32, device=self.device), z(1)
+        self._blk = torch.full((2 * self.max_blocks,), -1, dtype=torch.int32, device=self.device)
+        self.blk_group, self.blk_rows = self._blk[:self.max_blocks], self._blk[self.max_blocks:]   # expert / received rows per block
+        self.total_rows = z(1)
         d = _EpDesc()
         d.world, d.rank, d.num_experts, d.e_local, d.hidden, d.max_rows = self.size, self.rank, E, self.e_local, H, self.max_rows
         for r, base in enumerate(peers):
@@ -139,6 +141,7 @@ class EPContext:
 
     def grouped_scatter(self, act, w_down, rows):
         N, K = w_down.shape[0] // self.e_local, w_down.shape[1]
+        L.set_block_rows(self.blk_rows)
         rc = nv.lib().gllm_gemm_bf16_grouped_scatter(
             act.data_ptr(), act.stride(0), w_down.data_ptr(), w_down.stride(0), self.hidden, rows, N, K,
             self.blk_group.data_ptr(), self.e_local, 128, self.meta.data_ptr(),
@@ -168,6 +171,7 @@ class EPContext:
         rows = self.rows_bound()
         act = self.act_buffer(layer.inter)
         if getattr(layer, "bs_fmt", None) is None:
+            L.set_block_rows(self.blk_rows)
             L.gemm_glu(self.x_recv[:rows], layer.w_gate_up, act=model.act_id, out=act[:rows],
                        row_ss=self.ss_recv[:rows] if fused_norm else None, norm_dim=H if fused_norm else 0,
                        eps=c.rms_norm_eps if fused_norm else 0.0, bn=layer.glu_bn, mblk_group=self.blk_group,
@@ -199,10 +203,12 @@ class EPContext:
         B.quantize_act_rows(self.x_recv, fmt, xq, self.total_rows, tensor_scale=ts)
         xq.rows = rows
         rs = dict(row_ss=self.ss_recv[:rows], norm_dim=H, eps=c.rms_norm_eps) if fused_norm else {}
+        L.set_block_rows(self.blk_rows)
         B.gemm_glu(xq, layer.w_gate_up, act=model.act_id, out=act[:rows], bn=128, mblk_group=self.blk_group,
                    num_groups=self.e_local, **rs)
         B.quantize_act_rows(act, fmt, aq, self.total_rows, tensor_scale=ts)
         aq.rows = rows
+        L.set_block_rows(self.blk_rows)
         B.gemm_grouped_scatter(aq, layer.w_down, self.blk_group, self.e_local, ldo=self.hidden, scatter_meta=self.meta,
                                scatter_peers=self._y_peers, world=self.size)
 
