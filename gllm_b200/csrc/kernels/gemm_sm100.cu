@@ -31,6 +31,9 @@
 // that the producing kernel's epilogue left behind.
 #include <cuda_fp8.h>
 
+#include <atomic>
+#include <mutex>
+
 #include "common.cuh"
 
 extern "C" int gllm_sm_count();
@@ -2271,7 +2274,25 @@ struct SplitKWorkspace {
   long long scratch_floats = 0;
   unsigned int* barrier = nullptr;
 };
-static SplitKWorkspace g_splitk[64];
+static SplitKWorkspace g_splitk[64];          // per device: used by every stream without a workspace of its own
+// Streams with their own split-K scratch and barrier words (gllm_gemm_set_splitk_workspace_stream): GEMMs launched on
+// two such streams, or on one of them and on the default workspace, do not share a partial-sum buffer or a barrier,
+// so they may overlap. Append-only; readers take no lock.
+struct StreamWorkspace {
+  int dev;
+  cudaStream_t stream;
+  SplitKWorkspace ws;
+};
+constexpr int kMaxStreamWorkspaces = 16;
+static StreamWorkspace g_stream_ws[kMaxStreamWorkspaces];
+static std::atomic<int> g_stream_ws_n{0};
+static std::mutex g_stream_ws_mu;
+static const SplitKWorkspace& workspace_for(int dev, cudaStream_t stream) {
+  const int n = g_stream_ws_n.load(std::memory_order_acquire);
+  for (int i = 0; i < n; ++i)
+    if (g_stream_ws[i].dev == dev && g_stream_ws[i].stream == stream) return g_stream_ws[i].ws;
+  return g_splitk[dev & 63];
+}
 
 // Pick the number of K splits with a small cost model (microseconds): one SM pulls about 100 GB/s into
 // shared memory, work items run in waves of `sms`, a split costs the dump of its partial tile, and the
@@ -2390,7 +2411,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   int sms = max_ctas;
   if (sms <= 0) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = p.num_m * p.num_n;
-  const SplitKWorkspace& ws = g_splitk[dev & 63];
+  const SplitKWorkspace& ws = workspace_for(dev, stream);
   const long long tile_floats = static_cast<long long>(MT) * kBM * BN;
   const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
   int splits = 1;
@@ -2603,7 +2624,7 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
     return -1;
   }
   const int tiles = p.num_m * p.num_n;
-  const SplitKWorkspace& ws = g_splitk[dev & 63];
+  const SplitKWorkspace& ws = workspace_for(dev, stream);
   const long long tile_floats = 2ll * kBM * BN;
   const long long out_floats = static_cast<long long>(p.M) * p.num_n * BN;
   int splits = 1;
@@ -2766,6 +2787,38 @@ GLLM_API int gllm_gemm_set_splitk_workspace(float* scratch, long long scratch_fl
   ws.scratch = scratch;
   ws.scratch_floats = scratch ? scratch_floats : 0;
   ws.barrier = reinterpret_cast<unsigned int*>(counters);
+  return 0;
+}
+
+// The same for ONE stream of the current device: split-K GEMMs launched on `stream` (also while it captures a graph)
+// reduce through this scratch and meet at these barrier words instead of the device-wide ones. At most 16 streams;
+// registering a stream again replaces its workspace.
+GLLM_API int gllm_gemm_set_splitk_workspace_stream(void* stream, float* scratch, long long scratch_floats, int* counters,
+                                                   int num_counters) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (!scratch || !counters || num_counters < 2) {
+    set_last_error("split-K stream workspace needs scratch and at least two zeroed counters");
+    return -1;
+  }
+  std::lock_guard<std::mutex> lock(g_stream_ws_mu);
+  const int n = g_stream_ws_n.load(std::memory_order_relaxed);
+  int slot = -1;
+  for (int i = 0; i < n; ++i)
+    if (g_stream_ws[i].dev == dev && g_stream_ws[i].stream == static_cast<cudaStream_t>(stream)) slot = i;
+  if (slot < 0) {
+    if (n >= kMaxStreamWorkspaces) {
+      set_last_error("split-K stream workspaces: table full (%d)", kMaxStreamWorkspaces);
+      return -1;
+    }
+    slot = n;
+  }
+  g_stream_ws[slot].dev = dev;
+  g_stream_ws[slot].stream = static_cast<cudaStream_t>(stream);
+  g_stream_ws[slot].ws.scratch = scratch;
+  g_stream_ws[slot].ws.scratch_floats = scratch_floats;
+  g_stream_ws[slot].ws.barrier = reinterpret_cast<unsigned int*>(counters);
+  if (slot == n) g_stream_ws_n.store(n + 1, std::memory_order_release);
   return 0;
 }
 

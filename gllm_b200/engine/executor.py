@@ -528,8 +528,14 @@ class LLMEngine:
         return int(st.get("max_new_tokens", 1 << 30)) - int(st.get("num_generated", 0))
 
     def _capture(self, B: int):
-        # warm up outside capture so lazy initialisation (attribute setting, descriptor cache) is done
-        s = torch.cuda.Stream(device=self.device)
+        # One capture stream for all decode graphs, with its own split-K scratch and grid-barrier words: the GEMMs inside
+        # the graphs then share nothing with eager launches on other streams (prefill chunks), so the two may overlap.
+        # Warm up outside capture so lazy initialisation (attribute setting, descriptor cache) is done.
+        if getattr(self, "_graph_stream", None) is None:
+            from ..ops import _native as nv_
+            self._graph_stream = torch.cuda.Stream(device=self.device)
+            nv_.stream_splitk_workspace(self._graph_stream)
+        s = self._graph_stream
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             self._decode_body(B)

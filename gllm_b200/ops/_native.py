@@ -27,6 +27,7 @@ _SIGNATURES = {
     "gllm_gemm_bf16": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, I, I]),
     "gllm_gemm_bf16_softcap": (I, [P, L, P, L, P, L, I, I, I, I, P, P, I, F, F, I, P, F]),
     "gllm_gemm_set_splitk_workspace": (I, [P, L, P, I]),
+    "gllm_gemm_set_splitk_workspace_stream": (I, [P, P, L, P, I]),
     "gllm_gemm_bf16_residual": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I]),
     "gllm_gemm_set_pair": (I, [I, I]),
     "gllm_gemm_set_pair_big_m": (I, [I]),
@@ -239,8 +240,9 @@ _splitk_ws = {}
 
 
 def ensure_splitk_workspace(device, scratch_floats: int = 64 << 20, num_counters: int = 8192):
-    """Allocate (once per device) and register the scratch that split-K GEMMs reduce through.
-    It is shared by every GEMM on the device, so split-K GEMMs must run on one stream at a time."""
+    """Allocate (once per device) and register the scratch that split-K GEMMs reduce through. Every stream without a
+    workspace of its own shares it, so their split-K GEMMs must not overlap; ``stream_splitk_workspace`` gives a stream
+    its own."""
     import torch
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx in _splitk_ws:
@@ -253,6 +255,26 @@ def ensure_splitk_workspace(device, scratch_floats: int = 64 << 20, num_counters
             raise RuntimeError("could not register the split-K workspace")
     _splitk_ws[idx] = (scratch, counters)
     return _splitk_ws[idx]
+
+
+_stream_ws = {}
+
+
+def stream_splitk_workspace(stream, scratch_floats: int = 32 << 20, num_counters: int = 8192):
+    """Give ``stream`` (a torch.cuda.Stream) its own split-K scratch and barrier words: GEMMs launched on it, or
+    captured into a graph on it, then never share a partial-sum buffer or a grid barrier with GEMMs of other streams
+    (a prefill stream next to the decode graphs, for instance)."""
+    import torch
+    key = (stream.device.index, stream.cuda_stream)
+    if key in _stream_ws:
+        return _stream_ws[key]
+    with torch.cuda.device(stream.device):
+        scratch = torch.empty(scratch_floats, dtype=torch.float32, device=stream.device)
+        counters = torch.zeros(num_counters, dtype=torch.int32, device=stream.device)
+        check(lib().gllm_gemm_set_splitk_workspace_stream(stream.cuda_stream, scratch.data_ptr(), scratch_floats,
+                                                         counters.data_ptr(), num_counters), "gemm_set_splitk_workspace_stream")
+    _stream_ws[key] = (scratch, counters)
+    return _stream_ws[key]
 
 
 def ptr(t):

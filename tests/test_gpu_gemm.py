@@ -261,3 +261,28 @@ def test_gemm_qkv_fused_fp8_kv_cache(M, splits):
     got, ref = kv.float() * kv_scale, kv_ref.float() * kv_scale
     assert (got - ref).abs().max().item() <= 0.13 * ref.abs().max().item()      # at most one e4m3 step apart
     assert torch.nn.functional.cosine_similarity(got.flatten(), ref.flatten(), dim=0).item() > 0.999
+
+
+def test_split_k_gemms_on_two_streams_with_their_own_workspaces():
+    """A stream with its own split-K scratch and barrier words: split-K GEMMs launched on it overlap GEMMs of the default
+    workspace (another stream) and both give the right result, many times over."""
+    from gllm_b200.ops import _native as nv
+    torch.manual_seed(5)
+    M, N, K = 256, 4096, 4096
+    a1, w1 = _rand(M, K), _rand(N, K, scale=0.05)
+    a2, w2 = _rand(M, K), _rand(N, K, scale=0.05)
+    ref1, ref2 = a1.float() @ w1.float().t(), a2.float() @ w2.float().t()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    nv.stream_splitk_workspace(s1)
+    o1 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    o2 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    for _ in range(20):
+        with torch.cuda.stream(s1):
+            ops.gemm(a1, w1, out=o1, bn=128, splits=4)
+        with torch.cuda.stream(s2):
+            ops.gemm(a2, w2, out=o2, bn=128, splits=4)
+    torch.cuda.synchronize()
+    _close(o1, ref1)
+    _close(o2, ref2)
+    assert nv.device_error() == 0
