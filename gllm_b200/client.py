@@ -67,6 +67,8 @@ class ClientConfig:
     compute_dtype: str = "bf16"
     intent: str = "throughput"       # latency | throughput (arbiter input)
     seed: int = 0
+    kv_cache_dtype: str = "auto"     # bf16 | fp8 | auto (the KV decision matrix picks from what fits in HBM)
+    kv_scale: float = 0.05           # per-tensor scale of an fp8 KV cache
 
 
 @dataclass
@@ -223,8 +225,9 @@ class Client:
                     if kind in (ModelKind.EMBEDDING, ModelKind.RERANKER, ModelKind.CLASSIFIER) and cfg.num_labels == 0 \
                             and kind != ModelKind.EMBEDDING and kind != ModelKind.RERANKER:
                         raise InvalidModelTypeError(f"{model_id} has no classifier head")
+                    kv_kw = self._kv_cache_plan(cfg, dev)
                     model = DecoderModel(cfg, weights, device=dev, dtype=dt,
-                                         max_positions=min(cfg.max_position_embeddings, self.config.max_model_len))
+                                         max_positions=min(cfg.max_position_embeddings, self.config.max_model_len), **kv_kw)
                     ec = EngineConfig(max_num_seqs=self.config.max_num_seqs, max_model_len=self.config.max_model_len,
                                       max_batch_tokens=self.config.max_batch_tokens,
                                       prefill_chunk=self.config.max_batch_tokens,
@@ -240,6 +243,28 @@ class Client:
             except torch.cuda.OutOfMemoryError as e:  # pragma: no cover - needs a GPU
                 raise OutOfMemoryError(str(e)) from e
             self._state = _State(model_id, kind, loaded, model, engine, tokenizer, be)
+
+    def _kv_cache_plan(self, cfg, dev) -> dict:
+        """Precision of the KV cache for this model on this device. ``auto`` asks the KV decision matrix
+        (kv_cache/decision.py) whether the bf16 cache for max_num_seqs x max_model_len tokens fits beside the weights;
+        when it does not, or when the checkpoint asks for it, the cache is fp8 (e4m3), the low-precision tier the
+        attention kernels read directly. The chosen variant is kept in ``self.kv_plan``."""
+        from .kv_cache.decision import HardwareProfile, KvDecisionMatrix
+        pref = (self.config.kv_cache_dtype or "auto").lower()
+        hw = HardwareProfile()
+        if dev.type == "cuda":
+            hw = HardwareProfile(hbm_bytes=int(torch.cuda.get_device_properties(dev).total_memory))
+        tokens = self.config.max_num_seqs * self.config.max_model_len
+        bf16_per_token = cfg.kv_bytes_per_token() * (2 if cfg.kv_cache_dtype in ("fp8", "fp8_e4m3") else 1)
+        variant = KvDecisionMatrix(hw).choose(bf16_per_token * tokens, cfg.param_count() * 2,
+                                              long_context=self.config.max_model_len > 32768,
+                                              latency_sensitive=self.config.intent == "latency")
+        want_fp8 = pref in ("fp8", "fp8_e4m3") or (pref == "auto" and (variant.kivi or cfg.kv_cache_dtype in ("fp8", "fp8_e4m3")))
+        self.kv_plan = {"variant": variant, "kv_cache_dtype": "fp8" if want_fp8 and dev.type == "cuda" else "bf16",
+                        "bf16_bytes": bf16_per_token * tokens}
+        if want_fp8 and dev.type == "cuda" and not cfg.is_mla:
+            return dict(kv_dtype=torch.float8_e4m3fn, kv_scale=float(self.config.kv_scale))
+        return {}
 
     def unload_model(self):
         with self._lock:

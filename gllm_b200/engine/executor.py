@@ -179,6 +179,10 @@ class LLMEngine:
         self.gen = torch.Generator().manual_seed(ec.seed)
         self._all_greedy = True
         self._req_params: Dict[int, tuple] = {}
+        from ..scheduler.request_state import RequestStateTable
+        self.req_table = RequestStateTable(self.ms, self.device)
+        self._slot_of: Dict[int, int] = {}
+        self._req_limits: Dict[int, tuple] = {}
         self._vetoed: Dict[int, str] = {}
         self._spec_idx: Dict[int, object] = {}      # request -> n-gram index of its prompt + generated tokens
         self.spec_stats = dict(steps=0, drafted=0, accepted=0, emitted=0)
@@ -226,6 +230,7 @@ class LLMEngine:
             idx.extend(prompt_ids)
             self._spec_idx[rid] = idx
         self._req_params[rid] = (float(temperature), int(top_k), float(top_p))
+        self._req_limits[rid] = (int(max_tokens), int(eos[0]) if eos else -1)
         return rid
 
     submit = add_request
@@ -708,6 +713,7 @@ class LLMEngine:
             if it.start == 0 or self.slot_params[it.slot, 3] != float(it.seq_id):
                 sp = self._params_of(it.seq_id)
                 self.slot_params[it.slot] = (sp[0], sp[1], sp[2], float(it.seq_id))
+                self._bind_slot(int(it.seq_id), int(it.slot))
         dec_tokens = np.zeros(self.ms, np.int32)
         pf_tokens = np.zeros(0, np.int32)
         spec_extra = {}
@@ -803,6 +809,7 @@ class LLMEngine:
             if it.start == 0 or self.slot_params[it.slot, 3] != float(it.seq_id):
                 sp = self._params_of(it.seq_id)
                 self.slot_params[it.slot] = (sp[0], sp[1], sp[2], float(it.seq_id))
+                self._bind_slot(int(it.seq_id), int(it.slot))
         dec_tokens = np.zeros(self.ms, np.int32)
         pf_tokens = np.zeros(0, np.int32)
         if any_decode:
@@ -833,10 +840,32 @@ class LLMEngine:
     def _params_of(self, rid):
         return self._req_params.get(rid, (0.0, 0, 1.0))
 
+    def _bind_slot(self, rid: int, slot: int):
+        """The per-slot request record (scheduler/request_state.py: 32 bytes per slot in pinned memory, the table a
+        kernel or a monitoring thread can read) starts when a request's first prefill chunk gets its slot."""
+        old = self._slot_of.get(rid)
+        if old == slot:
+            return
+        generated = 0
+        if old is not None and int(self.req_table.rec[old]["request_id"]) == rid:
+            generated = int(self.req_table.rec[old]["generated"])      # a preempted request resumes in another slot
+            self.req_table.release(old)
+        self._slot_of[rid] = slot
+        p = self._req_limits.get(rid, (1 << 30, -1))
+        self.req_table.assign(slot, rid, p[0], p[1])
+        self.req_table.rec[slot]["generated"] = generated
+
+    def request_states(self):
+        """Snapshot of the live per-slot records (numpy structured array, one entry per slot)."""
+        return self.req_table.rec.copy()
+
     def _observe(self, rid: int, tok: int, now: float):
         st = self.reqs.get(rid)
         if st is None:
             return
+        slot = self._slot_of.get(rid)
+        if slot is not None:
+            self.req_table.advance(slot, tok)
         if st.n_out == 0:
             st.t_first = now
         st.t_last = now
@@ -850,6 +879,9 @@ class LLMEngine:
             decision = st.hook(rid, tok, st.n_out)
             if decision in ("veto", "terminate"):
                 self._vetoed[rid] = decision
+                if slot is not None:
+                    from ..scheduler.request_state import ExitFlag
+                    self.req_table.set_flag(slot, ExitFlag.VETO)
 
     def _collect(self) -> List[GenerateResult]:
         out = []
@@ -861,6 +893,10 @@ class LLMEngine:
                 self.kv_swap.forget(f.id)
                 self.kv_swap.drop(f.id)
             st = self.reqs.pop(f.id, None)
+            slot = self._slot_of.pop(f.id, None)
+            if slot is not None and int(self.req_table.rec[slot]["request_id"]) == f.id:
+                self.req_table.release(slot)
+            self._req_limits.pop(f.id, None)
             self._req_params.pop(f.id, None)
             self._spec_idx.pop(f.id, None)
             self._mtp_cand.pop(f.id, None)

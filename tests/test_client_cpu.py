@@ -126,3 +126,18 @@ def test_misc_api():
     c.unload_model()
     with pytest.raises(NoModelLoadedError):
         c.generate("x").generate()
+
+
+def test_kv_cache_plan_comes_from_the_decision_matrix():
+    """Client.load picks the KV cache precision through the decision matrix: a cache that fits stays bf16, one that does
+    not fit beside the weights asks for the low-precision variant (fp8 pages on a GPU)."""
+    import torch
+    from gllm_b200.client import Client, ClientConfig
+    from gllm_b200.models.config import preset
+    c = Client.__new__(Client)
+    c.config = ClientConfig(max_num_seqs=8, max_model_len=1024)
+    plan_kw = c._kv_cache_plan(preset("qwen3-8b"), torch.device("cpu"))
+    assert plan_kw == {} and c.kv_plan["kv_cache_dtype"] == "bf16" and not c.kv_plan["variant"].kivi
+    c.config = ClientConfig(max_num_seqs=4096, max_model_len=131072)      # 74 TB of bf16 KV: cannot fit
+    c._kv_cache_plan(preset("qwen3-8b"), torch.device("cpu"))
+    assert c.kv_plan["variant"].kivi and c.kv_plan["bf16_bytes"] > 180 << 30

@@ -311,3 +311,31 @@ def test_decoder_weights_live_in_one_blob():
     la = a.forward(fb(), a.alloc_kv_cache(2))
     lb = b.forward(fb(), b.alloc_kv_cache(2))
     torch.testing.assert_close(la, lb)
+
+
+def test_engine_keeps_the_per_slot_request_table():
+    """LLMEngine mirrors every running request in the 32-byte-per-slot record table (phase, counters, exit flags): the
+    record appears with the first prefill chunk, advances with every token and is released when the request ends."""
+    import torch
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.scheduler.request_state import Phase
+    cfg = preset("tiny-qwen3")
+    model = DecoderModel(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=2, std=0.05), device="cpu",
+                         dtype=torch.float32, max_positions=128)
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=4, max_model_len=64, max_batch_tokens=64, num_pages=32))
+    a = eng.add_request([3, 4, 5, 6], max_tokens=5, temperature=0.0, eos_ids=[])
+    b = eng.add_request([7, 8, 9], max_tokens=2, temperature=0.0, eos_ids=[])
+    eng.step()          # prefill: both get a slot and their first token
+    rec = eng.request_states()
+    live = {int(r["request_id"]): r for r in rec if r["phase"] != Phase.IDLE}
+    assert set(live) == {a, b}
+    assert live[a]["generated"] == 1 and live[a]["max_tokens"] == 5 and live[a]["phase"] == Phase.DECODE
+    eng.step()
+    rec = eng.request_states()
+    assert [int(r["generated"]) for r in rec if int(r["request_id"]) == a and r["phase"] != Phase.IDLE] == [2]
+    done = eng.run_until_done()
+    assert {r.request_id for r in done} == {a, b}
+    assert all(r["phase"] == Phase.IDLE for r in eng.request_states())
