@@ -36,7 +36,7 @@ def save_sessions(engine, path: str) -> Dict[str, int]:
 
 def load_sessions(engine, path: str) -> Dict[str, int]:
     """Restores sessions into ``engine`` (same model geometry). Returns {session id: tokens restored}."""
-    snap = torch.load(path, map_location="cpu", weights_only=False)
+    snap = torch.load(path, map_location="cpu", weights_only=True)     # tensors, lists, dicts and scalars only
     if snap.get("version") != FORMAT_VERSION:
         raise ValueError("unknown session snapshot version")
     if tuple(snap["page_shape"]) != tuple(engine.kv_caches[0].shape[1:]) or snap["layers"] != len(engine.kv_caches):

@@ -449,3 +449,96 @@ def test_onnx_graph_import_recovers_fused_ops_and_names_anonymous_weights(tmp_pa
     prov = OnnxProvider(tmp_path / "enc.onnx", dtype=torch.float32)
     # MatMul weights are stored [in, out] in the export; the provider hands out [out, in]
     assert torch.equal(prov.get("L0.up_proj"), torch.from_numpy(inits[up]).t())
+
+
+def _ref_gllm_bytes(name=b"L0.q_proj", shape=(2, 4), payload=None, data_off=4096, rel=0, count=1, dir_off=64,
+                    meta_off=None, version=1, magic=0x4D4C4C47):
+    """A .gllm file in the reference's byte layout, field by field (header offsets 0/4/8/12/20/24/32/40, 72-byte
+    entries, names after the directory, MessagePack metadata, page-aligned data region)."""
+    import struct
+    import msgpack
+    payload = payload if payload is not None else torch.arange(8, dtype=torch.float32).numpy().tobytes()
+    strings_off = dir_off + 72 * count
+    meta = msgpack.packb({"config": {"arch": "llama"}}, use_bin_type=True)
+    meta_off = strings_off + len(name) if meta_off is None else meta_off
+    buf = bytearray(data_off + rel + len(payload))
+    struct.pack_into("<I", buf, 0, magic)
+    struct.pack_into("<I", buf, 4, version)
+    struct.pack_into("<I", buf, 8, 0)
+    struct.pack_into("<Q", buf, 12, meta_off)
+    struct.pack_into("<I", buf, 20, count)
+    struct.pack_into("<Q", buf, 24, dir_off)
+    struct.pack_into("<Q", buf, 32, data_off)
+    struct.pack_into("<I", buf, 40, 4096)
+    e = dir_off
+    struct.pack_into("<I", buf, e + 0, 0)               # name_offset
+    struct.pack_into("<H", buf, e + 4, len(name))       # name_len
+    buf[e + 6] = len(shape)                              # ndim
+    buf[e + 7] = 0                                       # dtype: F32
+    for i, d in enumerate(shape):
+        struct.pack_into("<Q", buf, e + 8 + 8 * i, d)
+    buf[e + 40] = 0                                      # quant_format: none
+    struct.pack_into("<Q", buf, e + 48, rel)             # data offset inside the data region
+    struct.pack_into("<Q", buf, e + 56, 0)               # compressed size
+    struct.pack_into("<Q", buf, e + 64, len(payload))    # original size
+    buf[strings_off:strings_off + len(name)] = name
+    if meta_off + len(meta) <= data_off:
+        buf[meta_off:meta_off + len(meta)] = meta
+    buf[data_off + rel:data_off + rel + len(payload)] = payload
+    return bytes(buf)
+
+
+def test_gllm_reference_layout_byte_exact_and_bounds_checks(tmp_path):
+    """The reader takes a file laid out byte for byte as the reference writes it, and refuses files whose directory,
+    names, metadata or payloads leave the file, whose names repeat, or whose magic / version are wrong."""
+    from gllm_b200.loader.gllm_format import GllmFile, GllmFormatError, write_gllm
+    p = tmp_path / "ref.gllm"
+    p.write_bytes(_ref_gllm_bytes())
+    f = GllmFile(p)
+    assert f.layout == "reference" and f.page_size == 4096 and f.metadata["config"]["arch"] == "llama"
+    torch.testing.assert_close(f.tensor("L0.q_proj"), torch.arange(8, dtype=torch.float32).reshape(2, 4))
+    bad = {
+        "magic": _ref_gllm_bytes(magic=0xBADBAD),
+        "version": _ref_gllm_bytes(version=99),
+        "directory": _ref_gllm_bytes(count=1000),
+        "payload": _ref_gllm_bytes(rel=1 << 20)[:8192],
+        "names": _ref_gllm_bytes(name=b"x" * 5000),
+        "metadata": _ref_gllm_bytes(meta_off=1 << 30),
+        "short": b"GLLM",
+    }
+    for what, raw in bad.items():
+        q = tmp_path / f"bad_{what}.gllm"
+        q.write_bytes(raw)
+        with pytest.raises(GllmFormatError):
+            GllmFile(q)
+    # the writer produces the same layout: header fields at the reference's offsets, 72-byte entries
+    import struct
+    w = tmp_path / "w.gllm"
+    write_gllm(w, {"a": torch.ones(3, 5, dtype=torch.bfloat16), "b": torch.arange(4, dtype=torch.int32)}, {"k": 1})
+    raw = w.read_bytes()
+    assert struct.unpack_from("<I", raw, 0)[0] == 0x4D4C4C47 and struct.unpack_from("<I", raw, 4)[0] == 1
+    assert struct.unpack_from("<I", raw, 20)[0] == 2 and struct.unpack_from("<Q", raw, 24)[0] == 64
+    data_off = struct.unpack_from("<Q", raw, 32)[0]
+    assert data_off % 4096 == 0 and raw[64 + 7] == 2 and raw[64 + 6] == 2          # first entry: bf16, two dimensions
+    g = GllmFile(w)
+    assert g.metadata == {"k": 1} and g.tensor("b").tolist() == [0, 1, 2, 3] and g.tensor("a").dtype == torch.bfloat16
+
+
+def test_gllm_private_layout_still_reads(tmp_path):
+    """Files written by earlier versions of this package (magic "GLLMB200") are still readable."""
+    import msgpack
+    from gllm_b200.loader.gllm_format import PRIVATE_ENTRY, PRIVATE_HEADER, PRIVATE_MAGIC, GllmFile
+    t = torch.arange(6, dtype=torch.float32)
+    name, meta = b"final_norm", msgpack.packb({"v": 2}, use_bin_type=True)
+    eoff = PRIVATE_HEADER.size
+    soff = eoff + PRIVATE_ENTRY.size
+    moff = soff + len(name)
+    doff = (moff + len(meta) + 255) // 256 * 256
+    raw = PRIVATE_HEADER.pack(PRIVATE_MAGIC, 1, 1, eoff, soff, len(name), moff, len(meta), doff)
+    raw += PRIVATE_ENTRY.pack(0, len(name), 100, 1, 0, 6, 0, 0, 0, 0, 24) + name + meta
+    raw += b"\0" * (doff - len(raw)) + t.numpy().tobytes()
+    p = tmp_path / "old.gllm"
+    p.write_bytes(raw)
+    f = GllmFile(p)
+    assert f.layout == "private" and f.metadata == {"v": 2}
+    torch.testing.assert_close(f.tensor("final_norm"), t)
