@@ -373,6 +373,101 @@ __device__ __forceinline__ void attend_page_t(const uint32_t (&qt)[8][2], uint32
   }
 }
 
+// The same for fp8 (e4m3) pages, on f16 MMAs. A 16-byte shared-memory chunk holds 16 features, so ldmatrix hands a thread
+// four consecutive features (4t .. 4t + 3) of a token: the contraction index of the S^T product is permuted inside each
+// 16-feature block (MMA k = 2t, 2t + 1 <-> features 4t, 4t + 1; k = 2t + 8, 2t + 9 <-> features 4t + 2, 4t + 3) and the
+// Q^T fragments are loaded in the same order. A transposed 8 x 8 b16 matrix of V hands a thread the bytes {token 2t:
+// features 2g, 2g + 1 | token 2t + 1: features 2g, 2g + 1}: bytes 0, 2 are an A fragment of the even features, bytes
+// 1, 3 of the odd ones, so a 32-feature span gives two MMA row tiles: rows g / g + 8 of tile 2i + e are the features
+// 32 i + 2g + e and 32 i + 16 + 2g + e.
+__device__ __forceinline__ void load_qT_frags8(const __nv_bfloat16* qb, int group, uint32_t (&qt)[8][2]) {
+  const int g = (threadIdx.x & 31) >> 2, t = threadIdx.x & 3;
+  const __nv_bfloat16* row = qb + g * kHD;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    const uint2 v = g < group ? *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4) : make_uint2(0u, 0u);
+    qt[ks][0] = bf16x2_to_f16x2(v.x);
+    qt[ks][1] = bf16x2_to_f16x2(v.y);
+  }
+}
+// Feature of accumulator register pair (c0, c1 | c2, c3) of row tile `mt` in the fp8 form.
+__device__ __forceinline__ int out_feature_t8(int mt, int half) {
+  const int g = (threadIdx.x & 31) >> 2;
+  return 32 * (mt >> 1) + 16 * half + 2 * g + (mt & 1);
+}
+__device__ __forceinline__ void attend_page_t8(const uint32_t (&qt)[8][2], uint32_t k_smem, uint32_t v_smem, int tok_base,
+                                               int lo, int hi, float scale_log2, float (&o)[8][4], SoftmaxStateT& st) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const int tok = (lane & 7) + (((lane >> 3) & 1) << 3);
+    const int csel = lane >> 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {      // chunks 2i and 2i + 1 = k-steps 2i and 2i + 1
+      const int chunk = 2 * i + csel;
+      const uint32_t addr = k_smem + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t r0, r1, r2, r3;        // (tokens 0-7, chunk 2i) (tokens 8-15, chunk 2i) (0-7, 2i + 1) (8-15, 2i + 1)
+      ldsm_x4(addr, r0, r1, r2, r3);
+      const uint32_t a0[4] = {e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r1 >> 16)};
+      const uint32_t a1[4] = {e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r2 >> 16), e4m3x2_to_f16x2(r3 >> 16)};
+      mma_f16_16816(sa, a0, qt[2 * i][0], qt[2 * i][1]);
+      mma_f16_16816(sb, a1, qt[2 * i + 1][0], qt[2 * i + 1][1]);
+    }
+  }
+  float s0 = (sa[0] + sb[0]) * scale_log2, s1 = (sa[1] + sb[1]) * scale_log2;
+  float s2 = (sa[2] + sb[2]) * scale_log2, s3 = (sa[3] + sb[3]) * scale_log2;
+  const int t0 = tok_base + g, t1 = t0 + 8;
+  if (t0 < lo || t0 >= hi) s0 = s1 = -INFINITY;
+  if (t1 < lo || t1 >= hi) s2 = s3 = -INFINITY;
+  float mxA = fmaxf(s0, s2), mxB = fmaxf(s1, s3);
+#pragma unroll
+  for (int d = 4; d <= 16; d <<= 1) {
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, d));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, d));
+  }
+  const float mnA = fmaxf(st.mA, mxA), mnB = fmaxf(st.mB, mxB);
+  const float msA = (mnA == -INFINITY) ? 0.f : mnA, msB = (mnB == -INFINITY) ? 0.f : mnB;
+  const float corrA = exp2f(st.mA - msA), corrB = exp2f(st.mB - msB);
+  const bool rescale = __any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f);
+  st.mA = mnA;
+  st.mB = mnB;
+  s0 = exp2f(s0 - msA);
+  s1 = exp2f(s1 - msB);
+  s2 = exp2f(s2 - msA);
+  s3 = exp2f(s3 - msB);
+  st.lA = st.lA * corrA + (s0 + s2);
+  st.lB = st.lB * corrB + (s1 + s3);
+  const uint32_t pb0 = movmatrix_trans(pack_f16x2(s0, s1));
+  const uint32_t pb1 = movmatrix_trans(pack_f16x2(s2, s3));
+  {
+    const int tok = (lane & 7) + ((lane >> 4) << 3);
+    const int csel = (lane >> 3) & 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int chunk = 2 * i + csel;
+      const uint32_t addr = v_smem + tok * 128 + ((chunk ^ (tok & 7)) << 4);
+      uint32_t r0, r1, r2, r3;        // (tokens 0-7, chunk 2i) (0-7, 2i + 1) (8-15, 2i) (8-15, 2i + 1)
+      ldsm_x4_t(addr, r0, r1, r2, r3);
+      if (rescale) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          o[2 * i + e][0] *= corrA;
+          o[2 * i + e][1] *= corrB;
+          o[2 * i + e][2] *= corrA;
+          o[2 * i + e][3] *= corrB;
+        }
+      }
+      const uint32_t ae[4] = {e4m3x2_to_f16x2(__byte_perm(r0, 0u, 0x4420)), e4m3x2_to_f16x2(__byte_perm(r1, 0u, 0x4420)),
+                              e4m3x2_to_f16x2(__byte_perm(r2, 0u, 0x4420)), e4m3x2_to_f16x2(__byte_perm(r3, 0u, 0x4420))};
+      const uint32_t ao[4] = {e4m3x2_to_f16x2(__byte_perm(r0, 0u, 0x4431)), e4m3x2_to_f16x2(__byte_perm(r1, 0u, 0x4431)),
+                              e4m3x2_to_f16x2(__byte_perm(r2, 0u, 0x4431)), e4m3x2_to_f16x2(__byte_perm(r3, 0u, 0x4431))};
+      mma_f16_16816(o[2 * i], ae, pb0, pb1);
+      mma_f16_16816(o[2 * i + 1], ao, pb0, pb1);
+    }
+  }
+}
+
 template <bool KV8>
 __device__ __forceinline__ void load_page_kv(const CUtensorMap* tmap, uint8_t* dst, uint64_t* bar, int page,
                                              int n_kv_heads, int kvh) {
@@ -461,7 +556,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
 
   // bf16 pages with at most 8 heads per group take the swapped form (tokens as MMA rows, heads as columns); fp8
   // pages and larger groups keep the heads as rows
-  constexpr bool kSwapOk = !KV8;
+  constexpr bool kSwapOk = true;
   const bool swapped = kSwapOk && p.group <= 8;
   // Q fragments: rows = the `group` q heads of this kv head (rows >= group are zero)
   uint32_t qf[8][4];
@@ -470,7 +565,8 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     const int r0 = lane >> 2, r1 = r0 + 8;
     const __nv_bfloat16* qb = p.q + (static_cast<long long>(b) * p.n_q_heads + kvh * p.group) * kHD;
     if (swapped) {
-      if constexpr (kSwapOk) load_qT_frags(qb, p.group, qt);
+      if constexpr (KV8) load_qT_frags8(qb, p.group, qt);
+      else load_qT_frags(qb, p.group, qt);
     } else {
       load_q_frags<KV8>(qb + r0 * kHD, qb + r1 * kHD, r0 < p.group, r1 < p.group, qf);
     }
@@ -522,7 +618,10 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     const uint32_t kaddr = smem_u32(my_ring + stg * 2 * kTile);
     const int tok_base = (p0 + warp + i * kDecWarps) * kPage;
     if (swapped) {
-      if constexpr (kSwapOk)
+      if constexpr (KV8)
+        attend_page_t8(qt, kaddr, kaddr + kTile, tok_base, first_tok, ctx, p.scale_log2,
+                       *reinterpret_cast<float(*)[8][4]>(&o[0][0]), stt);
+      else
         attend_page_t(qt, kaddr, kaddr + kTile, tok_base, first_tok, ctx, p.scale_log2,
                       *reinterpret_cast<float(*)[8][4]>(&o[0][0]), stt);
     } else {
@@ -556,10 +655,12 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodePar
     float* wB = wA + kHD;
 #pragma unroll
     for (int mt = 0; mt < 8; ++mt) {
-      wA[mt * 16 + g] = o[mt][0];
-      wB[mt * 16 + g] = o[mt][1];
-      wA[mt * 16 + g + 8] = o[mt][2];
-      wB[mt * 16 + g + 8] = o[mt][3];
+      const int d0 = KV8 ? out_feature_t8(mt, 0) : mt * 16 + g;
+      const int d1 = KV8 ? out_feature_t8(mt, 1) : mt * 16 + g + 8;
+      wA[d0] = o[mt][0];
+      wB[d0] = o[mt][1];
+      wA[d1] = o[mt][2];
+      wB[d1] = o[mt][3];
     }
     if (g == 0) {
       mml[(warp * 16 + 2 * t) * 2 + 0] = stt.mA;
