@@ -47,6 +47,10 @@ class LoaderConfig:
     gguf_file_filter: Optional[str] = None   # substring / regex picking one quantisation of a multi-file repo
     offline: bool = field(default_factory=lambda: os.environ.get("HF_HUB_OFFLINE", "0") == "1")
     dtype: torch.dtype = torch.bfloat16
+    static_compression: str = field(default_factory=lambda: os.environ.get("GLLM_STATIC_COMPRESSION", ""))
+    #   "" | "dead_columns": FFN neurons whose gate / up row or down column is zero are dropped when the layer is packed
+    device_weight_budget: Optional[int] = None    # bytes of device memory for weights: a tier plan is attached when set
+    host_weight_budget: int = 256 << 30
 
     @staticmethod
     def from_env() -> "LoaderConfig":
@@ -212,6 +216,20 @@ class LoadedModel:
     weights: TensorProvider
     tokenizer: Optional[object]
     features: Optional[arch_mod.ArchFeatures] = None
+    tier_plan: Optional[list] = None      # loader/weight_tier.py placements when a device budget was given
+
+    def plan_tiers(self, device_budget: int, host_budget: int = 256 << 30, bytes_per_element: int = 2):
+        """Which tensors stay on the device, which go to pinned host memory and which stay memory-mapped, for a device
+        budget in bytes (loader/weight_tier.py: attention, norms, router and embeddings always stay resident)."""
+        from .weight_tier import plan_weight_tiers
+        sizes = {}
+        for name, shape in self.weights.shapes.items():
+            n = 1
+            for d in shape:
+                n *= int(d)
+            sizes[name] = n * bytes_per_element
+        self.tier_plan = plan_weight_tiers(sizes, device_budget, host_budget)
+        return self.tier_plan
 
 
 class Loader:
@@ -268,7 +286,12 @@ class Loader:
                 tokenizer = TokenizerHandle.from_file(tj)
         if prov.quant_summary and not cfg.quant:
             cfg.quant = "+".join(sorted(prov.quant_summary))
-        return LoadedModel(path=path, format=fmt, config=cfg, weights=prov, tokenizer=tokenizer, features=feats)
+        if self.cfg.static_compression:
+            cfg.static_compression = self.cfg.static_compression
+        loaded = LoadedModel(path=path, format=fmt, config=cfg, weights=prov, tokenizer=tokenizer, features=feats)
+        if self.cfg.device_weight_budget is not None:
+            loaded.plan_tiers(self.cfg.device_weight_budget, self.cfg.host_weight_budget)
+        return loaded
 
     # ------------------------------------------------------------------------------------------
     def _config_for(self, root: Path, prov: TensorProvider) -> ModelConfig:

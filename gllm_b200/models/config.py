@@ -59,6 +59,7 @@ class ModelConfig:
     hidden_act: str = "silu"
     sliding_window: int = 0
     num_kv_shared_layers: int = 0      # trailing layers that reuse an earlier layer's KV cache (see kv_donor)
+    static_compression: str = ""       # "dead_columns": drop dead FFN neurons when a layer is packed (loader option)
     attention_pattern: Optional[List[int]] = None  # per layer: 1 = sliding, 0 = global
     attention_sinks: bool = False
     embedding_scale: float = 1.0

@@ -275,6 +275,11 @@ def pack_mlp(cfg: ModelConfig, src, prefix: str, rank: int, world: int, fused: b
     g = shard_tensor(prefix + "gate_proj", src.get(prefix + "gate_proj"), rank, world)
     u = shard_tensor(prefix + "up_proj", src.get(prefix + "up_proj"), rank, world)
     d = shard_tensor(prefix + "down_proj", src.get(prefix + "down_proj"), rank, world)
+    if getattr(cfg, "static_compression", "") == "dead_columns" and world == 1:
+        # load-time static compression (loader/static_compression.py): neurons that cannot contribute leave all three
+        # matrices; the kept count stays a multiple of 128 so that every tile width still divides it
+        from ..loader.static_compression import prune_dead_ffn_columns
+        g, u, d, _ = prune_dead_ffn_columns(g, u, d, multiple_of=128)
     inter = g.shape[0]
     if fused:
         # 256-wide tiles (128 gate + 128 up rows): a weight tile pulled into shared memory once serves

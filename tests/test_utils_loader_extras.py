@@ -86,3 +86,47 @@ def test_download_cli_offline(tmp_path, capsys, monkeypatch):
     assert str(d) in capsys.readouterr().out
     monkeypatch.setenv("HF_HUB_OFFLINE", "1")
     assert download_main(["org/absent", "--cache-dir", str(tmp_path)]) == 1
+
+
+def test_static_compression_and_tier_plan_are_wired_into_loading():
+    """``static_compression="dead_columns"`` drops dead FFN neurons when a layer is packed (same logits, narrower
+    matrices), and a loaded model can plan its weight tiers for a device budget."""
+    import torch
+    from gllm_b200.engine.batch import ForwardBatch
+    from gllm_b200.loader.loader import LoadedModel, WeightFormat
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    cfg.intermediate_size = 512
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    base_get = src.get
+
+    def get(name):              # neurons 128..383 of every FFN are dead: zero gate rows
+        t = base_get(name)
+        if name.endswith("gate_proj"):
+            t = t.clone()
+            t[128:384] = 0
+        return t
+    src.get = get
+    dense = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=64, weight_blob=False)
+    cfg2 = preset("tiny-qwen3")
+    cfg2.intermediate_size = 512
+    cfg2.static_compression = "dead_columns"
+    pruned = DecoderModel(cfg2, src, device="cpu", dtype=torch.float32, max_positions=64, weight_blob=False)
+    assert dense.layers[0].w_down.shape[1] == 512 and pruned.layers[0].w_down.shape[1] == 256
+    T = 7
+    i32 = dict(dtype=torch.int32)
+    fb = lambda: ForwardBatch(token_ids=torch.arange(T, **i32) + 5, positions=torch.arange(T, **i32),
+                              slot_mapping=torch.arange(T, **i32), block_tables=torch.arange(2, **i32)[None],
+                              ctx_lens=torch.tensor([T], **i32), q_start=torch.tensor([0], **i32),
+                              q_len=torch.tensor([T], **i32), max_q_len=T)
+    torch.testing.assert_close(pruned.forward(fb(), pruned.alloc_kv_cache(2)), dense.forward(fb(), dense.alloc_kv_cache(2)),
+                               rtol=1e-4, atol=1e-4)
+
+    class Shapes:
+        shapes = {"embed_tokens": (1000, 64), "L0.q_proj": (64, 64), "L0.gate_proj": (4096, 64), "L1.gate_proj": (4096, 64)}
+    lm = LoadedModel(path=None, format=WeightFormat.SAFETENSORS, config=cfg, weights=Shapes(), tokenizer=None)
+    plan = {p.name: p.tier for p in lm.plan_tiers(device_budget=700_000, host_budget=600_000)}
+    assert plan["embed_tokens"] == 1 and plan["L0.q_proj"] == 1          # always resident
+    assert sorted([plan["L0.gate_proj"], plan["L1.gate_proj"]]) == [1, 2]   # one fits on the device, one goes to the host
