@@ -1887,7 +1887,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-              if (p.ar_push) {
+              if (p.ar_ll) {
+                // low-latency form with several tiles per CTA (prefill sizes): the same self-validating words, stored
+                // by the epilogue warps tile after tile; the reduce and gather phases follow the tile loop
+                if (!p.ar_drop_flags) {
+                  const int rows_per = ar_rows_per(p);
+                  const int owner = m / rows_per, lrow = m - owner * rows_per;
+                  __nv_bfloat16* dst = ar_ll_recv(p, owner, static_cast<int>(ar_launch_s & 1ull)) +
+                                       (static_cast<long long>(ks * p.ar_world + p.ar_rank) * rows_per + lrow) * n_pad +
+                                       n_blk * BN + c * 32;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    uint4 w;
+                    w.x = ll_word(pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]));
+                    w.y = ll_word(pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]));
+                    w.z = ll_word(pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]));
+                    w.w = ll_word(pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]));
+                    st_volatile_u4(dst + j * 8, w);
+                  }
+                }
+              } else if (p.ar_push) {
                 // straight into the receive slots of the rank that owns this row (a peer store over NVLink)
                 store_bf16x32(ar_recv_slot(p, ks * p.ar_world + p.ar_rank, m, n_pad, n_blk * BN + c * 32), v);
               } else {
@@ -2206,7 +2225,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   if constexpr (BN % 128 == 0) {  // 192-wide tiles never split (their lanes would need 12-byte vectors)
     if (fused_ar && p.ar_ll) {
-      if constexpr (EPI == EPI_RESIDUAL && BN == 128) {
+      if constexpr (EPI == EPI_RESIDUAL) {
         GLLM_STAMP(threadIdx.x == 0, 7);     // tile sent
         const int parity = static_cast<int>(ar_launch_s & 1ull);
         ar_ll_reduce<BN>(p, parity, abort_flag);
@@ -2458,10 +2477,12 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     const long long n_pad = static_cast<long long>(p.num_n) * BN;
     const long long need = static_cast<long long>(p.ar_world) * splits * rows_per * n_pad * 2;
     const long long need_res = static_cast<long long>(p.M) * n_pad * 2;
+    // one parked tile per CTA (decode sizes), or any number of tiles per CTA without a local K split (prefill sizes)
     const bool parks = BN == 128 && park_allowed && part_fits && tiles * splits <= sms && p.mblk_group == nullptr;
-    if (!parks || need > p.ar_ll_recv_bytes || need_res > p.ar_ll_res_bytes || n_pad % 256 != 0) {
-      set_last_error("fused all-reduce (low latency): one 128-wide tile per CTA (%d tiles x %d splits on %d SMs), %lld "
-                     "receive bytes (have %lld), %lld result bytes (have %lld), padded width %% 256",
+    if ((!parks && splits != 1) || p.mblk_group != nullptr || need > p.ar_ll_recv_bytes ||
+        (!p.ar_rs_only && need_res > p.ar_ll_res_bytes) || n_pad % 256 != 0) {
+      set_last_error("fused all-reduce (low latency): %d tiles x %d splits on %d SMs, %lld receive bytes (have %lld), "
+                     "%lld result bytes (have %lld), padded width %% 256",
                      tiles, splits, sms, need, p.ar_ll_recv_bytes, need_res, p.ar_ll_res_bytes);
       return -1;
     }
@@ -2968,7 +2989,7 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_push(const void* A, long long lda
 // 0x80008000 in every word between launches (the caller fills them once, and again after a launch that timed out).
 GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, const void* B, long long ldb, void* out,
                                                   long long ldo, float* row_ss_out, int M, int N, int K,
-                                                  const float* bias, void* stream, int world, int rank,
+                                                  const float* bias, int bn, void* stream, int world, int rank,
                                                   void* mc_base, void* const* peer_base, long long region_bytes, long long recv_off,
                                                   long long recv_bytes, long long res_off, long long res_bytes,
                                                   unsigned long long* state) {
@@ -2993,7 +3014,7 @@ GLLM_API int gllm_gemm_bf16_residual_allreduce_ll(const void* A, long long lda, 
   p.ar_ll_res_off = res_off; p.ar_ll_res_bytes = res_bytes;
   p.ar_drop_flags = settings().ar_drop_flags;
   p.err = gllm_error_word();
-  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, 128, (cudaStream_t)stream, 0, 0);
+  return dispatch_gemm<EPI_RESIDUAL, false>(A, lda, B, ldb, N, p, bn == 256 ? 256 : 128, (cudaStream_t)stream, 0, 0);
 }
 
 // Reduce-scatter form of the low-latency fused kernel: out_shard[lrow] = sum_ranks(A @ B^T)[rank * ceil(M / W) + lrow]

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "gllm_gemm_set_pair_big_m": (I, [I]),
     "gllm_gemm_bf16_residual_allreduce": (I, [P, L, P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, I, I, P, P, P, P, P, L]),
     "gllm_gemm_bf16_residual_allreduce_push": (I, [P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, P, P, L, L, L, L, L, L, P]),
-    "gllm_gemm_bf16_residual_allreduce_ll": (I, [P, L, P, L, P, L, P, I, I, I, P, P, I, I, P, P, L, L, L, L, L, P]),
+    "gllm_gemm_bf16_residual_allreduce_ll": (I, [P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, P, P, L, L, L, L, L, P]),
     "gllm_gemm_bf16_residual_reduce_scatter": (I, [P, L, P, L, P, L, P, I, I, I, P, P, I, I, P, L, L, L, P]),
     "gllm_gemm_set_block_rows": (I, [P]),
     "gllm_gemm_set_allgather_input": (I, [P, L, P, L, I, I, P, P, L, L, L, P]),

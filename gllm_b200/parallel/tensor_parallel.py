@@ -20,7 +20,9 @@ or meetings at all. Every 32-bit word of the receive and result slots is either 
 bf16 negative zeros, which the writers replace by +0) or data; readers poll the data words themselves and put the
 sentinel back after reading, and two parity sets of slots alternate between launches. The finished rows go into
 every rank's result slots and each rank copies them into its ordinary activation tensor, computing the norm
-statistics on the way. Larger M (prefill) takes the push kernel.
+statistics on the way. At decode sizes every CTA holds one 128-wide tile (parked in shared memory, K split inside the
+rank); at prefill sizes the CTAs run several 256-wide tiles and their epilogue warps store the rows as the tiles
+retire, the reduce and gather phases follow the tile loop.
 
 ``pull`` (``gllm_gemm_bf16_residual_allreduce``): every rank stores its partial tiles in its own symmetric buffer,
 all ranks meet at an arrival counter, and every rank pulls the sum (``multimem.ld_reduce`` or peer loads), one-shot
@@ -59,7 +61,8 @@ class TPContext:
         self.requested_mode = mode
         self.mode = "nccl"
         self.form = "none"            # "ll" | "push" | "pull" once the fused kernel is set up
-        self.ll_max_tokens = min(1024, max_tokens)
+        self.ll_max_tokens = max_tokens          # the low-latency form takes every M the context was sized for
+        self.ag_max_tokens = min(1024, max_tokens)
         self.uses_multimem = False
         self.max_tokens = max_tokens
         self.hidden = hidden
@@ -94,7 +97,7 @@ class TPContext:
             nonlocal off
             lay[name] = (off, nbytes)
             off = _align(off + nbytes)
-        if self.form in ("push", "ll"):
+        if self.form == "push":
             recv_rows = max(T + 8, min(4 * (T + 8), 4160))     # room for K splits inside a rank at decode sizes
             take("recv", recv_rows * self.n_pad * 2)
             take("x", T * self.hidden * 2)
@@ -102,15 +105,17 @@ class TPContext:
                 take(name, T * parts * 4)
             take("flags", _FLAG_COUNT * 4)
             take("done", 64)
-            if self.form == "ll":
-                # one parity set: up to four K splits of every rank's partial rows / all finished rows
-                self._ll_recv_bytes = _align(4 * (self.ll_max_tokens + 8) * self.n_pad * 2)
-                self._ll_res_bytes = _align(self.ll_max_tokens * self.n_pad * 2)
-                take("ll_recv", 2 * self._ll_recv_bytes)
-                take("ll_res", 2 * self._ll_res_bytes)
-                # slots of the all-gather in front of a column-parallel GEMM (sequence-parallel activations)
-                self._ag_bytes = _align(self.ll_max_tokens * self.n_pad * 2)
-                take("ag_slots", 2 * self._ag_bytes)
+        elif self.form == "ll":
+            # one parity set of receive slots: every rank's partial rows, times up to four K splits at decode sizes
+            # (one split at prefill sizes); one parity set of result slots: all finished rows
+            recv_rows = max(4 * (min(T, 1024) + 8), T + 8)
+            self._ll_recv_bytes = _align(recv_rows * self.n_pad * 2)
+            self._ll_res_bytes = _align(T * self.n_pad * 2)
+            take("ll_recv", 2 * self._ll_recv_bytes)
+            take("ll_res", 2 * self._ll_res_bytes)
+            # slots of the all-gather in front of a column-parallel GEMM (sequence-parallel activations)
+            self._ag_bytes = _align(self.ag_max_tokens * self.n_pad * 2)
+            take("ag_slots", 2 * self._ag_bytes)
         else:
             take("pull", 3 * self.buf_elems * 2)
             take("counters", 64)
@@ -172,7 +177,7 @@ class TPContext:
         """Activation buffer and norm-statistics buffers inside the symmetric region, for a model whose residual
         stream the push kernel updates on every rank. None when the push form is not in use or ``tokens`` exceeds
         what the region was sized for."""
-        if self.mode != "fused" or self.form not in ("push", "ll") or tokens > self.max_tokens:
+        if self.mode != "fused" or self.form != "push" or tokens > self.max_tokens:
             return None
         parts = (self.hidden + 127) // 128
         return dict(x=self._view("x", torch.bfloat16, (self.max_tokens, self.hidden))[:tokens],
@@ -190,20 +195,22 @@ class TPContext:
         N = w.shape[0]
         k_ok = self.requested_mode != "auto" or K <= self.fused_max_k
         fused = self.mode == "fused" and not self.baseline and k_ok and N <= self.n_pad
-        if fused and self.form == "ll" and M <= self.ll_max_tokens and x.stride(0) * 2 % 16 == 0 and \
-                ((M + 127) // 128) * (self.n_pad // 128) <= self._sms:
+        if fused and self.form == "ll" and M <= self.ll_max_tokens and x.stride(0) * 2 % 16 == 0:
             parts = (N + 255) // 256
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
                 raise ValueError("row statistics buffer must be [tokens, parts] contiguous")
             lay = self._lay
+            # decode sizes: 128-wide tiles, one per CTA (parked in shared memory, local K split); prefill sizes: 256-wide
+            # tiles, several per CTA, rows stored by the epilogue warps as the tiles retire
+            one_per_cta = ((M + 127) // 128) * (self.n_pad // 128) <= self._sms
             rc = nv.lib().gllm_gemm_bf16_residual_allreduce_ll(
                 a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), x.data_ptr(), x.stride(0), ss.data_ptr(), M, N, K,
-                None, nv.stream_ptr(), self.size, self.rank, self._mc_base, ctypes.cast(self._peer_base, ctypes.c_void_p),
+                None, 128 if one_per_cta or N % 256 else 256, nv.stream_ptr(), self.size, self.rank, self._mc_base, ctypes.cast(self._peer_base, ctypes.c_void_p),
                 self._total, lay["ll_recv"][0], self._ll_recv_bytes, lay["ll_res"][0], self._ll_res_bytes, self._state.data_ptr())
             nv.check(rc, "gemm_bf16_residual_allreduce_ll")
             return ss
-        if fused and self.form in ("push", "ll") and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:
+        if fused and self.form == "push" and M <= self.max_tokens and x.stride(0) * 2 % 16 == 0:
             parts = (N + 255) // 256  # the fused kernel reports statistics per 256-column group
             ss = ss_out[:M, :parts]
             if not ss.is_contiguous():
@@ -267,7 +274,7 @@ class TPContext:
         lo, n_own = self.shard_rows(M)
         parts = (N + 255) // 256
         ss = ss_out[:max(n_own, 1), :parts]
-        fused = (self.mode == "fused" and self.form == "ll" and not self.baseline and M <= self.ll_max_tokens and
+        fused = (self.mode == "fused" and self.form == "ll" and not self.baseline and M <= min(self.ll_max_tokens, 1024) and
                  N <= self.n_pad and ((M + 127) // 128) * (self.n_pad // 128) <= self._sms and ss.is_contiguous())
         if fused:
             lay = self._lay

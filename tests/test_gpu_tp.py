@@ -44,6 +44,26 @@ def test_fused_allreduce_world1_protocol(mode):
     assert int(tp._state[1]) == 5  # five launches advanced the launch state five times
 
 
+def test_low_latency_allreduce_prefill_sizes_world1():
+    """The low-latency form with several tiles per CTA (M in the thousands: 256-wide tiles, rows stored by the epilogue
+    warps tile after tile), interleaved with a decode-sized launch, world size 1 on ordinary memory."""
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H = 1024
+    tp = single_gpu_context(dev, hidden=H, max_tokens=4096, mode="ll_p2p")
+    torch.manual_seed(6)
+    for it, (M, K) in enumerate([(4096, 512), (3000, 1024), (256, 512), (4096, 512), (2049, 256)]):
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(H, K, device=dev) * 0.05).to(torch.bfloat16)
+        x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+        ref = (a.float() @ w.float().t() + x.float()).to(torch.bfloat16)
+        ss_buf = torch.zeros(4096, H // 256, device=dev)
+        ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, None)
+        _rows_close(x, ref, f"launch {it} (M={M})")
+        torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-3, atol=1e-3)
+    assert int(tp._state[1]) == 5
+
+
 def test_push_allreduce_in_place_on_symmetric_buffers():
     """The serving path: x and the statistics live inside the symmetric region, nothing is staged."""
     from gllm_b200.parallel.tensor_parallel import single_gpu_context

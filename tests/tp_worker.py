@@ -20,12 +20,14 @@ def main():
     from gllm_b200.ops import _native as nv
     from gllm_b200.parallel.tensor_parallel import TPContext
     H = 2048
-    tp = TPContext(rank, world, dev, mode=mode, max_tokens=512, hidden=H)
+    tp = TPContext(rank, world, dev, mode=mode, max_tokens=2048, hidden=H)
     if mode != "nccl":
         assert tp.mode == "fused", getattr(tp, "setup_error", "")
     g = torch.Generator(device="cpu").manual_seed(7)
-    for it, (M, K) in enumerate([(256, 1024), (77, 512), (256, 1024), (512, 2048), (128, 2048), (64, 4096),
-                                   (256, 3072)]):
+    shapes = [(256, 1024), (77, 512), (256, 1024), (512, 2048), (128, 2048), (64, 4096), (256, 3072)]
+    if not mode.startswith("pull"):      # prefill sizes: several tiles per CTA (the pull form stays at decode sizes)
+        shapes += [(2048, 512), (1500, 1024), (256, 1024)]
+    for it, (M, K) in enumerate(shapes):
         a_full = torch.randn(M, K * world, generator=g).to(torch.bfloat16)
         w_full = (torch.randn(H, K * world, generator=g) * 0.05).to(torch.bfloat16)
         x0 = torch.randn(M, H, generator=g).to(torch.bfloat16)
@@ -33,8 +35,8 @@ def main():
         a = a_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
         w = w_full[:, rank * K:(rank + 1) * K].contiguous().to(dev)
         x = x0.clone().to(dev)
-        ss_buf = torch.zeros(512, H // 256, device=dev)
-        part = torch.empty(512, H, device=dev, dtype=torch.bfloat16)
+        ss_buf = torch.zeros(2048, H // 256, device=dev)
+        part = torch.empty(2048, H, device=dev, dtype=torch.bfloat16)
         ss = tp.gemm_allreduce_residual(a, w, x, ss_buf, part, bn=256)
         torch.cuda.synchronize()
         err = (x.float().cpu() - ref).abs().max().item()
@@ -44,7 +46,7 @@ def main():
         assert bad.numel() == 0, f"rank {rank} iter {it} mode {mode}: rows {bad[:8].tolist()} wrong"
         if it == 0:      # the same launch again gives the same bits (no race in the flag protocol)
             x2 = x0.clone().to(dev)
-            tp.gemm_allreduce_residual(a, w, x2, torch.zeros(512, H // 256, device=dev), part, bn=256)
+            tp.gemm_allreduce_residual(a, w, x2, torch.zeros(2048, H // 256, device=dev), part, bn=256)
             torch.cuda.synchronize()
             assert torch.equal(x2, x), f"rank {rank} mode {mode}: repeat differs"
         got = ss.reshape(M, -1).sum(-1).cpu()
