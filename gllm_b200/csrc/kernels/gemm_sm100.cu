@@ -1870,7 +1870,58 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
-      if (!p.cluster_sk && !p.park && (splits > 1 || fused_ar)) {
+      bool staged_ll = false;
+      if constexpr (EPI == EPI_RESIDUAL && MT == 1 && !PAIR && BN % 128 == 0) {
+        if (!p.cluster_sk && !p.park && fused_ar && p.ar_ll) {
+          // Low-latency form, several tiles per CTA: the tile's rows go to their owners' receive slots. A thread holds
+          // one ROW of the accumulator, so storing from registers would put 16 bytes of 32 different rows into every
+          // store instruction (16-byte NVLink writes: measured 80 GB/s). The warp transposes 32 rows x 128 columns
+          // through its 8 KB staging area instead and stores 256 contiguous bytes of a row per half warp.
+          finisher = false;
+          staged_ll = true;
+          const long long n_pad = static_cast<long long>(p.num_n) * BN;
+          const int rows_per = ar_rows_per(p);
+          const int parity = static_cast<int>(ar_launch_s & 1ull);
+          uint8_t* stg = smem + kStages * kStageBytes + 1024 + q * 8192;     // [32 rows][16 chunks of 16 bytes], swizzled
+          const int m_base = m_sup * kBM + q * 32;
+#pragma unroll 1
+          for (int h = 0; h < BN / 128; ++h) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(taddr0 + h * 128 + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 w;
+                w.x = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1])));
+                w.y = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3])));
+                w.z = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5])));
+                w.w = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7])));
+                *reinterpret_cast<uint4*>(stg + lane * 256 + (((c * 4 + j) ^ (lane & 15)) << 4)) = w;
+              }
+            }
+            __syncwarp();
+            if (!p.ar_drop_flags) {
+              const int chunk = lane & 15;
+#pragma unroll 1
+              for (int rr = 0; rr < 16; ++rr) {
+                const int row = 2 * rr + (lane >> 4);
+                const int m = m_base + row;
+                if (m >= p.M) continue;
+                const uint4 w = *reinterpret_cast<const uint4*>(stg + row * 256 + ((chunk ^ (row & 15)) << 4));
+                const int owner = m / rows_per, lrow = m - owner * rows_per;
+                __nv_bfloat16* dst = ar_ll_recv(p, owner, parity) +
+                                     (static_cast<long long>(p.ar_rank) * rows_per + lrow) * n_pad + n_blk * BN + h * 128 +
+                                     chunk * 8;
+                st_volatile_u4(dst, w);
+              }
+            }
+            __syncwarp();
+          }
+        }
+      }
+      if (!staged_ll && !p.cluster_sk && !p.park && (splits > 1 || fused_ar)) {
         finisher = false;
         const long long n_pad = static_cast<long long>(p.num_n) * BN;
         const long long ar_off = fused_ar ? static_cast<long long>(ar_launch_s & 1u) * p.ar_buf_elems : 0;
@@ -2417,10 +2468,14 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   }
   static bool attr_set[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
   auto kern = gemm_tn_kernel<BN, MT, EPI, FP8>;
+  // the residual kernels carry 32 KB of staging behind the barriers (four epilogue warps x 8 KB): the multi-tile
+  // low-latency all-reduce transposes its rows there
+  constexpr int kSmemLaunch = Cfg::kSmemBytes + ((EPI == EPI_RESIDUAL && MT == 1 && BN % 128 == 0) ? 32768 : 0);
+  static_assert(kSmemLaunch <= 232448 - 512, "dynamic shared memory beyond 227 KB");
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLaunch);
     if (e != cudaSuccess) {
       set_last_error("gemm: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
       return -1;
@@ -2525,7 +2580,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(items, 1, 1);
     cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.dynamicSmemBytes = kSmemLaunch;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -2557,7 +2612,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
   }
   p.park = (BN == 128 && park_allowed && (splits > 1 || p.ar_world > 0) && items <= grid && part_fits &&
             p.mblk_group == nullptr) ? 1 : 0;
-  cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, true, 0, ta, tb, ta32, p);
+  cudaError_t e = launch_kernel(kern, dim3(grid), dim3(kGemmThreads), kSmemLaunch, stream, true, 0, ta, tb, ta32, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     set_last_error("gemm launch failed: %s", cudaGetErrorString(e));
