@@ -736,12 +736,15 @@ class LLMEngine:
         now = time.perf_counter()
         ids = plan.dec_seq_ids
         # hooks / streaming observe the sampled tokens before they are committed
-        for sl in np.nonzero(ids >= 0)[0]:
+        live = np.nonzero(ids >= 0)[0]
+        self.req_table.advance_many(live, dec_tokens[live])       # the per-slot records, one vector update per step
+        for sl in live:
             self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
         k = 0
         handoff = []
         for it in plan.prefill:
             if it.last:
+                self.req_table.advance(int(it.slot), int(pf_tokens[k]))
                 self._observe(int(it.seq_id), int(pf_tokens[k]), now)
                 if self.cfg.pd_role == "prefill_only":
                     handoff.append((int(it.seq_id), int(pf_tokens[k])))
@@ -752,7 +755,10 @@ class LLMEngine:
         for rid, _ in handoff:                 # the decode side continues the request; it ends here
             self._vetoed[rid] = "handoff"
         for rid, toks in spec_extra.items():       # the accepted drafts beyond the first token, and the bonus token
+            slot = self._slot_of.get(rid)
             for t in toks:
+                if slot is not None:
+                    self.req_table.advance(slot, int(t))
                 self._observe(rid, int(t), now)
             self.batcher.commit_tokens(rid, [int(t) for t in toks])
         return self._collect()
@@ -827,11 +833,14 @@ class LLMEngine:
         self._check_device_status(plan)
         now = time.perf_counter()
         ids = plan.dec_seq_ids
-        for sl in np.nonzero(ids >= 0)[0]:
+        live = np.nonzero(ids >= 0)[0]
+        self.req_table.advance_many(live, dec_tokens[live])       # the per-slot records, one vector update per step
+        for sl in live:
             self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
         k = 0
         for it in plan.prefill:
             if it.last:
+                self.req_table.advance(int(it.slot), int(pf_tokens[k]))
                 self._observe(int(it.seq_id), int(pf_tokens[k]), now)
                 k += 1
         self.batcher.commit(plan, dec_tokens, pf_tokens)
@@ -863,9 +872,6 @@ class LLMEngine:
         st = self.reqs.get(rid)
         if st is None:
             return
-        slot = self._slot_of.get(rid)
-        if slot is not None:
-            self.req_table.advance(slot, tok)
         if st.n_out == 0:
             st.t_first = now
         st.t_last = now
@@ -879,6 +885,7 @@ class LLMEngine:
             decision = st.hook(rid, tok, st.n_out)
             if decision in ("veto", "terminate"):
                 self._vetoed[rid] = decision
+                slot = self._slot_of.get(rid)
                 if slot is not None:
                     from ..scheduler.request_state import ExitFlag
                     self.req_table.set_flag(slot, ExitFlag.VETO)

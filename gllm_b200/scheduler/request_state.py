@@ -59,6 +59,21 @@ class RequestStateTable:
             r["phase"] = Phase.FINISHED
         return int(r["exit_flags"])
 
+    def advance_many(self, slots, tokens):
+        """``advance`` for many slots at once (one decode step): numpy field arithmetic, no per-token Python work."""
+        if len(slots) == 0:
+            return
+        r = self.rec
+        slots = np.asarray(slots)
+        tokens = np.asarray(tokens)
+        r["generated"][slots] += 1
+        r["position"][slots] += 1
+        flags = r["exit_flags"][slots]
+        flags = flags | np.where(tokens == r["eos_token"][slots], int(ExitFlag.EOS), 0).astype(np.uint8)
+        flags = flags | np.where(r["generated"][slots] >= r["max_tokens"][slots], int(ExitFlag.LENGTH), 0).astype(np.uint8)
+        r["exit_flags"][slots] = flags
+        r["phase"][slots] = np.where(flags != 0, int(Phase.FINISHED), int(Phase.DECODE)).astype(np.uint8)
+
     def set_flag(self, slot: int, flag: ExitFlag):
         self.rec[slot]["exit_flags"] |= int(flag)
         self.rec[slot]["phase"] = Phase.FINISHED
