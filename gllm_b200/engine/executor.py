@@ -182,6 +182,12 @@ class LLMEngine:
         from ..scheduler.request_state import RequestStateTable
         self.req_table = RequestStateTable(self.ms, self.device)
         self._slot_of: Dict[int, int] = {}
+        # per-slot token counters and timestamps of the decode fast path: one vector update per step; requests with a
+        # hook, a stream callback or a draft index are the only ones that still get per-token Python work
+        self._sl_nout = np.zeros(self.ms, np.int64)
+        self._sl_tfirst = np.zeros(self.ms, np.float64)
+        self._sl_tlast = np.zeros(self.ms, np.float64)
+        self._sl_slow = np.zeros(self.ms, bool)
         self._req_limits: Dict[int, tuple] = {}
         self._vetoed: Dict[int, str] = {}
         self._spec_idx: Dict[int, object] = {}      # request -> n-gram index of its prompt + generated tokens
@@ -737,9 +743,7 @@ class LLMEngine:
         ids = plan.dec_seq_ids
         # hooks / streaming observe the sampled tokens before they are committed
         live = np.nonzero(ids >= 0)[0]
-        self.req_table.advance_many(live, dec_tokens[live])       # the per-slot records, one vector update per step
-        for sl in live:
-            self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
+        self._count_decode(live, ids, dec_tokens, now)
         k = 0
         handoff = []
         for it in plan.prefill:
@@ -834,9 +838,7 @@ class LLMEngine:
         now = time.perf_counter()
         ids = plan.dec_seq_ids
         live = np.nonzero(ids >= 0)[0]
-        self.req_table.advance_many(live, dec_tokens[live])       # the per-slot records, one vector update per step
-        for sl in live:
-            self._observe(int(ids[sl]), int(dec_tokens[sl]), now)
+        self._count_decode(live, ids, dec_tokens, now)
         k = 0
         for it in plan.prefill:
             if it.last:
@@ -856,10 +858,15 @@ class LLMEngine:
         if old == slot:
             return
         generated = 0
+        carried = (0, 0.0, 0.0)
         if old is not None and int(self.req_table.rec[old]["request_id"]) == rid:
             generated = int(self.req_table.rec[old]["generated"])      # a preempted request resumes in another slot
+            carried = (int(self._sl_nout[old]), float(self._sl_tfirst[old]), float(self._sl_tlast[old]))
             self.req_table.release(old)
         self._slot_of[rid] = slot
+        self._sl_nout[slot], self._sl_tfirst[slot], self._sl_tlast[slot] = carried
+        st = self.reqs.get(rid)
+        self._sl_slow[slot] = bool(st is not None and (st.hook is not None or st.stream is not None)) or rid in self._spec_idx
         p = self._req_limits.get(rid, (1 << 30, -1))
         self.req_table.assign(slot, rid, p[0], p[1])
         self.req_table.rec[slot]["generated"] = generated
@@ -868,24 +875,44 @@ class LLMEngine:
         """Snapshot of the live per-slot records (numpy structured array, one entry per slot)."""
         return self.req_table.rec.copy()
 
-    def _observe(self, rid: int, tok: int, now: float):
+    def _count_decode(self, live, ids, dec_tokens, now: float):
+        """One decode step's tokens: the per-slot record table and the token counters / timestamps as vector updates;
+        only the slots of requests that asked for per-token work (hook, stream, draft index) go through ``_observe``."""
+        self.req_table.advance_many(live, dec_tokens[live])
+        bound = live[self.req_table.rec["request_id"][live] == ids[live].astype(np.uint64)]
+        fresh = bound[self._sl_nout[bound] == 0]
+        self._sl_tfirst[fresh] = now
+        self._sl_tlast[bound] = now
+        self._sl_nout[bound] += 1
+        slow = live[self._sl_slow[live]] if len(bound) == len(live) else live
+        for sl in slow:
+            self._observe(int(ids[sl]), int(dec_tokens[sl]), now, counted=bool(self._slot_of.get(int(ids[sl])) == sl))
+
+    def _observe(self, rid: int, tok: int, now: float, counted: bool = False):
         st = self.reqs.get(rid)
         if st is None:
             return
-        if st.n_out == 0:
-            st.t_first = now
-        st.t_last = now
-        st.n_out += 1
+        slot = self._slot_of.get(rid)
+        if not counted:
+            if slot is not None:
+                if self._sl_nout[slot] == 0 and st.n_out == 0:
+                    self._sl_tfirst[slot] = now
+                self._sl_tlast[slot] = now
+                self._sl_nout[slot] += 1
+            else:
+                if st.n_out == 0:
+                    st.t_first = now
+                st.t_last = now
+                st.n_out += 1
         idx = self._spec_idx.get(rid)
         if idx is not None:
             idx.extend([tok])
         if st.stream is not None:
             st.stream(rid, tok)
         if st.hook is not None:
-            decision = st.hook(rid, tok, st.n_out)
+            decision = st.hook(rid, tok, st.n_out + (int(self._sl_nout[slot]) if slot is not None else 0))
             if decision in ("veto", "terminate"):
                 self._vetoed[rid] = decision
-                slot = self._slot_of.get(rid)
                 if slot is not None:
                     from ..scheduler.request_state import ExitFlag
                     self.req_table.set_flag(slot, ExitFlag.VETO)
@@ -902,6 +929,12 @@ class LLMEngine:
             st = self.reqs.pop(f.id, None)
             slot = self._slot_of.pop(f.id, None)
             if slot is not None and int(self.req_table.rec[slot]["request_id"]) == f.id:
+                if st is not None and self._sl_nout[slot]:      # fold the fast-path counters into the request's state
+                    st.t_first = st.t_first or float(self._sl_tfirst[slot])
+                    st.t_last = max(st.t_last, float(self._sl_tlast[slot]))
+                    st.n_out += int(self._sl_nout[slot])
+                self._sl_nout[slot] = 0
+                self._sl_slow[slot] = False
                 self.req_table.release(slot)
             self._req_limits.pop(f.id, None)
             self._req_params.pop(f.id, None)
