@@ -293,7 +293,7 @@ def main():
         engine.step()
         now = time.perf_counter()
         for rid, st in engine.reqs.items():
-            if st.n_out > 0 and rid not in first_token_at:
+            if st.t_first > 0 and rid not in first_token_at:
                 first_token_at[rid] = st.t_first - t_submit
         guard += 1
     ttft = sorted(first_token_at.values())

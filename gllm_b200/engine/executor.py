@@ -882,6 +882,10 @@ class LLMEngine:
         bound = live[self.req_table.rec["request_id"][live] == ids[live].astype(np.uint64)]
         fresh = bound[self._sl_nout[bound] == 0]
         self._sl_tfirst[fresh] = now
+        for sl in fresh:                      # first token produced by a decode step (a request imported after prefill)
+            st = self.reqs.get(int(ids[sl]))
+            if st is not None and not st.t_first:
+                st.t_first = now
         self._sl_tlast[bound] = now
         self._sl_nout[bound] += 1
         slow = live[self._sl_slow[live]] if len(bound) == len(live) else live
@@ -897,6 +901,7 @@ class LLMEngine:
             if slot is not None:
                 if self._sl_nout[slot] == 0 and st.n_out == 0:
                     self._sl_tfirst[slot] = now
+                    st.t_first = now          # time to first token is readable while the request still runs
                 self._sl_tlast[slot] = now
                 self._sl_nout[slot] += 1
             else:
