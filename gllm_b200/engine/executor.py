@@ -691,6 +691,18 @@ class LLMEngine:
         raise nv.DeviceStatusError(code, f"in engine step; {len(failed)} request(s) failed")
 
     # ------------------------------------------------------------------------------------------
+    @property
+    def coordinators(self):
+        """The engine's seams under the reference's coordinator names (dispatch, kv, compute, inference, model context,
+        observability): engine/coordinators.py. Built on first use."""
+        c = getattr(self, "_coordinators", None)
+        if c is None:
+            from ..parallel.config import PdRole
+            from .coordinators import Coordinators
+            role = {"prefill_only": PdRole.PREFILL_ONLY, "decode_only": PdRole.DECODE_ONLY}.get(self.cfg.pd_role, PdRole.COLLOCATED)
+            c = self._coordinators = Coordinators.of(self, pd_role=role, swap=getattr(self.kv_swap, "swap", None))
+        return c
+
     def step(self) -> List[GenerateResult]:
         """One scheduler iteration: decode replay for the running set, then one prefill chunk batch."""
         if self.cfg.pd_role == "decode_only" and getattr(self.pd_link, "nonblocking", False):
@@ -700,6 +712,11 @@ class LLMEngine:
             # memory is tight: the batcher's next victims follow the eviction policy, not "youngest first"
             running = [rid for rid in self.reqs if rid not in self.kv_swap.keys]
             self.batcher.set_victim_order(self.kv_swap.victim_order(running))
+        self._steps = getattr(self, "_steps", 0) + 1
+        if self._steps % 16 == 1:
+            # the observability coordinator samples the system state (free pages, fragmentation, queue depths) and
+            # hands it to the batcher's policy, as the reference's step loop does through its coordinators
+            self.coordinators.observability.capture()
         plan = self.batcher.schedule()
         self.stats["preemptions"] += len(plan.preempted)
         if self.kv_swap is not None:
