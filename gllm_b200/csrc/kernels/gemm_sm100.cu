@@ -176,6 +176,8 @@ struct GemmParams {
   char* ag_peer[8]; char* ag_mc;            // symmetric region bases (and the multicast mapping or null)
   long long ag_slot_off, ag_slot_bytes;     // bytes: offset of the slots in the region, size of one parity set
   unsigned long long* ag_state;             // local: [0] launch index (parity)
+  float* ag_ss_out;                         // optional [M, K / 256]: sums of squares of the gathered rows per 256 columns
+                                            // (the row statistics a fused-norm epilogue of the same GEMM reads)
   unsigned long long wait_ns, peer_wait_ns;   // limits of the bounded waits
   long long* trace;   // debugging aid (GLLM_TRACE builds): CTA 0 writes SM clock stamps of its phases here (9 slots)
   int* err;
@@ -220,7 +222,10 @@ __device__ __forceinline__ float row_scale_of(const GemmParams& p, int m) {
   if (p.row_ss_in == nullptr) return p.out_scale != 0.f ? p.out_scale : 1.0f;
   float ss = 0.f;
   const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
-  if ((p.ss_in_parts & 3) == 0 && (reinterpret_cast<uintptr_t>(p.row_ss_in) & 15) == 0) {
+  if (p.ag_ss_out != nullptr) {
+    // the statistics were written by this very launch (all-gather phase, other SMs): read them from L2
+    for (int i = 0; i < p.ss_in_parts; ++i) ss += __ldcg(src + i);
+  } else if ((p.ss_in_parts & 3) == 0 && (reinterpret_cast<uintptr_t>(p.row_ss_in) & 15) == 0) {
     for (int i = 0; i < p.ss_in_parts; i += 4) {   // 16-byte loads: a row has up to hidden/128 partial sums
       const float4 f = *reinterpret_cast<const float4*>(src + i);
       ss += (f.x + f.y) + (f.z + f.w);
@@ -237,7 +242,11 @@ __device__ __forceinline__ float row_scale_warp(const GemmParams& p, int m, int 
   if (p.row_ss_in == nullptr) return p.out_scale != 0.f ? p.out_scale : 1.0f;
   const float* src = p.row_ss_in + static_cast<long long>(m) * p.ss_in_parts;
   float ss = 0.f;
-  for (int i = lane; i < p.ss_in_parts; i += 32) ss += __ldg(src + i);
+  if (p.ag_ss_out != nullptr) {
+    for (int i = lane; i < p.ss_in_parts; i += 32) ss += __ldcg(src + i);
+  } else {
+    for (int i = lane; i < p.ss_in_parts; i += 32) ss += __ldg(src + i);
+  }
   ss = warp_sum(ss);
   return rsqrtf(ss * p.norm_inv_dim + p.norm_eps) * (p.out_scale != 0.f ? p.out_scale : 1.0f);
 }
@@ -1333,6 +1342,17 @@ __device__ bool ag_ll_phase(const GemmParams& p, int parity, volatile int* abort
       break;
     }
     *reinterpret_cast<uint4*>(p.ag_dst + static_cast<long long>(m) * p.ag_dst_ld + c0) = v;
+    if (p.ag_ss_out) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) p.ag_ss_out[static_cast<long long>(m) * groups + grp] = ss;
+    }
   }
   fence_proxy_async_global();   // the rows were written by ordinary stores and are read by TMA
   return all_ok;
@@ -2405,6 +2425,7 @@ struct PendingAllGather {
   void* peer[8] = {}; void* mc = nullptr;
   long long slot_off = 0, slot_bytes = 0;
   unsigned long long* state = nullptr;
+  float* ss_out = nullptr;
 };
 static thread_local PendingAllGather g_pending_ag;
 static thread_local const int* g_pending_block_rows = nullptr;
@@ -2428,6 +2449,7 @@ static int launch_gemm(const void* A, long long lda, const void* B, long long ld
     for (int r = 0; r < ag.world; ++r) p.ag_peer[r] = static_cast<char*>(ag.peer[r]);
     p.ag_mc = static_cast<char*>(ag.mc);
     p.ag_slot_off = ag.slot_off; p.ag_slot_bytes = ag.slot_bytes; p.ag_state = ag.state;
+    p.ag_ss_out = ag.ss_out;
     p.peer_wait_ns = static_cast<unsigned long long>(settings().peer_wait_ns);
   }
   constexpr int kElemsPerKB = FP8 ? 128 : 64;
@@ -2759,6 +2781,7 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
     const int pair_max_m = pair_max_m_setting();
     bool use_pair = p.M > 128 && p.M <= pair_max_m && ((g_pair_epi_mask >> EPI) & 1) && p.mblk_group == nullptr &&
                     p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0;
+    const bool ag_pending = g_pending_ag.active;      // the CTA-pair kernels have no all-gather phase
     if (EPI == EPI_GLU && g_pair_epi_mask != 0xF && bn < 192) use_pair = false;   // narrow GLU tiles: single CTAs win
     if (EPI == EPI_GLU && !use_pair && g_pair_max_m > 0 && p.M > 128 && p.M <= g_pair_max_m && bn >= 192 &&
         p.mblk_group == nullptr && p.ar_world == 0 && max_ctas <= 0) {
@@ -2775,6 +2798,7 @@ static int dispatch_gemm(const void* A, long long lda, const void* B, long long 
     if (EPI != EPI_QKV && bn == 256 && g_pair_big_m > 0 && p.M >= g_pair_big_m && p.mblk_group == nullptr &&
         p.ar_world == 0 && p.scatter_meta == nullptr && max_ctas <= 0)
       use_pair = true;
+    if (ag_pending) use_pair = false;
     if (use_pair) {
       if constexpr (EPI == EPI_GLU) {
         if (bn == 192) return launch_gemm_pair<192, EPI>(A, lda, B, ldb, b_rows, p, stream, 1);
@@ -3118,7 +3142,8 @@ GLLM_API int gllm_gemm_set_block_rows(const int* rows) {
 // launch counter owned by this all-gather site. The descriptor is consumed by the next launch, whatever its outcome.
 GLLM_API int gllm_gemm_set_allgather_input(const void* src, long long src_ld, void* dst, long long dst_ld, int world,
                                            int rank, void* mc_base, void* const* peer_base, long long region_bytes,
-                                           long long slot_off, long long slot_bytes, unsigned long long* state) {
+                                           long long slot_off, long long slot_bytes, unsigned long long* state,
+                                           float* ss_out) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world || !peer_base || !state || !src || !dst ||
       (slot_off & 15) || (slot_bytes & 15) || slot_off < 0 || slot_off + 2 * slot_bytes > region_bytes ||
       (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15) || (src_ld & 7) || (dst_ld & 7)) {
@@ -3132,6 +3157,7 @@ GLLM_API int gllm_gemm_set_allgather_input(const void* src, long long src_ld, vo
   for (int r = 0; r < world; ++r) ag.peer[r] = peer_base[r];
   ag.mc = mc_base;
   ag.slot_off = slot_off; ag.slot_bytes = slot_bytes; ag.state = state;
+  ag.ss_out = ss_out;     // optional [M, K / 256] floats: row statistics of the gathered rows, written before the main loop
   return 0;
 }
 

@@ -56,16 +56,27 @@ class Workspace:
         self.ss_a = sym["ss_a"] if sym else torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
         self.ss_b = sym["ss_b"] if sym else torch.zeros((T, self.parts), dtype=torch.float32, device=dev)
         self.partial = torch.zeros((T, H), dtype=dt, device=dev) if model.tp_size > 1 else None
+        if getattr(model, "sequence_parallel", False):
+            # sequence parallel: the residual stream lives as row shards (`xs`), `h` receives the gathered rows in front
+            # of the column-parallel GEMMs, statistics come per 256 columns from the gather / reduce-scatter kernels
+            per = (T + model.tp_size - 1) // model.tp_size
+            self.xs = torch.zeros((per, H), dtype=dt, device=dev)
+            self.ss_g = torch.zeros((T, H // 256), dtype=torch.float32, device=dev)
+            self.ss_s = torch.zeros((per, H // 256), dtype=torch.float32, device=dev)
 
 
 class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
                  quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0, expert_quant: Optional[str] = None,
-                 weight_blob: Optional[bool] = None):
+                 weight_blob: Optional[bool] = None, sequence_parallel: bool = False):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
-        ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage."""
+        ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage.
+        ``sequence_parallel``: between the tensor-parallel GEMMs the residual stream stays sharded by rows (each rank
+        keeps ceil(T / tp) rows): the row-parallel GEMMs end in a reduce-scatter instead of an all-reduce and the
+        column-parallel GEMMs gather their input rows first (dense bf16 layers of the fused path only)."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
+        self.sequence_parallel = bool(sequence_parallel) and tp is not None
         self.tp_rank = tp.rank if tp else 0
         self.tp_size = tp.size if tp else 1
         self.layer_ids = list(layers) if layers is not None else list(range(cfg.num_layers))
@@ -85,7 +96,11 @@ class DecoderModel:
         # the fused layer is the CUDA path; block-scaled models also run it on CPU tensors (every fused op has its fp32
         # restatement), so that the CPU model quantises the same activations as the GPU one and can serve as its oracle
         self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and (
-            self.device.type == "cuda" or self.bs_fmt is not None)
+            self.device.type == "cuda" or self.bs_fmt is not None or self.sequence_parallel)
+        if self.sequence_parallel and (not self.fused or self.bs_fmt is not None or cfg.is_mla or cfg.is_moe or
+                                       cfg.hidden_size % 256 != 0):
+            raise ValueError("sequence_parallel needs the fused dense bf16 layer (no MLA, MoE or block-scaled weights) and "
+                             "a hidden size that is a multiple of 256")
         if cfg.num_heads % self.tp_size or (cfg.num_kv_heads % self.tp_size and cfg.num_kv_heads >= self.tp_size) or (
                 cfg.num_kv_heads < self.tp_size and self.tp_size % cfg.num_kv_heads):
             # with fewer KV heads than ranks each KV head is replicated over tp / num_kv_heads ranks (pack_attention)
@@ -306,6 +321,10 @@ class DecoderModel:
     def forward(self, batch: ForwardBatch, kv_caches: List[torch.Tensor], *, hidden_in=None, decode_ws=None,
                 return_hidden: bool = False, capture_layers=None):
         """Returns fp32 logits [R, vocab_local_padded] on the last pipeline stage, else the hidden states."""
+        if self.sequence_parallel:
+            if capture_layers is not None:
+                raise ValueError("capture_layers is not available with sequence_parallel (no rank holds whole layers' rows)")
+            return self._forward_sp(batch, kv_caches, hidden_in=hidden_in, decode_ws=decode_ws, return_hidden=return_hidden)
         c = self.cfg
         T = batch.num_tokens
         ws = self.workspace(T)
@@ -413,6 +432,71 @@ class DecoderModel:
                                                          eps=c.rms_norm_eps, bn=256))
                 else:
                     self.last_mtp_logits.append(ops.gemm(hn, w, out_dtype=torch.float32, bn=256))
+        return logits
+
+    def _forward_sp(self, batch: ForwardBatch, kv_caches, *, hidden_in=None, decode_ws=None, return_hidden=False):
+        """The fused dense layer with the residual stream sharded by rows over the tensor-parallel ranks.
+
+        Per layer: [all-gather rows + QKV GEMM] -> attention -> [o_proj GEMM + reduce-scatter into the row shard]
+        -> [all-gather rows + gate/up GEMM] -> [down GEMM + reduce-scatter]. Each bracket is one kernel in the
+        low-latency form of the TP context (ordinary collectives otherwise). Against the all-reduce form a rank
+        receives (W-1)/W of the rows once per GEMM pair instead of twice, and the norm statistics are computed on the
+        gathered rows. The first layer reads the embedding rows, which every rank computes itself. Reference:
+        tp_reduce_scatter / tp_column_parallel_all_gather (src/engine/coordinator/compute.rs:148-164, 246-271)."""
+        c, tp = self.cfg, self.tp
+        T = batch.num_tokens
+        ws = self.workspace(T)
+        H = c.hidden_size
+        x, h, xs, ss_g = ws.x[:T], ws.h[:T], ws.xs, ws.ss_g[:T]
+        lo, n_own = tp.shard_rows(T)
+        tm = getattr(self, "op_timer", None)
+        mark = tm.mark if tm is not None else (lambda name: None)
+        mark("begin")
+        if self.first_stage and hidden_in is None:
+            ops.embed_gather(batch.token_ids, self.embed, scale=c.embedding_scale, out=x, ss_out=ws.ss0[:T])
+        else:
+            x.copy_(hidden_in)
+            ops.rmsnorm(x, None, c.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)
+        if n_own:
+            xs[:n_own].copy_(x[lo:lo + n_own])
+        a_in, ss_in = x, ws.ss0[:T]
+        for idx, (li, lw) in enumerate(zip(self.layer_ids, self.layers)):
+            shared = lw.kv_donor is not None
+            kv = kv_caches[(lw.kv_donor if shared else li) - self.layer_ids[0]]
+            slots = None if shared else batch.slot_mapping
+            if idx > 0:
+                tp.allgather_input(xs, h, ss_out=ss_g)      # consumed by the QKV GEMM below
+                a_in, ss_in = h, ss_g
+            ops.gemm_qkv(a_in, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv, slot_mapping=slots,
+                         positions=batch.positions, cos_t=self.cos, sin_t=self.sin, q_norm_w=lw.q_norm,
+                         k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps,
+                         bias=lw.qkv_bias, kv_scale=self.kv_scale)
+            mark("qkv_gemm")
+            self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+            mark("attention")
+            tp.gemm_reduce_scatter_residual(ws.attn[:T], lw.wo, xs, ws.ss_s, T)
+            mark("o_proj")
+            tp.allgather_input(xs, h, ss_out=ss_g)          # consumed by the gate/up GEMM below
+            inter = lw.w_down.shape[1]
+            glu_bn = 256 if (T > 1024 and lw.w_gate_up.shape[0] % 256 == 0) else lw.glu_bn
+            ops.gemm_glu(h, lw.w_gate_up, act=self.act_id, out=ws.act[:T, :inter], row_ss=ss_g, norm_dim=H,
+                         eps=c.rms_norm_eps, bn=glu_bn)
+            mark("gate_up_gemm")
+            tp.gemm_reduce_scatter_residual(ws.act[:T, :inter], lw.w_down, xs, ws.ss_s, T)
+            mark("down_proj")
+        tp.allgather_rows(xs, x, ss_out=ss_g)
+        if not self.last_stage or return_hidden:
+            return x
+        rows = batch.logits_rows
+        xr, sr = (x, ss_g) if rows is None else (x.index_select(0, rows), ss_g.index_select(0, rows))
+        logits = ops.gemm(xr, self.lm_head, out_dtype=torch.float32, row_ss=sr, norm_dim=H, eps=c.rms_norm_eps, bn=256,
+                          softcap=float(c.logit_softcap or 0.0))
+        mark("lm_head")
+        self.last_mtp_logits = []
+        if self.mtp_heads and getattr(batch, "want_mtp", False):
+            for w in self.mtp_heads:
+                self.last_mtp_logits.append(ops.gemm(xr, w, out_dtype=torch.float32, row_ss=sr, norm_dim=H,
+                                                     eps=c.rms_norm_eps, bn=256))
         return logits
 
     # ------------------------------------------------------------------------------------------

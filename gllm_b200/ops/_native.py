@@ -36,7 +36,7 @@ _SIGNATURES = {
     "gllm_gemm_bf16_residual_allreduce_ll": (I, [P, L, P, L, P, L, P, I, I, I, P, I, P, I, I, P, P, L, L, L, L, L, P]),
     "gllm_gemm_bf16_residual_reduce_scatter": (I, [P, L, P, L, P, L, P, I, I, I, P, P, I, I, P, L, L, L, P]),
     "gllm_gemm_set_block_rows": (I, [P]),
-    "gllm_gemm_set_allgather_input": (I, [P, L, P, L, I, I, P, P, L, L, L, P]),
+    "gllm_gemm_set_allgather_input": (I, [P, L, P, L, I, I, P, P, L, L, L, P, P]),
     "gllm_set_option": (L, [ctypes.c_char_p, L]),
     "gllm_get_option": (L, [ctypes.c_char_p]),
     "gllm_gemm_trace_enabled": (I, []),

@@ -297,34 +297,51 @@ class TPContext:
         ss[:n_own].copy_(sq.reshape(n_own, parts, 256).sum(-1))
         return ss
 
-    def allgather_input(self, a_shard, a_full):
+    def allgather_rows(self, a_shard, a_full, ss_out=None):
+        """Plain all-gather of row shards into ``a_full`` (no GEMM behind it), with the rows' sums of squares per 256
+        columns in ``ss_out`` when given."""
+        import torch.distributed as dist
+        M, K = a_full.shape
+        lo, n_own = self.shard_rows(M)
+        if self.size == 1:
+            a_full[:n_own].copy_(a_shard[:n_own])
+        else:
+            per = (M + self.size - 1) // self.size
+            buf = torch.zeros((self.size * per, K), dtype=a_full.dtype, device=a_full.device)
+            mine = torch.zeros((per, K), dtype=a_full.dtype, device=a_full.device)
+            mine[:n_own].copy_(a_shard[:n_own])
+            dist.all_gather_into_tensor(buf, mine, group=self.group)
+            a_full.copy_(buf[:M])
+        if ss_out is not None:
+            G = ss_out.shape[1]
+            sq = a_full.float().pow(2)
+            pad = G * 256 - K
+            if pad:
+                sq = torch.nn.functional.pad(sq, (0, pad))
+            ss_out[:M].copy_(sq.reshape(M, G, 256).sum(-1))
+        return a_full
+
+    def allgather_input(self, a_shard, a_full, ss_out=None):
         """Column-parallel GEMM over sequence-parallel activations: the NEXT GEMM op called with ``a_full`` ([M, K]
         local tensor) as its A operand first gathers the ranks' row shards (``a_shard``: this rank's
         ``shard_rows(M)`` rows) into it, inside the same kernel, while its first weight tiles are already in flight.
-        Without the fused form the rows are gathered here with an ordinary all-gather. Reference:
-        tp_column_parallel_all_gather (src/engine/coordinator/compute.rs:246-271)."""
+        Without the fused form the rows are gathered here with an ordinary all-gather. ``ss_out`` [M, K / 256] fp32
+        receives the gathered rows' sums of squares per 256 columns (written by the same kernel before its main loop,
+        so the GEMM may take it as its ``row_ss``). Reference: tp_column_parallel_all_gather
+        (src/engine/coordinator/compute.rs:246-271)."""
         M, K = a_full.shape
         lo, n_own = self.shard_rows(M)
         fused = (self.mode == "fused" and self.form == "ll" and not self.baseline and a_full.is_cuda and
-                 M * K * 2 <= self._ag_bytes and K % 256 == 0 and a_full.dtype == torch.bfloat16)
+                 M * K * 2 <= self._ag_bytes and K % 256 == 0 and a_full.dtype == torch.bfloat16 and
+                 (ss_out is None or (ss_out.is_contiguous() and ss_out.shape[1] == K // 256)))
         if fused:
             rc = nv.lib().gllm_gemm_set_allgather_input(
                 a_shard.data_ptr(), a_shard.stride(0), a_full.data_ptr(), a_full.stride(0), self.size, self.rank,
                 self._mc_base, ctypes.cast(self._peer_base, ctypes.c_void_p), self._total, self._lay["ag_slots"][0],
-                self._ag_bytes, self._ag_state.data_ptr())
+                self._ag_bytes, self._ag_state.data_ptr(), nv.ptr(ss_out))
             nv.check(rc, "gemm_set_allgather_input")
             return a_full
-        import torch.distributed as dist
-        if self.size == 1:
-            a_full[:n_own].copy_(a_shard[:n_own])
-            return a_full
-        per = (M + self.size - 1) // self.size
-        buf = torch.zeros((self.size * per, K), dtype=a_full.dtype, device=a_full.device)
-        mine = torch.zeros((per, K), dtype=a_full.dtype, device=a_full.device)
-        mine[:n_own].copy_(a_shard[:n_own])
-        dist.all_gather_into_tensor(buf, mine, group=self.group)
-        a_full.copy_(buf[:M])
-        return a_full
+        return self.allgather_rows(a_shard, a_full, ss_out)
 
     def reset(self):
         """Clear the flags, done words and launch state after a failed launch (collective: every rank calls it)."""

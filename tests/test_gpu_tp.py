@@ -147,6 +147,78 @@ def test_sequence_parallel_forms_world1_protocol():
     assert int(tp._ag_state[0]) == 4 and int(tp._state[1]) == 4
 
 
+def test_allgather_statistics_feed_the_gemm_of_the_same_launch():
+    """The all-gather phase writes the gathered rows' sums of squares per 256 columns; the GEMM behind it (same launch)
+    normalises its rows with them: QKV and GLU epilogues against the fp32 product of the normalised rows."""
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H = 1024
+    tp = single_gpu_context(dev, hidden=H, max_tokens=256, mode="ll_p2p")
+    torch.manual_seed(6)
+    for it, M in enumerate([256, 77, 129]):
+        x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+        w1 = (torch.randn(768, H, device=dev) * 0.05).to(torch.bfloat16)
+        a_full = torch.zeros(M, H, device=dev, dtype=torch.bfloat16)
+        ss = torch.zeros(M, H // 256, device=dev)
+        tp.allgather_input(x, a_full, ss_out=ss)
+        mid = ops.gemm(a_full, w1, bn=128, row_ss=ss, norm_dim=H, eps=1e-6)
+        torch.cuda.synchronize()
+        assert torch.equal(a_full, x)
+        torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=1e-4, atol=1e-3)
+        xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+        _rows_close(mid, xn @ w1.float().t(), f"normalised all-gather GEMM, launch {it}")
+    assert nv.device_error() == 0
+
+
+def test_sequence_parallel_decoder_world1_matches_plain_model():
+    """The sequence-parallel layer (gather + QKV, o_proj + scatter, gather + gate/up, down + scatter as four fused
+    kernels) with one rank against the ordinary fused layer: same logits, same cache."""
+    from gllm_b200.engine.batch import ForwardBatch
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    cfg = preset("tiny-qwen3")
+    cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim = 1024, 8, 2, 128
+    cfg.intermediate_size, cfg.num_layers, cfg.vocab_size = 2048, 3, 2048
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=5, std=0.04)
+    tp = single_gpu_context(dev, hidden=cfg.hidden_size, max_tokens=256, mode="ll_p2p")
+    sp = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=512, sequence_parallel=True)
+    plain = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, max_positions=512)
+
+    def i32(v):
+        return torch.as_tensor(v, dtype=torch.int32, device=dev)
+    for T in (256, 77, 1):
+        ids = ((torch.arange(T, dtype=torch.int32) * 7 + 3) % cfg.vocab_size).to(dev)
+        def batch():
+            return ForwardBatch(token_ids=ids, positions=i32(list(range(T))), slot_mapping=i32(list(range(T))),
+                                block_tables=i32([list(range(16))]), ctx_lens=i32([T]), q_start=i32([0]),
+                                q_len=i32([T]), max_q_len=T)
+        kv_a, kv_b = sp.alloc_kv_cache(16), plain.alloc_kv_cache(16)
+        got = sp.forward(batch(), kv_a).float()
+        want = plain.forward(batch(), kv_b).float()
+        torch.cuda.synchronize()
+        _rows_close(got, want, f"sequence-parallel logits, T={T}")
+        for a, b in zip(kv_a, kv_b):
+            torch.testing.assert_close(a.float(), b.float(), rtol=0.05, atol=0.05)
+    assert nv.device_error() == 0
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("mode", ["ll", "nccl"])
+def test_sequence_parallel_decoder_two_gpus(mode):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29871 + (mode == "ll")), os.path.join(ROOT, "tests", "sp_decoder_worker.py"),
+           mode]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_DECODER_WORKER_OK") == 2
+
+
 @pytest.mark.multigpu
 @pytest.mark.parametrize("mode", ["ll", "ll_p2p", "nccl"])
 def test_sequence_parallel_block_two_gpus(mode):

@@ -329,6 +329,17 @@ def test_tp4_dense_decoder_matches_unsplit_model_with_replicated_kv_heads(heads,
     assert r.stdout.count("TP_DENSE_WORKER_OK") == 4
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_sequence_parallel_decoder_matches_allreduce_and_unsplit_models(world):
+    """Residual stream sharded by rows between the tensor-parallel GEMMs (gloo ranks; uneven and empty shards)."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29860 + world), os.path.join(ROOT, "tests", "sp_decoder_worker.py"), "cpu"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("SP_DECODER_WORKER_OK") == world
+
+
 def test_lockstep_engines_with_expert_parallel_moe_match_unsplit_engine():
     """Two serving engines, each with its own requests, share the expert-parallel MoE; outputs equal the plain engine's."""
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
