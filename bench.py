@@ -45,6 +45,8 @@ def parse_args():
                     help="linear weights (and activations) block-scaled on the tensor cores")
     ap.add_argument("--expert-quant", default=None, choices=[None, "mxfp8", "nvfp4"], help="MoE expert weights block-scaled")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="tensor parallel with the residual stream sharded by rows (reduce-scatter / all-gather forms)")
     ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"],
                     help="fp8: e4m3 KV cache (half the KV bytes); not the headline configuration, reported as invalid for it")
     ap.add_argument("--op-breakdown", action="store_true",
@@ -203,7 +205,8 @@ def main():
     src = RandomWeights(cfg, dev, torch.bfloat16, seed=0)
     kv_kw = dict(kv_dtype=torch.float8_e4m3fn, kv_scale=0.05) if args.kv_dtype == "fp8" else {}
     model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, tp=tp, max_positions=max_len, layers=layers, ep=ep,
-                         weight_quant=args.weight_quant, expert_quant=args.expert_quant, **kv_kw)
+                         weight_quant=args.weight_quant, expert_quant=args.expert_quant,
+                         sequence_parallel=bool(args.sequence_parallel and tp is not None), **kv_kw)
     # data-parallel attention: every rank serves its own share of the requests
     conc_total = args.concurrency
     if ep_mode:
@@ -407,7 +410,7 @@ def main():
                        "parallelism": (f"ep{world} experts + data-parallel attention" if ep_mode else
                                        f"tp{tp_size}" + (f"pp{pp_size}" if pp_size > 1 else "")), "kv_page": 16, "shared_prefix": args.shared_prefix,
                        "l2": "inputs larger than L2: every step streams all weights and the KV cache",
-                       "tp_form": getattr(tp, "form", "none"), "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
+                       "tp_form": getattr(tp, "form", "none"), "sequence_parallel": bool(getattr(model, "sequence_parallel", False)), "tp_mode": (getattr(tp, "mode", "none") + ("+multimem" if getattr(tp, "uses_multimem", False) else "")), "cuda_graphs": not args.no_graphs,
                        "layers": cfg.num_layers, "kv_dtype": args.kv_dtype,
                        "weight_quant": args.weight_quant, "expert_quant": args.expert_quant,
                        "valid": args.layers == 0 and (args.kv_dtype == "bf16" or args.model != "qwen3-8b")},

@@ -285,10 +285,19 @@ class TPContext:
             nv.check(rc, "gemm_bf16_residual_reduce_scatter")
             return ss
         import torch.distributed as dist
-        full = ops.gemm(a, w, out_dtype=torch.float32)
-        if self.size > 1:
-            dist.all_reduce(full, group=self.group)
-        mine = (full[lo:lo + n_own] + x_shard[:n_own].float()).to(x_shard.dtype)
+        if self.size > 1 and a.is_cuda:
+            # bf16 partial products, each rank receives only its rows of the sum (NCCL reduce-scatter)
+            per = (M + self.size - 1) // self.size
+            buf = torch.zeros((self.size * per, N), dtype=a.dtype, device=a.device)
+            ops.gemm(a, w, out=buf[:M])
+            got = torch.empty((per, N), dtype=a.dtype, device=a.device)
+            dist.reduce_scatter_tensor(got, buf, group=self.group)
+            mine = (got[:n_own].float() + x_shard[:n_own].float()).to(x_shard.dtype)
+        else:
+            full = ops.gemm(a, w, out_dtype=torch.float32)
+            if self.size > 1:      # gloo has no reduce-scatter
+                dist.all_reduce(full, group=self.group)
+            mine = (full[lo:lo + n_own] + x_shard[:n_own].float()).to(x_shard.dtype)
         x_shard[:n_own].copy_(mine)
         pad = parts * 256 - N
         sq = mine.float().pow(2)
