@@ -104,6 +104,10 @@ def mla_attention(model, w: MlaWeights, h, batch, cache, out):
     if batch.is_decode and h.is_cuda and d_c == 512 and rope_d == 64:
         lat = MLA.latent_decode(q_full, cache, batch.block_tables, batch.ctx_lens, n_heads=nh, scale=model.scale,
                                 max_ctx=model.max_positions)
+    elif h.is_cuda and d_c == 512 and rope_d == 64:
+        # prefill chunks on the same tensor-core kernel: one row = one query token over its sequence's pages
+        lat = MLA.latent_prefill(q_full, cache, batch.block_tables, row_seq, batch.positions, batch.ctx_lens, n_heads=nh,
+                                 scale=model.scale, causal=batch.causal and c.causal, max_ctx=model.max_positions)
     else:
         lat = MLA.latent_attention(q_full, cache, batch.block_tables, q_start, q_len, batch.ctx_lens, row_seq, n_heads=nh,
                                    d_v=d_c, scale=model.scale, causal=batch.causal and c.causal)

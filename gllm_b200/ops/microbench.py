@@ -276,6 +276,28 @@ def run(op: str, iters: int):
         fl = 2 * B * nh * ctx * (2 * d_c + d_r)
         out.update(shape=dict(batch=B, heads=nh, ctx=ctx, d_c=d_c, d_rope=d_r), us=t * 1e6, kv_gbs=byts / t / 1e9,
                    frac_of_hbm_peak=byts / t / 1e9 / hbm, tflops=fl / t / 1e12)
+    elif op == "mla_prefill":
+        # one prefill chunk of the absorbed attention: S prompts of L tokens, 16 heads (DeepSeek-V3 at eight ranks)
+        from . import mla as MLA
+        nh, d_c, d_r = 16, 512, 64
+        S, Lq = int(os.environ.get("GLLM_MLA_SEQS", 2)), int(os.environ.get("GLLM_MLA_LEN", 2048))
+        T = S * Lq
+        pages = T // 16
+        cache = rnd(pages, 16, d_c + d_r, scale=0.3)
+        q = rnd(T, nh * (d_c + d_r), scale=0.3)
+        bt = torch.arange(pages, device=dev, dtype=torch.int32).reshape(S, Lq // 16)
+        qs = torch.arange(S, device=dev, dtype=torch.int32) * Lq
+        ql = torch.full((S,), Lq, device=dev, dtype=torch.int32)
+        row_seq = torch.repeat_interleave(torch.arange(S, device=dev, dtype=torch.int32), Lq)
+        pos = torch.arange(Lq, device=dev, dtype=torch.int32).repeat(S)
+        o = torch.empty(T, nh * d_c, device=dev, dtype=torch.bfloat16)
+        if os.environ.get("GLLM_MLA_CUDA_CORES", "0") == "1":
+            t = _time(lambda: MLA.latent_attention(q, cache, bt, qs, ql, ql, row_seq, n_heads=nh, d_v=d_c, scale=0.04, out=o), iters)
+        else:
+            t = _time(lambda: MLA.latent_prefill(q, cache, bt, row_seq, pos, ql, n_heads=nh, scale=0.04, max_ctx=Lq, out=o), iters)
+        fl = 2 * S * nh * (Lq * (Lq + 1) // 2) * (2 * d_c + d_r)
+        out.update(shape=dict(seqs=S, len=Lq, heads=nh, d_c=d_c, d_rope=d_r), us=t * 1e6, tflops=fl / t / 1e12,
+                   frac_of_bf16_peak=fl / t / 1e12 / tf, cuda_cores=os.environ.get("GLLM_MLA_CUDA_CORES", "0") == "1")
     elif op in ("decode_attn", "prefill_attn"):
         nq, nkv, D = 32, 8, 128
         if op == "decode_attn":

@@ -103,7 +103,9 @@ def latent_decode(q, cache, block_tables, ctx_lens, *, n_heads, scale, max_ctx=4
                                 scale=scale, out=out)
     if out is None:
         out = torch.empty((B, n_heads * 512), dtype=q.dtype, device=q.device)
-    need = int(nv.lib().gllm_mla_decode_scratch_floats(B, n_heads, 16))
+    if splits <= 0 and B * ((n_heads + 15) // 16) >= 2 * int(nv.lib().gllm_sm_count()):
+        splits = 1          # the rows alone fill the GPU: no KV split, no scratch
+    need = int(nv.lib().gllm_mla_decode_scratch_floats(B, n_heads, 16 if splits <= 0 else splits))
     key = (q.device.index, need)
     sc = _decode_scratch.get(key)
     if sc is None:
@@ -113,3 +115,21 @@ def latent_decode(q, cache, block_tables, ctx_lens, *, n_heads, scale, max_ctx=4
                                   sc.data_ptr(), sc.numel(), nv.stream_ptr())
     nv.check(rc, "mla_decode")
     return out
+
+
+def latent_prefill(q, cache, block_tables, row_seq, positions, ctx_lens, *, n_heads, scale, causal=True, max_ctx=4096,
+                   out=None):
+    """Prefill rows of the absorbed attention on the tensor-core kernel of ``latent_decode``: every query row runs as
+    a one-token sequence whose context ends at its own position (causal) or at its sequence's end, over its
+    sequence's pages. The 16 heads of a tile still share every latent row they read; rows of one sequence re-read the
+    same pages, which stay in L2 (a 4 k-token prompt's latent rows are 4.7 MB). q [T, n_heads * 576] ->
+    [T, n_heads * 512]. ``row_seq`` [T] maps rows to sequences, ``positions`` [T] are the rows' absolute positions.
+    Reference parity: MlaAttention over the latent cache
+    (src/arch/auto_graph_fragments/build_graph.inc.rs:1527-1578)."""
+    tables = block_tables.index_select(0, row_seq.long())
+    if causal:
+        row_ctx = (positions + 1).to(torch.int32)
+    else:
+        row_ctx = ctx_lens.index_select(0, row_seq.long()).to(torch.int32)
+    return latent_decode(q, cache, tables.contiguous(), row_ctx.contiguous(), n_heads=n_heads, scale=scale,
+                         max_ctx=max_ctx, out=out)

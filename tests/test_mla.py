@@ -128,3 +128,29 @@ def test_mla_tensor_core_decode_matches_reference(n_heads, splits):
     torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=2e-2)
     from gllm_b200.ops import _native as nv
     assert nv.device_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [True, False])
+def test_mla_tensor_core_prefill_rows_match_reference(causal):
+    """Prefill chunks on the tensor-core kernel (one row per query token): whole prompts, a continued chunk whose
+    context is longer than its query, a single token; against the fp32 statement of the absorbed attention."""
+    dev = torch.device("cuda")
+    torch.manual_seed(5)
+    nh, pages = 16, 64
+    seqs = [(70, 70), (33, 120), (1, 47), (129, 129)]          # (q_len, ctx_len)
+    T = sum(s[0] for s in seqs)
+    q = (torch.randn(T, nh * 576) * 0.3).to(torch.bfloat16)
+    cache = (torch.randn(pages, 16, 576) * 0.5).to(torch.bfloat16)
+    bt = torch.stack([torch.randperm(pages)[:10] for _ in seqs]).to(torch.int32)
+    q_len = torch.tensor([s[0] for s in seqs], dtype=torch.int32)
+    ctx = torch.tensor([s[1] for s in seqs], dtype=torch.int32)
+    q_start = torch.cat([torch.zeros(1, dtype=torch.int32), q_len.cumsum(0)[:-1].to(torch.int32)])
+    row_seq = torch.repeat_interleave(torch.arange(len(seqs), dtype=torch.int32), q_len.long())
+    positions = torch.cat([torch.arange(c - l, c, dtype=torch.int32) for l, c in seqs])
+    want = MLA.latent_attention_ref(q.float(), cache.float(), bt, q_start, q_len, ctx, nh, 512, 0.06, causal=causal)
+    got = MLA.latent_prefill(q.to(dev), cache.to(dev), bt.to(dev), row_seq.to(dev), positions.to(dev), ctx.to(dev),
+                             n_heads=nh, scale=0.06, causal=causal)
+    torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=2e-2)
+    from gllm_b200.ops import _native as nv
+    assert nv.device_error() == 0
