@@ -1185,7 +1185,10 @@ __device__ void ar_ll_push_parked(const GemmParams& p, const float* part, int ro
     const int m = m_row0 + r;
     if (m >= p.M) continue;
     const int owner = m / rows_per, lrow = m - owner * rows_per;
-    const float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    float4 v = *reinterpret_cast<const float4*>(part + r * kClusterPartStride + lane * 4);
+    if (p.out_scale != 0.f) {      // block-scaled operands with per-tensor scales: the partial products carry them
+      v.x *= p.out_scale; v.y *= p.out_scale; v.z *= p.out_scale; v.w *= p.out_scale;
+    }
     __nv_bfloat16* dst = ar_ll_recv(p, owner, parity) + (static_cast<long long>(src) * rows_per + lrow) * n_pad + n_blk * 128 + lane * 4;
     st_volatile_u2(dst, ll_word(pack_bf16x2(v.x, v.y)), ll_word(pack_bf16x2(v.z, v.w)));
   }
@@ -1904,6 +1907,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int parity = static_cast<int>(ar_launch_s & 1ull);
           uint8_t* stg = smem + kStages * kStageBytes + 1024 + q * 8192;     // [32 rows][16 chunks of 16 bytes], swizzled
           const int m_base = m_sup * kBM + q * 32;
+          const float osc = p.out_scale != 0.f ? p.out_scale : 1.0f;
 #pragma unroll 1
           for (int h = 0; h < BN / 128; ++h) {
 #pragma unroll 1
@@ -1914,10 +1918,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint4 w;
-                w.x = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1])));
-                w.y = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3])));
-                w.z = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5])));
-                w.w = ll_word(pack_bf16x2(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7])));
+                w.x = ll_word(pack_bf16x2(osc * __uint_as_float(r[j * 8 + 0]), osc * __uint_as_float(r[j * 8 + 1])));
+                w.y = ll_word(pack_bf16x2(osc * __uint_as_float(r[j * 8 + 2]), osc * __uint_as_float(r[j * 8 + 3])));
+                w.z = ll_word(pack_bf16x2(osc * __uint_as_float(r[j * 8 + 4]), osc * __uint_as_float(r[j * 8 + 5])));
+                w.w = ll_word(pack_bf16x2(osc * __uint_as_float(r[j * 8 + 6]), osc * __uint_as_float(r[j * 8 + 7])));
                 *reinterpret_cast<uint4*>(stg + lane * 256 + (((c * 4 + j) ^ (lane & 15)) << 4)) = w;
               }
             }
@@ -1956,8 +1960,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tmem_ld_wait();
             if (m < p.M && fused_ar) {
               float v[32];
+              const float osc = p.out_scale != 0.f ? p.out_scale : 1.0f;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < 32; ++j) v[j] = osc * __uint_as_float(r[j]);
               if (p.ar_ll) {
                 // low-latency form with several tiles per CTA (prefill sizes): the same self-validating words, stored
                 // by the epilogue warps tile after tile; the reduce and gather phases follow the tile loop
@@ -2763,7 +2768,8 @@ static int launch_gemm_pair(const void* A, long long lda, const void* B, long lo
 template <int EPI, int OPM>
 static int dispatch_gemm_bs(const void* A, long long lda, const void* B, long long ldb, long long b_rows,
                             const GemmParams& p, int bn, cudaStream_t stream, int max_ctas, int force_splits) {
-  const bool rows2 = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr;
+  // the fused all-reduce keeps 128-row tiles (one parked tile per CTA at decode sizes, staged rows at prefill sizes)
+  const bool rows2 = p.M > 128 && p.M <= 1024 && p.mblk_group == nullptr && p.ar_world == 0;
   if constexpr (EPI != EPI_QKV) {
     if (bn == 256 && !rows2) return launch_gemm<256, 1, EPI, OPM>(A, lda, B, ldb, b_rows, p, stream, max_ctas, force_splits);
   }
@@ -3238,6 +3244,10 @@ struct GllmBsGemmArgs {
   const float* q_norm_w; const float* k_norm_w; float qk_eps; float kv_inv_scale;
   void* stream;
   const int* scatter_meta; void* const* scatter_peer; int scatter_world;   // EPI_STORE: rows scattered into peers
+  // EPI_RESIDUAL fused with the tensor-parallel all-reduce (low-latency form, GemmParams::ar_ll): `out` holds the
+  // residual on entry; ar_world == 0 = no all-reduce
+  int ar_world, ar_rank; void* ar_mc_base; void* const* ar_peer_base; long long ar_region_bytes;
+  long long ar_recv_off, ar_recv_bytes, ar_res_off, ar_res_bytes; unsigned long long* ar_state;
 };
 
 template <int OPM>
@@ -3266,6 +3276,27 @@ static int bs_gemm_call(const GllmBsGemmArgs& a) {
       return dispatch_gemm_bs<EPI_STORE, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
     case EPI_RESIDUAL:
       p.residual = static_cast<const __nv_bfloat16*>(a.residual); p.ldr = a.ldr; p.row_ss_out = a.row_ss_out;
+      if (a.ar_world > 0) {
+        if (a.ar_world > 8 || a.ar_rank < 0 || a.ar_rank >= a.ar_world || !a.ar_peer_base || !a.ar_state || !a.out ||
+            a.mblk_group) {
+          set_last_error("block-scaled gemm + all-reduce: bad world/rank/pointers (world %d rank %d)", a.ar_world, a.ar_rank);
+          return -1;
+        }
+        if ((a.ar_recv_off & 15) || (a.ar_res_off & 15) || (a.ar_recv_bytes & 15) || (a.ar_res_bytes & 15) ||
+            a.ar_recv_off < 0 || a.ar_res_off < 0 || a.ar_recv_off + 2 * a.ar_recv_bytes > a.ar_region_bytes ||
+            a.ar_res_off + 2 * a.ar_res_bytes > a.ar_region_bytes) {
+          set_last_error("block-scaled gemm + all-reduce: bad region layout");
+          return -1;
+        }
+        p.residual = static_cast<const __nv_bfloat16*>(a.out); p.ldr = a.ldo;
+        p.ar_world = a.ar_world; p.ar_rank = a.ar_rank; p.ar_mc_buf = static_cast<__nv_bfloat16*>(a.ar_mc_base);
+        for (int r = 0; r < a.ar_world; ++r) p.ar_peer_buf[r] = static_cast<__nv_bfloat16*>(a.ar_peer_base[r]);
+        p.ar_state = a.ar_state;
+        p.ar_ll = 1;
+        p.ar_ll_recv_off = a.ar_recv_off; p.ar_ll_recv_bytes = a.ar_recv_bytes;
+        p.ar_ll_res_off = a.ar_res_off; p.ar_ll_res_bytes = a.ar_res_bytes;
+        p.ar_drop_flags = settings().ar_drop_flags;
+      }
       return dispatch_gemm_bs<EPI_RESIDUAL, OPM>(a.a, a.lda, a.b, a.ldb, b_rows, p, a.bn, st, a.max_ctas, fs);
     case EPI_GLU:
       p.glu_act = a.glu_act;

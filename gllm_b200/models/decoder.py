@@ -292,7 +292,10 @@ class DecoderModel:
             ss = ss_out.reshape(-1)[:T * parts].view(T, parts)
             B.gemm_residual(aq, w, x, out=x, row_ss_out=ss, bn=bn)
             return ss
-        # tensor parallel: partial products on the tensor cores, the sum over ranks on NCCL
+        if aq.codes.is_cuda and hasattr(self.tp, "can_fuse_blockscaled") and self.tp.can_fuse_blockscaled(T, N):
+            # tensor parallel: the all-reduce runs in the GEMM's epilogue (low-latency form)
+            return self.tp.gemm_allreduce_residual_bs(aq, w, x, ss_out)
+        # tensor parallel without the fused form: partial products on the tensor cores, the sum over ranks on NCCL
         import torch.distributed as dist
         p = self._ws.partial[:T]
         B.gemm(aq, w, out=p, bn=128 if T <= 1024 else 256)

@@ -141,10 +141,11 @@ class BlockScaled:
 
     def dequantize(self) -> torch.Tensor:
         """fp32 [rows, K]: exactly the values the tensor core multiplies (times tensor_scale)."""
+        codes = self.codes[:self.rows]      # activation buffers are allocated for more rows than they hold
         if self.fmt == MXFP8:
-            v = e4m3_decode(self.codes)
+            v = e4m3_decode(codes)
         else:
-            v = e2m1_decode(unpack_nibbles(self.codes))
+            v = e2m1_decode(unpack_nibbles(codes))
         s = self.scales().repeat_interleave(self.vec, dim=1)
         return v * s * self.tensor_scale
 
@@ -315,7 +316,10 @@ class _Args(ctypes.Structure):
                 ("n_q_heads", nv.I), ("n_kv_heads", nv.I), ("q_out", nv.P), ("kv_cache", nv.P), ("num_pages", nv.I),
                 ("slot_mapping", nv.P), ("positions", nv.P), ("cos_table", nv.P), ("sin_table", nv.P), ("max_pos", nv.I),
                 ("q_norm_w", nv.P), ("k_norm_w", nv.P), ("qk_eps", nv.F), ("kv_inv_scale", nv.F), ("stream", nv.P),
-                ("scatter_meta", nv.P), ("scatter_peer", nv.P), ("scatter_world", nv.I)]
+                ("scatter_meta", nv.P), ("scatter_peer", nv.P), ("scatter_world", nv.I),
+                ("ar_world", nv.I), ("ar_rank", nv.I), ("ar_mc_base", nv.P), ("ar_peer_base", nv.P),
+                ("ar_region_bytes", nv.L), ("ar_recv_off", nv.L), ("ar_recv_bytes", nv.L), ("ar_res_off", nv.L),
+                ("ar_res_bytes", nv.L), ("ar_state", nv.P)]
 
 
 nv.register("gllm_gemm_blockscaled", ctypes.c_int, [ctypes.POINTER(_Args)])
@@ -426,6 +430,24 @@ def gemm_residual(a: BlockScaled, w: BlockScaled, residual, *, out=None, row_ss_
     g.residual, g.ldr, g.row_ss_out = residual.data_ptr(), residual.stride(0), row_ss_out.data_ptr()
     nv.check(nv.lib().gllm_gemm_blockscaled(ctypes.byref(g)), "gemm_blockscaled_residual")
     return out, row_ss_out
+
+
+def gemm_residual_allreduce(a: BlockScaled, w: BlockScaled, x, row_ss_out, *, bn: int, world: int, rank: int, mc_base,
+                            peer_base, region_bytes: int, recv_off: int, recv_bytes: int, res_off: int, res_bytes: int,
+                            state):
+    """x <- sum over ranks of (A @ W.T) + x in one kernel: the block-scaled row-parallel GEMM with the low-latency
+    all-reduce of ``parallel.tensor_parallel.TPContext`` in its epilogue (partials leave for the rows' owners as bf16,
+    per-tensor scales applied). ``row_ss_out`` [M, ceil(N / 256)] receives the sums of squares of the new rows."""
+    M, N = a.rows, w.rows
+    nv.ensure_splitk_workspace(a.device)
+    g = _base_args(a, w, M, N, EPI_RESIDUAL, bn, 0, 0)
+    g.out, g.ldo = x.data_ptr(), x.stride(0)
+    g.residual, g.ldr, g.row_ss_out = x.data_ptr(), x.stride(0), row_ss_out.data_ptr()
+    g.ar_world, g.ar_rank, g.ar_mc_base, g.ar_peer_base = world, rank, mc_base, peer_base
+    g.ar_region_bytes, g.ar_recv_off, g.ar_recv_bytes = region_bytes, recv_off, recv_bytes
+    g.ar_res_off, g.ar_res_bytes, g.ar_state = res_off, res_bytes, state
+    nv.check(nv.lib().gllm_gemm_blockscaled(ctypes.byref(g)), "gemm_blockscaled_residual_allreduce")
+    return row_ss_out
 
 
 def gemm_glu(a: BlockScaled, w_packed: BlockScaled, *, act=0, out=None, row_ss=None, norm_dim=0, eps=0.0, bn: int = 128,

@@ -257,6 +257,28 @@ class TPContext:
         ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
         return ss
 
+    def can_fuse_blockscaled(self, M: int, N: int) -> bool:
+        """Whether ``gemm_allreduce_residual_bs`` runs as one kernel for an [M, N] output."""
+        return (self.mode == "fused" and self.form == "ll" and not self.baseline and M <= self.ll_max_tokens and
+                N <= self.n_pad and N % 256 == 0)
+
+    def gemm_allreduce_residual_bs(self, aq, w, x, ss_out):
+        """Block-scaled (MXFP8 / NVFP4) row-parallel GEMM with the low-latency all-reduce in its epilogue:
+        x <- sum_ranks(aq @ w.T) + x; returns the row statistics [M, ceil(N / 256)] of the new x. ``aq`` / ``w`` are
+        ``ops.blockscale.BlockScaled`` operands. Callers check ``can_fuse_blockscaled`` first."""
+        from ..ops import blockscale as B
+        M, N = aq.rows, w.rows
+        parts = (N + 255) // 256
+        ss = ss_out.reshape(-1)[:M * parts].view(M, parts)
+        one_per_cta = ((M + 127) // 128) * (self.n_pad // 128) <= self._sms
+        lay = self._lay
+        B.gemm_residual_allreduce(
+            aq, w, x, ss, bn=128 if one_per_cta or N % 256 else 256, world=self.size, rank=self.rank,
+            mc_base=self._mc_base, peer_base=ctypes.cast(self._peer_base, ctypes.c_void_p), region_bytes=self._total,
+            recv_off=lay["ll_recv"][0], recv_bytes=self._ll_recv_bytes, res_off=lay["ll_res"][0],
+            res_bytes=self._ll_res_bytes, state=self._state.data_ptr())
+        return ss
+
     # ---- sequence-parallel forms: rows of the activations sharded over the ranks ----------------------------
     def shard_rows(self, M: int):
         """(first row, row count) of this rank's shard of an [M, ...] activation: rows [r * ceil(M / W), ...)."""

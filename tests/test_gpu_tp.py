@@ -147,6 +147,35 @@ def test_sequence_parallel_forms_world1_protocol():
     assert int(tp._ag_state[0]) == 4 and int(tp._state[1]) == 4
 
 
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_blockscaled_gemm_with_fused_allreduce_world1(fmt):
+    """The block-scaled row-parallel GEMM with the low-latency all-reduce in its epilogue, one rank: parked tiles at
+    decode sizes, staged rows at prefill sizes, per-tensor scales of NVFP4 carried by the partials; against the
+    block-scaled residual GEMM without the all-reduce and against fp32 on the dequantised operands."""
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.ops import blockscale as B
+    from gllm_b200.parallel.tensor_parallel import single_gpu_context
+    dev = torch.device("cuda")
+    H, K = 2048, 1024
+    tp = single_gpu_context(dev, hidden=H, max_tokens=2048, mode="ll_p2p")
+    torch.manual_seed(8)
+    w = B.quantize((torch.randn(H, K) * 0.05).to(torch.bfloat16), fmt).to(dev)
+    for it, M in enumerate([256, 77, 1500, 256]):
+        a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        aq = B.quantize_act(a, fmt, tensor_scale=1.0 / 64.0) if fmt == "nvfp4" else B.quantize_act(a, fmt)
+        x0 = torch.randn(M, H, device=dev).to(torch.bfloat16)
+        assert tp.can_fuse_blockscaled(M, H)
+        x = x0.clone()
+        ss = tp.gemm_allreduce_residual_bs(aq, w, x, torch.zeros(M, H // 128, device=dev))
+        want, _ = B.gemm_residual(aq, w, x0)
+        torch.cuda.synchronize()
+        _rows_close(x, want.float(), f"{fmt} launch {it} (M={M}) against the plain residual GEMM")
+        ref = aq.dequantize()[:M].float() @ w.dequantize().float().t() + x0.float()
+        _rows_close(x, ref, f"{fmt} launch {it} (M={M}) against fp32")
+        torch.testing.assert_close(ss.sum(-1), x.float().pow(2).sum(-1), rtol=2e-3, atol=2e-3)
+    assert nv.device_error() == 0
+
+
 def test_allgather_statistics_feed_the_gemm_of_the_same_launch():
     """The all-gather phase writes the gathered rows' sums of squares per 256 columns; the GEMM behind it (same launch)
     normalises its rows with them: QKV and GLU epilogues against the fp32 product of the normalised rows."""
@@ -205,6 +234,18 @@ def test_sequence_parallel_decoder_world1_matches_plain_model():
         for a, b in zip(kv_a, kv_b):
             torch.testing.assert_close(a.float(), b.float(), rtol=0.05, atol=0.05)
     assert nv.device_error() == 0
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_blockscaled_gemm_with_fused_allreduce_two_gpus(fmt):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29881 + (fmt == "nvfp4")), os.path.join(ROOT, "tests", "tp_bs_worker.py"),
+           "ll", fmt]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_BS_WORKER_OK" in r.stdout
 
 
 @pytest.mark.multigpu
