@@ -28,6 +28,7 @@ class ForwardBatch:
     token_type_ids: Optional[torch.Tensor] = None
     causal: bool = True
     want_mtp: bool = False           # also run the model's multi-token-prediction heads on the logits rows
+    cp: Optional[object] = None      # parallel.context_parallel.CpPrefill: exchange of KV pages before each attention
 
     @property
     def num_tokens(self) -> int:

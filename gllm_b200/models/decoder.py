@@ -261,6 +261,10 @@ class DecoderModel:
     # ------------------------------------------------------------------------------------------
     def _attention(self, q, kv, batch: ForwardBatch, out, layer: int, decode_ws):
         window = self.cfg.layer_window(layer)
+        cp = getattr(batch, "cp", None)
+        if cp is not None and self.layers[layer - self.layer_ids[0]].kv_donor is None:
+            # context-parallel prefill: the other ranks' shards of this layer's K/V arrive before the attention
+            cp.exchange(kv)
         if batch.is_decode:
             return ops.paged_decode(q, kv, batch.block_tables, batch.ctx_lens, n_q=self.n_q_local, n_kv=self.n_kv_local,
                                     scale=self.scale, out=out, workspace=decode_ws, window=window,

@@ -7,6 +7,12 @@ remainder spread over the first ranks (src/engine/coordinator/context_parallel.r
 LSE merge (:286-390, 460-476), sliding-window step skipping (:103-127). The reference stages f32 on the host;
 here blocks are device tensors in the KV dtype and the exchange is NCCL p2p (gloo on CPU for the tests).
 Each rank lands the peer's block in its own memory before using it (no remote TMA).
+
+``CpPrefill`` is the form the decoder runs: a long prompt is cut into page-aligned contiguous shards, every rank runs
+all layers on its shard only, and after each layer's K/V write the ranks exchange the freshly written KV pages
+(one all-gather over NVSwitch: every peer is one hop away, so the blocks need not travel round a ring) and attend
+with the ordinary paged prefill kernel over the pages of all earlier shards plus their own. Every rank ends with
+the whole prompt's KV pages, so decoding continues on any of them.
 """
 from __future__ import annotations
 
@@ -117,3 +123,98 @@ class RingAttention:
             self.comm.recv(incoming, prv)
             self.comm.send(payload, nxt)
         return incoming[0], incoming[1]
+
+
+class CpPrefill:
+    """Context-parallel prefill of whole prompts inside ``DecoderModel.forward``.
+
+    ``seq_lens``: prompt lengths; ``block_tables`` [S, max_blocks]: the sequences' pages, identical on every rank
+    (each rank's cache uses the same page ids). Rank r of W owns pages [r * ceil(P / W), (r + 1) * ceil(P / W)) of a
+    sequence of P pages. ``local_batch`` builds the rank's ``ForwardBatch`` (its shard's tokens at their absolute
+    positions; context = everything up to the shard's end); the model calls ``exchange`` after each layer wrote its
+    K/V; ``last_logits`` returns each sequence's last-token logits on every rank.
+    Reference: CpConfig / RingAttentionPlan (src/engine/coordinator/context_parallel.rs:76-127, 286-390); the ring
+    of send/recv rounds becomes one all-gather of pages per layer."""
+
+    def __init__(self, cfg: CpConfig, seq_lens, block_tables: torch.Tensor, group=None, page: int = 16):
+        self.cfg, self.group, self.page = cfg, group, page
+        self.seq_lens = [int(x) for x in seq_lens]
+        self.block_tables = block_tables
+        W = cfg.cp_size
+        self.bounds = []           # per sequence: [(tok0, tok1)] per rank
+        for L in self.seq_lens:
+            pages = (L + page - 1) // page
+            per = (pages + W - 1) // W
+            self.bounds.append([(min(L, r * per * page), min(L, (r + 1) * per * page)) for r in range(W)])
+        # pages each rank writes (over all sequences), padded to one length for the all-gather
+        bt = block_tables.cpu()
+        self.rank_pages = []
+        for r in range(W):
+            ids = []
+            for s, b in enumerate(self.bounds):
+                t0, t1 = b[r]
+                if t1 > t0:
+                    ids += bt[s, t0 // page:(t1 + page - 1) // page].tolist()
+            self.rank_pages.append(ids)
+        self.max_pages = max(1, max(len(x) for x in self.rank_pages))
+        dev = block_tables.device
+        self._idx = [torch.tensor(ids, dtype=torch.long, device=dev) for ids in self.rank_pages]
+        pad = self.rank_pages[cfg.cp_rank] + [self.rank_pages[cfg.cp_rank][-1] if self.rank_pages[cfg.cp_rank] else 0] * (
+            self.max_pages - len(self.rank_pages[cfg.cp_rank]))
+        self._mine_padded = torch.tensor(pad, dtype=torch.long, device=dev)
+        self.owner = [max((r for r in range(W) if b[r][1] > b[r][0]), default=0) for b in self.bounds]
+
+    def local_batch(self, token_ids_per_seq):
+        """The rank's prefill batch: for each sequence the tokens of its shard (possibly none)."""
+        from ..engine.batch import ForwardBatch
+        r, page = self.cfg.cp_rank, self.page
+        dev = self.block_tables.device
+        toks, pos, slots, q_start, q_len, ctx, rows = [], [], [], [], [], [], []
+        bt = self.block_tables.cpu()
+        n = 0
+        for s, ids in enumerate(token_ids_per_seq):
+            t0, t1 = self.bounds[s][r]
+            q_start.append(n)
+            q_len.append(t1 - t0)
+            ctx.append(t1 if t1 > t0 else 0)
+            for t in range(t0, t1):
+                toks.append(int(ids[t]))
+                pos.append(t)
+                slots.append(int(bt[s, t // page]) * page + t % page)
+            n += t1 - t0
+            rows.append(max(n - 1, 0))        # the shard's last row (the sequence's last token on its owner rank)
+        if n == 0:
+            raise ValueError("context parallel prefill: this rank received no tokens (prompts shorter than one page per rank)")
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        b = ForwardBatch(token_ids=i32(toks), positions=i32(pos), slot_mapping=i32(slots), block_tables=self.block_tables,
+                         ctx_lens=i32(ctx), q_start=i32(q_start), q_len=i32(q_len), max_q_len=max(q_len),
+                         logits_rows=torch.tensor(rows, dtype=torch.long, device=dev))
+        b.cp = self
+        return b
+
+    def exchange(self, kv: torch.Tensor):
+        """After this rank wrote its shard's K/V into ``kv`` [pages, ...]: fetch the pages the other ranks wrote."""
+        W = self.cfg.cp_size
+        if W == 1:
+            return
+        import torch.distributed as dist
+        flat = kv.view(torch.uint8).reshape(kv.shape[0], -1)      # bytes: every backend moves them
+        send = flat.index_select(0, self._mine_padded)
+        recv = torch.empty((W * send.shape[0], send.shape[1]), dtype=send.dtype, device=send.device)
+        dist.all_gather_into_tensor(recv, send, group=self.group)
+        recv = recv.view(W, send.shape[0], send.shape[1])
+        for r in range(W):
+            if r != self.cfg.cp_rank and len(self.rank_pages[r]):
+                flat.index_copy_(0, self._idx[r], recv[r, :len(self.rank_pages[r])])
+
+    def last_logits(self, local_logits: torch.Tensor) -> torch.Tensor:
+        """[S, V] last-token logits of every sequence on every rank (from the rank that owns each last token)."""
+        W = self.cfg.cp_size
+        if W == 1:
+            return local_logits
+        import torch.distributed as dist
+        S, V = local_logits.shape
+        allv = torch.empty((W * S, V), dtype=local_logits.dtype, device=local_logits.device)
+        dist.all_gather_into_tensor(allv, local_logits.contiguous(), group=self.group)
+        allv = allv.view(W, S, V)
+        return torch.stack([allv[self.owner[s], s] for s in range(len(self.seq_lens))])

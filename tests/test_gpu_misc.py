@@ -139,3 +139,62 @@ def test_shared_kv_donor_layers_on_the_gpu(fused):
         out[dev] = (pre, dec)
     for a, b in zip(out["cuda"], out["cpu"]):
         assert torch.nn.functional.cosine_similarity(a, b, dim=0) > 0.995
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rank", [0, 1, 2])
+def test_context_parallel_shard_on_one_gpu(rank):
+    """One rank's part of a three-rank context-parallel prefill on a single GPU: the other ranks' KV pages are put
+    into the cache by the test (from a whole-prompt prefill) where the all-gather would deliver them; the shard's
+    last-row logits and K/V pages must equal the whole-prompt run (tcgen05 prefill attention with a context longer
+    than the query, and sequences without any token on this rank)."""
+    from gllm_b200.engine.batch import ForwardBatch
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    from gllm_b200.ops import _native as nv
+    from gllm_b200.parallel.context_parallel import CpConfig, CpPrefill
+    dev = torch.device("cuda")
+    cfg = preset("tiny-qwen3")
+    cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim = 512, 4, 2, 128
+    cfg.intermediate_size, cfg.num_layers, cfg.vocab_size = 768, 3, 1024
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=5, std=0.05)
+    model = DecoderModel(cfg, src, device=dev, dtype=torch.bfloat16, max_positions=512)
+    lens, pages = [300, 40, 129], 64
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(3))
+    bt = torch.stack([perm[i * 20:(i + 1) * 20] for i in range(len(lens))]).to(torch.int32).to(dev)
+    prompts = [((torch.arange(L) * (7 + i) + 3) % cfg.vocab_size).tolist() for i, L in enumerate(lens)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    toks, pos, slots, qs, n = [], [], [], [], 0
+    btc = bt.cpu()
+    for s_, L in enumerate(lens):
+        qs.append(n)
+        for t in range(L):
+            toks.append(prompts[s_][t]); pos.append(t); slots.append(int(btc[s_, t // 16]) * 16 + t % 16)
+        n += L
+    kv_ref = model.alloc_kv_cache(pages)
+    full = ForwardBatch(token_ids=i32(toks), positions=i32(pos), slot_mapping=i32(slots), block_tables=bt, ctx_lens=i32(lens),
+                        q_start=i32(qs), q_len=i32(lens), max_q_len=max(lens))
+    want_all = model.forward(full, kv_ref)[:, :cfg.vocab_size].float()
+
+    class OneRank(CpPrefill):
+        def exchange(self, kv):      # what the all-gather delivers: the pages the other ranks wrote
+            ref = by_ptr[kv.data_ptr()]
+            for r in range(self.cfg.cp_size):
+                if r != self.cfg.cp_rank and len(self.rank_pages[r]):
+                    kv.index_copy_(0, self._idx[r], ref.index_select(0, self._idx[r]))
+
+    cp = OneRank(CpConfig(3, rank), lens, bt)
+    kv_cp = model.alloc_kv_cache(pages)
+    by_ptr = {a.data_ptr(): b for a, b in zip(kv_cp, kv_ref)}
+    batch = cp.local_batch(prompts)
+    got = model.forward(batch, kv_cp)[:, :cfg.vocab_size].float()
+    torch.cuda.synchronize()
+    for s_, L in enumerate(lens):
+        t0, t1 = cp.bounds[s_][rank]
+        if t1 > t0:      # this rank's last row of the sequence is token t1 - 1
+            torch.testing.assert_close(got[s_], want_all[qs[s_] + t1 - 1], rtol=0.05, atol=0.05)
+    used = torch.cat([btc[s_, :(L + 15) // 16] for s_, L in enumerate(lens)]).long().to(dev)
+    for a, b in zip(kv_cp, kv_ref):
+        torch.testing.assert_close(a.float().index_select(0, used), b.float().index_select(0, used), rtol=0.05, atol=0.05)
+    assert nv.device_error() == 0

@@ -237,6 +237,17 @@ def test_sequence_parallel_decoder_world1_matches_plain_model():
 
 
 @pytest.mark.multigpu
+def test_context_parallel_prefill_two_gpus():
+    """Two ranks prefill halves of the prompts (tcgen05 attention over the exchanged pages) against one rank."""
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29885", os.path.join(ROOT, "tests", "cp_worker.py"), "cuda"]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("CP_WORKER_OK") == 2
+
+
+@pytest.mark.multigpu
 @pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
 def test_blockscaled_gemm_with_fused_allreduce_two_gpus(fmt):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
