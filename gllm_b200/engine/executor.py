@@ -51,6 +51,10 @@ class EngineConfig:
     swap_space_pages: int = 0
     swap_path: Optional[str] = None
     swap_nvme_pages: int = 0
+    # a 4-bit tier in front of the host: preempted sequences are first packed into a byte pool on the GPU itself
+    # (3.1x smaller than bf16, no PCIe traffic, lossy) and unpacked when they resume; when the pool is full they go
+    # to the host as before. Takes effect together with swap_space_pages > 0.
+    kv_kivi_pool_pages: int = 0
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
@@ -108,7 +112,7 @@ class LLMEngine:
         if ec.swap_space_pages > 0:
             from .kv_swap import KvSwapManager
             self.kv_swap = KvSwapManager(self.kv_caches, ec.swap_space_pages, swap_path=ec.swap_path,
-                                         nvme_pages=ec.swap_nvme_pages)
+                                         nvme_pages=ec.swap_nvme_pages, device_pool_pages=ec.kv_kivi_pool_pages)
         self.ms = ec.max_num_seqs
         dev = self.device
         cuda = dev.type == "cuda"
@@ -710,7 +714,7 @@ class LLMEngine:
                 self.import_handoff(h)
         if self.kv_swap is not None and self.batcher.num_free_pages < max(8, self.num_pages // 16):
             # memory is tight: the batcher's next victims follow the eviction policy, not "youngest first"
-            running = [rid for rid in self.reqs if rid not in self.kv_swap.keys]
+            running = [rid for rid in self.reqs if rid not in self.kv_swap.keys and rid not in self.kv_swap.packed]
             self.batcher.set_victim_order(self.kv_swap.victim_order(running))
         self._steps = getattr(self, "_steps", 0) + 1
         if self._steps % 16 == 1:

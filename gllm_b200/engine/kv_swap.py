@@ -25,8 +25,14 @@ from ..scheduler.types import PayloadKind, UnifiedVirtualPage
 
 class KvSwapManager:
     def __init__(self, kv_caches: List[torch.Tensor], host_pages: int, *, swap_path: Optional[str] = None,
-                 nvme_pages: int = 0, hgal: Optional[HgalConfig] = None):
+                 nvme_pages: int = 0, hgal: Optional[HgalConfig] = None, device_pool_pages: int = 0):
         layers = [t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in kv_caches]
+        # the 4-bit tier on the device itself (bf16 / fp32 caches in the [pages, 2, n_kv, 16, D] layout only)
+        self.device_tier = None
+        self.packed: Dict[int, List[int]] = {}     # sequence packed on the device -> its pool slots, logical order
+        if device_pool_pages > 0 and kv_caches[0].dim() == 5 and kv_caches[0].dtype != torch.float8_e4m3fn:
+            from ..kv_cache.device_tier import Kivi4Pool
+            self.device_tier = Kivi4Pool(kv_caches, device_pool_pages)
         self.swap = ThreeTierSwap(LayeredPool(layers), host_pages, swap_path=swap_path, nvme_slots=nvme_pages,
                                   policy=SwapPolicy())
         # victims must be allowed right away in a serving step: the warm-up window only protects pages from the
@@ -34,7 +40,8 @@ class KvSwapManager:
         self.hgal = Hgal(hgal or HgalConfig(warmup_ms=0.0))
         self.keys: Dict[int, List[int]] = {}       # swapped-out sequence -> its page keys, logical order
         self._next_key = 1
-        self.stats = {"swapped_out_seqs": 0, "swapped_in_seqs": 0, "pages_out": 0, "pages_in": 0, "to_nvme": 0}
+        self.stats = {"swapped_out_seqs": 0, "swapped_in_seqs": 0, "pages_out": 0, "pages_in": 0, "to_nvme": 0,
+                      "packed_seqs": 0, "packed_pages": 0, "unpacked_pages": 0}
 
     # ---- who leaves ----------------------------------------------------------------------------------
     def _now_ms(self) -> float:
@@ -85,7 +92,17 @@ class KvSwapManager:
             raise MemoryError("swap space exhausted on both the host and the NVMe tier")
 
     def swap_out(self, item):
-        """Copy the pages of a preempted sequence to the host (before the step's kernels may reuse them)."""
+        """Copy the pages of a preempted sequence to the host (before the step's kernels may reuse them); with a
+        device tier they are packed to 4 bits in place of the copy while the pool has room."""
+        if self.device_tier is not None:
+            slots = self.device_tier.pack([int(p) for p in item.pages])
+            if slots is not None:
+                self.packed[int(item.seq_id)] = slots
+                self.forget(int(item.seq_id))
+                self.stats["swapped_out_seqs"] += 1
+                self.stats["packed_seqs"] += 1
+                self.stats["packed_pages"] += len(slots)
+                return
         self._make_room_on_host(len(item.pages))
         keys = []
         for page in item.pages:
@@ -102,6 +119,13 @@ class KvSwapManager:
 
     def swap_in(self, item):
         """Bring a sequence back into the pages the batcher just gave it (the last page may be a fresh, empty one)."""
+        slots = self.packed.pop(int(item.seq_id), None)
+        if slots is not None:
+            self.device_tier.unpack(slots, [int(p) for p in item.pages][:len(slots)])
+            self.track(int(item.seq_id))
+            self.stats["swapped_in_seqs"] += 1
+            self.stats["unpacked_pages"] += len(slots)
+            return
         keys = self.keys.pop(int(item.seq_id), [])
         pairs = list(zip(keys, item.pages))
         # pages still in host memory first (each frees a host slot), then the ones that went down to the file tier:
@@ -122,6 +146,9 @@ class KvSwapManager:
 
     def drop(self, seq_id: int):
         """A swapped-out sequence was aborted: release its copies."""
+        slots = self.packed.pop(int(seq_id), None)
+        if slots is not None:
+            self.device_tier.release(slots)
         for key in self.keys.pop(int(seq_id), []):
             r = self.swap.records.pop(key, None)
             if r is None:
