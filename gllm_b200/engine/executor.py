@@ -113,6 +113,9 @@ class LLMEngine:
             from .kv_swap import KvSwapManager
             self.kv_swap = KvSwapManager(self.kv_caches, ec.swap_space_pages, swap_path=ec.swap_path,
                                          nvme_pages=ec.swap_nvme_pages, device_pool_pages=ec.kv_kivi_pool_pages)
+            self.kv_swap.tier_policy = self._swap_tier
+        self._sessions = set()                # requests that belong to a multi-turn session (conversation pipeline)
+        self.kv_importance: Dict[int, int] = {}      # request -> importance score 0..255 (callers / telemetry may set it)
         self.ms = ec.max_num_seqs
         dev = self.device
         cuda = dev.type == "cuda"
@@ -228,6 +231,8 @@ class LLMEngine:
                               max_new_tokens=int(max_tokens), eos_ids=eos)
         self.batcher.add_request(rid, [int(t) for t in prompt_ids], sp, session_id or "")
         self.reqs[rid] = _ReqState(t_submit=time.perf_counter(), hook=hook, stream=stream)
+        if session_id:
+            self._sessions.add(rid)
         if self.cfg.pd_role == "prefill_only":
             self._pd_prompts[rid] = [int(t) for t in prompt_ids]
             self._req_params[rid] = (float(temperature), int(top_k), float(top_p))
@@ -244,6 +249,15 @@ class LLMEngine:
         return rid
 
     submit = add_request
+
+    def _swap_tier(self, rid: int):
+        """Precision tier in which a preempted request's KV pages may wait: the KV optimiser's decision from the
+        request's importance score and pipeline (a session's pages never drop below fp8, so they go to the host
+        unchanged; scratch requests may wait as 4-bit pages on the device)."""
+        from ..scheduler.kv_optimizer import decide_tier
+        from ..scheduler.types import KvPipeline
+        pipeline = KvPipeline.CONVERSATION if rid in self._sessions else KvPipeline.WORKING
+        return decide_tier(int(self.kv_importance.get(rid, 100)), pipeline)
 
     def has_work(self) -> bool:
         return bool(self.reqs)
@@ -953,6 +967,8 @@ class LLMEngine:
                 self.kv_swap.forget(f.id)
                 self.kv_swap.drop(f.id)
             st = self.reqs.pop(f.id, None)
+            self._sessions.discard(f.id)
+            self.kv_importance.pop(f.id, None)
             slot = self._slot_of.pop(f.id, None)
             if slot is not None and int(self.req_table.rec[slot]["request_id"]) == f.id:
                 if st is not None and self._sl_nout[slot]:      # fold the fast-path counters into the request's state

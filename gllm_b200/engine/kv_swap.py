@@ -29,6 +29,7 @@ class KvSwapManager:
         layers = [t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t for t in kv_caches]
         # the 4-bit tier on the device itself (bf16 / fp32 caches in the [pages, 2, n_kv, 16, D] layout only)
         self.device_tier = None
+        self.tier_policy = None        # callable(seq_id) -> PrecisionTier the sequence may wait in (None: KIVI4)
         self.packed: Dict[int, List[int]] = {}     # sequence packed on the device -> its pool slots, logical order
         if device_pool_pages > 0 and kv_caches[0].dim() == 5 and kv_caches[0].dtype != torch.float8_e4m3fn:
             from ..kv_cache.device_tier import Kivi4Pool
@@ -94,7 +95,9 @@ class KvSwapManager:
     def swap_out(self, item):
         """Copy the pages of a preempted sequence to the host (before the step's kernels may reuse them); with a
         device tier they are packed to 4 bits in place of the copy while the pool has room."""
-        if self.device_tier is not None:
+        from ..kv_cache.header import PrecisionTier
+        tier = self.tier_policy(int(item.seq_id)) if self.tier_policy is not None else PrecisionTier.KIVI4
+        if self.device_tier is not None and tier >= PrecisionTier.KIVI4:
             slots = self.device_tier.pack([int(p) for p in item.pages])
             if slots is not None:
                 self.packed[int(item.seq_id)] = slots

@@ -90,6 +90,32 @@ def test_engine_packs_preempted_sequences_on_the_device():
     assert same >= 0.5 * 240, same
 
 
+def test_sessions_and_important_requests_keep_full_precision():
+    """The KV optimiser decides where a victim waits: a session's pages (conversation pipeline: never below fp8) and
+    requests marked important go to the host unchanged; the rest may be packed to 4 bits on the device."""
+    from gllm_b200.kv_cache.header import PrecisionTier
+    from tests.test_engine_extras import _tiny_engine
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 33, 48, 37, 45, 30)]
+    want = [r.token_ids for r in _tiny_engine(num_pages=128).generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])]
+    eng = _tiny_engine(num_pages=22, swap_space_pages=64, kv_kivi_pool_pages=32)
+    rids = [eng.add_request(p, max_tokens=40, temperature=0.0, eos_ids=[], session_id=f"chat-{i}") for i, p in enumerate(prompts)]
+    assert eng._swap_tier(rids[0]) <= PrecisionTier.FP8
+    while eng.has_work():
+        eng.step()
+    got = [eng.results[r].token_ids for r in rids]
+    assert got == want                                     # nothing was quantised: same tokens as without pressure
+    assert eng.kv_swap.stats["packed_seqs"] == 0 and eng.kv_swap.stats["pages_out"] > 0
+    # without a session the same request may wait in 4 bits, unless its importance says otherwise
+    rid = eng.add_request(prompts[0], max_tokens=4, temperature=0.0, eos_ids=[])
+    assert eng._swap_tier(rid) == PrecisionTier.KIVI4
+    eng.kv_importance[rid] = 230
+    assert eng._swap_tier(rid) == PrecisionTier.FP16
+    while eng.has_work():
+        eng.step()
+    assert rid not in eng.kv_importance and not eng._sessions
+
+
 @pytest.mark.gpu
 def test_device_kernels_match_the_cpu_statement():
     from gllm_b200.ops import _native as nv
