@@ -82,13 +82,53 @@ class ObservabilityCoordinator:
 
     def __init__(self, engine):
         self.engine, self.observer = engine, BasicObserver()
+        self.eplb = None              # moe.eplb.Eplb of an MoE model: sliding window of per-expert token counts
+        self.eplb_state: Dict[str, object] = {}
 
     def capture(self):
         b = self.engine.batcher
         st = self.observer.system_state(free_pages=b.num_free_pages, total_pages=b.num_total_pages,
                                         fragmentation=b.fragmentation, running=b.num_running, waiting=b.num_waiting)
         b.set_system_state(st)
+        self.capture_expert_load()
         return st
+
+    def capture_expert_load(self, reduce: bool = False):
+        """Expert-load sample for the load balancer: the most recent routing decision of the model's MoE layers goes
+        into the sliding window; the window's totals give the imbalance (max / mean) and, beyond the threshold, the
+        hot experts a HotCold placement would mirror. The step loop samples this rank's own routing only;
+        ``reduce=True`` sums the windows over the expert-parallel ranks first and is a collective: every rank of the
+        group has to make the call (e.g. from the serving loop's periodic maintenance point).
+        Reference: EPLB window, cross-rank reduction and decision (src/moe/eplb.rs:18-243)."""
+        model = self.engine.model
+        cfg = getattr(model, "cfg", None)
+        if cfg is None or not getattr(cfg, "is_moe", False):
+            return None
+        holder = getattr(model, "__dict__", {}).get("_moe_ws") or {}
+        ids = next((ws.last_ids for ws in holder.values() if getattr(ws, "last_ids", None) is not None), None)
+        if ids is None:
+            return None
+        import torch
+        from ..moe.eplb import Eplb
+        from ..parallel.config import MoeDistConfig
+        if self.eplb is None:
+            self.eplb = Eplb(cfg.num_experts)
+        counts = torch.bincount(ids.reshape(-1).long().clamp_(0, cfg.num_experts - 1), minlength=cfg.num_experts)
+        self.eplb.record(counts)
+        totals = self.eplb.local_totals()
+        ep = getattr(model, "ep", None)
+        group = getattr(ep, "group", None)
+        if reduce and ep is not None and getattr(ep, "size", 1) > 1:
+            import torch.distributed as dist
+            t = totals.to(ids.device)
+            dist.all_reduce(t, group=group)
+            totals = t.cpu()
+        dist_cfg = MoeDistConfig()
+        decision = self.eplb.decide(totals, dist_cfg)
+        self.eplb_state = {"imbalance": self.eplb.imbalance(totals), "totals": totals,
+                           "hot_experts": list(decision.hot_experts) if decision is not None else [],
+                           "placement": decision.placement if decision is not None else dist_cfg.placement}
+        return self.eplb_state
 
 
 @dataclass

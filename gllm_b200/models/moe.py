@@ -99,9 +99,11 @@ class MoeLayerWeights:
         logits = ops.gemm(x, self.router, out=ws.logits[:T], out_dtype=torch.float32, row_ss=row_ss,
                           norm_dim=norm_dim, eps=eps, bn=128)
         E = c.num_experts
-        return M.route(logits[:, :E], c.num_experts_per_tok, norm_topk=c.norm_topk_prob, scoring=c.router_scoring,
-                       sel_bias=self.router_bias, scale=c.routed_scaling_factor,
-                       out_ids=ws.ids[:T] if x.is_cuda else None, out_w=ws.w[:T] if x.is_cuda else None)
+        ids, w = M.route(logits[:, :E], c.num_experts_per_tok, norm_topk=c.norm_topk_prob, scoring=c.router_scoring,
+                         sel_bias=self.router_bias, scale=c.routed_scaling_factor,
+                         out_ids=ws.ids[:T] if x.is_cuda else None, out_w=ws.w[:T] if x.is_cuda else None)
+        ws.last_ids = ids      # the load balancer samples the most recent routing decision from here
+        return ids, w
 
     def forward(self, model, x, ss_in, ss_out, T):
         """Fused path: ``x`` is the residual stream (bf16), ``ss_in`` its row statistics; the post-attention

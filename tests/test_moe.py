@@ -74,3 +74,16 @@ def test_moe_layer_matches_dense_masked_reference_and_generates():
     eng = LLMEngine(m, EngineConfig(max_num_seqs=4, max_model_len=128, max_batch_tokens=64, prefill_chunk=32))
     out = eng.generate_batch([[1, 2, 3, 4, 5], list(range(40))], max_tokens=4, temperature=0.0, eos_ids=[])
     assert [len(r.token_ids) for r in out] == [4, 4]
+    # the observability coordinator sampled the routing for the load balancer while the engine ran
+    obs = eng.coordinators.observability
+    assert obs.eplb is not None and obs.eplb_state["totals"].sum() > 0
+    assert obs.eplb_state["imbalance"] >= 1.0 and isinstance(obs.eplb_state["hot_experts"], list)
+    # a skewed window: one expert takes most of the tokens -> it is named hot and the placement becomes HotCold
+    from gllm_b200.parallel.config import MoePlacement
+    skew = torch.ones(cfg.num_experts, dtype=torch.int64)
+    skew[2] = 50 * cfg.num_experts
+    obs.eplb.samples.clear()
+    obs.eplb.record(skew)
+    m._moe_ws[next(iter(m._moe_ws))].last_ids = torch.full((4, cfg.num_experts_per_tok), 2, dtype=torch.int32)
+    st = obs.capture_expert_load()
+    assert st["hot_experts"] == [2] and st["placement"] == MoePlacement.HOT_COLD and st["imbalance"] > 2.0
