@@ -43,6 +43,31 @@ class KvCoordinator:
         b = self.engine.batcher
         return 1.0 - b.num_free_pages / max(b.num_total_pages, 1)
 
+    @property
+    def memory(self):
+        """The three-tier page accounting (``GlobalMemoryManager``) over this engine's pools: HBM pages of the batcher,
+        pinned host pages and NVMe slots of the swap tier. Occupancy is refreshed from the pools on every call."""
+        from ..scheduler.memory_manager import GlobalMemoryManager
+        from ..scheduler.types import Tier
+        b = self.engine.batcher
+        sw = self.swap
+        host = int(sw.host_pool.shape[0]) if sw is not None else 0
+        nvme = (len(sw.nvme.free) + sum(1 for r in sw.records.values() if int(r.tier) == 2)) if (
+            sw is not None and sw.nvme is not None) else 0
+        if getattr(self, "_mem", None) is None or self._mem.cap[Tier.L1_GPU] != b.num_total_pages:
+            self._mem = GlobalMemoryManager(b.num_total_pages, host, nvme)
+        m = self._mem
+        m.used[Tier.L1_GPU] = b.num_total_pages - b.num_free_pages
+        if sw is not None:
+            m.used[Tier.L2_CPU] = host - len(sw.host_free)
+            m.used[Tier.L3_NVME] = nvme - len(sw.nvme.free) if sw.nvme is not None else 0
+        return m
+
+    def plan_prefill(self, prompt_tokens: int):
+        """Whether a prompt's pages fit the free HBM pages now (``fully_resident``) or the prefill has to run chunk by
+        chunk with part of its pages waiting in the host tier (``pipelined``)."""
+        return self.memory.plan_prefill(prompt_tokens, chunk_tokens=self.engine.cfg.prefill_chunk)
+
     def reclaim(self, pages: int) -> int:
         """Ask the swap tier (when there is one) to make room."""
         if self.swap is None:

@@ -120,6 +120,16 @@ def test_coordinators_and_backend_context():
     co.inference.drain()
     assert len(eng.results[rid].token_ids) == 3 and co.model_ctx.config is cfg
     assert co.kv.plan()["store_heads"] == list(range(cfg.num_kv_heads))
+    # three-tier accounting over the engine's pools, and the prefill page plan it gives
+    from gllm_b200.scheduler.types import Tier
+    mem = co.kv.memory
+    assert mem.cap[Tier.L1_GPU] == 32 and mem.used[Tier.L1_GPU] == 32 - eng.batcher.num_free_pages
+    assert co.kv.plan_prefill(100).kind == "fully_resident"
+    big = co.kv.plan_prefill(16 * 40)
+    assert big.kind == "pipelined" and big.l2_prefetch > 0 and sum(big.chunk_schedule) == 16 * 40
+    swp = _tiny_engine(num_pages=22, swap_space_pages=12)
+    m2 = swp.coordinators.kv.memory
+    assert m2.cap[Tier.L2_CPU] == 12 and m2.used[Tier.L2_CPU] == 0
 
 
 def test_engine_step_raises_on_a_device_status_code_and_fails_the_requests():
