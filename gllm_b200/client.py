@@ -69,6 +69,12 @@ class ClientConfig:
     seed: int = 0
     kv_cache_dtype: str = "auto"     # bf16 | fp8 | auto (the KV decision matrix picks from what fits in HBM)
     kv_scale: float = 0.05           # per-tensor scale of an fp8 KV cache
+    # How the dense projections are held on the device. "bf16": a quantised checkpoint (GGUF K-quants, AWQ, GPTQ, fp8
+    # blocks ...) is dequantised at load and runs the fused bf16 layer. "mxfp8" / "nvfp4": the projections are
+    # (re)quantised to block-scaled operands and every GEMM of the fused layer runs block-scaled on the tensor cores.
+    # "auto": nvfp4 for a checkpoint quantised to 4-5 bits, mxfp8 for 6-8 bits, bf16 otherwise (on a GPU, when the model
+    # has the shapes of the fused layer).
+    weight_quant: str = "bf16"
 
 
 @dataclass
@@ -226,6 +232,7 @@ class Client:
                             and kind != ModelKind.EMBEDDING and kind != ModelKind.RERANKER:
                         raise InvalidModelTypeError(f"{model_id} has no classifier head")
                     kv_kw = self._kv_cache_plan(cfg, dev)
+                    kv_kw["weight_quant"] = self._weight_quant_plan(cfg, dev)
                     model = DecoderModel(cfg, weights, device=dev, dtype=dt,
                                          max_positions=min(cfg.max_position_embeddings, self.config.max_model_len), **kv_kw)
                     ec = EngineConfig(max_num_seqs=self.config.max_num_seqs, max_model_len=self.config.max_model_len,
@@ -243,6 +250,33 @@ class Client:
             except torch.cuda.OutOfMemoryError as e:  # pragma: no cover - needs a GPU
                 raise OutOfMemoryError(str(e)) from e
             self._state = _State(model_id, kind, loaded, model, engine, tokenizer, be)
+
+    _BITS_4 = ("q4", "q5", "iq4", "q3", "iq3", "q2", "iq2", "iq1", "awq", "gptq", "nvfp4", "mxfp4", "int4")
+    _BITS_8 = ("q8", "q6", "fp8", "mxfp8", "int8")
+
+    def _weight_quant_plan(self, cfg, dev) -> Optional[str]:
+        """``DecoderModel(weight_quant=...)`` for this checkpoint on this device (see ``ClientConfig.weight_quant``)."""
+        from .models.weights import can_fuse
+        want = (self.config.weight_quant or "bf16").lower()
+        if want in ("bf16", "none", ""):
+            return None
+        if want not in ("auto", "mxfp8", "nvfp4"):
+            raise ValueError(f"weight_quant must be bf16, auto, mxfp8 or nvfp4, got {want!r}")
+        if want == "auto":
+            if dev.type != "cuda":
+                return None
+            tags = (cfg.quant or "").lower()
+            want = "nvfp4" if any(t in tags for t in self._BITS_4) else ("mxfp8" if any(t in tags for t in self._BITS_8) else "")
+            if not want:
+                return None
+        mult = 256 if want == "nvfp4" else 128
+        shapes_ok = (can_fuse(cfg, 1) and not cfg.is_mla and cfg.hidden_size % mult == 0 and
+                     (cfg.is_moe or cfg.intermediate_size % mult == 0) and (cfg.num_heads * cfg.head_dim) % mult == 0)
+        if not shapes_ok:
+            if self.config.weight_quant.lower() == "auto":
+                return None
+            raise ValueError(f"{want}: the model's shapes do not fit the block-scaled fused layer")
+        return want
 
     def _kv_cache_plan(self, cfg, dev) -> dict:
         """Precision of the KV cache for this model on this device. ``auto`` asks the KV decision matrix

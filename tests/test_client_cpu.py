@@ -141,3 +141,38 @@ def test_kv_cache_plan_comes_from_the_decision_matrix():
     c.config = ClientConfig(max_num_seqs=4096, max_model_len=131072)      # 74 TB of bf16 KV: cannot fit
     c._kv_cache_plan(preset("qwen3-8b"), torch.device("cpu"))
     assert c.kv_plan["variant"].kivi and c.kv_plan["bf16_bytes"] > 180 << 30
+
+
+def test_weight_quant_plan_of_the_client():
+    """``ClientConfig.weight_quant``: explicit block-scaled formats build the fused block-scaled model (here on CPU
+    tensors through the fp32 restatements of the fused ops); ``auto`` reads the checkpoint's quantisation tags and only
+    acts on a GPU; shapes that do not fit are refused by name."""
+    import pytest
+    import torch
+    from gllm_b200.client import Client
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.intermediate_size = 256, 2, 2, 128, 512
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    c = Client.from_model(cfg, src, device="cpu", dtype=torch.float32, max_num_seqs=2, max_model_len=128,
+                          max_batch_tokens=64, weight_quant="mxfp8")
+    model = c._state.model
+    assert model.bs_fmt == "mxfp8" and model.fused
+    r = c.generate("hello world").max_tokens(3).temperature(0.0).generate()
+    assert 1 <= len(r.token_ids) <= 3
+    # auto: tags of a 4-bit checkpoint -> nvfp4 on a GPU, nothing on the CPU
+    cfg.quant = "Q4_K+Q6_K"
+    plain = Client.from_model(cfg, src, device="cpu", dtype=torch.float32, max_num_seqs=2, max_model_len=128,
+                              max_batch_tokens=64, weight_quant="auto")
+    assert plain._state.model.bs_fmt is None
+    assert plain._weight_quant_plan(cfg, torch.device("cuda")) == "nvfp4"
+    cfg.quant = "Q8_0"
+    assert plain._weight_quant_plan(cfg, torch.device("cuda")) == "mxfp8"
+    cfg.quant = ""
+    assert plain._weight_quant_plan(cfg, torch.device("cuda")) is None
+    small = preset("tiny-qwen3")
+    small.head_dim, small.num_heads, small.num_kv_heads = 64, 4, 2      # not the head size of the fused layer
+    with pytest.raises(ValueError, match="do not fit"):
+        Client.from_model(small, RandomWeights(small, "cpu", torch.float32, seed=2), device="cpu", dtype=torch.float32,
+                          max_num_seqs=2, max_model_len=128, max_batch_tokens=64, weight_quant="nvfp4")
