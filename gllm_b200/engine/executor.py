@@ -185,6 +185,7 @@ class LLMEngine:
         self.launches_per_graph: Dict[int, int] = {}
         self.gen = torch.Generator().manual_seed(ec.seed)
         self._all_greedy = True
+        self._topk_cap = 0      # tensor parallel, every sampling row has 0 < top_k <= 64: candidates instead of the vocabulary
         self._req_params: Dict[int, tuple] = {}
         from ..scheduler.request_state import RequestStateTable
         self.req_table = RequestStateTable(self.ms, self.device)
@@ -327,7 +328,7 @@ class LLMEngine:
         """Per-op device milliseconds of one captured decode step of bucket ``B`` (event nodes inside a fresh graph of
         the same step; the graph used for serving is left as it was)."""
         from ..utils.tracing import GraphTimer
-        key = (B, self._all_greedy)
+        key = self._graph_key(B)
         keep = self.graphs.get(key)
         self.model.op_timer = GraphTimer()
         trace_k = int(os.environ.get("GLLM_TRACE_K", "0"))   # also stamp the phases of the GEMMs with this K (and N)
@@ -371,12 +372,26 @@ class LLMEngine:
         self.d_offsets[:B] -= replays
         return res
 
+    def _set_sampling_mode(self, rows):
+        """``rows``: [n, 4] host rows {temperature, top_k, top_p, _} of the step's sampling slots."""
+        self._all_greedy = bool((rows[:, 0] <= 0).all())
+        self._topk_cap = 0
+        tp = self.model.tp
+        if not self._all_greedy and tp is not None and tp.size > 1:
+            k = rows[rows[:, 0] > 0, 1]
+            if k.size and bool(((k > 0) & (k <= 64)).all()):
+                self._topk_cap = 64
+
+    def _graph_key(self, B):
+        return (B, True if self._all_greedy else ("topk" if self._topk_cap else False))
+
     def _sample(self, logits, params, offsets, out):
         tp = self.model.tp
         if tp is not None and tp.size > 1:
             # the greedy fast path (pairs instead of full logit rows) is fixed per captured graph
             tp.sample_vocab_parallel(logits, self.model.vocab_local, self.model.vocab_start, params, self.cfg.seed,
-                                     offsets, out, self.mc.vocab_size, greedy=self._all_greedy)
+                                     offsets, out, self.mc.vocab_size, greedy=self._all_greedy,
+                                     topk_cap=0 if self._all_greedy else self._topk_cap)
         else:
             ops.sample(logits, params, vocab=self.mc.vocab_size, seed=self.cfg.seed, step_offsets=offsets, out=out,
                        generator=self.gen)
@@ -400,9 +415,9 @@ class LLMEngine:
         self.d_bt.copy_(self.h_bt, non_blocking=cuda)
         self.d_params.copy_(self.h_params, non_blocking=cuda)
         self.stats["h2d_bytes"] += self.h_dec.numel() * 4 + self.h_bt.numel() * 4 + self.h_params.numel() * 4
-        self._all_greedy = bool((self.slot_params[:, 0] <= 0).all())
+        self._set_sampling_mode(self.slot_params)
         if cuda and self.cfg.use_cuda_graphs:
-            key = (B, self._all_greedy)
+            key = self._graph_key(B)
             g = self.graphs.get(key)
             if g is None and self.lockstep is None:
                 g = self._capture(B)
@@ -577,8 +592,8 @@ class LLMEngine:
         with torch.cuda.graph(g, stream=s):
             self._decode_body(B)
         self.launches_per_graph[B] = nv.CALLS[0] - n0
-        self.graphs[(B, self._all_greedy)] = g
-        self._register_variant((B, self._all_greedy), g)
+        self.graphs[self._graph_key(B)] = g
+        self._register_variant(self._graph_key(B), g)
         return g
 
     def _variant_key(self, key):
@@ -651,7 +666,7 @@ class LLMEngine:
         finally:
             self.model.op_timer = None
         last_slots = self.h_pf.numpy()[o + n_last:o + 2 * n_last]
-        self._all_greedy = bool((self.slot_params[last_slots, 0] <= 0).all())
+        self._set_sampling_mode(self.slot_params[last_slots])
         self.h_pf_params.numpy()[:n_last] = self.slot_params[last_slots]
         self.d_pf_params[:n_last].copy_(self.h_pf_params[:n_last], non_blocking=cuda)
         sl = dp[o + n_last:o + 2 * n_last]

@@ -211,7 +211,12 @@ def sample(logits, params, *, vocab=None, seed=0, step_offsets=None, out=None, o
     if not logits.is_cuda:
         for b in range(B):
             t, k, p = float(params[b, 0]), int(params[b, 1]), float(params[b, 2])
-            u = float(torch.rand((), generator=generator)) if t > 0 else 0.0
+            gen = generator
+            if gen is None and step_offsets is not None:
+                # counter-based like the device sampler: the draw depends on (seed, row, the row's step counter) only,
+                # so tensor-parallel ranks sampling the same row agree
+                gen = torch.Generator().manual_seed((int(seed) * 1000003 + int(step_offsets[b]) * 7919 + b) & 0x7FFFFFFFFFFF)
+            u = float(torch.rand((), generator=gen)) if t > 0 else 0.0
             out[b] = sample_ref(logits[b, :vocab], t, k, p, u)
         return out
     rc = nv.lib().gllm_sample(logits.data_ptr(), logits.stride(0), 1 if logits.dtype == torch.bfloat16 else 0, B, vocab,

@@ -393,12 +393,28 @@ class TPContext:
             dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------------------------------
-    def sample_vocab_parallel(self, logits, vocab_local, vocab_start, params, seed, offsets, out, vocab, greedy=True):
+    def sample_vocab_parallel(self, logits, vocab_local, vocab_start, params, seed, offsets, out, vocab, greedy=True,
+                              topk_cap: int = 0):
         """Each rank holds logits for vocabulary rows [vocab_start, vocab_start+vocab_local). Greedy requests
-        exchange only (max, argmax) pairs; otherwise the shards are gathered and sampled identically on every
-        rank (same Philox seed and offsets), so all ranks agree on the token without another broadcast."""
+        exchange only (max, argmax) pairs. ``topk_cap`` > 0 (every row samples with 0 < top_k <= topk_cap): each rank
+        sends its ``topk_cap`` best (logit, index) pairs per row, the union holds every row's global top-k, and all
+        ranks sample from it (top-k first, then top-p inside it, as the sampler orders them): W * topk_cap pairs per row
+        on the wire instead of the vocabulary. Otherwise the shards are gathered whole. Every rank samples with the
+        same Philox seed and offsets, so all agree on the token without another broadcast."""
         import torch.distributed as dist
         B = logits.shape[0]
+        if not greedy and topk_cap > 0:
+            k = min(int(topk_cap), int(vocab_local))
+            vals, idx = torch.topk(logits[:, :vocab_local].float(), k, dim=1)
+            pair = torch.cat([vals, (idx + vocab_start).to(torch.float32)], 1).contiguous()     # indices < 2^24: exact
+            allp = torch.empty((self.size * B, 2 * k), dtype=torch.float32, device=logits.device)
+            dist.all_gather_into_tensor(allp, pair, group=self.group)
+            allp = allp.view(self.size, B, 2 * k)
+            cand_vals = allp[:, :, :k].permute(1, 0, 2).reshape(B, self.size * k).contiguous()
+            cand_idx = allp[:, :, k:].permute(1, 0, 2).reshape(B, self.size * k)
+            pick = ops.sample(cand_vals, params, vocab=self.size * k, seed=seed, step_offsets=offsets)
+            out.copy_(cand_idx.gather(1, pick.long()[:, None]).squeeze(1).to(torch.int32))
+            return out
         if greedy:
             vals = torch.empty(B, dtype=torch.float32, device=logits.device)
             idx = torch.empty(B, dtype=torch.int32, device=logits.device)
