@@ -6,8 +6,8 @@ RAG inject, residual-bus bridge (src/engine/callbacks/*); port layers: RAG injec
 0.786 L, intent recall 0.75 L, guardrail L-2 (src/engine/executor_builder.rs:9-13,287-304); the 8-slot C-ABI
 callback table (src/engine/mega_kernel_callback.rs:17-100).
 
-The decoder exposes ``capture_layers``; callbacks run on the captured hidden states between graph segments (the
-eager path), never inside a captured CUDA graph.
+``DecoderModel.forward(callbacks=chain)`` runs the chain on the residual stream before / after the layers it names
+(the eager forward, never inside a captured CUDA graph); ``LLMEngine`` takes a chain in ``EngineConfig.callbacks``.
 """
 from __future__ import annotations
 

@@ -55,6 +55,10 @@ class EngineConfig:
     # (3.1x smaller than bf16, no PCIe traffic, lossy) and unpacked when they resume; when the pool is full they go
     # to the host as before. Takes effect together with swap_space_pages > 0.
     kv_kivi_pool_pages: int = 0
+    # engine.callbacks.CallbackChain run on the residual stream of every forward (RAG / knowledge injection, probes that
+    # veto, early exit). Steps then run eagerly (no CUDA graphs). The stock callbacks look at the last row of the step,
+    # i.e. they are meant for one request at a time (max_num_seqs = 1); a veto ends every request of the step.
+    callbacks: Optional[object] = None
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
@@ -317,7 +321,8 @@ class LLMEngine:
             self.pp.share_tokens(self.d_out[:B])
             self.d_offsets[:B] += 1
             return
-        logits = self.model.forward(self._decode_batch(B), self.kv_caches, decode_ws=self.decode_ws)
+        logits = self.model.forward(self._decode_batch(B), self.kv_caches, decode_ws=self.decode_ws,
+                                    **({"callbacks": self.cfg.callbacks} if self.cfg.callbacks is not None else {}))
         self._sample(logits, self.d_params[:B], self.d_offsets[:B], self.d_out[:B])
         self.d_offsets[:B] += 1
         tm = getattr(self.model, "op_timer", None)
@@ -385,6 +390,13 @@ class LLMEngine:
     def _graph_key(self, B):
         return (B, True if self._all_greedy else ("topk" if self._topk_cap else False))
 
+    def _note_callback_veto(self, rids):
+        """A callback of the chain vetoed during the last forward: the step's requests end with that reason."""
+        from .callbacks import CallbackAction
+        if getattr(self.model, "callback_action", None) == CallbackAction.VETO:
+            for rid in rids:
+                self._vetoed[rid] = "vetoed by a layer callback"
+
     def _sample(self, logits, params, offsets, out):
         tp = self.model.tp
         if tp is not None and tp.size > 1:
@@ -416,7 +428,7 @@ class LLMEngine:
         self.d_params.copy_(self.h_params, non_blocking=cuda)
         self.stats["h2d_bytes"] += self.h_dec.numel() * 4 + self.h_bt.numel() * 4 + self.h_params.numel() * 4
         self._set_sampling_mode(self.slot_params)
-        if cuda and self.cfg.use_cuda_graphs:
+        if cuda and self.cfg.use_cuda_graphs and self.cfg.callbacks is None:
             key = self._graph_key(B)
             g = self.graphs.get(key)
             if g is None and self.lockstep is None:
@@ -428,6 +440,8 @@ class LLMEngine:
                 self._decode_body(B)
         else:
             self._decode_body(B)
+            if self.cfg.callbacks is not None:
+                self._note_callback_veto(int(i) for i in plan.dec_seq_ids if i >= 0)
         if self.d_status is not None:
             self.h_status.copy_(self.d_status, non_blocking=True)      # lands before the blocking copy below returns
         self.h_out.copy_(self.d_out, non_blocking=False)
@@ -662,7 +676,9 @@ class LLMEngine:
                 self.model.forward(batch, self.kv_caches, return_hidden=True)
                 return np.zeros(0, np.int32)
             else:
-                logits = self.model.forward(batch, self.kv_caches)
+                logits = self.model.forward(batch, self.kv_caches,
+                                            **({"callbacks": self.cfg.callbacks} if self.cfg.callbacks is not None else {}))
+                self._note_callback_veto(int(it.seq_id) for it in plan.prefill)
         finally:
             self.model.op_timer = None
         last_slots = self.h_pf.numpy()[o + n_last:o + 2 * n_last]

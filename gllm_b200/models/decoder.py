@@ -326,11 +326,16 @@ class DecoderModel:
         return self.tp.gemm_allreduce_residual(a, w, x, ss, self._ws.partial[:T], bn=bn)
 
     def forward(self, batch: ForwardBatch, kv_caches: List[torch.Tensor], *, hidden_in=None, decode_ws=None,
-                return_hidden: bool = False, capture_layers=None):
-        """Returns fp32 logits [R, vocab_local_padded] on the last pipeline stage, else the hidden states."""
+                return_hidden: bool = False, capture_layers=None, callbacks=None):
+        """Returns fp32 logits [R, vocab_local_padded] on the last pipeline stage, else the hidden states.
+        ``callbacks``: an ``engine.callbacks.CallbackChain`` run on the residual stream before / after the layers it
+        names (eager forward only, never inside a captured graph): a callback may replace the hidden states (RAG or
+        knowledge injection, layer skipping), end the layer loop early, or veto; what happened is left in
+        ``self.callback_action`` / ``self.callback_info``."""
         if self.sequence_parallel:
-            if capture_layers is not None:
-                raise ValueError("capture_layers is not available with sequence_parallel (no rank holds whole layers' rows)")
+            if capture_layers is not None or callbacks is not None:
+                raise ValueError("capture_layers / callbacks are not available with sequence_parallel (no rank holds "
+                                 "whole layers' rows)")
             return self._forward_sp(batch, kv_caches, hidden_in=hidden_in, decode_ws=decode_ws, return_hidden=return_hidden)
         c = self.cfg
         T = batch.num_tokens
@@ -348,7 +353,13 @@ class DecoderModel:
             if self.fused:
                 ops.rmsnorm(x, None, c.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)
         ss_in = ws.ss0[:T]
+        self.callback_action, self.callback_info = None, {}
+        stop = False
         for li, lw in zip(self.layer_ids, self.layers):
+            if callbacks is not None:
+                ss_in, stop = self._run_callbacks(callbacks, "pre", li, x, ss_in, ws, T)
+                if stop:
+                    break
             # a shared-KV layer projects queries only (n_kv = 0: no K / V tiles, nothing written) and attends over its
             # donor's pages
             shared = lw.kv_donor is not None
@@ -416,6 +427,10 @@ class DecoderModel:
                     self._row_parallel(act, lw.w_down, x, ws.ss_a[:T], T)
             if capture_layers is not None and li in capture_layers:
                 captured[li] = x.clone()
+            if callbacks is not None:
+                ss_in, stop = self._run_callbacks(callbacks, "post", li, x, ss_in, ws, T)
+                if stop:
+                    break
         if capture_layers is not None:
             self.captured = captured
         if not self.last_stage or return_hidden:
@@ -440,6 +455,26 @@ class DecoderModel:
                 else:
                     self.last_mtp_logits.append(ops.gemm(hn, w, out_dtype=torch.float32, bn=256))
         return logits
+
+    def _run_callbacks(self, callbacks, when: str, li: int, x, ss_in, ws, T: int):
+        """One port of the callback chain. Returns (row statistics of x for the next fused GEMM, stop the layer loop)."""
+        from ..engine.callbacks import CallbackAction
+        if li not in callbacks.layers_of_interest(self.cfg.num_layers):
+            return ss_in, False
+        r = callbacks.run(when, li, x)
+        self.callback_info.update(r.info)
+        if r.hidden is not None:
+            x.copy_(r.hidden.to(x.dtype))
+            if self.fused:      # the statistics came from the previous GEMM's epilogue: recompute them for the new rows
+                ops.rmsnorm(x, None, self.cfg.rms_norm_eps, ss_out=ws.ss0[:T], want_y=False)
+                ss_in = ws.ss0[:T]
+        if r.action in (CallbackAction.EXIT_EARLY, CallbackAction.VETO):
+            self.callback_action = r.action
+            self.callback_info.setdefault("stopped_at", (when, li))
+            return ss_in, True
+        if r.action == CallbackAction.REPLACE:
+            self.callback_action = self.callback_action or r.action
+        return ss_in, False
 
     def _forward_sp(self, batch: ForwardBatch, kv_caches, *, hidden_in=None, decode_ws=None, return_hidden=False):
         """The fused dense layer with the residual stream sharded by rows over the tensor-parallel ranks.

@@ -124,6 +124,63 @@ class SemanticGatekeeper:
         self.fired.append((key.key_id, sim))
         return key, sim, payload
 
+    def as_callback(self, device=None, dtype=torch.float32) -> "SgDetectInjectCallback":
+        """The detect / inject pair as one layer callback on the model's device: the detect matrix and the knowledge
+        vectors move there once; per forward it costs one GEMV and, when a key fires, one row update."""
+        return SgDetectInjectCallback(self.layer, self.mem, self.cfg, device=device, dtype=dtype)
+
     def injection_vector(self, key_id: int) -> Optional[torch.Tensor]:
         v = self.mem.knowledge.get(key_id)
         return None if v is None else self.cfg.inject_scale * v
+
+
+from ..engine.callbacks import CallbackAction, CallbackResult, LayerCallback  # noqa: E402
+
+
+class SgDetectInjectCallback(LayerCallback):
+    """SgDetect + SgInject on the residual stream (the reference runs them as ops inside its layer loop: detect at
+    layer L / 2 against the pre-computed keys, injection of the matching knowledge vector into the same stream,
+    src/semantic_gatekeeper/mod.rs, src/engine/mega_kernel_callback.rs:119-201). Here: after the detect layer the last
+    row's hidden state is compared (cosine) with every key in one matrix-vector product on the device; when the best
+    key passes its level's threshold and the cool-down has run out, its knowledge vector (scaled) is added to that row."""
+    priority = 4
+
+    def __init__(self, layer: int, mem: SgSharedMemory, cfg: SemanticGatekeeperConfig, device=None, dtype=torch.float32):
+        self.layers = [layer]
+        self.cfg = cfg
+        self.keys = list(mem.keys)
+        dev = device or "cpu"
+        self.detect = (mem.detect if mem.detect is not None else torch.zeros(0, 1)).to(dev, dtype)
+        self.thresholds = torch.tensor([cfg.thresholds[k.level] for k in self.keys], dtype=torch.float32, device=dev)
+        width = self.detect.shape[1] if self.detect.numel() else 1
+        self.knowledge = torch.zeros((len(self.keys), width), dtype=dtype, device=dev)
+        self.has_knowledge = torch.zeros(len(self.keys), dtype=torch.bool, device=dev)
+        for i, k in enumerate(self.keys):
+            v = mem.knowledge.get(k.key_id)
+            if v is not None:
+                self.knowledge[i] = v.to(dev, dtype)
+                self.has_knowledge[i] = True
+        self._cool = 0
+        self.fired: List[tuple] = []
+
+    def post_layer(self, layer, hidden):
+        if not self.keys:
+            return CallbackResult()
+        if self._cool > 0:
+            self._cool -= 1
+            return CallbackResult()
+        q = torch.nn.functional.normalize(hidden[-1].to(self.detect.dtype), dim=-1)
+        sims = self.detect @ q                                   # [keys]
+        margin = sims.float() - self.thresholds
+        i = int(torch.argmax(margin))
+        if float(margin[i]) < 0:
+            return CallbackResult(info={"sg_best": float(sims[i])})
+        self._cool = self.cfg.cooldown_tokens
+        key = self.keys[i]
+        self.fired.append((key.key_id, float(sims[i])))
+        info = {"sg_fired": key.key_id, "sg_similarity": float(sims[i])}
+        if not bool(self.has_knowledge[i]):
+            return CallbackResult(info=info)
+        h = hidden.clone()
+        h[-1] = (h[-1].float() + self.cfg.inject_scale * self.knowledge[i].float()).to(h.dtype)
+        return CallbackResult(CallbackAction.REPLACE, h, info)
