@@ -196,9 +196,10 @@ class Client:
         return ClientBuilder().model(model_id).kind(ModelKind.CLASSIFIER).config(**kw).build()
 
     @staticmethod
-    def from_model(cfg, weights, tokenizer=None, kind=ModelKind.CHAT, device=None, dtype=None, **kw) -> "Client":
+    def from_model(cfg, weights, tokenizer=None, kind=ModelKind.CHAT, device=None, dtype=None, distributed=None,
+                   **kw) -> "Client":
         """Build a client around in-memory weights (synthetic models, tests)."""
-        c = Client(ClientConfig(**kw))
+        c = Client(ClientConfig(**kw), distributed=distributed)
         c._install(model_id="<memory>", kind=kind, loaded=None, cfg=cfg, weights=weights, tokenizer=tokenizer,
                    device=device, dtype=dtype)
         return c
@@ -233,6 +234,9 @@ class Client:
                         raise InvalidModelTypeError(f"{model_id} has no classifier head")
                     kv_kw = self._kv_cache_plan(cfg, dev)
                     kv_kw["weight_quant"] = self._weight_quant_plan(cfg, dev)
+                    tp = self._tensor_parallel_context(cfg, dev)
+                    if tp is not None:
+                        kv_kw["tp"] = tp
                     model = DecoderModel(cfg, weights, device=dev, dtype=dt,
                                          max_positions=min(cfg.max_position_embeddings, self.config.max_model_len), **kv_kw)
                     ec = EngineConfig(max_num_seqs=self.config.max_num_seqs, max_model_len=self.config.max_model_len,
@@ -250,6 +254,36 @@ class Client:
             except torch.cuda.OutOfMemoryError as e:  # pragma: no cover - needs a GPU
                 raise OutOfMemoryError(str(e)) from e
             self._state = _State(model_id, kind, loaded, model, engine, tokenizer, be)
+
+    def _tensor_parallel_context(self, cfg, dev):
+        """``ClientBuilder.distributed(DistributedConfig)``: with ``parallel.tp`` = world size > 1 every rank of the job
+        (one process per GPU, started by ``torch.distributed.run``) builds its shard of the model over a
+        ``TPContext`` and makes the same client calls with the same arguments; every rank returns the same result.
+        Pipeline stages, expert parallelism and context-parallel prefill are reached through the engine-level APIs
+        (``engine.pp``, ``EPContext``, ``CpPrefill``). Reference: DistributedConfig on the client builder
+        (src/client_fragments/builder.inc.rs:88-220)."""
+        d = self._distributed
+        if d is None:
+            return None
+        import os
+        import torch.distributed as dist
+        world = dist.get_world_size() if dist.is_initialized() else int(os.environ.get("WORLD_SIZE", "1"))
+        d.validate(world)
+        p = d.parallel
+        if p.pp > 1 or p.cp > 1 or (p.ep > 1 and not p.ep_shares_tp):
+            raise GllmError("Client: only tensor-parallel layouts (tp = world size) are built by the client; pipeline, "
+                            "expert-parallel and context-parallel layouts go through the engine-level APIs")
+        if p.tp == 1:
+            return None
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            if dev.type == "cuda":
+                dist.init_process_group("nccl", device_id=dev)
+            else:
+                dist.init_process_group("gloo")
+        from .parallel.tensor_parallel import TPContext
+        return TPContext(dist.get_rank(), world, dev, mode="auto" if dev.type == "cuda" else "nccl",
+                         max_tokens=self.config.max_batch_tokens, hidden=cfg.hidden_size)
 
     _BITS_4 = ("q4", "q5", "iq4", "q3", "iq3", "q2", "iq2", "iq1", "awq", "gptq", "nvfp4", "mxfp4", "int4")
     _BITS_8 = ("q8", "q6", "fp8", "mxfp8", "int8")

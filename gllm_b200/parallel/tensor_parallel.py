@@ -420,8 +420,9 @@ class TPContext:
             idx = torch.empty(B, dtype=torch.int32, device=logits.device)
             ops.argmax(logits, vocab_local, out=idx, out_vals=vals)
             pair = torch.stack([vals, (idx + vocab_start).to(torch.float32)], 1).contiguous()
-            allp = torch.empty((self.size, B, 2), dtype=torch.float32, device=logits.device)
+            allp = torch.empty((self.size * B, 2), dtype=torch.float32, device=logits.device)
             dist.all_gather_into_tensor(allp, pair, group=self.group)
+            allp = allp.view(self.size, B, 2)
             best = allp[:, :, 0].argmax(0)  # first rank wins ties -> lowest vocabulary index
             out.copy_(allp[best, torch.arange(B, device=logits.device), 1].to(torch.int32))
             return out
@@ -430,8 +431,9 @@ class TPContext:
         width = (vocab + self.size - 1) // self.size
         if shard.shape[1] < width:
             shard = torch.nn.functional.pad(shard, (0, width - shard.shape[1]), value=float("-inf"))
-        allv = torch.empty((self.size, B, width), dtype=torch.float32, device=logits.device)
+        allv = torch.empty((self.size * B, width), dtype=torch.float32, device=logits.device)
         dist.all_gather_into_tensor(allv, shard, group=self.group)
+        allv = allv.view(self.size, B, width)
         full = allv.permute(1, 0, 2).reshape(B, self.size * width)
         if self.size * width != vocab:
             from ..models.weights import shard_range

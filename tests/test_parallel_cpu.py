@@ -340,6 +340,17 @@ def test_sequence_parallel_decoder_matches_allreduce_and_unsplit_models(world):
     assert r.stdout.count("SP_DECODER_WORKER_OK") == world
 
 
+def test_client_with_a_tensor_parallel_distributed_config():
+    """The public client under torch.distributed.run: DistributedConfig(parallel.tp = world) builds each rank's shard;
+    every rank makes the same calls and returns the tokens of the unsplit client."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29896", os.path.join(ROOT, "tests", "tp_client_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_CLIENT_WORKER_OK") == 2
+
+
 def test_vocab_parallel_sampling_from_top_k_candidates():
     """Three gloo ranks: every rank sends its 64 best (logit, index) pairs per row instead of its vocabulary shard;
     all ranks sample the same token, inside the global top-k of its row; top-1 and greedy rows give the argmax."""
