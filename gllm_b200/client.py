@@ -75,6 +75,9 @@ class ClientConfig:
     # "auto": nvfp4 for a checkpoint quantised to 4-5 bits, mxfp8 for 6-8 bits, bf16 otherwise (on a GPU, when the model
     # has the shapes of the fused layer).
     weight_quant: str = "bf16"
+    # MoE models with weight paging enabled (ClientBuilder.weight_paging_enabled): experts of every layer kept on the
+    # device, the rest are paged in from pinned host memory per step. 0 = max(4 * experts per token, experts / 4).
+    expert_slots: int = 0
 
 
 @dataclass
@@ -153,7 +156,8 @@ class ClientBuilder:
     def build(self) -> "Client":
         if not self._model:
             raise GllmError("ClientBuilder: model() is required")
-        c = Client(self._cfg, backend=self._backend, distributed=self._distributed, gguf_filter=self._gguf_filter)
+        c = Client(self._cfg, backend=self._backend, distributed=self._distributed, gguf_filter=self._gguf_filter,
+                   weight_paging=self._weight_paging)
         c.load_model(self._model, self._kind)
         if self._reranker:
             c._aux["reranker"] = Client(self._cfg, backend=self._backend)
@@ -166,8 +170,9 @@ class ClientBuilder:
 
 class Client:
     def __init__(self, config: Optional[ClientConfig] = None, backend: Optional[str] = None, distributed=None,
-                 gguf_filter: Optional[str] = None):
+                 gguf_filter: Optional[str] = None, weight_paging: bool = False):
         self.config = config or ClientConfig()
+        self._weight_paging = bool(weight_paging)
         self._backend_name, self._distributed, self._gguf_filter = backend, distributed, gguf_filter
         self._state: Optional[_State] = None
         self._lock = threading.RLock()
@@ -197,9 +202,9 @@ class Client:
 
     @staticmethod
     def from_model(cfg, weights, tokenizer=None, kind=ModelKind.CHAT, device=None, dtype=None, distributed=None,
-                   **kw) -> "Client":
+                   weight_paging: bool = False, **kw) -> "Client":
         """Build a client around in-memory weights (synthetic models, tests)."""
-        c = Client(ClientConfig(**kw), distributed=distributed)
+        c = Client(ClientConfig(**kw), distributed=distributed, weight_paging=weight_paging)
         c._install(model_id="<memory>", kind=kind, loaded=None, cfg=cfg, weights=weights, tokenizer=tokenizer,
                    device=device, dtype=dtype)
         return c
@@ -237,6 +242,9 @@ class Client:
                     tp = self._tensor_parallel_context(cfg, dev)
                     if tp is not None:
                         kv_kw["tp"] = tp
+                    if self._weight_paging and cfg.is_moe and tp is None and not kv_kw.get("weight_quant"):
+                        kv_kw["expert_slots"] = self.config.expert_slots or max(4 * cfg.num_experts_per_tok,
+                                                                                cfg.num_experts // 4)
                     model = DecoderModel(cfg, weights, device=dev, dtype=dt,
                                          max_positions=min(cfg.max_position_embeddings, self.config.max_model_len), **kv_kw)
                     ec = EngineConfig(max_num_seqs=self.config.max_num_seqs, max_model_len=self.config.max_model_len,

@@ -43,15 +43,17 @@ class MoeLayerWeights:
     bs_fmt: Optional[str] = None         # "mxfp8" / "nvfp4": the expert stacks are block-scaled operands (ops/blockscale.py)
     act_tensor_scale: float = 1.0 / 64.0
     _ws: Optional[M.MoeWorkspace] = None
+    paged: Optional["PagedExperts"] = None   # expert stacks in host memory, a few slots of them on the device
 
     # ------------------------------------------------------------------------------------------
     def workspace(self, model, T):
         holder = model.__dict__.setdefault("_moe_ws", {})
-        key = (self.e_local, self.inter)
+        groups = self.paged.slots if self.paged is not None else self.e_local      # paged experts: the groups are slots
+        key = (groups, self.inter)
         ws = holder.get(key)
         if ws is None or ws.ids.shape[0] < T:
             c = self.cfg
-            ws = M.MoeWorkspace(max(T, 256), c.num_experts_per_tok, c.hidden_size, self.inter, self.e_local,
+            ws = M.MoeWorkspace(max(T, 256), c.num_experts_per_tok, c.hidden_size, self.inter, groups,
                                 model.device, model.dtype)
             ws.logits = torch.zeros((max(T, 256), self.router.shape[0]), dtype=torch.float32, device=model.device)
             holder[key] = ws
@@ -64,13 +66,16 @@ class MoeLayerWeights:
         H = c.hidden_size
         rs = dict(row_ss=ws.ss_perm, norm_dim=H, eps=c.rms_norm_eps) if fused_norm else {}
         if self.bs_fmt is None:
+            # paged experts: the stacks are the device slots, the "experts" of the block table are slot numbers
+            w_gu, w_dn, groups = (self.paged.dev_gu, self.paged.dev_dn, self.paged.slots) if self.paged is not None else (
+                self.w_gate_up, self.w_down, self.e_local)
             rows = getattr(ws, "blk_rows", None)      # routed rows per block: padding rows are neither loaded nor stored
             L.set_block_rows(rows)
-            L.gemm_glu(ws.a_perm, self.w_gate_up, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
-                       num_groups=self.e_local, **rs)
+            L.gemm_glu(ws.a_perm, w_gu, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
+                       num_groups=groups, **rs)
             mark("moe_gate_up")
             L.set_block_rows(rows)
-            L.gemm_grouped(ws.act, self.w_down, ws.blk_group, self.e_local, out=ws.y_perm, bn=128)
+            L.gemm_grouped(ws.act, w_dn, ws.blk_group, groups, out=ws.y_perm, bn=128)
             mark("moe_down")
             return
         # block-scaled experts: the routed rows are quantised straight from the token rows into their expert blocks,
@@ -119,6 +124,8 @@ class MoeLayerWeights:
             return self.ep.moe_forward(self, model, x, ss_in, ss_out, ids, w, ws, T)
         if self.tp_experts is not None:
             return self._forward_tp_experts(model, x, x, ss_in, ss_out, ids, w, ws, T, fused_norm=True)
+        if self.paged is not None:
+            return self._forward_paged(model, x, x, ss_in, ss_out, ids, w, ws, T, fused_norm=True)
         M.permute(x, ss_in, ids, ws, self.e0, self.e_local)
         mark("moe_permute")
         self._expert_ffn(model, x, ws, T, fused_norm=True, mark=mark)
@@ -160,6 +167,39 @@ class MoeLayerWeights:
         ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
         return ss
 
+    def _forward_paged(self, model, x, src, ss_in, ss_out, ids, w, ws, T, fused_norm: bool):
+        """Experts paged in from host memory: the step's experts are made resident wave by wave (as many as there are
+        device slots), each wave runs the ordinary grouped GEMMs over the slots and adds its weighted rows to a
+        partial sum; the residual add (and the next norm's statistics) follow once. Costs one host read of the routing
+        per layer, the price of serving a model whose experts do not fit the device."""
+        c = self.cfg
+        H = c.hidden_size
+        pg = self.paged
+        holder = model.__dict__.setdefault("_moe_partial", {})
+        part = holder.get("buf")
+        if part is None or part.shape[0] < T:
+            part = holder["buf"] = torch.zeros((max(T, 256), H), dtype=x.dtype, device=x.device)
+        p = part[:T]
+        p.zero_()
+        used = [int(e) - self.e0 for e in torch.unique(ids).tolist() if self.e0 <= int(e) < self.e0 + self.e_local]
+        pg.after_gate(ids)
+        for i in range(0, len(used), pg.slots):
+            wave = used[i:i + pg.slots]
+            pg.ensure(wave)
+            slot_ids = pg.slot_map(wave).index_select(0, (ids.reshape(-1).long() - self.e0).clamp_(0, self.e_local - 1))
+            outside = (ids.reshape(-1) < self.e0) | (ids.reshape(-1) >= self.e0 + self.e_local)
+            slot_ids = torch.where(outside, torch.full_like(slot_ids, pg.slots), slot_ids).reshape(ids.shape).contiguous()
+            M.permute(src, ss_in if fused_norm else None, slot_ids, ws, 0, pg.slots)
+            self._expert_ffn(model, src, ws, T, fused_norm)
+            M.combine(p, ws.y_perm, ws.dest, w)
+        if self.shared_gate_up is not None:
+            sa = L.gemm_glu(src, self.shared_gate_up, act=model.act_id, row_ss=ss_in if fused_norm else None,
+                            norm_dim=H if fused_norm else 0, eps=c.rms_norm_eps if fused_norm else 0.0, bn=self.shared_bn)
+            p.add_(ops.gemm(sa, self.shared_down, out_dtype=x.dtype, bn=128))
+        ss = None if ss_out is None else ss_out.reshape(-1)[:T].view(T, 1)
+        ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
+        return ss
+
     def forward_unfused(self, model, x, h, T):
         """Unfused path: ``h`` is the already normalised input; adds the MoE output into ``x``."""
         c = self.cfg
@@ -170,6 +210,9 @@ class MoeLayerWeights:
             return
         if self.tp_experts is not None:
             self._forward_tp_experts(model, x, h, None, None, ids, w, ws, T, fused_norm=False)
+            return
+        if self.paged is not None:
+            self._forward_paged(model, x, h, None, None, ids, w, ws, T, fused_norm=False)
             return
         M.permute(h, None, ids, ws, self.e0, self.e_local)
         self._expert_ffn(model, h, ws, T, fused_norm=False)
@@ -229,3 +272,131 @@ def pack_moe_layer(cfg: ModelConfig, src, i: int, tp_rank: int, tp_size: int, de
         lw.shared_gate_up = L.interleave_gate_up(g, u, lw.shared_bn)
         lw.shared_down = L.pad_rows(src.get(p + "shared_expert.down_proj").to(device, dtype), 128).contiguous()
     return lw
+
+
+class PagedExperts:
+    """The expert stacks of one MoE layer in (pinned) host memory with ``slots`` experts resident on the device.
+
+    ``ensure(experts)`` makes a set of experts resident (least recently used slots are reused; loads go through the
+    layer's ``ExpertFaultHandler``, so every miss is counted and retried like a page fault); ``slot_map`` gives the
+    device tensor expert -> slot for the resident ones (``slots`` = not resident, which the grouped GEMMs skip);
+    ``after_gate`` feeds the cross-layer prefetcher, which loads the experts it expects next into slots the current
+    step does not need. Reference: expert weight paging, fault handler and prefetch after the gate
+    (src/scheduler/weight_paging.rs:26-601, src/moe/fault_handler.rs, src/moe/prefetch.rs)."""
+
+    def __init__(self, layer: MoeLayerWeights, layer_index: int, slots: int, pager=None):
+        if layer.bs_fmt is not None or layer.ep is not None or layer.tp_experts is not None:
+            raise ValueError("paged experts: bf16 expert stacks on one rank only")
+        from ..moe.residency import ExpertFaultHandler
+        self.layer_index, self.pager = layer_index, pager
+        self.e_local = layer.e_local
+        self.slots = max(1, min(int(slots), layer.e_local))
+        dev = layer.w_gate_up.device
+        self.rows_gu = layer.w_gate_up.shape[0] // layer.e_local
+        self.rows_dn = layer.w_down.shape[0] // layer.e_local
+        pin = dev.type == "cuda"
+        self.host_gu = layer.w_gate_up.to("cpu").contiguous()
+        self.host_dn = layer.w_down.to("cpu").contiguous()
+        if pin:
+            self.host_gu, self.host_dn = self.host_gu.pin_memory(), self.host_dn.pin_memory()
+        self.dev_gu = torch.zeros((self.slots * self.rows_gu, layer.w_gate_up.shape[1]), dtype=layer.w_gate_up.dtype, device=dev)
+        self.dev_dn = torch.zeros((self.slots * self.rows_dn, layer.w_down.shape[1]), dtype=layer.w_down.dtype, device=dev)
+        layer.w_gate_up = layer.w_down = None          # the full stacks leave the device
+        self.slot_of: dict = {}                        # expert -> slot, least recently used first
+        self.free = list(range(self.slots - 1, -1, -1))
+        self._map = torch.full((self.e_local,), self.slots, dtype=torch.int32, device=dev)
+        self._protected: set = set()
+        self.handler = ExpertFaultHandler(self._load)
+        self.stats = {"hits": 0, "misses": 0, "evictions": 0, "prefetched": 0}
+
+    def resident_bytes(self) -> int:
+        return self.dev_gu.numel() * self.dev_gu.element_size() + self.dev_dn.numel() * self.dev_dn.element_size()
+
+    def _load(self, layer_index: int, e: int):
+        if self.free:
+            slot = self.free.pop()
+        else:
+            victim = next((x for x in self.slot_of if x not in self._protected), None)
+            if victim is None:
+                raise RuntimeError("paged experts: every slot is needed by the current wave")
+            slot = self.slot_of.pop(victim)
+            self.handler.evict(self.layer_index, victim)
+            self._map[victim] = self.slots
+            self.stats["evictions"] += 1
+        self.dev_gu[slot * self.rows_gu:(slot + 1) * self.rows_gu].copy_(self.host_gu[e * self.rows_gu:(e + 1) * self.rows_gu],
+                                                                        non_blocking=True)
+        self.dev_dn[slot * self.rows_dn:(slot + 1) * self.rows_dn].copy_(self.host_dn[e * self.rows_dn:(e + 1) * self.rows_dn],
+                                                                        non_blocking=True)
+        self.slot_of[e] = slot
+        self._map[e] = slot
+
+    def ensure(self, experts):
+        """Make these (local) experts resident; they cannot evict one another."""
+        if len(experts) > self.slots:
+            raise ValueError(f"{len(experts)} experts do not fit {self.slots} slots")
+        self._protected = set(int(e) for e in experts)
+        for e in self._protected:
+            if e in self.slot_of:
+                self.slot_of[e] = self.slot_of.pop(e)      # most recently used
+                self.stats["hits"] += 1
+            else:
+                self.stats["misses"] += 1
+                if not self.handler.ensure(self.layer_index, e):
+                    raise RuntimeError(f"layer {self.layer_index}: expert {e} could not be loaded: "
+                                       f"{self.handler.errors.get((self.layer_index, e))}")
+
+    def slot_map(self, experts) -> torch.Tensor:
+        """[e_local] int32 on the device: slot of each of ``experts``, ``slots`` for every other expert (resident or
+        not: a wave computes only its own experts)."""
+        m = torch.full_like(self._map, self.slots)
+        idx = torch.as_tensor(list(experts), dtype=torch.long, device=m.device)
+        if idx.numel():
+            m[idx] = self._map[idx]
+        return m
+
+    def prefetch(self, e: int) -> bool:
+        """Load an expert the prefetcher expects, into a free slot or over an expert the current wave does not need."""
+        if e in self.slot_of:
+            return False
+        if not self.free and all(x in self._protected for x in self.slot_of):
+            return False
+        if self.handler.ensure(self.layer_index, int(e)):
+            self.stats["prefetched"] += 1
+            return True
+        return False
+
+    def after_gate(self, ids):
+        if self.pager is not None:
+            self.pager.after_gate(self.layer_index, ids)
+
+
+class ExpertPager:
+    """All paged MoE layers of a model and the prefetcher that links them: the experts chosen at layer l predict the
+    experts of the next layers (transition counts learnt while serving), which are loaded ahead of their gate."""
+
+    def __init__(self, num_layers: int, num_experts: int, depth: int = 1, top: int = 4):
+        from ..moe.residency import ExpertPrefetcher
+        self.layers: dict = {}
+        self.prefetcher = ExpertPrefetcher(num_layers, num_experts, depth=depth, top=top)
+
+    def add(self, layer_index: int, paged: PagedExperts):
+        self.layers[layer_index] = paged
+        paged.pager = self
+
+    def after_gate(self, layer_index: int, ids):
+        host = ids.detach().to("cpu")
+        self.prefetcher.observe(layer_index, host)
+        for req in self.prefetcher.predict(layer_index, host):
+            tgt = self.layers.get(req.layer)
+            if tgt is not None:
+                tgt._protected = set()
+                tgt.prefetch(req.expert)
+
+    def stats(self) -> dict:
+        out = {"hits": 0, "misses": 0, "evictions": 0, "prefetched": 0, "faults": 0, "resident_bytes": 0}
+        for pg in self.layers.values():
+            for k in ("hits", "misses", "evictions", "prefetched"):
+                out[k] += pg.stats[k]
+            out["faults"] += pg.handler.stats["faults"]
+            out["resident_bytes"] += pg.resident_bytes()
+        return out

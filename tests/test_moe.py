@@ -87,3 +87,66 @@ def test_moe_layer_matches_dense_masked_reference_and_generates():
     m._moe_ws[next(iter(m._moe_ws))].last_ids = torch.full((4, cfg.num_experts_per_tok), 2, dtype=torch.int32)
     st = obs.capture_expert_load()
     assert st["hot_experts"] == [2] and st["placement"] == MoePlacement.HOT_COLD and st["imbalance"] > 2.0
+
+
+def test_paged_experts_match_the_resident_model():
+    """Experts paged in from host memory (fewer device slots than experts: several waves per layer, evictions, the
+    cross-layer prefetcher) give the logits of the model with every expert resident, in the fused-layout (block
+    table over slots) and through the serving engine."""
+    cfg = preset("tiny-moe")
+    cfg.num_shared_experts = 1
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    full = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256)
+    paged = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256, expert_slots=3)
+    assert cfg.num_experts > 3 and paged.expert_pager is not None
+    moe_layers = [lw.moe for lw in paged.layers if lw.moe is not None]
+    assert all(m.w_gate_up is None and m.paged.slots == 3 for m in moe_layers)
+    from gllm_b200.engine.batch import ForwardBatch
+
+    def batch(T):
+        ids = (torch.arange(T, dtype=torch.int32) * 7 + 2) % cfg.vocab_size
+        return ForwardBatch(token_ids=ids, positions=torch.arange(T, dtype=torch.int32),
+                            slot_mapping=torch.arange(T, dtype=torch.int32), block_tables=torch.arange(4, dtype=torch.int32)[None],
+                            ctx_lens=torch.tensor([T], dtype=torch.int32), q_start=torch.tensor([0], dtype=torch.int32),
+                            q_len=torch.tensor([T], dtype=torch.int32), max_q_len=T)
+    for T in (23, 1, 40):
+        want = full.forward(batch(T), full.alloc_kv_cache(4))
+        got = paged.forward(batch(T), paged.alloc_kv_cache(4))
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    st = paged.expert_pager.stats()
+    assert st["misses"] > 0 and st["evictions"] > 0 and st["faults"] >= st["misses"]
+    one = moe_layers[0].paged
+    assert one.resident_bytes() * cfg.num_experts == 3 * (one.host_gu.numel() + one.host_dn.numel()) * 4
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    ecfg = dict(max_num_seqs=4, max_model_len=128, max_batch_tokens=64, prefill_chunk=32)
+    prompts = [[1, 2, 3, 4, 5], list(range(40))]
+    a = LLMEngine(full, EngineConfig(**ecfg)).generate_batch(prompts, max_tokens=5, temperature=0.0, eos_ids=[])
+    b = LLMEngine(paged, EngineConfig(**ecfg)).generate_batch(prompts, max_tokens=5, temperature=0.0, eos_ids=[])
+    assert [r.token_ids for r in a] == [r.token_ids for r in b]
+    # a load that fails is retried, then reported by name
+    bad = moe_layers[0].paged
+    calls = {"n": 0}
+    good_load = bad.handler.load_fn
+
+    def flaky(layer, e):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise IOError("host copy failed")
+        return good_load(layer, e)
+    bad.handler.load_fn = flaky
+    missing = next(e for e in range(cfg.num_experts) if e not in bad.slot_of)
+    bad.ensure([missing])
+    assert missing in bad.slot_of and calls["n"] == 2
+
+
+def test_client_weight_paging_pages_experts():
+    from gllm_b200.client import Client
+    cfg = preset("tiny-moe")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    kw = dict(device="cpu", dtype=torch.float32, max_num_seqs=2, max_model_len=128, max_batch_tokens=64)
+    plain = Client.from_model(cfg, src, **kw)
+    paging = Client.from_model(cfg, src, weight_paging=True, expert_slots=2, **kw)
+    assert paging._state.model.expert_pager is not None and getattr(plain._state.model, "expert_pager", None) is None
+    a = plain.generate("expert paging").max_tokens(5).temperature(0.0).generate().token_ids
+    b = paging.generate("expert paging").max_tokens(5).temperature(0.0).generate().token_ids
+    assert a == b and paging._state.model.expert_pager.stats()["misses"] > 0
