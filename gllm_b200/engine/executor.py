@@ -101,6 +101,8 @@ class LLMEngine:
         self.device = model.device
         ec = self.cfg
         ec.max_model_len = min(ec.max_model_len, model.max_positions)
+        if ec.callbacks is not None or getattr(model, "expert_pager", None) is not None:
+            ec.use_cuda_graphs = False      # host decisions inside the forward (callback chain, expert paging): eager steps
         self.max_blocks = (ec.max_model_len + 15) // 16
         self.num_pages = ec.num_pages or self._auto_pages()
         self.kv_caches = model.alloc_kv_cache(self.num_pages)
