@@ -401,7 +401,13 @@ class Client:
                                             hook=self._hook_fn(b._hooks), stream=stream_cb)
             except ValueError as e:
                 raise RuntimeGllmError(str(e)) from e
-            st.engine.run_until_done()
+            keep_cb = st.engine.cfg.callbacks
+            if b._callbacks is not None:
+                st.engine.cfg.callbacks = b._callbacks       # the lock is held: this request runs alone
+            try:
+                st.engine.run_until_done()
+            finally:
+                st.engine.cfg.callbacks = keep_cb
             res: GenerateResult = st.engine.results.pop(rid)
         toks = res.token_ids
         if toks and toks[-1] in eos and res.finish_reason == "eos":

@@ -91,6 +91,13 @@ class GenerationBuilder:
         self._images: list = []
         self._audio: list = []
         self._stop: List[int] = []
+        self._callbacks = None
+
+    def callbacks(self, chain):
+        """Run an ``engine.callbacks.CallbackChain`` on the residual stream while this request is generated (RAG or
+        knowledge injection, probes that veto, early exit). The call then runs alone and eagerly."""
+        self._callbacks = chain
+        return self
 
     def max_tokens(self, n: int):
         self._max_tokens = int(n)

@@ -69,3 +69,13 @@ class LateFusionRag:
         _, idx, val = self.retrieve(query, top_k)
         w = torch.softmax(val / temperature, 0)
         return (w[:, None] * self.vecs[idx]).sum(0)
+
+    def generate(self, query: str, *, top_k: int = 2, scale: float = 1.0, **gen):
+        """Answer ``query`` with the best documents fused into the residual stream at the injection layer (no longer
+        prompt): ``gen`` are the generation settings (max_tokens, temperature, ...). Returns the client's response."""
+        from ..engine.callbacks import CallbackChain, RagInjectCallback
+        vec = self.fusion_vector(query, top_k)
+        b = self.client.generate(query).callbacks(CallbackChain([RagInjectCallback(self.layer, vec, scale)]))
+        for k, v in gen.items():
+            b = getattr(b, k)(v)
+        return b.generate()

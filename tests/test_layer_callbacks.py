@@ -127,3 +127,23 @@ def test_engine_runs_the_chain_and_a_veto_ends_the_request():
     eng2 = LLMEngine(m, EngineConfig(callbacks=veto, **base))
     r = eng2.generate_batch([[5, 6, 7, 8]], max_tokens=6, temperature=0.0, eos_ids=[])[0]
     assert r.finish_reason == "vetoed by a layer callback" and len(r.token_ids) <= 1
+
+
+def test_client_generation_with_a_chain_and_late_fusion_rag():
+    from gllm_b200.client import Client
+    from gllm_b200.sdk.rag import LateFusionRag
+    cfg = preset("tiny-qwen3")
+    cfg.num_layers = 4
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    c = Client.from_model(cfg, src, device="cpu", dtype=torch.float32, max_num_seqs=2, max_model_len=128, max_batch_tokens=64)
+    plain = c.generate("what is the capital").max_tokens(6).temperature(0.0).generate()
+    vec = torch.randn(cfg.hidden_size, generator=torch.Generator().manual_seed(2)) * 5.0
+    steered = c.generate("what is the capital").max_tokens(6).temperature(0.0).callbacks(
+        CallbackChain([RagInjectCallback(2, vec, 1.0)])).generate()
+    assert steered.token_ids != plain.token_ids
+    # the chain was for that call only
+    assert c.generate("what is the capital").max_tokens(6).temperature(0.0).generate().token_ids == plain.token_ids
+    rag = LateFusionRag(c)
+    rag.index(["paris is the capital of france", "the mitochondria is the powerhouse of the cell"])
+    out = rag.generate("what is the capital", top_k=1, scale=4.0, max_tokens=6, temperature=0.0)
+    assert len(out.token_ids) >= 1 and c._state.engine.cfg.callbacks is None
