@@ -54,6 +54,35 @@ class Guardrail:
         out = self.check(prompt + r.text)
         return (r if out.allowed else None), out
 
+    def as_callback(self):
+        """The probe as a layer callback (the reference's form: the veto comes out of the forward itself, through
+        callback slot 1, instead of re-encoding the text): after the probe layer the mean of the step's rows (the
+        prompt's tokens in a prefill step, the new token's row in a decode step) is scored; an unsafe score vetoes."""
+        from ..engine.callbacks import CallbackAction, CallbackResult, LayerCallback
+        guard = self
+        unsafe = self.probe.labels.index(self.unsafe_label)
+
+        class _Probe(LayerCallback):
+            priority = 20
+            layers = [guard.layer]
+
+            def post_layer(self, layer, hidden):
+                p = guard.probe.probabilities(hidden.float().mean(0, keepdim=True).cpu())[0]
+                info = {"guardrail_score": float(p[unsafe])}
+                if float(p[unsafe]) > guard.threshold:
+                    return CallbackResult(CallbackAction.VETO, info=info)
+                return CallbackResult(info=info)
+        return _Probe()
+
+    def guarded_generate_in_flight(self, prompt: str, **kw):
+        """Generate with the probe inside the forward: the request ends with finish reason ``vetoed by a layer
+        callback`` as soon as a step's hidden state scores unsafe. Returns the client's response."""
+        from ..engine.callbacks import CallbackChain
+        b = self.client.generate(prompt).callbacks(CallbackChain([self.as_callback()]))
+        for k, val in kw.items():
+            b = getattr(b, k)(val)
+        return b.generate()
+
     def hook(self, prompt: str, every: int = 16) -> GenerationHook:
         """A generation hook that re-checks the running text every ``every`` tokens and terminates on a veto."""
         guard = self

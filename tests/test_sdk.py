@@ -49,6 +49,13 @@ def test_guardrail_intent_stream_guard():
     assert v is not None
     hook = g.hook(unsafe[0], every=1)
     assert hook.post_step(5, 1) in (HookDecision.TERMINATE, HookDecision.CONTINUE)
+    # the probe inside the forward: an unsafe prompt is vetoed by its own prefill step, a safe one generates
+    bad = g.guarded_generate_in_flight(unsafe[0], max_tokens=4, temperature=0.0)
+    assert bad.finish_reason == "vetoed by a layer callback" and len(bad.token_ids) <= 1
+    assert c._st().model.callback_info["guardrail_score"] > g.threshold
+    lax = Guardrail(c, g.probe, g.layer, threshold=2.0)          # a threshold no score reaches: nothing is vetoed
+    good = lax.guarded_generate_in_flight(safe[1], max_tokens=4, temperature=0.0)
+    assert good.finish_reason != "vetoed by a layer callback" and len(good.token_ids) >= 1
     ic = IntentClassifier.train(c, {"greet": safe, "noise": unsafe})
     assert ic.top(safe[2]) == "greet" and ic.top(unsafe[3]) == "noise"
     tr = IntentTracker(ic)
