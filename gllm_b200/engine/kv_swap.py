@@ -30,6 +30,12 @@ class KvSwapManager:
         # the 4-bit tier on the device itself (bf16 / fp32 caches in the [pages, 2, n_kv, 16, D] layout only)
         self.device_tier = None
         self.tier_policy = None        # callable(seq_id) -> PrecisionTier the sequence may wait in (None: KIVI4)
+        # the packed tier keeps the sequence's attention-sink tokens (its first tokens) in 16 bit, as the TurboQuant
+        # runtime of the KV cache does: the pages that hold them take the lossless host path
+        from ..kv_cache.turboquant import TurboQuantConfig
+        self.turboquant = TurboQuantConfig(enabled=device_pool_pages > 0)
+        self.sink_pages = (self.turboquant.sink_tokens + 15) // 16 if self.turboquant.enabled else 0
+        self.sink_keys: Dict[int, List[int]] = {}  # sequence packed on the device -> host keys of its sink pages
         self.packed: Dict[int, List[int]] = {}     # sequence packed on the device -> its pool slots, logical order
         if device_pool_pages > 0 and kv_caches[0].dim() == 5 and kv_caches[0].dtype != torch.float8_e4m3fn:
             from ..kv_cache.device_tier import Kivi4Pool
@@ -98,8 +104,21 @@ class KvSwapManager:
         from ..kv_cache.header import PrecisionTier
         tier = self.tier_policy(int(item.seq_id)) if self.tier_policy is not None else PrecisionTier.KIVI4
         if self.device_tier is not None and tier >= PrecisionTier.KIVI4:
-            slots = self.device_tier.pack([int(p) for p in item.pages])
+            pages = [int(p) for p in item.pages]
+            n_sink = min(self.sink_pages, len(pages))
+            slots = self.device_tier.pack(pages[n_sink:])
             if slots is not None:
+                if n_sink:
+                    self._make_room_on_host(n_sink)
+                    keys = []
+                    for page in pages[:n_sink]:
+                        key = self._next_key
+                        self._next_key += 1
+                        self.swap.register(key, page)
+                        self.swap.execute(DmaCommand.EVICT_TO_DRAM, key)
+                        keys.append(key)
+                    self.swap.tick()
+                    self.sink_keys[int(item.seq_id)] = keys
                 self.packed[int(item.seq_id)] = slots
                 self.forget(int(item.seq_id))
                 self.stats["swapped_out_seqs"] += 1
@@ -124,7 +143,15 @@ class KvSwapManager:
         """Bring a sequence back into the pages the batcher just gave it (the last page may be a fresh, empty one)."""
         slots = self.packed.pop(int(item.seq_id), None)
         if slots is not None:
-            self.device_tier.unpack(slots, [int(p) for p in item.pages][:len(slots)])
+            pages = [int(p) for p in item.pages]
+            keys = self.sink_keys.pop(int(item.seq_id), [])
+            for key, page in zip(keys, pages):
+                if self.swap.records[key].tier == StorageTier.NVME:
+                    self._make_room_on_host(1)
+                self.swap.execute(DmaCommand.PROMOTE_TO_HBM, key, dev_page=page)
+                del self.swap.records[key]
+            self.swap.dev_free.clear()
+            self.device_tier.unpack(slots, pages[len(keys):len(keys) + len(slots)])
             self.track(int(item.seq_id))
             self.stats["swapped_in_seqs"] += 1
             self.stats["unpacked_pages"] += len(slots)
@@ -152,6 +179,7 @@ class KvSwapManager:
         slots = self.packed.pop(int(seq_id), None)
         if slots is not None:
             self.device_tier.release(slots)
+            self.keys[int(seq_id)] = self.sink_keys.pop(int(seq_id), [])      # released with the host copies below
         for key in self.keys.pop(int(seq_id), []):
             r = self.swap.records.pop(key, None)
             if r is None:

@@ -86,6 +86,7 @@ def test_engine_packs_preempted_sequences_on_the_device():
     assert st["packed_seqs"] > 0 and st["packed_pages"] == st["unpacked_pages"] > 0
     assert st["pages_out"] > 0                               # the 8-slot pool overflowed into the host tier
     assert not eng.kv_swap.packed and len(eng.kv_swap.device_tier.free) == 8
+    assert eng.kv_swap.sink_pages == 1 and not eng.kv_swap.sink_keys and not eng.kv_swap.swap.records   # sink pages came back too
     same = sum(a == b for r, w in zip(res, want) for a, b in zip(r.token_ids, w))
     assert same >= 0.5 * 240, same
 
