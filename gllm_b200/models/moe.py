@@ -302,8 +302,13 @@ class PagedExperts:
         self.dev_gu = torch.zeros((self.slots * self.rows_gu, layer.w_gate_up.shape[1]), dtype=layer.w_gate_up.dtype, device=dev)
         self.dev_dn = torch.zeros((self.slots * self.rows_dn, layer.w_down.shape[1]), dtype=layer.w_down.dtype, device=dev)
         layer.w_gate_up = layer.w_down = None          # the full stacks leave the device
-        self.slot_of: dict = {}                        # expert -> slot, least recently used first
-        self.free = list(range(self.slots - 1, -1, -1))
+        # the slots are the arena of a weight page table (one unit per expert): it keeps the LRU order, evicts, and
+        # retries failed copies; pages of the wave being computed are pinned so that they cannot evict one another
+        from ..scheduler.weight_paging import WeightPageTable
+        self.table = WeightPageTable(self.slots, self._copy_in, max_retries=1)
+        for e in range(self.e_local):
+            self.table.add(self._key(e), 1)
+        self.slot_of: dict = {}                        # resident expert -> slot
         self._map = torch.full((self.e_local,), self.slots, dtype=torch.int32, device=dev)
         self._protected: set = set()
         self.handler = ExpertFaultHandler(self._load)
@@ -312,32 +317,42 @@ class PagedExperts:
     def resident_bytes(self) -> int:
         return self.dev_gu.numel() * self.dev_gu.element_size() + self.dev_dn.numel() * self.dev_dn.element_size()
 
-    def _load(self, layer_index: int, e: int):
-        if self.free:
-            slot = self.free.pop()
-        else:
-            victim = next((x for x in self.slot_of if x not in self._protected), None)
-            if victim is None:
-                raise RuntimeError("paged experts: every slot is needed by the current wave")
-            slot = self.slot_of.pop(victim)
-            self.handler.evict(self.layer_index, victim)
-            self._map[victim] = self.slots
-            self.stats["evictions"] += 1
+    def _key(self, e: int) -> str:
+        return f"L{self.layer_index}.experts.{int(e)}"
+
+    def _copy_in(self, page, slot: int):
+        e = int(page.key.rsplit(".", 1)[1])
         self.dev_gu[slot * self.rows_gu:(slot + 1) * self.rows_gu].copy_(self.host_gu[e * self.rows_gu:(e + 1) * self.rows_gu],
                                                                         non_blocking=True)
         self.dev_dn[slot * self.rows_dn:(slot + 1) * self.rows_dn].copy_(self.host_dn[e * self.rows_dn:(e + 1) * self.rows_dn],
                                                                         non_blocking=True)
-        self.slot_of[e] = slot
-        self._map[e] = slot
+
+    def _load(self, layer_index: int, e: int):
+        from ..scheduler.types import Tier
+        slot = self.table.ensure_resident(self._key(e))
+        for other in [x for x in self.slot_of if self.table.pages[self._key(x)].tier != Tier.L1_GPU]:
+            del self.slot_of[other]                      # evicted by the table to make room
+            self._map[other] = self.slots
+            self.handler.evict(self.layer_index, other)
+        self.slot_of[int(e)] = slot
+        self._map[int(e)] = slot
+        self.stats["evictions"] = self.table.stats["evictions"]
+
+    def _pin(self, experts):
+        for e in self._protected:
+            self.table.pages[self._key(e)].pinned = False
+        self._protected = set(int(e) for e in experts)
+        for e in self._protected:
+            self.table.pages[self._key(e)].pinned = True
 
     def ensure(self, experts):
         """Make these (local) experts resident; they cannot evict one another."""
         if len(experts) > self.slots:
             raise ValueError(f"{len(experts)} experts do not fit {self.slots} slots")
-        self._protected = set(int(e) for e in experts)
+        self._pin(experts)
         for e in self._protected:
             if e in self.slot_of:
-                self.slot_of[e] = self.slot_of.pop(e)      # most recently used
+                self.table.ensure_resident(self._key(e))   # a hit: refreshes its place in the LRU order
                 self.stats["hits"] += 1
             else:
                 self.stats["misses"] += 1
@@ -358,7 +373,7 @@ class PagedExperts:
         """Load an expert the prefetcher expects, into a free slot or over an expert the current wave does not need."""
         if e in self.slot_of:
             return False
-        if not self.free and all(x in self._protected for x in self.slot_of):
+        if len(self.slot_of) >= self.slots and all(x in self._protected for x in self.slot_of):
             return False
         if self.handler.ensure(self.layer_index, int(e)):
             self.stats["prefetched"] += 1
@@ -389,7 +404,7 @@ class ExpertPager:
         for req in self.prefetcher.predict(layer_index, host):
             tgt = self.layers.get(req.layer)
             if tgt is not None:
-                tgt._protected = set()
+                tgt._pin(())
                 tgt.prefetch(req.expert)
 
     def stats(self) -> dict:
