@@ -69,14 +69,16 @@ class DecoderModel:
     def __init__(self, cfg: ModelConfig, src, *, device="cpu", dtype=torch.bfloat16, tp=None, max_positions=None,
                  fused: Optional[bool] = None, layers: Optional[range] = None, weight_quant: Optional[str] = None,
                  quant_group: int = 32, ep=None, kv_dtype=None, kv_scale: float = 1.0, expert_quant: Optional[str] = None,
-                 weight_blob: Optional[bool] = None, sequence_parallel: bool = False, expert_slots: Optional[int] = None):
+                 weight_blob: Optional[bool] = None, sequence_parallel: bool = False, expert_slots: Optional[int] = None,
+                 cpu_experts: bool = False):
         """``src`` exposes ``get(name)`` / ``has(name)`` over canonical names; ``tp`` is a
         ``parallel.tensor_parallel.TPContext`` (or None); ``layers`` restricts to a pipeline stage.
         ``sequence_parallel``: between the tensor-parallel GEMMs the residual stream stays sharded by rows (each rank
         keeps ceil(T / tp) rows): the row-parallel GEMMs end in a reduce-scatter instead of an all-reduce and the
         column-parallel GEMMs gather their input rows first (dense bf16 layers of the fused path only).
         ``expert_slots``: keep only this many experts of every MoE layer on the device; the stacks live in pinned host
-        memory and are paged in per step (``models.moe.PagedExperts``), for models whose experts do not fit."""
+        memory and are paged in per step (``models.moe.PagedExperts``), for models whose experts do not fit;
+        ``cpu_experts``: experts that are not resident and received few rows run on the host instead of being fetched."""
         self.cfg, self.device, self.dtype, self.tp = cfg, torch.device(device), dtype, tp
         self.sequence_parallel = bool(sequence_parallel) and tp is not None
         self.tp_rank = tp.rank if tp else 0
@@ -144,7 +146,7 @@ class DecoderModel:
                     from .moe import ExpertPager, PagedExperts
                     if getattr(self, "expert_pager", None) is None:
                         self.expert_pager = ExpertPager(cfg.num_layers, cfg.num_experts)
-                    self.expert_pager.add(i, PagedExperts(lw.moe, i, expert_slots))
+                    self.expert_pager.add(i, PagedExperts(lw.moe, i, expert_slots, cpu_experts=cpu_experts))
                     lw.moe.paged = self.expert_pager.layers[i]
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None

@@ -181,8 +181,21 @@ class MoeLayerWeights:
             part = holder["buf"] = torch.zeros((max(T, 256), H), dtype=x.dtype, device=x.device)
         p = part[:T]
         p.zero_()
-        used = [int(e) - self.e0 for e in torch.unique(ids).tolist() if self.e0 <= int(e) < self.e0 + self.e_local]
+        # where each of the step's experts runs: resident ones on the device right away, with host compute enabled a
+        # bounded share of the rows (experts with few rows that are not resident) on the host from the host copy of the
+        # weights, the rest is fetched (moe.routing.MoeHardwareDispatcher: gpu / cpu / remote)
+        from ..moe.routing import MoeHardwareDispatcher
+        flat = ids.reshape(-1).long() - self.e0
+        local = flat[(flat >= 0) & (flat < self.e_local)]
+        counts = torch.bincount(local, minlength=self.e_local).tolist()
+        pg.thermal.step(counts)
+        plan = MoeHardwareDispatcher(list(pg.slot_of), max_cpu_ratio=pg.max_cpu_ratio,
+                                     cpu_enabled=pg.cpu_experts).dispatch(counts)
+        pg.last_plan = plan
+        used = [a.expert_idx for a in plan.gpu_experts] + [a.expert_idx for a in plan.remote_experts]
         pg.after_gate(ids)
+        for a in plan.cpu_experts:
+            pg.run_on_host(a.expert_idx, src, ss_in if fused_norm else None, ids, w, p, self, model)
         for i in range(0, len(used), pg.slots):
             wave = used[i:i + pg.slots]
             pg.ensure(wave)
@@ -284,7 +297,13 @@ class PagedExperts:
     step does not need. Reference: expert weight paging, fault handler and prefetch after the gate
     (src/scheduler/weight_paging.rs:26-601, src/moe/fault_handler.rs, src/moe/prefetch.rs)."""
 
-    def __init__(self, layer: MoeLayerWeights, layer_index: int, slots: int, pager=None):
+    def __init__(self, layer: MoeLayerWeights, layer_index: int, slots: int, pager=None, cpu_experts: bool = False,
+                 max_cpu_ratio: float = 0.2):
+        from ..moe.routing import ExpertThermalTracker
+        self.cpu_experts, self.max_cpu_ratio = bool(cpu_experts), float(max_cpu_ratio)
+        self.thermal = ExpertThermalTracker(layer.e_local)
+        self.last_plan = None
+        self.glu_bn = layer.glu_bn
         if layer.bs_fmt is not None or layer.ep is not None or layer.tp_experts is not None:
             raise ValueError("paged experts: bf16 expert stacks on one rank only")
         from ..moe.residency import ExpertFaultHandler
@@ -383,6 +402,27 @@ class PagedExperts:
     def after_gate(self, ids):
         if self.pager is not None:
             self.pager.after_gate(self.layer_index, ids)
+
+    def run_on_host(self, e: int, src, row_ss, ids, w, acc, layer: MoeLayerWeights, model):
+        """One expert's rows on the host, from the host copy of its weights (no weight transfer: only the few routed
+        rows cross the bus, twice): acc[t] += w[t, k] * expert_e(src[t]) for every (t, k) routed to ``e``."""
+        c = layer.cfg
+        hit = (ids.long() == (e + layer.e0))                              # [T, k]
+        tok = hit.any(1).nonzero().reshape(-1)
+        if tok.numel() == 0:
+            return
+        x = src.index_select(0, tok).float().cpu()
+        if row_ss is not None:                                            # fused layout: the norm weight is in the weights
+            ss = row_ss.index_select(0, tok).float().reshape(tok.numel(), -1).sum(-1).cpu()
+            x = x * torch.rsqrt(ss / c.hidden_size + c.rms_norm_eps)[:, None]
+        gu = self.host_gu[e * self.rows_gu:(e + 1) * self.rows_gu].float()
+        g, u = L.deinterleave_gate_up(gu, self.glu_bn)
+        a = L._act_ref(x @ g.t(), model.act_id) * (x @ u.t())
+        dn = self.host_dn[e * self.rows_dn:(e + 1) * self.rows_dn].float()[:c.hidden_size]
+        y = a[:, :dn.shape[1]] @ dn.t()
+        wt = (w.float() * hit).sum(1).index_select(0, tok).cpu()
+        acc.index_add_(0, tok, (y * wt[:, None]).to(acc.dtype).to(acc.device))
+        self.stats["host_rows"] = self.stats.get("host_rows", 0) + int(tok.numel())
 
 
 class ExpertPager:

@@ -150,3 +150,30 @@ def test_client_weight_paging_pages_experts():
     a = plain.generate("expert paging").max_tokens(5).temperature(0.0).generate().token_ids
     b = paging.generate("expert paging").max_tokens(5).temperature(0.0).generate().token_ids
     assert a == b and paging._state.model.expert_pager.stats()["misses"] > 0
+
+
+def test_paged_experts_with_host_compute_for_cold_experts():
+    """Hardware dispatch of a paged layer: resident experts on the device, a bounded share of the rows (experts that are
+    not resident and got few rows) computed on the host from the host weights, the rest fetched. Same logits."""
+    cfg = preset("tiny-moe")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=1, std=0.05)
+    full = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256)
+    mixed = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=256, expert_slots=2, cpu_experts=True)
+    from gllm_b200.engine.batch import ForwardBatch
+    T = 31
+    ids = (torch.arange(T, dtype=torch.int32) * 7 + 2) % cfg.vocab_size
+    mk = lambda: ForwardBatch(token_ids=ids, positions=torch.arange(T, dtype=torch.int32),
+                              slot_mapping=torch.arange(T, dtype=torch.int32), block_tables=torch.arange(4, dtype=torch.int32)[None],
+                              ctx_lens=torch.tensor([T], dtype=torch.int32), q_start=torch.tensor([0], dtype=torch.int32),
+                              q_len=torch.tensor([T], dtype=torch.int32), max_q_len=T)
+    want = full.forward(mk(), full.alloc_kv_cache(4))
+    for _ in range(2):      # the second pass starts with resident experts: all three destinations are in the plan
+        got = mixed.forward(mk(), mixed.alloc_kv_cache(4))
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    pgs = [lw.moe.paged for lw in mixed.layers if lw.moe is not None]
+    assert sum(pg.stats.get("host_rows", 0) for pg in pgs) > 0
+    plan = pgs[0].last_plan
+    assert plan.gpu_experts and plan.cpu_experts
+    rows = sum(a.token_count for a in plan.gpu_experts + plan.cpu_experts + plan.remote_experts)
+    assert sum(a.token_count for a in plan.cpu_experts) <= 0.2 * rows + 1e-9
+    assert pgs[0].thermal.state(plan.gpu_experts[0].expert_idx) in ("hot", "warm")
