@@ -78,6 +78,7 @@ class ClientConfig:
     # MoE models with weight paging enabled (ClientBuilder.weight_paging_enabled): experts of every layer kept on the
     # device, the rest are paged in from pinned host memory per step. 0 = max(4 * experts per token, experts / 4).
     expert_slots: int = 0
+    debug: bool = False              # ClientBuilder.debug_jit(): eager steps with per-layer NaN / Inf checks
 
 
 @dataclass
@@ -141,7 +142,10 @@ class ClientBuilder:
         return self
 
     def debug_jit(self, on: bool = True):
+        """Debug serving. The reference dumps its JIT's instruction stream here; this engine has no JIT, so the switch
+        turns on what debugging a forward needs instead: eager steps and a non-finite check after every layer."""
         self._debug = on
+        self._cfg.debug = bool(on)
         return self
 
     def weight_paging_enabled(self, on: bool = True):
@@ -251,7 +255,8 @@ class Client:
                                       max_batch_tokens=self.config.max_batch_tokens,
                                       prefill_chunk=self.config.max_batch_tokens,
                                       enable_prefix_cache=self.config.enable_prefix_cache,
-                                      use_cuda_graphs=self.config.use_cuda_graphs, seed=self.config.seed)
+                                      use_cuda_graphs=self.config.use_cuda_graphs, seed=self.config.seed,
+                                      debug=self.config.debug)
                     if dev.type != "cuda":
                         ec.num_pages = max(64, self.config.max_num_seqs * ((ec.max_model_len + 15) // 16) // 4)
                     engine = LLMEngine(model, ec, tokenizer=tokenizer)

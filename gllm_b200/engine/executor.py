@@ -59,6 +59,9 @@ class EngineConfig:
     # veto, early exit). Steps then run eagerly (no CUDA graphs). The stock callbacks look at the last row of the step,
     # i.e. they are meant for one request at a time (max_num_seqs = 1); a veto ends every request of the step.
     callbacks: Optional[object] = None
+    # debug serving: eager steps with a NaN / Inf check of the residual stream after every layer and of the logits
+    # (engine/guard.py::NanTrap; FloatingPointError names the first offender; tensors are dumped to GLLM_DUMP_DIR)
+    debug: bool = False
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
@@ -101,6 +104,14 @@ class LLMEngine:
         self.device = model.device
         ec = self.cfg
         ec.max_model_len = min(ec.max_model_len, model.max_positions)
+        self.nan_trap = None
+        if ec.debug:
+            from .callbacks import CallbackChain
+            from .guard import NanTrap, nan_check_callback
+            self.nan_trap = NanTrap(enabled=True)
+            chain = ec.callbacks if ec.callbacks is not None else CallbackChain([])
+            chain.add(nan_check_callback(self.nan_trap))
+            ec.callbacks = chain
         if ec.callbacks is not None or getattr(model, "expert_pager", None) is not None:
             ec.use_cuda_graphs = False      # host decisions inside the forward (callback chain, expert paging): eager steps
         self.max_blocks = (ec.max_model_len + 15) // 16
@@ -400,6 +411,8 @@ class LLMEngine:
                 self._vetoed[rid] = "vetoed by a layer callback"
 
     def _sample(self, logits, params, offsets, out):
+        if self.nan_trap is not None:
+            self.nan_trap.check("logits", logits)
         tp = self.model.tp
         if tp is not None and tp.size > 1:
             # the greedy fast path (pairs instead of full logit rows) is fixed per captured graph

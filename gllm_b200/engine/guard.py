@@ -81,3 +81,18 @@ def dump_tensors(tensors: Dict[str, torch.Tensor], directory: str):
     os.makedirs(directory, exist_ok=True)
     for name, t in tensors.items():
         torch.save(t.detach().cpu(), os.path.join(directory, name.replace("/", "_") + ".pt"))
+
+
+def nan_check_callback(trap: "NanTrap"):
+    """A layer callback that runs the trap on the residual stream after every layer (debug serving: the first layer
+    that produces a non-finite value is named in the exception)."""
+    from .callbacks import CallbackResult, LayerCallback
+
+    class _NanCheck(LayerCallback):
+        priority = 100
+        layers = None
+
+        def post_layer(self, layer, hidden):
+            trap.check(f"hidden after layer {layer}", hidden)
+            return CallbackResult()
+    return _NanCheck()

@@ -147,3 +147,21 @@ def test_client_generation_with_a_chain_and_late_fusion_rag():
     rag.index(["paris is the capital of france", "the mitochondria is the powerhouse of the cell"])
     out = rag.generate("what is the capital", top_k=1, scale=4.0, max_tokens=6, temperature=0.0)
     assert len(out.token_ids) >= 1 and c._state.engine.cfg.callbacks is None
+
+
+def test_debug_serving_names_the_first_non_finite_layer():
+    import pytest
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    cfg, src, m = _model()
+    base = dict(max_num_seqs=1, max_model_len=96, max_batch_tokens=64, prefill_chunk=64, enable_prefix_cache=False, num_pages=16)
+    eng = LLMEngine(m, EngineConfig(debug=True, **base))
+    ok = eng.generate_batch([[5, 6, 7, 8]], max_tokens=3, temperature=0.0, eos_ids=[])[0]
+    assert len(ok.token_ids) == 3 and eng.nan_trap.checked > 0
+    # poison one weight of layer 2: the trap names that layer
+    w = m.layers[2].wo
+    keep = w.clone()
+    w[0, 0] = float("nan")
+    eng2 = LLMEngine(m, EngineConfig(debug=True, **base))
+    with pytest.raises(FloatingPointError, match="hidden after layer 2"):
+        eng2.generate_batch([[5, 6, 7, 8]], max_tokens=3, temperature=0.0, eos_ids=[])
+    w.copy_(keep)
