@@ -594,6 +594,42 @@ class LLMEngine:
         return self.add_request(h.prompt, max_tokens=p["max_tokens"], temperature=p["temperature"], top_k=p["top_k"],
                                 top_p=p["top_p"], eos_ids=p["eos_ids"], request_id=h.request_id)
 
+    def add_request_context_parallel(self, prompt_ids: List[int], cp_rank: int, cp_size: int, group=None, **kw) -> int:
+        """A long prompt prefilled by ``cp_size`` engines together (every rank of ``group`` makes this call with the same
+        prompt): each rank runs the layers on its page-aligned shard of the prompt's full pages, the ranks exchange
+        the KV pages layer by layer (``parallel.context_parallel.CpPrefill``), and every rank ends with the whole
+        prompt's pages as cached prefix pages of its own pool. The request is then admitted as usual: it finds the
+        pages and computes only the partial last page before decoding, on every rank alike (or on the one rank that
+        keeps the request, when the others abort theirs). Falls back to a plain ``add_request`` on all ranks when any
+        rank cannot take part (prefix already cached there, too few free pages, a prompt shorter than one page per
+        rank). Reference: context-parallel prefill (src/engine/coordinator/context_parallel.rs:76-127, 286-390)."""
+        prompt = [int(t) for t in prompt_ids]
+        n_full = len(prompt) // 16
+        per = (n_full + cp_size - 1) // max(cp_size, 1)
+        ok = (cp_size > 1 and self.cfg.enable_prefix_cache and per * (cp_size - 1) < n_full
+              and not self.mc.is_mla and self.pp is None
+              and len(self.batcher.lookup_prefix_pages(prompt[:n_full * 16])) == 0
+              and self.batcher.num_free_pages >= n_full + (len(prompt) + int(kw.get("max_tokens", 256))) // 16 + 2)
+        if cp_size > 1:
+            import torch.distributed as dist
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            ok = bool(int(flag[0]))
+        if not ok:
+            return self.add_request(prompt, **kw)
+        from ..parallel.context_parallel import CpConfig, CpPrefill
+        dst = self.batcher.import_prefix(prompt[:n_full * 16], "")
+        if len(dst) != n_full or min(dst) < 0:
+            raise RuntimeError("context-parallel prefill: the page pool changed between the check and the import")
+        bt = torch.tensor([dst], dtype=torch.int32, device=self.device)
+        cp = CpPrefill(CpConfig(cp_size, cp_rank), [n_full * 16], bt, group=group)
+        batch = cp.local_batch([prompt[:n_full * 16]])
+        self._ep_bound(False)
+        self.model.forward(batch, self.kv_caches, return_hidden=True)
+        self.stats["cp_prefill_tokens"] = self.stats.get("cp_prefill_tokens", 0) + batch.num_tokens
+        self.stats["cp_prefills"] = self.stats.get("cp_prefills", 0) + 1
+        return self.add_request(prompt, **kw)
+
     def _remaining_tokens(self, rid: int) -> int:
         st = self.batcher.state_of(rid)
         if st is None:

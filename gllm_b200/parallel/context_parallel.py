@@ -128,8 +128,8 @@ class RingAttention:
 class CpPrefill:
     """Context-parallel prefill of whole prompts inside ``DecoderModel.forward``.
 
-    ``seq_lens``: prompt lengths; ``block_tables`` [S, max_blocks]: the sequences' pages, identical on every rank
-    (each rank's cache uses the same page ids). Rank r of W owns pages [r * ceil(P / W), (r + 1) * ceil(P / W)) of a
+    ``seq_lens``: prompt lengths; ``block_tables`` [S, max_blocks]: the sequences' pages in THIS rank's cache (the
+    ranks may hold a logical page under different page ids: what travels is page contents, in logical order). Rank r of W owns pages [r * ceil(P / W), (r + 1) * ceil(P / W)) of a
     sequence of P pages. ``local_batch`` builds the rank's ``ForwardBatch`` (its shard's tokens at their absolute
     positions; context = everything up to the shard's end); the model calls ``exchange`` after each layer wrote its
     K/V; ``last_logits`` returns each sequence's last-token logits on every rank.

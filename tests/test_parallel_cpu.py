@@ -351,6 +351,18 @@ def test_client_with_a_tensor_parallel_distributed_config():
     assert r.stdout.count("TP_CLIENT_WORKER_OK") == 2
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_engines_prefill_a_long_prompt_together(world):
+    """``LLMEngine.add_request_context_parallel``: the ranks' engines split the prompt's full pages, exchange KV pages
+    per layer, admit the request on the cached pages; tokens equal a single engine's, pools may differ per rank."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29840 + world), os.path.join(ROOT, "tests", "cp_engine_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("CP_ENGINE_WORKER_OK") == world
+
+
 def test_vocab_parallel_sampling_from_top_k_candidates():
     """Three gloo ranks: every rank sends its 64 best (logit, index) pairs per row instead of its vocabulary shard;
     all ranks sample the same token, inside the global top-k of its row; top-1 and greedy rows give the argmax."""
