@@ -605,8 +605,10 @@ class LLMEngine:
         rank). Reference: context-parallel prefill (src/engine/coordinator/context_parallel.rs:76-127, 286-390)."""
         prompt = [int(t) for t in prompt_ids]
         n_full = len(prompt) // 16
-        per = (n_full + cp_size - 1) // max(cp_size, 1)
-        ok = (cp_size > 1 and self.cfg.enable_prefix_cache and per * (cp_size - 1) < n_full
+        from ..parallel.context_parallel import CpConfig, CpPrefill
+        zigzag = n_full >= 4 * cp_size          # balanced causal work once every rank gets two chunks of some size
+        ok = (cp_size > 1 and self.cfg.enable_prefix_cache
+              and CpPrefill.every_rank_has_tokens(n_full * 16, cp_size, zigzag)
               and not self.mc.is_mla and self.pp is None
               and len(self.batcher.lookup_prefix_pages(prompt[:n_full * 16])) == 0
               and self.batcher.num_free_pages >= n_full + (len(prompt) + int(kw.get("max_tokens", 256))) // 16 + 2)
@@ -617,12 +619,11 @@ class LLMEngine:
             ok = bool(int(flag[0]))
         if not ok:
             return self.add_request(prompt, **kw)
-        from ..parallel.context_parallel import CpConfig, CpPrefill
         dst = self.batcher.import_prefix(prompt[:n_full * 16], "")
         if len(dst) != n_full or min(dst) < 0:
             raise RuntimeError("context-parallel prefill: the page pool changed between the check and the import")
         bt = torch.tensor([dst], dtype=torch.int32, device=self.device)
-        cp = CpPrefill(CpConfig(cp_size, cp_rank), [n_full * 16], bt, group=group)
+        cp = CpPrefill(CpConfig(cp_size, cp_rank), [n_full * 16], bt, group=group, zigzag=zigzag)
         batch = cp.local_batch([prompt[:n_full * 16]])
         self._ep_bound(False)
         self.model.forward(batch, self.kv_caches, return_hidden=True)

@@ -136,24 +136,32 @@ class CpPrefill:
     Reference: CpConfig / RingAttentionPlan (src/engine/coordinator/context_parallel.rs:76-127, 286-390); the ring
     of send/recv rounds becomes one all-gather of pages per layer."""
 
-    def __init__(self, cfg: CpConfig, seq_lens, block_tables: torch.Tensor, group=None, page: int = 16):
-        self.cfg, self.group, self.page = cfg, group, page
+    def __init__(self, cfg: CpConfig, seq_lens, block_tables: torch.Tensor, group=None, page: int = 16,
+                 zigzag: bool = False):
+        """``zigzag``: a sequence is cut into 2 W page-aligned chunks and rank r takes chunks r and 2 W - 1 - r, so that
+        under a causal mask every rank attends over about the same number of (query, key) pairs (with contiguous
+        shards the last rank does 2 W - 1 times the work of the first)."""
+        self.cfg, self.group, self.page, self.zigzag = cfg, group, page, zigzag
         self.seq_lens = [int(x) for x in seq_lens]
         self.block_tables = block_tables
         W = cfg.cp_size
-        self.bounds = []           # per sequence: [(tok0, tok1)] per rank
+        n_chunks = 2 * W if zigzag else W
+        self.bounds = []           # per sequence: (tok0, tok1) of chunk c
+        self.chunks = []           # per sequence: per rank the list of its non-empty (tok0, tok1) chunks, ascending
         for L in self.seq_lens:
             pages = (L + page - 1) // page
-            per = (pages + W - 1) // W
-            self.bounds.append([(min(L, r * per * page), min(L, (r + 1) * per * page)) for r in range(W)])
+            per = (pages + n_chunks - 1) // n_chunks
+            cb = [(min(L, c * per * page), min(L, (c + 1) * per * page)) for c in range(n_chunks)]
+            self.bounds.append(cb)
+            mine = [[cb[r]] + ([cb[2 * W - 1 - r]] if zigzag else []) for r in range(W)]
+            self.chunks.append([[c for c in m if c[1] > c[0]] for m in mine])
         # pages each rank writes (over all sequences), padded to one length for the all-gather
         bt = block_tables.cpu()
         self.rank_pages = []
         for r in range(W):
             ids = []
-            for s, b in enumerate(self.bounds):
-                t0, t1 = b[r]
-                if t1 > t0:
+            for s in range(len(self.seq_lens)):
+                for t0, t1 in self.chunks[s][r]:
                     ids += bt[s, t0 // page:(t1 + page - 1) // page].tolist()
             self.rank_pages.append(ids)
         self.max_pages = max(1, max(len(x) for x in self.rank_pages))
@@ -162,31 +170,45 @@ class CpPrefill:
         pad = self.rank_pages[cfg.cp_rank] + [self.rank_pages[cfg.cp_rank][-1] if self.rank_pages[cfg.cp_rank] else 0] * (
             self.max_pages - len(self.rank_pages[cfg.cp_rank]))
         self._mine_padded = torch.tensor(pad, dtype=torch.long, device=dev)
-        self.owner = [max((r for r in range(W) if b[r][1] > b[r][0]), default=0) for b in self.bounds]
+        self.owner = [next((r for r in range(W) if any(t1 == L for _, t1 in self.chunks[s][r])), 0)
+                      for s, L in enumerate(self.seq_lens)]
+
+    @staticmethod
+    def every_rank_has_tokens(n_tokens: int, cp_size: int, zigzag: bool = False, page: int = 16) -> bool:
+        """Whether cutting ``n_tokens`` this way leaves no rank without a token (a rank without rows cannot run)."""
+        n_chunks = 2 * cp_size if zigzag else cp_size
+        pages = (n_tokens + page - 1) // page
+        per = (pages + n_chunks - 1) // n_chunks
+        return per > 0 and (cp_size - 1) * per < pages       # chunk W - 1 (every rank's lowest chunk index is <= it)
 
     def local_batch(self, token_ids_per_seq):
-        """The rank's prefill batch: for each sequence the tokens of its shard (possibly none)."""
+        """The rank's prefill batch: one entry per chunk it owns (a chunk's queries are the last tokens of the context
+        that ends with it); ``logits_rows`` has one row per sequence (its last token's row on the owner rank)."""
         from ..engine.batch import ForwardBatch
         r, page = self.cfg.cp_rank, self.page
         dev = self.block_tables.device
-        toks, pos, slots, q_start, q_len, ctx, rows = [], [], [], [], [], [], []
+        toks, pos, slots, q_start, q_len, ctx, entry_seq = [], [], [], [], [], [], []
+        rows = [0] * len(self.seq_lens)
         bt = self.block_tables.cpu()
         n = 0
         for s, ids in enumerate(token_ids_per_seq):
-            t0, t1 = self.bounds[s][r]
-            q_start.append(n)
-            q_len.append(t1 - t0)
-            ctx.append(t1 if t1 > t0 else 0)
-            for t in range(t0, t1):
-                toks.append(int(ids[t]))
-                pos.append(t)
-                slots.append(int(bt[s, t // page]) * page + t % page)
-            n += t1 - t0
-            rows.append(max(n - 1, 0))        # the shard's last row (the sequence's last token on its owner rank)
+            for t0, t1 in self.chunks[s][r]:
+                q_start.append(n)
+                q_len.append(t1 - t0)
+                ctx.append(t1)
+                entry_seq.append(s)
+                for t in range(t0, t1):
+                    toks.append(int(ids[t]))
+                    pos.append(t)
+                    slots.append(int(bt[s, t // page]) * page + t % page)
+                n += t1 - t0
+                if t1 == self.seq_lens[s]:
+                    rows[s] = n - 1       # the sequence's last token lives on this rank
         if n == 0:
             raise ValueError("context parallel prefill: this rank received no tokens (prompts shorter than one page per rank)")
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-        b = ForwardBatch(token_ids=i32(toks), positions=i32(pos), slot_mapping=i32(slots), block_tables=self.block_tables,
+        tables = self.block_tables.index_select(0, torch.tensor(entry_seq, dtype=torch.long, device=dev)).contiguous()
+        b = ForwardBatch(token_ids=i32(toks), positions=i32(pos), slot_mapping=i32(slots), block_tables=tables,
                          ctx_lens=i32(ctx), q_start=i32(q_start), q_len=i32(q_len), max_q_len=max(q_len),
                          logits_rows=torch.tensor(rows, dtype=torch.long, device=dev))
         b.cp = self

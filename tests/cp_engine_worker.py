@@ -33,6 +33,16 @@ def main():
         one = LLMEngine(model, EngineConfig(**ecfg))
         want = one.generate_batch([prompt], max_tokens=6, temperature=0.0, eos_ids=[])[0].token_ids
         assert res.token_ids == want, (res.token_ids, want)
+    # a prompt long enough for two chunks per rank: zig-zag shards (balanced causal work)
+    if world == 2:
+        long2 = ((torch.arange(140) * 13 + 1) % cfg.vocab_size).tolist()      # 8 full pages + 12 tokens
+        rid3 = eng.add_request_context_parallel(long2, rank, world, max_tokens=4, temperature=0.0, eos_ids=[])
+        eng.run_until_done()
+        assert eng.stats["cp_prefills"] == 2 and eng.results[rid3].telemetry.cached_prefix_tokens == 128
+        if rank == 0:
+            one = LLMEngine(model, EngineConfig(**ecfg))
+            assert eng.results[rid3].token_ids == one.generate_batch([long2], max_tokens=4, temperature=0.0, eos_ids=[])[0].token_ids
+        eng.stats["cp_prefills"] = 1
     # a short prompt: every rank falls back to the ordinary path
     rid2 = eng.add_request_context_parallel(prompt[:20], rank, world, max_tokens=2, temperature=0.0, eos_ids=[])
     eng.run_until_done()

@@ -9,6 +9,8 @@ import torch.distributed as dist
 
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "cpu"
+    zigzag = mode.endswith("_zigzag")
+    mode = mode.replace("_zigzag", "")
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     cpu = mode == "cpu"
     if cpu:
@@ -37,7 +39,9 @@ def main():
     prompts = [((torch.arange(L) * (7 + i) + 3) % cfg.vocab_size).tolist() for i, L in enumerate(lens)]
 
     # context parallel: this rank's shard of every prompt
-    cp = CpPrefill(CpConfig(world, rank), lens, bt)
+    cp = CpPrefill(CpConfig(world, rank), lens, bt, zigzag=zigzag)
+    if zigzag and world == 2:      # rank 0 takes the first and the last quarter of the long prompt
+        assert [len(c) for c in cp.chunks[0]] == [2, 2] and cp.owner[0] == 0
     kv_cp = model.alloc_kv_cache(pages)
     local = model.forward(cp.local_batch(prompts), kv_cp)[:, :cfg.vocab_size].float()
     got = cp.last_logits(local)

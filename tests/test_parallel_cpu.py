@@ -379,11 +379,12 @@ def test_context_parallel_prefill_matches_single_rank_prefill(world):
     """Page-aligned prompt shards, KV pages exchanged after every layer's K/V write: same last-token logits and the
     same cache contents on every rank as one rank prefilling the whole prompts (gloo ranks)."""
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29850 + world), os.path.join(ROOT, "tests", "cp_worker.py"), "cpu"]
-    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
-    assert r.stdout.count("CP_WORKER_OK") == world
+    for mode in ("cpu", "cpu_zigzag"):      # contiguous shards, then two chunks per rank (balanced causal work)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+               "127.0.0.1", "--master-port", str(29850 + world), os.path.join(ROOT, "tests", "cp_worker.py"), mode]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        assert r.stdout.count("CP_WORKER_OK") == world
 
 
 def test_lockstep_engines_with_expert_parallel_moe_match_unsplit_engine():
