@@ -202,8 +202,7 @@ class CpPrefill:
                     pos.append(t)
                     slots.append(int(bt[s, t // page]) * page + t % page)
                 n += t1 - t0
-                if t1 == self.seq_lens[s]:
-                    rows[s] = n - 1       # the sequence's last token lives on this rank
+                rows[s] = n - 1           # last row of the rank's highest chunk: on the owner rank the sequence's last token
         if n == 0:
             raise ValueError("context parallel prefill: this rank received no tokens (prompts shorter than one page per rank)")
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
