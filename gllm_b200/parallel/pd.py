@@ -97,6 +97,29 @@ class SaguaroLink:
         self.comm.recv(buf, self.draft_rank)
         return buf[1:1 + int(buf[0])].tolist()
 
+    def send_tokens(self, tokens: Sequence[int], dst: int, cap="draft", length_field=None):
+        """A variable-length token message: one int32 header [length or a negative control code, capacity], then the
+        body. ``cap=None`` sizes the body to the message (prompts); the default body has ``max_draft + 1`` slots."""
+        n = len(tokens)
+        size = n if cap is None else self.max_draft + 1
+        if n > size:
+            raise ValueError(f"{n} tokens do not fit a message of {size}")
+        self.comm.send(torch.tensor([n if length_field is None else length_field, size], dtype=torch.int32), dst)
+        if size:
+            body = torch.full((size,), -1, dtype=torch.int32)
+            body[:n] = torch.as_tensor(list(tokens), dtype=torch.int32)
+            self.comm.send(body, dst)
+
+    def recv_tokens(self, src: int, cap="draft"):
+        """(tokens, length field) of a ``send_tokens`` message."""
+        head = torch.empty(2, dtype=torch.int32)
+        self.comm.recv(head, src)
+        n, size = int(head[0]), int(head[1])
+        body = torch.empty(size, dtype=torch.int32)
+        if size:
+            self.comm.recv(body, src)
+        return body[:max(n, 0)].tolist(), n
+
     def send_verdict(self, accepted: int, correction: int):
         self.comm.send(torch.tensor([accepted, correction], dtype=torch.int32), self.draft_rank)
 

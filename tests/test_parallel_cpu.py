@@ -363,6 +363,18 @@ def test_engines_prefill_a_long_prompt_together(world):
     assert r.stdout.count("CP_ENGINE_WORKER_OK") == world
 
 
+@pytest.mark.parametrize("how", ["same", "other"])
+def test_saguaro_draft_and_verify_on_different_ranks(how):
+    """Rank 1 drafts with its own model, rank 0 verifies inside the serving engine: tokens equal plain greedy decoding
+    of the target; with identical weights every draft is accepted, with another draft model some are rejected."""
+    env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29830 + (how == "same")), os.path.join(ROOT, "tests", "saguaro_worker.py"), how]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("SAGUARO_WORKER_OK") == 2
+
+
 def test_vocab_parallel_sampling_from_top_k_candidates():
     """Three gloo ranks: every rank sends its 64 best (logit, index) pairs per row instead of its vocabulary shard;
     all ranks sample the same token, inside the global top-k of its row; top-1 and greedy rows give the argmax."""
