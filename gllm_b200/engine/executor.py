@@ -575,20 +575,41 @@ class LLMEngine:
         if self.pd_link is not None:
             self.pd_link.send(PdHandoff(rid, prompt, first_token, meta, pages))
 
+    def export_prefix_pages(self, tokens: List[int]):
+        """(number of cached full pages, their KV [layers, pages, ...]) of the longest cached prefix of ``tokens`` in this
+        pool, or (0, None): what a peer needs to continue the same conversation (KV distribution modes)."""
+        n_full = len(tokens) // 16
+        have = list(self.batcher.lookup_prefix_pages([int(t) for t in tokens[:n_full * 16]])) if n_full else []
+        if not have:
+            return 0, None
+        idx = torch.as_tensor(have, dtype=torch.long, device=self.device)
+        pages = torch.stack([(c.view(torch.uint8) if c.dtype == torch.float8_e4m3fn else c).index_select(0, idx)
+                             for c in self.kv_caches]).contiguous()
+        return len(have), pages
+
+    def import_prefix_pages(self, tokens: List[int], pages) -> int:
+        """The first ``pages.shape[1]`` full pages of ``tokens`` become cached prefix pages of this pool (pages already
+        cached here are kept as they are). Returns how many pages were written."""
+        n = 0 if pages is None else int(pages.shape[1])
+        if n == 0:
+            return 0
+        dst = self.batcher.import_prefix([int(t) for t in tokens[:n * 16]], "")
+        sel = [i for i, p in enumerate(dst) if p >= 0]          # -1: that page is already cached here
+        if sel:
+            src_idx = torch.as_tensor(sel, dtype=torch.long, device=self.device)
+            dst_idx = torch.as_tensor([dst[i] for i in sel], dtype=torch.long, device=self.device)
+            pages = pages.to(self.device)
+            for l, c in enumerate(self.kv_caches):
+                tgt = c.view(torch.uint8) if c.dtype == torch.float8_e4m3fn else c
+                tgt.index_copy_(0, dst_idx, pages[l].index_select(0, src_idx))
+        return len(sel)
+
     def import_handoff(self, h) -> int:
         """Decode-only role: the prompt's full pages become cached prefix pages of this pool, then the request is
         admitted; its admission finds them and computes only the partial last page before decoding."""
         n_full = len(h.prompt) // 16
         if n_full and h.pages is not None:
-            dst = self.batcher.import_prefix(h.prompt[:n_full * 16], "")
-            sel = [i for i, p in enumerate(dst) if p >= 0]          # -1: that page is already cached here
-            if sel:
-                src_idx = torch.as_tensor(sel, dtype=torch.long, device=self.device)
-                dst_idx = torch.as_tensor([dst[i] for i in sel], dtype=torch.long, device=self.device)
-                pages = h.pages.to(self.device)
-                for l, c in enumerate(self.kv_caches):
-                    tgt = c.view(torch.uint8) if c.dtype == torch.float8_e4m3fn else c
-                    tgt.index_copy_(0, dst_idx, pages[l].index_select(0, src_idx))
+            self.import_prefix_pages(h.prompt[:n_full * 16], h.pages)
         self.stats["pd_imported"] = self.stats.get("pd_imported", 0) + 1
         p = h.params
         return self.add_request(h.prompt, max_tokens=p["max_tokens"], temperature=p["temperature"], top_k=p["top_k"],

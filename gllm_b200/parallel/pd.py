@@ -79,6 +79,56 @@ def kv_dist_plan(mode: KvDistMode, rank: int, world: int, n_kv_heads: int) -> Di
     return {"store_heads": list(range(n_kv_heads)), "fetch_on_miss": True, "mirror_to": [], "tiered": True}
 
 
+class KvDistributor:
+    """The KV distribution modes over a set of serving engines (one per rank; here reachable as objects: engines of
+    one process, or proxies that move the page tensors over a ``CommHandle``).
+
+    LOCAL: nothing moves. MIRROR: after a request finishes, the full pages of its conversation are copied into every
+    peer's prefix cache, so the next turn may land anywhere. ON_DEMAND (and TIERED / PARTIAL_HEAD_MIRROR for the part
+    that fetches): before a request is admitted on a rank whose cache misses its prefix, the longest cached prefix
+    any peer holds is fetched. Pages arrive as cached prefix pages (``LLMEngine.import_prefix_pages``); the admission
+    then computes only what is missing. Reference: KvDistMode behaviours (src/engine/coordinator/kv.rs:52-156, 395-569)."""
+
+    def __init__(self, engines: Dict[int, object], mode: KvDistMode):
+        self.engines, self.mode = dict(engines), mode
+        self.stats = {"mirrored_pages": 0, "fetched_pages": 0, "fetches": 0}
+
+    def after_finish(self, rank: int, tokens: Sequence[int]) -> int:
+        """Call with the conversation's tokens (prompt + generated) once a request has finished on ``rank``."""
+        plan = kv_dist_plan(self.mode, rank, len(self.engines), 1)
+        if not plan["mirror_to"]:
+            return 0
+        n, pages = self.engines[rank].export_prefix_pages(list(tokens))
+        moved = 0
+        for peer in plan["mirror_to"]:
+            if n and peer in self.engines:
+                moved += self.engines[peer].import_prefix_pages(list(tokens), pages)
+        self.stats["mirrored_pages"] += moved
+        return moved
+
+    def before_admit(self, rank: int, tokens: Sequence[int]) -> int:
+        """Call before ``add_request`` on ``rank``: fetches the longest prefix a peer has cached and this rank lacks."""
+        plan = kv_dist_plan(self.mode, rank, len(self.engines), 1)
+        if not plan["fetch_on_miss"]:
+            return 0
+        toks = list(tokens)
+        mine = len(self.engines[rank].batcher.lookup_prefix_pages([int(t) for t in toks[:len(toks) // 16 * 16]]))
+        best, best_n = None, mine
+        for peer, eng in self.engines.items():
+            if peer == rank:
+                continue
+            n = len(eng.batcher.lookup_prefix_pages([int(t) for t in toks[:len(toks) // 16 * 16]]))
+            if n > best_n:
+                best, best_n = peer, n
+        if best is None:
+            return 0
+        n, pages = self.engines[best].export_prefix_pages(toks)
+        got = self.engines[rank].import_prefix_pages(toks, pages)
+        self.stats["fetches"] += 1
+        self.stats["fetched_pages"] += got
+        return got
+
+
 # ------------------------------------------------------------------------------------------------
 # SAGUARO: draft rank proposes, verify rank checks (tens of bytes per round)
 # ------------------------------------------------------------------------------------------------

@@ -349,3 +349,32 @@ def test_engine_keeps_the_per_slot_request_table():
     done = eng.run_until_done()
     assert {r.request_id for r in done} == {a, b}
     assert all(r["phase"] == Phase.IDLE for r in eng.request_states())
+
+
+def test_kv_distribution_modes_move_cached_prefixes_between_engines():
+    """MIRROR: a finished conversation's pages are copied into the peers' prefix caches; ON_DEMAND: a rank that misses a
+    prefix fetches it from the peer that has it; LOCAL: nothing moves. The next turn on the other engine starts from
+    the cached pages and gives the tokens of an engine that computed everything itself."""
+    from gllm_b200.parallel.config import KvDistMode
+    from gllm_b200.parallel.pd import KvDistributor
+    g = torch.Generator().manual_seed(11)
+    turn1 = torch.randint(0, 1000, (53,), generator=g).tolist()
+    for mode in (KvDistMode.MIRROR, KvDistMode.ON_DEMAND, KvDistMode.LOCAL):
+        a, b = _tiny_engine(num_pages=64, enable_prefix_cache=True), _tiny_engine(num_pages=64, enable_prefix_cache=True)
+        dist_ = KvDistributor({0: a, 1: b}, mode)
+        r1 = a.generate_batch([turn1], max_tokens=12, temperature=0.0, eos_ids=[])[0]
+        convo = turn1 + r1.token_ids
+        moved = dist_.after_finish(0, convo)
+        turn2 = convo + torch.randint(0, 1000, (9,), generator=g).tolist()
+        fetched = dist_.before_admit(1, turn2)
+        r2 = b.generate_batch([turn2], max_tokens=6, temperature=0.0, eos_ids=[])[0]
+        want = _tiny_engine(num_pages=64).generate_batch([turn2], max_tokens=6, temperature=0.0, eos_ids=[])[0]
+        assert r2.token_ids == want.token_ids
+        full = len(convo) // 16 * 16
+        if mode == KvDistMode.MIRROR:
+            assert moved == full // 16 and fetched == 0 and r2.telemetry.cached_prefix_tokens == full
+        elif mode == KvDistMode.ON_DEMAND:
+            assert moved == 0 and fetched == full // 16 and r2.telemetry.cached_prefix_tokens == full
+            assert dist_.stats["fetches"] == 1
+        else:
+            assert moved == 0 and fetched == 0 and r2.telemetry.cached_prefix_tokens == 0
