@@ -59,6 +59,12 @@ class ModelConfig:
     hidden_act: str = "silu"
     sliding_window: int = 0
     num_kv_shared_layers: int = 0      # trailing layers that reuse an earlier layer's KV cache (see kv_donor)
+    # Gemma-3n residual structure (models/gemma_ops.py): AltUp keeps ``altup_num_inputs`` residual streams and runs the
+    # layer on one of them, LAuReL adds a low-rank path beside the attention, PLE feeds a per-layer token embedding
+    altup_num_inputs: int = 0
+    altup_active_idx: int = 0
+    laurel_rank: int = 0
+    ple_dim: int = 0
     static_compression: str = ""       # "dead_columns": drop dead FFN neurons when a layer is packed (loader option)
     attention_pattern: Optional[List[int]] = None  # per layer: 1 = sliding, 0 = global
     attention_sinks: bool = False
@@ -142,6 +148,10 @@ class ModelConfig:
     def layer_is_moe(self, layer: int) -> bool:
         return self.is_moe and layer >= self.first_k_dense and (layer % max(self.moe_layer_freq, 1) == 0
                                                                  or self.moe_layer_freq <= 1)
+
+    @property
+    def gemma3n_structure(self) -> bool:
+        return self.altup_num_inputs > 1 or self.laurel_rank > 0 or self.ple_dim > 0
 
     def kv_donor(self, layer: int):
         """Shared-KV layers (the last ``num_kv_shared_layers`` of the stack) project no keys or values of their own:
@@ -229,6 +239,10 @@ class ModelConfig:
             hidden_act=str(g("hidden_act", "hidden_activation", "activation_function", default="silu")),
             sliding_window=int(g("sliding_window", default=0) or 0) if g("use_sliding_window", default=True) else 0,
             num_kv_shared_layers=int(g("num_kv_shared_layers", default=0) or 0),
+            altup_num_inputs=int(g("altup_num_inputs", default=0) or 0),
+            altup_active_idx=int(g("altup_active_idx", default=0) or 0),
+            laurel_rank=int(g("laurel_rank", default=0) or 0),
+            ple_dim=int(g("hidden_size_per_layer_input", default=0) or 0),
             num_experts=int(g("num_experts", "num_local_experts", "n_routed_experts", default=0) or 0),
             num_experts_per_tok=int(g("num_experts_per_tok", default=0) or 0),
             moe_intermediate_size=int(g("moe_intermediate_size", default=0) or 0),

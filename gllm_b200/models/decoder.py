@@ -97,6 +97,12 @@ class DecoderModel:
         self.act_tensor_scale = 1.0 / 64.0      # NVFP4 activations: static second-level scale (values up to 42 exact range)
         if weight_quant is not None and self.bs_fmt is None:
             fused = False        # the dequantising GEMM has no epilogue fusions
+        if cfg.gemma3n_structure:
+            # several residual streams, a low-rank path beside the attention, per-layer embeddings: the layer runs as
+            # separate ops around the stream bookkeeping (models/gemma_ops.py)
+            if tp is not None and tp.size > 1:
+                raise ValueError("the AltUp / LAuReL / PLE layer structure runs on one rank")
+            fused = False
         # the fused layer is the CUDA path; block-scaled models also run it on CPU tensors (every fused op has its fp32
         # restatement), so that the CPU model quantises the same activations as the GPU one and can serve as its oracle
         self.fused = (can_fuse(cfg, self.tp_size) if fused is None else fused) and (
@@ -134,6 +140,8 @@ class DecoderModel:
                 if isinstance(val, torch.Tensor):
                     setattr(lw, name, val.to(self.device, None if val.dtype == torch.float32 and (
                         name.endswith("norm") or name.endswith("bias")) else (dtype if val.is_floating_point() else None)).contiguous())
+            if cfg.gemma3n_structure:
+                self._load_gemma3n_layer(lw, src, i)
             if weight_quant is not None:
                 self._quantize_layer(lw, weight_quant, quant_group)
             if cfg.layer_is_moe(i):
@@ -150,6 +158,14 @@ class DecoderModel:
                     lw.moe.paged = self.expert_pager.layers[i]
             self.layers.append(lw)
         self.final_norm = src.get("final_norm").float().to(self.device).contiguous() if self.last_stage else None
+        self.altup_proj = self.altup_unproj = []
+        self.ple_table = None
+        if cfg.gemma3n_structure:
+            n_alt = max(cfg.altup_num_inputs, 1)
+            self.altup_proj = [src.get(f"altup_proj.{k}").to(self.device, dtype).contiguous() for k in range(n_alt - 1)]
+            self.altup_unproj = [src.get(f"altup_unproj.{k}").to(self.device, dtype).contiguous() for k in range(n_alt - 1)]
+            if cfg.ple_dim > 0:
+                self.ple_table = src.get("ple_table").to(self.device, dtype).contiguous()
         self.lm_head = None
         if not hasattr(self, "ep"):
             self.ep = None
@@ -179,6 +195,19 @@ class DecoderModel:
         self.blob = None
         if weight_blob if weight_blob is not None else self.device.type == "cuda":
             self._pack_blob()
+
+    def _load_gemma3n_layer(self, lw, src, i: int):
+        """AltUp / LAuReL / per-layer-embedding tensors of layer ``i`` into ``lw.extra`` (fp32: they are small)."""
+        from . import gemma_ops as G
+        c, p = self.cfg, layer_prefix(i)
+        f = lambda name: src.get(p + name).float().to(self.device).contiguous()
+        if c.altup_num_inputs > 1:
+            lw.extra["altup"] = G.AltUpWeights(router=f("altup_router"), predict=f("altup_predict"), correct=f("altup_correct"),
+                                               router_norm=f("altup_router_norm"), out_scale=f("altup_out_scale"))
+        if c.laurel_rank > 0:
+            lw.extra["laurel"] = G.LaurelWeights(down=f("laurel_down"), up=f("laurel_up"), norm=f("laurel_norm"))
+        if c.ple_dim > 0:
+            lw.extra["ple_gate"], lw.extra["ple_proj"], lw.extra["ple_norm"] = f("ple_gate"), f("ple_proj"), f("ple_norm")
 
     def _pack_blob(self):
         """Re-home the packed dense tensors (per-layer projections and norms, embedding, heads) in ONE contiguous,
@@ -342,6 +371,10 @@ class DecoderModel:
         names (eager forward only, never inside a captured graph): a callback may replace the hidden states (RAG or
         knowledge injection, layer skipping), end the layer loop early, or veto; what happened is left in
         ``self.callback_action`` / ``self.callback_info``."""
+        if self.cfg.gemma3n_structure:
+            if capture_layers is not None or callbacks is not None or hidden_in is not None:
+                raise ValueError("capture_layers / callbacks / hidden_in are not available with the AltUp layer structure")
+            return self._forward_gemma3n(batch, kv_caches, decode_ws=decode_ws, return_hidden=return_hidden)
         if self.sequence_parallel:
             if capture_layers is not None or callbacks is not None:
                 raise ValueError("capture_layers / callbacks are not available with sequence_parallel (no rank holds "
@@ -465,6 +498,75 @@ class DecoderModel:
                 else:
                     self.last_mtp_logits.append(ops.gemm(hn, w, out_dtype=torch.float32, bn=256))
         return logits
+
+    def _forward_gemma3n(self, batch: ForwardBatch, kv_caches, *, decode_ws=None, return_hidden=False):
+        """The Gemma-3n residual structure around the ordinary attention and MLP ops.
+
+        ``altup_num_inputs`` residual streams [n, T, H] (stream 0 is the embedding, the others are projections of it
+        rescaled to its magnitude); per layer: AltUp predicts every stream from all of them, the layer runs on the
+        ACTIVE stream only (attention with the LAuReL low-rank path beside it, then the MLP), AltUp spreads the
+        layer's innovation to all streams, and the layer's slice of the per-layer token embedding, gated by the active
+        stream, is added to the other streams. After the last layer the streams are projected back and averaged.
+        Reference: AltUpPredict / AltUpCorrect / AltUpInject, LAuReL and the PLE gather in the graph builder
+        (src/arch/auto_graph_fragments/build_graph.inc.rs:695, 1064, 1115, 1811-1846)."""
+        from . import gemma_ops as G
+        c = self.cfg
+        T = batch.num_tokens
+        ws = self.workspace(T)
+        x, h = ws.x[:T], ws.h[:T]
+        eps = c.rms_norm_eps
+        n, act_i = max(c.altup_num_inputs, 1), c.altup_active_idx
+        ops.embed_gather(batch.token_ids, self.embed, scale=c.embedding_scale, out=x, ss_out=ws.ss0[:T])
+        x0 = x.clone()
+        rms = lambda t: t.float().pow(2).mean(-1, keepdim=True).clamp_min(1e-12).sqrt()
+        streams = [x0]
+        for w in self.altup_proj:                         # the other streams start as projections at the same magnitude
+            p = ops.gemm(x0, w, out_dtype=self.dtype, bn=128)[:, :c.hidden_size].float()
+            streams.append((p * rms(x0) / rms(p)).to(self.dtype))
+        streams = torch.stack(streams)                    # [n, T, H]
+        for li, lw in zip(self.layer_ids, self.layers):
+            shared = lw.kv_donor is not None
+            kv = kv_caches[(lw.kv_donor if shared else li) - self.layer_ids[0]]
+            slots = None if shared else batch.slot_mapping
+            aw = lw.extra.get("altup")
+            pred = G.altup_predict(streams, aw, act_i, eps) if aw is not None else streams
+            x.copy_(pred[act_i])
+            ops.rmsnorm(x, lw.input_norm, eps, one_plus_w=c.norm_one_plus_w, out=h)
+            qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T, :lw.wqkv.shape[0]], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
+            ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
+                              positions=batch.positions, slot_mapping=slots, cos_t=self.cos, sin_t=self.sin, q_out=ws.q[:T],
+                              kv_cache=kv, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, kv_scale=self.kv_scale)
+            self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
+            self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)                       # x = stream + attention
+            if "laurel" in lw.extra:                      # (x + h + norm(up(down(h)))) / sqrt(2), h the normalised input
+                x.copy_(G.laurel(h, x, lw.extra["laurel"], eps))
+            ops.rmsnorm(x, lw.post_attn_norm, eps, one_plus_w=c.norm_one_plus_w, out=h)
+            gu = ops.gemm(h, lw.w_gate_up, out=ws.gu[:T, :lw.w_gate_up.shape[0]], out_dtype=self.dtype, bn=128)
+            a = ops.glu(gu, self.act_id, out=ws.act[:T, :lw.w_down.shape[1]])
+            self._row_parallel(a, lw.w_down, x, ws.ss_a[:T], T)
+            if aw is None:
+                streams = x.clone()[None]
+                continue
+            corr = G.altup_correct(pred, x, aw, act_i, eps)
+            ple = None
+            if self.ple_table is not None:
+                pe = G.ple_gather(self.ple_table, batch.token_ids, li, c.num_layers)           # [T, d]
+                g = L._act_ref(corr[act_i].float() @ lw.extra["ple_gate"].t(), self.act_id) * pe
+                ple = g @ lw.extra["ple_proj"].t()
+                ple = ple * torch.rsqrt(ple.pow(2).mean(-1, keepdim=True) + eps) * lw.extra["ple_norm"]
+            streams = G.altup_inject(corr, ple, aw, act_i)
+        out = [streams[0].float()]
+        for k, w in enumerate(self.altup_unproj):          # back to the embedding's space and magnitude, then the mean
+            u = ops.gemm(streams[k + 1].contiguous(), w, out_dtype=self.dtype, bn=128)[:, :c.hidden_size].float()
+            out.append(u * rms(streams[0]) / rms(u))
+        x.copy_(torch.stack(out).mean(0).to(self.dtype))
+        if not self.last_stage or return_hidden:
+            return x
+        rows = batch.logits_rows
+        xr = x if rows is None else x.index_select(0, rows)
+        hn = ops.rmsnorm(xr, self.final_norm, eps, one_plus_w=c.norm_one_plus_w)
+        self.last_mtp_logits = []
+        return ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256, softcap=float(c.logit_softcap or 0.0))
 
     def _run_callbacks(self, callbacks, when: str, li: int, x, ss_in, ws, T: int):
         """One port of the callback chain. Returns (row statistics of x for the next fused GEMM, stop the layer loop)."""

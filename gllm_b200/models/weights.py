@@ -115,6 +115,15 @@ class RandomWeights:
                 "classifier_bias": (max(getattr(c, "num_labels", 0) or 1, 1),)})
         if base in table:
             return table[base]
+        n_alt, r_l, d_ple = max(c.altup_num_inputs, 1), max(c.laurel_rank, 1), max(c.ple_dim, 1)
+        gemma3n = {"altup_router": (n_alt, H), "altup_predict": (n_alt * n_alt, n_alt), "altup_correct": (n_alt, n_alt),
+                   "altup_router_norm": (H,), "altup_out_scale": (H,), "laurel_down": (r_l, H), "laurel_up": (H, r_l),
+                   "laurel_norm": (H,), "ple_table": (c.vocab_size, c.num_layers * d_ple), "ple_gate": (d_ple, H),
+                   "ple_proj": (H, d_ple), "ple_norm": (H,)}
+        if base in gemma3n:
+            return gemma3n[base]
+        if name.startswith("altup_proj.") or name.startswith("altup_unproj."):
+            return (H, H)
         inter = c.intermediate_size
         if ".experts." in name:
             inter = c.moe_intermediate_size
@@ -138,7 +147,7 @@ class RandomWeights:
     def get(self, name: str) -> torch.Tensor:
         base = name.rsplit(".", 1)[-1]
         shape = self.shape_of(name)
-        return self._gen(name, shape, ones=base.endswith("norm"))
+        return self._gen(name, shape, ones=base.endswith("norm") or base == "altup_out_scale")
 
     def has(self, name: str) -> bool:
         c = self.cfg

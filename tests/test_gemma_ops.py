@@ -113,3 +113,85 @@ def test_shared_kv_donor_layers():
     _, kv = _run_tokens(m, ids[:-1])
     step, _ = _run_tokens(m, ids[-1:], kv=kv, start=len(ids) - 1)
     assert torch.nn.functional.cosine_similarity(step, ref, dim=0) > 0.999
+
+
+def _g3n_cfg(**kw):
+    from gllm_b200.models.config import preset
+    cfg = preset("tiny-qwen3")
+    cfg.num_layers = 3
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return cfg
+
+
+def _g3n_batch(ids, start, n, pages=4, decode=False):
+    from gllm_b200.engine.batch import ForwardBatch
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    pos = list(range(start, start + n))
+    return ForwardBatch(token_ids=ids[start:start + n], positions=i32(pos), slot_mapping=i32(pos),
+                        block_tables=torch.arange(pages, dtype=torch.int32)[None], ctx_lens=i32([start + n]),
+                        q_start=i32([0]), q_len=i32([n]), max_q_len=n, is_decode=decode)
+
+
+def test_altup_with_neutral_weights_is_the_plain_decoder():
+    """The stream bookkeeping inside the decoder: with a silent AltUp router (prediction = identity, correction = the
+    layer's innovation on every stream), identity projections and unit output scale all streams follow the active one,
+    so the logits equal the plain model's."""
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+
+    class Neutral(RandomWeights):
+        def get(self, name):
+            base = name.rsplit(".", 1)[-1]
+            if base == "altup_router":
+                return torch.zeros(self.shape_of(name))
+            if base == "altup_out_scale":
+                return torch.ones(self.shape_of(name))
+            if name.startswith("altup_proj.") or name.startswith("altup_unproj."):
+                return torch.eye(self.cfg.hidden_size)
+            return super().get(name)
+
+    plain_cfg, alt_cfg = _g3n_cfg(), _g3n_cfg(altup_num_inputs=3)
+    plain = DecoderModel(plain_cfg, RandomWeights(plain_cfg, "cpu", torch.float32, seed=2, std=0.05), device="cpu",
+                         dtype=torch.float32, max_positions=64)
+    alt = DecoderModel(alt_cfg, Neutral(alt_cfg, "cpu", torch.float32, seed=2, std=0.05), device="cpu", dtype=torch.float32,
+                       max_positions=64)
+    assert not alt.fused and len(alt.altup_proj) == 2
+    ids = (torch.arange(20, dtype=torch.int32) * 7 + 1) % plain_cfg.vocab_size
+    want = plain.forward(_g3n_batch(ids, 0, 20), plain.alloc_kv_cache(4))
+    got = alt.forward(_g3n_batch(ids, 0, 20), alt.alloc_kv_cache(4))
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+
+
+def test_gemma3n_structure_prefill_and_decode_agree():
+    """AltUp (4 streams), LAuReL and per-layer embeddings with random weights: the logits of position t are the same
+    whether the prompt is prefilled at once, in two chunks, or the last token is decoded on the cached pages; every
+    feature changes the logits; the model serves through the engine."""
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    feats = dict(altup_num_inputs=4, laurel_rank=8, ple_dim=16)
+    cfg = _g3n_cfg(**feats)
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=5, std=0.05)
+    m = DecoderModel(cfg, src, device="cpu", dtype=torch.float32, max_positions=64)
+    ids = (torch.arange(24, dtype=torch.int32) * 5 + 3) % cfg.vocab_size
+    full = m.forward(_g3n_batch(ids, 0, 24), m.alloc_kv_cache(4))
+    assert torch.isfinite(full).all()
+    kv = m.alloc_kv_cache(4)
+    a = m.forward(_g3n_batch(ids, 0, 17), kv)
+    b = m.forward(_g3n_batch(ids, 17, 6), kv)
+    c = m.forward(_g3n_batch(ids, 23, 1, decode=True), kv)
+    torch.testing.assert_close(torch.cat([a, b, c]), full, rtol=2e-4, atol=2e-4)
+    base = DecoderModel(_g3n_cfg(), RandomWeights(_g3n_cfg(), "cpu", torch.float32, seed=5, std=0.05), device="cpu",
+                        dtype=torch.float32, max_positions=64).forward(_g3n_batch(ids, 0, 24), m.alloc_kv_cache(4))
+    for name, val in feats.items():
+        one = _g3n_cfg(**{name: val})
+        lg = DecoderModel(one, RandomWeights(one, "cpu", torch.float32, seed=5, std=0.05), device="cpu", dtype=torch.float32,
+                          max_positions=64).forward(_g3n_batch(ids, 0, 24), m.alloc_kv_cache(4))
+        if name == "ple_dim":       # per-layer embeddings enter through the non-active streams only: silent without AltUp
+            torch.testing.assert_close(lg, base)
+        else:
+            assert not torch.allclose(lg, base), name
+    from gllm_b200.engine.executor import EngineConfig, LLMEngine
+    eng = LLMEngine(m, EngineConfig(max_num_seqs=2, max_model_len=64, max_batch_tokens=32, prefill_chunk=32, num_pages=16))
+    out = eng.generate_batch([ids[:9].tolist(), ids[:20].tolist()], max_tokens=4, temperature=0.0, eos_ids=[])
+    assert [len(r.token_ids) for r in out] == [4, 4]
