@@ -232,6 +232,7 @@ class ModelConfig:
             max_position_embeddings=g("max_position_embeddings", "n_positions", default=4096),
             rms_norm_eps=g("rms_norm_eps", "layer_norm_epsilon", "layer_norm_eps", default=1e-12),
             rope_theta=float(g("rope_theta", default=10000.0)),
+            rope_local_theta=float(g("rope_local_base_freq", default=0.0) or 0.0),
             partial_rotary_factor=float(g("partial_rotary_factor", default=1.0)),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", tc.get("tie_word_embeddings", False))),
             attention_bias=bool(g("attention_bias", "qkv_bias", default=arch in ("qwen2",))),

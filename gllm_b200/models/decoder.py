@@ -122,6 +122,13 @@ class DecoderModel:
                             cfg.intermediate_size // self.tp_size)
         self.max_positions = max_positions or cfg.max_position_embeddings
         self.cos, self.sin = rope.build_tables(cfg, self.max_positions, self.device)
+        # dual RoPE (Gemma 3): sliding-window layers rotate with their own base and no long-context scaling
+        self.cos_local = self.sin_local = None
+        if cfg.rope_local_theta > 0 and cfg.rotary_dim > 0:
+            inv, _ = rope.inv_frequencies(cfg.rotary_dim, cfg.rope_local_theta, type(cfg.rope_scaling)(), self.max_positions)
+            ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
+            self.cos_local = ang.cos().float().contiguous().to(self.device)
+            self.sin_local = ang.sin().float().contiguous().to(self.device)
         self.act_id = L.ACT_IDS.get(cfg.hidden_act, 0)
         self.res_bn = 256 if cfg.hidden_size % 256 == 0 else 128  # tile width of the residual GEMMs
         self.scale = cfg.attention_scale()
@@ -298,6 +305,12 @@ class DecoderModel:
         return self._ws
 
     # ------------------------------------------------------------------------------------------
+    def _rope(self, layer: int):
+        """(cos, sin) tables of a layer: the local tables on sliding-window layers of a dual-RoPE model."""
+        if self.cos_local is not None and self.cfg.layer_window(layer) > 0:
+            return self.cos_local, self.sin_local
+        return self.cos, self.sin
+
     def _attention(self, q, kv, batch: ForwardBatch, out, layer: int, decode_ws):
         window = self.cfg.layer_window(layer)
         cp = getattr(batch, "cp", None)
@@ -408,17 +421,18 @@ class DecoderModel:
             shared = lw.kv_donor is not None
             kv = kv_caches[(lw.kv_donor if shared else li) - self.layer_ids[0]]
             slots = None if shared else batch.slot_mapping
+            cos_l, sin_l = self._rope(li)
             if self.fused:
                 if self.bs_fmt is not None:
                     from ..ops import blockscale as B
                     B.gemm_qkv(self._act_q(x, T), lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
-                               slot_mapping=slots, positions=batch.positions, cos_t=self.cos,
-                               sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
+                               slot_mapping=slots, positions=batch.positions, cos_t=cos_l,
+                               sin_t=sin_l, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                                row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 else:
                     ops.gemm_qkv(x, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv,
-                                 slot_mapping=slots, positions=batch.positions, cos_t=self.cos,
-                                 sin_t=self.sin, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
+                                 slot_mapping=slots, positions=batch.positions, cos_t=cos_l,
+                                 sin_t=sin_l, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps,
                                  row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps, bias=lw.qkv_bias, kv_scale=self.kv_scale)
                 mark("qkv_gemm")
                 self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
@@ -456,8 +470,8 @@ class DecoderModel:
                 else:
                     qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T, :lw.wqkv.shape[0]], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
                     ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
-                                      positions=batch.positions, slot_mapping=slots, cos_t=self.cos,
-                                      sin_t=self.sin, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
+                                      positions=batch.positions, slot_mapping=slots, cos_t=cos_l,
+                                      sin_t=sin_l, q_out=ws.q[:T], kv_cache=kv, q_norm_w=lw.q_norm,
                                       k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, kv_scale=self.kv_scale)
                     self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
                     self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)
@@ -534,7 +548,8 @@ class DecoderModel:
             ops.rmsnorm(x, lw.input_norm, eps, one_plus_w=c.norm_one_plus_w, out=h)
             qkv = ops.gemm(h, lw.wqkv, out=ws.qkv[:T, :lw.wqkv.shape[0]], out_dtype=self.dtype, bias=lw.qkv_bias, bn=128)
             ops.rope_kv_write(qkv, n_q=lw.n_q, n_kv=lw.n_kv, head_dim=c.head_dim, rot_dim=c.rotary_dim,
-                              positions=batch.positions, slot_mapping=slots, cos_t=self.cos, sin_t=self.sin, q_out=ws.q[:T],
+                              positions=batch.positions, slot_mapping=slots, cos_t=self._rope(li)[0], sin_t=self._rope(li)[1],
+                              q_out=ws.q[:T],
                               kv_cache=kv, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, kv_scale=self.kv_scale)
             self._attention(ws.q[:T], kv, batch, ws.attn[:T], li, decode_ws)
             self._row_parallel(ws.attn[:T], lw.wo, x, ws.ss_b[:T], T)                       # x = stream + attention
@@ -622,7 +637,7 @@ class DecoderModel:
                 tp.allgather_input(xs, h, ss_out=ss_g)      # consumed by the QKV GEMM below
                 a_in, ss_in = h, ss_g
             ops.gemm_qkv(a_in, lw.wqkv, n_q=lw.n_q, n_kv=lw.n_kv, q_out=ws.q[:T], kv_cache=kv, slot_mapping=slots,
-                         positions=batch.positions, cos_t=self.cos, sin_t=self.sin, q_norm_w=lw.q_norm,
+                         positions=batch.positions, cos_t=self._rope(li)[0], sin_t=self._rope(li)[1], q_norm_w=lw.q_norm,
                          k_norm_w=lw.k_norm, qk_eps=c.qk_norm_eps, row_ss=ss_in, norm_dim=H, eps=c.rms_norm_eps,
                          bias=lw.qkv_bias, kv_scale=self.kv_scale)
             mark("qkv_gemm")

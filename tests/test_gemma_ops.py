@@ -195,3 +195,33 @@ def test_gemma3n_structure_prefill_and_decode_agree():
     eng = LLMEngine(m, EngineConfig(max_num_seqs=2, max_model_len=64, max_batch_tokens=32, prefill_chunk=32, num_pages=16))
     out = eng.generate_batch([ids[:9].tolist(), ids[:20].tolist()], max_tokens=4, temperature=0.0, eos_ids=[])
     assert [len(r.token_ids) for r in out] == [4, 4]
+
+
+def test_dual_rope_rotates_sliding_layers_with_the_local_base():
+    """Gemma-3 style: layers with a sliding window rotate q / k with ``rope_local_theta``, global layers with
+    ``rope_theta``. Checked against the same model where the pattern makes every layer global / every layer local."""
+    from gllm_b200.models.decoder import DecoderModel
+    from gllm_b200.models.weights import RandomWeights
+    ids = (torch.arange(30, dtype=torch.int32) * 3 + 2) % 1000
+
+    def logits(**kw):
+        cfg = _g3n_cfg(num_layers=2, **kw)
+        m = DecoderModel(cfg, RandomWeights(cfg, "cpu", torch.float32, seed=7, std=0.05), device="cpu", dtype=torch.float32,
+                         max_positions=64)
+        return m, m.forward(_g3n_batch(ids, 0, 30), m.alloc_kv_cache(4))
+
+    # window 64 >= sequence: the window itself changes nothing, only the rotation base can
+    m, mixed = logits(rope_theta=1e6, rope_local_theta=1e4, sliding_window=64, attention_pattern=[1, 0])
+    assert m.cos_local is not None and m._rope(0)[0] is m.cos_local and m._rope(1)[0] is m.cos
+    _, all_global = logits(rope_theta=1e6, rope_local_theta=1e4, sliding_window=64, attention_pattern=[0, 0])
+    _, plain_global = logits(rope_theta=1e6)
+    torch.testing.assert_close(all_global, plain_global)
+    _, all_local = logits(rope_theta=1e6, rope_local_theta=1e4, sliding_window=64, attention_pattern=[1, 1])
+    _, plain_local = logits(rope_theta=1e4)
+    torch.testing.assert_close(all_local, plain_local)
+    assert not torch.allclose(mixed, all_global) and not torch.allclose(mixed, all_local)
+    # layer 0 local + layer 1 global equals a hand-built pair of tables used per layer
+    import gllm_b200.models.rope as rope
+    cfg = m.cfg
+    lo = rope.build_tables(cfg, 64, "cpu", theta=1e4)
+    torch.testing.assert_close(m.cos_local, lo[0])
