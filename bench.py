@@ -429,7 +429,7 @@ def main():
             "kv_pages": engine.num_pages,
         }
         if nccl_ms is not None:
-            # the baseline BASELINE.md names: this engine with every collective on NCCL, measured in the same run
+            # the baseline arm: this engine with every collective on NCCL, measured in the same run
             out["baseline"] = {"what": "same engine, unfused row-parallel GEMM + ncclAllReduce + norm kernel (CUDA graph)",
                                "value": round(n_active * K / (nccl_ms / 1e3), 1), "unit": "tokens/s",
                                "ms_per_step": round(nccl_ms / K, 4)}
