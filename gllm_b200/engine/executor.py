@@ -222,8 +222,18 @@ class LLMEngine:
         if ec.mtp_depth > 0 and getattr(model, "mtp_heads", None):
             from ..speculative.mtp_executor import MtpExecutor
             self.mtp = MtpExecutor(min(ec.mtp_depth, len(model.mtp_heads)))
+        self.eagle = None                           # speculative.heads.EagleHead (attach_eagle): feature-level drafts
+        self.eagle_depth = 0
+        self._eagle_feat: Dict[int, torch.Tensor] = {}      # request -> hidden state behind its last committed token
 
     # ------------------------------------------------------------------------------------------
+    def attach_eagle(self, head, depth: int = 3):
+        """Draft with an EAGLE head: it continues the target's last hidden feature and the last token for ``depth``
+        steps; the target verifies the chain in one forward, so the output stays the target's greedy output. Verify
+        steps run eagerly (the feature behind the last kept token is read back from them).
+        Reference: EAGLE feature-head drafts (src/speculative/engine.rs:29-420)."""
+        self.eagle, self.eagle_depth = head, int(depth)
+
     def _auto_pages(self) -> int:
         per_page = 16 * self.mc.kv_bytes_per_token(self.model.tp_size) * len(self.model.layer_ids) // max(
             self.mc.num_layers, 1)
@@ -489,12 +499,17 @@ class LLMEngine:
                 idx = self._spec_idx.get(rid)
                 cand = idx.lookup(k) if idx is not None else []
                 d = [int(t) for t in cand[0][:k]] if cand else []
+            if not d and self.eagle is not None and rid in self._eagle_feat:
+                tok = torch.tensor([int(plan.dec_tokens[sl])], device=self.device)
+                d = [int(t[0]) for t in self.eagle.draft(self._eagle_feat[rid][None], tok, self.eagle_depth)]
+                bad = next((i for i, t in enumerate(d) if not 0 <= t < self.mc.vocab_size), len(d))
+                d = d[:bad]               # a head reading through a padded lm_head may name a padding row
             left = self._remaining_tokens(rid)
             d = d[:max(0, left - 1)]            # never draft past the request's length limit
             if d and not self.batcher.reserve_tokens(rid, 1 + len(d)):
                 d = []
             drafts[sl] = d
-        if not any(drafts.values()) and (self.mtp is None or self.mtp.active_depth() == 0):
+        if not any(drafts.values()) and (self.mtp is None or self.mtp.active_depth() == 0) and self.eagle is None:
             return None      # nothing to verify (and no candidates wanted): the captured one-token decode step runs
         self.batcher.copy_slot_block_tables_into(self.h_bt.numpy().reshape(-1))
         bt = self.h_bt.numpy()
@@ -517,7 +532,12 @@ class LLMEngine:
                              q_start=i32(q_start), q_len=i32(q_len), max_q_len=max(q_len), want_mtp=self.mtp is not None)
         self.stats["h2d_bytes"] += 4 * (3 * T + 3 * len(slots)) + bt[slots].nbytes
         self._ep_bound(False)
-        logits = self.model.forward(batch, self.kv_caches)
+        hid = None
+        if self.eagle is not None and self.mtp is None:
+            hid = self.model.forward(batch, self.kv_caches, return_hidden=True)
+            logits = self.model.head_logits(hid)
+        else:
+            logits = self.model.forward(batch, self.kv_caches)
         out = torch.empty(T, dtype=torch.int32, device=dev)
         greedy = torch.zeros((T, 4), dtype=torch.float32, device=dev)
         zeros = torch.zeros(T, dtype=torch.int64, device=dev)
@@ -551,6 +571,8 @@ class LLMEngine:
             st["drafted"] += len(d)
             st["accepted"] += n_acc
             st["emitted"] += len(new)
+            if hid is not None:           # the feature behind the last token that stays: the next draft starts there
+                self._eagle_feat[int(ids[sl])] = hid[q_start[j] + n_acc].clone()
             self.stats["decode_tokens"] += len(new)
             if self.mtp is not None:
                 if from_mtp.get(sl):
@@ -864,7 +886,8 @@ class LLMEngine:
         spec_extra = {}
         if plan.num_decode > 0:
             spec = None
-            if (self.cfg.speculative_tokens > 0 or self.mtp is not None) and bool((self.slot_params[:, 0] <= 0).all()):
+            if (self.cfg.speculative_tokens > 0 or self.mtp is not None or self.eagle is not None) and bool(
+                    (self.slot_params[:, 0] <= 0).all()):
                 with nvtx_range("speculative_step"):
                     spec = self._run_speculative_decode(plan)
             if spec is not None:
@@ -1086,6 +1109,7 @@ class LLMEngine:
             self._req_params.pop(f.id, None)
             self._spec_idx.pop(f.id, None)
             self._mtp_cand.pop(f.id, None)
+            self._eagle_feat.pop(f.id, None)
             toks = [int(t) for t in f.tokens]
             reason = S.FINISH_REASONS.get(f.finish, "length")
             if f.id in vetoed:

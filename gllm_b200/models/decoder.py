@@ -669,6 +669,20 @@ class DecoderModel:
         return logits
 
     # ------------------------------------------------------------------------------------------
+    def head_logits(self, xr):
+        """fp32 logits [R, vocab_local_padded] of residual-stream rows ``xr`` (what ``forward(return_hidden=True)``
+        returns): final norm + lm_head, with the soft cap; in the fused layout the norm weight lives in the head and
+        the rows' statistics are taken here."""
+        c = self.cfg
+        cap = float(c.logit_softcap or 0.0)
+        if self.fused:
+            ss = torch.empty((xr.shape[0], 1), dtype=torch.float32, device=xr.device)
+            ops.rmsnorm(xr, None, c.rms_norm_eps, ss_out=ss, want_y=False)
+            return ops.gemm(xr, self.lm_head, out_dtype=torch.float32, row_ss=ss, norm_dim=c.hidden_size, eps=c.rms_norm_eps,
+                            bn=256, softcap=cap)
+        hn = ops.rmsnorm(xr, self.final_norm, c.rms_norm_eps, one_plus_w=c.norm_one_plus_w)
+        return ops.gemm(hn, self.lm_head, out_dtype=torch.float32, bn=256, softcap=cap)
+
     def final_hidden(self, x):
         """Final-norm hidden states (embedding / head-routing consumers)."""
         return ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, one_plus_w=self.cfg.norm_one_plus_w)

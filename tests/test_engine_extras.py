@@ -378,3 +378,41 @@ def test_kv_distribution_modes_move_cached_prefixes_between_engines():
             assert dist_.stats["fetches"] == 1
         else:
             assert moved == 0 and fetched == 0 and r2.telemetry.cached_prefix_tokens == 0
+
+
+def test_eagle_head_drafts_are_verified_by_the_target():
+    """An EAGLE head attached to the engine: drafts continue the target's last hidden feature; whatever the head
+    proposes (here an untrained one, and one that is made to agree with the target), the tokens equal plain greedy
+    decoding, and agreeing drafts shorten the run."""
+    from gllm_b200.speculative.heads import EagleHead
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (19, 33)]
+    plain = _tiny_engine(num_pages=64)
+    want = [r.token_ids for r in plain.generate_batch(prompts, max_tokens=12, temperature=0.0, eos_ids=[])]
+    eng = _tiny_engine(num_pages=64)
+    m = eng.model
+    head = EagleHead(m.cfg.hidden_size, m.embed, m.lm_head, m.final_norm, seed=1, dtype=torch.float32)
+    eng.attach_eagle(head, depth=3)
+    got = [r.token_ids for r in eng.generate_batch(prompts, max_tokens=12, temperature=0.0, eos_ids=[])]
+    assert got == want
+    st = eng.spec_stats
+    assert st["steps"] > 0 and st["drafted"] > 0 and not eng._eagle_feat       # features dropped with the requests
+
+    class Oracle:      # a "head" that knows the target's continuation: every draft is accepted
+        def __init__(self, answers):
+            self.answers = answers
+
+        def draft(self, feature, token, depth):
+            t = int(token[0])
+            for seq in self.answers:
+                if t in seq:
+                    i = seq.index(t)
+                    return [torch.tensor([x]) for x in seq[i + 1:i + 1 + depth]]
+            return []
+    eng2 = _tiny_engine(num_pages=64)
+    eng2.attach_eagle(Oracle(want), depth=3)
+    got2 = [r.token_ids for r in eng2.generate_batch(prompts, max_tokens=12, temperature=0.0, eos_ids=[])]
+    assert got2 == want
+    if all(len(set(w)) == len(w) for w in want):      # unambiguous look-ups: every proposed token was right
+        assert eng2.spec_stats["accepted"] == eng2.spec_stats["drafted"] > 0
+        assert eng2.stats["decode_steps"] < plain.stats["decode_steps"]
