@@ -294,8 +294,8 @@ class Client:
                 dist.init_process_group("nccl", device_id=dev)
             else:
                 dist.init_process_group("gloo")
-        from .parallel.tensor_parallel import TPContext
-        return TPContext(dist.get_rank(), world, dev, mode="auto" if dev.type == "cuda" else "nccl",
+        from .parallel.tensor_parallel import TPContext, mode_for_comm_config
+        return TPContext(dist.get_rank(), world, dev, mode=mode_for_comm_config(d.comm) if dev.type == "cuda" else "nccl",
                          max_tokens=self.config.max_batch_tokens, hidden=cfg.hidden_size)
 
     _BITS_4 = ("q4", "q5", "iq4", "q3", "iq3", "q2", "iq2", "iq1", "awq", "gptq", "nvfp4", "mxfp4", "int4")

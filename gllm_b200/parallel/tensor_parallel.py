@@ -448,6 +448,25 @@ class TPContext:
         self._handle = None
 
 
+def mode_for_comm_config(comm) -> str:
+    """``TPContext`` mode for a ``parallel.config.CommConfig``: which of the engine's all-reduce forms stands for each
+    algorithm family of the reference's communication layer.
+
+    FLUX_PIPELINE (GEMM fused with its collective) and the automatic choices -> ``auto`` (the low-latency ownership
+    form, multimem broadcast when the switch offers it); HARDWARE_REDUCE / COLLNET_DIRECT (in-switch reduction) ->
+    ``pull`` (``multimem.ld_reduce``); DIRECT (one-shot peer access) -> ``ll_p2p`` (plain peer stores, no multimem);
+    CHUNKED_PIPELINE -> ``fused`` (per-tile pushes with flags); the ring / tree families have no hand-written
+    counterpart on an NVSwitch box and take NCCL. ``overlap`` = ``prefer_isolated`` also selects NCCL (collective and
+    GEMM as separate kernels). Reference: CommAlgorithm selection (src/engine/coordinator/compute.rs:122-436)."""
+    from .config import CommAlgorithm
+    if str(getattr(comm, "overlap", "auto")) == "prefer_isolated":
+        return "nccl"
+    table = {CommAlgorithm.FLUX_PIPELINE: "auto", CommAlgorithm.HARDWARE_REDUCE: "pull", CommAlgorithm.COLLNET_DIRECT: "pull",
+             CommAlgorithm.DIRECT: "ll_p2p", CommAlgorithm.CHUNKED_PIPELINE: "fused", CommAlgorithm.RING: "nccl",
+             CommAlgorithm.TREE: "nccl", CommAlgorithm.TOPO_AWARE_RING: "nccl", CommAlgorithm.HIERARCHICAL_RING: "nccl"}
+    return table.get(getattr(comm, "algorithm", CommAlgorithm.FLUX_PIPELINE), "auto")
+
+
 def single_gpu_context(device, hidden: int, max_tokens: int = 1024, mode: str = "fused_p2p") -> TPContext:
     """A world-size-1 context on ordinary device memory: exercises the fused kernel's protocol (receive slots, tile
     flags, done words, launch state; with ``mode="ll_p2p"`` the self-validating slots; with ``mode="pull_p2p"``

@@ -447,3 +447,13 @@ def test_sequence_parallel_block_allgather_gemm_reduce_scatter_on_gloo(world):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("SP_WORKER_OK") == world
+
+
+def test_comm_config_selects_the_all_reduce_form():
+    from gllm_b200.parallel.config import CommAlgorithm, CommConfig
+    from gllm_b200.parallel.tensor_parallel import mode_for_comm_config
+    assert mode_for_comm_config(CommConfig()) == "auto"
+    assert mode_for_comm_config(CommConfig(algorithm=CommAlgorithm.HARDWARE_REDUCE)) == "pull"
+    assert mode_for_comm_config(CommConfig(algorithm=CommAlgorithm.DIRECT)) == "ll_p2p"
+    assert mode_for_comm_config(CommConfig(algorithm=CommAlgorithm.RING)) == "nccl"
+    assert mode_for_comm_config(CommConfig(overlap="prefer_isolated")) == "nccl"
