@@ -39,6 +39,35 @@ class IntentClassifier:
         c = self.classify(text)
         return max(c, key=c.get)
 
+    def as_callback(self):
+        """The classifier on the intent port of the residual bus (0.75 L): the prompt's intent is read from the prefill
+        forward of the generation itself (mean of the prompt rows at the probe layer), no second encode. The result is
+        left in ``callback.scores`` and in the model's ``callback_info["intent"]``."""
+        from ..engine.callbacks import CallbackResult, LayerCallback
+        clf = self
+
+        class _Intent(LayerCallback):
+            priority = 5
+            layers = [clf.layer]
+            scores: Optional[Dict[str, float]] = None
+
+            def post_layer(self, layer, hidden):
+                if hidden.shape[0] < 2 and self.scores is not None:
+                    return CallbackResult()          # decode steps: the prompt's intent stands
+                p = clf.probe.probabilities(hidden.float().mean(0, keepdim=True).cpu())[0]
+                self.scores = {l: float(v) for l, v in zip(clf.probe.labels, p)}
+                return CallbackResult(info={"intent": max(self.scores, key=self.scores.get)})
+        return _Intent()
+
+    def generate_with_intent(self, prompt: str, **gen):
+        """(response, intent scores of the prompt) from one generation call."""
+        from ..engine.callbacks import CallbackChain
+        cb = self.as_callback()
+        b = self.client.generate(prompt).callbacks(CallbackChain([cb]))
+        for k, v in gen.items():
+            b = getattr(b, k)(v)
+        return b.generate(), cb.scores
+
 
 def _rmsnorm(x, eps=1e-6):
     return x * torch.rsqrt(x.pow(2).mean() + eps)

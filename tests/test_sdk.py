@@ -58,6 +58,9 @@ def test_guardrail_intent_stream_guard():
     assert good.finish_reason != "vetoed by a layer callback" and len(good.token_ids) >= 1
     ic = IntentClassifier.train(c, {"greet": safe, "noise": unsafe})
     assert ic.top(safe[2]) == "greet" and ic.top(unsafe[3]) == "noise"
+    out, scores = ic.generate_with_intent(unsafe[3], max_tokens=3, temperature=0.0)      # read from the generation's own prefill
+    assert max(scores, key=scores.get) == "noise" and len(out.token_ids) >= 1
+    assert abs(scores["noise"] - ic.classify(unsafe[3])["noise"]) < 0.05
     tr = IntentTracker(ic)
     tr.update(safe[0]); tr.update(safe[1]); assert not tr.switched()
     tr.update(unsafe[0]); tr.update(unsafe[1]); tr.update(unsafe[2])
