@@ -62,6 +62,9 @@ class EngineConfig:
     # debug serving: eager steps with a NaN / Inf check of the residual stream after every layer and of the logits
     # (engine/guard.py::NanTrap; FloatingPointError names the first offender; tensors are dumped to GLLM_DUMP_DIR)
     debug: bool = False
+    # every this many engine steps the attention telemetry of the running sequences' KV pages is sampled into the page
+    # headers and each request's importance score is refreshed (engine/kv_telemetry.py); 0 = never
+    kv_telemetry_every: int = 0
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
@@ -131,6 +134,10 @@ class LLMEngine:
             self.kv_swap = KvSwapManager(self.kv_caches, ec.swap_space_pages, swap_path=ec.swap_path,
                                          nvme_pages=ec.swap_nvme_pages, device_pool_pages=ec.kv_kivi_pool_pages)
             self.kv_swap.tier_policy = self._swap_tier
+        self.kv_telemetry = None
+        if ec.kv_telemetry_every > 0:
+            from .kv_telemetry import KvTelemetry
+            self.kv_telemetry = KvTelemetry(self)
         self._sessions = set()                # requests that belong to a multi-turn session (conversation pipeline)
         self.kv_importance: Dict[int, int] = {}      # request -> importance score 0..255 (callers / telemetry may set it)
         self.ms = ec.max_num_seqs
@@ -895,6 +902,8 @@ class LLMEngine:
             else:
                 with nvtx_range("decode_step"):
                     dec_tokens = self._run_decode(plan).copy()
+                if self.kv_telemetry is not None and self._steps % self.cfg.kv_telemetry_every == 0:
+                    self.kv_telemetry.sample(plan)      # before a prefill chunk reuses the workspace rows
         if plan.num_prefill_seqs > 0:
             with nvtx_range("prefill_chunk"):
                 pf_tokens = self._run_prefill(plan)

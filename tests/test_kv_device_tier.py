@@ -149,3 +149,39 @@ def test_device_kernels_match_the_cpu_statement():
                                         max_q_len=7, n_q=n_q, n_kv=n_kv, scale=D ** -0.5)
         torch.testing.assert_close(got.float().cpu(), want, rtol=2e-2, atol=2e-2)
     assert nv.device_error() == 0
+
+
+def test_kv_page_telemetry_feeds_headers_and_importance():
+    """After a decode step the sampled pass recomputes the last layer's attention of every running sequence from the
+    workspace queries and the cache pages: its output equals what the step itself computed (so the rows, positions and
+    pages line up), the per-page masses sum to one, the 64-byte headers carry the telemetry, and every request gets an
+    importance score the swap tier decision reads."""
+    from tests.test_engine_extras import _tiny_engine
+    from gllm_b200.kv_cache.header import PrecisionTier
+    eng = _tiny_engine(num_pages=64, kv_telemetry_every=1)
+    g = torch.Generator().manual_seed(2)
+    rids = [eng.add_request(torch.randint(0, 1000, (n,), generator=g).tolist(), max_tokens=6, temperature=0.0, eos_ids=[])
+            for n in (37, 18)]
+    checked = 0
+    while eng.has_work():
+        before = eng.kv_telemetry.samples
+        eng.step()
+        if eng.kv_telemetry.samples > before:
+            lo = eng.kv_telemetry.last_out
+            mine = lo["out"].reshape(-1)
+            theirs = eng.model._ws.attn[lo["slot"]].float()[:mine.numel()]
+            if eng.model._ws.attn.shape[0] and torch.isfinite(theirs).all():
+                torch.testing.assert_close(mine, theirs, rtol=1e-4, atol=1e-5)
+                checked += 1
+    assert checked > 0 and eng.kv_telemetry.samples >= 4
+    h = eng.kv_telemetry.headers.h
+    used = h[h["ref_count"] > 0]
+    assert len(used) >= 3 and set(int(x) for x in used["sequence_id"]) <= set(rids)
+    assert (used["importance"] > 0).any() and all(0 <= int(t) <= int(PrecisionTier.EVICTED) for t in used["precision_tier"])
+    assert (used["centroid"].astype("float32") >= 0).all() and float(used["entropy"].astype("float32").max()) <= 6.94
+    # masses of one sequence's pages sum to one (checked through the stats function directly)
+    from gllm_b200.engine.kv_telemetry import attention_page_stats
+    kv = eng.kv_caches[-1]
+    q = torch.randn(eng.model.n_q_local * kv.shape[-1])
+    st = attention_page_stats(q, kv, [3, 1, 2], 40, eng.model.n_q_local, eng.model.n_kv_local, 0.1)
+    assert abs(float(st["mass"].sum()) - 1.0) < 1e-5 and st["entropy"].shape == (3,) and float(st["softmax_max"].max()) <= 1.0
