@@ -149,6 +149,37 @@ class GateSkipCallback(LayerCallback):
         return CallbackResult(CallbackAction.REPLACE, self._saved.pop(layer), {"skipped": layer})
 
 
+class LayerTelemetryCallback(LayerCallback):
+    """Feeds the epilogue aggregator: per layer the relative change of the residual stream (delta rho = ||x_out -
+    x_in|| / ||x_in||, on the device through ``ops.telemetry.layer_telemetry`` when the rows live there). The
+    aggregator's advice names the layers that barely move the stream (candidates for ``GateSkipCallback``) and
+    whether drafts are likely to be accepted. Reference: epilogue telemetry signals and their consumers
+    (src/jit/epilogue.rs, src/engine/executor_step.rs:265-393)."""
+    priority = 50
+    layers = None
+
+    def __init__(self, aggregator):
+        self.agg = aggregator
+        self._in: Dict[int, torch.Tensor] = {}
+
+    def pre_layer(self, layer, hidden):
+        self._in[layer] = hidden.clone()
+        return CallbackResult()
+
+    def post_layer(self, layer, hidden):
+        from ...runtime.epilogue import EpilogueSignal, signals_from_tensors
+        x_in = self._in.pop(layer, None)
+        if x_in is None:
+            return CallbackResult()
+        if hidden.is_cuda:
+            from ...ops.telemetry import layer_telemetry
+            sig = EpilogueSignal(layer, delta_rho=float(layer_telemetry(x_in, hidden)["delta_rho"]))
+        else:
+            sig = signals_from_tensors(layer, x_in, hidden)
+        self.agg.push(sig)
+        return CallbackResult()
+
+
 class ProbeVetoCallback(LayerCallback):
     """Linear probe on a mid-layer hidden state; vetoes the request when the score crosses the threshold."""
     priority = 20

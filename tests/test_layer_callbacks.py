@@ -165,3 +165,22 @@ def test_debug_serving_names_the_first_non_finite_layer():
     with pytest.raises(FloatingPointError, match="hidden after layer 2"):
         eng2.generate_batch([[5, 6, 7, 8]], max_tokens=3, temperature=0.0, eos_ids=[])
     w.copy_(keep)
+
+
+def test_layer_telemetry_feeds_the_epilogue_aggregator_and_its_advice_skips_a_quiet_layer():
+    """The telemetry callback measures how much every layer moves the residual stream; a layer made silent (zero output
+    projections) shows up as a bypass candidate, and skipping it with GateSkipCallback changes nothing."""
+    from gllm_b200.engine.callbacks import LayerTelemetryCallback
+    from gllm_b200.runtime.epilogue import EpilogueAggregator
+    cfg, src, m = _model(layers=6)
+    m.layers[3].wo.zero_()
+    m.layers[3].w_down.zero_()
+    agg = EpilogueAggregator(cfg.num_layers)
+    plain = m.forward(_batch(9), m.alloc_kv_cache(4)).clone()
+    seen = m.forward(_batch(9), m.alloc_kv_cache(4), callbacks=CallbackChain([LayerTelemetryCallback(agg)]))
+    torch.testing.assert_close(seen, plain)                      # observing changes nothing
+    assert set(agg.ema) == set(range(6)) and agg.ema[3].delta_rho < 1e-6 < agg.ema[2].delta_rho
+    advice = agg.advice()
+    assert advice.bypass_layers == [3]
+    skipped = m.forward(_batch(9), m.alloc_kv_cache(4), callbacks=CallbackChain([GateSkipCallback(advice.bypass_layers)]))
+    torch.testing.assert_close(skipped, plain, rtol=1e-5, atol=1e-6)
