@@ -234,6 +234,25 @@ class LLMEngine:
         self._eagle_feat: Dict[int, torch.Tensor] = {}      # request -> hidden state behind its last committed token
 
     # ------------------------------------------------------------------------------------------
+    def generate_with_mtp(self, prompt_ids: List[int], max_tokens: int = 256, temperature: float = 0.0, top_k: int = 0,
+                          top_p: float = 1.0, eos_ids=None) -> dict:
+        """One request through the multi-token-prediction path: the model's MTP heads propose candidates behind every
+        committed token, the next step's forward verifies them, rejected ones are rolled back. Returns
+        ``{"committed_tokens", "total_mtp_candidates", "total_mtp_accepted", "steps", "finish_reason"}``. Without MTP
+        heads (or with ``mtp_depth`` 0) it is an ordinary generation with zero candidates; sampling requests
+        (temperature > 0) do not speculate. Reference: generate_with_mtp / MtpGenerateResult
+        (src/engine/executor_api.rs:178-260, src/engine/mtp_executor.rs:15-40)."""
+        before = dict(self.spec_stats)
+        rid = self.add_request(prompt_ids, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p,
+                               eos_ids=eos_ids)
+        while rid not in self.results and self.has_work():
+            self.step()
+        res = self.results.pop(rid)
+        st = self.spec_stats
+        return {"committed_tokens": list(res.token_ids), "total_mtp_candidates": st["drafted"] - before["drafted"],
+                "total_mtp_accepted": st["accepted"] - before["accepted"], "steps": st["steps"] - before["steps"],
+                "finish_reason": res.finish_reason}
+
     def attach_eagle(self, head, depth: int = 3):
         """Draft with an EAGLE head: it continues the target's last hidden feature and the last token for ``depth``
         steps; the target verifies the chain in one forward, so the output stays the target's greedy output. Verify

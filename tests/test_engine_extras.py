@@ -245,6 +245,12 @@ def test_mtp_heads_in_the_model_feed_the_verify_step():
     got = [r.token_ids for r in eng.generate_batch(prompts, max_tokens=48, temperature=0.0, eos_ids=[])]
     assert got == want
     assert eng.spec_stats["drafted"] > 0 and 0.0 <= eng.mtp.controller.ema <= 1.0
+    # the single-request entry point with the reference's result fields
+    r = LLMEngine(model, EngineConfig(mtp_depth=2, **ec)).generate_with_mtp(prompts[0], max_tokens=48, eos_ids=[])
+    assert r["committed_tokens"] == want[0] and r["total_mtp_candidates"] > 0
+    assert 0 <= r["total_mtp_accepted"] <= r["total_mtp_candidates"] and r["steps"] > 0
+    r0 = LLMEngine(model, EngineConfig(**ec)).generate_with_mtp(prompts[0], max_tokens=48, eos_ids=[])
+    assert r0["committed_tokens"] == want[0] and r0["total_mtp_candidates"] == 0
 
 
 def test_prefill_and_decode_roles_hand_requests_over_with_their_kv_pages():
