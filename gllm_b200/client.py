@@ -256,7 +256,7 @@ class Client:
                                       prefill_chunk=self.config.max_batch_tokens,
                                       enable_prefix_cache=self.config.enable_prefix_cache,
                                       use_cuda_graphs=self.config.use_cuda_graphs, seed=self.config.seed,
-                                      debug=self.config.debug)
+                                      debug=self.config.debug or self._env_debug())
                     if dev.type != "cuda":
                         ec.num_pages = max(64, self.config.max_num_seqs * ((ec.max_model_len + 15) // 16) // 4)
                     engine = LLMEngine(model, ec, tokenizer=tokenizer)
@@ -297,6 +297,12 @@ class Client:
         from .parallel.tensor_parallel import TPContext, mode_for_comm_config
         return TPContext(dist.get_rank(), world, dev, mode=mode_for_comm_config(d.comm) if dev.type == "cuda" else "nccl",
                          max_tokens=self.config.max_batch_tokens, hidden=cfg.hidden_size)
+
+    @staticmethod
+    def _env_debug() -> bool:
+        """GLLM_DEBUG_JIT=1 in the environment turns the debug serving mode on, like ``ClientBuilder.debug_jit()``."""
+        import os
+        return os.environ.get("GLLM_DEBUG_JIT", "0") not in ("", "0", "false", "False")
 
     _BITS_4 = ("q4", "q5", "iq4", "q3", "iq3", "q2", "iq2", "iq1", "awq", "gptq", "nvfp4", "mxfp4", "int4")
     _BITS_8 = ("q8", "q6", "fp8", "mxfp8", "int8")
