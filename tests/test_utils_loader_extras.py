@@ -130,3 +130,29 @@ def test_static_compression_and_tier_plan_are_wired_into_loading():
     plan = {p.name: p.tier for p in lm.plan_tiers(device_budget=700_000, host_budget=600_000)}
     assert plan["embed_tokens"] == 1 and plan["L0.q_proj"] == 1          # always resident
     assert sorted([plan["L0.gate_proj"], plan["L1.gate_proj"]]) == [1, 2]   # one fits on the device, one goes to the host
+
+
+def test_checkpoint_inspector_and_dump_comparison(tmp_path, capsys):
+    import torch
+    from gllm_b200.engine.guard import dump_tensors
+    from gllm_b200.loader.gguf import write_gguf
+    from gllm_b200.loader.inspect import describe, main as inspect_main
+    from gllm_b200.loader.safetensors import save_file
+    from gllm_b200.utils.compare_dumps import compare, main as compare_main
+    st = tmp_path / "m.safetensors"
+    save_file({"model.embed_tokens.weight": torch.zeros(8, 4, dtype=torch.bfloat16), "model.norm.weight": torch.ones(4)}, st)
+    d = describe(st)
+    assert d["format"] == "safetensors" and len(d["tensors"]) == 2 and d["total_bytes"] == 8 * 4 * 2 + 4 * 4
+    gg = tmp_path / "m.gguf"
+    write_gguf(gg, {"general.architecture": "llama", "llama.block_count": 2}, {"token_embd.weight": torch.zeros(8, 32)})
+    d = describe(gg)
+    assert d["format"].startswith("gguf") and d["metadata"]["llama.block_count"] == 2 and d["tensors"][0]["shape"] == [8, 32]
+    assert inspect_main([str(gg), "--tensors", "--keys", "--filter", "token"]) == 0
+    assert "token_embd.weight" in capsys.readouterr().out
+    a, b = tmp_path / "a", tmp_path / "b"
+    x = torch.randn(4, 8)
+    dump_tensors({"layer0/out": x, "layer1/out": x * 2}, str(a))
+    dump_tensors({"layer0/out": x + 1e-5, "layer1/out": x * 2 + 0.5}, str(b))
+    rows = compare(str(a), str(b))
+    assert rows[0]["name"].startswith("layer1") and not rows[0]["ok"] and rows[1]["ok"]
+    assert compare_main([str(a), str(b)]) == 1 and compare_main([str(a), str(a)]) == 0
