@@ -313,6 +313,14 @@ class LLMEngine:
         pipeline = KvPipeline.CONVERSATION if rid in self._sessions else KvPipeline.WORKING
         return decide_tier(int(self.kv_importance.get(rid, 100)), pipeline)
 
+    def abort(self, rid: int, reason: str = "aborted") -> bool:
+        """Cancel a waiting or running request: it ends at the next step with ``finish_reason = reason`` and the tokens
+        it has so far; its pages (and swap copies) are released. False when the request is unknown or already done."""
+        if rid not in self.reqs:
+            return False
+        self._vetoed[rid] = reason
+        return True
+
     def has_work(self) -> bool:
         return bool(self.reqs)
 

@@ -422,3 +422,19 @@ def test_eagle_head_drafts_are_verified_by_the_target():
     if all(len(set(w)) == len(w) for w in want):      # unambiguous look-ups: every proposed token was right
         assert eng2.spec_stats["accepted"] == eng2.spec_stats["drafted"] > 0
         assert eng2.stats["decode_steps"] < plain.stats["decode_steps"]
+
+
+def test_abort_cancels_waiting_and_running_requests():
+    eng = _tiny_engine(num_pages=64, max_num_seqs=2)
+    g = torch.Generator().manual_seed(1)
+    rids = [eng.add_request(torch.randint(0, 1000, (20,), generator=g).tolist(), max_tokens=30, temperature=0.0, eos_ids=[])
+            for _ in range(3)]                       # two run, one waits
+    for _ in range(4):
+        eng.step()
+    assert eng.abort(rids[0], "cancelled by the caller") and eng.abort(rids[2]) and not eng.abort(12345)
+    eng.run_until_done()
+    a, b, c = (eng.results[r] for r in rids)
+    assert a.finish_reason == "cancelled by the caller" and 0 < len(a.token_ids) < 30
+    assert c.finish_reason == "aborted" and len(c.token_ids) == 0
+    assert b.finish_reason == "length" and len(b.token_ids) == 30
+    assert eng.batcher.num_free_pages == eng.batcher.num_total_pages or eng.cfg.enable_prefix_cache
