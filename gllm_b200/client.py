@@ -706,13 +706,59 @@ class ClassifyBuilder:
 
 
 class AsyncClient:
-    """Thread-offload wrapper: every call returns a ``concurrent.futures.Future``."""
+    """Every call returns a ``concurrent.futures.Future``. With ``continuous=True`` generation requests go to a serving
+    loop that owns the engine (``engine.serving.ServingLoop``): calls from many threads are batched together step by
+    step instead of running one after the other; the future resolves to a ``GenerationResponse`` all the same."""
 
-    def __init__(self, client: Client, workers: int = 1):
+    def __init__(self, client: Client, workers: int = 1, continuous: bool = False):
         self._c = client
         self._pool = cf.ThreadPoolExecutor(max_workers=workers)
+        self._loop = None
+        if continuous:
+            from .engine.serving import ServingLoop
+            st = client._st()
+            if st.engine is None:
+                raise InvalidModelTypeError("continuous generation needs a decoder model")
+            self._loop = ServingLoop(st.engine)
+
+    def _generate_continuous(self, prompt, kw) -> "cf.Future":
+        c, st = self._c, self._c._st()
+        b = c.generate(prompt)
+        for k, v in kw.items():
+            getattr(b, k)(v)
+        ids = c._prompt_ids(b._prompt)
+        eos = st.tokenizer.eos_ids(st.model.cfg.eos_token_ids) + list(b._stop)
+        inner = self._loop.submit(ids, max_tokens=b._max_tokens, temperature=b._temperature, top_k=b._top_k, top_p=b._top_p,
+                                  eos_ids=eos, session_id=b._session_id, hook=c._hook_fn(b._hooks))
+        outer: "cf.Future" = cf.Future()
+
+        def done(f):
+            try:
+                res = f.result()
+            except Exception as exc:
+                outer.set_exception(exc)
+                return
+            toks = res.token_ids
+            if toks and toks[-1] in eos and res.finish_reason == "eos":
+                toks = toks[:-1]
+            text = st.tokenizer.decode(toks)
+            thinking, answer = split_thinking_content(text) if b._reasoning else ("", text)
+            t = res.telemetry
+            outer.set_result(GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
+                                                prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
+                                                ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms))
+        inner.add_done_callback(done)
+        outer.inner = inner
+        return outer
+
+    def cancel(self, fut: "cf.Future", reason: str = "aborted") -> bool:
+        """Continuous mode: end a submitted generation early."""
+        return self._loop is not None and self._loop.cancel(getattr(fut, "inner", fut), reason)
 
     def generate(self, prompt, **kw) -> "cf.Future":
+        if self._loop is not None:
+            return self._generate_continuous(prompt, kw)
+
         def run():
             b = self._c.generate(prompt)
             for k, v in kw.items():
@@ -730,4 +776,6 @@ class AsyncClient:
         return self._pool.submit(lambda: self._c.generate_batch(requests))
 
     def shutdown(self):
+        if self._loop is not None:
+            self._loop.shutdown()
         self._pool.shutdown(wait=True)

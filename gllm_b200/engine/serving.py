@@ -1,0 +1,108 @@
+"""A serving loop around one engine: callers on any thread submit requests and get futures; one worker thread owns
+the engine, admits what has arrived, steps, and resolves the futures of the requests that finished. Requests that
+arrive while others are decoding join the running batch at the next step (continuous batching across callers), which
+a blocking ``generate`` per caller cannot give.
+
+Reference parity: the request queue in front of the executor's step loop
+(src/engine/batch_executor.rs:18-579, src/engine/executor_step.rs:859-973).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import queue
+import threading
+from typing import List, Optional
+
+
+class ServingLoop:
+    def __init__(self, engine, idle_wait_s: float = 0.002):
+        self.engine = engine
+        self._inbox: "queue.Queue" = queue.Queue()
+        self._futures = {}
+        self._stop = threading.Event()
+        self._idle_wait = idle_wait_s
+        self.stats = {"submitted": 0, "finished": 0, "steps": 0, "max_running": 0, "errors": 0}
+        self._thread = threading.Thread(target=self._run, name="gllm-serving-loop", daemon=True)
+        self._thread.start()
+
+    # ---- callers --------------------------------------------------------------------------------------
+    def submit(self, prompt_ids: List[int], **params) -> "cf.Future":
+        """``params`` as for ``LLMEngine.add_request`` (max_tokens, temperature, top_k, top_p, eos_ids, session_id,
+        stream, hook). The future resolves to the request's ``GenerateResult``; ``future.request_id`` is set once the
+        engine has admitted it (None before)."""
+        if self._stop.is_set():
+            raise RuntimeError("the serving loop has been shut down")
+        fut: cf.Future = cf.Future()
+        fut.request_id = None
+        self._inbox.put((list(prompt_ids), params, fut))
+        self.stats["submitted"] += 1
+        return fut
+
+    def cancel(self, fut: "cf.Future", reason: str = "aborted") -> bool:
+        """Ask for a submitted request to end early (its future still resolves, with that finish reason)."""
+        if fut.done():
+            return False
+        self._inbox.put(("cancel", fut, reason))
+        return True
+
+    def shutdown(self, wait: bool = True):
+        self._stop.set()
+        if wait:
+            self._thread.join()
+
+    # ---- the worker ------------------------------------------------------------------------------------
+    def _admit(self):
+        while True:
+            try:
+                item = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            if item[0] == "cancel":
+                _, fut, reason = item
+                if fut.request_id is not None:
+                    self.engine.abort(fut.request_id, reason)
+                else:
+                    fut.cancelled_reason = reason
+                continue
+            prompt, params, fut = item
+            if not fut.set_running_or_notify_cancel():
+                continue
+            try:
+                rid = self.engine.add_request(prompt, **params)
+            except Exception as exc:          # bad request: the caller gets the error, the loop goes on
+                fut.set_exception(exc)
+                self.stats["errors"] += 1
+                continue
+            fut.request_id = rid
+            self._futures[rid] = fut
+            if getattr(fut, "cancelled_reason", None):
+                self.engine.abort(rid, fut.cancelled_reason)
+
+    def _run(self):
+        eng = self.engine
+        while True:
+            self._admit()
+            if not eng.has_work():
+                if self._stop.is_set() and self._inbox.empty():
+                    return
+                try:                          # sleep until something arrives
+                    item = self._inbox.get(timeout=self._idle_wait if not self._stop.is_set() else 0.0)
+                    self._inbox.put(item)
+                except queue.Empty:
+                    pass
+                continue
+            try:
+                eng.step()
+            except Exception as exc:          # an engine fault ends every request in flight; the loop stays usable
+                for rid, fut in list(self._futures.items()):
+                    if not fut.done():
+                        fut.set_exception(exc)
+                    self._futures.pop(rid, None)
+                self.stats["errors"] += 1
+                continue
+            self.stats["steps"] += 1
+            self.stats["max_running"] = max(self.stats["max_running"], int(eng.batcher.num_running))
+            for rid in [r for r in self._futures if r in eng.results]:
+                fut = self._futures.pop(rid)
+                fut.set_result(eng.results.pop(rid))
+                self.stats["finished"] += 1

@@ -176,3 +176,45 @@ def test_weight_quant_plan_of_the_client():
     with pytest.raises(ValueError, match="do not fit"):
         Client.from_model(small, RandomWeights(small, "cpu", torch.float32, seed=2), device="cpu", dtype=torch.float32,
                           max_num_seqs=2, max_model_len=128, max_batch_tokens=64, weight_quant="nvfp4")
+
+
+def test_async_client_batches_concurrent_callers_through_the_serving_loop():
+    """Continuous mode: requests submitted from several threads run in one engine batch (more than one running
+    sequence per step), every future resolves to what the blocking client returns, a request can be cancelled, and a
+    bad request fails its own future only."""
+    import threading
+    import torch
+    from gllm_b200.client import AsyncClient, Client
+    from gllm_b200.models.config import preset
+    from gllm_b200.models.weights import RandomWeights
+    cfg = preset("tiny-qwen3")
+    src = RandomWeights(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    kw = dict(device="cpu", dtype=torch.float32, max_num_seqs=8, max_model_len=128, max_batch_tokens=128)
+    prompts = [f"request number {i} says hello" for i in range(6)]
+    blocking = Client.from_model(cfg, src, **kw)
+    want = [blocking.generate(p).max_tokens(12).temperature(0.0).generate().token_ids for p in prompts]
+    ac = AsyncClient(Client.from_model(cfg, src, **kw), continuous=True)
+    futs = [None] * len(prompts)
+
+    def caller(i):
+        futs[i] = ac.generate(prompts[i], max_tokens=12, temperature=0.0)
+    threads = [threading.Thread(target=caller, args=(i,)) for i in range(len(prompts))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    got = [f.result(timeout=120).token_ids for f in futs]
+    assert got == want
+    assert ac._loop.stats["max_running"] > 1 and ac._loop.stats["finished"] == 6
+    slow = ac.generate(prompts[0], max_tokens=100, temperature=0.0)
+    assert ac.cancel(slow, "client went away")
+    r = slow.result(timeout=120)
+    assert r.finish_reason == "client went away" and len(r.token_ids) < 100
+    bad = ac.generate("x " * 400, max_tokens=50)               # longer than the model allows
+    try:
+        bad.result(timeout=60)
+        raised = False
+    except Exception:
+        raised = True
+    assert raised and ac.generate(prompts[1], max_tokens=3, temperature=0.0).result(timeout=60).token_ids == want[1][:3]
+    ac.shutdown()
