@@ -253,6 +253,24 @@ class LLMEngine:
                 "total_mtp_accepted": st["accepted"] - before["accepted"], "steps": st["steps"] - before["steps"],
                 "finish_reason": res.finish_reason}
 
+    def rebalance_experts(self, reduce: bool = True) -> List[int]:
+        """Expert load balancing for the expert-sharded tensor-parallel MoE mode: the load balancer's window (summed
+        over the ranks with ``reduce``) names the hot experts, which are then mirrored on every rank so that their rows
+        are shared out (``MoeLayerWeights.set_mirrors``); captured decode graphs are dropped because the expert stacks
+        and block tables change. A collective over the tensor-parallel group: every rank calls it at the same point of
+        its (identical) schedule. Returns the hot experts now mirrored."""
+        st = self.coordinators.observability.capture_expert_load(reduce=reduce)
+        hot = sorted(st["hot_experts"]) if st else []
+        layers = [lw.moe for lw in self.model.layers if getattr(lw, "moe", None) is not None
+                  and lw.moe.tp_experts is not None and lw.moe.bs_fmt is None]
+        if not layers or tuple(hot) == tuple(layers[0].mirrored):
+            return list(layers[0].mirrored) if layers else []
+        for m in layers:
+            m.set_mirrors(hot, self.model)
+        self.graphs.clear()
+        self.stats["expert_rebalances"] = self.stats.get("expert_rebalances", 0) + 1
+        return hot
+
     def attach_eagle(self, head, depth: int = 3):
         """Draft with an EAGLE head: it continues the target's last hidden feature and the last token for ``depth``
         steps; the target verifies the chain in one forward, so the output stays the target's greedy output. Verify

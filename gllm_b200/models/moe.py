@@ -44,11 +44,16 @@ class MoeLayerWeights:
     act_tensor_scale: float = 1.0 / 64.0
     _ws: Optional[M.MoeWorkspace] = None
     paged: Optional["PagedExperts"] = None   # expert stacks in host memory, a few slots of them on the device
+    # hot experts mirrored on every rank of the expert-sharded tensor-parallel mode (set_mirrors): their stacks sit
+    # behind the rank's own experts, mirror_map[e] is the mirror slot of expert e (-1: not mirrored)
+    n_mirror: int = 0
+    mirror_map: Optional[torch.Tensor] = None
+    mirrored: tuple = ()
 
     # ------------------------------------------------------------------------------------------
     def workspace(self, model, T):
         holder = model.__dict__.setdefault("_moe_ws", {})
-        groups = self.paged.slots if self.paged is not None else self.e_local      # paged experts: the groups are slots
+        groups = self.paged.slots if self.paged is not None else self.e_local + self.n_mirror   # paged experts: slots
         key = (groups, self.inter)
         ws = holder.get(key)
         if ws is None or ws.ids.shape[0] < T:
@@ -68,7 +73,7 @@ class MoeLayerWeights:
         if self.bs_fmt is None:
             # paged experts: the stacks are the device slots, the "experts" of the block table are slot numbers
             w_gu, w_dn, groups = (self.paged.dev_gu, self.paged.dev_dn, self.paged.slots) if self.paged is not None else (
-                self.w_gate_up, self.w_down, self.e_local)
+                self.w_gate_up, self.w_down, self.e_local + self.n_mirror)
             rows = getattr(ws, "blk_rows", None)      # routed rows per block: padding rows are neither loaded nor stored
             L.set_block_rows(rows)
             L.gemm_glu(ws.a_perm, w_gu, act=model.act_id, out=ws.act, bn=self.glu_bn, mblk_group=ws.blk_group,
@@ -147,7 +152,19 @@ class MoeLayerWeights:
         import torch.distributed as dist
         c = self.cfg
         H = c.hidden_size
-        M.permute(src, ss_in if fused_norm else None, ids, ws, self.e0, self.e_local)
+        if self.n_mirror:
+            # rows routed to a mirrored (hot) expert are shared out over the ranks by token index; every other row
+            # stays with the rank that owns its expert
+            tpc = self.tp_experts
+            m = self.mirror_map.index_select(0, ids.reshape(-1).long()).reshape(ids.shape)          # -1 or mirror slot
+            mine = (torch.arange(T, device=ids.device)[:, None] % tpc.size) == tpc.rank
+            out_of_range = torch.full_like(ids, c.num_experts + self.n_mirror + 1)
+            own = (ids >= self.e0) & (ids < self.e0 + self.e_local)       # the mirror slots extend the local id range:
+            ids_local = torch.where(m >= 0, torch.where(mine, (self.e0 + self.e_local + m).to(ids.dtype), out_of_range),
+                                    torch.where(own, ids, out_of_range))     # other ranks' experts must stay outside it
+            M.permute(src, ss_in if fused_norm else None, ids_local.contiguous(), ws, self.e0, self.e_local + self.n_mirror)
+        else:
+            M.permute(src, ss_in if fused_norm else None, ids, ws, self.e0, self.e_local)
         self._expert_ffn(model, src, ws, T, fused_norm)
         holder = model.__dict__.setdefault("_moe_partial", {})
         part = holder.get("buf")
@@ -166,6 +183,45 @@ class MoeLayerWeights:
         ss = None if ss_out is None else ss_out.reshape(-1)[:T].view(T, 1)
         ops.rmsnorm(p, None, 0.0, residual=x, h_out=x, ss_out=ss, want_y=False)
         return ss
+
+    def set_mirrors(self, hot, model=None):
+        """Load-balancer placement for the expert-sharded tensor-parallel mode: the ``hot`` experts are mirrored on
+        every rank (their weights are broadcast from the owner and stacked behind the rank's own experts) and their
+        rows are shared out over the ranks; ``hot = []`` goes back to the plain placement. A collective: every rank of
+        the tensor-parallel group calls it with the same list. Reference: HotCold placement with mirrored hot experts
+        (src/moe/distributed_dispatch.rs:19-285, src/moe/eplb.rs:180-243)."""
+        import torch.distributed as dist
+        tpc = self.tp_experts
+        if tpc is None or self.bs_fmt is not None or self.paged is not None:
+            raise ValueError("mirrors: bf16 experts sharded over the tensor-parallel ranks only")
+        hot = sorted(set(int(e) for e in hot))
+        rows_gu = self.w_gate_up.shape[0] // (self.e_local + self.n_mirror)
+        rows_dn = self.w_down.shape[0] // (self.e_local + self.n_mirror)
+        own_gu, own_dn = self.w_gate_up[:self.e_local * rows_gu], self.w_down[:self.e_local * rows_dn]
+        per = self.cfg.num_experts // tpc.size
+        gus, dns = [own_gu], [own_dn]
+        for e in hot:
+            owner = e // per
+            g = torch.empty((rows_gu, own_gu.shape[1]), dtype=own_gu.dtype, device=own_gu.device)
+            d = torch.empty((rows_dn, own_dn.shape[1]), dtype=own_dn.dtype, device=own_dn.device)
+            if tpc.rank == owner:
+                l = e - self.e0
+                g.copy_(own_gu[l * rows_gu:(l + 1) * rows_gu])
+                d.copy_(own_dn[l * rows_dn:(l + 1) * rows_dn])
+            if tpc.size > 1:
+                src_rank = dist.get_global_rank(tpc.group, owner) if tpc.group is not None else owner
+                dist.broadcast(g, src=src_rank, group=tpc.group)
+                dist.broadcast(d, src=src_rank, group=tpc.group)
+            gus.append(g)
+            dns.append(d)
+        self.w_gate_up, self.w_down = torch.cat(gus, 0).contiguous(), torch.cat(dns, 0).contiguous()
+        self.n_mirror, self.mirrored = len(hot), tuple(hot)
+        mm = torch.full((self.cfg.num_experts,), -1, dtype=torch.int32, device=own_gu.device)
+        for slot, e in enumerate(hot):
+            mm[e] = slot
+        self.mirror_map = mm
+        if model is not None:
+            model.__dict__.get("_moe_ws", {}).clear()      # the block tables have one more group per mirror
 
     def _forward_paged(self, model, x, src, ss_in, ss_out, ids, w, ws, T, fused_norm: bool):
         """Experts paged in from host memory: the step's experts are made resident wave by wave (as many as there are
