@@ -20,6 +20,7 @@ class ServingLoop:
         self._inbox: "queue.Queue" = queue.Queue()
         self._futures = {}
         self._stop = threading.Event()
+        self._wake = threading.Event()
         self._idle_wait = idle_wait_s
         self.stats = {"submitted": 0, "finished": 0, "steps": 0, "max_running": 0, "errors": 0}
         self._thread = threading.Thread(target=self._run, name="gllm-serving-loop", daemon=True)
@@ -35,6 +36,7 @@ class ServingLoop:
         fut: cf.Future = cf.Future()
         fut.request_id = None
         self._inbox.put((list(prompt_ids), params, fut))
+        self._wake.set()
         self.stats["submitted"] += 1
         return fut
 
@@ -43,10 +45,12 @@ class ServingLoop:
         if fut.done():
             return False
         self._inbox.put(("cancel", fut, reason))
+        self._wake.set()
         return True
 
     def shutdown(self, wait: bool = True):
         self._stop.set()
+        self._wake.set()
         if wait:
             self._thread.join()
 
@@ -85,11 +89,8 @@ class ServingLoop:
             if not eng.has_work():
                 if self._stop.is_set() and self._inbox.empty():
                     return
-                try:                          # sleep until something arrives
-                    item = self._inbox.get(timeout=self._idle_wait if not self._stop.is_set() else 0.0)
-                    self._inbox.put(item)
-                except queue.Empty:
-                    pass
+                self._wake.wait(self._idle_wait)      # sleep until something arrives (arrival order is kept)
+                self._wake.clear()
                 continue
             try:
                 eng.step()
