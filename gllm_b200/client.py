@@ -728,14 +728,27 @@ class AsyncClient:
             getattr(b, k)(v)
         ids = c._prompt_ids(b._prompt)
         eos = st.tokenizer.eos_ids(st.model.cfg.eos_token_ids) + list(b._stop)
+        stream, on_token = None, None
+        if b._stream:          # pieces of text arrive on ``future.stream`` while the request runs in the shared batch
+            stream, pending, emitted = GenerationStream(), [], [""]
+
+            def on_token(rid, tok):
+                pending.append(tok)
+                text = st.tokenizer.decode(pending)
+                if text and not text.endswith("\ufffd"):
+                    stream._push(text[len(emitted[0]):])
+                    emitted[0] = text
         inner = self._loop.submit(ids, max_tokens=b._max_tokens, temperature=b._temperature, top_k=b._top_k, top_p=b._top_p,
-                                  eos_ids=eos, session_id=b._session_id, hook=c._hook_fn(b._hooks))
+                                  eos_ids=eos, session_id=b._session_id, hook=c._hook_fn(b._hooks), stream=on_token)
         outer: "cf.Future" = cf.Future()
+        outer.stream = stream
 
         def done(f):
             try:
                 res = f.result()
             except Exception as exc:
+                if stream is not None:
+                    stream._finish(error=exc)
                 outer.set_exception(exc)
                 return
             toks = res.token_ids
@@ -744,9 +757,12 @@ class AsyncClient:
             text = st.tokenizer.decode(toks)
             thinking, answer = split_thinking_content(text) if b._reasoning else ("", text)
             t = res.telemetry
-            outer.set_result(GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
-                                                prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
-                                                ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms))
+            resp = GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
+                                      prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
+                                      ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms)
+            if stream is not None:
+                stream._finish(resp)
+            outer.set_result(resp)
         inner.add_done_callback(done)
         outer.inner = inner
         return outer

@@ -206,6 +206,11 @@ def test_async_client_batches_concurrent_callers_through_the_serving_loop():
     got = [f.result(timeout=120).token_ids for f in futs]
     assert got == want
     assert ac._loop.stats["max_running"] > 1 and ac._loop.stats["finished"] == 6
+    streamed = ac.generate(prompts[2], max_tokens=12, temperature=0.0, stream=True)
+    other = ac.generate(prompts[3], max_tokens=12, temperature=0.0)
+    pieces = list(streamed.stream)                      # text arrives while both requests share the batch
+    assert "".join(pieces) == streamed.result(timeout=60).text and streamed.result().token_ids == want[2]
+    assert other.result(timeout=60).token_ids == want[3] and other.stream is None
     slow = ac.generate(prompts[0], max_tokens=100, temperature=0.0)
     assert ac.cancel(slow, "client went away")
     r = slow.result(timeout=120)
