@@ -759,7 +759,9 @@ class LLMEngine:
 
     def _variant_key(self, key):
         from ..runtime.variants import MechanismId, VariantKey
-        mech = (MechanismId.DENSE,) if key[1] else (MechanismId.DENSE, MechanismId.SAMPLED)
+        mech = (MechanismId.DENSE,) if key[1] is True else (MechanismId.DENSE, MechanismId.SAMPLED)
+        if key[1] == "topk":          # sampled from per-rank candidates: a graph of its own beside the full-vocabulary one
+            mech = mech + (MechanismId.SAMPLED,)
         if self.mc.is_moe:
             mech = mech + (MechanismId.MOE_EP,) if getattr(self.model, "ep", None) is not None else mech
         return VariantKey(int(key[0]), mech)
