@@ -138,6 +138,9 @@ class LLMEngine:
         if ec.kv_telemetry_every > 0:
             from .kv_telemetry import KvTelemetry
             self.kv_telemetry = KvTelemetry(self)
+            if self.kv_swap is not None:      # per-page tiers for the packed tier come from the sampled page headers
+                hdr = self.kv_telemetry.headers.h
+                self.kv_swap.page_tier = lambda page: (int(hdr["precision_tier"][page]) if int(hdr["ref_count"][page]) else 2)
         self._sessions = set()                # requests that belong to a multi-turn session (conversation pipeline)
         self.kv_importance: Dict[int, int] = {}      # request -> importance score 0..255 (callers / telemetry may set it)
         self.ms = ec.max_num_seqs

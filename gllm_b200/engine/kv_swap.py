@@ -35,7 +35,9 @@ class KvSwapManager:
         from ..kv_cache.turboquant import TurboQuantConfig
         self.turboquant = TurboQuantConfig(enabled=device_pool_pages > 0)
         self.sink_pages = (self.turboquant.sink_tokens + 15) // 16 if self.turboquant.enabled else 0
-        self.sink_keys: Dict[int, List[int]] = {}  # sequence packed on the device -> host keys of its sink pages
+        self.sink_keys: Dict[int, List[int]] = {}  # sequence packed on the device -> host keys of its lossless pages
+        self.layout: Dict[int, list] = {}          # sequence packed on the device -> per logical page ("host", key) | ("pool", slot)
+        self.page_tier = None                      # callable(page) -> PrecisionTier from the page headers (KV telemetry)
         self.packed: Dict[int, List[int]] = {}     # sequence packed on the device -> its pool slots, logical order
         if device_pool_pages > 0 and kv_caches[0].dim() == 5 and kv_caches[0].dtype != torch.float8_e4m3fn:
             from ..kv_cache.device_tier import Kivi4Pool
@@ -105,25 +107,32 @@ class KvSwapManager:
         tier = self.tier_policy(int(item.seq_id)) if self.tier_policy is not None else PrecisionTier.KIVI4
         if self.device_tier is not None and tier >= PrecisionTier.KIVI4:
             pages = [int(p) for p in item.pages]
-            n_sink = min(self.sink_pages, len(pages))
-            slots = self.device_tier.pack(pages[n_sink:])
+            # which pages keep full precision (host path): the sink pages, and with page telemetry those the KV optimiser
+            # wants above 4 bits (page_tier(page) -> PrecisionTier, from the page headers)
+            lossless = [j < self.sink_pages or (self.page_tier is not None and self.page_tier(pg) < PrecisionTier.KIVI4)
+                        for j, pg in enumerate(pages)]
+            slots = self.device_tier.pack([pg for pg, keep in zip(pages, lossless) if not keep])
             if slots is not None:
-                if n_sink:
-                    self._make_room_on_host(n_sink)
-                    keys = []
-                    for page in pages[:n_sink]:
+                n_host = sum(lossless)
+                keys = []
+                if n_host:
+                    self._make_room_on_host(n_host)
+                    for pg in (pg for pg, keep in zip(pages, lossless) if keep):
                         key = self._next_key
                         self._next_key += 1
-                        self.swap.register(key, page)
+                        self.swap.register(key, pg)
                         self.swap.execute(DmaCommand.EVICT_TO_DRAM, key)
                         keys.append(key)
                     self.swap.tick()
-                    self.sink_keys[int(item.seq_id)] = keys
+                ki, si = iter(keys), iter(slots)
+                self.layout[int(item.seq_id)] = [("host", next(ki)) if keep else ("pool", next(si)) for keep in lossless]
+                self.sink_keys[int(item.seq_id)] = keys
                 self.packed[int(item.seq_id)] = slots
                 self.forget(int(item.seq_id))
                 self.stats["swapped_out_seqs"] += 1
                 self.stats["packed_seqs"] += 1
                 self.stats["packed_pages"] += len(slots)
+                self.stats["pages_out"] += len(keys)
                 return
         self._make_room_on_host(len(item.pages))
         keys = []
@@ -144,17 +153,24 @@ class KvSwapManager:
         slots = self.packed.pop(int(item.seq_id), None)
         if slots is not None:
             pages = [int(p) for p in item.pages]
-            keys = self.sink_keys.pop(int(item.seq_id), [])
-            for key, page in zip(keys, pages):
-                if self.swap.records[key].tier == StorageTier.NVME:
-                    self._make_room_on_host(1)
-                self.swap.execute(DmaCommand.PROMOTE_TO_HBM, key, dev_page=page)
-                del self.swap.records[key]
+            layout = self.layout.pop(int(item.seq_id))
+            self.sink_keys.pop(int(item.seq_id), None)
+            pool_slots, pool_pages = [], []
+            for (kind, ref), page in zip(layout, pages):       # logical order: entry j goes to the j-th new page
+                if kind == "host":
+                    if self.swap.records[ref].tier == StorageTier.NVME:
+                        self._make_room_on_host(1)
+                    self.swap.execute(DmaCommand.PROMOTE_TO_HBM, ref, dev_page=page)
+                    del self.swap.records[ref]
+                    self.stats["pages_in"] += 1
+                else:
+                    pool_slots.append(ref)
+                    pool_pages.append(page)
             self.swap.dev_free.clear()
-            self.device_tier.unpack(slots, pages[len(keys):len(keys) + len(slots)])
+            self.device_tier.unpack(pool_slots, pool_pages)
             self.track(int(item.seq_id))
             self.stats["swapped_in_seqs"] += 1
-            self.stats["unpacked_pages"] += len(slots)
+            self.stats["unpacked_pages"] += len(pool_slots)
             return
         keys = self.keys.pop(int(item.seq_id), [])
         pairs = list(zip(keys, item.pages))
@@ -179,6 +195,7 @@ class KvSwapManager:
         slots = self.packed.pop(int(seq_id), None)
         if slots is not None:
             self.device_tier.release(slots)
+            self.layout.pop(int(seq_id), None)
             self.keys[int(seq_id)] = self.sink_keys.pop(int(seq_id), [])      # released with the host copies below
         for key in self.keys.pop(int(seq_id), []):
             r = self.swap.records.pop(key, None)

@@ -185,3 +185,28 @@ def test_kv_page_telemetry_feeds_headers_and_importance():
     q = torch.randn(eng.model.n_q_local * kv.shape[-1])
     st = attention_page_stats(q, kv, [3, 1, 2], 40, eng.model.n_q_local, eng.model.n_kv_local, 0.1)
     assert abs(float(st["mass"].sum()) - 1.0) < 1e-5 and st["entropy"].shape == (3,) and float(st["softmax_max"].max()) <= 1.0
+
+
+def test_per_page_tiers_split_a_victim_between_the_pool_and_the_host():
+    """With page telemetry the KV optimiser's tier of every page decides where it waits: pages it wants above 4 bits
+    (and the sink page) go to the host unchanged, the others are packed; they come back in logical order."""
+    from gllm_b200.kv_cache.header import PrecisionTier
+    from tests.test_engine_extras import _tiny_engine
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (40, 33, 48, 37, 45, 30)]
+    want = [r.token_ids for r in _tiny_engine(num_pages=128).generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])]
+    # every page lossless (the policy says FP16 for all): the pool is never used, tokens are exact
+    eng = _tiny_engine(num_pages=22, swap_space_pages=64, kv_kivi_pool_pages=32, kv_telemetry_every=1)
+    assert eng.kv_swap.page_tier is not None
+    eng.kv_swap.page_tier = lambda page: PrecisionTier.FP16
+    got = [r.token_ids for r in eng.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])]
+    assert got == want and eng.kv_swap.stats["packed_pages"] == 0 and eng.kv_swap.stats["pages_out"] > 0
+    # odd pages lossless, even pages packed: both tiers are used for the same victim
+    eng2 = _tiny_engine(num_pages=22, swap_space_pages=64, kv_kivi_pool_pages=32)
+    eng2.kv_swap.page_tier = lambda page: PrecisionTier.FP16 if page % 2 else PrecisionTier.KIVI4
+    res = eng2.generate_batch(prompts, max_tokens=40, temperature=0.0, eos_ids=[])
+    st = eng2.kv_swap.stats
+    assert [len(r.token_ids) for r in res] == [40] * 6
+    assert st["packed_pages"] == st["unpacked_pages"] > 0 and st["pages_out"] == st["pages_in"] > 0
+    assert not eng2.kv_swap.layout and not eng2.kv_swap.packed and not eng2.kv_swap.swap.records
+    assert len(eng2.kv_swap.device_tier.free) == 32
