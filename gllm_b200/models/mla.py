@@ -83,7 +83,11 @@ def mla_attention(model, w: MlaWeights, h, batch, cache, out):
             cached[idx_key] = _row_index(batch, T, h.device)
         row_seq, q_start, q_len = cached[idx_key]
     else:
-        row_seq, q_start, q_len = _row_index(batch, T, h.device)
+        # the same for every layer of this forward: computed once and kept on the batch
+        cached = batch.__dict__.setdefault("_mla_rows", {})
+        if "idx" not in cached:
+            cached["idx"] = _row_index(batch, T, h.device)
+        row_seq, q_start, q_len = cached["idx"]
     # queries
     if w.q_a is not None:
         qa = ops.gemm(h, w.q_a, out_dtype=h.dtype, bn=128)[:, :c.q_lora_rank].contiguous()
@@ -106,8 +110,13 @@ def mla_attention(model, w: MlaWeights, h, batch, cache, out):
                                 max_ctx=model.max_positions)
     elif h.is_cuda and d_c == 512 and rope_d == 64:
         # prefill chunks on the same tensor-core kernel: one row = one query token over its sequence's pages
-        lat = MLA.latent_prefill(q_full, cache, batch.block_tables, row_seq, batch.positions, batch.ctx_lens, n_heads=nh,
-                                 scale=model.scale, causal=batch.causal and c.causal, max_ctx=model.max_positions)
+        rows = batch.__dict__.setdefault("_mla_rows", {})
+        if "tables" not in rows:       # per-row block tables and context lengths: once per forward, not once per layer
+            rows["tables"] = batch.block_tables.index_select(0, row_seq.long()).contiguous()
+            rows["ctx"] = ((batch.positions + 1) if (batch.causal and c.causal) else
+                           batch.ctx_lens.index_select(0, row_seq.long())).to(torch.int32).contiguous()
+        lat = MLA.latent_decode(q_full, cache, rows["tables"], rows["ctx"], n_heads=nh, scale=model.scale,
+                                max_ctx=model.max_positions)
     else:
         lat = MLA.latent_attention(q_full, cache, batch.block_tables, q_start, q_len, batch.ctx_lens, row_seq, n_heads=nh,
                                    d_v=d_c, scale=model.scale, causal=batch.causal and c.causal)
