@@ -84,6 +84,9 @@ class ServingLoop:
 
     def _run(self):
         eng = self.engine
+        if getattr(eng.device, "type", "cpu") == "cuda":      # the current device is a per-thread setting
+            import torch
+            torch.cuda.set_device(eng.device)
         while True:
             self._admit()
             if not eng.has_work():
