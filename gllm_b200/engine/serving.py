@@ -71,6 +71,10 @@ class ServingLoop:
             prompt, params, fut = item
             if not fut.set_running_or_notify_cancel():
                 continue
+            if getattr(self.engine, "unhealthy", None):      # a device fault: nothing is served until the rank is reset
+                fut.set_exception(RuntimeError(f"engine unhealthy: {self.engine.unhealthy}"))
+                self.stats["errors"] += 1
+                continue
             try:
                 rid = self.engine.add_request(prompt, **params)
             except Exception as exc:          # bad request: the caller gets the error, the loop goes on

@@ -57,6 +57,8 @@ def create_app(client, embedding_client=None):
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
         created = int(time.time())
         stream = bool(body.get("stream", False))
+        if getattr(ac._loop.engine, "unhealthy", None):
+            raise HTTPException(status_code=503, detail=f"engine unhealthy: {ac._loop.engine.unhealthy}")
         try:
             fut = ac.generate(prompt, stream=stream, **_params(body))
         except Exception as exc:

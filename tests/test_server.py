@@ -52,3 +52,10 @@ def test_completion_chat_stream_health_and_metrics():
         assert http.get("/v1/models").json()["data"][0]["object"] == "model"
         m = http.get("/metrics")
         assert m.status_code == 200 and "gllm_" in m.text
+        # a device fault marks the engine unhealthy: the front end answers 503 and says why
+        app.state.async_client._loop.engine.unhealthy = "device status 5 (timeout waiting for a peer)"
+        r = http.post("/v1/completions", json={"prompt": "hello", "max_tokens": 2})
+        assert r.status_code == 503 and "unhealthy" in r.json()["detail"]
+        assert http.get("/health").json()["status"] == "unhealthy"
+        app.state.async_client._loop.engine.unhealthy = None
+        assert http.post("/v1/completions", json={"prompt": "hello", "max_tokens": 2, "temperature": 0.0}).status_code == 200
