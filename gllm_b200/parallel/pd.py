@@ -80,8 +80,9 @@ def kv_dist_plan(mode: KvDistMode, rank: int, world: int, n_kv_heads: int) -> Di
 
 
 class KvDistributor:
-    """The KV distribution modes over a set of serving engines (one per rank; here reachable as objects: engines of
-    one process, or proxies that move the page tensors over a ``CommHandle``).
+    """The KV distribution modes over a set of serving engines reachable as objects: the engines of one process (one
+    per GPU of a node, each e.g. behind its own ``ServingLoop``); page tensors move device to device with ``.to()``.
+    Engines of different processes hand pages over with the ``engine.pd`` links instead.
 
     LOCAL: nothing moves. MIRROR: after a request finishes, the full pages of its conversation are copied into every
     peer's prefix cache, so the next turn may land anywhere. ON_DEMAND (and TIERED / PARTIAL_HEAD_MIRROR for the part
