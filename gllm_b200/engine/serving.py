@@ -40,6 +40,14 @@ class ServingLoop:
         self.stats["submitted"] += 1
         return fut
 
+    def run_in_loop(self, fn) -> "cf.Future":
+        """Run ``fn()`` on the worker thread between two steps (the only thread that may touch the engine: prefix
+        look-ups, page export / import for the KV distribution modes). The future resolves to its return value."""
+        fut: cf.Future = cf.Future()
+        self._inbox.put(("call", fn, fut))
+        self._wake.set()
+        return fut
+
     def cancel(self, fut: "cf.Future", reason: str = "aborted") -> bool:
         """Ask for a submitted request to end early (its future still resolves, with that finish reason)."""
         if fut.done():
@@ -61,6 +69,13 @@ class ServingLoop:
                 item = self._inbox.get_nowait()
             except queue.Empty:
                 return
+            if item[0] == "call":
+                _, fn, fut = item
+                try:
+                    fut.set_result(fn())
+                except Exception as exc:
+                    fut.set_exception(exc)
+                continue
             if item[0] == "cancel":
                 _, fut, reason = item
                 if fut.request_id is not None:
@@ -114,3 +129,60 @@ class ServingLoop:
                 fut = self._futures.pop(rid)
                 fut.set_result(eng.results.pop(rid))
                 self.stats["finished"] += 1
+
+
+class ReplicaRouter:
+    """Data-parallel replicas of one model in one process (one engine per GPU, each behind its own ``ServingLoop``):
+    a request goes to the replica whose prefix cache already holds the longest prefix of its prompt (a follow-up turn
+    lands where the conversation lives), ties go to the replica with the fewest requests in flight. With
+    ``fetch_on_miss`` a replica that lacks a prefix another one holds (the preferred replica is over ``max_in_flight``)
+    receives the pages first (the ON_DEMAND behaviour of the KV distribution modes: export on the owner's thread, import
+    on the target's, device to device). Reference: KV distribution modes of the coordinator
+    (src/engine/coordinator/kv.rs:52-156, 395-569)."""
+
+    def __init__(self, loops, fetch_on_miss: bool = True, max_in_flight: int = 1 << 30):
+        self.loops = list(loops)
+        self.fetch_on_miss, self.max_in_flight = fetch_on_miss, max_in_flight
+        self.in_flight = [0] * len(self.loops)
+        self._lock = threading.Lock()
+        self.stats = {"routed": [0] * len(self.loops), "affinity_hits": 0, "fetched_pages": 0}
+
+    def _cached_pages(self, i: int, tokens) -> int:
+        full = [int(t) for t in tokens[:len(tokens) // 16 * 16]]
+        if not full:
+            return 0
+        eng = self.loops[i].engine
+        return len(self.loops[i].run_in_loop(lambda: eng.batcher.lookup_prefix_pages(full)).result())
+
+    def submit(self, prompt_ids, **params) -> "cf.Future":
+        tokens = list(prompt_ids)
+        cached = [self._cached_pages(i, tokens) for i in range(len(self.loops))]
+        with self._lock:
+            load = list(self.in_flight)
+        best = max(range(len(self.loops)), key=lambda i: (cached[i], -load[i]))
+        target = best
+        if load[best] >= self.max_in_flight and len(self.loops) > 1:      # the replica that has the prefix is saturated
+            target = min((i for i in range(len(self.loops)) if i != best), key=lambda i: load[i])
+        if cached[best] > 0 and target == best:
+            self.stats["affinity_hits"] += 1
+        if target != best and self.fetch_on_miss and cached[best] > cached[target]:
+            src, dst = self.loops[best].engine, self.loops[target].engine
+            n, pages = self.loops[best].run_in_loop(lambda: src.export_prefix_pages(tokens)).result()
+            if n:
+                got = self.loops[target].run_in_loop(lambda: dst.import_prefix_pages(tokens, pages)).result()
+                self.stats["fetched_pages"] += got
+        with self._lock:
+            self.in_flight[target] += 1
+        self.stats["routed"][target] += 1
+        fut = self.loops[target].submit(tokens, **params)
+        fut.replica = target
+
+        def done(_):
+            with self._lock:
+                self.in_flight[target] -= 1
+        fut.add_done_callback(done)
+        return fut
+
+    def shutdown(self):
+        for lp in self.loops:
+            lp.shutdown()

@@ -438,3 +438,33 @@ def test_abort_cancels_waiting_and_running_requests():
     assert c.finish_reason == "aborted" and len(c.token_ids) == 0
     assert b.finish_reason == "length" and len(b.token_ids) == 30
     assert eng.batcher.num_free_pages == eng.batcher.num_total_pages or eng.cfg.enable_prefix_cache
+
+
+def test_replica_router_keeps_conversations_on_their_replica_and_fetches_pages_when_it_cannot():
+    from gllm_b200.engine.serving import ReplicaRouter, ServingLoop
+    g = torch.Generator().manual_seed(21)
+    a, b = _tiny_engine(num_pages=96, enable_prefix_cache=True), _tiny_engine(num_pages=96, enable_prefix_cache=True)
+    router = ReplicaRouter([ServingLoop(a), ServingLoop(b)])
+    turn1 = torch.randint(0, 1000, (50,), generator=g).tolist()
+    other = torch.randint(0, 1000, (45,), generator=g).tolist()
+    f1 = router.submit(turn1, max_tokens=10, temperature=0.0, eos_ids=[])
+    f2 = router.submit(other, max_tokens=10, temperature=0.0, eos_ids=[])          # the less loaded replica takes it
+    r1, r2 = f1.result(timeout=120), f2.result(timeout=120)
+    assert {f1.replica, f2.replica} == {0, 1}
+    convo = turn1 + r1.token_ids
+    turn2 = convo + torch.randint(0, 1000, (7,), generator=g).tolist()
+    f3 = router.submit(turn2, max_tokens=5, temperature=0.0, eos_ids=[])
+    r3 = f3.result(timeout=120)
+    assert f3.replica == f1.replica and router.stats["affinity_hits"] >= 1          # the turn follows its conversation
+    assert r3.telemetry.cached_prefix_tokens == len(convo) // 16 * 16
+    want = _tiny_engine(num_pages=96).generate_batch([turn2], max_tokens=5, temperature=0.0, eos_ids=[])[0]
+    assert r3.token_ids == want.token_ids
+    # the owner is "saturated": the other replica gets the request and fetches the conversation's pages first
+    router.max_in_flight = 0
+    turn3 = turn2 + r3.token_ids + [5, 6, 7]
+    f4 = router.submit(turn3, max_tokens=4, temperature=0.0, eos_ids=[])
+    r4 = f4.result(timeout=120)
+    assert router.stats["fetched_pages"] > 0 and r4.telemetry.cached_prefix_tokens > 0
+    want4 = _tiny_engine(num_pages=96).generate_batch([turn3], max_tokens=4, temperature=0.0, eos_ids=[])[0]
+    assert r4.token_ids == want4.token_ids
+    router.shutdown()
