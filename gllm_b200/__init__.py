@@ -9,6 +9,8 @@ __version__ = "0.1.0"
 _LAZY = {
     "Client": "client", "ClientBuilder": "client", "AsyncClient": "client", "GllmError": "client",
     "GenerateRequest": "engine.batch", "ModelKind": "models.registry",
+    "LLMEngine": "engine.executor", "EngineConfig": "engine.executor", "ServingLoop": "engine.serving",
+    "ReplicaRouter": "engine.serving", "DecoderModel": "models.decoder", "ModelConfig": "models.config",
 }
 
 
