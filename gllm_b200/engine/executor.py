@@ -68,6 +68,7 @@ class EngineConfig:
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
+    speculative_max_batch: int = 32    # no speculative steps while more sequences than this are decoding
     # multi-token prediction: use the model's MTP heads (when the checkpoint has them) as the draft source; every step
     # verifies the previous step's candidates (0 = off)
     mtp_depth: int = 0
@@ -232,6 +233,10 @@ class LLMEngine:
         if ec.mtp_depth > 0 and getattr(model, "mtp_heads", None):
             from ..speculative.mtp_executor import MtpExecutor
             self.mtp = MtpExecutor(min(ec.mtp_depth, len(model.mtp_heads)))
+        # when speculation pays: off for large batches (compute bound), under memory pressure, or once the acceptance
+        # average has fallen too low; the draft length follows the acceptance average (speculative/engine.py)
+        from ..speculative.engine import SpecDecodingState, SpecMode
+        self.spec_state = SpecDecodingState(mode=SpecMode.NGRAM, max_batch_for_spec=max(32, ec.speculative_max_batch))
         self.eagle = None                           # speculative.heads.EagleHead (attach_eagle): feature-level drafts
         self.eagle_depth = 0
         self._eagle_feat: Dict[int, torch.Tensor] = {}      # request -> hidden state behind its last committed token
@@ -540,8 +545,10 @@ class LLMEngine:
         Reference parity: ``draft_phase`` / ``verify_phase`` (src/speculative/engine.rs:310-420), PLD spine and n-gram
         index (src/speculative/tree.rs:93-340,394-452), KV rollback by position (src/engine/mtp_executor.rs)."""
         from ..speculative.verify import verify_greedy
-        k = self.cfg.speculative_tokens
         ids = plan.dec_seq_ids
+        pressure = 1.0 - self.batcher.num_free_pages / max(self.batcher.num_total_pages, 1)
+        lookup_on = self.spec_state.should_speculate(int((ids >= 0).sum()), pressure)
+        k = min(self.cfg.speculative_tokens, self.spec_state.controller.draft_len()) if lookup_on else 0
         slots = [int(sl) for sl in np.nonzero(ids >= 0)[0]]
         drafts, from_mtp = {}, {}
         for sl in slots:
@@ -626,6 +633,8 @@ class LLMEngine:
             st["drafted"] += len(d)
             st["accepted"] += n_acc
             st["emitted"] += len(new)
+            if d and not from_mtp.get(sl):
+                self.spec_state.record(len(d), n_acc)
             if hid is not None:           # the feature behind the last token that stays: the next draft starts there
                 self._eagle_feat[int(ids[sl])] = hid[q_start[j] + n_acc].clone()
             self.stats["decode_tokens"] += len(new)

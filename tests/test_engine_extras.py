@@ -468,3 +468,30 @@ def test_replica_router_keeps_conversations_on_their_replica_and_fetches_pages_w
     want4 = _tiny_engine(num_pages=96).generate_batch([turn3], max_tokens=4, temperature=0.0, eos_ids=[])[0]
     assert r4.token_ids == want4.token_ids
     router.shutdown()
+
+
+def test_speculation_switches_off_when_drafts_keep_failing_and_for_large_batches():
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 1000, (24,), generator=g).tolist()
+    want = _tiny_engine(num_pages=64).generate_batch([prompt], max_tokens=40, temperature=0.0, eos_ids=[])[0].token_ids
+
+    class Wrong:                      # a draft source that is always wrong
+        def extend(self, toks):
+            pass
+
+        def lookup(self, k, top=1):
+            return [[1001 % 1000 + 7] * k]
+    eng = _tiny_engine(num_pages=64, speculative_tokens=4)
+    rid = eng.add_request(prompt, max_tokens=40, temperature=0.0, eos_ids=[])
+    eng._spec_idx[rid] = Wrong()
+    eng.run_until_done()
+    assert eng.results[rid].token_ids == want
+    st = eng.spec_stats
+    assert eng.spec_state.controller.draft_len() == 0            # the acceptance average fell below the switch-off level
+    assert 0 < st["steps"] < 30 and st["accepted"] <= 2          # it stopped drafting long before the request ended
+    # more decoding sequences than speculative_max_batch: the plain (captured) decode step runs instead
+    many = _tiny_engine(num_pages=256, speculative_tokens=4, speculative_max_batch=32, max_num_seqs=40)
+    base = torch.randint(0, 1000, (6,), generator=g).tolist()
+    outs = many.generate_batch([base * 3 + [i] for i in range(36)], max_tokens=6, temperature=0.0, eos_ids=[])
+    assert all(len(r.token_ids) == 6 for r in outs)
+    assert many.spec_stats["steps"] < many.stats["decode_steps"]
