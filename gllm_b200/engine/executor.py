@@ -961,6 +961,8 @@ class LLMEngine:
             else:
                 with nvtx_range("decode_step"):
                     dec_tokens = self._run_decode(plan).copy()
+                if self.mtp is not None:
+                    self.mtp.controller.update(0, 0)        # a plain step: counts towards switching the heads back on
                 if self.kv_telemetry is not None and self._steps % self.cfg.kv_telemetry_every == 0:
                     self.kv_telemetry.sample(plan)      # before a prefill chunk reuses the workspace rows
         if plan.num_prefill_seqs > 0:

@@ -181,3 +181,24 @@ def test_observer_request_state_and_chunking():
     assert compaction_plan([0, 3, 5]) == [(3, 1), (5, 2)]
     sk = SwiftKvPlan(32)
     assert sk.cut_layer == 16 and len(sk.skipped_layers()) == 16 and sk.prefill_flop_ratio() == 0.5
+
+
+def test_mtp_controller_follows_the_reference_policy():
+    """alpha 0.1 from 0.5; three low steps in a row switch the heads off; five plain steps switch them back on; the depth
+    follows the average (> 0.8 full, > 0.5 two, > 0.3 one)."""
+    from gllm_b200.speculative.mtp_executor import MtpController
+    c = MtpController(4)
+    assert c.enabled and c.draft_len() == 1 and abs(c.ema - 0.5) < 1e-9            # 0.5 is not > 0.5
+    c.update(4, 4)
+    assert abs(c.ema - 0.55) < 1e-6 and c.draft_len() == 2
+    for _ in range(30):
+        c.update(4, 4)
+    assert c.ema > 0.8 and c.draft_len() == 4
+    assert c.update(0, 4) and c.update(1, 4) and not c.update(0, 4)               # the third low step in a row
+    assert c.draft_len() == 0
+    for _ in range(4):
+        assert not c.update(0, 0)
+    assert c.update(0, 0) and c.enabled                                            # the fifth plain step
+    c2 = MtpController(4)
+    c2.update(0, 4); c2.update(4, 4); c2.update(0, 4); c2.update(0, 4)
+    assert c2.enabled                                                              # the streak was broken
