@@ -84,6 +84,7 @@ PYBIND11_MODULE(_sched, m) {
       .def_readwrite("watermark_pages", &PolicyConfig::watermark_pages)
       .def_readwrite("enable_prefix_cache", &PolicyConfig::enable_prefix_cache)
       .def_readwrite("preempt_swap", &PolicyConfig::preempt_swap)
+      .def_readwrite("adaptive_chunk", &PolicyConfig::adaptive_chunk)
       .def_readwrite("phase_isolated", &PolicyConfig::phase_isolated)
       .def_readwrite("order", &PolicyConfig::order);
 

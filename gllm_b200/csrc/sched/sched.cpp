@@ -488,7 +488,15 @@ StepPlan ContinuousBatcher::schedule() {
     const int known = static_cast<int>(s.tokens.size());
     const int remaining = known - s.num_computed;
     if (remaining <= 0 || budget <= 0) return false;
-    int chunk = std::min(remaining, std::min(budget, cfg_.prefill_chunk));
+    int cap = cfg_.prefill_chunk;
+    if (cfg_.adaptive_chunk) {
+      const double free_ratio = static_cast<double>(alloc_.num_free()) / std::max(1, num_total_pages());
+      const int lo = std::min(cfg_.min_prefill_chunk, cfg_.prefill_chunk);
+      if (free_ratio < 0.25) cap = lo;
+      else if (free_ratio < 0.75) cap = lo + static_cast<int>((cfg_.prefill_chunk - lo) * (free_ratio - 0.25) / 0.5);
+      cap = std::max(page_size_, cap / page_size_ * page_size_);      // whole pages
+    }
+    int chunk = std::min(remaining, std::min(budget, cap));
     // A sliver left over by the budget is not worth a launch, unless the step would otherwise be empty
     // (progress guarantee) or the configured chunk cap itself is that small.
     const int min_chunk = std::min(cfg_.min_prefill_chunk, cfg_.prefill_chunk);

@@ -127,6 +127,9 @@ struct PolicyConfig {
   // again later); true = swap (the plan lists the victim's pages in `swap_out`, the caller copies them to host memory
   // before the step runs, the sequence keeps its position and comes back through `swap_in` when pages are free).
   bool preempt_swap = false;
+  // Prefill chunk size from the share of free pages: under a quarter free the smallest chunk, above three quarters the
+  // largest, linear in between (the reference's adaptive chunk: src/scheduler/vllm2024.rs:24-68).
+  bool adaptive_chunk = false;
 };
 
 struct SystemState {

@@ -65,6 +65,9 @@ class EngineConfig:
     # every this many engine steps the attention telemetry of the running sequences' KV pages is sampled into the page
     # headers and each request's importance score is refreshed (engine/kv_telemetry.py); 0 = never
     kv_telemetry_every: int = 0
+    # prefill chunk size follows the share of free KV pages (64 tokens under a quarter free, ``prefill_chunk`` above three
+    # quarters, linear in between) instead of always taking ``prefill_chunk``
+    adaptive_prefill_chunk: bool = False
     # speculative decoding by prompt lookup: up to this many draft tokens per sequence and step (0 = off)
     speculative_tokens: int = 0
     speculative_ngram: int = 3
@@ -128,6 +131,7 @@ class LLMEngine:
         pc.enable_prefix_cache = ec.enable_prefix_cache
         pc.order = ec.order
         pc.preempt_swap = ec.swap_space_pages > 0
+        pc.adaptive_chunk = bool(ec.adaptive_prefill_chunk)
         self.batcher = S.ContinuousBatcher(self.num_pages, 16, ec.max_num_seqs, self.max_blocks, pc)
         self.kv_swap = None
         if ec.swap_space_pages > 0:

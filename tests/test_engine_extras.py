@@ -495,3 +495,28 @@ def test_speculation_switches_off_when_drafts_keep_failing_and_for_large_batches
     outs = many.generate_batch([base * 3 + [i] for i in range(36)], max_tokens=6, temperature=0.0, eos_ids=[])
     assert all(len(r.token_ids) == 6 for r in outs)
     assert many.spec_stats["steps"] < many.stats["decode_steps"]
+
+
+def test_adaptive_prefill_chunk_follows_free_pages():
+    """Plenty of free pages: the prompt is prefilled in one chunk of up to ``prefill_chunk`` tokens; with the pool
+    partly taken the chunk shrinks (between the minimum of 64 and the maximum, by the share of free pages: two prefill
+    steps here), and the tokens do not change."""
+    g = torch.Generator().manual_seed(13)
+    long_prompt = torch.randint(0, 1000, (100,), generator=g).tolist()
+    filler = [torch.randint(0, 1000, (60,), generator=g).tolist() for _ in range(7)]
+    base = dict(max_num_seqs=8, max_model_len=200, max_batch_tokens=512, prefill_chunk=128, enable_prefix_cache=False)
+    want = _tiny_engine(num_pages=256, **base).generate_batch([long_prompt], max_tokens=4, temperature=0.0, eos_ids=[])[0]
+    roomy = _tiny_engine(num_pages=256, adaptive_prefill_chunk=True, **base)
+    r = roomy.generate_batch([long_prompt], max_tokens=4, temperature=0.0, eos_ids=[])[0]
+    assert r.token_ids == want.token_ids and roomy.stats["prefill_steps"] == 1
+    tight = _tiny_engine(num_pages=48, adaptive_prefill_chunk=True, **base)
+    for p in filler:
+        tight.add_request(p, max_tokens=40, temperature=0.0, eos_ids=[])
+    tight.step()                             # the fillers' prompts hold 28 of the 48 pages now
+    assert 0.25 < tight.batcher.num_free_pages / tight.batcher.num_total_pages < 0.5      # chunk cap about 80 tokens
+    before = tight.stats["prefill_steps"]
+    rid = tight.add_request(long_prompt, max_tokens=4, temperature=0.0, eos_ids=[])
+    while rid not in tight.results:
+        tight.step()
+    assert tight.results[rid].token_ids == want.token_ids
+    assert tight.stats["prefill_steps"] - before >= 2                                    # 80 + 20 tokens
