@@ -1,6 +1,6 @@
 """What is in a checkpoint file: tensors (name, type, shape, bytes) and metadata, for GGUF, SafeTensors and .gllm.
 
-    python -m gllm_b200.loader.inspect model.gguf [--tensors] [--keys] [--filter substring] [--json]
+    python -m gllm_b200.loader.describe model.gguf [--tensors] [--keys] [--filter substring] [--json]
 
 Reference parity: the inspection examples of the reference (examples/gguf_inspect.rs, list_gguf_keys.rs,
 list_gguf_tensors.rs, gguf_tensors.rs, list_qwen3_tensors.rs).

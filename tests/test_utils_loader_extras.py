@@ -136,7 +136,7 @@ def test_checkpoint_inspector_and_dump_comparison(tmp_path, capsys):
     import torch
     from gllm_b200.engine.guard import dump_tensors
     from gllm_b200.loader.gguf import write_gguf
-    from gllm_b200.loader.inspect import describe, main as inspect_main
+    from gllm_b200.loader.describe import describe, main as inspect_main
     from gllm_b200.loader.safetensors import save_file
     from gllm_b200.utils.compare_dumps import compare, main as compare_main
     st = tmp_path / "m.safetensors"
