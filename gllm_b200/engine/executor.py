@@ -968,7 +968,7 @@ class LLMEngine:
                 if self.mtp is not None:
                     self.mtp.controller.update(0, 0)        # a plain step: counts towards switching the heads back on
                 if self.kv_telemetry is not None and self._steps % self.cfg.kv_telemetry_every == 0:
-                    self.kv_telemetry.sample(plan)      # before a prefill chunk reuses the workspace rows
+                    self.kv_telemetry.sample(plan, max_sequences=32)      # before a prefill chunk reuses the workspace rows
         if plan.num_prefill_seqs > 0:
             with nvtx_range("prefill_chunk"):
                 pf_tokens = self._run_prefill(plan)

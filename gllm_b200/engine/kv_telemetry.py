@@ -77,7 +77,10 @@ class KvTelemetry:
             return {}            # the workspace holds the LAST layer's queries and that layer has no pages of its own
         kv = eng.kv_caches[layer]
         out: Dict[int, int] = {}
-        slots = [int(sl) for sl in (plan.dec_seq_ids >= 0).nonzero()[0]][:max_sequences]
+        slots = [int(sl) for sl in (plan.dec_seq_ids >= 0).nonzero()[0]]
+        if max_sequences is not None and len(slots) > max_sequences:      # a rotating window over the running set
+            start = (self.samples * max_sequences) % len(slots)
+            slots = (slots + slots)[start:start + max_sequences]
         for slot in slots:
             rid, ctx = int(plan.dec_seq_ids[slot]), int(plan.dec_positions[slot]) + 1
             pages = list(eng.batcher.block_table_of(rid))
