@@ -224,6 +224,30 @@ class Client:
             raise ModelNotFoundError(str(e)) from e
         k = kind or ModelKind(loaded.config.kind if loaded.config.kind in ModelKind._value2member_map_ else "chat")
         self._install(model_id, k, loaded, loaded.config, loaded.weights, loaded.tokenizer)
+        self._attach_checkpoint_encoder(loaded)
+
+    def _attach_checkpoint_encoder(self, loaded):
+        """A multimodal SafeTensors checkpoint (a ``vision_config`` in its config.json and a SigLIP / CLIP style tower
+        among its tensors) gets its image encoder without a ``set_multimodal_encoder`` call."""
+        import json
+        from pathlib import Path
+        raw = getattr(loaded.weights, "model", None)
+        root = Path(loaded.path) if Path(loaded.path).is_dir() else Path(loaded.path).parent
+        cj = root / "config.json"
+        if raw is None or not hasattr(raw, "keys") or not cj.exists() or not loaded.config.causal:
+            return
+        try:
+            hf = json.loads(cj.read_text())
+        except ValueError:
+            return
+        if not hf.get("vision_config"):
+            return
+        from .models.multimodal import MultimodalEncoder
+        model = self._st().model
+        enc = MultimodalEncoder.from_checkpoint(list(raw.keys()), raw.tensor, hf, loaded.config.hidden_size,
+                                                device=model.device, dtype=model.dtype)
+        if enc is not None:
+            self._multimodal_encoder = enc
 
     def _install(self, model_id, kind, loaded, cfg, weights, tokenizer, device=None, dtype=None):
         from .backend import detect_backend

@@ -107,7 +107,10 @@ _GLOBAL_RULES = [
 ]
 _GLOBAL_RULES = [(re.compile(p), c, r) for p, c, r in _GLOBAL_RULES]
 
-_LAYER_PREFIX = re.compile(r"^(?:model\.|transformer\.|bert\.|roberta\.|encoder\.)*(?:layers|h|layer|blocks|blk|encoder\.layer)\.(\d+)\.(.+)$")
+_LAYER_PREFIX = re.compile(r"^(?:model\.|language_model\.|text_model\.|transformer\.|bert\.|roberta\.|encoder\.)*(?:layers|h|layer|blocks|blk|encoder\.layer)\.(\d+)\.(.+)$")
+# tensors of a multimodal checkpoint's towers and projectors are not the language model's: they have their own loaders
+_NOT_LANGUAGE = re.compile(r"(^|\.)(vision_tower|vision_model|visual|audio_tower|audio_model|multi_modal_projector|"
+                           r"embed_vision|embed_audio|mm_projector)\.")
 _SUFFIXES = (".weight", ".bias", ".qweight", ".qzeros", ".scales", ".g_idx", ".weight_scale", ".weight_scale_2",
              ".weight_scale_inv", ".input_scale", "_blocks", "_scales", "_bias")
 
@@ -126,6 +129,8 @@ def match_tensor_role(name: str) -> Tuple[TensorRole, Optional[int], Optional[st
     Canonical names carry ``_bias`` for biases and the raw suffix for quantisation companions.
     """
     stem, suffix = split_suffix(name)
+    if _NOT_LANGUAGE.search(name):
+        return TensorRole.UNKNOWN, None, None, suffix
     m = _LAYER_PREFIX.match(stem)
     if m:
         layer, rest = int(m.group(1)), m.group(2)

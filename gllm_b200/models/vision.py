@@ -44,7 +44,8 @@ class VisionWeights:
         g = torch.Generator().manual_seed(seed)
         mk = lambda *s, std=0.02: (torch.randn(*s, generator=g) * std).to(device, dtype)
         H = cfg.hidden
-        t = tensors or {}
+        # supplied tensors move to the tower's device; matrices take its dtype, norm weights and biases stay as they are
+        t = {k: (v.to(device, dtype) if v.dim() >= 2 else v.to(device)) for k, v in (tensors or {}).items()}
         pd = cfg.channels * cfg.patch_size * cfg.patch_size
         self.patch_w = t.get("patch_embed.weight", mk(H, pd))
         self.patch_b = t.get("patch_embed.bias", torch.zeros(H, device=device, dtype=torch.float32))
@@ -63,6 +64,37 @@ class VisionWeights:
         self.post_w = t.get("post_ln.weight", torch.ones(H, device=device))
         self.post_b = t.get("post_ln.bias", torch.zeros(H, device=device))
         self.proj_w = t.get("proj.weight", mk(cfg.out_hidden, H)) if cfg.out_hidden else None
+
+
+def siglip_tensors(cfg: VisionConfig, get, has=None, prefix: str = "vision_model.") -> dict:
+    """Checkpoint tensors of a SigLIP / CLIP style vision tower under their Hugging Face names -> the names
+    ``VisionWeights`` reads: the convolutional patch embedding [H, C, p, p] becomes a [H, C * p * p] matrix, the three
+    attention projections of a layer are stacked into one qkv matrix. ``get(name)`` returns a tensor, ``has(name)``
+    (optional) says whether it exists. Reference: SigLIP tower weights behind the multimodal projector
+    (src/arch/auto_graph_fragments/build_graph.inc.rs vision branch, src/loader/name_map.rs)."""
+    has = has or (lambda n: True)
+    t = {}
+    pe = get(prefix + "embeddings.patch_embedding.weight")
+    t["patch_embed.weight"] = pe.reshape(pe.shape[0], -1)
+    if has(prefix + "embeddings.patch_embedding.bias"):
+        t["patch_embed.bias"] = get(prefix + "embeddings.patch_embedding.bias").float()
+    t["pos_embed"] = get(prefix + "embeddings.position_embedding.weight")
+    for l in range(cfg.layers):
+        src, dst = f"{prefix}encoder.layers.{l}.", f"layers.{l}."
+        t[dst + "ln1.weight"], t[dst + "ln1.bias"] = get(src + "layer_norm1.weight"), get(src + "layer_norm1.bias")
+        t[dst + "ln2.weight"], t[dst + "ln2.bias"] = get(src + "layer_norm2.weight"), get(src + "layer_norm2.bias")
+        t[dst + "qkv.weight"] = torch.cat([get(src + f"self_attn.{n}_proj.weight") for n in "qkv"], 0)
+        t[dst + "qkv.bias"] = torch.cat([get(src + f"self_attn.{n}_proj.bias") for n in "qkv"], 0)
+        t[dst + "o.weight"], t[dst + "o.bias"] = get(src + "self_attn.out_proj.weight"), get(src + "self_attn.out_proj.bias")
+        t[dst + "fc1.weight"], t[dst + "fc1.bias"] = get(src + "mlp.fc1.weight"), get(src + "mlp.fc1.bias")
+        t[dst + "fc2.weight"], t[dst + "fc2.bias"] = get(src + "mlp.fc2.weight"), get(src + "mlp.fc2.bias")
+    t["post_ln.weight"], t["post_ln.bias"] = get(prefix + "post_layernorm.weight"), get(prefix + "post_layernorm.bias")
+    for cand in ("multi_modal_projector.linear.weight", "multi_modal_projector.mm_input_projection_weight"):
+        if cfg.out_hidden and has(cand):
+            w = get(cand)
+            t["proj.weight"] = w if w.shape[0] == cfg.out_hidden else w.t().contiguous()
+            break
+    return t
 
 
 def patchify(images: torch.Tensor, patch: int) -> torch.Tensor:
