@@ -785,6 +785,8 @@ class AsyncClient:
                                       prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
                                       ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms)
             if stream is not None:
+                if len(text) > len(emitted[0]) and text.startswith(emitted[0]):
+                    stream._push(text[len(emitted[0]):])       # a tail that was held back as an incomplete character
                 stream._finish(resp)
             outer.set_result(resp)
         inner.add_done_callback(done)

@@ -59,3 +59,79 @@ def test_completion_chat_stream_health_and_metrics():
         assert http.get("/health").json()["status"] == "unhealthy"
         app.state.async_client._loop.engine.unhealthy = None
         assert http.post("/v1/completions", json={"prompt": "hello", "max_tokens": 2, "temperature": 0.0}).status_code == 200
+
+
+def test_stop_cutter_holds_back_a_straddling_stop_string():
+    from gllm_b200.server import StopCutter
+    c = StopCutter(["END", "\n\n"])
+    out = [c.feed(p) for p in ("abc", "dE", "N", "D tail", "more")]
+    assert "".join(out) == "abcd" and c.hit and c.flush() == ""
+    c = StopCutter(["END"])
+    shown = c.feed("hello E") + c.feed("N")
+    assert shown == "hello " and not c.hit and shown + c.flush() == "hello EN"
+
+
+def test_stop_strings_rerank_and_classify_routes():
+    from types import SimpleNamespace as NS
+    from fastapi.testclient import TestClient
+    from gllm_b200.client import ClassifyResult, RerankResult
+    from gllm_b200.server import create_app
+
+    class Builder:
+        def __init__(self, rows):
+            self.rows = rows
+
+        def top_n(self, n):
+            return Builder(self.rows[:n])
+
+        def generate(self):
+            return self.rows
+
+    class Aux:                                          # what the routes need of a reranker / classifier client
+        def _st(self):
+            return NS(model_id="aux")
+
+        def rerank(self, q, docs):
+            return Builder(sorted((RerankResult(i, float(len(d)), d) for i, d in enumerate(docs)), key=lambda r: -r.score))
+
+        def classify(self, texts):
+            return Builder([ClassifyResult(len(t) % 2, 0.75, [0.25, 0.75][::1 if len(t) % 2 else -1]) for t in texts])
+
+    c, _ = _app()
+    app = create_app(c, None, Aux(), Aux())
+    with TestClient(app) as http:
+        # the stop logic against a scripted stream (a random-weight model's text is not a stable fixture)
+        ac, cancelled = app.state.async_client, []
+        real_generate, real_cancel = ac.generate, ac.cancel
+
+        def scripted(prompt, **kw):
+            assert kw.get("stream") is True
+            res = NS(text="abcdEND tail", token_ids=[1, 2, 3, 4], prompt_tokens=3, cached_prefix_tokens=0,
+                     finish_reason="length", ttft_ms=1.0, tpot_ms=1.0)
+            return NS(stream=iter(["abc", "dE", "ND", " tail"]), result=lambda: res, done=lambda: True)
+        ac.generate, ac.cancel = scripted, lambda fut, reason="aborted": cancelled.append(reason)
+        r = http.post("/v1/completions", json={"prompt": "p", "stop": "END"}).json()
+        assert r["choices"][0]["text"] == "abcd" and r["choices"][0]["finish_reason"] == "stop" and cancelled == ["stop"]
+        r = http.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "p"}], "stop": ["zz", "c"]}).json()
+        assert r["choices"][0]["message"]["content"] == "ab" and r["choices"][0]["finish_reason"] == "stop"
+        r = http.post("/v1/completions", json={"prompt": "p", "stop": "never"}).json()
+        assert r["choices"][0]["text"] == "abcdEND tail" and r["choices"][0]["finish_reason"] == "length"
+        pieces, finish = [], None
+        with http.stream("POST", "/v1/completions", json={"prompt": "p", "stop": ["END"], "stream": True}) as resp:
+            for line in resp.iter_lines():
+                if line.startswith("data: ") and line != "data: [DONE]":
+                    ev = json.loads(line[6:])
+                    pieces.append(ev["choices"][0]["text"])
+                    finish = ev["choices"][0]["finish_reason"] or finish
+        assert "".join(pieces) == "abcd" and finish == "stop"
+        ac.generate, ac.cancel = real_generate, real_cancel
+        # through the engine: a stop string that never appears changes nothing
+        r = http.post("/v1/completions", json={"prompt": "stop test prompt", "max_tokens": 12, "temperature": 0.0,
+                                               "stop": "\x00never\x00"}).json()
+        assert r["choices"][0]["finish_reason"] == "length" and r["usage"]["completion_tokens"] == 12
+        rr = http.post("/v1/rerank", json={"query": "q", "documents": ["a", "ccc", "bb"], "top_n": 2}).json()
+        assert [x["index"] for x in rr["results"]] == [1, 2] and rr["model"] == "aux"
+        cl = http.post("/v1/classify", json={"input": ["ab", "abc"]}).json()
+        assert [x["label"] for x in cl["data"]] == [0, 1] and abs(sum(cl["data"][0]["probs"]) - 1) < 1e-6
+        assert http.post("/v1/rerank", json={"query": "q"}).status_code == 400
+        assert http.get("/health").json()["running"] == 0
