@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .engine.batch import GenerateRequest, GenerateResult
-from .generation import (GenerationBuilder, GenerationHook, GenerationResponse, GenerationStream, HookDecision,
+from .generation import (GenerationBuilder, GenerationHook, GenerationResponse, GenerationStream, HookDecision, StopStringHook,
                          split_thinking_content)
 from .models.registry import ModelKind
 
@@ -429,11 +429,13 @@ class Client:
         eos = st.tokenizer.eos_ids(st.model.cfg.eos_token_ids) + list(b._stop)
         if b._images or b._audio:
             return self._execute_multimodal(b, ids, eos)
+        stop_hook = StopStringHook(st.tokenizer.decode, b._stop_strings) if b._stop_strings else None
+        hooks = list(b._hooks) + ([stop_hook] if stop_hook else [])
         with self._lock:
             try:
                 rid = st.engine.add_request(ids, max_tokens=b._max_tokens, temperature=b._temperature, top_k=b._top_k,
                                             top_p=b._top_p, eos_ids=eos, session_id=b._session_id,
-                                            hook=self._hook_fn(b._hooks), stream=stream_cb)
+                                            hook=self._hook_fn(hooks), stream=stream_cb)
             except ValueError as e:
                 raise RuntimeGllmError(str(e)) from e
             keep_cb = st.engine.cfg.callbacks
@@ -449,8 +451,11 @@ class Client:
             toks = toks[:-1]
         text = st.tokenizer.decode(toks)
         thinking, answer = split_thinking_content(text) if b._reasoning else ("", text)
+        reason = res.finish_reason
+        if stop_hook is not None and stop_hook.hit:
+            answer, reason = stop_hook.cut(answer), "stop"
         t = res.telemetry
-        return GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
+        return GenerationResponse(text=answer, token_ids=toks, finish_reason=reason, thinking=thinking,
                                   prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
                                   ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms)
 
@@ -762,8 +767,10 @@ class AsyncClient:
                 if text and not text.endswith("\ufffd"):
                     stream._push(text[len(emitted[0]):])
                     emitted[0] = text
+        stop_hook = StopStringHook(st.tokenizer.decode, b._stop_strings) if b._stop_strings else None
+        hooks = list(b._hooks) + ([stop_hook] if stop_hook else [])
         inner = self._loop.submit(ids, max_tokens=b._max_tokens, temperature=b._temperature, top_k=b._top_k, top_p=b._top_p,
-                                  eos_ids=eos, session_id=b._session_id, hook=c._hook_fn(b._hooks), stream=on_token)
+                                  eos_ids=eos, session_id=b._session_id, hook=c._hook_fn(hooks), stream=on_token)
         outer: "cf.Future" = cf.Future()
         outer.stream = stream
 
@@ -780,8 +787,10 @@ class AsyncClient:
                 toks = toks[:-1]
             text = st.tokenizer.decode(toks)
             thinking, answer = split_thinking_content(text) if b._reasoning else ("", text)
-            t = res.telemetry
-            resp = GenerationResponse(text=answer, token_ids=toks, finish_reason=res.finish_reason, thinking=thinking,
+            t, reason = res.telemetry, res.finish_reason
+            if stop_hook is not None and stop_hook.hit:
+                answer, reason = stop_hook.cut(answer), "stop"
+            resp = GenerationResponse(text=answer, token_ids=toks, finish_reason=reason, thinking=thinking,
                                       prompt_tokens=t.prompt_tokens, cached_prefix_tokens=t.cached_prefix_tokens,
                                       ttft_ms=t.ttft_ms, tpot_ms=t.tpot_ms)
             if stream is not None:

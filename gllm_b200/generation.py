@@ -28,6 +28,30 @@ class GenerationHook:
         return HookDecision.CONTINUE
 
 
+class StopStringHook(GenerationHook):
+    """Ends a request once its decoded text contains one of ``strings`` (``GenerationBuilder.stop``): the token that
+    completed the stop string is kept by the engine, the response text is cut before the string with ``cut``."""
+
+    def __init__(self, decode: Callable[[List[int]], str], strings):
+        self.decode, self.strings = decode, [s for s in strings if s]
+        self.tokens: List[int] = []
+        self.hit = False
+
+    def _first(self, text: str) -> int:
+        return min((i for i in (text.find(s) for s in self.strings) if i >= 0), default=-1)
+
+    def post_step(self, token_id: int, n_generated: int) -> HookDecision:
+        self.tokens.append(int(token_id))
+        if self._first(self.decode(self.tokens)) >= 0:
+            self.hit = True
+            return HookDecision.TERMINATE
+        return HookDecision.CONTINUE
+
+    def cut(self, text: str) -> str:
+        at = self._first(text)
+        return text if at < 0 else text[:at]
+
+
 @dataclass
 class GenerationResponse:
     text: str
@@ -91,6 +115,7 @@ class GenerationBuilder:
         self._images: list = []
         self._audio: list = []
         self._stop: List[int] = []
+        self._stop_strings: List[str] = []
         self._callbacks = None
 
     def callbacks(self, chain):
@@ -145,6 +170,12 @@ class GenerationBuilder:
 
     def stop_token_ids(self, ids):
         self._stop = [int(i) for i in ids]
+        return self
+
+    def stop(self, strings):
+        """Stop strings: generation ends when the text contains one; the response holds the text before it
+        (``finish_reason = "stop"``)."""
+        self._stop_strings = [strings] if isinstance(strings, str) else [str(s) for s in strings]
         return self
 
     # ------------------------------------------------------------------------------------------

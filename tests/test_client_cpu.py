@@ -223,3 +223,26 @@ def test_async_client_batches_concurrent_callers_through_the_serving_loop():
         raised = True
     assert raised and ac.generate(prompts[1], max_tokens=3, temperature=0.0).result(timeout=60).token_ids == want[1][:3]
     ac.shutdown()
+
+
+def test_stop_strings_cut_the_text_and_end_the_request_early():
+    from gllm_b200.client import AsyncClient
+    from gllm_b200.generation import HookDecision, StopStringHook
+    h = StopStringHook(lambda ids: "".join(chr(97 + i) for i in ids), ["de", "zz"])
+    assert [h.post_step(t, i + 1) for i, t in enumerate([0, 1, 2, 3])] == [HookDecision.CONTINUE] * 4 and not h.hit
+    assert h.post_step(4, 5) == HookDecision.TERMINATE and h.hit and h.cut("abcde") == "abc"
+    c = _chat()
+    c._st().tokenizer.decode = lambda ids: "".join(chr(97 + (int(i) % 26)) for i in ids)     # one letter per token
+    full = c.generate("hello there").max_tokens(10).temperature(0.0).generate()
+    assert len(full.text) == len(full.token_ids) == 10 and full.finish_reason == "length"
+    stop = full.text[4:6]
+    at = full.text.find(stop)
+    r = c.generate("hello there").max_tokens(10).temperature(0.0).stop(stop).generate()
+    assert r.text == full.text[:at] and r.finish_reason == "stop" and len(r.token_ids) == at + 2
+    assert c.generate("hello there").max_tokens(10).temperature(0.0).stop(["#"]).generate().text == full.text
+    ac = AsyncClient(c, continuous=True)
+    try:
+        r2 = ac.generate("hello there", max_tokens=10, temperature=0.0, stop=[stop]).result(timeout=120)
+        assert r2.text == r.text and r2.finish_reason == "stop"
+    finally:
+        ac.shutdown()
